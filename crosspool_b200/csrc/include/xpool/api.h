@@ -1,0 +1,84 @@
+/* C ABI of libxpool_kernels.so. Every struct here is mirrored field-for-field by
+ * a ctypes.Structure in crosspool_b200/native/__init__.py; bump XP_ABI_VERSION
+ * when a layout changes (the Python side checks it at import, like the
+ * reference checks its native ABI number, src/xpool/cext.py:1-30). */
+#ifndef XPOOL_API_H_
+#define XPOOL_API_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#define XP_ABI_VERSION 7
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct XpGemmArgs {
+  const void* w;       /* [w_rows_total, k] bf16 weights (nn.Linear layout) */
+  const void* x;       /* [rows, k] bf16 activations */
+  void* out;           /* [rows, ld_out] */
+  const void* resid;   /* optional [rows, ld_resid] bf16 */
+  const float* bias;   /* optional fp32 per weight row */
+  float* ws;           /* split-K workspace (optional) */
+  uint32_t* counters;  /* split-K tile counters, zeroed once by the caller */
+  uint32_t* status;    /* optional device word; first non-zero error code wins */
+  void* stream;        /* cudaStream_t */
+  size_t ws_bytes;
+  size_t counter_bytes;
+  int w_rows_total;    /* 0: derived from n_out / up_offset */
+  int n_out;           /* features produced, multiple of 128 */
+  int k;               /* multiple of 64 */
+  int rows;
+  int ldw, ldx, ld_out, ld_resid; /* element strides; 0 = dense */
+  int epilogue;        /* 0 store bf16, 1 swiglu (dual), 2 residual add, 3 store fp32 */
+  int dual;
+  int up_offset;       /* first weight row of the up projection */
+  int splits;          /* 0 = choose */
+  int bn;              /* 0 = choose */
+  int num_sms;         /* 0 = all */
+  int w_evict_first;
+  float gate_limit, up_add, act_alpha;
+} XpGemmArgs;
+
+typedef struct XpGemmPlan {
+  size_t ws_bytes;
+  size_t counter_bytes;
+  int bn, nacc, splits, tiles, grid, smem_bytes, smem_budget, stages;
+} XpGemmPlan;
+
+
+/* Fused [wait partials] -> ordered sum -> (+residual) -> RMSNorm -> local store / peer push ->
+ * release flags. One CTA per row. */
+typedef struct XpNormArgs {
+  const void* parts[8];        /* bf16 [rows, ld_parts] inputs summed in index order */
+  const uint32_t* wait_flags[8]; /* optional, one per part: wait until >= wait_seq */
+  void* out_peers[8];          /* bf16 [rows, ld_out] destinations (peer or local memory) */
+  uint32_t* peer_flags[8];     /* sequence word released after all rows are stored */
+  uint32_t* peer_meta[8];      /* optional 4-word invocation record written before the flag */
+  void* resid;                 /* optional bf16 [rows, hidden], updated in place */
+  const void* weight;          /* bf16 [hidden]; null = residual add only */
+  void* out_local;             /* optional bf16 [rows, ld_out] */
+  uint32_t* done_counter;      /* zeroed word used to find the last CTA */
+  uint32_t* status;            /* optional error word */
+  const uint32_t* cancel;      /* optional: non-zero aborts waits */
+  uint64_t wait_ns;            /* wait limit */
+  int rows, hidden, ld_parts, ld_out, nparts, npeers;
+  uint32_t wait_seq, publish_seq, meta_layer, meta_mode, meta_deadline_us;
+  float eps;
+} XpNormArgs;
+
+int xp_norm_publish(const XpNormArgs* a, void* stream);
+int xp_swiglu(const void* gate_up, void* out, int rows, int inter, float limit, float up_add,
+              float alpha, void* stream);
+
+int xp_abi_version(void);
+int xp_gemm_plan(const XpGemmArgs* a, XpGemmPlan* plan);
+int xp_gemm(const XpGemmArgs* a);
+int xp_encode_tmap_2d(void* out128, const void* base, uint64_t rows, uint64_t cols,
+                      uint64_t pitch_bytes, uint32_t box_rows, uint32_t elem_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XPOOL_API_H_ */

@@ -1,0 +1,408 @@
+// Weight-stationary tcgen05 GEMM tile engine for sm_100a.
+//
+// Computes Y[r, f] = sum_k X[r, k] * W[f, k]  (torch.nn.Linear layout) with the
+// WEIGHT rows on the tensor core's M axis (always a full 128-row tile) and the
+// activation rows on its N axis (16..256, chosen per call). Decode batches of a
+// few rows and prefill chunks of thousands of rows go through the same code;
+// the epilogue thread that owns TMEM lane `f` writes consecutive features, so
+// global stores are coalesced without a shared-memory transpose.
+//
+// Roles inside one 192-thread CTA:
+//   warp 0      TMA producer (one elected thread), non-multicast 2-D tile loads
+//   warp 1      TMEM allocation + tcgen05.mma issue (one elected thread)
+//   warps 2..5  epilogue: tcgen05.ld -> registers -> fused epilogue -> global
+// Accumulators are double-buffered in TMEM when they fit, so the epilogue of one
+// tile overlaps the main loop of the next (the CTA loops over tiles).
+//
+// The "dual" form multiplies one activation tile with a gate tile and an up
+// tile of the same weight tensor and applies SwiGLU in the epilogue; this
+// replaces the reference's matmul + activation kernels
+// (src/xpool/runtime/ffnagent/operators/{linear,activation,dense}.py).
+#pragma once
+
+#include "xpool/sm100.cuh"
+
+namespace xpool {
+namespace gemm {
+
+constexpr int kTileM = 128;    // weight rows per tile (UMMA M)
+constexpr int kTileK = 64;     // bf16 elements per K block = one 128-byte swizzle row
+constexpr int kUmmaK = 16;     // K per tcgen05.mma for 16-bit inputs
+constexpr int kMaxStages = 8;
+constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
+
+enum Epilogue : int {
+  kEpiStore = 0,     // out = acc (+ bias)
+  kEpiSwiglu = 1,    // dual: out = silu(round(g)) * round(u)
+  kEpiResidual = 2,  // out = round(acc) + resid
+  kEpiStoreF32 = 3,  // fp32 out = acc (+ bias)
+};
+
+enum Status : uint32_t {
+  kOk = 0,
+  kTimeoutProducer = 1,
+  kTimeoutMma = 2,
+  kTimeoutEpilogue = 3,
+  kTimeoutFlag = 4,
+  kBadArgument = 5,
+};
+
+// One GEMM problem. All pointers are device pointers valid on the executing GPU
+// (out / resid may be peer memory; they are only touched with plain stores and
+// loads, never by TMA).
+struct Problem {
+  const CUtensorMap* tmap_w;  // [n_rows_total, k], box {64, 128}
+  const CUtensorMap* tmap_x;  // [rows, k], box {64, bn}
+  void* out;                  // [rows, ld_out]
+  const void* resid;          // [rows, ld_resid] bf16 or null
+  const float* bias;          // [n_out] or null
+  float* ws;                  // split-K workspace or null
+  uint32_t* counters;         // one per (m, n) tile, zero between calls
+  int n_out;                  // features produced (multiple of 128)
+  int k;                      // multiple of 64
+  int rows;                   // live activation rows
+  int ld_out;
+  int ld_resid;
+  int bn;                     // activation rows per tile: 16, 32, 64, 128 or 256
+  int splits;                 // split-K factor (>= 1)
+  int epilogue;               // Epilogue
+  int dual;                   // 1: gate rows [0, n_out), up rows [up_offset, up_offset + n_out)
+  int up_offset;
+  int w_evict_first;          // stream weights through L2
+  float gate_limit;           // > 0: clamp gate from above and up to [-limit, limit]
+  float up_add;               // added to up before the product (0 for plain SwiGLU)
+  float act_alpha;            // 0: silu(g); else g * sigmoid(alpha * g)
+};
+
+struct SmemLayout {
+  int stages;
+  int a_bytes;      // per stage, all A tiles
+  int b_bytes;      // per stage
+  int stage_bytes;
+  int total_bytes;  // including barriers and alignment slack
+};
+
+__host__ __device__ inline SmemLayout smem_layout(int bn, int dual, int budget_bytes) {
+  SmemLayout s;
+  s.a_bytes = kTileM * kTileK * 2 * (dual ? 2 : 1);
+  s.b_bytes = bn * kTileK * 2;
+  // B tiles start on 1024-byte boundaries (128-byte swizzle atoms).
+  int b_pad = (s.b_bytes + 1023) / 1024 * 1024;
+  s.stage_bytes = s.a_bytes + b_pad;
+  int st = (budget_bytes - 2048) / s.stage_bytes;
+  if (st > kMaxStages) st = kMaxStages;
+  if (st < 2) st = 2;
+  s.stages = st;
+  s.total_bytes = st * s.stage_bytes + 1024 /*align slack*/ + 512 /*barriers*/;
+  return s;
+}
+
+struct Barriers {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  uint32_t bcast;
+  uint32_t pad;
+};
+
+__device__ __forceinline__ void record_status(uint32_t* status, uint32_t code) {
+  if (status != nullptr) atomicCAS(status, 0u, code);
+}
+
+__device__ __forceinline__ float silu_like(float g, float alpha) {
+  float a = alpha == 0.f ? 1.f : alpha;
+  return g / (1.f + __expf(-a * g));
+}
+
+__device__ __forceinline__ float round_bf16(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// Pipeline position carried across tiles by each role.
+struct PipeState {
+  uint32_t stage = 0;
+  uint32_t phase = 0;
+  uint32_t acc = 0;
+  uint32_t acc_phase = 0;
+  __device__ __forceinline__ void advance(uint32_t stages) {
+    if (++stage == stages) {
+      stage = 0;
+      phase ^= 1;
+    }
+  }
+  __device__ __forceinline__ void advance_acc(uint32_t nacc) {
+    if (++acc == nacc) {
+      acc = 0;
+      acc_phase ^= 1;
+    }
+  }
+};
+
+struct TileCoord {
+  int m0;     // first weight row / feature
+  int n0;     // first activation row
+  int split;  // split-K index
+  int mn;     // linear (m, n) tile index
+  int kb0;    // first K block
+  int kbn;    // number of K blocks
+};
+
+__device__ __forceinline__ int tiles_m(const Problem& p) { return p.n_out / kTileM; }
+__device__ __forceinline__ int tiles_n(const Problem& p) { return (p.rows + p.bn - 1) / p.bn; }
+__device__ __forceinline__ int tile_count(const Problem& p) {
+  return tiles_m(p) * tiles_n(p) * p.splits;
+}
+
+__device__ __forceinline__ TileCoord tile_coord(const Problem& p, int t) {
+  TileCoord c;
+  int tm = tiles_m(p);
+  c.split = t % p.splits;
+  int mn = t / p.splits;
+  c.mn = mn;
+  c.m0 = (mn % tm) * kTileM;
+  c.n0 = (mn / tm) * p.bn;
+  int kb_total = p.k / kTileK;
+  int per = (kb_total + p.splits - 1) / p.splits;
+  c.kb0 = c.split * per;
+  int end = c.kb0 + per;
+  if (end > kb_total) end = kb_total;
+  c.kbn = end > c.kb0 ? end - c.kb0 : 0;
+  return c;
+}
+
+// ---------------------------------------------------------------- producer
+
+__device__ __forceinline__ bool produce_tile(const Problem& p, const TileCoord& c,
+                                             const SmemLayout& L, uint8_t* tiles, Barriers* bar,
+                                             PipeState& st, uint64_t deadline) {
+  uint64_t pol = 0;
+  if (p.w_evict_first) pol = sm100::l2_policy_evict_first();
+  const uint32_t tx = static_cast<uint32_t>(L.a_bytes + L.b_bytes);
+  for (int kb = c.kb0; kb < c.kb0 + c.kbn; ++kb) {
+    if (!sm100::mbar_wait(&bar->empty[st.stage], st.phase ^ 1, deadline)) return false;
+    uint8_t* a = tiles + static_cast<size_t>(st.stage) * L.stage_bytes;
+    uint8_t* b = a + L.a_bytes;
+    sm100::mbar_arrive_expect_tx(&bar->full[st.stage], tx);
+    if (p.w_evict_first) {
+      sm100::tma_load_2d_hint(a, p.tmap_w, &bar->full[st.stage], kb * kTileK, c.m0, pol);
+      if (p.dual)
+        sm100::tma_load_2d_hint(a + kTileM * kTileK * 2, p.tmap_w, &bar->full[st.stage],
+                                kb * kTileK, p.up_offset + c.m0, pol);
+    } else {
+      sm100::tma_load_2d(a, p.tmap_w, &bar->full[st.stage], kb * kTileK, c.m0);
+      if (p.dual)
+        sm100::tma_load_2d(a + kTileM * kTileK * 2, p.tmap_w, &bar->full[st.stage], kb * kTileK,
+                           p.up_offset + c.m0);
+    }
+    sm100::tma_load_2d(b, p.tmap_x, &bar->full[st.stage], kb * kTileK, c.n0);
+    st.advance(L.stages);
+  }
+  return true;
+}
+
+// After a failed wait: give loads still in flight a bounded time to land so that
+// nothing writes this CTA's shared memory after it has exited.
+__device__ __forceinline__ void producer_drain(const SmemLayout& L, Barriers* bar,
+                                               const PipeState& st) {
+  uint64_t deadline = sm100::global_timer_ns() + 2000000ull;  // 2 ms
+  for (uint32_t s = 0; s < static_cast<uint32_t>(L.stages); ++s) {
+    // Stages below the cursor were armed in the current phase, the others in the
+    // previous one (a never-armed barrier passes the previous-phase test at once).
+    const uint32_t parity = s < st.stage ? st.phase : (st.phase ^ 1);
+    if (!sm100::mbar_wait(&bar->full[s], parity, deadline)) break;
+  }
+}
+
+// ---------------------------------------------------------------- MMA issuer
+
+__device__ __forceinline__ bool mma_tile(const Problem& p, const TileCoord& c, const SmemLayout& L,
+                                         uint8_t* tiles, Barriers* bar, PipeState& st, int nacc,
+                                         uint64_t deadline) {
+  const uint32_t acc_cols = static_cast<uint32_t>(p.bn * (p.dual ? 2 : 1));
+  const uint32_t tmem_acc = bar->tmem_base + st.acc * acc_cols;
+  const uint32_t idesc = sm100::umma_idesc_bf16(kTileM, static_cast<uint32_t>(p.bn));
+  if (!sm100::mbar_wait(&bar->acc_empty[st.acc], st.acc_phase ^ 1, deadline)) return false;
+  sm100::tc_fence_after_sync();
+  for (int i = 0; i < c.kbn; ++i) {
+    if (!sm100::mbar_wait(&bar->full[st.stage], st.phase, deadline)) return false;
+    sm100::tc_fence_after_sync();
+    uint8_t* a = tiles + static_cast<size_t>(st.stage) * L.stage_bytes;
+    const uint32_t a_addr = sm100::smem_u32(a);
+    const uint32_t b_addr = a_addr + L.a_bytes;
+    const uint64_t da = sm100::umma_desc_sw128(a_addr);
+    const uint64_t du = sm100::umma_desc_sw128(a_addr + kTileM * kTileK * 2);
+    const uint64_t db = sm100::umma_desc_sw128(b_addr);
+#pragma unroll
+    for (int k = 0; k < kTileK / kUmmaK; ++k) {
+      const uint64_t koff = static_cast<uint64_t>((k * kUmmaK * 2) >> 4);  // 32 bytes per step
+      const uint32_t accum = (i > 0 || k > 0) ? 1u : 0u;
+      sm100::umma_bf16(tmem_acc, da + koff, db + koff, idesc, accum);
+      if (p.dual) sm100::umma_bf16(tmem_acc + p.bn, du + koff, db + koff, idesc, accum);
+    }
+    sm100::umma_commit(&bar->empty[st.stage]);  // frees the stage when these MMAs retire
+    st.advance(L.stages);
+  }
+  sm100::umma_commit(&bar->acc_full[st.acc]);
+  st.advance_acc(nacc);
+  return true;
+}
+
+// ---------------------------------------------------------------- epilogue
+
+__device__ __forceinline__ void epi_bar_sync() {
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+// Applies the fused epilogue to 16 accumulator columns (activation rows
+// n .. n+15) of feature f and stores them.
+__device__ __forceinline__ void epilogue_store16(const Problem& p, int f, int n_first,
+                                                 const float* g, const float* u) {
+  const float bias = p.bias != nullptr ? p.bias[f] : 0.f;
+  const float bias_u = (p.bias != nullptr && p.dual) ? p.bias[p.up_offset + f] : 0.f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const int n = n_first + j;
+    if (n >= p.rows) break;
+    float v = g[j] + bias;
+    const size_t o = static_cast<size_t>(n) * p.ld_out + f;
+    if (p.epilogue == kEpiSwiglu) {
+      float gg = round_bf16(v);
+      float uu = round_bf16(u[j] + bias_u);
+      if (p.gate_limit > 0.f) {
+        gg = fminf(gg, p.gate_limit);
+        uu = fminf(fmaxf(uu, -p.gate_limit), p.gate_limit);
+      }
+      v = silu_like(gg, p.act_alpha) * (uu + p.up_add);
+      reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
+    } else if (p.epilogue == kEpiResidual) {
+      const __nv_bfloat16* r = reinterpret_cast<const __nv_bfloat16*>(p.resid);
+      v = round_bf16(v) + __bfloat162float(r[static_cast<size_t>(n) * p.ld_resid + f]);
+      reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
+    } else if (p.epilogue == kEpiStoreF32) {
+      reinterpret_cast<float*>(p.out)[o] = v;
+    } else {
+      reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
+// Runs on the 128 epilogue threads. `ew` is the warp's TMEM lane quarter.
+__device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord& c, Barriers* bar,
+                                              PipeState& st, int nacc, int ew, int lane,
+                                              uint64_t deadline) {
+  const uint32_t acc_cols = static_cast<uint32_t>(p.bn * (p.dual ? 2 : 1));
+  const uint32_t tmem_acc =
+      bar->tmem_base + st.acc * acc_cols + (static_cast<uint32_t>(ew * 32) << 16);
+  const int lane_in_tile = ew * 32 + lane;
+  const int f = c.m0 + lane_in_tile;
+  if (!sm100::mbar_wait(&bar->acc_full[st.acc], st.acc_phase, deadline)) return false;
+  sm100::tc_fence_after_sync();
+
+  float g[16], u[16];
+  if (p.splits == 1) {
+    for (int col = 0; col < p.bn; col += 16) {
+      if (c.n0 + col >= p.rows) break;
+      sm100::tmem_ld16(tmem_acc + col, g);
+      if (p.dual) sm100::tmem_ld16(tmem_acc + p.bn + col, u);
+      epilogue_store16(p, f, c.n0 + col, g, u);
+    }
+  } else {
+    // Split-K: park raw partial sums, last-arriving CTA folds them in split order.
+    float* ws = p.ws + (static_cast<size_t>(c.mn) * p.splits + c.split) * acc_cols * kTileM;
+    for (uint32_t col = 0; col < acc_cols; col += 16) {
+      sm100::tmem_ld16(tmem_acc + col, g);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) ws[static_cast<size_t>(col + j) * kTileM + lane_in_tile] = g[j];
+    }
+  }
+  // The accumulator buffer is free again once every epilogue warp has read it.
+  sm100::tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) sm100::mbar_arrive(&bar->acc_empty[st.acc]);
+  st.advance_acc(nacc);
+
+  if (p.splits > 1) {
+    __threadfence();
+    epi_bar_sync();
+    if (ew == 0 && lane == 0) bar->bcast = atomicAdd(&p.counters[c.mn], 1u);
+    epi_bar_sync();
+    const bool last = bar->bcast == static_cast<uint32_t>(p.splits - 1);
+    epi_bar_sync();  // everyone has read bcast before a later tile overwrites it
+    if (last) {
+      __threadfence();
+      const float* base = p.ws + static_cast<size_t>(c.mn) * p.splits * acc_cols * kTileM;
+      for (int col = 0; col < p.bn; col += 16) {
+        if (c.n0 + col >= p.rows) break;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float sg = 0.f, su = 0.f;
+          for (int s = 0; s < p.splits; ++s) {
+            const float* w = base + static_cast<size_t>(s) * acc_cols * kTileM;
+            sg += __ldcg(&w[static_cast<size_t>(col + j) * kTileM + lane_in_tile]);
+            if (p.dual) su += __ldcg(&w[static_cast<size_t>(p.bn + col + j) * kTileM + lane_in_tile]);
+          }
+          g[j] = sg;
+          u[j] = su;
+        }
+        epilogue_store16(p, f, c.n0 + col, g, u);
+      }
+      if (ew == 0 && lane == 0) p.counters[c.mn] = 0;  // ready for the next call
+    }
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------- CTA set-up / tear-down
+
+__device__ __forceinline__ uint32_t tmem_columns_needed(int bn, int dual, int nacc) {
+  uint32_t need = static_cast<uint32_t>(bn * (dual ? 2 : 1) * nacc);
+  uint32_t cols = 32;
+  while (cols < need) cols <<= 1;
+  return cols;
+}
+
+// Called by all threads of the CTA once. Returns the aligned tile area.
+__device__ __forceinline__ uint8_t* cta_setup(uint8_t* smem_raw, const SmemLayout& L,
+                                              Barriers** bar_out, uint32_t tmem_cols, int warp,
+                                              int lane) {
+  uint8_t* tiles = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  Barriers* bar = reinterpret_cast<Barriers*>(tiles + static_cast<size_t>(L.stages) * L.stage_bytes);
+  *bar_out = bar;
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < kMaxStages; ++s) {
+      sm100::mbar_init(&bar->full[s], 1);
+      sm100::mbar_init(&bar->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      sm100::mbar_init(&bar->acc_full[a], 1);
+      sm100::mbar_init(&bar->acc_empty[a], 4);
+    }
+    bar->abort_flag = 0;
+    sm100::mbar_fence_init();
+  }
+  if (warp == 1) {
+    sm100::tmem_alloc(&bar->tmem_base, tmem_cols);
+    sm100::tmem_relinquish();
+  }
+  sm100::tc_fence_before_sync();
+  __syncthreads();
+  sm100::tc_fence_after_sync();
+  return tiles;
+}
+
+__device__ __forceinline__ void cta_teardown(Barriers* bar, uint32_t tmem_cols, int warp) {
+  sm100::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    sm100::tc_fence_after_sync();
+    sm100::tmem_dealloc(bar->tmem_base, tmem_cols);
+  }
+}
+
+}  // namespace gemm
+}  // namespace xpool

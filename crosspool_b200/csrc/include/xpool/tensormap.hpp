@@ -1,0 +1,91 @@
+// Host-side helper that encodes 2-D TMA tensor maps without linking libcuda:
+// the driver entry point is looked up through the CUDA runtime.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <tuple>
+#include <map>
+
+namespace xpool {
+namespace tmap {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                              const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeFn encode_fn() {
+  static EncodeFn fn = []() -> EncodeFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// Row-major matrix [rows, cols] of `elem_bytes`-byte elements with a row pitch of
+// `pitch_bytes`; box = {box_cols, box_rows}; 128-byte swizzle (box_cols *
+// elem_bytes must be 128). Out-of-range reads return zero. Returns 0 on success.
+inline int encode_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                     uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
+                     uint32_t elem_bytes) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (pitch_bytes & 15) != 0) return -2;
+  if (box_cols * elem_bytes != 128 || box_rows == 0 || box_rows > 256) return -3;
+  CUtensorMapDataType dt = elem_bytes == 2   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+// Small cache: encoding costs a few microseconds and serving reuses the same
+// (pointer, shape) pairs on every step.
+class Cache {
+ public:
+  using Key = std::tuple<const void*, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t>;
+  int get(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+          uint32_t box_rows, uint32_t elem_bytes) {
+    Key k{base, rows, cols, pitch_bytes, box_rows, elem_bytes};
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = map_.find(k);
+    if (it != map_.end()) {
+      *out = it->second;
+      return 0;
+    }
+    CUtensorMap m;
+    int rc = encode_2d(&m, base, rows, cols, pitch_bytes, box_rows, 128 / elem_bytes, elem_bytes);
+    if (rc != 0) return rc;
+    if (map_.size() > 8192) map_.clear();
+    map_.emplace(k, m);
+    *out = m;
+    return 0;
+  }
+
+ private:
+  std::mutex mu_;
+  std::map<Key, CUtensorMap> map_;
+};
+
+inline Cache& cache() {
+  static Cache c;
+  return c;
+}
+
+}  // namespace tmap
+}  // namespace xpool

@@ -1,0 +1,188 @@
+// Stream-launched entry points of the weight-stationary tcgen05 GEMM
+// (see xpool/gemm_ws.cuh). Exported with C linkage and loaded through ctypes.
+#include <algorithm>
+
+#include "xpool/api.h"
+#include "xpool/gemm_ws.cuh"
+#include "xpool/tensormap.hpp"
+
+namespace xpool {
+namespace gemm {
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_ws_kernel(const __grid_constant__ CUtensorMap tmap_w,
+               const __grid_constant__ CUtensorMap tmap_x, Problem p, int nacc, int smem_budget,
+               uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  p.tmap_w = &tmap_w;
+  p.tmap_x = &tmap_x;
+  const SmemLayout L = smem_layout(p.bn, p.dual, smem_budget);
+  const uint32_t tmem_cols = tmem_columns_needed(p.bn, p.dual, nacc);
+  Barriers* bar;
+  uint8_t* tiles = cta_setup(smem_raw, L, &bar, tmem_cols, warp, lane);
+  const int ntiles = tile_count(p);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      sm100::tma_prefetch_desc(p.tmap_w);
+      sm100::tma_prefetch_desc(p.tmap_x);
+      PipeState st;
+      for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const uint64_t deadline = sm100::global_timer_ns() + sm100::kPipelineWaitNs;
+        if (!produce_tile(p, tile_coord(p, t), L, tiles, bar, st, deadline)) {
+          record_status(status, kTimeoutProducer);
+          producer_drain(L, bar, st);
+          break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      PipeState st;
+      for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const uint64_t deadline = sm100::global_timer_ns() + sm100::kPipelineWaitNs;
+        if (!mma_tile(p, tile_coord(p, t), L, tiles, bar, st, nacc, deadline)) {
+          record_status(status, kTimeoutMma);
+          break;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    PipeState st;
+    const int ew = warp & 3;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+      const uint64_t deadline = sm100::global_timer_ns() + sm100::kPipelineWaitNs;
+      if (!epilogue_tile(p, tile_coord(p, t), bar, st, nacc, ew, lane, deadline)) {
+        record_status(status, kTimeoutEpilogue);
+        break;
+      }
+    }
+  }
+  cta_teardown(bar, tmem_cols, warp);
+}
+
+static int pick_bn(int rows, int dual) {
+  const int cap = dual ? 128 : 256;
+  int bn = 16;
+  while (bn < rows && bn < cap) bn <<= 1;
+  return bn;
+}
+
+}  // namespace gemm
+}  // namespace xpool
+
+using namespace xpool;
+
+extern "C" int xp_gemm_plan(const XpGemmArgs* a, XpGemmPlan* plan) {
+  if (a->n_out <= 0 || a->n_out % gemm::kTileM != 0 || a->k <= 0 || a->k % gemm::kTileK != 0 ||
+      a->rows <= 0)
+    return -10;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static int sm_count_cache[64] = {0};
+  if (dev < 64 && sm_count_cache[dev] == 0)
+    cudaDeviceGetAttribute(&sm_count_cache[dev], cudaDevAttrMultiProcessorCount, dev);
+  int sms = a->num_sms > 0 ? a->num_sms : (dev < 64 ? sm_count_cache[dev] : 148);
+  if (sms <= 0) sms = 148;
+  int bn = a->bn > 0 ? a->bn : gemm::pick_bn(a->rows, a->dual);
+  if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return -11;
+  if (a->dual && bn > 256) return -11;
+  const int acc_cols = bn * (a->dual ? 2 : 1);
+  const int nacc = acc_cols * 2 <= 512 ? 2 : 1;
+  const int tm = a->n_out / gemm::kTileM;
+  const int tn = (a->rows + bn - 1) / bn;
+  const int kb = a->k / gemm::kTileK;
+  int splits = a->splits;
+  if (splits <= 0) {
+    splits = 1;
+    const int tiles = tm * tn;
+    if (tiles * 2 <= sms) {
+      splits = std::min(sms / tiles, std::max(1, kb / 4));
+      splits = std::min(splits, 16);
+    }
+  }
+  if (splits > kb) splits = kb;
+  // every split must own at least one K block
+  while (splits > 1 && (splits - 1) * ((kb + splits - 1) / splits) >= kb) --splits;
+  plan->bn = bn;
+  plan->nacc = nacc;
+  plan->splits = splits;
+  plan->tiles = tm * tn * splits;
+  plan->grid = std::min(plan->tiles, sms);
+  plan->ws_bytes = splits > 1 ? static_cast<size_t>(tm) * tn * splits * acc_cols * gemm::kTileM * 4 : 0;
+  plan->counter_bytes = splits > 1 ? static_cast<size_t>(tm) * tn * 4 : 0;
+  plan->smem_budget = 200 * 1024;
+  gemm::SmemLayout L = gemm::smem_layout(bn, a->dual, plan->smem_budget);
+  plan->smem_bytes = L.total_bytes;
+  plan->stages = L.stages;
+  return 0;
+}
+
+extern "C" int xp_gemm(const XpGemmArgs* a) {
+  XpGemmPlan plan;
+  int rc = xp_gemm_plan(a, &plan);
+  if (rc != 0) return rc;
+  if (plan.splits > 1) {
+    if (a->ws == nullptr || a->counters == nullptr || a->ws_bytes < plan.ws_bytes ||
+        a->counter_bytes < plan.counter_bytes) {
+      // fall back to no split-K rather than touching memory we do not own
+      XpGemmArgs b = *a;
+      b.splits = 1;
+      b.bn = plan.bn;
+      return xp_gemm(&b);
+    }
+  }
+  CUtensorMap tw, tx;
+  const int w_rows = a->w_rows_total > 0 ? a->w_rows_total : (a->dual ? a->up_offset + a->n_out : a->n_out);
+  rc = tmap::cache().get(&tw, a->w, w_rows, a->k, static_cast<uint64_t>(a->ldw > 0 ? a->ldw : a->k) * 2,
+                         gemm::kTileM, 2);
+  if (rc != 0) return -20 + 0 * rc;
+  rc = tmap::cache().get(&tx, a->x, a->rows, a->k, static_cast<uint64_t>(a->ldx > 0 ? a->ldx : a->k) * 2,
+                         plan.bn, 2);
+  if (rc != 0) return -21;
+
+  gemm::Problem p{};
+  p.out = a->out;
+  p.resid = a->resid;
+  p.bias = a->bias;
+  p.ws = a->ws;
+  p.counters = a->counters;
+  p.n_out = a->n_out;
+  p.k = a->k;
+  p.rows = a->rows;
+  p.ld_out = a->ld_out > 0 ? a->ld_out : a->n_out;
+  p.ld_resid = a->ld_resid > 0 ? a->ld_resid : p.ld_out;
+  p.bn = plan.bn;
+  p.splits = plan.splits;
+  p.epilogue = a->epilogue;
+  p.dual = a->dual;
+  p.up_offset = a->up_offset;
+  p.w_evict_first = a->w_evict_first;
+  p.gate_limit = a->gate_limit;
+  p.up_add = a->up_add;
+  p.act_alpha = a->act_alpha;
+
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm::gemm_ws_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return -30;
+    attr_set[dev] = true;
+  }
+  gemm::gemm_ws_kernel<<<plan.grid, gemm::kThreads, plan.smem_bytes,
+                         reinterpret_cast<cudaStream_t>(a->stream)>>>(
+      tw, tx, p, plan.nacc, plan.smem_budget, a->status);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);
+}
+
+extern "C" int xp_encode_tmap_2d(void* out128, const void* base, uint64_t rows, uint64_t cols,
+                                 uint64_t pitch_bytes, uint32_t box_rows, uint32_t elem_bytes) {
+  return tmap::encode_2d(reinterpret_cast<CUtensorMap*>(out128), base, rows, cols, pitch_bytes,
+                         box_rows, 128 / elem_bytes, elem_bytes);
+}

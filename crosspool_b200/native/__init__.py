@@ -1,0 +1,141 @@
+"""ctypes bindings of the in-tree native libraries.
+
+``kernels()`` loads ``libxpool_kernels.so`` (CUDA, sm_100a) and ``runtime()`` loads
+``libxpool_runtime.so`` (host-only C++). Both check the ABI number baked into the library against
+``EXPECTED_ABI`` — the same contract as the reference's ``EXPECTED_NATIVE_ABI_VERSION``
+(src/xpool/cext.py:1-30).
+
+On a machine with a GPU a missing kernel library is an error, never a silent fallback: the Python
+operators in :mod:`crosspool_b200.ops` have no eager substitute on the hot path.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import functools
+from pathlib import Path
+
+EXPECTED_ABI = 7
+HERE = Path(__file__).resolve().parent
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("w", C.c_void_p),
+        ("x", C.c_void_p),
+        ("out", C.c_void_p),
+        ("resid", C.c_void_p),
+        ("bias", C.c_void_p),
+        ("ws", C.c_void_p),
+        ("counters", C.c_void_p),
+        ("status", C.c_void_p),
+        ("stream", C.c_void_p),
+        ("ws_bytes", C.c_size_t),
+        ("counter_bytes", C.c_size_t),
+        ("w_rows_total", C.c_int),
+        ("n_out", C.c_int),
+        ("k", C.c_int),
+        ("rows", C.c_int),
+        ("ldw", C.c_int),
+        ("ldx", C.c_int),
+        ("ld_out", C.c_int),
+        ("ld_resid", C.c_int),
+        ("epilogue", C.c_int),
+        ("dual", C.c_int),
+        ("up_offset", C.c_int),
+        ("splits", C.c_int),
+        ("bn", C.c_int),
+        ("num_sms", C.c_int),
+        ("w_evict_first", C.c_int),
+        ("gate_limit", C.c_float),
+        ("up_add", C.c_float),
+        ("act_alpha", C.c_float),
+    ]
+
+
+class GemmPlan(C.Structure):
+    _fields_ = [
+        ("ws_bytes", C.c_size_t),
+        ("counter_bytes", C.c_size_t),
+        ("bn", C.c_int),
+        ("nacc", C.c_int),
+        ("splits", C.c_int),
+        ("tiles", C.c_int),
+        ("grid", C.c_int),
+        ("smem_bytes", C.c_int),
+        ("smem_budget", C.c_int),
+        ("stages", C.c_int),
+    ]
+
+
+class NormArgs(C.Structure):
+    _fields_ = [
+        ("parts", C.c_void_p * 8),
+        ("wait_flags", C.c_void_p * 8),
+        ("out_peers", C.c_void_p * 8),
+        ("peer_flags", C.c_void_p * 8),
+        ("peer_meta", C.c_void_p * 8),
+        ("resid", C.c_void_p),
+        ("weight", C.c_void_p),
+        ("out_local", C.c_void_p),
+        ("done_counter", C.c_void_p),
+        ("status", C.c_void_p),
+        ("cancel", C.c_void_p),
+        ("wait_ns", C.c_uint64),
+        ("rows", C.c_int),
+        ("hidden", C.c_int),
+        ("ld_parts", C.c_int),
+        ("ld_out", C.c_int),
+        ("nparts", C.c_int),
+        ("npeers", C.c_int),
+        ("wait_seq", C.c_uint32),
+        ("publish_seq", C.c_uint32),
+        ("meta_layer", C.c_uint32),
+        ("meta_mode", C.c_uint32),
+        ("meta_deadline_us", C.c_uint32),
+        ("eps", C.c_float),
+    ]
+
+
+def _load(name: str) -> C.CDLL:
+    path = HERE / name
+    if not path.exists():
+        raise NativeLibraryError(
+            f"{path} is missing; build it with `python -m crosspool_b200.native.build`"
+        )
+    return C.CDLL(str(path))
+
+
+@functools.lru_cache(maxsize=None)
+def kernels() -> C.CDLL:
+    lib = _load("libxpool_kernels.so")
+    lib.xp_abi_version.restype = C.c_int
+    got = lib.xp_abi_version()
+    if got != EXPECTED_ABI:
+        raise NativeLibraryError(f"libxpool_kernels.so has ABI {got}, expected {EXPECTED_ABI}; rebuild")
+    for fn in ("xp_gemm", "xp_gemm_plan", "xp_norm_publish", "xp_swiglu", "xp_fill_u32", "xp_l2_flush",
+               "xp_encode_tmap_2d"):
+        getattr(lib, fn).restype = C.c_int
+    lib.xp_gemm.argtypes = [C.POINTER(GemmArgs)]
+    lib.xp_gemm_plan.argtypes = [C.POINTER(GemmArgs), C.POINTER(GemmPlan)]
+    lib.xp_norm_publish.argtypes = [C.POINTER(NormArgs), C.c_void_p]
+    lib.xp_swiglu.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_float, C.c_float,
+                              C.c_void_p]
+    lib.xp_fill_u32.argtypes = [C.c_void_p, C.c_uint32, C.c_size_t, C.c_void_p]
+    lib.xp_l2_flush.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.xp_encode_tmap_2d.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32,
+                                      C.c_uint32]
+    return lib
+
+
+def kernels_available() -> bool:
+    return (HERE / "libxpool_kernels.so").exists()
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise NativeLibraryError(f"{what} failed with code {rc}")

@@ -1,0 +1,136 @@
+"""Python face of the weight-stationary tcgen05 GEMM (``csrc/kernels/gemm.cu``).
+
+``linear(x, w)`` computes ``x @ w.T`` for an ``nn.Linear``-layout weight; ``gateup_swiglu`` fuses the
+gate and up projections with the SwiGLU epilogue (the reference's ``i_proj`` + activation,
+src/xpool/runtime/ffnagent/operators/dense.py); ``linear(..., resid=r)`` fuses the residual add
+(``o_proj``/down-projection followed by the add).
+
+There is no eager fallback here: on CUDA tensors the native kernel runs or an error is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from .. import native
+
+EPI_STORE = 0
+EPI_SWIGLU = 1
+EPI_RESIDUAL = 2
+EPI_STORE_F32 = 3
+
+_WS_BYTES = 96 << 20
+_COUNTER_WORDS = 1 << 16
+
+
+@dataclass
+class _Scratch:
+    ws: torch.Tensor
+    counters: torch.Tensor
+    status: torch.Tensor
+
+
+_scratch: dict[int, _Scratch] = {}
+
+
+def scratch(device: torch.device) -> _Scratch:
+    """Per-device split-K workspace, tile counters and the error word of the GEMM kernels."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    s = _scratch.get(idx)
+    if s is None:
+        s = _Scratch(
+            ws=torch.empty(_WS_BYTES // 4, dtype=torch.float32, device=device),
+            counters=torch.zeros(_COUNTER_WORDS, dtype=torch.int32, device=device),
+            status=torch.zeros(4, dtype=torch.int32, device=device),
+        )
+        _scratch[idx] = s
+    return s
+
+
+def check_status(device: torch.device) -> None:
+    """Raises if a kernel recorded a bounded-wait timeout since the last check (synchronises)."""
+    s = scratch(device)
+    code = int(s.status[0].item())
+    if code != 0:
+        s.status.zero_()
+        raise RuntimeError(f"xpool kernel reported device status {code}")
+
+
+def _args(x, w, out, *, n_out, rows, epilogue, dual=0, up_offset=0, bias=None, resid=None, splits=0, bn=0,
+          num_sms=0, evict_first=None, gate_limit=0.0, up_add=0.0, act_alpha=0.0) -> native.GemmArgs:
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1
+    k = x.shape[-1]
+    assert w.shape[-1] == k, (w.shape, x.shape)
+    s = scratch(x.device)
+    a = native.GemmArgs()
+    a.w = w.data_ptr()
+    a.x = x.data_ptr()
+    a.out = out.data_ptr()
+    a.resid = resid.data_ptr() if resid is not None else None
+    a.bias = bias.data_ptr() if bias is not None else None
+    a.ws = s.ws.data_ptr()
+    a.counters = s.counters.data_ptr()
+    a.status = s.status.data_ptr()
+    a.stream = torch.cuda.current_stream(x.device).cuda_stream
+    a.ws_bytes = s.ws.numel() * 4
+    a.counter_bytes = s.counters.numel() * 4
+    a.w_rows_total = w.shape[0]
+    a.n_out = n_out
+    a.k = k
+    a.rows = rows
+    a.ldw = w.stride(0)
+    a.ldx = x.stride(0)
+    a.ld_out = out.stride(0)
+    a.ld_resid = resid.stride(0) if resid is not None else 0
+    a.epilogue = epilogue
+    a.dual = dual
+    a.up_offset = up_offset
+    a.splits = splits
+    a.bn = bn
+    a.num_sms = num_sms
+    # decode-sized calls stream the weights once: keep them from evicting activations in L2
+    a.w_evict_first = int(rows <= 64) if evict_first is None else int(evict_first)
+    a.gate_limit = gate_limit
+    a.up_add = up_add
+    a.act_alpha = act_alpha
+    return a
+
+
+def plan(a: native.GemmArgs) -> native.GemmPlan:
+    p = native.GemmPlan()
+    native.check(native.kernels().xp_gemm_plan(C.byref(a), C.byref(p)), "xp_gemm_plan")
+    return p
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, *, out: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+           resid: torch.Tensor | None = None, out_fp32: bool = False, splits: int = 0, bn: int = 0,
+           num_sms: int = 0) -> torch.Tensor:
+    """``x[rows, k] @ w[n, k].T`` (+ fp32 ``bias``) (+ ``resid``) on the tcgen05 kernel."""
+    x2 = x.reshape(-1, x.shape[-1])
+    rows, n = x2.shape[0], w.shape[0]
+    if out is None:
+        out = torch.empty(rows, n, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
+    epi = EPI_STORE_F32 if out.dtype == torch.float32 else (EPI_RESIDUAL if resid is not None else EPI_STORE)
+    a = _args(x2, w, out, n_out=n, rows=rows, epilogue=epi, bias=bias, resid=resid, splits=splits, bn=bn,
+              num_sms=num_sms)
+    native.check(native.kernels().xp_gemm(C.byref(a)), "xp_gemm")
+    return out.reshape(*x.shape[:-1], n) if x.dim() != 2 else out
+
+
+def gateup_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, *, out: torch.Tensor | None = None,
+                  bias: torch.Tensor | None = None, gate_limit: float = 0.0, up_add: float = 0.0,
+                  act_alpha: float = 0.0, splits: int = 0, bn: int = 0, num_sms: int = 0) -> torch.Tensor:
+    """``silu(x @ Wg.T) * (x @ Wu.T)`` with ``w_gate_up = cat([Wg, Wu])`` of shape ``[2*I, k]``."""
+    x2 = x.reshape(-1, x.shape[-1])
+    rows = x2.shape[0]
+    inter = w_gate_up.shape[0] // 2
+    if out is None:
+        out = torch.empty(rows, inter, dtype=torch.bfloat16, device=x.device)
+    a = _args(x2, w_gate_up, out, n_out=inter, rows=rows, epilogue=EPI_SWIGLU, dual=1, up_offset=inter, bias=bias,
+              splits=splits, bn=bn, num_sms=num_sms, gate_limit=gate_limit, up_add=up_add, act_alpha=act_alpha)
+    native.check(native.kernels().xp_gemm(C.byref(a)), "xp_gemm(swiglu)")
+    return out
