@@ -72,6 +72,57 @@ int xp_norm_publish(const XpNormArgs* a, void* stream);
 int xp_swiglu(const void* gate_up, void* out, int rows, int inter, float limit, float up_add,
               float alpha, void* stream);
 
+/* q/k RMSNorm + rotary embedding + paged KV scatter over a fused QKV projection. */
+typedef struct XpRopeArgs {
+  const void* qkv;            /* bf16 [rows, ld_qkv]: q heads, k heads, v heads */
+  void* q_out;                /* bf16 [rows, q_heads, head_dim] */
+  void* k_cache;              /* bf16 [pages, page_size, kv_heads, head_dim] */
+  void* v_cache;
+  const void* q_norm_weight;  /* optional bf16 [head_dim] */
+  const void* k_norm_weight;
+  const int* positions;       /* [rows] */
+  const int* slots;           /* [rows] page * page_size + offset, -1 = skip */
+  int rows, ld_qkv, q_heads, kv_heads, head_dim;
+  float eps, log2_theta;
+} XpRopeArgs;
+
+typedef struct XpDecodeAttnArgs {
+  const void* q;              /* bf16 [batch, q_heads, head_dim] */
+  const void* k_cache;
+  const void* v_cache;
+  void* out;                  /* bf16 [batch, q_heads, head_dim] */
+  float* ws;                  /* [batch, q_heads, splits, head_dim + 2] when splits > 1 */
+  const int* block_table;     /* [batch, max_blocks] */
+  const int* seq_lens;        /* [batch] tokens in cache including the current one */
+  int batch, q_heads, kv_heads, head_dim, page_size, max_blocks, num_splits;
+  float scale;
+} XpDecodeAttnArgs;
+
+typedef struct XpPrefillAttnArgs {
+  const void* q;              /* bf16 [total_q, q_heads, head_dim], sequences packed */
+  const void* k_cache;
+  const void* v_cache;
+  void* out;                  /* bf16 [total_q, q_heads, head_dim] */
+  const int* block_table;     /* [num_seqs, max_blocks] */
+  const int* q_starts;        /* [num_seqs] first packed row of the chunk */
+  const int* q_lens;          /* [num_seqs] rows in the chunk */
+  const int* ctx_lens;        /* [num_seqs] tokens cached before the chunk */
+  int num_seqs, max_q_len, q_heads, kv_heads, head_dim, page_size, max_blocks;
+  float scale;
+} XpPrefillAttnArgs;
+
+int xp_rope_kv(const XpRopeArgs* a, void* stream);
+int xp_decode_attn_splits(int batch, int kv_heads, int max_len);
+int xp_decode_attn(const XpDecodeAttnArgs* a, void* stream);
+int xp_prefill_attn(const XpPrefillAttnArgs* a, void* stream);
+
+/* Small row-wise helpers. */
+int xp_embedding(const int* ids, const void* table, void* out, int rows, int hidden, int vocab,
+                 void* stream);
+int xp_argmax(const void* logits, int is_fp32, int* out, int rows, int vocab, int ld, void* stream);
+int xp_fill_u32(void* p, uint32_t v, size_t n, void* stream);
+int xp_l2_flush(void* p, size_t bytes, void* stream);
+
 int xp_abi_version(void);
 int xp_gemm_plan(const XpGemmArgs* a, XpGemmPlan* plan);
 int xp_gemm(const XpGemmArgs* a);

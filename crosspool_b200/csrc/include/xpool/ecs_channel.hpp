@@ -1,0 +1,109 @@
+// Elastic Context State control channel: one POSIX-shm block shared by the
+// daemon (capacity policy), the AtnAgents (device memory reports) and the
+// Instance ranks (demand / completion), with one seqlock per published record.
+//
+// Down:  QuotaCommand{sequence, target_bytes}            daemon   -> instance
+// Up:    QuotaDemand{evaluated_sequence, required_bytes,
+//                    deadline_monotonic_ns}              instance -> daemon
+//        QuotaCompletion{sequence, mapped_bytes}         instance -> daemon
+//        DeviceMemoryReport{free, total}                 atnagent -> daemon
+// (Reference: src/cext-include/xpool/ecs/{layout,channel}.hpp,
+// src/cext/ecs/channel.cpp:28-35 for the odd/even revision protocol.)
+#pragma once
+
+#include <stdint.h>
+
+#include <atomic>
+
+namespace xpool {
+namespace ecs {
+
+constexpr uint64_t kChannelMagic = 0x5850423230304b56ull;  // "XPB200KV"
+
+struct QuotaCommand {
+  uint64_t sequence;
+  uint64_t target_bytes;
+};
+struct QuotaDemand {
+  uint64_t evaluated_sequence;
+  uint64_t required_bytes;
+  uint64_t deadline_monotonic_ns;
+  uint64_t mapped_bytes;
+};
+struct QuotaCompletion {
+  uint64_t sequence;
+  uint64_t mapped_bytes;
+};
+struct DeviceMemoryReport {
+  uint64_t free_bytes;
+  uint64_t total_bytes;
+  uint64_t report_sequence;
+};
+
+template <typename T>
+struct alignas(64) SeqRecord {
+  std::atomic<uint64_t> revision;  // odd while a writer is inside
+  T value;
+};
+
+struct alignas(64) ChannelHeader {
+  uint64_t magic;
+  uint32_t abi_version;
+  uint32_t device_count;
+  uint32_t partition_count;
+  uint32_t generation;
+  uint64_t total_bytes;
+};
+
+struct alignas(64) DeviceEntry {
+  uint32_t device;
+  uint32_t reserved;
+  SeqRecord<DeviceMemoryReport> report;
+};
+
+// One Instance rank's KV partition on one attention device.
+struct alignas(64) PartitionEntry {
+  uint32_t device;
+  uint32_t group;  // attention TP group the rank belongs to
+  uint32_t rank;
+  uint32_t reserved;
+  uint64_t floor_bytes;
+  uint64_t reservation_bytes;
+  SeqRecord<QuotaCommand> command;
+  SeqRecord<QuotaDemand> demand;
+  SeqRecord<QuotaCompletion> completion;
+};
+
+inline uint64_t channel_bytes(uint32_t devices, uint32_t partitions) {
+  return sizeof(ChannelHeader) + static_cast<uint64_t>(devices) * sizeof(DeviceEntry) +
+         static_cast<uint64_t>(partitions) * sizeof(PartitionEntry);
+}
+
+template <typename T>
+inline void seq_publish(SeqRecord<T>* r, const T& v) {
+  uint64_t rev = r->revision.load(std::memory_order_relaxed);
+  r->revision.store(rev + 1, std::memory_order_seq_cst);  // odd: write in progress
+  r->value = v;
+  r->revision.store(rev + 2, std::memory_order_seq_cst);
+}
+
+// Returns false if no stable snapshot could be taken within `attempts`.
+template <typename T>
+inline bool seq_read(const SeqRecord<T>* r, T* out, uint64_t* revision, int attempts = 1000) {
+  for (int i = 0; i < attempts; ++i) {
+    uint64_t a = r->revision.load(std::memory_order_seq_cst);
+    if (a & 1) continue;
+    T v = r->value;
+    std::atomic_thread_fence(std::memory_order_seq_cst);
+    uint64_t b = r->revision.load(std::memory_order_seq_cst);
+    if (a == b) {
+      *out = v;
+      if (revision != nullptr) *revision = a;
+      return true;
+    }
+  }
+  return false;
+}
+
+}  // namespace ecs
+}  // namespace xpool

@@ -1,0 +1,222 @@
+// Paged decode attention for grouped-query heads with split-KV ("flash
+// decoding"). One CTA handles every query head that shares one KV head over one
+// slice of the sequence; a second small kernel merges the slices. The op is
+// bound by reading the KV cache once, so the layout aims at wide coalesced
+// loads: 8 lanes cooperate on one cached token (16 or 32 bytes each), 16 tokens
+// are in flight per CTA iteration.
+//
+// The reference has no attention code of its own (SGLang/FlashInfer provide
+// it, pyproject.toml:17-35); the oracle is a plain fp32 softmax(QK^T)V.
+#include <math_constants.h>
+
+#include "xpool/api.h"
+#include "xpool/sm100.cuh"
+
+namespace xpool {
+namespace attn {
+
+constexpr int kDecodeThreads = 128;
+
+template <int E>
+__device__ __forceinline__ void load_bf16_vec(const __nv_bfloat16* p, float* out) {
+  static_assert(E == 8 || E == 16, "E");
+#pragma unroll
+  for (int c = 0; c < E / 8; ++c) {
+    uint4 raw = __ldg(reinterpret_cast<const uint4*>(p) + c);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(h[j]);
+      out[c * 8 + 2 * j] = f.x;
+      out[c * 8 + 2 * j + 1] = f.y;
+    }
+  }
+}
+
+// Partial result layout in the workspace: [batch, q_head, split, D + 2] floats:
+// D un-normalised accumulators, running max (log2 domain), running sum.
+template <int D, int GMAX>
+__global__ void __launch_bounds__(kDecodeThreads)
+decode_attn_kernel(XpDecodeAttnArgs a) {
+  constexpr int E = D / 8;  // elements per lane
+  __shared__ float q_s[GMAX][D];
+  __shared__ float red[4][GMAX][D + 2];
+
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int G = a.q_heads / a.kv_heads;
+  const int len = a.seq_lens[b];
+  const int nsplit = gridDim.x;
+  int chunk = (len + nsplit - 1) / nsplit;
+  chunk = (chunk + 15) & ~15;
+  const int t0 = split * chunk;
+  const int t1 = min(len, t0 + chunk);
+
+  // q pre-scaled into the exp2 domain
+  const float qscale = a.scale * 1.4426950408889634f;
+  for (int i = threadIdx.x; i < GMAX * D; i += kDecodeThreads) {
+    const int g = i / D, d = i % D;
+    float v = 0.f;
+    if (g < G)
+      v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(
+              a.q)[(static_cast<size_t>(b) * a.q_heads + hk * G + g) * D + d]) * qscale;
+    q_s[g][d] = v;
+  }
+  __syncthreads();
+
+  const int grp = threadIdx.x >> 3, gl = threadIdx.x & 7;
+  float m[GMAX], l[GMAX], acc[GMAX][E];
+#pragma unroll
+  for (int g = 0; g < GMAX; ++g) {
+    m[g] = -CUDART_INF_F;
+    l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
+  }
+  const int* table = a.block_table + static_cast<size_t>(b) * a.max_blocks;
+  const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(a.k_cache);
+  const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.v_cache);
+  for (int t = t0 + grp; t < t1; t += 16) {
+    const int page = table[t / a.page_size];
+    const size_t tok = static_cast<size_t>(page) * a.page_size + (t % a.page_size);
+    const size_t off = (tok * a.kv_heads + hk) * D + gl * E;
+    float kf[E], vf[E];
+    load_bf16_vec<E>(kc + off, kf);
+    load_bf16_vec<E>(vc + off, vf);
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) {
+      if (g >= G) break;
+      float s = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) s += q_s[g][gl * E + e] * kf[e];
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      const float mn = fmaxf(m[g], s);
+      const float corr = exp2f(m[g] - mn);
+      const float p = exp2f(s - mn);
+      m[g] = mn;
+      l[g] = l[g] * corr + p;
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[g][e] = acc[g][e] * corr + p * vf[e];
+    }
+  }
+  // merge the four token groups of a warp (lanes differing in bits 3 and 4)
+#pragma unroll
+  for (int g = 0; g < GMAX; ++g) {
+#pragma unroll
+    for (int o = 8; o <= 16; o <<= 1) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
+      const float lo = __shfl_xor_sync(0xffffffffu, l[g], o);
+      const float mn = fmaxf(m[g], mo);
+      const float c0 = (m[g] == -CUDART_INF_F) ? 0.f : exp2f(m[g] - mn);
+      const float c1 = (mo == -CUDART_INF_F) ? 0.f : exp2f(mo - mn);
+      l[g] = l[g] * c0 + lo * c1;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float ao = __shfl_xor_sync(0xffffffffu, acc[g][e], o);
+        acc[g][e] = acc[g][e] * c0 + ao * c1;
+      }
+      m[g] = mn;
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane < 8) {
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) red[warp][g][lane * E + e] = acc[g][e];
+      if (lane == 0) {
+        red[warp][g][D] = m[g];
+        red[warp][g][D + 1] = l[g];
+      }
+    }
+  }
+  __syncthreads();
+  // merge the four warps; thread -> (g, d)
+  for (int i = threadIdx.x; i < G * D; i += kDecodeThreads) {
+    const int g = i / D, d = i % D;
+    float mm = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red[w][g][D]);
+    float ll = 0.f, av = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = red[w][g][D];
+      const float c = (mw == -CUDART_INF_F) ? 0.f : exp2f(mw - mm);
+      ll += red[w][g][D + 1] * c;
+      av += red[w][g][d] * c;
+    }
+    const int hq = hk * G + g;
+    if (nsplit == 1) {
+      const float o = ll > 0.f ? av / ll : 0.f;
+      reinterpret_cast<__nv_bfloat16*>(a.out)[(static_cast<size_t>(b) * a.q_heads + hq) * D + d] =
+          __float2bfloat16_rn(o);
+    } else {
+      float* ws = a.ws + ((static_cast<size_t>(b) * a.q_heads + hq) * nsplit + split) * (D + 2);
+      ws[d] = av;
+      if (d == 0) {
+        ws[D] = mm;
+        ws[D + 1] = ll;
+      }
+    }
+  }
+}
+
+template <int D>
+__global__ void decode_combine_kernel(XpDecodeAttnArgs a, int nsplit) {
+  const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const float* ws = a.ws + (static_cast<size_t>(b) * a.q_heads + hq) * nsplit * (D + 2);
+  float mm = -CUDART_INF_F;
+  for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, ws[s * (D + 2) + D]);
+  float ll = 0.f, av = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float ms = ws[s * (D + 2) + D];
+    const float c = (ms == -CUDART_INF_F) ? 0.f : exp2f(ms - mm);
+    ll += ws[s * (D + 2) + D + 1] * c;
+    av += ws[s * (D + 2) + d] * c;
+  }
+  reinterpret_cast<__nv_bfloat16*>(a.out)[(static_cast<size_t>(b) * a.q_heads + hq) * D + d] =
+      __float2bfloat16_rn(ll > 0.f ? av / ll : 0.f);
+}
+
+template <int D, int GMAX>
+static int launch_decode(const XpDecodeAttnArgs& a, int nsplit, cudaStream_t s) {
+  dim3 grid(nsplit, a.kv_heads, a.batch);
+  decode_attn_kernel<D, GMAX><<<grid, kDecodeThreads, 0, s>>>(a);
+  if (nsplit > 1) decode_combine_kernel<D><<<dim3(a.q_heads, a.batch), D, 0, s>>>(a, nsplit);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);
+}
+
+}  // namespace attn
+}  // namespace xpool
+
+extern "C" int xp_decode_attn_splits(int batch, int kv_heads, int max_len) {
+  // enough CTAs to fill 148 SMs a few times over, at least 256 tokens per slice
+  int want = (148 * 4 + batch * kv_heads - 1) / (batch * kv_heads);
+  int cap = (max_len + 255) / 256;
+  int n = want < cap ? want : cap;
+  if (n < 1) n = 1;
+  if (n > 64) n = 64;
+  return n;
+}
+
+extern "C" int xp_decode_attn(const XpDecodeAttnArgs* a, void* stream) {
+  using namespace xpool::attn;
+  if (a->batch <= 0) return 0;
+  if (a->q_heads % a->kv_heads != 0) return -10;
+  const int G = a->q_heads / a->kv_heads;
+  int nsplit = a->num_splits > 0 ? a->num_splits : 1;
+  if (nsplit > 1 && a->ws == nullptr) return -11;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (a->head_dim == 128) {
+    if (G <= 2) return launch_decode<128, 2>(*a, nsplit, s);
+    if (G <= 4) return launch_decode<128, 4>(*a, nsplit, s);
+    if (G <= 8) return launch_decode<128, 8>(*a, nsplit, s);
+  } else if (a->head_dim == 64) {
+    if (G <= 2) return launch_decode<64, 2>(*a, nsplit, s);
+    if (G <= 4) return launch_decode<64, 4>(*a, nsplit, s);
+    if (G <= 8) return launch_decode<64, 8>(*a, nsplit, s);
+  }
+  return -12;
+}

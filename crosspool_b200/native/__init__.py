@@ -129,6 +129,7 @@ def kernels() -> C.CDLL:
     lib.xp_l2_flush.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
     lib.xp_encode_tmap_2d.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32,
                                       C.c_uint32]
+    _declare_attention(lib)
     return lib
 
 
@@ -139,3 +140,76 @@ def kernels_available() -> bool:
 def check(rc: int, what: str) -> None:
     if rc != 0:
         raise NativeLibraryError(f"{what} failed with code {rc}")
+
+
+class RopeArgs(C.Structure):
+    _fields_ = [
+        ("qkv", C.c_void_p),
+        ("q_out", C.c_void_p),
+        ("k_cache", C.c_void_p),
+        ("v_cache", C.c_void_p),
+        ("q_norm_weight", C.c_void_p),
+        ("k_norm_weight", C.c_void_p),
+        ("positions", C.c_void_p),
+        ("slots", C.c_void_p),
+        ("rows", C.c_int),
+        ("ld_qkv", C.c_int),
+        ("q_heads", C.c_int),
+        ("kv_heads", C.c_int),
+        ("head_dim", C.c_int),
+        ("eps", C.c_float),
+        ("log2_theta", C.c_float),
+    ]
+
+
+class DecodeAttnArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p),
+        ("k_cache", C.c_void_p),
+        ("v_cache", C.c_void_p),
+        ("out", C.c_void_p),
+        ("ws", C.c_void_p),
+        ("block_table", C.c_void_p),
+        ("seq_lens", C.c_void_p),
+        ("batch", C.c_int),
+        ("q_heads", C.c_int),
+        ("kv_heads", C.c_int),
+        ("head_dim", C.c_int),
+        ("page_size", C.c_int),
+        ("max_blocks", C.c_int),
+        ("num_splits", C.c_int),
+        ("scale", C.c_float),
+    ]
+
+
+class PrefillAttnArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p),
+        ("k_cache", C.c_void_p),
+        ("v_cache", C.c_void_p),
+        ("out", C.c_void_p),
+        ("block_table", C.c_void_p),
+        ("q_starts", C.c_void_p),
+        ("q_lens", C.c_void_p),
+        ("ctx_lens", C.c_void_p),
+        ("num_seqs", C.c_int),
+        ("max_q_len", C.c_int),
+        ("q_heads", C.c_int),
+        ("kv_heads", C.c_int),
+        ("head_dim", C.c_int),
+        ("page_size", C.c_int),
+        ("max_blocks", C.c_int),
+        ("scale", C.c_float),
+    ]
+
+
+def _declare_attention(lib: C.CDLL) -> None:
+    for fn in ("xp_rope_kv", "xp_decode_attn", "xp_prefill_attn", "xp_embedding", "xp_argmax",
+               "xp_decode_attn_splits"):
+        getattr(lib, fn).restype = C.c_int
+    lib.xp_rope_kv.argtypes = [C.POINTER(RopeArgs), C.c_void_p]
+    lib.xp_decode_attn.argtypes = [C.POINTER(DecodeAttnArgs), C.c_void_p]
+    lib.xp_prefill_attn.argtypes = [C.POINTER(PrefillAttnArgs), C.c_void_p]
+    lib.xp_decode_attn_splits.argtypes = [C.c_int, C.c_int, C.c_int]
+    lib.xp_embedding.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.xp_argmax.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
