@@ -1,0 +1,337 @@
+"""Deployment configuration: one declarative registry, four sources.
+
+Every setting names its TOML path, optional environment variable, optional CLI flag, parser and
+default; the effective value is resolved with the precedence **CLI > environment > TOML > default**.
+``XPOOL_CONFIG`` (or ``--config``) points at the TOML file. The key set and the precedence are the
+reference's (src/xpool/config.py:86-402, docs/designs/control-plane.md:10-20) so that an existing
+deployment TOML loads unchanged; ``digest()`` lets every joining process prove to the daemon that it
+resolved the same effective configuration (``POST /config/check``).
+"""
+
+from __future__ import annotations
+
+import argparse
+import hashlib
+import json
+import os
+import tomllib
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Callable, Mapping, Sequence
+
+_MISSING = object()
+
+
+class ConfigError(ValueError):
+    pass
+
+
+def _bool(v: Any) -> bool:
+    if isinstance(v, bool):
+        return v
+    s = str(v).strip().lower()
+    if s in ("1", "true", "yes", "on"):
+        return True
+    if s in ("0", "false", "no", "off"):
+        return False
+    raise ConfigError(f"not a boolean: {v!r}")
+
+
+def _int(lo: int | None = None, hi: int | None = None) -> Callable[[Any], int]:
+    def parse(v: Any) -> int:
+        if isinstance(v, bool):
+            raise ConfigError(f"not an integer: {v!r}")
+        try:
+            i = int(v)
+        except (TypeError, ValueError):
+            raise ConfigError(f"not an integer: {v!r}") from None
+        if (lo is not None and i < lo) or (hi is not None and i > hi):
+            raise ConfigError(f"{i} outside [{lo}, {hi}]")
+        return i
+
+    return parse
+
+
+def _float(lo: float | None = None, hi: float | None = None) -> Callable[[Any], float]:
+    def parse(v: Any) -> float:
+        try:
+            f = float(v)
+        except (TypeError, ValueError):
+            raise ConfigError(f"not a number: {v!r}") from None
+        if (lo is not None and f < lo) or (hi is not None and f > hi):
+            raise ConfigError(f"{f} outside [{lo}, {hi}]")
+        return f
+
+    return parse
+
+
+def _choice(*allowed: str) -> Callable[[Any], str]:
+    def parse(v: Any) -> str:
+        s = str(v).lower()
+        if s not in allowed:
+            raise ConfigError(f"{v!r} not one of {allowed}")
+        return s
+
+    return parse
+
+
+def _devices(v: Any) -> tuple[int, ...]:
+    if isinstance(v, str):
+        v = [p for p in v.replace(",", " ").split() if p]
+    try:
+        out = tuple(int(x) for x in v)
+    except (TypeError, ValueError):
+        raise ConfigError(f"not a device list: {v!r}") from None
+    if len(set(out)) != len(out) or any(d < 0 for d in out):
+        raise ConfigError(f"device list has duplicates or negatives: {out}")
+    return out
+
+
+def _slo(v: Any) -> "Slo":
+    if isinstance(v, Slo):
+        return v
+    if not isinstance(v, Mapping) or set(v) - {"ttft_ms", "tbt_ms"}:
+        raise ConfigError(f"slo must be a table with ttft_ms and tbt_ms, got {v!r}")
+    try:
+        return Slo(float(v["ttft_ms"]), float(v["tbt_ms"]))
+    except KeyError as e:
+        raise ConfigError(f"slo misses {e.args[0]}") from None
+
+
+@dataclass(frozen=True)
+class Slo:
+    ttft_ms: float
+    tbt_ms: float
+
+    def __post_init__(self):
+        if self.ttft_ms <= 0 or self.tbt_ms <= 0:
+            raise ConfigError("slo values must be positive")
+
+
+@dataclass(frozen=True)
+class ModelEntry:
+    id: str
+    path: str
+    atn_tp_size: int = 1
+    atn_dp_size: int = 1
+    ffn_tp_size: int | None = None  # None: all FFN devices
+    ffn_ep_size: int = 1            # expert parallelism (not in the reference, which rejects EP)
+    slo: Slo | None = None
+
+    @property
+    def atn_world_size(self) -> int:
+        return self.atn_tp_size * self.atn_dp_size
+
+
+@dataclass(frozen=True)
+class ConfigSetting:
+    name: str
+    path: tuple[str, ...] | None          # TOML path; None = bootstrap-only (no TOML source)
+    parser: Callable[[Any], Any]
+    default: Any = _MISSING
+    cli: str | None = None
+    env_var: str | None = None
+    required: bool = False
+    description: str = ""
+
+
+def _observer(name: str) -> list[ConfigSetting]:
+    up = name.upper()
+    return [
+        ConfigSetting(f"debug_{name}_observer_enable", ("debug", f"{name}_observer", "enable"), _bool, False,
+                      env_var=f"XPOOL_DEBUG_{up}_OBSERVER_ENABLE", description=f"record {name} events"),
+        ConfigSetting(f"debug_{name}_observer_outdir", ("debug", f"{name}_observer", "outdir"), str, "",
+                      env_var=f"XPOOL_DEBUG_{up}_OBSERVER_OUTDIR", description="artifact directory"),
+        ConfigSetting(f"debug_{name}_observer_record_capacity", ("debug", f"{name}_observer", "record_capacity"),
+                      _int(1), 65536, env_var=f"XPOOL_DEBUG_{up}_OBSERVER_RECORD_CAPACITY",
+                      description="events kept before dropping"),
+    ]
+
+
+CONFIG_REGISTRY: tuple[ConfigSetting, ...] = (
+    ConfigSetting("cache_root", ("cache_root",), str, ".xpool-cache", cli="--cache-root", env_var="XPOOL_CACHE_ROOT",
+                  description="directory for calibration profiles and caches"),
+    ConfigSetting("config", None, str, "", cli="--config", env_var="XPOOL_CONFIG",
+                  description="path of the deployment TOML"),
+    ConfigSetting("logging_level", ("logging", "level"), _choice("debug", "info", "warning", "error"), "info",
+                  cli="--log-level", env_var="XPOOL_LOG_LEVEL"),
+    ConfigSetting("logging_color", ("logging", "color"), _choice("auto", "always", "never"), "auto"),
+    *_observer("graph"), *_observer("transport"), *_observer("fabric"), *_observer("ffn_routing"),
+    ConfigSetting("vendor_model_base_uri", ("vendor", "model_base_uri"), str, ""),
+    ConfigSetting("atn_devices", ("atn", "devices"), _devices, required=True),
+    ConfigSetting("atn_device_memory_utilization", ("atn", "device_memory_utilization"), _float(0.05, 1.0), 0.95),
+    ConfigSetting("ffn_devices", ("ffn", "devices"), _devices, required=True),
+    ConfigSetting("ffn_device_memory_calibration", ("ffn", "device_memory_calibration"), _bool, False,
+                  env_var="XPOOL_FFN_DEVICE_MEMORY_CALIBRATION"),
+    ConfigSetting("ffn_device_memory_extra_margin_bytes", ("ffn", "device_memory_extra_margin_bytes"), _int(0), 0),
+    ConfigSetting("ffn_loader_parallelism", ("ffn", "loader", "parallelism"), _int(1, 256), 4,
+                  cli="--ffn-loader-parallelism", env_var="XPOOL_FFN_LOADER_PARALLELISM"),
+    ConfigSetting("ffn_placement_parallelism", ("ffn", "placement", "parallelism"), _int(1, 256), 1,
+                  cli="--ffn-placement-parallelism", env_var="XPOOL_FFN_PLACEMENT_PARALLELISM"),
+    ConfigSetting("ffn_placement_timeout_seconds", ("ffn", "placement", "timeout_seconds"), _float(0.001), 60.0),
+    ConfigSetting("daemon_host", ("daemon", "host"), str, "127.0.0.1", cli="--daemon-host"),
+    ConfigSetting("daemon_port", ("daemon", "port"), _int(1, 65535), 9810, cli="--daemon-port"),
+    ConfigSetting("scheduler_ffn_concurrency", ("scheduler", "ffn_concurrency"), _int(1, 64), 1,
+                  cli="--ffn-concurrency", description="Executor Lanes per FFN device"),
+    ConfigSetting("scheduler_ffn_policy", ("scheduler", "ffn_policy"), _choice("fifo", "random", "slo"), "fifo",
+                  cli="--ffn-policy"),
+    ConfigSetting("scheduler_ffn_random_seed", ("scheduler", "ffn_random_seed"), _int(0), 0),
+    ConfigSetting("scheduler_slo", ("scheduler", "slo"), _slo, required=True),
+)
+
+_BY_NAME = {s.name: s for s in CONFIG_REGISTRY}
+
+
+def _toml_get(doc: Mapping[str, Any], path: Sequence[str]) -> Any:
+    cur: Any = doc
+    for p in path:
+        if not isinstance(cur, Mapping) or p not in cur:
+            return _MISSING
+        cur = cur[p]
+    return cur
+
+
+def _parse_models(doc: Mapping[str, Any], ffn_devices: tuple[int, ...]) -> tuple[ModelEntry, ...]:
+    out = []
+    seen = set()
+    for i, m in enumerate(doc.get("models", []) or []):
+        if not isinstance(m, Mapping):
+            raise ConfigError(f"models[{i}] is not a table")
+        extra = set(m) - {"id", "path", "atn_tp_size", "atn_dp_size", "ffn_tp_size", "ffn_ep_size", "slo"}
+        if extra:
+            raise ConfigError(f"models[{i}] has unknown keys {sorted(extra)}")
+        if "id" not in m:
+            raise ConfigError(f"models[{i}] misses id")
+        mid = str(m["id"])
+        if mid in seen:
+            raise ConfigError(f"duplicate model id {mid}")
+        seen.add(mid)
+        tp = _int(1)(m.get("atn_tp_size", 1))
+        dp = _int(1)(m.get("atn_dp_size", 1))
+        if tp > 1 and dp > 1:
+            # same restriction as the reference (src/cext/fabric/projection.cpp:27-28)
+            raise ConfigError(f"model {mid}: combined attention TP-by-DP is not supported")
+        ftp = m.get("ffn_tp_size")
+        ftp = _int(1, max(1, len(ffn_devices)))(ftp) if ftp is not None else None
+        ep = _int(1, max(1, len(ffn_devices)))(m.get("ffn_ep_size", 1))
+        out.append(ModelEntry(mid, str(m.get("path", mid)), tp, dp, ftp, ep, _slo(m["slo"]) if "slo" in m else None))
+    return tuple(out)
+
+
+@dataclass(frozen=True)
+class XpoolConfig:
+    values: Mapping[str, Any]
+    models: tuple[ModelEntry, ...] = ()
+    sources: Mapping[str, str] = field(default_factory=dict, compare=False)
+
+    def __getattr__(self, name: str) -> Any:
+        try:
+            return self.__dict__["values"][name]
+        except KeyError:
+            raise AttributeError(name) from None
+
+    def model(self, model_id: str) -> ModelEntry:
+        for m in self.models:
+            if m.id == model_id:
+                return m
+        raise KeyError(model_id)
+
+    def slo_for(self, model_id: str) -> Slo:
+        m = self.model(model_id)
+        return m.slo or self.values["scheduler_slo"]
+
+    def ffn_tp_for(self, model_id: str) -> int:
+        m = self.model(model_id)
+        return m.ffn_tp_size or max(1, len(self.values["ffn_devices"]))
+
+    def as_dict(self) -> dict[str, Any]:
+        def enc(v):
+            if isinstance(v, Slo):
+                return {"ttft_ms": v.ttft_ms, "tbt_ms": v.tbt_ms}
+            if isinstance(v, tuple):
+                return list(v)
+            return v
+
+        d = {k: enc(v) for k, v in sorted(self.values.items()) if k != "config"}
+        d["models"] = [{"id": m.id, "path": m.path, "atn_tp_size": m.atn_tp_size, "atn_dp_size": m.atn_dp_size,
+                        "ffn_tp_size": m.ffn_tp_size, "ffn_ep_size": m.ffn_ep_size, "slo": enc(m.slo) if m.slo else None}
+                       for m in self.models]
+        return d
+
+    def digest(self) -> str:
+        return hashlib.sha256(json.dumps(self.as_dict(), sort_keys=True).encode()).hexdigest()
+
+
+def add_cli_arguments(parser: argparse.ArgumentParser) -> None:
+    for s in CONFIG_REGISTRY:
+        if s.cli:
+            parser.add_argument(s.cli, dest=f"cfg_{s.name}", default=None, help=s.description or s.name)
+
+
+def cli_overrides(ns: argparse.Namespace) -> dict[str, Any]:
+    return {s.name: getattr(ns, f"cfg_{s.name}") for s in CONFIG_REGISTRY
+            if s.cli and getattr(ns, f"cfg_{s.name}", None) is not None}
+
+
+def load_config(cli: Mapping[str, Any] | None = None, env: Mapping[str, str] | None = None,
+                toml_text: str | None = None, require: bool = True) -> XpoolConfig:
+    """Resolves the effective configuration. ``toml_text`` overrides reading the file named by
+    ``--config`` / ``XPOOL_CONFIG``."""
+    cli = dict(cli or {})
+    env = os.environ if env is None else env
+    path = cli.get("config") or env.get("XPOOL_CONFIG") or ""
+    doc: Mapping[str, Any] = {}
+    if toml_text is not None:
+        doc = tomllib.loads(toml_text)
+    elif path:
+        p = Path(path)
+        if not p.exists():
+            raise ConfigError(f"config file {path} does not exist")
+        doc = tomllib.loads(p.read_text())
+    values: dict[str, Any] = {}
+    sources: dict[str, str] = {}
+    for s in CONFIG_REGISTRY:
+        raw, src = _MISSING, "default"
+        if s.name in cli and cli[s.name] is not None:
+            raw, src = cli[s.name], "cli"
+        elif s.env_var and s.env_var in env:
+            raw, src = env[s.env_var], "env"
+        elif s.path is not None and (v := _toml_get(doc, s.path)) is not _MISSING:
+            raw, src = v, "toml"
+        elif s.default is not _MISSING:
+            raw = s.default
+        if raw is _MISSING:
+            if s.required and require:
+                raise ConfigError(f"required setting {'.'.join(s.path or (s.name,))} is missing")
+            values[s.name] = None
+            sources[s.name] = "missing"
+            continue
+        try:
+            values[s.name] = s.parser(raw)
+        except ConfigError as e:
+            raise ConfigError(f"{'.'.join(s.path or (s.name,))} ({src}): {e}") from None
+        sources[s.name] = src
+    values["config"] = str(path)
+    atn, ffn = values.get("atn_devices") or (), values.get("ffn_devices") or ()
+    if set(atn) & set(ffn):
+        raise ConfigError(f"devices {sorted(set(atn) & set(ffn))} are listed under both [atn] and [ffn]")
+    models = _parse_models(doc, ffn)
+    for m in models:
+        if m.atn_world_size > max(1, len(atn)) and require:
+            raise ConfigError(f"model {m.id} needs {m.atn_world_size} attention devices, {len(atn)} configured")
+    return XpoolConfig(values, models, sources)
+
+
+_GLOBAL: XpoolConfig | None = None
+
+
+def init_global_config(cli: Mapping[str, Any] | None = None, **kw) -> XpoolConfig:
+    global _GLOBAL
+    _GLOBAL = load_config(cli, **kw)
+    return _GLOBAL
+
+
+def global_config() -> XpoolConfig:
+    if _GLOBAL is None:
+        raise ConfigError("configuration not initialised")
+    return _GLOBAL

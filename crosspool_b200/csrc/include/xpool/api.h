@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 7
+#define XP_ABI_VERSION 8
 
 #ifdef __cplusplus
 extern "C" {
@@ -38,6 +38,7 @@ typedef struct XpGemmArgs {
   int bn;              /* 0 = choose */
   int num_sms;         /* 0 = all */
   int w_evict_first;
+  int w_tiled;         /* weights pre-tiled into contiguous 128x64 blocks */
   float gate_limit, up_add, act_alpha;
 } XpGemmArgs;
 

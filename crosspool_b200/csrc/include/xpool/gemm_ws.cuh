@@ -70,6 +70,7 @@ struct Problem {
   int dual;                   // 1: gate rows [0, n_out), up rows [up_offset, up_offset + n_out)
   int up_offset;
   int w_evict_first;          // stream weights through L2
+  int w_tiled;                // weights stored as contiguous 128x64 tiles (see tile_weight)
   float gate_limit;           // > 0: clamp gate from above and up to [-limit, limit]
   float up_add;               // added to up before the product (0 for plain SwiGLU)
   float act_alpha;            // 0: silu(g); else g * sigmoid(alpha * g)
@@ -187,16 +188,20 @@ __device__ __forceinline__ bool produce_tile(const Problem& p, const TileCoord& 
     uint8_t* a = tiles + static_cast<size_t>(st.stage) * L.stage_bytes;
     uint8_t* b = a + L.a_bytes;
     sm100::mbar_arrive_expect_tx(&bar->full[st.stage], tx);
+    // Row-major weights: box at (k, row). Tiled weights: every 128x64 tile is one
+    // contiguous 16 KB run, tile index = m_tile * k_tiles + k_tile.
+    const int kb_total = p.k / kTileK;
+    const int wc0 = p.w_tiled ? 0 : kb * kTileK;
+    const int wc1 = p.w_tiled ? ((c.m0 / kTileM) * kb_total + kb) * kTileM : c.m0;
+    const int uc1 = p.w_tiled ? (((p.up_offset + c.m0) / kTileM) * kb_total + kb) * kTileM
+                              : p.up_offset + c.m0;
     if (p.w_evict_first) {
-      sm100::tma_load_2d_hint(a, p.tmap_w, &bar->full[st.stage], kb * kTileK, c.m0, pol);
+      sm100::tma_load_2d_hint(a, p.tmap_w, &bar->full[st.stage], wc0, wc1, pol);
       if (p.dual)
-        sm100::tma_load_2d_hint(a + kTileM * kTileK * 2, p.tmap_w, &bar->full[st.stage],
-                                kb * kTileK, p.up_offset + c.m0, pol);
+        sm100::tma_load_2d_hint(a + kTileM * kTileK * 2, p.tmap_w, &bar->full[st.stage], wc0, uc1, pol);
     } else {
-      sm100::tma_load_2d(a, p.tmap_w, &bar->full[st.stage], kb * kTileK, c.m0);
-      if (p.dual)
-        sm100::tma_load_2d(a + kTileM * kTileK * 2, p.tmap_w, &bar->full[st.stage], kb * kTileK,
-                           p.up_offset + c.m0);
+      sm100::tma_load_2d(a, p.tmap_w, &bar->full[st.stage], wc0, wc1);
+      if (p.dual) sm100::tma_load_2d(a + kTileM * kTileK * 2, p.tmap_w, &bar->full[st.stage], wc0, uc1);
     }
     sm100::tma_load_2d(b, p.tmap_x, &bar->full[st.stage], kb * kTileK, c.n0);
     st.advance(L.stages);
@@ -299,7 +304,8 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
       bar->tmem_base + st.acc * acc_cols + (static_cast<uint32_t>(ew * 32) << 16);
   const int lane_in_tile = ew * 32 + lane;
   const int f = c.m0 + lane_in_tile;
-  if (!sm100::mbar_wait(&bar->acc_full[st.acc], st.acc_phase, deadline)) return false;
+  // all lanes agree on the outcome so that the aligned TMEM loads below stay convergent
+  if (!__all_sync(0xffffffffu, sm100::mbar_wait(&bar->acc_full[st.acc], st.acc_phase, deadline))) return false;
   sm100::tc_fence_after_sync();
 
   float g[16], u[16];

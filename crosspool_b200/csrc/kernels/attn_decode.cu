@@ -75,29 +75,40 @@ decode_attn_kernel(XpDecodeAttnArgs a) {
   const int* table = a.block_table + static_cast<size_t>(b) * a.max_blocks;
   const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(a.k_cache);
   const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.v_cache);
-  for (int t = t0 + grp; t < t1; t += 16) {
-    const int page = table[t / a.page_size];
-    const size_t tok = static_cast<size_t>(page) * a.page_size + (t % a.page_size);
-    const size_t off = (tok * a.kv_heads + hk) * D + gl * E;
+  // The trip count is uniform across the CTA (lanes past the slice's end idle
+  // inside the loop) because the dot-product shuffles below name every lane.
+  for (int tb = t0; tb < t1; tb += 16) {
+    const int t = tb + grp;
+    const bool valid = t < t1;
     float kf[E], vf[E];
-    load_bf16_vec<E>(kc + off, kf);
-    load_bf16_vec<E>(vc + off, vf);
+    if (valid) {
+      const int page = table[t / a.page_size];
+      const size_t tok = static_cast<size_t>(page) * a.page_size + (t % a.page_size);
+      const size_t off = (tok * a.kv_heads + hk) * D + gl * E;
+      load_bf16_vec<E>(kc + off, kf);
+      load_bf16_vec<E>(vc + off, vf);
+    } else {
+#pragma unroll
+      for (int e = 0; e < E; ++e) kf[e] = vf[e] = 0.f;
+    }
 #pragma unroll
     for (int g = 0; g < GMAX; ++g) {
-      if (g >= G) break;
+      if (g >= G) break;  // G is uniform
       float s = 0.f;
 #pragma unroll
       for (int e = 0; e < E; ++e) s += q_s[g][gl * E + e] * kf[e];
       s += __shfl_xor_sync(0xffffffffu, s, 1);
       s += __shfl_xor_sync(0xffffffffu, s, 2);
       s += __shfl_xor_sync(0xffffffffu, s, 4);
-      const float mn = fmaxf(m[g], s);
-      const float corr = exp2f(m[g] - mn);
-      const float p = exp2f(s - mn);
-      m[g] = mn;
-      l[g] = l[g] * corr + p;
+      if (valid) {
+        const float mn = fmaxf(m[g], s);
+        const float corr = exp2f(m[g] - mn);
+        const float p = exp2f(s - mn);
+        m[g] = mn;
+        l[g] = l[g] * corr + p;
 #pragma unroll
-      for (int e = 0; e < E; ++e) acc[g][e] = acc[g][e] * corr + p * vf[e];
+        for (int e = 0; e < E; ++e) acc[g][e] = acc[g][e] * corr + p * vf[e];
+      }
     }
   }
   // merge the four token groups of a warp (lanes differing in bits 3 and 4)

@@ -137,9 +137,15 @@ extern "C" int xp_gemm(const XpGemmArgs* a) {
   }
   CUtensorMap tw, tx;
   const int w_rows = a->w_rows_total > 0 ? a->w_rows_total : (a->dual ? a->up_offset + a->n_out : a->n_out);
-  rc = tmap::cache().get(&tw, a->w, w_rows, a->k, static_cast<uint64_t>(a->ldw > 0 ? a->ldw : a->k) * 2,
-                         gemm::kTileM, 2);
-  if (rc != 0) return -20 + 0 * rc;
+  if (a->w_tiled) {
+    if (w_rows % gemm::kTileM != 0 || (a->dual && a->up_offset % gemm::kTileM != 0)) return -22;
+    rc = tmap::cache().get(&tw, a->w, static_cast<uint64_t>(w_rows) * (a->k / gemm::kTileK), gemm::kTileK,
+                           gemm::kTileK * 2, gemm::kTileM, 2);
+  } else {
+    rc = tmap::cache().get(&tw, a->w, w_rows, a->k, static_cast<uint64_t>(a->ldw > 0 ? a->ldw : a->k) * 2,
+                           gemm::kTileM, 2);
+  }
+  if (rc != 0) return -20;
   rc = tmap::cache().get(&tx, a->x, a->rows, a->k, static_cast<uint64_t>(a->ldx > 0 ? a->ldx : a->k) * 2,
                          plan.bn, 2);
   if (rc != 0) return -21;
@@ -161,6 +167,7 @@ extern "C" int xp_gemm(const XpGemmArgs* a) {
   p.dual = a->dual;
   p.up_offset = a->up_offset;
   p.w_evict_first = a->w_evict_first;
+  p.w_tiled = a->w_tiled;
   p.gate_limit = a->gate_limit;
   p.up_add = a->up_add;
   p.act_alpha = a->act_alpha;

@@ -1,0 +1,437 @@
+"""Attention-side engine of one Instance on one attention device.
+
+Owns embedding, attention (paged KV), norms, LM head, greedy sampling and a continuous-batching
+scheduler with chunked prefill; every decoder FFN goes through an :class:`FfnPort` — in-stream on
+the same GPU (loopback), or published to the FFN tier over peer memory. The reference borrows all of
+this from SGLang and only swaps the MLP for a shim (src/xpool/integrations/sglang/shim.py:94-192);
+here the engine is native so that the kernel which produces the post-attention hidden states is
+itself the transport producer.
+
+Per decode step the host does one pinned H2D copy of the step's metadata (token ids, positions, KV
+slots, sequence lengths, block table), replays one CUDA graph for the batch-size bucket, and reads
+the sampled token ids back with one D2H copy.
+"""
+
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.weights import AttentionWeights
+from ..ops import attention as A
+from ..ops import gemm, norm
+from .kv_cache import OutOfPages, PagedKvCache
+
+MODE_PREFILL, MODE_DECODE = 1, 2
+
+
+def capacity_buckets(max_rows: int) -> list[int]:
+    """Powers of two up to the maximum plus the exact maximum — the reference's Capacity rule
+    (src/xpool/runtime/ffnagent/execution.py:166-177)."""
+    out, c = [], 1
+    while c < max_rows:
+        out.append(c)
+        c *= 2
+    out.append(max_rows)
+    return out
+
+
+@dataclass
+class EngineConfig:
+    max_batch: int = 256
+    prefill_chunk: int = 2048
+    max_seq_len: int = 4096
+    page_size: int = 16
+    num_pages: int = 0  # 0: sized for max_batch sequences of max_seq_len
+    max_prefill_seqs: int = 64
+    use_cuda_graph: bool = True
+    decode_buckets: list[int] | None = None
+
+
+@dataclass
+class Sequence:
+    seq_id: int
+    prompt: list[int]
+    max_new_tokens: int
+    arrival: float = 0.0
+    deadline: float = 0.0
+    computed: int = 0                # tokens whose KV is cached
+    generated: list[int] = field(default_factory=list)
+    first_token_time: float | None = None
+    finish_time: float | None = None
+    token_times: list[float] = field(default_factory=list)
+
+    @property
+    def total_len(self) -> int:
+        return len(self.prompt) + len(self.generated)
+
+    @property
+    def prefill_done(self) -> bool:
+        return self.computed >= len(self.prompt)
+
+    @property
+    def finished(self) -> bool:
+        return len(self.generated) >= self.max_new_tokens
+
+
+class FfnPort:
+    """Where a layer's FFN runs. ``run`` receives the normalised hidden states of ``rows`` tokens
+    and returns the tensors whose fixed-order sum is the FFN output (one per FFN TP rank)."""
+
+    def attach(self, engine: "AttentionEngine") -> None:  # pragma: no cover - interface
+        pass
+
+    def run(self, layer: int, x: torch.Tensor, rows: int, mode: int) -> list[torch.Tensor]:
+        raise NotImplementedError
+
+    # Ports that receive the hidden states straight from the norm kernel return publish targets.
+    def publish_targets(self, layer: int, rows: int, mode: int) -> dict | None:
+        return None
+
+    def wait_args(self) -> dict:
+        return {}
+
+
+class AttentionEngine:
+    def __init__(self, cfg: ModelConfig, weights: AttentionWeights, port: FfnPort, ecfg: EngineConfig | None = None,
+                 device: str | torch.device = "cuda", kv: PagedKvCache | None = None):
+        self.cfg, self.w, self.port = cfg, weights, port
+        self.ecfg = ecfg or EngineConfig()
+        self.device = torch.device(device)
+        e = self.ecfg
+        self.max_blocks = (e.max_seq_len + e.page_size - 1) // e.page_size
+        if kv is None:
+            pages = e.num_pages or e.max_batch * self.max_blocks
+            kv = PagedKvCache.fixed(cfg, pages, e.page_size, self.device)
+        self.kv = kv
+        self.cap = max(e.max_batch, e.prefill_chunk)
+        self._alloc_buffers()
+        self.waiting: deque[Sequence] = deque()
+        self.running: list[Sequence] = []
+        self.prefilling: list[Sequence] = []
+        self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self._buckets = e.decode_buckets or capacity_buckets(e.max_batch)
+        self._next_id = 0
+        self._last_was_prefill = False
+        self.stats = {"prefill_steps": 0, "decode_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0, "launches": 0}
+        self.stream = torch.cuda.Stream(self.device)
+        port.attach(self)
+
+    # ------------------------------------------------------------------ buffers
+    def _alloc_buffers(self) -> None:
+        cfg, e, dev = self.cfg, self.ecfg, self.device
+        bf = torch.bfloat16
+        cap, B = self.cap, e.max_batch
+        self.resid = torch.zeros(cap, cfg.hidden_size, dtype=bf, device=dev)
+        self.x = torch.zeros(cap, cfg.hidden_size, dtype=bf, device=dev)
+        self.x2 = torch.zeros(cap, cfg.hidden_size, dtype=bf, device=dev)
+        self.qkv = torch.zeros(cap, cfg.q_size + 2 * cfg.kv_size, dtype=bf, device=dev)
+        self.q = torch.zeros(cap, cfg.num_q_heads, cfg.head_dim, dtype=bf, device=dev)
+        self.attn_out = torch.zeros(cap, cfg.num_q_heads, cfg.head_dim, dtype=bf, device=dev)
+        self.o = torch.zeros(cap, cfg.hidden_size, dtype=bf, device=dev)
+        self.sel = torch.zeros(max(B, e.max_prefill_seqs), cfg.hidden_size, dtype=bf, device=dev)
+        self.logits = torch.zeros(max(B, e.max_prefill_seqs), cfg.vocab_size, dtype=bf, device=dev)
+        self.tokens = torch.zeros(max(B, e.max_prefill_seqs), dtype=torch.int32, device=dev)
+        self.tokens_host = torch.zeros(max(B, e.max_prefill_seqs), dtype=torch.int32).pin_memory()
+        # decode metadata: ids | positions | slots | seq_lens | block_table, one pinned mirror
+        self._dec_words = 4 * B + B * self.max_blocks
+        self.dec_meta = torch.zeros(self._dec_words, dtype=torch.int32, device=dev)
+        self.dec_meta_host = torch.zeros(self._dec_words, dtype=torch.int32).pin_memory()
+        # prefill metadata: ids | positions | slots (chunk) + q_starts | q_lens | ctx_lens | last_idx + table
+        P, S = e.prefill_chunk, e.max_prefill_seqs
+        self._pre_words = 3 * P + 4 * S + S * self.max_blocks
+        self.pre_meta = torch.zeros(self._pre_words, dtype=torch.int32, device=dev)
+        self.pre_meta_host = torch.zeros(self._pre_words, dtype=torch.int32).pin_memory()
+        splits = max(A.decode_splits(b, cfg.num_kv_heads, e.max_seq_len) for b in (1, B))
+        self.attn_ws = torch.zeros(B * cfg.num_q_heads * max(splits, 1) * (cfg.head_dim + 2), dtype=torch.float32,
+                                   device=dev)
+
+    def _dec_views(self, B: int):
+        m, cap = self.dec_meta, self.ecfg.max_batch
+        return (m[0:B], m[cap:cap + B], m[2 * cap:2 * cap + B], m[3 * cap:3 * cap + B],
+                m[4 * cap:4 * cap + B * self.max_blocks].view(B, self.max_blocks))
+
+    # ------------------------------------------------------------------ request API
+    def add_request(self, prompt: list[int], max_new_tokens: int, arrival: float | None = None,
+                    deadline: float = 0.0) -> Sequence:
+        if len(prompt) + max_new_tokens > self.ecfg.max_seq_len:
+            raise ValueError("request exceeds max_seq_len")
+        s = Sequence(self._next_id, list(prompt), max_new_tokens, arrival if arrival is not None else time.monotonic(),
+                     deadline)
+        self._next_id += 1
+        self.waiting.append(s)
+        return s
+
+    @property
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running or self.prefilling)
+
+    # ------------------------------------------------------------------ model forward
+    def _layers(self, rows: int, mode: int, attn_fn) -> None:
+        """Runs all decoder layers over the first ``rows`` rows of the static buffers. ``resid``
+        holds the embeddings on entry and the final residual stream (before the last FFN add) on
+        exit; the last FFN output parts are left in ``self._parts``."""
+        cfg, w = self.cfg, self.w
+        resid, x, x2 = self.resid[:rows], self.x[:rows], self.x2[:rows]
+        parts: list[torch.Tensor] | None = None
+        for l, lw in enumerate(w.layers):
+            if parts is None:
+                norm.add_rmsnorm([resid], lw.input_norm, cfg.rms_norm_eps, out=x)
+            else:
+                norm.add_rmsnorm(parts, lw.input_norm, cfg.rms_norm_eps, resid=resid, out=x, **self.port.wait_args())
+            gemm.linear(x, lw.qkv, out=self.qkv[:rows], bias=lw.qkv_bias)
+            attn_fn(l, lw, rows)
+            gemm.linear(self.attn_out[:rows].view(rows, cfg.q_size), lw.o, out=self.o[:rows])
+            tgt = self.port.publish_targets(l, rows, mode)
+            if tgt is None:
+                norm.add_rmsnorm([self.o[:rows]], lw.post_attn_norm, cfg.rms_norm_eps, resid=resid, out=x2)
+            else:
+                norm.add_rmsnorm([self.o[:rows]], lw.post_attn_norm, cfg.rms_norm_eps, resid=resid, out=x2,
+                                 want_local=False, **tgt)
+            parts = self.port.run(l, x2, rows, mode)
+            self.stats["launches"] += 7
+        self._parts = parts
+
+    def _head(self, rows: int, n_sel: int, sel_idx: torch.Tensor | None) -> None:
+        """Final norm, row selection, LM head, greedy sampling into ``self.tokens[:n_sel]``."""
+        cfg = self.cfg
+        norm.add_rmsnorm(self._parts, self.w.final_norm, cfg.rms_norm_eps, resid=self.resid[:rows], out=self.x[:rows],
+                         **self.port.wait_args())
+        if sel_idx is None:
+            hsel = self.x[:n_sel]
+        else:
+            hsel = A.embedding(sel_idx, self.x[:rows], out=self.sel[:n_sel])
+        gemm.linear(hsel, self.w.lm_head, out=self.logits[:n_sel])
+        A.argmax(self.logits[:n_sel], out=self.tokens[:n_sel])
+
+    def _decode_forward(self, B: int) -> None:
+        cfg = self.cfg
+        ids, pos, slots, lens, table = self._dec_views(B)
+        A.embedding(ids, self.w.embed, out=self.resid[:B])
+        splits = A.decode_splits(B, cfg.num_kv_heads, self.ecfg.max_seq_len)
+
+        def attn(l, lw, rows):
+            A.rope_kv_write(self.qkv[:rows], self.q[:rows], self.kv.k[l], self.kv.v[l], pos, slots,
+                            q_heads=cfg.num_q_heads, kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim,
+                            theta=cfg.rope_theta, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_norm_eps)
+            A.paged_decode(self.q[:rows], self.kv.k[l], self.kv.v[l], table, lens, out=self.attn_out[:rows],
+                           num_splits=splits, ws=self.attn_ws)
+
+        self._layers(B, MODE_DECODE, attn)
+        self._head(B, B, None)
+
+    def _prefill_forward(self, rows: int, n_seqs: int, max_q: int) -> None:
+        cfg, P, S = self.cfg, self.ecfg.prefill_chunk, self.ecfg.max_prefill_seqs
+        m = self.pre_meta
+        ids, pos, slots = m[0:rows], m[P:P + rows], m[2 * P:2 * P + rows]
+        b = 3 * P
+        q_starts, q_lens, ctx_lens, last_idx = (m[b:b + n_seqs], m[b + S:b + S + n_seqs],
+                                                m[b + 2 * S:b + 2 * S + n_seqs], m[b + 3 * S:b + 3 * S + n_seqs])
+        table = m[b + 4 * S:b + 4 * S + n_seqs * self.max_blocks].view(n_seqs, self.max_blocks)
+        A.embedding(ids, self.w.embed, out=self.resid[:rows])
+
+        def attn(l, lw, r):
+            A.rope_kv_write(self.qkv[:r], self.q[:r], self.kv.k[l], self.kv.v[l], pos, slots,
+                            q_heads=cfg.num_q_heads, kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim,
+                            theta=cfg.rope_theta, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_norm_eps)
+            A.paged_prefill(self.q[:r], self.kv.k[l], self.kv.v[l], table, q_starts, q_lens, ctx_lens, max_q,
+                            out=self.attn_out[:r])
+
+        self._layers(rows, MODE_PREFILL, attn)
+        self._head(rows, n_seqs, last_idx)
+
+    # ------------------------------------------------------------------ stepping
+    def _bucket(self, n: int) -> int:
+        for b in self._buckets:
+            if b >= n:
+                return b
+        return self._buckets[-1]
+
+    def warmup(self) -> None:
+        """Runs every decode bucket once eagerly (allocates scratch) and captures its CUDA graph."""
+        with torch.cuda.stream(self.stream):
+            self.dec_meta_host.zero_()
+            hv = self.dec_meta_host.numpy()
+            hv[2 * self.ecfg.max_batch:3 * self.ecfg.max_batch] = -1  # no KV writes for padding rows
+            self.dec_meta.copy_(self.dec_meta_host, non_blocking=True)
+            for B in self._buckets:
+                self._decode_forward(B)
+            self.stream.synchronize()
+            gemm.check_status(self.device)
+            if self.ecfg.use_cuda_graph:
+                for B in self._buckets:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=self.stream):
+                        self._decode_forward(B)
+                    self._graphs[B] = g
+            self.stream.synchronize()
+
+    def _admit_prefill(self) -> tuple[list[tuple[Sequence, int]], int]:
+        """Chooses the sequences (and token counts) of the next prefill chunk."""
+        e = self.ecfg
+        budget, chosen = e.prefill_chunk, []
+        for s in list(self.prefilling):
+            if budget <= 0 or len(chosen) >= e.max_prefill_seqs:
+                break
+            n = min(len(s.prompt) - s.computed, budget)
+            chosen.append((s, n))
+            budget -= n
+        while self.waiting and budget > 0 and len(chosen) < e.max_prefill_seqs:
+            if len(self.running) + len(self.prefilling) >= e.max_batch:
+                break
+            s = self.waiting[0]
+            need = self.kv.pages_needed(s.seq_id, len(s.prompt) + 1)
+            if need > self.kv.allocator.free_pages:
+                break
+            self.waiting.popleft()
+            self.kv.ensure(s.seq_id, len(s.prompt) + 1)
+            self.prefilling.append(s)
+            n = min(len(s.prompt), budget)
+            chosen.append((s, n))
+            budget -= n
+        return chosen, e.prefill_chunk - budget
+
+    def _step_prefill(self, chosen: list[tuple[Sequence, int]], rows: int) -> list[tuple[Sequence, int]]:
+        e, P, S = self.ecfg, self.ecfg.prefill_chunk, self.ecfg.max_prefill_seqs
+        hv = self.pre_meta_host.numpy()
+        b = 3 * P
+        r = 0
+        ps = e.page_size
+        for i, (s, n) in enumerate(chosen):
+            toks = s.prompt[s.computed:s.computed + n]
+            hv[r:r + n] = toks
+            for j in range(n):
+                p = s.computed + j
+                hv[P + r + j] = p
+            t = self.kv.tables[s.seq_id]
+            base = s.computed
+            for j in range(n):
+                p = base + j
+                hv[2 * P + r + j] = t[p // ps] * ps + p % ps
+            hv[b + i] = r
+            hv[b + S + i] = n
+            hv[b + 2 * S + i] = s.computed
+            hv[b + 3 * S + i] = r + n - 1
+            tb = b + 4 * S + i * self.max_blocks
+            hv[tb:tb + len(t)] = t
+            r += n
+        with torch.cuda.stream(self.stream):
+            self.pre_meta.copy_(self.pre_meta_host, non_blocking=True)
+            self._prefill_forward(rows, len(chosen), max(n for _, n in chosen))
+            self.tokens_host[:len(chosen)].copy_(self.tokens[:len(chosen)], non_blocking=True)
+            self.stream.synchronize()
+        self.stats["prefill_steps"] += 1
+        self.stats["h2d_bytes"] += self._pre_words * 4
+        self.stats["d2h_bytes"] += len(chosen) * 4
+        now = time.monotonic()
+        out = []
+        th = self.tokens_host.numpy()
+        for i, (s, n) in enumerate(chosen):
+            s.computed += n
+            if s.prefill_done:
+                tok = int(th[i])
+                s.generated.append(tok)
+                s.first_token_time = now
+                s.token_times.append(now)
+                self.prefilling.remove(s)
+                out.append((s, tok))
+                if s.finished:
+                    self._finish(s, now)
+                else:
+                    self.running.append(s)
+        return out
+
+    def _finish(self, s: Sequence, now: float) -> None:
+        s.finish_time = now
+        self.kv.release(s.seq_id)
+
+    def _step_decode(self) -> list[tuple[Sequence, int]]:
+        e = self.ecfg
+        batch = self.running[:e.max_batch]
+        # every sequence needs a slot for the token it is about to cache
+        kept = []
+        for s in batch:
+            try:
+                self.kv.ensure(s.seq_id, s.total_len)
+                kept.append(s)
+            except OutOfPages:
+                self._retract(s)
+        batch = kept
+        n = len(batch)
+        if n == 0:
+            return []
+        B = self._bucket(n)
+        cap, ps = e.max_batch, e.page_size
+        hv = self.dec_meta_host.numpy()
+        hv[0:B] = 0
+        hv[cap:cap + B] = 0
+        hv[2 * cap:2 * cap + B] = -1
+        hv[3 * cap:3 * cap + B] = 0
+        for i, s in enumerate(batch):
+            p = s.total_len - 1  # position of the token fed in
+            t = self.kv.tables[s.seq_id]
+            hv[i] = s.generated[-1]
+            hv[cap + i] = p
+            hv[2 * cap + i] = t[p // ps] * ps + p % ps
+            hv[3 * cap + i] = p + 1
+            tb = 4 * cap + i * self.max_blocks
+            hv[tb:tb + len(t)] = t
+        with torch.cuda.stream(self.stream):
+            self.dec_meta.copy_(self.dec_meta_host, non_blocking=True)
+            g = self._graphs.get(B)
+            if g is not None:
+                g.replay()
+            else:
+                self._decode_forward(B)
+            self.tokens_host[:n].copy_(self.tokens[:n], non_blocking=True)
+            self.stream.synchronize()
+        self.stats["decode_steps"] += 1
+        self.stats["h2d_bytes"] += self._dec_words * 4
+        self.stats["d2h_bytes"] += n * 4
+        now = time.monotonic()
+        th = self.tokens_host.numpy()
+        out = []
+        for i, s in enumerate(batch):
+            tok = int(th[i])
+            s.computed = s.total_len
+            s.generated.append(tok)
+            s.token_times.append(now)
+            out.append((s, tok))
+            if s.finished:
+                self.running.remove(s)
+                self._finish(s, now)
+        return out
+
+    def _retract(self, s: Sequence) -> None:
+        """Gives the sequence's pages back and queues it for recomputation (prompt + generated)."""
+        self.running.remove(s)
+        self.kv.release(s.seq_id)
+        s.prompt = s.prompt + s.generated
+        s.max_new_tokens -= len(s.generated)
+        s.generated = []
+        s.computed = 0
+        self.waiting.appendleft(s)
+
+    def step(self) -> list[tuple[Sequence, int]]:
+        """One engine iteration: a prefill chunk or a decode step. Returns (sequence, token) pairs."""
+        want_prefill = bool(self.waiting or self.prefilling)
+        if want_prefill and (not self.running or not self._last_was_prefill):
+            chosen, rows = self._admit_prefill()
+            if chosen:
+                self._last_was_prefill = True
+                return self._step_prefill(chosen, rows)
+        self._last_was_prefill = False
+        if self.running:
+            return self._step_decode()
+        return []
+
+    def generate(self, prompts: list[list[int]], max_new_tokens: int) -> list[list[int]]:
+        """Convenience: run the given prompts to completion, return generated ids per prompt."""
+        seqs = [self.add_request(p, max_new_tokens) for p in prompts]
+        while self.has_work:
+            self.step()
+        return [s.generated for s in seqs]

@@ -1,0 +1,39 @@
+"""Loopback FFN port: the layer's FFN runs in-stream on the attention GPU.
+
+Used when one GPU hosts both roles (kernels that wait on one another must never be separate
+launches on one GPU, so the loopback path is stream-ordered and flag-free). Dense layers are two
+launches: gate/up GEMM with the SwiGLU epilogue, then the down projection.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.weights import FfnLayerWeights
+from ..ops import gemm
+from .atn_engine import FfnPort
+
+
+class LocalFfnPort(FfnPort):
+    def __init__(self, cfg: ModelConfig, weights: list[FfnLayerWeights]):
+        self.cfg, self.weights = cfg, weights
+        self.act = None
+        self.y = None
+
+    def attach(self, engine) -> None:
+        inter = max(w.gate_up.shape[-2] // 2 for w in self.weights)
+        self.act = torch.zeros(engine.cap, inter, dtype=torch.bfloat16, device=engine.device)
+        self.y = torch.zeros(engine.cap, self.cfg.hidden_size, dtype=torch.bfloat16, device=engine.device)
+
+    def run(self, layer: int, x: torch.Tensor, rows: int, mode: int) -> list[torch.Tensor]:
+        w = self.weights[layer]
+        if w.is_moe:
+            from ..ops import moe
+
+            return [moe.moe_forward(x, w, self.cfg, out=self.y[:rows])]
+        inter = w.gate_up.shape[0] // 2
+        act = self.act[:rows, :inter]
+        gemm.gateup_swiglu(x, w.gate_up, out=act, bias=w.gate_up_bias)
+        gemm.linear(act, w.down, out=self.y[:rows], bias=w.down_bias)
+        return [self.y[:rows]]

@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 7
+EXPECTED_ABI = 8
 HERE = Path(__file__).resolve().parent
 
 
@@ -51,6 +51,7 @@ class GemmArgs(C.Structure):
         ("bn", C.c_int),
         ("num_sms", C.c_int),
         ("w_evict_first", C.c_int),
+        ("w_tiled", C.c_int),
         ("gate_limit", C.c_float),
         ("up_add", C.c_float),
         ("act_alpha", C.c_float),

@@ -59,10 +59,38 @@ def check_status(device: torch.device) -> None:
         raise RuntimeError(f"xpool kernel reported device status {code}")
 
 
+class TiledWeight:
+    """A weight matrix ``[n, k]`` stored as contiguous 128x64 tiles (tile index = row_tile * k_tiles +
+    k_tile). One TMA box then reads one 16 KB run of HBM instead of 128 separate 128-byte pieces of
+    128 different rows, which is what a weight-streaming (decode) GEMM needs to approach the
+    memory roofline. Built once at load time with :func:`tile_weight`."""
+
+    __slots__ = ("data", "shape", "dtype", "device")
+
+    def __init__(self, data: torch.Tensor, n: int, k: int):
+        self.data, self.shape, self.dtype, self.device = data, (n, k), data.dtype, data.device
+
+    def data_ptr(self) -> int:
+        return self.data.data_ptr()
+
+    def untiled(self) -> torch.Tensor:
+        n, k = self.shape
+        return self.data.view(n // 128, k // 64, 128, 64).permute(0, 2, 1, 3).reshape(n, k)
+
+
+def tile_weight(w: torch.Tensor) -> TiledWeight:
+    n, k = w.shape
+    if n % 128 or k % 64:
+        raise ValueError(f"cannot tile a {n}x{k} weight into 128x64 blocks")
+    t = w.view(n // 128, 128, k // 64, 64).permute(0, 2, 1, 3).contiguous()
+    return TiledWeight(t.view(-1), n, k)
+
+
 def _args(x, w, out, *, n_out, rows, epilogue, dual=0, up_offset=0, bias=None, resid=None, splits=0, bn=0,
           num_sms=0, evict_first=None, gate_limit=0.0, up_add=0.0, act_alpha=0.0) -> native.GemmArgs:
+    tiled = isinstance(w, TiledWeight)
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-    assert x.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1
+    assert x.stride(-1) == 1 and out.stride(-1) == 1 and (tiled or w.stride(-1) == 1)
     k = x.shape[-1]
     assert w.shape[-1] == k, (w.shape, x.shape)
     s = scratch(x.device)
@@ -82,7 +110,8 @@ def _args(x, w, out, *, n_out, rows, epilogue, dual=0, up_offset=0, bias=None, r
     a.n_out = n_out
     a.k = k
     a.rows = rows
-    a.ldw = w.stride(0)
+    a.ldw = k if tiled else w.stride(0)
+    a.w_tiled = int(tiled)
     a.ldx = x.stride(0)
     a.ld_out = out.stride(0)
     a.ld_resid = resid.stride(0) if resid is not None else 0

@@ -1,0 +1,79 @@
+"""Configuration registry: sources, precedence, validation."""
+import pytest
+
+from crosspool_b200 import config as C
+
+TOML = """
+cache_root = "/tmp/cache"
+[daemon]
+port = 9999
+[logging]
+level = "warning"
+[atn]
+devices = [0, 1]
+[ffn]
+devices = [2, 3, 4]
+[ffn.loader]
+parallelism = 8
+[scheduler]
+ffn_concurrency = 2
+ffn_policy = "random"
+[scheduler.slo]
+ttft_ms = 1000
+tbt_ms = 50
+[[models]]
+id = "Qwen/Qwen3-8B"
+path = "/models/q8"
+atn_tp_size = 2
+ffn_tp_size = 2
+[[models]]
+id = "Qwen/Qwen3-0.6B"
+slo = { ttft_ms = 500, tbt_ms = 20 }
+"""
+
+
+def test_precedence_cli_over_env_over_toml_over_default():
+    cfg = C.load_config(cli={"logging_level": "debug"}, env={"XPOOL_LOG_LEVEL": "error",
+                        "XPOOL_FFN_LOADER_PARALLELISM": "16"}, toml_text=TOML)
+    assert cfg.logging_level == "debug" and cfg.sources["logging_level"] == "cli"
+    assert cfg.ffn_loader_parallelism == 16 and cfg.sources["ffn_loader_parallelism"] == "env"
+    assert cfg.daemon_port == 9999 and cfg.sources["daemon_port"] == "toml"
+    assert cfg.daemon_host == "127.0.0.1" and cfg.sources["daemon_host"] == "default"
+    assert cfg.atn_devices == (0, 1) and cfg.ffn_devices == (2, 3, 4)
+    assert cfg.scheduler_ffn_policy == "random" and cfg.scheduler_ffn_concurrency == 2
+
+
+def test_models_and_slo_overrides():
+    cfg = C.load_config(env={}, toml_text=TOML)
+    assert [m.id for m in cfg.models] == ["Qwen/Qwen3-8B", "Qwen/Qwen3-0.6B"]
+    assert cfg.ffn_tp_for("Qwen/Qwen3-8B") == 2
+    assert cfg.ffn_tp_for("Qwen/Qwen3-0.6B") == 3  # default: all FFN devices
+    assert cfg.slo_for("Qwen/Qwen3-8B") == C.Slo(1000, 50)
+    assert cfg.slo_for("Qwen/Qwen3-0.6B") == C.Slo(500, 20)
+
+
+def test_digest_is_stable_and_sensitive():
+    a = C.load_config(env={}, toml_text=TOML)
+    b = C.load_config(env={}, toml_text=TOML)
+    c = C.load_config(env={}, toml_text=TOML.replace("9999", "9998"))
+    assert a.digest() == b.digest() != c.digest()
+
+
+@pytest.mark.parametrize("bad,msg", [
+    (TOML.replace("devices = [2, 3, 4]", "devices = [1, 2]"), "both"),
+    (TOML.replace("[scheduler.slo]\nttft_ms = 1000\ntbt_ms = 50", ""), "scheduler.slo"),
+    (TOML.replace('ffn_policy = "random"', 'ffn_policy = "lifo"'), "ffn_policy"),
+    (TOML.replace("atn_tp_size = 2", "atn_tp_size = 2\natn_dp_size = 2"), "TP-by-DP"),
+    (TOML.replace('id = "Qwen/Qwen3-0.6B"', 'id = "Qwen/Qwen3-8B"'), "duplicate"),
+    (TOML.replace("port = 9999", "port = 0"), "daemon.port"),
+])
+def test_rejections(bad, msg):
+    with pytest.raises(C.ConfigError, match=msg):
+        C.load_config(env={}, toml_text=bad)
+
+
+def test_observer_env_switches():
+    cfg = C.load_config(env={"XPOOL_DEBUG_FABRIC_OBSERVER_ENABLE": "1",
+                             "XPOOL_DEBUG_FABRIC_OBSERVER_RECORD_CAPACITY": "128"}, toml_text=TOML)
+    assert cfg.debug_fabric_observer_enable is True and cfg.debug_fabric_observer_record_capacity == 128
+    assert cfg.debug_graph_observer_enable is False

@@ -1,0 +1,84 @@
+"""Single-GPU loopback engine against the monolithic PyTorch forward."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _build(preset, layers=None, **ecfg):
+    from crosspool_b200.engine.atn_engine import AttentionEngine, EngineConfig
+    from crosspool_b200.engine.ffn_local import LocalFfnPort
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.models.reference import ReferenceModel
+    from crosspool_b200.models.weights import random_attention_weights, random_ffn_weights
+
+    cfg = mc.preset(preset)
+    if layers:
+        cfg = cfg.with_layers(layers)
+    aw = random_attention_weights(cfg, 1, "cuda", torch.bfloat16)
+    fw = random_ffn_weights(cfg, 1, "cuda", torch.bfloat16)
+    eng = AttentionEngine(cfg, aw, LocalFfnPort(cfg, fw), EngineConfig(**ecfg))
+    return cfg, eng, ReferenceModel(cfg, aw, fw)
+
+
+def _kl(p_logits, q_logits):
+    p = p_logits.float().log_softmax(-1)
+    q = q_logits.float().log_softmax(-1)
+    return (p.exp() * (p - q)).sum(-1)
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_loopback_engine_matches_reference_logits(graph):
+    cfg, eng, ref = _build("Qwen/Qwen3-0.6B", layers=4, max_batch=8, prefill_chunk=256, max_seq_len=512,
+                           use_cuda_graph=graph)
+    eng.warmup()
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 33, 70, 128)]
+    seqs = [eng.add_request(p, 6) for p in prompts]
+    logits_per_step = {s.seq_id: [] for s in seqs}
+    while eng.has_work:
+        done = eng.step()
+        for i, (s, tok) in enumerate(done):
+            logits_per_step[s.seq_id].append(eng.logits[i].clone())
+    from crosspool_b200.ops import gemm
+    gemm.check_status(eng.device)
+    for s, p in zip(seqs, prompts):
+        toks, ref_logits = ref.generate(torch.tensor(p, device="cuda"), 6)
+        got = torch.stack(logits_per_step[s.seq_id])
+        # feed the reference the engine's own tokens when they diverge is not needed: compare
+        # step by step only while the greedy paths agree
+        agree = 0
+        for a, b in zip(s.generated, toks):
+            if a != b:
+                break
+            agree += 1
+        assert agree >= 1
+        kl = _kl(ref_logits[:agree], got[:agree])
+        # acceptance limits of the reference: 0.05 nats prefill, 0.001 nats decode
+        assert kl[0].item() <= 0.05
+        if agree > 1:
+            assert kl[1:].max().item() <= 0.005
+
+
+def test_chunked_prefill_equals_single_chunk():
+    cfg, eng_small, _ = _build("Qwen/Qwen3-0.6B", layers=2, max_batch=4, prefill_chunk=64, max_seq_len=512,
+                               use_cuda_graph=False)
+    _, eng_big, _ = _build("Qwen/Qwen3-0.6B", layers=2, max_batch=4, prefill_chunk=512, max_seq_len=512,
+                           use_cuda_graph=False)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (200, 45)]
+    a = eng_small.generate(prompts, 4)
+    b = eng_big.generate(prompts, 4)
+    assert a == b
+
+
+def test_pages_are_returned_and_batches_pad_to_buckets():
+    cfg, eng, _ = _build("Qwen/Qwen3-0.6B", layers=2, max_batch=8, prefill_chunk=128, max_seq_len=256)
+    eng.warmup()
+    free0 = eng.kv.allocator.free_pages
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (3, 17, 40)]
+    out = eng.generate(prompts, 5)
+    assert [len(o) for o in out] == [5, 5, 5]
+    assert eng.kv.allocator.free_pages == free0
+    assert eng.stats["decode_steps"] >= 4 and eng.stats["prefill_steps"] >= 1

@@ -97,3 +97,17 @@ def test_repeated_calls_are_bitwise_stable():
     b = gemm.linear(x, w, splits=4)
     torch.cuda.synchronize()
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("rows", [4, 100, 600])
+def test_tiled_weight_layout_gives_identical_results(rows):
+    from crosspool_b200.ops import gemm
+
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    x = (torch.randn(rows, 1024, device="cuda", generator=g) * 0.5).bfloat16()
+    w = (torch.randn(768, 1024, device="cuda", generator=g) * 0.05).bfloat16()
+    wt = gemm.tile_weight(w)
+    assert torch.equal(wt.untiled(), w)
+    assert torch.equal(gemm.linear(x, wt), gemm.linear(x, w))
+    assert torch.equal(gemm.gateup_swiglu(x, wt), gemm.gateup_swiglu(x, w))
+    gemm.check_status(x.device)
