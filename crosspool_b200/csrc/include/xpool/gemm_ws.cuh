@@ -74,6 +74,7 @@ struct Problem {
   float gate_limit;           // > 0: clamp gate from above and up to [-limit, limit]
   float up_add;               // added to up before the product (0 for plain SwiGLU)
   float act_alpha;            // 0: silu(g); else g * sigmoid(alpha * g)
+  uint64_t* trace;            // pipeline observer (CTA 0 only): 3 timestamps per K block, or null
 };
 
 struct SmemLayout {
@@ -204,6 +205,8 @@ __device__ __forceinline__ bool produce_tile(const Problem& p, const TileCoord& 
       if (p.dual) sm100::tma_load_2d(a + kTileM * kTileK * 2, p.tmap_w, &bar->full[st.stage], wc0, uc1);
     }
     sm100::tma_load_2d(b, p.tmap_x, &bar->full[st.stage], kb * kTileK, c.n0);
+    if (p.trace != nullptr && blockIdx.x == 0 && kb - c.kb0 < 256)
+      p.trace[3 * (kb - c.kb0)] = sm100::global_timer_ns();
     st.advance(L.stages);
   }
   return true;
@@ -235,6 +238,7 @@ __device__ __forceinline__ bool mma_tile(const Problem& p, const TileCoord& c, c
   for (int i = 0; i < c.kbn; ++i) {
     if (!sm100::mbar_wait(&bar->full[st.stage], st.phase, deadline)) return false;
     sm100::tc_fence_after_sync();
+    if (p.trace != nullptr && blockIdx.x == 0 && i < 256) p.trace[3 * i + 1] = sm100::global_timer_ns();
     uint8_t* a = tiles + static_cast<size_t>(st.stage) * L.stage_bytes;
     const uint32_t a_addr = sm100::smem_u32(a);
     const uint32_t b_addr = a_addr + L.a_bytes;
@@ -249,6 +253,7 @@ __device__ __forceinline__ bool mma_tile(const Problem& p, const TileCoord& c, c
       if (p.dual) sm100::umma_bf16(tmem_acc + p.bn, du + koff, db + koff, idesc, accum);
     }
     sm100::umma_commit(&bar->empty[st.stage]);  // frees the stage when these MMAs retire
+    if (p.trace != nullptr && blockIdx.x == 0 && i < 256) p.trace[3 * i + 2] = sm100::global_timer_ns();
     st.advance(L.stages);
   }
   sm100::umma_commit(&bar->acc_full[st.acc]);
@@ -344,15 +349,23 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
       for (int col = 0; col < p.bn; col += 16) {
         if (c.n0 + col >= p.rows) break;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float sg = 0.f, su = 0.f;
-          for (int s = 0; s < p.splits; ++s) {
-            const float* w = base + static_cast<size_t>(s) * acc_cols * kTileM;
-            sg += __ldcg(&w[static_cast<size_t>(col + j) * kTileM + lane_in_tile]);
-            if (p.dual) su += __ldcg(&w[static_cast<size_t>(p.bn + col + j) * kTileM + lane_in_tile]);
+        for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
+        // Split order is the summation order (deterministic); the 16 (or 32)
+        // loads of one split are independent so that they overlap in flight.
+        for (int s = 0; s < p.splits; ++s) {
+          const float* w = base + static_cast<size_t>(s) * acc_cols * kTileM + lane_in_tile;
+          float tg[16], tu[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) tg[j] = __ldcg(&w[static_cast<size_t>(col + j) * kTileM]);
+          if (p.dual) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) tu[j] = __ldcg(&w[static_cast<size_t>(p.bn + col + j) * kTileM]);
           }
-          g[j] = sg;
-          u[j] = su;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            g[j] += tg[j];
+            if (p.dual) u[j] += tu[j];
+          }
         }
         epilogue_store16(p, f, c.n0 + col, g, u);
       }

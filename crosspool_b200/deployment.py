@@ -1,0 +1,121 @@
+"""Public serving API: a set of co-located Instances stepped together.
+
+``Deployment`` is what a user (and ``bench.py``) drives: add requests per model, call ``step()``,
+read tokens. Each Instance is an :class:`AttentionEngine` whose FFN port decides where the FFN runs:
+
+* :func:`build_loopback` — every role on one GPU, FFNs in-stream (1-GPU deployments);
+* :func:`crosspool_b200.parallel.fabric.build_rank` — one process per GPU under ``torchrun``,
+  attention ranks and FFN ranks connected by peer memory.
+
+``step()`` launches one iteration of every Instance before collecting any of them, so Instances
+overlap on the GPU(s): while one model's step waits for its FFN, another model's attention runs.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from .engine.atn_engine import AttentionEngine, EngineConfig, Sequence
+from .engine.ffn_local import LocalFfnPort
+from .models import config as model_config
+from .models.config import ModelConfig
+from .models.weights import random_attention_weights, random_ffn_weights
+
+
+@dataclass
+class InstanceHandle:
+    model_id: str
+    cfg: ModelConfig
+    engine: AttentionEngine
+
+
+@dataclass
+class StepResult:
+    tokens: dict[str, list[tuple[Sequence, int]]] = field(default_factory=dict)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(len(v) for v in self.tokens.values())
+
+
+class Deployment:
+    def __init__(self, instances: list[InstanceHandle]):
+        self.instances = instances
+        self._by_id = {i.model_id: i for i in instances}
+
+    def instance(self, model_id: str) -> InstanceHandle:
+        return self._by_id[model_id]
+
+    def warmup(self) -> None:
+        for i in self.instances:
+            i.engine.warmup()
+
+    def add_request(self, model_id: str, prompt: list[int], max_new_tokens: int, arrival: float | None = None
+                    ) -> Sequence:
+        return self._by_id[model_id].engine.add_request(prompt, max_new_tokens, arrival)
+
+    @property
+    def has_work(self) -> bool:
+        return any(i.engine.has_work for i in self.instances)
+
+    def step(self) -> StepResult:
+        """One iteration of every Instance that has work."""
+        active = [i for i in self.instances if i.engine.has_work]
+        for i in active:
+            i.engine.launch_step()
+        res = StepResult()
+        for i in active:
+            res.tokens[i.model_id] = i.engine.collect_step()
+        return res
+
+    def run_until_idle(self, max_steps: int = 1 << 30) -> int:
+        n = 0
+        while self.has_work and n < max_steps:
+            self.step()
+            n += 1
+        return n
+
+    def stats(self) -> dict:
+        out = {"h2d_bytes": 0, "d2h_bytes": 0, "launches": 0, "decode_steps": 0, "prefill_steps": 0}
+        for i in self.instances:
+            for k in out:
+                out[k] += i.engine.stats[k]
+        return out
+
+
+def build_loopback(models: list[tuple[str, str | ModelConfig, int]], ecfg: EngineConfig | None = None,
+                   device: str | torch.device = "cuda", tile_weights: bool = False) -> Deployment:
+    """``models`` = [(instance id, preset name or ModelConfig, seed)]; random-init weights."""
+    from .ops import gemm
+
+    handles = []
+    for model_id, preset, seed in models:
+        cfg = preset if isinstance(preset, ModelConfig) else model_config.load(preset)
+        aw = random_attention_weights(cfg, seed, device, torch.bfloat16)
+        fw = random_ffn_weights(cfg, seed, device, torch.bfloat16)
+        if tile_weights:
+            for l in fw:
+                if not l.is_moe:
+                    l.gate_up, l.down = gemm.tile_weight(l.gate_up), gemm.tile_weight(l.down)
+        eng = AttentionEngine(cfg, aw, LocalFfnPort(cfg, fw), ecfg, device)
+        handles.append(InstanceHandle(model_id, cfg, eng))
+    return Deployment(handles)
+
+
+def percentile(values: list[float], p: float) -> float:
+    """Linear-rank percentile ``(n - 1) * p / 100`` (the reference's definition,
+    src/xpool-dev/xbench/harness/serving/measure.py:431-460)."""
+    if not values:
+        return float("nan")
+    v = sorted(values)
+    r = (len(v) - 1) * p / 100.0
+    lo = int(r)
+    hi = min(lo + 1, len(v) - 1)
+    return v[lo] + (v[hi] - v[lo]) * (r - lo)
+
+
+def now() -> float:
+    return time.monotonic()

@@ -119,6 +119,11 @@ class AttentionEngine:
         self._last_was_prefill = False
         self.stats = {"prefill_steps": 0, "decode_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0, "launches": 0}
         self.stream = torch.cuda.Stream(self.device)
+        self._b_key = None
+        self._b_pos = None
+        self._b_last = None
+        self._inflight = None
+        self._graph_launches: dict[int, int] = {}
         port.attach(self)
 
     # ------------------------------------------------------------------ buffers
@@ -193,7 +198,6 @@ class AttentionEngine:
                 norm.add_rmsnorm([self.o[:rows]], lw.post_attn_norm, cfg.rms_norm_eps, resid=resid, out=x2,
                                  want_local=False, **tgt)
             parts = self.port.run(l, x2, rows, mode)
-            self.stats["launches"] += 7
         self._parts = parts
 
     def _head(self, rows: int, n_sel: int, sel_idx: torch.Tensor | None) -> None:
@@ -263,10 +267,14 @@ class AttentionEngine:
             self.stream.synchronize()
             gemm.check_status(self.device)
             if self.ecfg.use_cuda_graph:
+                from .. import native
+
                 for B in self._buckets:
                     g = torch.cuda.CUDAGraph()
+                    before = native.launch_count()
                     with torch.cuda.graph(g, stream=self.stream):
                         self._decode_forward(B)
+                    self._graph_launches[B] = native.launch_count() - before
                     self._graphs[B] = g
             self.stream.synchronize()
 
@@ -349,10 +357,38 @@ class AttentionEngine:
         s.finish_time = now
         self.kv.release(s.seq_id)
 
-    def _step_decode(self) -> list[tuple[Sequence, int]]:
+    def _decode_prepare(self) -> tuple[list[Sequence], int] | None:
+        """Fills the pinned decode metadata for the next step. When the batch membership did not
+        change since the previous step only the per-token fields advance (vectorised); the block
+        table gets a new entry only for sequences that cross into a fresh page."""
+        import numpy as np
+
         e = self.ecfg
+        cap, ps = e.max_batch, e.page_size
+        hv = self.dec_meta_host.numpy()
         batch = self.running[:e.max_batch]
-        # every sequence needs a slot for the token it is about to cache
+        key = tuple(s.seq_id for s in batch)
+        if key and key == self._b_key:
+            n = len(batch)
+            pos = self._b_pos
+            pos += 1
+            for i in np.nonzero(pos % ps == 0)[0]:
+                s = batch[int(i)]
+                try:
+                    t = self.kv.ensure(s.seq_id, int(pos[i]) + 1)
+                except OutOfPages:
+                    self._b_key = None
+                    self._retract(s)
+                    return self._decode_prepare()
+                hv[4 * cap + int(i) * self.max_blocks + int(pos[i]) // ps] = t[-1]
+            B = self._bucket(n)
+            table = hv[4 * cap:4 * cap + n * self.max_blocks].reshape(n, self.max_blocks)
+            hv[0:n] = self._b_last
+            hv[cap:cap + n] = pos
+            hv[2 * cap:2 * cap + n] = table[np.arange(n), pos // ps] * ps + pos % ps
+            hv[3 * cap:3 * cap + n] = pos + 1
+            return batch, B
+        # slow path: membership changed
         kept = []
         for s in batch:
             try:
@@ -363,23 +399,34 @@ class AttentionEngine:
         batch = kept
         n = len(batch)
         if n == 0:
-            return []
+            self._b_key = None
+            return None
         B = self._bucket(n)
-        cap, ps = e.max_batch, e.page_size
-        hv = self.dec_meta_host.numpy()
         hv[0:B] = 0
         hv[cap:cap + B] = 0
         hv[2 * cap:2 * cap + B] = -1
         hv[3 * cap:3 * cap + B] = 0
+        pos = np.empty(n, dtype=np.int32)
         for i, s in enumerate(batch):
             p = s.total_len - 1  # position of the token fed in
             t = self.kv.tables[s.seq_id]
+            pos[i] = p
             hv[i] = s.generated[-1]
             hv[cap + i] = p
             hv[2 * cap + i] = t[p // ps] * ps + p % ps
             hv[3 * cap + i] = p + 1
             tb = 4 * cap + i * self.max_blocks
             hv[tb:tb + len(t)] = t
+        self._b_key = tuple(s.seq_id for s in batch)
+        self._b_pos = pos
+        return batch, B
+
+    def _decode_launch(self) -> bool:
+        prep = self._decode_prepare()
+        if prep is None:
+            return False
+        batch, B = prep
+        n = len(batch)
         with torch.cuda.stream(self.stream):
             self.dec_meta.copy_(self.dec_meta_host, non_blocking=True)
             g = self._graphs.get(B)
@@ -388,23 +435,37 @@ class AttentionEngine:
             else:
                 self._decode_forward(B)
             self.tokens_host[:n].copy_(self.tokens[:n], non_blocking=True)
-            self.stream.synchronize()
+        self._inflight = (batch, n)
         self.stats["decode_steps"] += 1
         self.stats["h2d_bytes"] += self._dec_words * 4
         self.stats["d2h_bytes"] += n * 4
+        self.stats["launches"] += self._graph_launches.get(B, 0)
+        return True
+
+    def _decode_collect(self) -> list[tuple[Sequence, int]]:
+        batch, n = self._inflight
+        self._inflight = None
+        self.stream.synchronize()
         now = time.monotonic()
-        th = self.tokens_host.numpy()
+        toks = self.tokens_host[:n].numpy().copy()
+        self._b_last = toks
         out = []
-        for i, s in enumerate(batch):
-            tok = int(th[i])
+        changed = False
+        for s, tok in zip(batch, toks.tolist()):
             s.computed = s.total_len
             s.generated.append(tok)
             s.token_times.append(now)
             out.append((s, tok))
-            if s.finished:
+            if len(s.generated) >= s.max_new_tokens:
                 self.running.remove(s)
                 self._finish(s, now)
+                changed = True
+        if changed:
+            self._b_key = None
         return out
+
+    def _step_decode(self) -> list[tuple[Sequence, int]]:
+        return self._decode_collect() if self._decode_launch() else []
 
     def _retract(self, s: Sequence) -> None:
         """Gives the sequence's pages back and queues it for recomputation (prompt + generated)."""
@@ -416,18 +477,35 @@ class AttentionEngine:
         s.computed = 0
         self.waiting.appendleft(s)
 
-    def step(self) -> list[tuple[Sequence, int]]:
-        """One engine iteration: a prefill chunk or a decode step. Returns (sequence, token) pairs."""
+    def launch_step(self) -> None:
+        """Starts one engine iteration (a prefill chunk or a decode step) without waiting for the
+        GPU, so that a driver of several co-located Instances can overlap them; ``collect_step``
+        finishes it. Prefill chunks complete inside this call."""
+        self._pending: list[tuple[Sequence, int]] | None = None
         want_prefill = bool(self.waiting or self.prefilling)
         if want_prefill and (not self.running or not self._last_was_prefill):
             chosen, rows = self._admit_prefill()
             if chosen:
                 self._last_was_prefill = True
-                return self._step_prefill(chosen, rows)
+                self._b_key = None
+                self._pending = self._step_prefill(chosen, rows)
+                return
         self._last_was_prefill = False
-        if self.running:
-            return self._step_decode()
+        if self.running and not self._decode_launch():
+            self._pending = []
+
+    def collect_step(self) -> list[tuple[Sequence, int]]:
+        if self._pending is not None:
+            out, self._pending = self._pending, None
+            return out
+        if self._inflight is not None:
+            return self._decode_collect()
         return []
+
+    def step(self) -> list[tuple[Sequence, int]]:
+        """One engine iteration. Returns the (sequence, token) pairs it produced."""
+        self.launch_step()
+        return self.collect_step()
 
     def generate(self, prompts: list[list[int]], max_new_tokens: int) -> list[list[int]]:
         """Convenience: run the given prompts to completion, return generated ids per prompt."""

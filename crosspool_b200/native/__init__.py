@@ -34,6 +34,7 @@ class GemmArgs(C.Structure):
         ("counters", C.c_void_p),
         ("status", C.c_void_p),
         ("stream", C.c_void_p),
+        ("trace", C.c_void_p),
         ("ws_bytes", C.c_size_t),
         ("counter_bytes", C.c_size_t),
         ("w_rows_total", C.c_int),
@@ -138,9 +139,20 @@ def kernels_available() -> bool:
     return (HERE / "libxpool_kernels.so").exists()
 
 
-def check(rc: int, what: str) -> None:
+_launches = 0
+
+
+def check(rc: int, what: str, kernels_launched: int = 1) -> None:
+    """Raises on a non-zero native return code; counts the kernels the call launched."""
+    global _launches
     if rc != 0:
         raise NativeLibraryError(f"{what} failed with code {rc}")
+    _launches += kernels_launched
+
+
+def launch_count() -> int:
+    """Kernels of this library launched (or captured into a graph) so far by this process."""
+    return _launches
 
 
 class RopeArgs(C.Structure):

@@ -61,7 +61,8 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     a.batch, a.q_heads, a.kv_heads, a.head_dim = batch, q_heads, kv_heads, d
     a.page_size, a.max_blocks, a.num_splits = page_size, block_table.stride(0), num_splits
     a.scale = scale if scale is not None else d ** -0.5
-    native.check(native.kernels().xp_decode_attn(C.byref(a), _stream(q.device)), "xp_decode_attn")
+    native.check(native.kernels().xp_decode_attn(C.byref(a), _stream(q.device)), "xp_decode_attn",
+                 2 if num_splits > 1 else 1)
     return out
 
 
