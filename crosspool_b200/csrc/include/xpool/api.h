@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 8
+#define XP_ABI_VERSION 10
 
 #ifdef __cplusplus
 extern "C" {
@@ -24,7 +24,6 @@ typedef struct XpGemmArgs {
   uint32_t* counters;  /* split-K tile counters, zeroed once by the caller */
   uint32_t* status;    /* optional device word; first non-zero error code wins */
   void* stream;        /* cudaStream_t */
-  uint64_t* trace;     /* optional pipeline observer buffer: 768 words (CTA 0, 256 K blocks x 3) */
   size_t ws_bytes;
   size_t counter_bytes;
   int w_rows_total;    /* 0: derived from n_out / up_offset */

@@ -74,7 +74,6 @@ struct Problem {
   float gate_limit;           // > 0: clamp gate from above and up to [-limit, limit]
   float up_add;               // added to up before the product (0 for plain SwiGLU)
   float act_alpha;            // 0: silu(g); else g * sigmoid(alpha * g)
-  uint64_t* trace;            // pipeline observer (CTA 0 only): 3 timestamps per K block, or null
 };
 
 struct SmemLayout {
@@ -177,38 +176,73 @@ __device__ __forceinline__ TileCoord tile_coord(const Problem& p, int t) {
 }
 
 // ---------------------------------------------------------------- producer
+//
+// The producer and the MMA issuer are single threads; nothing hides the latency
+// of their scalar instructions, so the per-K-block bookkeeping is kept to a few
+// adds: shared-memory addresses, barrier addresses, TMA coordinates and UMMA
+// descriptors all advance incrementally (a tcgen05.mma of N <= 32 retires in
+// about 45 cycles, four of them per K block).
 
 __device__ __forceinline__ bool produce_tile(const Problem& p, const TileCoord& c,
                                              const SmemLayout& L, uint8_t* tiles, Barriers* bar,
                                              PipeState& st, uint64_t deadline) {
-  uint64_t pol = 0;
-  if (p.w_evict_first) pol = sm100::l2_policy_evict_first();
+  const uint64_t pol_w = p.w_evict_first ? sm100::l2_policy_evict_first() : sm100::l2_policy_evict_normal();
+  const uint64_t pol_x = sm100::l2_policy_evict_last();
   const uint32_t tx = static_cast<uint32_t>(L.a_bytes + L.b_bytes);
-  for (int kb = c.kb0; kb < c.kb0 + c.kbn; ++kb) {
-    if (!sm100::mbar_wait(&bar->empty[st.stage], st.phase ^ 1, deadline)) return false;
-    uint8_t* a = tiles + static_cast<size_t>(st.stage) * L.stage_bytes;
-    uint8_t* b = a + L.a_bytes;
-    sm100::mbar_arrive_expect_tx(&bar->full[st.stage], tx);
-    // Row-major weights: box at (k, row). Tiled weights: every 128x64 tile is one
-    // contiguous 16 KB run, tile index = m_tile * k_tiles + k_tile.
-    const int kb_total = p.k / kTileK;
-    const int wc0 = p.w_tiled ? 0 : kb * kTileK;
-    const int wc1 = p.w_tiled ? ((c.m0 / kTileM) * kb_total + kb) * kTileM : c.m0;
-    const int uc1 = p.w_tiled ? (((p.up_offset + c.m0) / kTileM) * kb_total + kb) * kTileM
-                              : p.up_offset + c.m0;
-    if (p.w_evict_first) {
-      sm100::tma_load_2d_hint(a, p.tmap_w, &bar->full[st.stage], wc0, wc1, pol);
-      if (p.dual)
-        sm100::tma_load_2d_hint(a + kTileM * kTileK * 2, p.tmap_w, &bar->full[st.stage], wc0, uc1, pol);
-    } else {
-      sm100::tma_load_2d(a, p.tmap_w, &bar->full[st.stage], wc0, wc1);
-      if (p.dual) sm100::tma_load_2d(a + kTileM * kTileK * 2, p.tmap_w, &bar->full[st.stage], wc0, uc1);
-    }
-    sm100::tma_load_2d(b, p.tmap_x, &bar->full[st.stage], kb * kTileK, c.n0);
-    if (p.trace != nullptr && blockIdx.x == 0 && kb - c.kb0 < 256)
-      p.trace[3 * (kb - c.kb0)] = sm100::global_timer_ns();
-    st.advance(L.stages);
+  const uint32_t tiles_addr = sm100::smem_u32(tiles);
+  const uint32_t full0 = sm100::smem_u32(&bar->full[0]);
+  const uint32_t empty0 = sm100::smem_u32(&bar->empty[0]);
+  const uint32_t stage_bytes = static_cast<uint32_t>(L.stage_bytes);
+  const uint32_t a_bytes = static_cast<uint32_t>(L.a_bytes);
+  const uint32_t stages = static_cast<uint32_t>(L.stages);
+  const uint64_t tw = reinterpret_cast<uint64_t>(p.tmap_w);
+  const uint64_t tx_map = reinterpret_cast<uint64_t>(p.tmap_x);
+  // Row-major weights: box at (k, row). Tiled weights: every 128x64 tile is one
+  // contiguous 16 KB run, tile index = m_tile * k_tiles + k_tile.
+  const int kb_total = p.k / kTileK;
+  int wc0, wc1, uc1, dwc0, dwc1;
+  if (p.w_tiled) {
+    wc0 = 0;
+    dwc0 = 0;
+    wc1 = ((c.m0 / kTileM) * kb_total + c.kb0) * kTileM;
+    uc1 = (((p.up_offset + c.m0) / kTileM) * kb_total + c.kb0) * kTileM;
+    dwc1 = kTileM;
+  } else {
+    wc0 = c.kb0 * kTileK;
+    dwc0 = kTileK;
+    wc1 = c.m0;
+    uc1 = p.up_offset + c.m0;
+    dwc1 = 0;
   }
+  int xc0 = c.kb0 * kTileK;
+  uint32_t stage = st.stage, phase = st.phase;
+  uint32_t a_addr = tiles_addr + stage * stage_bytes;
+  const bool dual = p.dual != 0;
+  for (int i = 0; i < c.kbn; ++i) {
+    const uint32_t full = full0 + stage * 8, empty = empty0 + stage * 8;
+    if (!sm100::mbar_try_wait_addr(empty, phase ^ 1) &&
+        !sm100::mbar_wait_addr(empty, phase ^ 1, deadline)) {
+      st.stage = stage;
+      st.phase = phase;
+      return false;
+    }
+    sm100::mbar_arrive_expect_tx_addr(full, tx);
+    sm100::tma_load_2d_addr(a_addr, tw, full, wc0, wc1, pol_w);
+    if (dual) sm100::tma_load_2d_addr(a_addr + kTileM * kTileK * 2, tw, full, wc0, uc1, pol_w);
+    sm100::tma_load_2d_addr(a_addr + a_bytes, tx_map, full, xc0, c.n0, pol_x);
+    wc0 += dwc0;
+    wc1 += dwc1;
+    uc1 += dwc1;
+    xc0 += kTileK;
+    a_addr += stage_bytes;
+    if (++stage == stages) {
+      stage = 0;
+      phase ^= 1;
+      a_addr = tiles_addr;
+    }
+  }
+  st.stage = stage;
+  st.phase = phase;
   return true;
 }
 
@@ -230,32 +264,57 @@ __device__ __forceinline__ void producer_drain(const SmemLayout& L, Barriers* ba
 __device__ __forceinline__ bool mma_tile(const Problem& p, const TileCoord& c, const SmemLayout& L,
                                          uint8_t* tiles, Barriers* bar, PipeState& st, int nacc,
                                          uint64_t deadline) {
-  const uint32_t acc_cols = static_cast<uint32_t>(p.bn * (p.dual ? 2 : 1));
-  const uint32_t tmem_acc = bar->tmem_base + st.acc * acc_cols;
+  const uint32_t acc_w = static_cast<uint32_t>(p.bn * (p.dual ? 2 : 1));
+  const uint32_t tmem_g = bar->tmem_base + st.acc * acc_w;
+  const uint32_t tmem_u = tmem_g + p.bn;
   const uint32_t idesc = sm100::umma_idesc_bf16(kTileM, static_cast<uint32_t>(p.bn));
   if (!sm100::mbar_wait(&bar->acc_empty[st.acc], st.acc_phase ^ 1, deadline)) return false;
   sm100::tc_fence_after_sync();
+  const uint32_t tiles_addr = sm100::smem_u32(tiles);
+  const uint32_t full0 = sm100::smem_u32(&bar->full[0]);
+  const uint32_t empty0 = sm100::smem_u32(&bar->empty[0]);
+  const uint32_t stages = static_cast<uint32_t>(L.stages);
+  // descriptors of stage 0; a stage further adds stage_bytes / 16 to the address field
+  const uint64_t da0 = sm100::umma_desc_sw128(tiles_addr);
+  const uint64_t du0 = sm100::umma_desc_sw128(tiles_addr + kTileM * kTileK * 2);
+  const uint64_t db0 = sm100::umma_desc_sw128(tiles_addr + L.a_bytes);
+  const uint64_t dstage = static_cast<uint64_t>(L.stage_bytes >> 4);
+  uint32_t stage = st.stage, phase = st.phase;
+  uint64_t da = da0 + stage * dstage, du = du0 + stage * dstage, db = db0 + stage * dstage;
+  const bool dual = p.dual != 0;
+  uint32_t accum = 0;
   for (int i = 0; i < c.kbn; ++i) {
-    if (!sm100::mbar_wait(&bar->full[st.stage], st.phase, deadline)) return false;
-    sm100::tc_fence_after_sync();
-    if (p.trace != nullptr && blockIdx.x == 0 && i < 256) p.trace[3 * i + 1] = sm100::global_timer_ns();
-    uint8_t* a = tiles + static_cast<size_t>(st.stage) * L.stage_bytes;
-    const uint32_t a_addr = sm100::smem_u32(a);
-    const uint32_t b_addr = a_addr + L.a_bytes;
-    const uint64_t da = sm100::umma_desc_sw128(a_addr);
-    const uint64_t du = sm100::umma_desc_sw128(a_addr + kTileM * kTileK * 2);
-    const uint64_t db = sm100::umma_desc_sw128(b_addr);
-#pragma unroll
-    for (int k = 0; k < kTileK / kUmmaK; ++k) {
-      const uint64_t koff = static_cast<uint64_t>((k * kUmmaK * 2) >> 4);  // 32 bytes per step
-      const uint32_t accum = (i > 0 || k > 0) ? 1u : 0u;
-      sm100::umma_bf16(tmem_acc, da + koff, db + koff, idesc, accum);
-      if (p.dual) sm100::umma_bf16(tmem_acc + p.bn, du + koff, db + koff, idesc, accum);
+    const uint32_t full = full0 + stage * 8;
+    if (!sm100::mbar_try_wait_addr(full, phase) && !sm100::mbar_wait_addr(full, phase, deadline)) {
+      st.stage = stage;
+      st.phase = phase;
+      return false;
     }
-    sm100::umma_commit(&bar->empty[st.stage]);  // frees the stage when these MMAs retire
-    if (p.trace != nullptr && blockIdx.x == 0 && i < 256) p.trace[3 * i + 2] = sm100::global_timer_ns();
-    st.advance(L.stages);
+    sm100::tc_fence_after_sync();
+    // 32 bytes (two 16-byte units) per UMMA K step inside the 128-byte swizzle row
+    sm100::umma_bf16(tmem_g, da, db, idesc, accum);
+    if (dual) sm100::umma_bf16(tmem_u, du, db, idesc, accum);
+    sm100::umma_bf16(tmem_g, da + 2, db + 2, idesc, 1u);
+    if (dual) sm100::umma_bf16(tmem_u, du + 2, db + 2, idesc, 1u);
+    sm100::umma_bf16(tmem_g, da + 4, db + 4, idesc, 1u);
+    if (dual) sm100::umma_bf16(tmem_u, du + 4, db + 4, idesc, 1u);
+    sm100::umma_bf16(tmem_g, da + 6, db + 6, idesc, 1u);
+    if (dual) sm100::umma_bf16(tmem_u, du + 6, db + 6, idesc, 1u);
+    accum = 1;
+    sm100::umma_commit_addr(empty0 + stage * 8);  // frees the stage when these MMAs retire
+    da += dstage;
+    du += dstage;
+    db += dstage;
+    if (++stage == stages) {
+      stage = 0;
+      phase ^= 1;
+      da = da0;
+      du = du0;
+      db = db0;
+    }
   }
+  st.stage = stage;
+  st.phase = phase;
   sm100::umma_commit(&bar->acc_full[st.acc]);
   st.advance_acc(nacc);
   return true;

@@ -1,0 +1,112 @@
+// Device-resident state of an FFN device's Executor Lanes.
+//
+// An FFN device serves many Instances (models) with a few Lanes. A Lane is a
+// CUDA stream that keeps replaying one generic graph:
+//
+//   lane_wait      scans the Instances' invocation slots, lets the device-side
+//                  Scheduler pick one for this Lane (FIFO / Random / SLO), and
+//                  publishes the choice in LaneCur        (reference K3 + K5)
+//   gate/up GEMM   tcgen05 GEMM whose Problem is read from the descriptor table
+//                  entry of (instance, layer): weights are bound per call by
+//                  table lookup, not by patching graph nodes     (K6 + K18/K19)
+//   down GEMM      same, epilogue stores straight into the attention device's
+//                  partial buffer for this TP rank                   (K18 + K11)
+//   lane_complete  releases the completion word on the attention device and
+//                  returns the Lane to the Scheduler                      (K10)
+//
+// One graph therefore serves every layer signature of every model (the
+// reference captures one child graph per Signature x Capacity and switches
+// between them with conditional nodes, src/cext/ffnagent/runtime.cu:701-1006).
+// No Lane ever waits on another FFN device: TP partials are pushed to the
+// attention device and folded there in rank order.
+#pragma once
+
+#include "xpool/gemm_ws.cuh"
+#include "xpool/protocol.hpp"
+#include "xpool/scheduler.hpp"
+
+namespace xpool {
+namespace lane {
+
+constexpr int kMaxInstances = 32;
+constexpr int kMaxLanes = 8;
+constexpr int kBnVariants = 5;  // 16, 32, 64, 128, 256
+
+// Per (instance, layer): weight tensor maps and epilogue parameters.
+struct alignas(128) LayerEntry {
+  CUtensorMap tmap_gateup;  // [2 * inter_local (or inter_local), hidden] box {64, 128}
+  CUtensorMap tmap_down;    // [hidden, inter_local]
+  const float* bias_gateup;
+  const float* bias_down;
+  int inter_local;
+  int gated;                // 1: SwiGLU-style dual projection
+  int w_tiled;
+  int kind;                 // LayerKind
+  float gate_limit, up_add, act_alpha;
+  int reserved;
+};
+
+// Per instance slot on this FFN rank.
+struct alignas(128) InstanceSlot {
+  CUtensorMap tmap_x[kBnVariants];    // input payload [capacity, hidden]
+  CUtensorMap tmap_act[kBnVariants];  // activation scratch [capacity, max inter_local]
+  const uint32_t* in_flag;            // local word the attention side releases (sequence)
+  const InvocationRecord* record;     // local record written before the flag
+  void* act;                          // local scratch between the two GEMMs
+  void* out_peer;                     // attention device: partial buffer of this TP rank
+  uint32_t* done_flag_peer;           // attention device: completion sequence word
+  const LayerEntry* layers;           // this instance's layer table
+  int capacity_rows;
+  int hidden;
+  int num_layers;
+  int act_ld;                         // leading dimension of the scratch (max inter_local)
+};
+
+struct alignas(128) LaneCtl {
+  uint32_t lock;
+  uint32_t shutdown;       // host-written: Lanes stop waiting and report idle
+  uint32_t n_instances;
+  uint32_t n_lanes;
+  uint32_t policy;         // SchedulerPolicyKind
+  uint32_t reserved;
+  uint64_t seed;
+  uint64_t next_ticket;
+  uint64_t served[kMaxInstances];  // invocations completed per instance (statistics)
+  SchedulerEntry entries[kMaxInstances];
+  LaneState lanes[kMaxLanes];
+};
+
+// What a Lane is currently executing; written by lane_wait, read by the GEMMs.
+struct alignas(64) LaneCur {
+  uint32_t valid;     // 0: idle replay (lease ran out, shutdown or error)
+  uint32_t instance;
+  uint32_t layer;
+  uint32_t rows;
+  uint32_t sequence;  // invocation sequence being served
+  uint32_t mode;
+  uint64_t lease;     // scheduler lease
+  uint64_t t_start_ns;
+  uint32_t idle_replays;
+  uint32_t result_code;
+};
+
+__device__ __forceinline__ bool lock_acquire(uint32_t* lock, uint64_t deadline_ns) {
+  uint32_t spins = 0;
+  while (atomicCAS(lock, 0u, 1u) != 0u) {
+    if ((++spins & 0xffu) == 0 && sm100::global_timer_ns() > deadline_ns) return false;
+    __nanosleep(50);
+  }
+  __threadfence();
+  return true;
+}
+__device__ __forceinline__ void lock_release(uint32_t* lock) {
+  __threadfence();
+  atomicExch(lock, 0u);
+}
+
+__host__ __device__ inline int bn_index(int bn) {
+  return bn <= 16 ? 0 : bn <= 32 ? 1 : bn <= 64 ? 2 : bn <= 128 ? 3 : 4;
+}
+
+}  // namespace lane
+}  // namespace xpool

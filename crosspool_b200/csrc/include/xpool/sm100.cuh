@@ -261,3 +261,54 @@ __device__ __forceinline__ int wait_flag_ge(const uint32_t* p, uint32_t want, ui
 
 }  // namespace sm100
 }  // namespace xpool
+
+// ---------------------------------------------------------------- address-based variants
+// Same operations taking 32-bit shared-memory addresses that the caller keeps in
+// registers and advances incrementally (single-thread producer / issuer loops).
+namespace xpool {
+namespace sm100 {
+
+__device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+static __device__ __noinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity, uint64_t deadline_ns) {
+  uint32_t spins = 0;
+  while (!mbar_try_wait_addr(bar, parity)) {
+    if ((++spins & 0x3ffu) == 0 && global_timer_ns() > deadline_ns) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_addr(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_addr(uint32_t smem_dst, uint64_t tmap, uint32_t bar, int32_t c0,
+                                                 int32_t c1, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4}], [%2], %5;"
+      :
+      : "r"(smem_dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_addr(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+}  // namespace sm100
+}  // namespace xpool

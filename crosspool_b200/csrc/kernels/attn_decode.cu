@@ -18,12 +18,28 @@ namespace attn {
 constexpr int kDecodeThreads = 128;
 
 template <int E>
-__device__ __forceinline__ void load_bf16_vec(const __nv_bfloat16* p, float* out) {
+struct RawVec {
+  uint4 v[E / 8];
+};
+
+template <int E>
+__device__ __forceinline__ void load_raw(const __nv_bfloat16* p, RawVec<E>& r) {
   static_assert(E == 8 || E == 16, "E");
 #pragma unroll
+  for (int c = 0; c < E / 8; ++c) r.v[c] = __ldg(reinterpret_cast<const uint4*>(p) + c);
+}
+
+template <int E>
+__device__ __forceinline__ void zero_raw(RawVec<E>& r) {
+#pragma unroll
+  for (int c = 0; c < E / 8; ++c) r.v[c] = make_uint4(0, 0, 0, 0);
+}
+
+template <int E>
+__device__ __forceinline__ void unpack(const RawVec<E>& r, float* out) {
+#pragma unroll
   for (int c = 0; c < E / 8; ++c) {
-    uint4 raw = __ldg(reinterpret_cast<const uint4*>(p) + c);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r.v[c]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float2 f = __bfloat1622float2(h[j]);
@@ -77,20 +93,31 @@ decode_attn_kernel(XpDecodeAttnArgs a) {
   const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.v_cache);
   // The trip count is uniform across the CTA (lanes past the slice's end idle
   // inside the loop) because the dot-product shuffles below name every lane.
-  for (int tb = t0; tb < t1; tb += 16) {
-    const int t = tb + grp;
-    const bool valid = t < t1;
-    float kf[E], vf[E];
-    if (valid) {
+  // The next iteration's K/V rows are requested before the current ones are
+  // consumed, which doubles the bytes each SM keeps in flight.
+  auto fetch = [&](int t, RawVec<E>& kr, RawVec<E>& vr) {
+    if (t < t1) {
       const int page = table[t / a.page_size];
       const size_t tok = static_cast<size_t>(page) * a.page_size + (t % a.page_size);
       const size_t off = (tok * a.kv_heads + hk) * D + gl * E;
-      load_bf16_vec<E>(kc + off, kf);
-      load_bf16_vec<E>(vc + off, vf);
+      load_raw<E>(kc + off, kr);
+      load_raw<E>(vc + off, vr);
     } else {
-#pragma unroll
-      for (int e = 0; e < E; ++e) kf[e] = vf[e] = 0.f;
+      zero_raw<E>(kr);
+      zero_raw<E>(vr);
     }
+  };
+  RawVec<E> kr, vr, kn, vn;
+  fetch(t0 + grp, kr, vr);
+  for (int tb = t0; tb < t1; tb += 16) {
+    const int t = tb + grp;
+    const bool valid = t < t1;
+    fetch(t + 16, kn, vn);
+    float kf[E], vf[E];
+    unpack<E>(kr, kf);
+    unpack<E>(vr, vf);
+    kr = kn;
+    vr = vn;
 #pragma unroll
     for (int g = 0; g < GMAX; ++g) {
       if (g >= G) break;  // G is uniform

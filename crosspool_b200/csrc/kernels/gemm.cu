@@ -171,7 +171,6 @@ extern "C" int xp_gemm(const XpGemmArgs* a) {
   p.gate_limit = a->gate_limit;
   p.up_add = a->up_add;
   p.act_alpha = a->act_alpha;
-  p.trace = a->trace;
 
   static bool attr_set[64] = {false};
   int dev = 0;

@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 8
+EXPECTED_ABI = 10
 HERE = Path(__file__).resolve().parent
 
 
@@ -34,7 +34,6 @@ class GemmArgs(C.Structure):
         ("counters", C.c_void_p),
         ("status", C.c_void_p),
         ("stream", C.c_void_p),
-        ("trace", C.c_void_p),
         ("ws_bytes", C.c_size_t),
         ("counter_bytes", C.c_size_t),
         ("w_rows_total", C.c_int),

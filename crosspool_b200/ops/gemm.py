@@ -87,7 +87,7 @@ def tile_weight(w: torch.Tensor) -> TiledWeight:
 
 
 def _args(x, w, out, *, n_out, rows, epilogue, dual=0, up_offset=0, bias=None, resid=None, splits=0, bn=0,
-          num_sms=0, evict_first=None, gate_limit=0.0, up_add=0.0, act_alpha=0.0, trace=None) -> native.GemmArgs:
+          num_sms=0, evict_first=None, gate_limit=0.0, up_add=0.0, act_alpha=0.0) -> native.GemmArgs:
     tiled = isinstance(w, TiledWeight)
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     assert x.stride(-1) == 1 and out.stride(-1) == 1 and (tiled or w.stride(-1) == 1)
@@ -126,7 +126,6 @@ def _args(x, w, out, *, n_out, rows, epilogue, dual=0, up_offset=0, bias=None, r
     a.gate_limit = gate_limit
     a.up_add = up_add
     a.act_alpha = act_alpha
-    a.trace = trace.data_ptr() if trace is not None else None
     return a
 
 
@@ -138,7 +137,7 @@ def plan(a: native.GemmArgs) -> native.GemmPlan:
 
 def linear(x: torch.Tensor, w: torch.Tensor, *, out: torch.Tensor | None = None, bias: torch.Tensor | None = None,
            resid: torch.Tensor | None = None, out_fp32: bool = False, splits: int = 0, bn: int = 0,
-           num_sms: int = 0, evict_first: bool | None = None, trace: torch.Tensor | None = None) -> torch.Tensor:
+           num_sms: int = 0, evict_first: bool | None = None) -> torch.Tensor:
     """``x[rows, k] @ w[n, k].T`` (+ fp32 ``bias``) (+ ``resid``) on the tcgen05 kernel."""
     x2 = x.reshape(-1, x.shape[-1])
     rows, n = x2.shape[0], w.shape[0]
@@ -146,7 +145,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, out: torch.Tensor | None = None,
         out = torch.empty(rows, n, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
     epi = EPI_STORE_F32 if out.dtype == torch.float32 else (EPI_RESIDUAL if resid is not None else EPI_STORE)
     a = _args(x2, w, out, n_out=n, rows=rows, epilogue=epi, bias=bias, resid=resid, splits=splits, bn=bn,
-              num_sms=num_sms, evict_first=evict_first, trace=trace)
+              num_sms=num_sms, evict_first=evict_first)
     native.check(native.kernels().xp_gemm(C.byref(a)), "xp_gemm")
     return out.reshape(*x.shape[:-1], n) if x.dim() != 2 else out
 
