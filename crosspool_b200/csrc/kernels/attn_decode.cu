@@ -80,6 +80,19 @@ decode_attn_kernel(XpDecodeAttnArgs a) {
   __syncthreads();
 
   const int grp = threadIdx.x >> 3, gl = threadIdx.x & 7;
+  // this lane's slice of every query head, kept in registers (shared-memory reads
+  // here would collide on banks: the 8 lanes of a token sit 64 bytes apart)
+  // (for 8 heads per KV head the registers do not suffice; those read shared memory)
+  constexpr bool kQInRegs = GMAX <= 4;
+  float qr[kQInRegs ? GMAX : 1][E];
+  if constexpr (kQInRegs) {
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g)
+#pragma unroll
+      for (int e = 0; e < E; ++e) qr[g][e] = q_s[g][gl * E + e];
+  }
+  const int page_shift = 31 - __clz(a.page_size);  // page size is a power of two
+  const int page_mask = a.page_size - 1;
   float m[GMAX], l[GMAX], acc[GMAX][E];
 #pragma unroll
   for (int g = 0; g < GMAX; ++g) {
@@ -97,8 +110,8 @@ decode_attn_kernel(XpDecodeAttnArgs a) {
   // consumed, which doubles the bytes each SM keeps in flight.
   auto fetch = [&](int t, RawVec<E>& kr, RawVec<E>& vr) {
     if (t < t1) {
-      const int page = table[t / a.page_size];
-      const size_t tok = static_cast<size_t>(page) * a.page_size + (t % a.page_size);
+      const int page = table[t >> page_shift];
+      const size_t tok = (static_cast<size_t>(page) << page_shift) + (t & page_mask);
       const size_t off = (tok * a.kv_heads + hk) * D + gl * E;
       load_raw<E>(kc + off, kr);
       load_raw<E>(vc + off, vr);
@@ -123,18 +136,23 @@ decode_attn_kernel(XpDecodeAttnArgs a) {
       if (g >= G) break;  // G is uniform
       float s = 0.f;
 #pragma unroll
-      for (int e = 0; e < E; ++e) s += q_s[g][gl * E + e] * kf[e];
+      for (int e = 0; e < E; ++e) s += (kQInRegs ? qr[kQInRegs ? g : 0][e] : q_s[g][gl * E + e]) * kf[e];
       s += __shfl_xor_sync(0xffffffffu, s, 1);
       s += __shfl_xor_sync(0xffffffffu, s, 2);
       s += __shfl_xor_sync(0xffffffffu, s, 4);
       if (valid) {
-        const float mn = fmaxf(m[g], s);
-        const float corr = exp2f(m[g] - mn);
-        const float p = exp2f(s - mn);
-        m[g] = mn;
-        l[g] = l[g] * corr + p;
+        // rescale the running sums only when the maximum actually moves
+        if (s > m[g]) {
+          const float corr = exp2f(m[g] - s);
+          m[g] = s;
+          l[g] *= corr;
 #pragma unroll
-        for (int e = 0; e < E; ++e) acc[g][e] = acc[g][e] * corr + p * vf[e];
+          for (int e = 0; e < E; ++e) acc[g][e] *= corr;
+        }
+        const float p = exp2f(s - m[g]);
+        l[g] += p;
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[g][e] += p * vf[e];
       }
     }
   }

@@ -64,11 +64,57 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmap_w,
   cta_teardown(bar, tmem_cols, warp);
 }
 
-static int pick_bn(int rows, int dual) {
+// Estimated duration (microseconds) of one launch for a tile width and split-K
+// factor. The constants come from measurements on B200: one SM ingests about
+// 55 GB/s through TMA, HBM delivers about 6 TB/s in total, a tcgen05.mma of
+// M=128 retires in max(45, N/2) cycles, and a launch costs about 3 us of set-up,
+// pipeline fill and epilogue. Only relative order matters.
+static double estimate_us(int tm, int rows, int kb, int dual, int bn, int splits, int sms) {
+  const int tn = (rows + bn - 1) / bn;
+  const int ctas = tm * tn * splits;
+  const int waves = (ctas + sms - 1) / sms;
+  const int kb_per = (kb + splits - 1) / splits;
+  const double stage_kb = (kTileM * kTileK * 2 * (dual ? 2 : 1) + bn * kTileK * 2) / 1000.0;
+  const int active = std::min(ctas, sms);
+  const double bw = std::min(55.0, 6000.0 / active);  // KB per us per SM
+  const double t_mem = stage_kb / bw;
+  const double t_mma = (dual ? 8 : 4) * std::max(45.0, bn / 2.0) / 1900.0;
+  const int acc_cols = bn * (dual ? 2 : 1);
+  double t = 3.0 + kb_per * std::max(t_mem, t_mma) + (bn / 16) * 0.12;
+  if (splits > 1) t += 2.0 + splits * acc_cols * 0.512 / 55.0 + acc_cols * 0.004;
+  return waves * t;
+}
+
+struct TileChoice {
+  int bn, splits;
+};
+
+static TileChoice choose_tiles(int tm, int rows, int kb, int dual, int sms, int fixed_bn, int fixed_splits,
+                               size_t ws_bytes_available) {
   const int cap = dual ? 128 : 256;
-  int bn = 16;
-  while (bn < rows && bn < cap) bn <<= 1;
-  return bn;
+  int top = 16;
+  while (top < rows && top < cap) top <<= 1;
+  TileChoice best{top, 1};
+  double best_t = 1e30;
+  static const int kSplits[] = {1, 2, 3, 4, 6, 8, 12, 16};
+  for (int bn = 16; bn <= top; bn <<= 1) {
+    if (fixed_bn > 0 && bn != fixed_bn) continue;
+    if (fixed_bn <= 0 && bn * 4 < top && bn < 64) continue;  // no forests of tiny tiles
+    const int tn = (rows + bn - 1) / bn;
+    for (int s : kSplits) {
+      if (fixed_splits > 0 && s != fixed_splits) continue;
+      if (s > kb) continue;
+      if (s > 1 && (s - 1) * ((kb + s - 1) / s) >= kb) continue;  // every split owns a K block
+      const size_t ws = s > 1 ? static_cast<size_t>(tm) * tn * s * bn * (dual ? 2 : 1) * kTileM * 4 : 0;
+      if (ws > ws_bytes_available) continue;
+      const double t = estimate_us(tm, rows, kb, dual, bn, s, sms);
+      if (t < best_t) {
+        best_t = t;
+        best = TileChoice{bn, s};
+      }
+    }
+  }
+  return best;
 }
 
 }  // namespace gemm
@@ -87,26 +133,19 @@ extern "C" int xp_gemm_plan(const XpGemmArgs* a, XpGemmPlan* plan) {
     cudaDeviceGetAttribute(&sm_count_cache[dev], cudaDevAttrMultiProcessorCount, dev);
   int sms = a->num_sms > 0 ? a->num_sms : (dev < 64 ? sm_count_cache[dev] : 148);
   if (sms <= 0) sms = 148;
-  int bn = a->bn > 0 ? a->bn : gemm::pick_bn(a->rows, a->dual);
-  if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return -11;
-  if (a->dual && bn > 256) return -11;
+  const int tm = a->n_out / gemm::kTileM;
+  const int kb = a->k / gemm::kTileK;
+  if (a->bn > 0 && a->bn != 16 && a->bn != 32 && a->bn != 64 && a->bn != 128 && a->bn != 256) return -11;
+  int fixed_splits = a->splits;
+  if (fixed_splits > kb) fixed_splits = kb;
+  while (fixed_splits > 1 && (fixed_splits - 1) * ((kb + fixed_splits - 1) / fixed_splits) >= kb) --fixed_splits;
+  const size_t ws_avail = (a->ws != nullptr && a->counters != nullptr) ? a->ws_bytes : 0;
+  const gemm::TileChoice ch = gemm::choose_tiles(tm, a->rows, kb, a->dual, sms, a->bn, fixed_splits, ws_avail);
+  const int bn = a->bn > 0 ? a->bn : ch.bn;
+  int splits = fixed_splits > 0 ? fixed_splits : ch.splits;
   const int acc_cols = bn * (a->dual ? 2 : 1);
   const int nacc = acc_cols * 2 <= 512 ? 2 : 1;
-  const int tm = a->n_out / gemm::kTileM;
   const int tn = (a->rows + bn - 1) / bn;
-  const int kb = a->k / gemm::kTileK;
-  int splits = a->splits;
-  if (splits <= 0) {
-    splits = 1;
-    const int tiles = tm * tn;
-    if (tiles * 2 <= sms) {
-      splits = std::min(sms / tiles, std::max(1, kb / 4));
-      splits = std::min(splits, 16);
-    }
-  }
-  if (splits > kb) splits = kb;
-  // every split must own at least one K block
-  while (splits > 1 && (splits - 1) * ((kb + splits - 1) / splits) >= kb) --splits;
   plan->bn = bn;
   plan->nacc = nacc;
   plan->splits = splits;
