@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 10
+#define XP_ABI_VERSION 11
 
 #ifdef __cplusplus
 extern "C" {
@@ -67,7 +67,58 @@ typedef struct XpNormArgs {
   int rows, hidden, ld_parts, ld_out, nparts, npeers;
   uint32_t wait_seq, publish_seq, meta_layer, meta_mode, meta_deadline_us;
   float eps;
+  uint32_t* seq_counter;       /* optional device word: publish value = *seq_counter + 1, stored back */
 } XpNormArgs;
+
+/* Attention side: wait (bounded) until each flag reaches *want_ptr (or `want`). */
+typedef struct XpWaitArgs {
+  const uint32_t* flags[8];
+  const uint32_t* want_ptr;
+  const uint32_t* cancel;
+  uint32_t* status;
+  uint64_t wait_ns;
+  uint32_t want;
+  int n;
+} XpWaitArgs;
+
+/* FFN device Lane runtime (see xpool/lane.cuh). */
+typedef struct XpLaneInstanceDesc {
+  void* input;             /* local [capacity_rows, hidden] bf16 payload buffer */
+  void* act;               /* local [capacity_rows, act_ld] bf16 scratch */
+  const void* in_flag;     /* local sequence word released by the attention side */
+  const void* record;      /* local InvocationRecord */
+  void* out_peer;          /* attention device: [capacity_rows, hidden] partial of this TP rank */
+  void* done_record_peer;  /* attention device: CompletionRecord of this TP rank */
+  int capacity_rows, hidden, num_layers, act_ld;
+} XpLaneInstanceDesc;
+
+typedef struct XpLaneLayerDesc {
+  const void* w_gateup;    /* [(gated ? 2 : 1) * inter_local, hidden] bf16 (row-major or tiled) */
+  const void* w_down;      /* [hidden, inter_local] */
+  const float* bias_gateup;
+  const float* bias_down;
+  int inter_local, gated, w_tiled;
+  float gate_limit, up_add, act_alpha;
+} XpLaneLayerDesc;
+
+void* xp_lane_create(int n_instances, int n_lanes, int policy, uint64_t seed, size_t ws_bytes_per_lane);
+int xp_lane_set_instance(void* rt, int idx, const XpLaneInstanceDesc* d);
+int xp_lane_set_layer(void* rt, int inst, int layer, const XpLaneLayerDesc* d);
+int xp_lane_commit(void* rt);
+int xp_lane_launch(void* rt, int lane_index, uint64_t lease_ns, void* stream);
+int xp_lane_shutdown(void* rt, void* stream);
+int xp_lane_stats(void* rt, uint64_t* served, uint32_t* idle, uint32_t* status, void* stream);
+void xp_lane_destroy(void* rt);
+int xp_wait_flags(const XpWaitArgs* a, void* stream);
+
+/* Raw device memory shared between processes (CUDA IPC). */
+int xp_dev_alloc(void** ptr, size_t bytes);
+int xp_dev_free(void* ptr);
+int xp_ipc_get_handle(void* ptr, void* handle64);
+int xp_ipc_open(const void* handle64, void** ptr);
+int xp_ipc_close(void* ptr);
+int xp_memset_async(void* ptr, int value, size_t bytes, void* stream);
+int xp_enable_peer_access(int peer_device);
 
 int xp_norm_publish(const XpNormArgs* a, void* stream);
 int xp_swiglu(const void* gate_up, void* out, int rows, int inter, float limit, float up_add,

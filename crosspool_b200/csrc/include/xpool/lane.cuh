@@ -31,6 +31,7 @@ namespace lane {
 constexpr int kMaxInstances = 32;
 constexpr int kMaxLanes = 8;
 constexpr int kBnVariants = 5;  // 16, 32, 64, 128, 256
+constexpr int kRowBuckets = 16; // row-count buckets 2^0 .. 2^15 (the reference's Capacities)
 
 // Per (instance, layer): weight tensor maps and epilogue parameters.
 struct alignas(128) LayerEntry {
@@ -44,6 +45,9 @@ struct alignas(128) LayerEntry {
   int kind;                 // LayerKind
   float gate_limit, up_add, act_alpha;
   int reserved;
+  // tile width and split-K factor per row bucket, chosen on the host at install time
+  uint8_t bn_gateup[kRowBuckets], splits_gateup[kRowBuckets];
+  uint8_t bn_down[kRowBuckets], splits_down[kRowBuckets];
 };
 
 // Per instance slot on this FFN rank.

@@ -88,10 +88,12 @@ class Scheduler {
     return kNoLane;
   }
 
-  XP_HD Decision try_schedule() {
+  XP_HD Decision try_schedule() { return try_schedule_on(find_idle_lane()); }
+
+  // Schedules onto a specific idle Lane (a Lane that polls for its own work).
+  XP_HD Decision try_schedule_on(uint32_t lane) {
     Decision d{false, 0, kNoLane, 0};
-    const uint32_t lane = find_idle_lane();
-    if (lane == kNoLane) return d;
+    if (lane == kNoLane || lane >= nl_ || lanes_[lane].busy) return d;
     bool found = false;
     uint32_t best = 0;
     uint64_t best_key = 0, best_ticket = 0;

@@ -4,20 +4,18 @@
 
 #include "xpool/api.h"
 #include "xpool/gemm_ws.cuh"
+#include "xpool/lane.cuh"
 #include "xpool/tensormap.hpp"
 
 namespace xpool {
 namespace gemm {
 
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_ws_kernel(const __grid_constant__ CUtensorMap tmap_w,
-               const __grid_constant__ CUtensorMap tmap_x, Problem p, int nacc, int smem_budget,
-               uint32_t* status) {
+// Body shared by the stream-launched kernel and the Lane kernel: every CTA loops
+// over the tiles assigned to it.
+__device__ __forceinline__ void run_tiles(const Problem& p, int nacc, int smem_budget, uint32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  p.tmap_w = &tmap_w;
-  p.tmap_x = &tmap_x;
   const SmemLayout L = smem_layout(p.bn, p.dual, smem_budget);
   const uint32_t tmem_cols = tmem_columns_needed(p.bn, p.dual, nacc);
   Barriers* bar;
@@ -62,6 +60,68 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
   }
   cta_teardown(bar, tmem_cols, warp);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_ws_kernel(const __grid_constant__ CUtensorMap tmap_w,
+               const __grid_constant__ CUtensorMap tmap_x, Problem p, int nacc, int smem_budget,
+               uint32_t* status) {
+  p.tmap_w = &tmap_w;
+  p.tmap_x = &tmap_x;
+  run_tiles(p, nacc, smem_budget, status);
+}
+
+// Lane form: the problem is assembled on the device from the descriptor table
+// entry of the invocation the Lane was given (phase 0: gate/up projection with
+// the activation epilogue into local scratch; phase 1: down projection whose
+// epilogue stores into the attention device's partial buffer for this TP rank).
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int phase, float* ws,
+                 uint32_t* counters, int smem_budget, uint32_t* status) {
+  if (cur->valid == 0 || cur->rows == 0) return;  // idle replay: uniform exit
+  const lane::InstanceSlot& s = slots[cur->instance];
+  const lane::LayerEntry& le = s.layers[cur->layer];
+  const int rows = static_cast<int>(cur->rows);
+  int bucket = 0;
+  while ((1 << bucket) < rows && bucket < lane::kRowBuckets - 1) ++bucket;
+  Problem p{};
+  p.rows = rows;
+  p.ws = ws;
+  p.counters = counters;
+  p.w_tiled = le.w_tiled;
+  p.w_evict_first = rows <= 64;
+  if (phase == 0) {
+    p.bn = le.bn_gateup[bucket] == 255 ? 256 : le.bn_gateup[bucket];
+    p.splits = le.splits_gateup[bucket];
+    p.tmap_w = &le.tmap_gateup;
+    p.tmap_x = &s.tmap_x[lane::bn_index(p.bn)];
+    p.out = s.act;
+    p.bias = le.bias_gateup;
+    p.n_out = le.inter_local;
+    p.k = s.hidden;
+    p.ld_out = s.act_ld;
+    p.dual = le.gated;
+    p.up_offset = le.inter_local;
+    p.epilogue = le.gated ? kEpiSwiglu : kEpiStore;
+    p.gate_limit = le.gate_limit;
+    p.up_add = le.up_add;
+    p.act_alpha = le.act_alpha;
+  } else {
+    p.bn = le.bn_down[bucket] == 255 ? 256 : le.bn_down[bucket];
+    p.splits = le.splits_down[bucket];
+    p.tmap_w = &le.tmap_down;
+    p.tmap_x = &s.tmap_act[lane::bn_index(p.bn)];
+    p.out = s.out_peer;
+    p.bias = le.bias_down;
+    p.n_out = s.hidden;
+    p.k = le.inter_local;
+    p.ld_out = s.hidden;
+    p.epilogue = kEpiStore;
+  }
+  p.ld_resid = p.ld_out;
+  const int nacc = p.bn * (p.dual ? 2 : 1) * 2 <= 512 ? 2 : 1;
+  if (threadIdx.x == 0 && phase == 0) sm100::fence_proxy_async();  // payload arrived through peer stores
+  run_tiles(p, nacc, smem_budget, status);
 }
 
 // Estimated duration (microseconds) of one launch for a tile width and split-K
@@ -115,6 +175,10 @@ static TileChoice choose_tiles(int tm, int rows, int kb, int dual, int sms, int 
     }
   }
   return best;
+}
+
+TileChoice choose_tiles_host(int tm, int rows, int kb, int dual, int sms, size_t ws_bytes_available) {
+  return choose_tiles(tm, rows, kb, dual, sms, 0, 0, ws_bytes_available);
 }
 
 }  // namespace gemm

@@ -144,13 +144,18 @@ norm_publish_kernel(XpNormArgs a) {
   }
 
   // 4. last CTA releases the sequence word on every destination.
-  if (a.npeers > 0 && a.publish_seq != 0) {
+  if (a.npeers > 0 && (a.publish_seq != 0 || a.seq_counter != nullptr)) {
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
       const uint32_t prev = atomicAdd(a.done_counter, 1u);
       if (prev == gridDim.x - 1) {
         *a.done_counter = 0;
+        uint32_t seq = a.publish_seq;
+        if (a.seq_counter != nullptr) {
+          seq = *a.seq_counter + 1;
+          *a.seq_counter = seq;
+        }
         __threadfence_system();
         for (int d = 0; d < a.npeers; ++d) {
           if (a.peer_meta[d] != nullptr) {
@@ -160,7 +165,7 @@ norm_publish_kernel(XpNormArgs a) {
             a.peer_meta[d][2] = a.meta_mode;
             a.peer_meta[d][3] = a.meta_deadline_us;
           }
-          sm100::st_release_sys(a.peer_flags[d], a.publish_seq);
+          sm100::st_release_sys(a.peer_flags[d], seq);
         }
       }
     }

@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 10
+EXPECTED_ABI = 11
 HERE = Path(__file__).resolve().parent
 
 
@@ -99,6 +99,7 @@ class NormArgs(C.Structure):
         ("meta_mode", C.c_uint32),
         ("meta_deadline_us", C.c_uint32),
         ("eps", C.c_float),
+        ("seq_counter", C.c_void_p),
     ]
 
 
@@ -131,6 +132,7 @@ def kernels() -> C.CDLL:
     lib.xp_encode_tmap_2d.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32,
                                       C.c_uint32]
     _declare_attention(lib)
+    _declare_lane(lib)
     return lib
 
 
@@ -225,3 +227,72 @@ def _declare_attention(lib: C.CDLL) -> None:
     lib.xp_decode_attn_splits.argtypes = [C.c_int, C.c_int, C.c_int]
     lib.xp_embedding.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.xp_argmax.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+
+
+class WaitArgs(C.Structure):
+    _fields_ = [
+        ("flags", C.c_void_p * 8),
+        ("want_ptr", C.c_void_p),
+        ("cancel", C.c_void_p),
+        ("status", C.c_void_p),
+        ("wait_ns", C.c_uint64),
+        ("want", C.c_uint32),
+        ("n", C.c_int),
+    ]
+
+
+class LaneInstanceDesc(C.Structure):
+    _fields_ = [
+        ("input", C.c_void_p),
+        ("act", C.c_void_p),
+        ("in_flag", C.c_void_p),
+        ("record", C.c_void_p),
+        ("out_peer", C.c_void_p),
+        ("done_record_peer", C.c_void_p),
+        ("capacity_rows", C.c_int),
+        ("hidden", C.c_int),
+        ("num_layers", C.c_int),
+        ("act_ld", C.c_int),
+    ]
+
+
+class LaneLayerDesc(C.Structure):
+    _fields_ = [
+        ("w_gateup", C.c_void_p),
+        ("w_down", C.c_void_p),
+        ("bias_gateup", C.c_void_p),
+        ("bias_down", C.c_void_p),
+        ("inter_local", C.c_int),
+        ("gated", C.c_int),
+        ("w_tiled", C.c_int),
+        ("gate_limit", C.c_float),
+        ("up_add", C.c_float),
+        ("act_alpha", C.c_float),
+    ]
+
+
+def _declare_lane(lib: C.CDLL) -> None:
+    lib.xp_lane_create.restype = C.c_void_p
+    lib.xp_lane_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_size_t]
+    lib.xp_lane_destroy.restype = None
+    lib.xp_lane_destroy.argtypes = [C.c_void_p]
+    sig = {
+        "xp_lane_set_instance": [C.c_void_p, C.c_int, C.POINTER(LaneInstanceDesc)],
+        "xp_lane_set_layer": [C.c_void_p, C.c_int, C.c_int, C.POINTER(LaneLayerDesc)],
+        "xp_lane_commit": [C.c_void_p],
+        "xp_lane_launch": [C.c_void_p, C.c_int, C.c_uint64, C.c_void_p],
+        "xp_lane_shutdown": [C.c_void_p, C.c_void_p],
+        "xp_lane_stats": [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.c_void_p],
+        "xp_wait_flags": [C.POINTER(WaitArgs), C.c_void_p],
+        "xp_dev_alloc": [C.POINTER(C.c_void_p), C.c_size_t],
+        "xp_dev_free": [C.c_void_p],
+        "xp_ipc_get_handle": [C.c_void_p, C.c_void_p],
+        "xp_ipc_open": [C.c_void_p, C.POINTER(C.c_void_p)],
+        "xp_ipc_close": [C.c_void_p],
+        "xp_memset_async": [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p],
+        "xp_enable_peer_access": [C.c_int],
+    }
+    for name, args in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = C.c_int
+        fn.argtypes = args

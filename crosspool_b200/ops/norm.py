@@ -34,7 +34,7 @@ def add_rmsnorm(parts: Sequence[torch.Tensor] | torch.Tensor, weight: torch.Tens
                 peer_ptrs: Sequence[int] = (), peer_flag_ptrs: Sequence[int] = (), peer_meta_ptrs: Sequence[int] = (),
                 publish_seq: int = 0, wait_flag_ptrs: Sequence[int] = (), wait_seq: int = 0,
                 wait_ns: int = 5_000_000_000, meta: tuple[int, int, int] = (0, 0, 0),
-                want_local: bool = True) -> torch.Tensor | None:
+                want_local: bool = True, seq_counter_ptr: int = 0) -> torch.Tensor | None:
     """``y = rmsnorm(sum(parts) + resid) * weight``; ``resid`` is updated in place.
 
     ``parts`` are bf16 ``[rows, hidden]`` tensors (or raw device pointers paired with an explicit
@@ -71,6 +71,7 @@ def add_rmsnorm(parts: Sequence[torch.Tensor] | torch.Tensor, weight: torch.Tens
     a.wait_seq, a.publish_seq = wait_seq, publish_seq
     a.meta_layer, a.meta_mode, a.meta_deadline_us = meta
     a.eps = eps
+    a.seq_counter = seq_counter_ptr or None
     native.check(native.kernels().xp_norm_publish(C.byref(a), torch.cuda.current_stream(dev).cuda_stream),
                  "xp_norm_publish")
     return out

@@ -1,0 +1,351 @@
+"""The Fabric: attention ranks and FFN ranks connected by peer memory over NVLink.
+
+One process per GPU. Every rank allocates its arena with ``cudaMalloc`` and publishes a CUDA IPC
+handle; peers map it once and from then on all traffic is issued by kernels:
+
+* the attention side's norm kernel stores the post-attention hidden states straight into each FFN
+  rank's input buffer, writes the invocation record and releases the slot's sequence word
+  (``ops.norm.add_rmsnorm(peer_ptrs=...)``);
+* an FFN rank's Lane picks the invocation up, runs the two tcgen05 GEMMs, and the down-projection
+  epilogue stores the rank's partial into the attention rank's partial buffer, followed by the
+  completion record (``csrc/kernels/lane.cu``);
+* the attention side waits for the completion words of all TP ranks and the next add-RMSNorm folds
+  the partials in rank order with fp32 accumulation.
+
+Handles travel through ``torch.distributed`` object collectives here (bench, tests); a deployed
+system brokers the same hex handles through the daemon (``service.daemon``), as the reference does
+for Transport arenas (src/xpool/service/daemon/transport.py).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from collections import deque
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import native
+from ..engine.atn_engine import AttentionEngine, EngineConfig, FfnPort
+from ..models.config import ModelConfig
+from ..models.weights import FfnLayerWeights, random_attention_weights, random_ffn_layer
+from ..native import runtime as rt
+
+RECORD_SEQ_OFFSET = 32      # InvocationRecord.sequence
+COMPLETION_SEQ_OFFSET = 16  # CompletionRecord.sequence
+RECORD_BYTES = 256
+
+
+class PeerBuffer:
+    """A raw device allocation that other processes can map."""
+
+    def __init__(self, nbytes: int):
+        p = C.c_void_p()
+        native.check(native.kernels().xp_dev_alloc(C.byref(p), nbytes), "xp_dev_alloc", 0)
+        self.ptr, self.nbytes, self.owned = p.value, nbytes, True
+
+    def handle(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        native.check(native.kernels().xp_ipc_get_handle(self.ptr, buf), "xp_ipc_get_handle", 0)
+        return bytes(buf.raw)
+
+    @staticmethod
+    def open(handle: bytes) -> int:
+        p = C.c_void_p()
+        native.check(native.kernels().xp_ipc_open(handle, C.byref(p)), "xp_ipc_open", 0)
+        return p.value
+
+    def tensor(self, offset: int, shape: tuple[int, ...], dtype: torch.dtype, device) -> torch.Tensor:
+        return tensor_from_ptr(self.ptr + offset, shape, dtype, device)
+
+    def free(self) -> None:
+        if self.owned and self.ptr:
+            native.kernels().xp_dev_free(self.ptr)
+            self.ptr = 0
+
+
+class _CudaArray:
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
+
+
+def tensor_from_ptr(ptr: int, shape: tuple[int, ...], dtype: torch.dtype, device) -> torch.Tensor:
+    """A tensor view over raw device memory (bf16 goes through a 16-bit integer view)."""
+    if dtype == torch.bfloat16:
+        return torch.as_tensor(_CudaArray(ptr, shape, "<i2"), device=device).view(torch.bfloat16)
+    typestr = {torch.int32: "<i4", torch.float32: "<f4", torch.uint8: "|u1", torch.int64: "<i8"}[dtype]
+    return torch.as_tensor(_CudaArray(ptr, shape, typestr), device=device)
+
+
+# ------------------------------------------------------------------ topology
+
+@dataclass(frozen=True)
+class InstancePlacement:
+    """Where one Instance runs: one attention rank, and the FFN ranks of its TP group (rank order =
+    TP rank order = reduction order)."""
+
+    model_id: str
+    cfg: ModelConfig
+    seed: int
+    atn_rank: int
+    ffn_ranks: tuple[int, ...]
+    capacity_rows: int
+
+    @property
+    def tp(self) -> int:
+        return len(self.ffn_ranks)
+
+
+@dataclass
+class Topology:
+    world_size: int
+    instances: list[InstancePlacement]
+
+    def atn_ranks(self) -> list[int]:
+        return sorted({i.atn_rank for i in self.instances})
+
+    def ffn_ranks(self) -> list[int]:
+        return sorted({r for i in self.instances for r in i.ffn_ranks})
+
+    def role(self, rank: int) -> str:
+        a, f = rank in self.atn_ranks(), rank in self.ffn_ranks()
+        if a and f:
+            raise ValueError(f"rank {rank} has both roles; kernels that wait on one another must not share a GPU")
+        return "atn" if a else "ffn" if f else "idle"
+
+
+def ffn_slot_layout(p: InstancePlacement) -> rt.FfnSlotLayout:
+    inter = (p.cfg.moe_intermediate_size if p.cfg.is_moe else p.cfg.intermediate_size) // p.tp
+    return rt.plan_ffn_slot(p.capacity_rows, p.cfg.hidden_size, inter)
+
+
+def atn_slot_layout(p: InstancePlacement) -> rt.AtnSlotLayout:
+    return rt.plan_atn_slot(p.capacity_rows, p.cfg.hidden_size, p.tp)
+
+
+# ------------------------------------------------------------------ attention side
+
+class FabricFfnPort(FfnPort):
+    """FFN port of an Instance whose FFN lives on other GPUs."""
+
+    def __init__(self, place: InstancePlacement, local: PeerBuffer, ffn_bases: list[int], device):
+        self.place, self.local, self.device = place, local, torch.device(device)
+        self.alay, self.flay = atn_slot_layout(place), ffn_slot_layout(place)
+        self.ffn_bases = ffn_bases  # mapped base pointer of this instance's slot on each TP rank
+        tp = place.tp
+        self.parts = [local.tensor(self.alay.output_offset + r * self.alay.output_stride,
+                                   (place.capacity_rows, place.cfg.hidden_size), torch.bfloat16, self.device)
+                      for r in range(tp)]
+        self.done_flags = [local.ptr + self.alay.completion_offset + r * RECORD_BYTES + COMPLETION_SEQ_OFFSET
+                           for r in range(tp)]
+        self.seq = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.wait_ns = 5_000_000_000  # the reference's device wait limit (utils/wait.cuh:17-19)
+        self._wait = native.WaitArgs()
+        for r, f in enumerate(self.done_flags):
+            self._wait.flags[r] = f
+        self._wait.n = tp
+        self._wait.want_ptr = self.seq.data_ptr()
+        self._wait.wait_ns = self.wait_ns
+
+    def attach(self, engine: AttentionEngine) -> None:
+        from ..ops.gemm import scratch
+
+        if engine.cap > self.place.capacity_rows:
+            raise ValueError("engine row capacity exceeds the fabric slot capacity")
+        self._wait.status = scratch(self.device).status.data_ptr()
+
+    def publish_targets(self, layer: int, rows: int, mode: int) -> dict:
+        return dict(peer_ptrs=[b + self.flay.input_offset for b in self.ffn_bases],
+                    peer_flag_ptrs=[b + self.flay.record_offset + RECORD_SEQ_OFFSET for b in self.ffn_bases],
+                    peer_meta_ptrs=[b + self.flay.record_offset for b in self.ffn_bases],
+                    seq_counter_ptr=self.seq.data_ptr(), meta=(layer, mode, 0))
+
+    def run(self, layer: int, x: torch.Tensor, rows: int, mode: int) -> list[torch.Tensor]:
+        native.check(native.kernels().xp_wait_flags(C.byref(self._wait), torch.cuda.current_stream(self.device).cuda_stream),
+                     "xp_wait_flags")
+        return [p[:rows] for p in self.parts]
+
+
+# ------------------------------------------------------------------ FFN side
+
+@dataclass
+class FfnInstanceState:
+    place: InstancePlacement
+    tp_rank: int
+    slot: PeerBuffer
+    weights: list[FfnLayerWeights]
+    atn_base: int = 0
+
+
+class FfnRankRuntime:
+    """Everything an FFN rank owns: shards, slots, the native Lane runtime and the Lane threads."""
+
+    def __init__(self, device, n_lanes: int = 1, policy: int = rt.POLICY_FIFO, seed: int = 0,
+                 ws_bytes_per_lane: int = 64 << 20, tile_weights: bool = False):
+        self.device = torch.device(device)
+        self.n_lanes, self.policy, self.seed, self.ws_bytes = n_lanes, policy, seed, ws_bytes_per_lane
+        self.tile_weights = tile_weights
+        self.instances: list[FfnInstanceState] = []
+        self.handle = None
+        self._threads: list[threading.Thread] = []
+        self._stop = threading.Event()
+        self.errors: list[str] = []
+
+    def add_instance(self, place: InstancePlacement, tp_rank: int) -> FfnInstanceState:
+        lay = ffn_slot_layout(place)
+        slot = PeerBuffer(lay.total_bytes)
+        weights = [random_ffn_layer(place.cfg, l, place.seed, self.device, torch.bfloat16, tp_rank, place.tp)
+                   for l in range(place.cfg.num_layers)]
+        st = FfnInstanceState(place, tp_rank, slot, weights)
+        self.instances.append(st)
+        return st
+
+    def install(self) -> None:
+        """Builds the native Lane runtime once every instance knows its attention-side arena."""
+        from ..ops import gemm
+
+        lib = native.kernels()
+        self.handle = lib.xp_lane_create(len(self.instances), self.n_lanes, self.policy, self.seed, self.ws_bytes)
+        if not self.handle:
+            raise RuntimeError("xp_lane_create failed")
+        self._keep = []
+        for i, st in enumerate(self.instances):
+            p, flay, alay = st.place, ffn_slot_layout(st.place), atn_slot_layout(st.place)
+            inter = st.weights[0].gate_up.shape[0] // 2
+            d = native.LaneInstanceDesc()
+            d.input = st.slot.ptr + flay.input_offset
+            d.act = st.slot.ptr + flay.act_offset
+            d.in_flag = st.slot.ptr + flay.record_offset + RECORD_SEQ_OFFSET
+            d.record = st.slot.ptr + flay.record_offset
+            d.out_peer = st.atn_base + alay.output_offset + st.tp_rank * alay.output_stride
+            d.done_record_peer = st.atn_base + alay.completion_offset + st.tp_rank * RECORD_BYTES
+            d.capacity_rows, d.hidden, d.num_layers, d.act_ld = p.capacity_rows, p.cfg.hidden_size, p.cfg.num_layers, inter
+            native.check(lib.xp_lane_set_instance(self.handle, i, C.byref(d)), "xp_lane_set_instance", 0)
+            for l, w in enumerate(st.weights):
+                gu, dn = w.gate_up, w.down
+                if self.tile_weights:
+                    gu, dn = gemm.tile_weight(gu), gemm.tile_weight(dn)
+                    self._keep.append((gu, dn))
+                ld = native.LaneLayerDesc()
+                ld.w_gateup, ld.w_down = gu.data_ptr(), dn.data_ptr()
+                ld.bias_gateup = w.gate_up_bias.data_ptr() if w.gate_up_bias is not None else None
+                ld.bias_down = w.down_bias.data_ptr() if w.down_bias is not None else None
+                ld.inter_local, ld.gated, ld.w_tiled = inter, 1, int(self.tile_weights)
+                native.check(lib.xp_lane_set_layer(self.handle, i, l, C.byref(ld)), "xp_lane_set_layer", 0)
+        native.check(lib.xp_lane_commit(self.handle), "xp_lane_commit", 0)
+
+    def launch_once(self, lane: int = 0, lease_ms: float = 20.0, stream: torch.cuda.Stream | None = None) -> None:
+        s = stream or torch.cuda.current_stream(self.device)
+        native.check(native.kernels().xp_lane_launch(self.handle, lane, int(lease_ms * 1e6), s.cuda_stream),
+                     "xp_lane_launch", 4)
+
+    # -- serving threads ---------------------------------------------------------------------
+    def _lane_loop(self, lane: int, lease_ms: float, depth: int) -> None:
+        try:
+            torch.cuda.set_device(self.device)
+            stream = torch.cuda.Stream(self.device)
+            with torch.cuda.stream(stream):
+                self.launch_once(lane, lease_ms, stream)  # eager once: set-up work outside capture
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    self.launch_once(lane, lease_ms, stream)
+                pending: deque[torch.cuda.Event] = deque()
+                while not self._stop.is_set():
+                    graph.replay()
+                    ev = torch.cuda.Event()
+                    ev.record(stream)
+                    pending.append(ev)
+                    if len(pending) > depth:
+                        pending.popleft().synchronize()
+                stream.synchronize()
+        except Exception as e:  # pragma: no cover - surfaced through .errors
+            self.errors.append(f"lane {lane}: {e!r}")
+
+    def start(self, lease_ms: float = 20.0, depth: int = 3) -> None:
+        self._stop.clear()
+        for lane in range(self.n_lanes):
+            t = threading.Thread(target=self._lane_loop, args=(lane, lease_ms, depth), daemon=True, name=f"lane{lane}")
+            t.start()
+            self._threads.append(t)
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self.handle:
+            side = torch.cuda.Stream(self.device)
+            native.kernels().xp_lane_shutdown(self.handle, side.cuda_stream)
+            side.synchronize()
+        for t in self._threads:
+            t.join(30)
+        self._threads.clear()
+
+    def stats(self) -> dict:
+        served = (C.c_uint64 * len(self.instances))()
+        idle = (C.c_uint32 * self.n_lanes)()
+        status = C.c_uint32()
+        side = torch.cuda.Stream(self.device)
+        native.check(native.kernels().xp_lane_stats(self.handle, served, idle, C.byref(status), side.cuda_stream),
+                     "xp_lane_stats", 0)
+        return {"served": list(served), "idle_replays": list(idle), "status": status.value}
+
+    def close(self) -> None:
+        self.stop()
+        if self.handle:
+            native.kernels().xp_lane_destroy(self.handle)
+            self.handle = None
+        for st in self.instances:
+            st.slot.free()
+
+
+# ------------------------------------------------------------------ bring-up over torch.distributed
+
+@dataclass
+class RankContext:
+    rank: int
+    role: str
+    engines: dict[str, AttentionEngine] = field(default_factory=dict)
+    ffn: FfnRankRuntime | None = None
+    buffers: list[PeerBuffer] = field(default_factory=list)
+
+
+def build_rank(topo: Topology, rank: int, device, ecfg_for: dict[str, EngineConfig], group=None, n_lanes: int = 1,
+               policy: int = rt.POLICY_FIFO, tile_weights: bool = False) -> RankContext:
+    """Creates this rank's side of every Instance and exchanges arena handles with its peers.
+    Collective over ``group`` (any backend that supports object collectives)."""
+    import torch.distributed as dist
+
+    role = topo.role(rank)
+    ctx = RankContext(rank, role)
+    mine: dict[str, bytes] = {}
+    atn_local: dict[str, PeerBuffer] = {}
+    if role == "ffn":
+        ctx.ffn = FfnRankRuntime(device, n_lanes=n_lanes, policy=policy, tile_weights=tile_weights)
+        for p in topo.instances:
+            if rank in p.ffn_ranks:
+                st = ctx.ffn.add_instance(p, p.ffn_ranks.index(rank))
+                mine[f"ffn:{p.model_id}:{rank}"] = st.slot.handle()
+    elif role == "atn":
+        for p in topo.instances:
+            if p.atn_rank == rank:
+                buf = PeerBuffer(atn_slot_layout(p).total_bytes)
+                atn_local[p.model_id] = buf
+                ctx.buffers.append(buf)
+                mine[f"atn:{p.model_id}"] = buf.handle()
+    gathered: list[dict] = [None] * topo.world_size
+    dist.all_gather_object(gathered, mine, group=group)
+    handles = {k: v for d in gathered for k, v in d.items()}
+    if role == "ffn":
+        for st in ctx.ffn.instances:
+            st.atn_base = PeerBuffer.open(handles[f"atn:{st.place.model_id}"])
+        ctx.ffn.install()
+    elif role == "atn":
+        for p in topo.instances:
+            if p.atn_rank != rank:
+                continue
+            bases = [PeerBuffer.open(handles[f"ffn:{p.model_id}:{r}"]) for r in p.ffn_ranks]
+            port = FabricFfnPort(p, atn_local[p.model_id], bases, device)
+            aw = random_attention_weights(p.cfg, p.seed, device, torch.bfloat16)
+            ctx.engines[p.model_id] = AttentionEngine(p.cfg, aw, port, ecfg_for[p.model_id], device)
+    dist.barrier(group=group)
+    return ctx

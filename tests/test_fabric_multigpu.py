@@ -1,0 +1,30 @@
+"""Attention rank + FFN rank(s) as separate processes on separate GPUs (needs >= 2 GPUs)."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _run(nproc, extra):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29541", str(ROOT / "crosspool_b200/parallel/fabric_check.py")] + extra
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "FABRIC_CHECK_OK" in r.stdout
+
+
+def test_one_atn_one_ffn_matches_loopback_tokens():
+    _run(2, ["--tp", "1"])
+
+
+def test_one_atn_two_ffn_tensor_parallel():
+    _run(3, ["--tp", "2"])

@@ -1,0 +1,124 @@
+"""Executor-Lane kernels on one GPU. The invocation is published *before* the Lane iteration is
+enqueued, so nothing on the GPU waits for another launch: lane_wait finds the work at once, the two
+GEMMs run from the descriptor table, lane_complete publishes the completion record."""
+import ctypes as C
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _make(cfgs, n_lanes=1, policy=0, tile=False, cap=128):
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.parallel import fabric as F
+
+    ffn = F.FfnRankRuntime("cuda", n_lanes=n_lanes, policy=policy, tile_weights=tile)
+    places, atn = [], []
+    for i, (preset, layers) in enumerate(cfgs):
+        cfg = mc.preset(preset).with_layers(layers)
+        p = F.InstancePlacement(f"m{i}", cfg, seed=i + 1, atn_rank=0, ffn_ranks=(1,), capacity_rows=cap)
+        st = ffn.add_instance(p, 0)
+        buf = F.PeerBuffer(F.atn_slot_layout(p).total_bytes)  # stands in for the attention device's arena
+        st.atn_base = buf.ptr
+        places.append(p)
+        atn.append(buf)
+    ffn.install()
+    return ffn, places, atn
+
+
+def _publish(F, st, place, x, layer, seq, mode=2):
+    flay = F.ffn_slot_layout(place)
+    rows = x.shape[0]
+    st.slot.tensor(flay.input_offset, (place.capacity_rows, place.cfg.hidden_size), torch.bfloat16, "cuda")[:rows] = x
+    rec = st.slot.tensor(flay.record_offset, (64,), torch.int32, "cuda")
+    rec[0], rec[1], rec[2], rec[3] = rows, layer, mode, 0
+    rec[8] = seq  # InvocationRecord.sequence
+    torch.cuda.synchronize()
+
+
+def _result(F, buf, place, rows):
+    alay = F.atn_slot_layout(place)
+    out = buf.tensor(alay.output_offset, (place.capacity_rows, place.cfg.hidden_size), torch.bfloat16, "cuda")[:rows]
+    done = buf.tensor(alay.completion_offset, (64,), torch.int32, "cuda")
+    return out.clone(), int(done[0]), int(done[1]), int(done[4])
+
+
+def _ref(x, w):
+    inter = w.gate_up.shape[0] // 2
+    gu = (x.float() @ w.gate_up.float().t()).bfloat16().float()
+    act = (torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]).bfloat16().float()
+    return act @ w.down.float().t()
+
+
+@pytest.mark.parametrize("tile", [False, True])
+@pytest.mark.parametrize("rows", [1, 7, 64, 128])
+def test_lane_iteration_computes_the_layer_from_the_descriptor_table(rows, tile):
+    from crosspool_b200.ops import gemm
+    from crosspool_b200.parallel import fabric as F
+
+    ffn, places, atn = _make([("Qwen/Qwen3-0.6B", 3)], tile=tile)
+    try:
+        st, place = ffn.instances[0], places[0]
+        for seq, layer in enumerate([2, 0, 1], start=1):
+            x = (torch.randn(rows, place.cfg.hidden_size, device="cuda") * 0.5).bfloat16()
+            _publish(F, st, place, x, layer, seq)
+            ffn.launch_once(0, lease_ms=50)
+            torch.cuda.synchronize()
+            out, rc, nrows, done_seq = _result(F, atn[0], place, rows)
+            assert (rc, nrows, done_seq) == (0, rows, seq)
+            torch.testing.assert_close(out.float(), _ref(x, st.weights[layer]), atol=2e-2, rtol=2e-2)
+        s = ffn.stats()
+        assert s["served"] == [3] and s["status"] == 0
+        gemm.check_status(torch.device("cuda"))
+    finally:
+        ffn.close()
+
+
+def test_idle_lane_iteration_gives_up_after_its_lease_and_serves_later_work():
+    from crosspool_b200.parallel import fabric as F
+
+    ffn, places, atn = _make([("Qwen/Qwen3-0.6B", 1)])
+    try:
+        ffn.launch_once(0, lease_ms=5)  # nothing published: the bounded wait runs out, GEMMs are no-ops
+        torch.cuda.synchronize()
+        s = ffn.stats()
+        assert s["served"] == [0] and s["idle_replays"] == [1] and s["status"] == 0
+        st, place = ffn.instances[0], places[0]
+        x = (torch.randn(4, place.cfg.hidden_size, device="cuda") * 0.5).bfloat16()
+        _publish(F, st, place, x, 0, 1)
+        ffn.launch_once(0, lease_ms=5)
+        torch.cuda.synchronize()
+        out, rc, nrows, seq = _result(F, atn[0], place, 4)
+        assert (rc, nrows, seq) == (0, 4, 1)
+        torch.testing.assert_close(out.float(), _ref(x, st.weights[0]), atol=2e-2, rtol=2e-2)
+    finally:
+        ffn.close()
+
+
+def test_two_models_share_one_lane_in_fifo_order_and_bad_records_are_refused():
+    from crosspool_b200.parallel import fabric as F
+
+    ffn, places, atn = _make([("Qwen/Qwen3-0.6B", 2), ("Qwen/Qwen3-1.7B", 1)])
+    try:
+        xs = []
+        for i, (st, place) in enumerate(zip(ffn.instances, places)):
+            x = (torch.randn(5 + i, place.cfg.hidden_size, device="cuda") * 0.5).bfloat16()
+            xs.append(x)
+            _publish(F, st, place, x, 0, 1)
+        ffn.launch_once(0, lease_ms=20)
+        ffn.launch_once(0, lease_ms=20)
+        torch.cuda.synchronize()
+        for i, (st, place) in enumerate(zip(ffn.instances, places)):
+            out, rc, nrows, seq = _result(F, atn[i], place, 5 + i)
+            assert (rc, nrows, seq) == (0, 5 + i, 1)
+            torch.testing.assert_close(out.float(), _ref(xs[i], st.weights[0]), atol=2e-2, rtol=2e-2)
+        assert ffn.stats()["served"] == [1, 1]
+        # a record naming a layer that does not exist is answered with ProtocolMismatch, not executed
+        _publish(F, ffn.instances[0], places[0], xs[0], 99, 2)
+        ffn.launch_once(0, lease_ms=20)
+        torch.cuda.synchronize()
+        _, rc, nrows, seq = _result(F, atn[0], places[0], 5)
+        assert (rc, nrows, seq) == (2, 0, 2)
+    finally:
+        ffn.close()
