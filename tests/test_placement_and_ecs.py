@@ -1,0 +1,149 @@
+"""FFN placement with memory admission and the SLO-aware KV capacity policy (pure logic, fake
+channel, fake clock)."""
+import pytest
+
+from crosspool_b200.service.daemon.ecs import CapacityPolicy, Partition
+from crosspool_b200.service.daemon.placement import (DeviceSupply, ModelDemand, PlacementError, place_ffn_models,
+                                                     stage_bytes)
+
+GB = 1 << 30
+
+
+def _model(name, layers, layer_gb, tp, hidden=4096):
+    return ModelDemand(name, tuple([int(layer_gb * GB)] * layers), tp, hidden, max_rows=256, max_intermediate=4 * hidden)
+
+
+def test_whole_models_go_to_single_groups_and_balance_headroom():
+    devs = [DeviceSupply(d, 100 * GB) for d in (2, 3, 4, 5)]
+    r = place_ffn_models([_model("a", 10, 2.0, 2), _model("b", 10, 2.0, 2)], devs, ws_per_lane=1 << 20)
+    assert r.materializations == 4 and len(r.groups) == 2
+    used = [set(g.devices) for g in r.groups]
+    assert used[0].isdisjoint(used[1])  # best minimum headroom: the two models do not share devices
+    for g in r.groups:
+        assert (g.layer_begin, g.layer_end) == (0, 10)
+
+
+def test_a_model_that_does_not_fit_whole_is_split_by_layers():
+    devs = [DeviceSupply(d, 12 * GB) for d in (0, 1, 2)]
+    r = place_ffn_models([_model("big", 16, 1.0, 1)], devs, ws_per_lane=1 << 20)
+    ranges = sorted((g.layer_begin, g.layer_end) for g in r.groups)
+    assert ranges[0][0] == 0 and ranges[-1][1] == 16 and len(ranges) >= 2
+    assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+    assert all(h >= 0 for h in r.headroom.values())
+
+
+def test_admission_uses_the_peak_over_stages_and_the_margin():
+    devs = [DeviceSupply(0, 10 * GB)]
+    m = _model("m", 4, 2.0, 1)
+    place_ffn_models([m], devs, ws_per_lane=1 << 20)
+    with pytest.raises(PlacementError, match="do not fit"):
+        place_ffn_models([m], devs, margin_bytes=3 * GB, ws_per_lane=1 << 20)
+    with pytest.raises(PlacementError, match="exceeds"):
+        place_ffn_models([_model("t", 1, 0.1, 4)], devs)
+    s = stage_bytes(8 * GB, 1 * GB, 1, 4, lanes=2, ws_per_lane=64 << 20)
+    assert s.peak == s.execution_installation > s.fabric_join > s.weight_materialization - (64 << 20) - 1
+    r1 = place_ffn_models([m], [DeviceSupply(0, 64 * GB), DeviceSupply(1, 64 * GB)], ws_per_lane=1 << 20)
+    r2 = place_ffn_models([m], [DeviceSupply(0, 64 * GB), DeviceSupply(1, 64 * GB)], ws_per_lane=1 << 20)
+    assert r1.groups == r2.groups  # deterministic
+
+
+class FakeChannel:
+    def __init__(self, n, report):
+        self.demand = {i: (0, 0, 0, 0) for i in range(n)}
+        self.completion = {i: (0, 0) for i in range(n)}
+        self.commands = {i: [] for i in range(n)}
+        self.report = report
+
+    def read_demand(self, i):
+        return self.demand[i]
+
+    def read_completion(self, i):
+        return self.completion[i]
+
+    def publish_command(self, i, seq, target):
+        self.commands[i].append((seq, target))
+
+    def read_report(self, i):
+        return self.report
+
+    def complete(self, i):
+        seq, target = self.commands[i][-1]
+        self.completion[i] = (seq, target)
+
+
+def _policy(n=2, budget_free=100, floor=10, reservation=80, bundle=1):
+    ch = FakeChannel(n, (budget_free, 1000, 1))
+    parts = [Partition(i, f"m{i}:0", device=0, floor_bytes=floor, reservation_bytes=reservation, bundle_bytes=bundle)
+             for i in range(n)]
+    t = [0.0]
+    pol = CapacityPolicy(ch, parts, {0: 0}, utilization=1.0, clock=lambda: t[0])
+    return ch, parts, pol, t
+
+
+def test_freeze_splits_spare_equally_and_rejects_oversubscribed_floors():
+    ch, parts, pol, _ = _policy()
+    pol.freeze_pools()
+    assert [p.target_bytes for p in parts] == [50, 50] and pol.pools[0].unassigned_bytes == 0
+    assert ch.commands[0] == [(1, 50)] and ch.commands[1] == [(1, 50)]
+    ch2, parts2, pol2, _ = _policy(floor=60)
+    with pytest.raises(ValueError, match="floors"):
+        pol2.freeze_pools()
+
+
+def test_borrower_is_funded_by_shrinking_one_idle_donor_then_growing():
+    ch, parts, pol, t = _policy()
+    pol.freeze_pools()
+    for i in (0, 1):
+        ch.complete(i)
+    ch.demand[0] = (1, 70, int(5e9), 50)   # model 0 needs 70 bytes by t = 5 s; model 1 is idle
+    ev = pol.tick()
+    assert ev.kind == "shrink" and ev.partition == "m1:0" and ev.bytes == 20
+    assert parts[1].target_bytes == 30 and ch.commands[1][-1] == (2, 30)
+    assert pol.tick() is None               # one operation at a time: the shrink has not completed
+    ch.complete(1)
+    ev = pol.tick()
+    assert ev.kind == "grow" and ev.partition == "m0:0" and parts[0].target_bytes == 70
+    assert pol.pools[0].unassigned_bytes == 0
+
+
+def test_overdue_borrowers_first_then_earliest_deadline_and_donor_choice():
+    ch, parts, pol, t = _policy(n=3, budget_free=90, floor=10, reservation=90)
+    pol.freeze_pools()
+    for i in range(3):
+        ch.complete(i)
+    assert [p.target_bytes for p in parts] == [30, 30, 30]
+    t[0] = 10.0
+    ch.demand[0] = (1, 50, int(20e9), 30)   # due at 20 s
+    ch.demand[1] = (1, 40, int(5e9), 30)    # overdue (due at 5 s, now 10 s)
+    ch.demand[2] = (1, 12, int(99e9), 30)   # has demand but far below its target: can donate 18
+    ev = pol.tick()
+    assert ev.kind == "shrink" and ev.partition == "m2:0" and "for=m1:0" in ev.detail and ev.bytes == 10
+    ch.complete(2)
+    ev = pol.tick()
+    assert ev.kind == "grow" and ev.partition == "m1:0" and parts[1].target_bytes == 40
+    ch.complete(1)
+    ev = pol.tick()
+    assert ev.kind == "shrink" and ev.partition == "m2:0" and "for=m0:0" in ev.detail and ev.bytes == 8
+    # floors are never taken
+    assert parts[2].target_bytes == 12 >= parts[2].floor_bytes
+
+
+def test_command_is_rejected_when_the_demand_witness_changed():
+    ch, parts, pol, _ = _policy(budget_free=120)
+    pol.freeze_pools()
+    for i in (0, 1):
+        ch.complete(i)
+    pol.pools[0].unassigned_bytes = 20
+    ch.demand[0] = (1, 70, int(5e9), 60)
+    orig = ch.read_demand
+    calls = {"n": 0}
+
+    def flaky(i):
+        calls["n"] += 1
+        if i == 0 and calls["n"] > 3:  # the instance re-evaluated its demand between decision and command
+            return (2, 65, int(6e9), 60)
+        return orig(i)
+
+    ch.read_demand = flaky
+    ev = pol.tick()
+    assert ev.kind == "reject" and parts[0].target_bytes == 60
