@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 11
+#define XP_ABI_VERSION 12
 
 #ifdef __cplusplus
 extern "C" {
@@ -148,6 +148,7 @@ typedef struct XpDecodeAttnArgs {
   const int* seq_lens;        /* [batch] tokens in cache including the current one */
   int batch, q_heads, kv_heads, head_dim, page_size, max_blocks, num_splits;
   float scale;
+  int chunk_tokens;           /* > 0: slices of this many tokens (num_splits = ceil(max_len / chunk)) */
 } XpDecodeAttnArgs;
 
 typedef struct XpPrefillAttnArgs {

@@ -62,10 +62,17 @@ decode_attn_kernel(XpDecodeAttnArgs a) {
   const int G = a.q_heads / a.kv_heads;
   const int len = a.seq_lens[b];
   const int nsplit = gridDim.x;
-  int chunk = (len + nsplit - 1) / nsplit;
-  chunk = (chunk + 15) & ~15;
+  // Fixed-size slices (chunk_tokens > 0) give every CTA the same amount of work whatever the
+  // sequence length, so long and short sequences in one batch balance across the SMs; slices
+  // past a sequence's end have nothing to do. Otherwise the sequence is cut into nsplit even parts.
+  int chunk = a.chunk_tokens;
+  if (chunk <= 0) {
+    chunk = (len + nsplit - 1) / nsplit;
+    chunk = (chunk + 15) & ~15;
+  }
   const int t0 = split * chunk;
   const int t1 = min(len, t0 + chunk);
+  if (a.chunk_tokens > 0 && nsplit > 1 && t0 >= len) return;  // the merge kernel skips this slice
 
   // q pre-scaled into the exp2 domain
   const float qscale = a.scale * 1.4426950408889634f;
@@ -222,6 +229,10 @@ template <int D>
 __global__ void decode_combine_kernel(XpDecodeAttnArgs a, int nsplit) {
   const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const float* ws = a.ws + (static_cast<size_t>(b) * a.q_heads + hq) * nsplit * (D + 2);
+  if (a.chunk_tokens > 0) {
+    const int len = a.seq_lens[b];
+    nsplit = min(nsplit, (len + a.chunk_tokens - 1) / a.chunk_tokens);  // slices that ran
+  }
   float mm = -CUDART_INF_F;
   for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, ws[s * (D + 2) + D]);
   float ll = 0.f, av = 0.f;

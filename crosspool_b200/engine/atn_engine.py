@@ -151,7 +151,7 @@ class AttentionEngine:
         self._pre_words = 3 * P + 4 * S + S * self.max_blocks
         self.pre_meta = torch.zeros(self._pre_words, dtype=torch.int32, device=dev)
         self.pre_meta_host = torch.zeros(self._pre_words, dtype=torch.int32).pin_memory()
-        splits = max(A.decode_splits(b, cfg.num_kv_heads, e.max_seq_len) for b in (1, B))
+        splits = max(A.decode_plan(b, cfg.num_kv_heads, e.max_seq_len)[0] for b in (1, B))
         self.attn_ws = torch.zeros(B * cfg.num_q_heads * max(splits, 1) * (cfg.head_dim + 2), dtype=torch.float32,
                                    device=dev)
 
@@ -216,14 +216,14 @@ class AttentionEngine:
         cfg = self.cfg
         ids, pos, slots, lens, table = self._dec_views(B)
         A.embedding(ids, self.w.embed, out=self.resid[:B])
-        splits = A.decode_splits(B, cfg.num_kv_heads, self.ecfg.max_seq_len)
+        splits, chunk = A.decode_plan(B, cfg.num_kv_heads, self.ecfg.max_seq_len)
 
         def attn(l, lw, rows):
             A.rope_kv_write(self.qkv[:rows], self.q[:rows], self.kv.k[l], self.kv.v[l], pos, slots,
                             q_heads=cfg.num_q_heads, kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim,
                             theta=cfg.rope_theta, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_norm_eps)
             A.paged_decode(self.q[:rows], self.kv.k[l], self.kv.v[l], table, lens, out=self.attn_out[:rows],
-                           num_splits=splits, ws=self.attn_ws)
+                           num_splits=splits, ws=self.attn_ws, chunk_tokens=chunk)
 
         self._layers(B, MODE_DECODE, attn)
         self._head(B, B, None)

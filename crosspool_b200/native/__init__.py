@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 11
+EXPECTED_ABI = 12
 HERE = Path(__file__).resolve().parent
 
 
@@ -193,6 +193,7 @@ class DecodeAttnArgs(C.Structure):
         ("max_blocks", C.c_int),
         ("num_splits", C.c_int),
         ("scale", C.c_float),
+        ("chunk_tokens", C.c_int),
     ]
 
 

@@ -40,10 +40,19 @@ def decode_splits(batch: int, kv_heads: int, max_len: int) -> int:
     return native.kernels().xp_decode_attn_splits(batch, kv_heads, max_len)
 
 
+def decode_plan(batch: int, kv_heads: int, max_len: int) -> tuple[int, int]:
+    """(num_splits, chunk_tokens) for a decode batch. Large batches use fixed 256-token slices so that
+    sequences of very different lengths balance across the SMs; small ones split each sequence evenly."""
+    if batch * kv_heads >= 296 and max_len > 256:
+        chunk = 256
+        return (max_len + chunk - 1) // chunk, chunk
+    return decode_splits(batch, kv_heads, max_len), 0
+
+
 def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                  seq_lens: torch.Tensor, *, out: torch.Tensor | None = None, num_splits: int = 0,
-                 ws: torch.Tensor | None = None, scale: float | None = None, max_len: int | None = None
-                 ) -> torch.Tensor:
+                 ws: torch.Tensor | None = None, scale: float | None = None, max_len: int | None = None,
+                 chunk_tokens: int = 0) -> torch.Tensor:
     """q ``[batch, q_heads, d]`` against caches ``[pages, page, kv_heads, d]``."""
     batch, q_heads, d = q.shape
     page_size, kv_heads = k_cache.shape[1], k_cache.shape[2]
@@ -61,6 +70,7 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     a.batch, a.q_heads, a.kv_heads, a.head_dim = batch, q_heads, kv_heads, d
     a.page_size, a.max_blocks, a.num_splits = page_size, block_table.stride(0), num_splits
     a.scale = scale if scale is not None else d ** -0.5
+    a.chunk_tokens = chunk_tokens
     native.check(native.kernels().xp_decode_attn(C.byref(a), _stream(q.device)), "xp_decode_attn",
                  2 if num_splits > 1 else 1)
     return out

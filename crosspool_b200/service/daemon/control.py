@@ -36,7 +36,8 @@ from ..wire import (AgentStartupAdmission, AtnAgentRegistration, FabricPhase, Fa
                     ReadinessSnapshot, Role, ShardPlacement, TransportArenaBinding)
 from .placement import DeviceSupply, ModelDemand, PlacementError, place_ffn_models
 
-ABI_VERSION = 11
+from ...native import EXPECTED_ABI as ABI_VERSION  # noqa: E402  (one number for native code and wire)
+
 HEARTBEAT_STALE_SECONDS = 15.0       # reference registration.py:27
 PHASE_TIMEOUT_SECONDS = 60.0         # reference control.py:81-86
 INSTANCE_STARTUP_SECONDS = 600.0     # reference control.py:87

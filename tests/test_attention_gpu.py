@@ -139,3 +139,19 @@ def test_embedding_and_argmax():
     assert int(got[3]) == 77
     lb = logits.bfloat16()
     assert torch.equal(A.argmax(lb).long(), lb.float().argmax(-1))
+
+
+def test_paged_decode_fixed_chunks_balance_mixed_lengths():
+    from crosspool_b200.ops import attention as A
+
+    torch.manual_seed(4)
+    d, hq, hkv, page = 128, 16, 8, 16
+    lens = [1, 255, 256, 257, 700, 1500, 33] * 6
+    kc, vc, table = _paged(len(lens), lens, hkv, d, page)
+    q = torch.randn(len(lens), hq, d, device="cuda").bfloat16()
+    sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    splits, chunk = A.decode_plan(len(lens), hkv, 1520)
+    assert chunk == 256 and splits == 6
+    out = A.paged_decode(q, kc, vc, table, sl, num_splits=splits, chunk_tokens=chunk)
+    ref = A.paged_decode(q, kc, vc, table, sl, num_splits=1)
+    torch.testing.assert_close(out.float(), ref.float(), atol=1e-2, rtol=1e-2)
