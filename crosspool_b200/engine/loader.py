@@ -1,0 +1,195 @@
+"""FFN weight loader: reads only the local tensor-parallel shard of every projection.
+
+For each layer the loader turns the :class:`FfnModelSpec` into read descriptors (which rows or
+columns of which checkpoint tensor), reader threads stage the slices through a bounded set of pinned
+host slots, and the slices are copied to the device and assembled into the layout the kernels want:
+gate rows followed by up rows (``CONCATENATED``) for ``i_proj`` and the column shard for ``o_proj``.
+True TP as in the reference (src/xpool/runtime/ffnagent/preparation.py:164-334, loader.py:148-286):
+gate/up split by output rows, down by input columns, every expert alike; the output bias lives on TP
+rank 0 only so that the reduction adds it once.
+"""
+
+from __future__ import annotations
+
+import queue
+import threading
+from concurrent.futures import ThreadPoolExecutor
+from dataclasses import dataclass
+
+import torch
+
+from ..ffn import DenseFfnSpec, FfnModelSpec, GateUpOrder, MoeFfnSpec
+from ..models.weights import FfnLayerWeights
+from .checkpoint import CheckpointKeyView
+
+
+@dataclass(frozen=True)
+class TensorRead:
+    key: str
+    rows: slice | None = None   # slice of dim -2
+    cols: slice | None = None   # slice of dim -1
+    expert: int | None = None   # leading index of a stacked tensor
+    deinterleave: int | None = None  # 0: even rows (gate), 1: odd rows (up) of an interleaved tensor
+
+
+def _local(n: int, rank: int, size: int, quantum: int = 1) -> slice:
+    if n % (size * quantum):
+        raise ValueError(f"dimension {n} is not divisible into {size} shards of multiples of {quantum}")
+    w = n // size
+    return slice(rank * w, (rank + 1) * w)
+
+
+class _Reader:
+    """Opens each safetensors file once per thread and reads slices without loading whole tensors."""
+
+    def __init__(self, view: CheckpointKeyView):
+        self.view = view
+        self._tls = threading.local()
+
+    def _file(self, name: str):
+        from safetensors import safe_open
+
+        cache = getattr(self._tls, "files", None)
+        if cache is None:
+            cache = self._tls.files = {}
+        if name not in cache:
+            cache[name] = safe_open(str(self.view.root / name), framework="pt")
+        return cache[name]
+
+    def read(self, r: TensorRead) -> torch.Tensor:
+        sl = self._file(self.view.key_to_file[r.key]).get_slice(r.key)
+        nd = len(sl.get_shape())
+        idx: list = [slice(None)] * nd
+        if r.expert is not None:
+            idx[0] = r.expert
+        if r.deinterleave is not None:
+            n = sl.get_shape()[-2]
+            rows = r.rows or slice(0, n // 2)
+            idx[-2] = slice(2 * rows.start + r.deinterleave, 2 * rows.stop, 2)
+        elif r.rows is not None:
+            idx[-2 if nd >= 2 else -1] = r.rows
+        if r.cols is not None:
+            idx[-1] = r.cols
+        return sl[tuple(idx)]
+
+
+class PinnedStager:
+    """A bounded pool of pinned host slots: readers fill them, the copier drains them to the device,
+    so host memory stays bounded however large the model is ([ffn.loader] parallelism slots)."""
+
+    def __init__(self, slots: int, device):
+        self.device = torch.device(device)
+        self._sem = threading.Semaphore(max(1, slots))
+        self.pinned = self.device.type == "cuda"
+
+    def to_device(self, t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        with self._sem:
+            t = t.to(dtype).contiguous()
+            if self.pinned:
+                t = t.pin_memory()
+                out = t.to(self.device, non_blocking=True)
+                torch.cuda.current_stream(self.device).synchronize()
+                return out
+            return t.to(self.device)
+
+
+def _dense_reads(l: DenseFfnSpec, rank: int, size: int):
+    rows = _local(l.intermediate_size, rank, size)
+    ip = l.i_proj
+    reads = {}
+    if ip.packed is not None:
+        if ip.source_order == GateUpOrder.INTERLEAVED:
+            reads["gate"] = TensorRead(ip.packed.weight_key, rows=rows, deinterleave=0)
+            reads["up"] = TensorRead(ip.packed.weight_key, rows=rows, deinterleave=1)
+        else:
+            reads["gate"] = TensorRead(ip.packed.weight_key, rows=rows)
+            reads["up"] = TensorRead(ip.packed.weight_key, rows=slice(l.intermediate_size + rows.start, l.intermediate_size + rows.stop))
+    else:
+        if ip.gate is not None:
+            reads["gate"] = TensorRead(ip.gate.weight_key, rows=rows)
+            if ip.gate.bias_key:
+                reads["gate_bias"] = TensorRead(ip.gate.bias_key, rows=rows)
+        reads["up"] = TensorRead(ip.up.weight_key, rows=rows)
+        if ip.up.bias_key:
+            reads["up_bias"] = TensorRead(ip.up.bias_key, rows=rows)
+    reads["down"] = TensorRead(l.o_proj.weight_key, cols=rows)
+    if l.o_proj.bias_key and rank == 0:
+        reads["down_bias"] = TensorRead(l.o_proj.bias_key)
+    return reads
+
+
+def _moe_reads(l: MoeFfnSpec, rank: int, size: int, experts: range):
+    rows = _local(l.moe_intermediate_size, rank, size)
+    ex = l.experts
+    reads = {"router": TensorRead(l.router_weight_key)}
+    if l.router_bias_key:
+        reads["router_bias"] = TensorRead(l.router_bias_key)
+    if l.correction_bias_key:
+        reads["correction_bias"] = TensorRead(l.correction_bias_key)
+    for e in experts:
+        if ex.per_expert:
+            reads[f"gate{e}"] = TensorRead(ex.gate_key.format(expert=e), rows=rows)
+            reads[f"up{e}"] = TensorRead(ex.up_key.format(expert=e), rows=rows)
+            reads[f"down{e}"] = TensorRead(ex.down_key.format(expert=e), cols=rows)
+        else:
+            inter = l.moe_intermediate_size
+            if l.source_order == GateUpOrder.INTERLEAVED:
+                reads[f"gate{e}"] = TensorRead(ex.packed_key, rows=rows, expert=e, deinterleave=0)
+                reads[f"up{e}"] = TensorRead(ex.packed_key, rows=rows, expert=e, deinterleave=1)
+            else:
+                reads[f"gate{e}"] = TensorRead(ex.packed_key, rows=rows, expert=e)
+                reads[f"up{e}"] = TensorRead(ex.packed_key, rows=slice(inter + rows.start, inter + rows.stop), expert=e)
+            reads[f"down{e}"] = TensorRead(ex.down_key, cols=rows, expert=e)
+    if l.num_shared_experts:
+        srows = _local(l.shared_intermediate_size, rank, size)
+        reads["shared_gate"] = TensorRead(l.shared_gate_key, rows=srows)
+        reads["shared_up"] = TensorRead(l.shared_up_key, rows=srows)
+        reads["shared_down"] = TensorRead(l.shared_down_key, cols=srows)
+    return reads
+
+
+def materialize_layer_weights(spec: FfnModelSpec, view: CheckpointKeyView, layer: int, *, tp_rank: int = 0, tp_size: int = 1,
+                              device="cpu", dtype: torch.dtype = torch.bfloat16, parallelism: int = 4,
+                              experts: range | None = None) -> FfnLayerWeights:
+    """Loads one layer's local shard. ``experts`` restricts a MoE layer to a range (expert parallelism)."""
+    if spec.quantization != "none":
+        raise NotImplementedError(f"quantised checkpoints ({spec.quantization}) load through ops.quant")
+    l = spec.layers[layer]
+    stager, reader = PinnedStager(parallelism, device), _Reader(view)
+    if isinstance(l, DenseFfnSpec):
+        reads = _dense_reads(l, tp_rank, tp_size)
+    else:
+        experts = experts if experts is not None else range(l.num_experts)
+        reads = _moe_reads(l, tp_rank, tp_size, experts)
+
+    def fetch(item):
+        name, r = item
+        bias = name.endswith("bias")
+        return name, stager.to_device(reader.read(r), torch.float32 if bias else dtype)
+
+    with ThreadPoolExecutor(max_workers=max(1, parallelism)) as pool:
+        got = dict(pool.map(fetch, reads.items()))
+    if isinstance(l, DenseFfnSpec):
+        gated = "gate" in got
+        gate_up = torch.cat([got["gate"], got["up"]], 0) if gated else got["up"]
+        gub = None
+        if "up_bias" in got:
+            gub = torch.cat([got["gate_bias"], got["up_bias"]], 0) if "gate_bias" in got else got["up_bias"]
+        w = FfnLayerWeights(gate_up, got["down"], gate_up_bias=gub, down_bias=got.get("down_bias"))
+        w.extra["gated"] = gated
+        return w
+    gate_up = torch.stack([torch.cat([got[f"gate{e}"], got[f"up{e}"]], 0) for e in experts])
+    down = torch.stack([got[f"down{e}"] for e in experts])
+    w = FfnLayerWeights(gate_up, down, router=got["router"])
+    if "shared_gate" in got:
+        w.shared_gate_up = torch.cat([got["shared_gate"], got["shared_up"]], 0)
+        w.shared_down = got["shared_down"]
+    for k in ("router_bias", "correction_bias"):
+        if k in got:
+            w.extra[k] = got[k]
+    w.extra["experts"] = (experts.start, experts.stop)
+    return w
+
+
+def materialize_model_weights(spec: FfnModelSpec, view: CheckpointKeyView, layers: range, **kw) -> list[FfnLayerWeights]:
+    return [materialize_layer_weights(spec, view, l, **kw) for l in layers]

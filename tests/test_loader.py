@@ -1,0 +1,128 @@
+"""Architecture adapters, checkpoint coverage and TP-sharded loading from real safetensors files."""
+import json
+
+import pytest
+import torch
+from safetensors.torch import save_file
+
+from crosspool_b200.engine import checkpoint as ck
+from crosspool_b200.engine import loader
+from crosspool_b200.ffn import ActivationKind, DenseFfnSpec, MoeFfnSpec, RouterAlgorithm
+from crosspool_b200.models import adapters
+
+QWEN3 = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 64, "intermediate_size": 256, "num_hidden_layers": 2,
+         "num_attention_heads": 4, "vocab_size": 100, "hidden_act": "silu", "torch_dtype": "bfloat16"}
+QWEN3_MOE = {"architectures": ["Qwen3MoeForCausalLM"], "hidden_size": 64, "num_hidden_layers": 1, "num_experts": 4,
+             "num_experts_per_tok": 2, "moe_intermediate_size": 128, "norm_topk_prob": True, "num_attention_heads": 4,
+             "vocab_size": 100}
+
+
+def _dense_ckpt(tmp_path, shards=2):
+    g = torch.Generator().manual_seed(0)
+    tensors = {"model.embed_tokens.weight": torch.randn(100, 64, generator=g)}
+    for i in range(2):
+        p = f"model.layers.{i}."
+        tensors[p + "mlp.gate_proj.weight"] = torch.randn(256, 64, generator=g)
+        tensors[p + "mlp.up_proj.weight"] = torch.randn(256, 64, generator=g)
+        tensors[p + "mlp.down_proj.weight"] = torch.randn(64, 256, generator=g)
+        tensors[p + "self_attn.q_proj.weight"] = torch.randn(64, 64, generator=g)
+    keys = sorted(tensors)
+    wm = {}
+    for s in range(shards):
+        part = {k: tensors[k] for k in keys[s::shards]}
+        name = f"model-{s:05d}-of-{shards:05d}.safetensors"
+        save_file(part, str(tmp_path / name))
+        wm.update({k: name for k in part})
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wm}))
+    (tmp_path / "config.json").write_text(json.dumps(QWEN3))
+    return tensors
+
+
+def test_dense_spec_coverage_and_sharded_load(tmp_path):
+    tensors = _dense_ckpt(tmp_path)
+    view = ck.read_checkpoint_key_view(tmp_path)
+    spec = adapters.compile_ffn_spec("q", QWEN3, view.keys())
+    assert spec.num_layers == 2 and isinstance(spec.layers[0], DenseFfnSpec)
+    assert spec.layers[0].activation == ActivationKind.SILU and spec.payload_dtype == "bfloat16"
+    ck.validate_ffn_coverage(spec, view)
+    full = loader.materialize_layer_weights(spec, view, 1, dtype=torch.float32)
+    g, u, d = (tensors[f"model.layers.1.mlp.{n}_proj.weight"] for n in ("gate", "up", "down"))
+    assert torch.equal(full.gate_up, torch.cat([g, u])) and torch.equal(full.down, d)
+    parts = [loader.materialize_layer_weights(spec, view, 1, tp_rank=r, tp_size=4, dtype=torch.float32) for r in range(4)]
+    for r, p in enumerate(parts):
+        rows = slice(64 * r, 64 * (r + 1))
+        assert torch.equal(p.gate_up, torch.cat([g[rows], u[rows]])) and torch.equal(p.down, d[:, rows])
+    x = torch.randn(3, 64)
+    ref = (torch.nn.functional.silu(x @ g.t()) * (x @ u.t())) @ d.t()
+    tp = sum((torch.nn.functional.silu(x @ p.gate_up[:64].t()) * (x @ p.gate_up[64:].t())) @ p.down.t() for p in parts)
+    torch.testing.assert_close(tp, ref, atol=1e-4, rtol=1e-4)
+    assert spec.digest() == adapters.compile_ffn_spec("q", QWEN3, view.keys()).digest()
+
+
+def test_coverage_rejects_missing_and_unexplained_tensors(tmp_path):
+    _dense_ckpt(tmp_path, shards=1)
+    view = ck.read_checkpoint_key_view(tmp_path)
+    spec = adapters.compile_ffn_spec("q", QWEN3)
+    del view.key_to_file["model.layers.0.mlp.up_proj.weight"]
+    with pytest.raises(ck.CheckpointError, match="misses 1"):
+        ck.validate_ffn_coverage(spec, view)
+    with pytest.raises(adapters.UnsupportedModel, match="misses"):
+        adapters.compile_ffn_spec("q", QWEN3, view.keys())
+    view = ck.read_checkpoint_key_view(tmp_path)
+    view.key_to_file["model.layers.0.mlp.surprise.weight"] = "x"
+    with pytest.raises(ck.CheckpointError, match="does not cover"):
+        ck.validate_ffn_coverage(spec, view)
+
+
+def test_moe_spec_and_expert_parallel_load(tmp_path):
+    g = torch.Generator().manual_seed(1)
+    t = {"model.layers.0.mlp.gate.weight": torch.randn(4, 64, generator=g)}
+    for e in range(4):
+        for n, shape in (("gate_proj", (128, 64)), ("up_proj", (128, 64)), ("down_proj", (64, 128))):
+            t[f"model.layers.0.mlp.experts.{e}.{n}.weight"] = torch.randn(*shape, generator=g)
+    save_file(t, str(tmp_path / "model.safetensors"))
+    view = ck.read_checkpoint_key_view(tmp_path)
+    spec = adapters.compile_ffn_spec("m", QWEN3_MOE, view.keys())
+    l = spec.layers[0]
+    assert isinstance(l, MoeFfnSpec) and l.router_algorithm == RouterAlgorithm.SOFTMAX and l.effective_topk == 2
+    ck.validate_ffn_coverage(spec, view)
+    w = loader.materialize_layer_weights(spec, view, 0, dtype=torch.float32, tp_rank=1, tp_size=2, experts=range(2, 4))
+    assert w.gate_up.shape == (2, 128, 64) and w.down.shape == (2, 64, 64) and w.router.shape == (4, 64)
+    assert torch.equal(w.gate_up[0, :64], t["model.layers.0.mlp.experts.2.gate_proj.weight"][64:128])
+    assert torch.equal(w.down[1], t["model.layers.0.mlp.experts.3.down_proj.weight"][:, 64:128])
+
+
+@pytest.mark.parametrize("arch,cfg,check", [
+    ("LlamaForCausalLM", {"hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 1, "mlp_bias": True},
+     lambda s: s.layers[0].o_proj.bias_key == "model.layers.0.mlp.down_proj.bias"),
+    ("OPTForCausalLM", {"hidden_size": 64, "ffn_dim": 256, "num_hidden_layers": 1, "activation_function": "relu"},
+     lambda s: not s.layers[0].i_proj.gated and s.layers[0].activation == ActivationKind.RELU
+     and s.layers[0].o_proj.weight_key == "model.decoder.layers.0.fc2.weight"),
+    ("DeepseekV2ForCausalLM", {"hidden_size": 64, "intermediate_size": 256, "moe_intermediate_size": 32,
+                               "num_hidden_layers": 3, "n_routed_experts": 8, "num_experts_per_tok": 2,
+                               "first_k_dense_replace": 1, "n_shared_experts": 2, "routed_scaling_factor": 16.0},
+     lambda s: isinstance(s.layers[0], DenseFfnSpec) and isinstance(s.layers[1], MoeFfnSpec)
+     and s.layers[1].num_shared_experts == 2 and s.layers[1].routed_scaling_factor == 16.0
+     and s.layers[1].router_precision.value == "fp32_logits"),
+    ("Glm4MoeLiteForCausalLM", {"hidden_size": 64, "intermediate_size": 256, "moe_intermediate_size": 32,
+                                "num_hidden_layers": 2, "n_routed_experts": 8, "num_experts_per_tok": 2,
+                                "first_k_dense_replace": 1, "n_shared_experts": 1},
+     lambda s: s.layers[1].router_algorithm == RouterAlgorithm.SIGMOID
+     and s.layers[1].correction_bias_key.endswith("e_score_correction_bias")),
+    ("GptOssForCausalLM", {"hidden_size": 64, "intermediate_size": 64, "num_hidden_layers": 1, "num_local_experts": 4,
+                           "num_experts_per_tok": 2, "quantization_config": {"quant_method": "mxfp4"}},
+     lambda s: s.quantization == "mxfp4" and s.layers[0].gate_transform.alpha == 1.702
+     and s.layers[0].gate_transform.limit == 7.0 and s.layers[0].experts.packed_key.endswith("gate_up_proj_blocks")),
+])
+def test_architecture_adapters(arch, cfg, check):
+    spec = adapters.compile_ffn_spec("x", {"architectures": [arch], **cfg})
+    assert check(spec)
+
+
+def test_unsupported_models_are_named():
+    with pytest.raises(adapters.UnsupportedModel, match="no FFN adapter"):
+        adapters.compile_ffn_spec("x", {"architectures": ["MambaForCausalLM"], "hidden_size": 8})
+    with pytest.raises(adapters.UnsupportedModel, match="quantization"):
+        adapters.compile_ffn_spec("x", {**QWEN3, "quantization_config": {"quant_method": "awq"}})
+    with pytest.raises(adapters.UnsupportedModel, match="misses 'intermediate_size'"):
+        adapters.compile_ffn_spec("x", {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 8, "num_hidden_layers": 1})
