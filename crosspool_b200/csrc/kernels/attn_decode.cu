@@ -86,9 +86,11 @@ decode_attn_kernel(XpDecodeAttnArgs a) {
   }
   __syncthreads();
 
-  const int grp = threadIdx.x >> 3, gl = threadIdx.x & 7;
-  // this lane's slice of every query head, kept in registers (shared-memory reads
-  // here would collide on banks: the 8 lanes of a token sit 64 bytes apart)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g4 = lane >> 3, gl = lane & 7;  // token within the warp's group of four, lane within the token
+  // A lane owns E dims of every head: 16-byte chunk `gl` of the row, and for D = 128 also chunk
+  // `gl + 8` (so that the eight lanes of a token read one contiguous 128-byte run per load).
+  auto dim_of = [&](int e) { return e < 8 ? gl * 8 + e : D / 2 + gl * 8 + (e - 8); };
   // (for 8 heads per KV head the registers do not suffice; those read shared memory)
   constexpr bool kQInRegs = GMAX <= 4;
   float qr[kQInRegs ? GMAX : 1][E];
@@ -96,7 +98,7 @@ decode_attn_kernel(XpDecodeAttnArgs a) {
 #pragma unroll
     for (int g = 0; g < GMAX; ++g)
 #pragma unroll
-      for (int e = 0; e < E; ++e) qr[g][e] = q_s[g][gl * E + e];
+      for (int e = 0; e < E; ++e) qr[g][e] = q_s[g][dim_of(e)];
   }
   const int page_shift = 31 - __clz(a.page_size);  // page size is a power of two
   const int page_mask = a.page_size - 1;
@@ -111,39 +113,66 @@ decode_attn_kernel(XpDecodeAttnArgs a) {
   const int* table = a.block_table + static_cast<size_t>(b) * a.max_blocks;
   const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(a.k_cache);
   const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.v_cache);
-  // The trip count is uniform across the CTA (lanes past the slice's end idle
-  // inside the loop) because the dot-product shuffles below name every lane.
-  // The next iteration's K/V rows are requested before the current ones are
-  // consumed, which doubles the bytes each SM keeps in flight.
-  auto fetch = [&](int t, RawVec<E>& kr, RawVec<E>& vr) {
-    if (t < t1) {
-      const int page = table[t >> page_shift];
-      const size_t tok = (static_cast<size_t>(page) << page_shift) + (t & page_mask);
-      const size_t off = (tok * a.kv_heads + hk) * D + gl * E;
-      load_raw<E>(kc + off, kr);
-      load_raw<E>(vc + off, vr);
-    } else {
-      zero_raw<E>(kr);
-      zero_raw<E>(vr);
+
+  // K/V rows stream through a per-warp ring in shared memory filled with cp.async, so the bytes an
+  // SM keeps in flight are set by the ring depth, not by registers (the kernel is bound by HBM
+  // latency x bandwidth: about 64 KB must be in flight per SM). Each iteration a warp consumes four
+  // tokens; iteration i of warp w covers tokens t0 + (i * 4 + w) * 4 .. + 3. Trip counts are
+  // uniform across the CTA because the dot-product shuffles name every lane.
+  constexpr int kStages = 4;
+  constexpr int kRow = D * 2;             // bytes of one K (or V) row of this head
+  constexpr int kStageBytes = 8 * kRow;   // 4 tokens x (K + V)
+  extern __shared__ __align__(16) uint8_t ring_raw[];
+  uint8_t* ring = ring_raw + static_cast<size_t>(warp) * kStages * kStageBytes;
+  constexpr int kChunksPerRow = kRow / 16;
+  constexpr int kLoads = 8 * kChunksPerRow / 32;  // 16-byte copies per lane per stage (4 or 2)
+  const int iters = (t1 - t0 + 15) / 16;
+  auto issue = [&](int it) {
+    if (it < iters) {
+      uint8_t* st = ring + (it % kStages) * kStageBytes;
+      const int tbase = t0 + (it * 4 + warp) * 4;
+#pragma unroll
+      for (int j = 0; j < kLoads; ++j) {
+        const int c = lane + 32 * j;                 // chunk index within the stage
+        const int row = c / kChunksPerRow;           // 0..3 K rows, 4..7 V rows
+        const int part = c % kChunksPerRow;
+        const int t = tbase + (row & 3);
+        const bool ok = t < t1;
+        const int tt = ok ? t : t0;
+        const int page = table[tt >> page_shift];
+        const size_t tok = (static_cast<size_t>(page) << page_shift) + (tt & page_mask);
+        const __nv_bfloat16* src = (row < 4 ? kc : vc) + (tok * a.kv_heads + hk) * D + part * 8;
+        const uint32_t dst = sm100::smem_u32(st + row * kRow + part * 16);
+        const int sz = ok ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz));
+      }
     }
+    asm volatile("cp.async.commit_group;");
   };
-  RawVec<E> kr, vr, kn, vn;
-  fetch(t0 + grp, kr, vr);
-  for (int tb = t0; tb < t1; tb += 16) {
-    const int t = tb + grp;
+#pragma unroll
+  for (int i = 0; i < kStages - 1; ++i) issue(i);
+  for (int it = 0; it < iters; ++it) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kStages - 2) : "memory");
+    __syncwarp();
+    issue(it + kStages - 1);  // refills the slot consumed in the previous iteration
+    const uint8_t* st = ring + (it % kStages) * kStageBytes;
+    const int t = t0 + (it * 4 + warp) * 4 + g4;
     const bool valid = t < t1;
-    fetch(t + 16, kn, vn);
+    RawVec<E> kr, vr;
+#pragma unroll
+    for (int c = 0; c < E / 8; ++c) {
+      kr.v[c] = *reinterpret_cast<const uint4*>(st + g4 * kRow + (gl + 8 * c) * 16);
+      vr.v[c] = *reinterpret_cast<const uint4*>(st + (4 + g4) * kRow + (gl + 8 * c) * 16);
+    }
     float kf[E], vf[E];
     unpack<E>(kr, kf);
     unpack<E>(vr, vf);
-    kr = kn;
-    vr = vn;
 #pragma unroll
     for (int g = 0; g < GMAX; ++g) {
       if (g >= G) break;  // G is uniform
       float s = 0.f;
 #pragma unroll
-      for (int e = 0; e < E; ++e) s += (kQInRegs ? qr[kQInRegs ? g : 0][e] : q_s[g][gl * E + e]) * kf[e];
+      for (int e = 0; e < E; ++e) s += (kQInRegs ? qr[kQInRegs ? g : 0][e] : q_s[g][dim_of(e)]) * kf[e];
       s += __shfl_xor_sync(0xffffffffu, s, 1);
       s += __shfl_xor_sync(0xffffffffu, s, 2);
       s += __shfl_xor_sync(0xffffffffu, s, 4);
@@ -163,6 +192,7 @@ decode_attn_kernel(XpDecodeAttnArgs a) {
       }
     }
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   // merge the four token groups of a warp (lanes differing in bits 3 and 4)
 #pragma unroll
   for (int g = 0; g < GMAX; ++g) {
@@ -182,12 +212,11 @@ decode_attn_kernel(XpDecodeAttnArgs a) {
       m[g] = mn;
     }
   }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (lane < 8) {
 #pragma unroll
     for (int g = 0; g < GMAX; ++g) {
 #pragma unroll
-      for (int e = 0; e < E; ++e) red[warp][g][lane * E + e] = acc[g][e];
+      for (int e = 0; e < E; ++e) red[warp][g][dim_of(e)] = acc[g][e];
       if (lane == 0) {
         red[warp][g][D] = m[g];
         red[warp][g][D + 1] = l[g];
@@ -249,7 +278,13 @@ __global__ void decode_combine_kernel(XpDecodeAttnArgs a, int nsplit) {
 template <int D, int GMAX>
 static int launch_decode(const XpDecodeAttnArgs& a, int nsplit, cudaStream_t s) {
   dim3 grid(nsplit, a.kv_heads, a.batch);
-  decode_attn_kernel<D, GMAX><<<grid, kDecodeThreads, 0, s>>>(a);
+  constexpr int kRing = 4 /*warps*/ * 4 /*stages*/ * 8 * D * 2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(decode_attn_kernel<D, GMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
+    attr_set = true;
+  }
+  decode_attn_kernel<D, GMAX><<<grid, kDecodeThreads, kRing, s>>>(a);
   if (nsplit > 1) decode_combine_kernel<D><<<dim3(a.q_heads, a.batch), D, 0, s>>>(a, nsplit);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);

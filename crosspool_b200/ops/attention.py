@@ -43,8 +43,8 @@ def decode_splits(batch: int, kv_heads: int, max_len: int) -> int:
 def decode_plan(batch: int, kv_heads: int, max_len: int) -> tuple[int, int]:
     """(num_splits, chunk_tokens) for a decode batch. Large batches use fixed 256-token slices so that
     sequences of very different lengths balance across the SMs; small ones split each sequence evenly."""
-    if batch * kv_heads >= 296 and max_len > 256:
-        chunk = 256
+    chunk = 512 if batch * kv_heads >= 1024 else 256
+    if max_len > chunk:
         return (max_len + chunk - 1) // chunk, chunk
     return decode_splits(batch, kv_heads, max_len), 0
 
