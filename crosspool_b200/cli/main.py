@@ -1,0 +1,164 @@
+"""``xpool`` command line (reference: src/xpool/cli/main.py, subcommands/*).
+
+    xpool daemon serve | check     control plane (exit 20 if a failure was recorded, else 0)
+    xpool atnagent --device N      attention role for one GPU (hosts the Instances placed on it)
+    xpool ffnagent --device N      FFN role for one GPU
+    xpool exec -- <cmd ...>        normalise device visibility, export daemon endpoint, exec the command
+    xpool config dump              print the effective configuration
+    xpool memory-profile           print the analytic device memory estimate per FFN device
+    xpool bench ...                serving benchmark (load generator + metrics)
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+from .. import config as C
+
+
+def _parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="xpool", description="multi-model co-location serving for B200")
+    C.add_cli_arguments(p)
+    sub = p.add_subparsers(dest="command", required=True)
+    d = sub.add_parser("daemon", help="control plane")
+    ds = d.add_subparsers(dest="daemon_command", required=True)
+    ds.add_parser("serve")
+    ds.add_parser("check")
+    for name in ("atnagent", "ffnagent"):
+        a = sub.add_parser(name)
+        a.add_argument("--device", type=int, required=True)
+    e = sub.add_parser("exec", help="run a command in the deployment's environment")
+    e.add_argument("argv", nargs=argparse.REMAINDER)
+    c = sub.add_parser("config")
+    c.add_subparsers(dest="config_command", required=True).add_parser("dump")
+    sub.add_parser("memory-profile")
+    b = sub.add_parser("bench")
+    b.add_argument("rest", nargs=argparse.REMAINDER)
+    return p
+
+
+def _load(ns, require=True) -> C.XpoolConfig:
+    return C.init_global_config(C.cli_overrides(ns), require=require)
+
+
+def cmd_config_dump(ns) -> int:
+    cfg = _load(ns, require=False)
+    print(json.dumps({"digest": cfg.digest(), "config": cfg.as_dict(), "sources": dict(cfg.sources)}, indent=2))
+    return 0
+
+
+def cmd_daemon_serve(ns) -> int:
+    import uvicorn
+
+    from ..logging import init_logging
+    from ..service.daemon.app import create_app
+    from ..service.daemon.control import ControlPlane
+
+    cfg = _load(ns)
+    init_logging("Daemon", cfg.logging_level, cfg.logging_color)
+    cp = ControlPlane(cfg)
+    app = create_app(cfg, cp)
+    uvicorn.run(app, host=cfg.daemon_host, port=cfg.daemon_port, log_level="warning")
+    return cp.exit_code
+
+
+def cmd_daemon_check(ns) -> int:
+    from ..service.client import XpoolClient
+    from ..service.errors import ClientError, DaemonError
+
+    cfg = _load(ns, require=False)
+    cl = XpoolClient(cfg.daemon_host, cfg.daemon_port)
+    try:
+        snap = cl.ready()
+    except (ClientError, DaemonError) as e:
+        print(json.dumps({"reachable": False, "error": str(e)}))
+        return 1
+    print(snap.model_dump_json(indent=2))
+    return 0 if snap.system_ready else 1
+
+
+def exec_environment(cfg: C.XpoolConfig, environ: dict[str, str]) -> dict[str, str]:
+    """Environment for ``xpool exec``: all configured devices visible in configuration order, the
+    daemon endpoint and the config path exported. (The reference additionally exports its MPS pipe
+    directory, src/xpool/cli/subcommands/exec.py:29-48; this system runs one process per GPU and
+    needs no MPS.)"""
+    env = dict(environ)
+    devs = list(cfg.atn_devices or ()) + list(cfg.ffn_devices or ())
+    if devs:
+        env["CUDA_VISIBLE_DEVICES"] = ",".join(str(d) for d in devs)
+    env["XPOOL_DAEMON_HOST"] = str(cfg.daemon_host)
+    env["XPOOL_DAEMON_PORT"] = str(cfg.daemon_port)
+    if cfg.config:
+        env["XPOOL_CONFIG"] = str(cfg.config)
+    env.setdefault("SGLANG_PLUGINS", "xpool")
+    return env
+
+
+def cmd_exec(ns) -> int:
+    argv = [a for a in ns.argv if a != "--"] if ns.argv and ns.argv[0] == "--" else list(ns.argv)
+    if not argv:
+        print("xpool exec: no command given", file=sys.stderr)
+        return 2
+    cfg = _load(ns, require=False)
+    os.execvpe(argv[0], argv, exec_environment(cfg, dict(os.environ)))
+    return 127  # not reached
+
+
+def cmd_memory_profile(ns) -> int:
+    from ..models import config as mc
+    from ..service.daemon.placement import DeviceSupply, ModelDemand, place_ffn_models
+
+    cfg = _load(ns)
+    demands = []
+    for m in cfg.models:
+        c = mc.load(m.path if m.path in mc.PRESETS else m.id)
+        inter = c.moe_intermediate_size * max(1, c.num_experts_per_tok) if c.is_moe else c.intermediate_size
+        demands.append(ModelDemand(m.id, tuple(c.ffn_param_bytes_per_layer(l) for l in range(c.num_layers)),
+                                   cfg.ffn_tp_for(m.id), c.hidden_size, 4096, m.atn_world_size, inter))
+    devs = [DeviceSupply(d, 170 << 30, 180 << 30) for d in cfg.ffn_devices]
+    r = place_ffn_models(demands, devs, margin_bytes=cfg.ffn_device_memory_extra_margin_bytes,
+                         lanes=cfg.scheduler_ffn_concurrency)
+    out = {str(d): {"stages": vars(s), "peak": s.peak, "headroom": r.headroom[d]} for d, s in r.stages.items()}
+    print(json.dumps({"devices": out, "groups": [vars(g) for g in r.groups]}, indent=2, default=list))
+    return 0
+
+
+def cmd_agent(ns, role: str) -> int:
+    from ..runtime.launch import run_agent
+
+    cfg = _load(ns)
+    return run_agent(cfg, role, ns.device)
+
+
+def cmd_bench(ns) -> int:
+    from ..bench import serving
+
+    return serving.main(ns.rest)
+
+
+def main(argv: list[str] | None = None) -> int:
+    ns = _parser().parse_args(argv)
+    try:
+        if ns.command == "config":
+            return cmd_config_dump(ns)
+        if ns.command == "daemon":
+            return cmd_daemon_serve(ns) if ns.daemon_command == "serve" else cmd_daemon_check(ns)
+        if ns.command == "exec":
+            return cmd_exec(ns)
+        if ns.command == "memory-profile":
+            return cmd_memory_profile(ns)
+        if ns.command in ("atnagent", "ffnagent"):
+            return cmd_agent(ns, ns.command)
+        if ns.command == "bench":
+            return cmd_bench(ns)
+    except C.ConfigError as e:
+        print(f"xpool: configuration error: {e}", file=sys.stderr)
+        return 2
+    return 2
+
+
+if __name__ == "__main__":
+    sys.exit(main())

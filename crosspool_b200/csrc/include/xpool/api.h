@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 12
+#define XP_ABI_VERSION 13
 
 #ifdef __cplusplus
 extern "C" {
@@ -40,6 +40,10 @@ typedef struct XpGemmArgs {
   int w_evict_first;
   int w_tiled;         /* weights pre-tiled into contiguous 128x64 blocks */
   float gate_limit, up_add, act_alpha;
+  /* grouped (MoE) form: device tile table of int4 {group, feature tile, first row, row end} */
+  const void* tile_table;
+  const int* n_tiles;
+  int w_rows_per_group;
 } XpGemmArgs;
 
 typedef struct XpGemmPlan {
@@ -110,6 +114,39 @@ int xp_lane_shutdown(void* rt, void* stream);
 int xp_lane_stats(void* rt, uint64_t* served, uint32_t* idle, uint32_t* status, void* stream);
 void xp_lane_destroy(void* rt);
 int xp_wait_flags(const XpWaitArgs* a, void* stream);
+
+/* Mixture-of-experts helpers (csrc/kernels/moe.cu). */
+typedef struct XpRouterArgs {
+  const void* logits;           /* [rows, ld_logits] bf16 or fp32 */
+  const float* logit_bias;      /* optional [experts] added to the logits */
+  const float* correction_bias; /* optional [experts] added to the scores for selection only */
+  int* topk_ids;                /* [rows, top_k] */
+  float* topk_weights;          /* [rows, top_k] */
+  int rows, num_experts, top_k, ld_logits;
+  int logits_fp32, sigmoid, renormalize, round_weights_bf16;
+  float scale;
+} XpRouterArgs;
+
+typedef struct XpRouteArgs {
+  const int* topk_ids;          /* [rows, top_k] */
+  int* counts;                  /* [n_local] */
+  int* offsets;                 /* [n_local + 1] */
+  int* perm_token;              /* [rows * top_k] token of each ordered row */
+  int* route_pos;               /* [rows * top_k] ordered row of each route, -1 if not local */
+  void* tiles_gateup;           /* int4 tile table for the gate/up projection */
+  void* tiles_down;
+  int* n_tiles_gateup;
+  int* n_tiles_down;
+  int rows, top_k, expert_lo, expert_hi;
+  int tm_gateup, bn_gateup, tm_down, bn_down;
+} XpRouteArgs;
+
+int xp_router_topk(const XpRouterArgs* a, void* stream);
+int xp_moe_route(const XpRouteArgs* a, void* stream);
+int xp_moe_gather(const void* x, const int* perm_token, const int* n_rows_ptr, void* out, int max_rows,
+                  int hidden, int ldx, void* stream);
+int xp_moe_combine(const void* y, const int* route_pos, const float* weights, void* out, int rows, int top_k,
+                   int hidden, int ld_out, void* stream);
 
 /* Raw device memory shared between processes (CUDA IPC). */
 int xp_dev_alloc(void** ptr, size_t bytes);

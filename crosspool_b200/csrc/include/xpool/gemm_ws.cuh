@@ -74,6 +74,12 @@ struct Problem {
   float gate_limit;           // > 0: clamp gate from above and up to [-limit, limit]
   float up_add;               // added to up before the product (0 for plain SwiGLU)
   float act_alpha;            // 0: silu(g); else g * sigmoid(alpha * g)
+  // Grouped (mixture-of-experts) form: tiles come from a device table of
+  // {group, feature tile start, first row, row end}; group g uses weight rows
+  // [g * w_rows_per_group, ...). Activation rows of a group are contiguous.
+  const int4* tile_table;
+  const int* n_tiles;
+  int w_rows_per_group;
 };
 
 struct SmemLayout {
@@ -150,16 +156,31 @@ struct TileCoord {
   int mn;     // linear (m, n) tile index
   int kb0;    // first K block
   int kbn;    // number of K blocks
+  int w_row0; // first weight row in the weight tensor (differs from m0 for grouped problems)
+  int row_end;  // activation rows >= row_end are not stored
 };
 
 __device__ __forceinline__ int tiles_m(const Problem& p) { return p.n_out / kTileM; }
 __device__ __forceinline__ int tiles_n(const Problem& p) { return (p.rows + p.bn - 1) / p.bn; }
 __device__ __forceinline__ int tile_count(const Problem& p) {
+  if (p.tile_table != nullptr) return *p.n_tiles;
   return tiles_m(p) * tiles_n(p) * p.splits;
 }
 
 __device__ __forceinline__ TileCoord tile_coord(const Problem& p, int t) {
   TileCoord c;
+  if (p.tile_table != nullptr) {
+    const int4 e = p.tile_table[t];
+    c.m0 = e.y;
+    c.n0 = e.z;
+    c.row_end = e.w;
+    c.w_row0 = e.x * p.w_rows_per_group + e.y;
+    c.split = 0;
+    c.mn = t;
+    c.kb0 = 0;
+    c.kbn = p.k / kTileK;
+    return c;
+  }
   int tm = tiles_m(p);
   c.split = t % p.splits;
   int mn = t / p.splits;
@@ -172,6 +193,8 @@ __device__ __forceinline__ TileCoord tile_coord(const Problem& p, int t) {
   int end = c.kb0 + per;
   if (end > kb_total) end = kb_total;
   c.kbn = end > c.kb0 ? end - c.kb0 : 0;
+  c.w_row0 = c.m0;
+  c.row_end = p.rows;
   return c;
 }
 
@@ -204,14 +227,14 @@ __device__ __forceinline__ bool produce_tile(const Problem& p, const TileCoord& 
   if (p.w_tiled) {
     wc0 = 0;
     dwc0 = 0;
-    wc1 = ((c.m0 / kTileM) * kb_total + c.kb0) * kTileM;
-    uc1 = (((p.up_offset + c.m0) / kTileM) * kb_total + c.kb0) * kTileM;
+    wc1 = ((c.w_row0 / kTileM) * kb_total + c.kb0) * kTileM;
+    uc1 = (((p.up_offset + c.w_row0) / kTileM) * kb_total + c.kb0) * kTileM;
     dwc1 = kTileM;
   } else {
     wc0 = c.kb0 * kTileK;
     dwc0 = kTileK;
-    wc1 = c.m0;
-    uc1 = p.up_offset + c.m0;
+    wc1 = c.w_row0;
+    uc1 = p.up_offset + c.w_row0;
     dwc1 = 0;
   }
   int xc0 = c.kb0 * kTileK;
@@ -328,14 +351,14 @@ __device__ __forceinline__ void epi_bar_sync() {
 
 // Applies the fused epilogue to 16 accumulator columns (activation rows
 // n .. n+15) of feature f and stores them.
-__device__ __forceinline__ void epilogue_store16(const Problem& p, int f, int n_first,
+__device__ __forceinline__ void epilogue_store16(const Problem& p, int f, int n_first, int row_end,
                                                  const float* g, const float* u) {
   const float bias = p.bias != nullptr ? p.bias[f] : 0.f;
   const float bias_u = (p.bias != nullptr && p.dual) ? p.bias[p.up_offset + f] : 0.f;
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     const int n = n_first + j;
-    if (n >= p.rows) break;
+    if (n >= row_end) break;
     float v = g[j] + bias;
     const size_t o = static_cast<size_t>(n) * p.ld_out + f;
     if (p.epilogue == kEpiSwiglu) {
@@ -375,10 +398,10 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
   float g[16], u[16];
   if (p.splits == 1) {
     for (int col = 0; col < p.bn; col += 16) {
-      if (c.n0 + col >= p.rows) break;
+      if (c.n0 + col >= c.row_end) break;
       sm100::tmem_ld16(tmem_acc + col, g);
       if (p.dual) sm100::tmem_ld16(tmem_acc + p.bn + col, u);
-      epilogue_store16(p, f, c.n0 + col, g, u);
+      epilogue_store16(p, f, c.n0 + col, c.row_end, g, u);
     }
   } else {
     // Split-K: park raw partial sums, last-arriving CTA folds them in split order.
@@ -406,7 +429,7 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
       __threadfence();
       const float* base = p.ws + static_cast<size_t>(c.mn) * p.splits * acc_cols * kTileM;
       for (int col = 0; col < p.bn; col += 16) {
-        if (c.n0 + col >= p.rows) break;
+        if (c.n0 + col >= c.row_end) break;
 #pragma unroll
         for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
         // Split order is the summation order (deterministic); the 16 (or 32)
@@ -426,7 +449,7 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
             if (p.dual) u[j] += tu[j];
           }
         }
-        epilogue_store16(p, f, c.n0 + col, g, u);
+        epilogue_store16(p, f, c.n0 + col, c.row_end, g, u);
       }
       if (ew == 0 && lane == 0) p.counters[c.mn] = 0;  // ready for the next call
     }

@@ -274,6 +274,17 @@ extern "C" int xp_gemm(const XpGemmArgs* a) {
   p.gate_limit = a->gate_limit;
   p.up_add = a->up_add;
   p.act_alpha = a->act_alpha;
+  p.tile_table = reinterpret_cast<const int4*>(a->tile_table);
+  p.n_tiles = a->n_tiles;
+  p.w_rows_per_group = a->w_rows_per_group;
+  if (a->tile_table != nullptr) {
+    if (plan.splits != 1) return -13;
+    plan.grid = plan.smem_bytes > 0 ? 148 : 148;
+    int dev2 = 0, sms2 = 148;
+    cudaGetDevice(&dev2);
+    cudaDeviceGetAttribute(&sms2, cudaDevAttrMultiProcessorCount, dev2);
+    plan.grid = a->num_sms > 0 ? a->num_sms : sms2;
+  }
 
   static bool attr_set[64] = {false};
   int dev = 0;

@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 12
+EXPECTED_ABI = 13
 HERE = Path(__file__).resolve().parent
 
 
@@ -55,6 +55,9 @@ class GemmArgs(C.Structure):
         ("gate_limit", C.c_float),
         ("up_add", C.c_float),
         ("act_alpha", C.c_float),
+        ("tile_table", C.c_void_p),
+        ("n_tiles", C.c_void_p),
+        ("w_rows_per_group", C.c_int),
     ]
 
 
@@ -133,6 +136,7 @@ def kernels() -> C.CDLL:
                                       C.c_uint32]
     _declare_attention(lib)
     _declare_lane(lib)
+    _declare_moe(lib)
     return lib
 
 
@@ -292,6 +296,39 @@ def _declare_lane(lib: C.CDLL) -> None:
         "xp_ipc_close": [C.c_void_p],
         "xp_memset_async": [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p],
         "xp_enable_peer_access": [C.c_int],
+    }
+    for name, args in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = C.c_int
+        fn.argtypes = args
+
+
+class RouterArgs(C.Structure):
+    _fields_ = [
+        ("logits", C.c_void_p), ("logit_bias", C.c_void_p), ("correction_bias", C.c_void_p),
+        ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p),
+        ("rows", C.c_int), ("num_experts", C.c_int), ("top_k", C.c_int), ("ld_logits", C.c_int),
+        ("logits_fp32", C.c_int), ("sigmoid", C.c_int), ("renormalize", C.c_int), ("round_weights_bf16", C.c_int),
+        ("scale", C.c_float),
+    ]
+
+
+class RouteArgs(C.Structure):
+    _fields_ = [
+        ("topk_ids", C.c_void_p), ("counts", C.c_void_p), ("offsets", C.c_void_p), ("perm_token", C.c_void_p),
+        ("route_pos", C.c_void_p), ("tiles_gateup", C.c_void_p), ("tiles_down", C.c_void_p),
+        ("n_tiles_gateup", C.c_void_p), ("n_tiles_down", C.c_void_p),
+        ("rows", C.c_int), ("top_k", C.c_int), ("expert_lo", C.c_int), ("expert_hi", C.c_int),
+        ("tm_gateup", C.c_int), ("bn_gateup", C.c_int), ("tm_down", C.c_int), ("bn_down", C.c_int),
+    ]
+
+
+def _declare_moe(lib: C.CDLL) -> None:
+    sig = {
+        "xp_router_topk": [C.POINTER(RouterArgs), C.c_void_p],
+        "xp_moe_route": [C.POINTER(RouteArgs), C.c_void_p],
+        "xp_moe_gather": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p],
+        "xp_moe_combine": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p],
     }
     for name, args in sig.items():
         fn = getattr(lib, name)

@@ -14,7 +14,7 @@ from crosspool_b200.native import runtime as rt
 
 
 def test_abi_and_record_sizes():
-    assert rt.lib().xr_abi_version() == 12
+    assert rt.lib().xr_abi_version() == 13
     assert rt.lib().xr_record_bytes(0) == 256  # InvocationRecord
     assert rt.lib().xr_record_bytes(1) == 256  # CompletionRecord
 
