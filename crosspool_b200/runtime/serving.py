@@ -1,0 +1,167 @@
+"""Request serving for the Instances hosted by one attention process.
+
+``EngineLoop`` owns the :class:`Deployment` on a dedicated thread: it drains newly submitted requests
+into the engines, steps every Instance, and hands each produced token to the request's queue.
+``create_serving_app`` exposes it over HTTP: ``POST /generate`` with ``input_ids`` (or ``text`` when a
+tokenizer is configured), ``max_new_tokens`` and ``stream``; streaming answers are server-sent events,
+one per token, in the shape the reference's benchmark client consumes from SGLang
+(``/generate`` with ``stream: true``, src/xpool-dev/xbench/harness/serving/api.py:61-80).
+"""
+
+from __future__ import annotations
+
+import asyncio
+import json
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Optional, Protocol
+
+from pydantic import BaseModel
+
+
+class SteppedDeployment(Protocol):
+    def add_request(self, model_id: str, prompt: list[int], max_new_tokens: int, arrival: float | None = None): ...
+    def step(self): ...
+    @property
+    def has_work(self) -> bool: ...
+
+
+@dataclass
+class Pending:
+    model_id: str
+    prompt: list[int]
+    max_new_tokens: int
+    arrival: float
+    out: "queue.Queue[tuple[int, bool] | Exception]" = field(default_factory=queue.Queue)
+
+
+class EngineLoop:
+    def __init__(self, deployment: SteppedDeployment, idle_sleep: float = 0.0005):
+        self.dep = deployment
+        self._inbox: "queue.Queue[Pending]" = queue.Queue()
+        self._by_seq: dict[int, Pending] = {}
+        self._stop = threading.Event()
+        self._thread: threading.Thread | None = None
+        self.idle_sleep = idle_sleep
+        self.error: Exception | None = None
+        self.steps = 0
+        self.tokens = 0
+
+    def submit(self, model_id: str, prompt: list[int], max_new_tokens: int) -> Pending:
+        p = Pending(model_id, prompt, max_new_tokens, time.monotonic())
+        self._inbox.put(p)
+        return p
+
+    def _admit(self) -> None:
+        while True:
+            try:
+                p = self._inbox.get_nowait()
+            except queue.Empty:
+                return
+            try:
+                seq = self.dep.add_request(p.model_id, p.prompt, p.max_new_tokens, arrival=p.arrival)
+                self._by_seq[(p.model_id, seq.seq_id)] = p
+            except Exception as e:  # bad request: answer it, keep serving
+                p.out.put(e)
+
+    def _run(self) -> None:
+        try:
+            while not self._stop.is_set():
+                self._admit()
+                if not self.dep.has_work:
+                    time.sleep(self.idle_sleep)
+                    continue
+                res = self.dep.step()
+                self.steps += 1
+                for model_id, pairs in res.tokens.items():
+                    for seq, tok in pairs:
+                        p = self._by_seq.get((model_id, seq.seq_id))
+                        if p is None:
+                            continue
+                        done = seq.finished
+                        p.out.put((tok, done))
+                        self.tokens += 1
+                        if done:
+                            del self._by_seq[(model_id, seq.seq_id)]
+        except Exception as e:  # device failure: fail every waiting request, stop (fail-stop)
+            self.error = e
+            for p in self._by_seq.values():
+                p.out.put(e)
+
+    def start(self) -> None:
+        self._thread = threading.Thread(target=self._run, daemon=True, name="engine-loop")
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread:
+            self._thread.join(30)
+
+
+class GenerateRequest(BaseModel):
+    model: Optional[str] = None
+    input_ids: Optional[list[int]] = None
+    text: Optional[str] = None
+    max_new_tokens: int = 16
+    stream: bool = False
+
+
+def create_serving_app(loop: EngineLoop, models: list[str], tokenizer=None):
+    from fastapi import FastAPI, HTTPException
+    from fastapi.responses import StreamingResponse
+
+    app = FastAPI(title="xpool instance")
+
+    @app.get("/health")
+    def health():
+        if loop.error is not None:
+            raise HTTPException(status_code=503, detail=repr(loop.error))
+        return {"status": "ok", "models": models, "steps": loop.steps, "tokens": loop.tokens}
+
+    async def _next(p: Pending):
+        while True:
+            try:
+                return p.out.get_nowait()
+            except queue.Empty:
+                await asyncio.sleep(0.0005)
+
+    @app.post("/generate")
+    async def generate(req: GenerateRequest):
+        model = req.model or models[0]
+        if model not in models:
+            raise HTTPException(status_code=404, detail=f"model {model} is not served here")
+        ids = req.input_ids
+        if ids is None:
+            if req.text is None or tokenizer is None:
+                raise HTTPException(status_code=422, detail="input_ids required (no tokenizer configured)")
+            ids = tokenizer.encode(req.text)
+        p = loop.submit(model, list(ids), req.max_new_tokens)
+        if req.stream:
+            async def sse():
+                n = 0
+                while True:
+                    item = await _next(p)
+                    if isinstance(item, Exception):
+                        yield f"data: {json.dumps({'error': str(item)})}\n\n"
+                        break
+                    tok, done = item
+                    n += 1
+                    yield f"data: {json.dumps({'token_id': tok, 'index': n, 'finished': done})}\n\n"
+                    if done:
+                        break
+                yield "data: [DONE]\n\n"
+
+            return StreamingResponse(sse(), media_type="text/event-stream")
+        out = []
+        while True:
+            item = await _next(p)
+            if isinstance(item, Exception):
+                raise HTTPException(status_code=422 if isinstance(item, ValueError) else 500, detail=str(item))
+            out.append(item[0])
+            if item[1]:
+                break
+        return {"output_ids": out, "text": tokenizer.decode(out) if tokenizer else None}
+
+    return app
