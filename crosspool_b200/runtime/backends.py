@@ -1,0 +1,176 @@
+"""GPU backends of the agent roles: what ``prepare_join`` ... ``finalize`` do on a device.
+
+Arena handles travel as hex strings through the daemon's plan (``slot_handles``):
+``ffn:<model>:<atn rank>:<ffn pe>`` for an FFN rank's slot of one Instance rank and
+``atn:<model>:<atn rank>`` for the attention-side slot (completion records + TP partial buffers).
+"""
+
+from __future__ import annotations
+
+import threading
+import zlib
+
+import torch
+
+from ..config import XpoolConfig
+from ..engine.atn_engine import AttentionEngine, EngineConfig
+from ..models import config as mc
+from ..models.weights import random_attention_weights
+from ..native import runtime as rt
+from ..parallel import fabric as F
+from ..service.wire import FabricPlan, InvocationFailure, ServingListener
+
+_POLICY = {"fifo": rt.POLICY_FIFO, "random": rt.POLICY_RANDOM, "slo": rt.POLICY_SLO}
+
+
+def model_config_for(cfg: XpoolConfig, model_id: str):
+    """The model's shape: a preset named by ``path`` or ``id``, else the ``config.json`` under ``path``."""
+    m = cfg.model(model_id)
+    for name in (m.path, m.id):
+        if name in mc.PRESETS:
+            return mc.PRESETS[name]
+    return mc.load(m.path)
+
+
+def _placement(cfg: XpoolConfig, plan: FabricPlan, model_id: str, atn_rank: int, capacity_rows: int) -> F.InstancePlacement:
+    shards = sorted((s for s in plan.shards if s.model_id == model_id), key=lambda s: s.tp_rank)
+    if any(s.layer_begin != 0 or s.layer_end != shards[0].layer_end for s in shards):
+        raise NotImplementedError("layer-split placements are planned by the daemon but not routed per layer yet")
+    rank = next(r for r in plan.instance_ranks if r.model_id == model_id and r.rank == atn_rank)
+    seed = zlib.crc32(model_id.encode()) % 1000  # random-init deployments: same seed on every rank of a model
+    return F.InstancePlacement(model_id, model_config_for(cfg, model_id), seed, rank.pe, tuple(s.pe for s in shards),
+                               capacity_rows)
+
+
+class FfnBackend:
+    def __init__(self, cfg: XpoolConfig, device: int, capacity_rows: int = 4096, local_index: int | None = None):
+        self.cfg, self.device, self.capacity_rows = cfg, device, capacity_rows
+        self.cuda = torch.device(f"cuda:{device if local_index is None else local_index}")
+        self.rt: F.FfnRankRuntime | None = None
+        self._keys: list[tuple[F.FfnInstanceState, str]] = []
+
+    def prepare_join(self, plan: FabricPlan) -> dict[str, str]:
+        torch.cuda.set_device(self.cuda)
+        self.rt = F.FfnRankRuntime(self.cuda, n_lanes=plan.lanes_per_ffn_device, policy=_POLICY[plan.policy],
+                                   seed=self.cfg.scheduler_ffn_random_seed or 0)
+        my_pe = len(plan.atn_devices) + plan.ffn_devices.index(self.device)
+        handles = {}
+        for r in plan.instance_ranks:
+            place = _placement(self.cfg, plan, r.model_id, r.rank, self.capacity_rows)
+            if my_pe not in place.ffn_ranks:
+                continue
+            st = self.rt.add_instance(place, place.ffn_ranks.index(my_pe))
+            self._keys.append((st, f"atn:{r.model_id}:{r.rank}"))
+            handles[f"ffn:{r.model_id}:{r.rank}:{my_pe}"] = st.slot.handle().hex()
+        return handles
+
+    def join(self, plan: FabricPlan) -> None:
+        for st, key in self._keys:
+            st.atn_base = F.PeerBuffer.open(bytes.fromhex(plan.slot_handles[key]))
+
+    def prepare_execution(self, plan: FabricPlan) -> None:
+        self.rt.install()
+
+    def activate(self, plan: FabricPlan) -> None:
+        self.rt.start(lease_ms=20.0)
+
+    def poll_health(self) -> InvocationFailure | None:
+        if self.rt is None:
+            return None
+        if self.rt.errors:
+            raise RuntimeError("; ".join(self.rt.errors))
+        st = self.rt.stats()
+        if st["status"] != 0:
+            return InvocationFailure(result_code=3, origin_pe=-1, instance_index=0, invocation_sequence=0, layer_ordinal=0)
+        return None
+
+    def quiesce(self) -> None:
+        if self.rt:
+            self.rt.stop()
+
+    def drain(self) -> bool:
+        torch.cuda.synchronize(self.cuda)
+        return True
+
+    def finalize(self) -> None:
+        if self.rt:
+            self.rt.close()
+            self.rt = None
+
+
+class AtnBackend:
+    def __init__(self, cfg: XpoolConfig, device: int, instances: list[tuple[str, int]], ecfg: EngineConfig,
+                 capacity_rows: int = 4096, local_index: int | None = None, listen: tuple[str, int] | None = None):
+        self.cfg, self.device, self.instances, self.ecfg = cfg, device, instances, ecfg
+        self.capacity_rows = max(capacity_rows, ecfg.max_batch, ecfg.prefill_chunk)
+        self.cuda = torch.device(f"cuda:{device if local_index is None else local_index}")
+        self.buffers: dict[tuple[str, int], F.PeerBuffer] = {}
+        self.places: dict[tuple[str, int], F.InstancePlacement] = {}
+        self.engines: dict[str, AttentionEngine] = {}
+        self.loop = None
+        self._server = None
+        self._listen = listen
+        self.listener: ServingListener | None = None
+
+    def prepare_join(self, plan: FabricPlan) -> dict[str, str]:
+        torch.cuda.set_device(self.cuda)
+        handles = {}
+        for model_id, rank in self.instances:
+            place = _placement(self.cfg, plan, model_id, rank, self.capacity_rows)
+            buf = F.PeerBuffer(F.atn_slot_layout(place).total_bytes)
+            self.buffers[(model_id, rank)], self.places[(model_id, rank)] = buf, place
+            handles[f"atn:{model_id}:{rank}"] = buf.handle().hex()
+        return handles
+
+    def join(self, plan: FabricPlan) -> None:
+        self._bases = {}
+        for (model_id, rank), place in self.places.items():
+            self._bases[(model_id, rank)] = [F.PeerBuffer.open(bytes.fromhex(plan.slot_handles[f"ffn:{model_id}:{rank}:{pe}"]))
+                                             for pe in place.ffn_ranks]
+
+    def prepare_execution(self, plan: FabricPlan) -> None:
+        for (model_id, rank), place in self.places.items():
+            port = F.FabricFfnPort(place, self.buffers[(model_id, rank)], self._bases[(model_id, rank)], self.cuda)
+            aw = random_attention_weights(place.cfg, place.seed, self.cuda, torch.bfloat16)
+            self.engines[model_id] = AttentionEngine(place.cfg, aw, port, self.ecfg, self.cuda)
+
+    def activate(self, plan: FabricPlan) -> None:
+        pass  # engines warm up once the whole Fabric is executable (their graphs invoke the FFN tier)
+
+    def warm_and_serve(self) -> None:
+        from ..deployment import Deployment, InstanceHandle
+        from .serving import EngineLoop, create_serving_app
+
+        dep = Deployment([InstanceHandle(m, e.cfg, e) for m, e in self.engines.items()])
+        dep.warmup()
+        self.loop = EngineLoop(dep)
+        self.loop.start()
+        if self._listen is not None:
+            import uvicorn
+
+            app = create_serving_app(self.loop, list(self.engines))
+            conf = uvicorn.Config(app, host=self._listen[0], port=self._listen[1], log_level="warning")
+            self._server = uvicorn.Server(conf)
+            threading.Thread(target=self._server.run, daemon=True, name="serving-http").start()
+            self.listener = ServingListener(host=self._listen[0], port=self._listen[1])
+
+    def poll_health(self) -> InvocationFailure | None:
+        if self.loop is not None and self.loop.error is not None:
+            raise RuntimeError(f"engine loop failed: {self.loop.error!r}")
+        return None
+
+    def quiesce(self) -> None:
+        if self._server is not None:
+            self._server.should_exit = True
+        if self.loop is not None:
+            self.loop.stop()
+
+    def drain(self) -> bool:
+        torch.cuda.synchronize(self.cuda)
+        return True
+
+    def finalize(self) -> None:
+        self.engines.clear()
+        for b in self.buffers.values():
+            b.free()
+        self.buffers.clear()

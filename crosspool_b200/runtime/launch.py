@@ -1,0 +1,61 @@
+"""Process entry points of ``xpool atnagent`` / ``xpool ffnagent``."""
+
+from __future__ import annotations
+
+import os
+
+from ..config import XpoolConfig
+from ..logging import get_logger, init_logging, kv
+from ..service.client import XpoolClient
+from ..service.wire import InstanceFfnProfile, Role
+
+SERVING_BASE_PORT = 30000
+
+
+def hosted_instances(cfg: XpoolConfig, device: int) -> list[tuple[str, int]]:
+    """Instance ranks hosted on an attention device: rank r of every model lives on the r-th
+    attention device."""
+    out = []
+    for m in cfg.models:
+        for r in range(m.atn_world_size):
+            if cfg.atn_devices[r] == device:
+                out.append((m.id, r))
+    return out
+
+
+def run_agent(cfg: XpoolConfig, role: str, device: int) -> int:
+    import torch
+
+    from ..engine.atn_engine import EngineConfig
+    from ..native import EXPECTED_ABI
+    from ..service.client import self_ref
+    from .backends import AtnBackend, FfnBackend, model_config_for
+    from .roles import AtnAgent, FfnAgent
+
+    log = init_logging("AtnAgent" if role == "atnagent" else "FfnAgent", cfg.logging_level, cfg.logging_color)
+    client = XpoolClient(cfg.daemon_host, cfg.daemon_port)
+    owner = self_ref(EXPECTED_ABI)
+    client.check_config(owner, cfg.digest())
+    client.startup_agent(owner, Role.ATNAGENT if role == "atnagent" else Role.FFNAGENT, device)
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    local = [int(x) for x in visible.split(",")].index(device) if visible else device
+    torch.cuda.set_device(local)
+    max_rows = int(os.environ.get("XPOOL_MAX_ROWS", "4096"))
+    if role == "ffnagent":
+        free, total = torch.cuda.mem_get_info(local)
+        agent = FfnAgent(client, device, FfnBackend(cfg, device, capacity_rows=max_rows, local_index=local), free, total,
+                         owner=owner)
+    else:
+        insts = hosted_instances(cfg, device)
+        ecfg = EngineConfig(max_batch=int(os.environ.get("XPOOL_MAX_BATCH", "256")), prefill_chunk=min(max_rows, 2048),
+                            max_seq_len=int(os.environ.get("XPOOL_MAX_SEQ_LEN", "4096")))
+        port = SERVING_BASE_PORT + cfg.atn_devices.index(device)
+        backend = AtnBackend(cfg, device, insts, ecfg, capacity_rows=max_rows, local_index=local, listen=("127.0.0.1", port))
+        profs = [(m, r, InstanceFfnProfile(max_prefill_rows=ecfg.prefill_chunk, max_decode_rows=ecfg.max_batch,
+                                           hidden_size=model_config_for(cfg, m).hidden_size)) for m, r in insts]
+        agent = AtnAgent(client, device, backend, profs, owner=owner)
+    log.info(kv(event="start", role=role, device=device, pid=os.getpid()))
+    rc = agent.run()
+    if agent.failed:
+        get_logger().error(kv(event="failed", reason=agent.failed, retained=agent.retained))
+    return rc

@@ -66,6 +66,9 @@ class AtnAgent(Agent):
         from ..service.wire import FabricPhase
 
         if fp == FabricPhase.EXECUTABLE and not self._initialized and not self.failed:
+            warm = getattr(self.backend, "warm_and_serve", None)
+            if warm is not None:
+                warm()  # engine graphs invoke the FFN tier, so they are captured only now
             listener = getattr(self.backend, "listener", None)
             for model_id, rank, _ in self.instances:
                 self.client.instance_initialized(model_id, InstanceRankInitialized(

@@ -1,0 +1,83 @@
+"""End to end with real processes: ``xpool daemon serve`` + ``xpool atnagent`` + ``xpool ffnagent`` on two
+GPUs, requests over HTTP, graceful quiesce. Needs >= 2 GPUs."""
+import json
+import os
+import signal
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import httpx
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+TOML = """
+[daemon]
+port = 9831
+[atn]
+devices = [0]
+[ffn]
+devices = [1]
+[scheduler]
+ffn_concurrency = 2
+[scheduler.slo]
+ttft_ms = 2000
+tbt_ms = 50
+[[models]]
+id = "Qwen/Qwen3-0.6B"
+ffn_tp_size = 1
+"""
+
+
+def test_daemon_agents_serve_requests_and_retire(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    cfgp = tmp_path / "xpool.toml"
+    cfgp.write_text(TOML)
+    env = dict(os.environ, XPOOL_CONFIG=str(cfgp), PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0", XPOOL_MAX_ROWS="512",
+               XPOOL_MAX_BATCH="16", XPOOL_MAX_SEQ_LEN="512")
+    xp = [sys.executable, "-m", "crosspool_b200.cli.main"]
+    procs = [subprocess.Popen(xp + ["daemon", "serve"], env=env)]
+    try:
+        for _ in range(100):
+            try:
+                if httpx.get("http://127.0.0.1:9831/health", timeout=1).status_code == 200:
+                    break
+            except httpx.HTTPError:
+                time.sleep(0.2)
+        procs.append(subprocess.Popen(xp + ["ffnagent", "--device", "1"], env=env))
+        procs.append(subprocess.Popen(xp + ["atnagent", "--device", "0"], env=env))
+        ready = False
+        for _ in range(600):
+            r = httpx.get("http://127.0.0.1:9831/ready", timeout=2).json()
+            if r["system_ready"]:
+                ready = True
+                break
+            assert r["failure"] is None, r
+            time.sleep(0.5)
+        assert ready
+        assert subprocess.run(xp + ["daemon", "check"], env=env, capture_output=True).returncode == 0
+        out = httpx.post("http://127.0.0.1:30000/generate", json={"input_ids": list(range(1, 40)), "max_new_tokens": 5},
+                         timeout=60).json()
+        assert len(out["output_ids"]) == 5
+        again = httpx.post("http://127.0.0.1:30000/generate", json={"input_ids": list(range(1, 40)), "max_new_tokens": 5},
+                           timeout=60).json()
+        assert again["output_ids"] == out["output_ids"]  # greedy decoding is deterministic
+        assert httpx.post("http://127.0.0.1:9831/fabric/quiesce", json={"reason": "test"}, timeout=5).status_code == 200
+        for p in procs[1:]:
+            assert p.wait(60) == 0
+        plan = httpx.get("http://127.0.0.1:9831/fabric/plan", timeout=2).json()
+        assert plan["phase"] == "stopped"
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.send_signal(signal.SIGTERM)
+        for p in procs:
+            try:
+                p.wait(10)
+            except subprocess.TimeoutExpired:
+                p.kill()
