@@ -112,6 +112,8 @@ int xp_lane_commit(void* rt);
 int xp_lane_launch(void* rt, int lane_index, uint64_t lease_ns, void* stream);
 int xp_lane_shutdown(void* rt, void* stream);
 int xp_lane_stats(void* rt, uint64_t* served, uint32_t* idle, uint32_t* status, void* stream);
+int xp_lane_trace_enable(void* rt, uint32_t capacity);
+int64_t xp_lane_trace_read(void* rt, uint64_t* out, uint64_t max_events, uint64_t* dropped, void* stream);
 void xp_lane_destroy(void* rt);
 int xp_wait_flags(const XpWaitArgs* a, void* stream);
 

@@ -24,6 +24,7 @@
 #include "xpool/gemm_ws.cuh"
 #include "xpool/protocol.hpp"
 #include "xpool/scheduler.hpp"
+#include "xpool/trace.cuh"
 
 namespace xpool {
 namespace lane {
@@ -76,6 +77,7 @@ struct alignas(128) LaneCtl {
   uint64_t seed;
   uint64_t next_ticket;
   uint64_t served[kMaxInstances];  // invocations completed per instance (statistics)
+  trace::BufferView trace;         // fabric observer (null events pointer: off)
   SchedulerEntry entries[kMaxInstances];
   LaneState lanes[kMaxLanes];
 };

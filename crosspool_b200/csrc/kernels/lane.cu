@@ -35,6 +35,7 @@ __global__ void lane_wait_kernel(LaneCtl* ctl, const InstanceSlot* slots, LaneCu
   while (true) {
     if (sm100::ld_relaxed_sys(&ctl->shutdown) != 0) {
       cur->result_code = static_cast<uint32_t>(ResultCode::Shutdown);
+      trace::record(ctl->trace, trace::kLaneShutdown, lane_index, 0);
       return;
     }
     // cheap look before taking the lock: is any slot ahead of its completed sequence?
@@ -79,11 +80,14 @@ __global__ void lane_wait_kernel(LaneCtl* ctl, const InstanceSlot* slots, LaneCu
         cur->result_code = rc;
         __threadfence();
         cur->valid = 1;
+        if (rc != 0) trace::record(ctl->trace, trace::kLaneRejected, d.instance, rc);
+        trace::record(ctl->trace, trace::kLaneAdmitted, d.instance, (layer << 16) | (rows > 0xffffu ? 0xffffu : rows));
         return;
       }
     }
     if ((++spins & 0xfu) == 0 && sm100::global_timer_ns() > deadline) {
       cur->idle_replays += 1;
+      trace::record(ctl->trace, trace::kLaneIdle, lane_index, cur->idle_replays);
       return;
     }
     __nanosleep(200);
@@ -106,6 +110,7 @@ __global__ void lane_complete_kernel(LaneCtl* ctl, const InstanceSlot* slots, La
     ctl->served[cur->instance] += 1;
     lock_release(&ctl->lock);
   }
+  trace::record(ctl->trace, trace::kLaneCompleted, cur->instance, cur->sequence);
   cur->valid = 0;
   (void)lane_index;
 }
@@ -132,6 +137,9 @@ struct Runtime {
   float* ws_d = nullptr;
   uint32_t* counters_d = nullptr;
   uint32_t* status_d = nullptr;
+  trace::Event* trace_events_d = nullptr;
+  trace::BufferState* trace_state_d = nullptr;
+  uint32_t trace_capacity = 0;
   bool committed = false;
 };
 
@@ -313,9 +321,48 @@ extern "C" int xp_lane_stats(void* h, uint64_t* served, uint32_t* idle, uint32_t
   return 0;
 }
 
+// Fabric observer: allocates an event buffer and points the Lane kernels at it. Call before the
+// first launch; events are read back with xp_lane_trace_read while the Lanes are stopped or running.
+extern "C" int xp_lane_trace_enable(void* h, uint32_t capacity) {
+  auto* rt = static_cast<Runtime*>(h);
+  if (rt->trace_events_d != nullptr || capacity == 0) return -1;
+  if (cudaMalloc(&rt->trace_events_d, sizeof(trace::Event) * capacity) != cudaSuccess) return -2;
+  if (cudaMalloc(&rt->trace_state_d, sizeof(trace::BufferState)) != cudaSuccess) return -2;
+  cudaMemset(rt->trace_state_d, 0, sizeof(trace::BufferState));
+  rt->trace_capacity = capacity;
+  trace::BufferView v{rt->trace_events_d, rt->trace_state_d, capacity, 0};
+  return cudaMemcpy(&rt->ctl_d->trace, &v, sizeof(v), cudaMemcpyHostToDevice) == cudaSuccess ? 0 : -3;
+}
+
+// Copies up to max_events events as (kind << 32 | a, b, timestamp_ns) triples; returns the count,
+// *dropped receives the number of events that did not fit.
+extern "C" int64_t xp_lane_trace_read(void* h, uint64_t* out, uint64_t max_events, uint64_t* dropped, void* stream) {
+  auto* rt = static_cast<Runtime*>(h);
+  if (rt->trace_events_d == nullptr) return -1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  trace::BufferState st;
+  if (cudaMemcpyAsync(&st, rt->trace_state_d, sizeof(st), cudaMemcpyDeviceToHost, s) != cudaSuccess) return -2;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return -2;
+  uint64_t n = std::min<uint64_t>(std::min<uint64_t>(st.sequence, rt->trace_capacity), max_events);
+  std::vector<trace::Event> ev(n);
+  if (n > 0) {
+    cudaMemcpyAsync(ev.data(), rt->trace_events_d, sizeof(trace::Event) * n, cudaMemcpyDeviceToHost, s);
+    if (cudaStreamSynchronize(s) != cudaSuccess) return -2;
+  }
+  for (uint64_t i = 0; i < n; ++i) {
+    out[3 * i] = (static_cast<uint64_t>(ev[i].kind) << 32) | ev[i].a;
+    out[3 * i + 1] = ev[i].b;
+    out[3 * i + 2] = ev[i].timestamp_ns;
+  }
+  *dropped = st.dropped;
+  return static_cast<int64_t>(n);
+}
+
 extern "C" void xp_lane_destroy(void* h) {
   auto* rt = static_cast<Runtime*>(h);
   if (rt == nullptr) return;
+  if (rt->trace_events_d != nullptr) cudaFree(rt->trace_events_d);
+  if (rt->trace_state_d != nullptr) cudaFree(rt->trace_state_d);
   for (auto* p : rt->layers_d)
     if (p != nullptr) cudaFree(p);
   cudaFree(rt->ctl_d);

@@ -281,7 +281,10 @@ def _declare_lane(lib: C.CDLL) -> None:
     lib.xp_lane_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_size_t]
     lib.xp_lane_destroy.restype = None
     lib.xp_lane_destroy.argtypes = [C.c_void_p]
+    lib.xp_lane_trace_read.restype = C.c_int64
+    lib.xp_lane_trace_read.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.c_uint64, C.POINTER(C.c_uint64), C.c_void_p]
     sig = {
+        "xp_lane_trace_enable": [C.c_void_p, C.c_uint32],
         "xp_lane_set_instance": [C.c_void_p, C.c_int, C.POINTER(LaneInstanceDesc)],
         "xp_lane_set_layer": [C.c_void_p, C.c_int, C.c_int, C.POINTER(LaneLayerDesc)],
         "xp_lane_commit": [C.c_void_p],

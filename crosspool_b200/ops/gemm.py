@@ -135,6 +135,15 @@ def plan(a: native.GemmArgs) -> native.GemmPlan:
     return p
 
 
+def plan_shape(n_out: int, k: int, rows: int, dual: int = 0, num_sms: int = 148, ws_bytes: int = 96 << 20) -> dict:
+    """Tile plan the kernel would pick for a shape; needs no device (used by the graph observer)."""
+    a, p = native.GemmArgs(), native.GemmPlan()
+    a.n_out, a.k, a.rows, a.dual, a.num_sms = n_out, k, rows, dual, num_sms
+    a.ws, a.counters, a.ws_bytes, a.counter_bytes = 1, 1, ws_bytes, 1 << 16  # only tested for null by the planner
+    native.check(native.kernels().xp_gemm_plan(C.byref(a), C.byref(p)), "xp_gemm_plan", 0)
+    return {f: getattr(p, f) for f, _ in native.GemmPlan._fields_}
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, *, out: torch.Tensor | None = None, bias: torch.Tensor | None = None,
            resid: torch.Tensor | None = None, out_fp32: bool = False, splits: int = 0, bn: int = 0,
            num_sms: int = 0, evict_first: bool | None = None) -> torch.Tensor:

@@ -289,6 +289,23 @@ class FfnRankRuntime:
                      "xp_lane_stats", 0)
         return {"served": list(served), "idle_replays": list(idle), "status": status.value}
 
+    def enable_trace(self, capacity: int = 1 << 16) -> None:
+        """Turns the fabric observer on (after ``install``, before ``start``)."""
+        native.check(native.kernels().xp_lane_trace_enable(self.handle, capacity), "xp_lane_trace_enable", 0)
+        self._trace_capacity = capacity
+
+    def trace_events(self) -> tuple[list[tuple[int, int, int, int]], int]:
+        """(kind, a, b, timestamp_ns) per recorded Lane event, and the count of dropped events."""
+        cap = getattr(self, "_trace_capacity", 0)
+        if not cap:
+            return [], 0
+        out, dropped = (C.c_uint64 * (3 * cap))(), C.c_uint64()
+        side = torch.cuda.Stream(self.device)
+        n = native.kernels().xp_lane_trace_read(self.handle, out, cap, C.byref(dropped), side.cuda_stream)
+        if n < 0:
+            raise RuntimeError(f"xp_lane_trace_read failed with {n}")
+        return [(out[3 * i] >> 32, out[3 * i] & 0xFFFFFFFF, out[3 * i + 1], out[3 * i + 2]) for i in range(n)], dropped.value
+
     def close(self) -> None:
         self.stop()
         if self.handle:

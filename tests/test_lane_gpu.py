@@ -122,3 +122,27 @@ def test_two_models_share_one_lane_in_fifo_order_and_bad_records_are_refused():
         assert (rc, nrows, seq) == (2, 0, 2)
     finally:
         ffn.close()
+
+
+def test_fabric_observer_records_lane_events_in_order_and_counts_overflow():
+    from crosspool_b200 import devkit
+    from crosspool_b200.parallel import fabric as F
+
+    ffn, places, atn = _make([("Qwen/Qwen3-0.6B", 1)])
+    try:
+        ffn.enable_trace(4)
+        st, place = ffn.instances[0], places[0]
+        ffn.launch_once(0, lease_ms=2)                      # idle
+        x = (torch.randn(3, place.cfg.hidden_size, device="cuda") * 0.5).bfloat16()
+        for seq in (1, 2):
+            _publish(F, st, place, x, seq - 1, seq)
+            ffn.launch_once(0, lease_ms=20)
+            torch.cuda.synchronize()
+        art = devkit.FabricObserver(ffn).collect()
+        names = [e["name"] for e in art.events]
+        assert names == ["idle", "admitted", "completed", "admitted"] and art.dropped == 1   # capacity 4, never wraps
+        assert art.events[1]["rows"] == 3 and art.events[1]["layer"] == 0 and art.events[2]["sequence"] == 1
+        ts = [e["ts_ns"] for e in art.events]
+        assert ts == sorted(ts)
+    finally:
+        ffn.close()
