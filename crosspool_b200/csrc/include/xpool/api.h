@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 13
+#define XP_ABI_VERSION 14
 
 #ifdef __cplusplus
 extern "C" {
@@ -103,6 +103,14 @@ typedef struct XpLaneLayerDesc {
   const float* bias_down;
   int inter_local, gated, w_tiled;
   float gate_limit, up_add, act_alpha;
+  /* Mixture of experts when num_experts > 0: w_gateup is [n_local * 2 * inter_local, hidden] and w_down
+     [n_local * hidden, inter_local] for the experts [expert_lo, expert_hi) this rank owns. */
+  const void* router;            /* [num_experts rounded up to 128, hidden] bf16, padding rows zero */
+  const float* correction_bias;  /* optional [num_experts] */
+  const float* router_bias;      /* optional [num_experts] */
+  int num_experts, top_k, expert_lo, expert_hi, sigmoid, renormalize;
+  float scale;
+  int reserved;
 } XpLaneLayerDesc;
 
 void* xp_lane_create(int n_instances, int n_lanes, int policy, uint64_t seed, size_t ws_bytes_per_lane);

@@ -34,6 +34,20 @@ constexpr int kMaxLanes = 8;
 constexpr int kBnVariants = 5;  // 16, 32, 64, 128, 256
 constexpr int kRowBuckets = 16; // row-count buckets 2^0 .. 2^15 (the reference's Capacities)
 
+// Router and expert bookkeeping of a mixture-of-experts layer. The expert weights themselves are
+// bound through LayerEntry::tmap_gateup / tmap_down (all local experts stacked along the rows).
+struct alignas(128) MoeLayer {
+  CUtensorMap tmap_router;      // [e_pad, hidden] box {64, 128}; rows past num_experts are zero
+  const float* correction_bias; // optional, added to the scores for selection only
+  const float* router_bias;     // optional, added to the logits
+  int num_experts, top_k;
+  int expert_lo, expert_hi;     // experts this rank owns (expert parallelism); all of them under TP
+  int sigmoid, renormalize;
+  float scale;
+  int e_pad;
+  uint8_t bn_router[kRowBuckets], splits_router[kRowBuckets];
+};
+
 // Per (instance, layer): weight tensor maps and epilogue parameters.
 struct alignas(128) LayerEntry {
   CUtensorMap tmap_gateup;  // [2 * inter_local (or inter_local), hidden] box {64, 128}
@@ -46,6 +60,7 @@ struct alignas(128) LayerEntry {
   int kind;                 // LayerKind
   float gate_limit, up_add, act_alpha;
   int reserved;
+  const MoeLayer* moe;      // null for a dense layer
   // tile width and split-K factor per row bucket, chosen on the host at install time
   uint8_t bn_gateup[kRowBuckets], splits_gateup[kRowBuckets];
   uint8_t bn_down[kRowBuckets], splits_down[kRowBuckets];
@@ -55,6 +70,7 @@ struct alignas(128) LayerEntry {
 struct alignas(128) InstanceSlot {
   CUtensorMap tmap_x[kBnVariants];    // input payload [capacity, hidden]
   CUtensorMap tmap_act[kBnVariants];  // activation scratch [capacity, max inter_local]
+  const void* input;                  // the payload buffer tmap_x covers (plain loads by the MoE row gather)
   const uint32_t* in_flag;            // local word the attention side releases (sequence)
   const InvocationRecord* record;     // local record written before the flag
   void* act;                          // local scratch between the two GEMMs
@@ -66,6 +82,39 @@ struct alignas(128) InstanceSlot {
   int num_layers;
   int act_ld;                         // leading dimension of the scratch (max inter_local)
 };
+
+// Scratch of one Lane for mixture-of-experts layers (sized for the largest MoE instance).
+struct MoeLaneWs {
+  __nv_bfloat16* logits;  // [capacity_rows, e_pad of the layer]
+  int* ids;               // [capacity_rows, top_k]
+  float* weights;         // [capacity_rows, top_k]
+  int* offsets;           // [n_local + 1] first route position of every local expert
+  int* perm_token;        // [routes] token of the route at a position
+  int* route_pos;         // [capacity_rows, top_k] position of a route, -1 if another rank owns the expert
+  int4* tiles_gateup;     // grouped-GEMM tile tables
+  int4* tiles_down;
+  int* n_tiles;           // [2]
+  void* xp;               // [routes, hidden] gathered rows
+  void* act;              // [routes, inter_local]
+  void* yp;               // [routes, hidden] expert outputs
+  int cap_routes;
+  int reserved;
+};
+
+// Tensor maps over a Lane's MoE scratch, laid out for one instance's hidden / inter sizes.
+struct alignas(64) MoeLaneMaps {
+  CUtensorMap tmap_xp[kBnVariants];
+  CUtensorMap tmap_act[kBnVariants];
+};
+
+// Tile width of the grouped GEMMs: the power of two covering the mean routes per expert.
+__host__ __device__ inline int moe_tile_width(int rows, int top_k, int n_local) {
+  int avg = rows * top_k / (n_local > 0 ? n_local : 1);
+  if (avg < 1) avg = 1;
+  int bn = 16;
+  while (bn < avg && bn < 128) bn <<= 1;
+  return bn;
+}
 
 struct alignas(128) LaneCtl {
   uint32_t lock;

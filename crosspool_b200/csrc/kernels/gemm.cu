@@ -77,10 +77,13 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmap_w,
 // epilogue stores into the attention device's partial buffer for this TP rank).
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int phase, float* ws,
-                 uint32_t* counters, int smem_budget, uint32_t* status) {
+                 uint32_t* counters, int smem_budget, uint32_t* status, const lane::MoeLaneWs* mws,
+                 const lane::MoeLaneMaps* mmaps) {
   if (cur->valid == 0 || cur->rows == 0) return;  // idle replay: uniform exit
   const lane::InstanceSlot& s = slots[cur->instance];
   const lane::LayerEntry& le = s.layers[cur->layer];
+  const lane::MoeLayer* moe = le.moe;
+  if (phase == 2 && moe == nullptr) return;       // router projection: MoE layers only
   const int rows = static_cast<int>(cur->rows);
   int bucket = 0;
   while ((1 << bucket) < rows && bucket < lane::kRowBuckets - 1) ++bucket;
@@ -90,7 +93,54 @@ gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int 
   p.counters = counters;
   p.w_tiled = le.w_tiled;
   p.w_evict_first = rows <= 64;
-  if (phase == 0) {
+  if (phase == 2) {
+    p.bn = moe->bn_router[bucket] == 255 ? 256 : moe->bn_router[bucket];
+    p.splits = moe->splits_router[bucket];
+    p.tmap_w = &moe->tmap_router;
+    p.tmap_x = &s.tmap_x[lane::bn_index(p.bn)];
+    p.out = mws->logits;
+    p.n_out = moe->e_pad;
+    p.k = s.hidden;
+    p.ld_out = moe->e_pad;
+    p.epilogue = kEpiStore;
+    p.w_tiled = 0;
+  } else if (moe != nullptr) {
+    // grouped projections over the routes ordered by expert; tile tables come from moe_lane_route
+    const lane::MoeLaneMaps& mm = mmaps[cur->instance];
+    p.bn = lane::moe_tile_width(rows, moe->top_k, moe->expert_hi - moe->expert_lo);
+    p.splits = 1;
+    p.rows = rows * moe->top_k;
+    p.w_tiled = 0;
+    p.w_evict_first = 0;
+    if (phase == 0) {
+      p.tmap_w = &le.tmap_gateup;
+      p.tmap_x = &mm.tmap_xp[lane::bn_index(p.bn)];
+      p.out = mws->act;
+      p.n_out = le.inter_local;
+      p.k = s.hidden;
+      p.ld_out = le.inter_local;
+      p.dual = 1;
+      p.up_offset = le.inter_local;
+      p.epilogue = kEpiSwiglu;
+      p.gate_limit = le.gate_limit;
+      p.up_add = le.up_add;
+      p.act_alpha = le.act_alpha;
+      p.tile_table = mws->tiles_gateup;
+      p.n_tiles = mws->n_tiles;
+      p.w_rows_per_group = 2 * le.inter_local;
+    } else {
+      p.tmap_w = &le.tmap_down;
+      p.tmap_x = &mm.tmap_act[lane::bn_index(p.bn)];
+      p.out = mws->yp;
+      p.n_out = s.hidden;
+      p.k = le.inter_local;
+      p.ld_out = s.hidden;
+      p.epilogue = kEpiStore;
+      p.tile_table = mws->tiles_down;
+      p.n_tiles = mws->n_tiles + 1;
+      p.w_rows_per_group = s.hidden;
+    }
+  } else if (phase == 0) {
     p.bn = le.bn_gateup[bucket] == 255 ? 256 : le.bn_gateup[bucket];
     p.splits = le.splits_gateup[bucket];
     p.tmap_w = &le.tmap_gateup;
@@ -120,7 +170,7 @@ gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int 
   }
   p.ld_resid = p.ld_out;
   const int nacc = p.bn * (p.dual ? 2 : 1) * 2 <= 512 ? 2 : 1;
-  if (threadIdx.x == 0 && phase == 0) sm100::fence_proxy_async();  // payload arrived through peer stores
+  if (threadIdx.x == 0 && (phase == 0 || phase == 2)) sm100::fence_proxy_async();  // payload arrived through peer stores
   run_tiles(p, nacc, smem_budget, status);
 }
 

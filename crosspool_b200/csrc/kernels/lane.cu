@@ -17,8 +17,16 @@ struct TileChoice {
 };
 TileChoice choose_tiles_host(int tm, int rows, int kb, int dual, int sms, size_t ws_bytes_available);
 __global__ void gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int phase, float* ws,
-                                 uint32_t* counters, int smem_budget, uint32_t* status);
+                                 uint32_t* counters, int smem_budget, uint32_t* status, const lane::MoeLaneWs* mws,
+                                 const lane::MoeLaneMaps* mmaps);
 }  // namespace gemm
+namespace moe {
+// defined in moe.cu
+__global__ void moe_lane_topk_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws);
+__global__ void moe_lane_route_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws);
+__global__ void moe_lane_gather_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws);
+__global__ void moe_lane_combine_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws);
+}  // namespace moe
 
 namespace lane {
 
@@ -141,6 +149,14 @@ struct Runtime {
   trace::BufferState* trace_state_d = nullptr;
   uint32_t trace_capacity = 0;
   bool committed = false;
+  // mixture of experts (only when some installed layer has experts)
+  std::vector<std::vector<MoeLayer>> moe_h;   // per instance, one entry per MoE layer (dense layers keep a blank)
+  std::vector<MoeLayer*> moe_d;
+  std::vector<int> moe_top_k, moe_inter, moe_n_local, moe_e_pad;  // per instance maxima (0: dense instance)
+  MoeLaneWs* mws_d = nullptr;      // [n_lanes]
+  MoeLaneMaps* mmaps_d = nullptr;  // [n_lanes][n_instances]
+  std::vector<void*> moe_allocs;
+  bool has_moe = false;
 };
 
 constexpr size_t kCounterWords = 1 << 14;
@@ -163,6 +179,12 @@ extern "C" void* xp_lane_create(int n_instances, int n_lanes, int policy, uint64
   rt->slots_h.resize(n_instances);
   rt->layers_h.resize(n_instances);
   rt->layers_d.assign(n_instances, nullptr);
+  rt->moe_h.resize(n_instances);
+  rt->moe_d.assign(n_instances, nullptr);
+  rt->moe_top_k.assign(n_instances, 0);
+  rt->moe_inter.assign(n_instances, 0);
+  rt->moe_n_local.assign(n_instances, 0);
+  rt->moe_e_pad.assign(n_instances, 0);
   for (auto& s : rt->slots_h) memset(&s, 0, sizeof(s));
   lane::LaneCtl ctl;
   memset(&ctl, 0, sizeof(ctl));
@@ -203,6 +225,7 @@ extern "C" int xp_lane_set_instance(void* h, int idx, const XpLaneInstanceDesc* 
                         kBn[v], 64, 2) != 0)
       return -3;
   }
+  s.input = d->input;
   s.in_flag = reinterpret_cast<const uint32_t*>(d->in_flag);
   s.record = reinterpret_cast<const InvocationRecord*>(d->record);
   s.act = d->act;
@@ -213,6 +236,7 @@ extern "C" int xp_lane_set_instance(void* h, int idx, const XpLaneInstanceDesc* 
   s.num_layers = d->num_layers;
   s.act_ld = d->act_ld;
   rt->layers_h[idx].assign(d->num_layers, lane::LayerEntry{});
+  rt->moe_h[idx].assign(d->num_layers, lane::MoeLayer{});
   return 0;
 }
 
@@ -222,12 +246,49 @@ extern "C" int xp_lane_set_layer(void* h, int inst, int layer, const XpLaneLayer
   auto& layers = rt->layers_h[inst];
   if (layer < 0 || layer >= static_cast<int>(layers.size())) return -1;
   const lane::InstanceSlot& s = rt->slots_h[inst];
-  if (d->inter_local % 128 != 0 || s.hidden % 128 != 0 || d->inter_local > s.act_ld) return -2;
+  const bool is_moe = d->num_experts > 0;
+  if (d->inter_local % 128 != 0 || s.hidden % 128 != 0 || (!is_moe && d->inter_local > s.act_ld)) return -2;
   lane::LayerEntry& e = layers[layer];
   memset(&e, 0, sizeof(e));
-  const int gu_rows = d->inter_local * (d->gated ? 2 : 1);
+  const int n_local = is_moe ? d->expert_hi - d->expert_lo : 1;
+  if (is_moe && (d->w_tiled || !d->gated || n_local < 1 || n_local > 1024 || d->expert_lo < 0 ||
+                 d->expert_hi > d->num_experts || d->num_experts > 256 || d->top_k < 1 || d->top_k > 32 ||
+                 d->top_k > d->num_experts || d->router == nullptr))
+    return -4;
+  const int gu_rows = d->inter_local * (d->gated ? 2 : 1) * n_local;
+  const uint64_t down_rows = static_cast<uint64_t>(s.hidden) * n_local;
   int rc;
-  if (d->w_tiled) {
+  if (is_moe) {
+    rc = tmap::encode_2d(&e.tmap_gateup, d->w_gateup, gu_rows, s.hidden, static_cast<uint64_t>(s.hidden) * 2, 128, 64, 2);
+    if (rc == 0)
+      rc = tmap::encode_2d(&e.tmap_down, d->w_down, down_rows, d->inter_local, static_cast<uint64_t>(d->inter_local) * 2, 128, 64, 2);
+    lane::MoeLayer& m = rt->moe_h[inst][layer];
+    memset(&m, 0, sizeof(m));
+    m.e_pad = (d->num_experts + 127) / 128 * 128;
+    if (rc == 0)
+      rc = tmap::encode_2d(&m.tmap_router, d->router, m.e_pad, s.hidden, static_cast<uint64_t>(s.hidden) * 2, 128, 64, 2);
+    m.correction_bias = d->correction_bias;
+    m.router_bias = d->router_bias;
+    m.num_experts = d->num_experts;
+    m.top_k = d->top_k;
+    m.expert_lo = d->expert_lo;
+    m.expert_hi = d->expert_hi;
+    m.sigmoid = d->sigmoid;
+    m.renormalize = d->renormalize;
+    m.scale = d->scale;
+    for (int b = 0; b < lane::kRowBuckets; ++b) {
+      const int rows = std::min(1 << b, s.capacity_rows);
+      gemm::TileChoice r = gemm::choose_tiles_host(m.e_pad / 128, rows, s.hidden / 64, 0, rt->sms, rt->ws_bytes_per_lane);
+      m.bn_router[b] = static_cast<uint8_t>(r.bn == 256 ? 255 : r.bn);
+      m.splits_router[b] = static_cast<uint8_t>(r.splits);
+    }
+    rt->has_moe = true;
+    rt->moe_top_k[inst] = std::max(rt->moe_top_k[inst], d->top_k);
+    rt->moe_inter[inst] = std::max(rt->moe_inter[inst], d->inter_local);
+    rt->moe_n_local[inst] = std::max(rt->moe_n_local[inst], n_local);
+    rt->moe_e_pad[inst] = std::max(rt->moe_e_pad[inst], m.e_pad);
+    e.kind = 2;
+  } else if (d->w_tiled) {
     rc = tmap::encode_2d(&e.tmap_gateup, d->w_gateup, static_cast<uint64_t>(gu_rows) * (s.hidden / 64), 64, 128, 128, 64, 2);
     if (rc == 0)
       rc = tmap::encode_2d(&e.tmap_down, d->w_down, static_cast<uint64_t>(s.hidden) * (d->inter_local / 64), 64, 128, 128, 64, 2);
@@ -242,7 +303,7 @@ extern "C" int xp_lane_set_layer(void* h, int inst, int layer, const XpLaneLayer
   e.inter_local = d->inter_local;
   e.gated = d->gated;
   e.w_tiled = d->w_tiled;
-  e.kind = 1;
+  if (!is_moe) e.kind = 1;
   e.gate_limit = d->gate_limit;
   e.up_add = d->up_add;
   e.act_alpha = d->act_alpha;
@@ -258,11 +319,86 @@ extern "C" int xp_lane_set_layer(void* h, int inst, int layer, const XpLaneLayer
   return 0;
 }
 
+// Allocates the per-Lane MoE scratch (sized for the largest MoE instance) and the tensor maps
+// over it for every MoE instance.
+static int commit_moe(Runtime* rt) {
+  size_t routes = 0, rows = 0, hidden = 0, inter = 0, e_pad = 0, n_local = 0, tm = 0;
+  for (int i = 0; i < rt->n_instances; ++i) {
+    if (rt->moe_top_k[i] == 0) continue;
+    const lane::InstanceSlot& s = rt->slots_h[i];
+    routes = std::max<size_t>(routes, static_cast<size_t>(s.capacity_rows) * rt->moe_top_k[i]);
+    rows = std::max<size_t>(rows, s.capacity_rows);
+    hidden = std::max<size_t>(hidden, s.hidden);
+    inter = std::max<size_t>(inter, rt->moe_inter[i]);
+    e_pad = std::max<size_t>(e_pad, rt->moe_e_pad[i]);
+    n_local = std::max<size_t>(n_local, rt->moe_n_local[i]);
+    tm = std::max<size_t>(tm, std::max<size_t>(s.hidden / 128, rt->moe_inter[i] / 128));
+  }
+  const size_t max_tiles = tm * (routes / 16 + n_local) + 8;
+  std::vector<lane::MoeLaneWs> ws(rt->n_lanes);
+  std::vector<lane::MoeLaneMaps> maps(static_cast<size_t>(rt->n_lanes) * rt->n_instances);
+  auto alloc = [&](size_t bytes) -> void* {
+    void* p = nullptr;
+    if (cudaMalloc(&p, std::max<size_t>(bytes, 256)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, std::max<size_t>(bytes, 256));
+    rt->moe_allocs.push_back(p);
+    return p;
+  };
+  static const int kBn[lane::kBnVariants] = {16, 32, 64, 128, 256};
+  for (int l = 0; l < rt->n_lanes; ++l) {
+    lane::MoeLaneWs& w = ws[l];
+    w.logits = static_cast<__nv_bfloat16*>(alloc(rows * e_pad * 2));
+    w.ids = static_cast<int*>(alloc(routes * 4));
+    w.weights = static_cast<float*>(alloc(routes * 4));
+    w.offsets = static_cast<int*>(alloc((n_local + 1) * 4));
+    w.perm_token = static_cast<int*>(alloc(routes * 4));
+    w.route_pos = static_cast<int*>(alloc(routes * 4));
+    w.tiles_gateup = static_cast<int4*>(alloc(max_tiles * 16));
+    w.tiles_down = static_cast<int4*>(alloc(max_tiles * 16));
+    w.n_tiles = static_cast<int*>(alloc(8));
+    w.xp = alloc(routes * hidden * 2);
+    w.act = alloc(routes * inter * 2);
+    w.yp = alloc(routes * hidden * 2);
+    w.cap_routes = static_cast<int>(routes);
+    if (!w.logits || !w.ids || !w.weights || !w.offsets || !w.perm_token || !w.route_pos || !w.tiles_gateup || !w.tiles_down ||
+        !w.n_tiles || !w.xp || !w.act || !w.yp)
+      return -5;
+    for (int i = 0; i < rt->n_instances; ++i) {
+      if (rt->moe_top_k[i] == 0) continue;
+      const lane::InstanceSlot& s = rt->slots_h[i];
+      const uint64_t r = static_cast<uint64_t>(s.capacity_rows) * rt->moe_top_k[i];
+      lane::MoeLaneMaps& m = maps[static_cast<size_t>(l) * rt->n_instances + i];
+      for (int v = 0; v < lane::kBnVariants; ++v) {
+        if (tmap::encode_2d(&m.tmap_xp[v], w.xp, r, s.hidden, static_cast<uint64_t>(s.hidden) * 2, kBn[v], 64, 2) != 0) return -6;
+        if (tmap::encode_2d(&m.tmap_act[v], w.act, r, rt->moe_inter[i], static_cast<uint64_t>(rt->moe_inter[i]) * 2, kBn[v], 64, 2) != 0)
+          return -6;
+      }
+    }
+  }
+  if (cudaMalloc(&rt->mws_d, sizeof(lane::MoeLaneWs) * rt->n_lanes) != cudaSuccess) return -5;
+  if (cudaMalloc(&rt->mmaps_d, sizeof(lane::MoeLaneMaps) * maps.size()) != cudaSuccess) return -5;
+  cudaMemcpy(rt->mws_d, ws.data(), sizeof(lane::MoeLaneWs) * rt->n_lanes, cudaMemcpyHostToDevice);
+  cudaMemcpy(rt->mmaps_d, maps.data(), sizeof(lane::MoeLaneMaps) * maps.size(), cudaMemcpyHostToDevice);
+  return 0;
+}
+
 extern "C" int xp_lane_commit(void* h) {
   auto* rt = static_cast<Runtime*>(h);
+  if (rt->has_moe && rt->mws_d == nullptr) {
+    const int rc = commit_moe(rt);
+    if (rc != 0) return rc;
+  }
   for (int i = 0; i < rt->n_instances; ++i) {
     auto& L = rt->layers_h[i];
     if (L.empty()) return -1;
+    if (rt->moe_top_k[i] > 0) {
+      // every MoE layer of one instance must share the inter size the scratch maps were built for
+      for (size_t l = 0; l < L.size(); ++l)
+        if (L[l].kind == 2 && L[l].inter_local != rt->moe_inter[i]) return -7;
+      if (rt->moe_d[i] == nullptr && cudaMalloc(&rt->moe_d[i], sizeof(lane::MoeLayer) * L.size()) != cudaSuccess) return -2;
+      cudaMemcpy(rt->moe_d[i], rt->moe_h[i].data(), sizeof(lane::MoeLayer) * L.size(), cudaMemcpyHostToDevice);
+      for (size_t l = 0; l < L.size(); ++l) L[l].moe = L[l].kind == 2 ? rt->moe_d[i] + l : nullptr;
+    }
     if (rt->layers_d[i] == nullptr && cudaMalloc(&rt->layers_d[i], sizeof(lane::LayerEntry) * L.size()) != cudaSuccess) return -2;
     cudaMemcpy(rt->layers_d[i], L.data(), sizeof(lane::LayerEntry) * L.size(), cudaMemcpyHostToDevice);
     rt->slots_h[i].layers = rt->layers_d[i];
@@ -289,9 +425,22 @@ extern "C" int xp_lane_launch(void* h, int lane_index, uint64_t lease_ns, void* 
   uint32_t* counters = rt->counters_d + lane::kCounterWords * lane_index;
   const int smem_budget = 200 * 1024;
   const int smem = smem_budget + 2048;
+  const lane::MoeLaneWs* mws = rt->has_moe ? rt->mws_d + lane_index : nullptr;
+  const lane::MoeLaneMaps* mmaps = rt->has_moe ? rt->mmaps_d + static_cast<size_t>(lane_index) * rt->n_instances : nullptr;
   lane::lane_wait_kernel<<<1, 1, 0, s>>>(rt->ctl_d, rt->slots_d, cur, lane_index, lease_ns);
-  gemm::gemm_lane_kernel<<<rt->sms, gemm::kThreads, smem, s>>>(rt->slots_d, cur, 0, ws, counters, smem_budget, rt->status_d);
-  gemm::gemm_lane_kernel<<<rt->sms, gemm::kThreads, smem, s>>>(rt->slots_d, cur, 1, ws, counters, smem_budget, rt->status_d);
+  if (rt->has_moe) {
+    // MoE prologue; every kernel returns at once when the invocation's layer is dense
+    gemm::gemm_lane_kernel<<<rt->sms, gemm::kThreads, smem, s>>>(rt->slots_d, cur, 2, ws, counters, smem_budget, rt->status_d,
+                                                                 mws, mmaps);
+    moe::moe_lane_topk_kernel<<<rt->sms, 128, 0, s>>>(rt->slots_d, cur, mws);
+    moe::moe_lane_route_kernel<<<1, 1024, 0, s>>>(rt->slots_d, cur, mws);
+    moe::moe_lane_gather_kernel<<<rt->sms * 4, 128, 0, s>>>(rt->slots_d, cur, mws);
+  }
+  gemm::gemm_lane_kernel<<<rt->sms, gemm::kThreads, smem, s>>>(rt->slots_d, cur, 0, ws, counters, smem_budget, rt->status_d, mws,
+                                                               mmaps);
+  gemm::gemm_lane_kernel<<<rt->sms, gemm::kThreads, smem, s>>>(rt->slots_d, cur, 1, ws, counters, smem_budget, rt->status_d, mws,
+                                                               mmaps);
+  if (rt->has_moe) moe::moe_lane_combine_kernel<<<rt->sms * 4, 128, 0, s>>>(rt->slots_d, cur, mws);
   lane::lane_complete_kernel<<<1, 1, 0, s>>>(rt->ctl_d, rt->slots_d, cur, lane_index);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);
@@ -365,6 +514,11 @@ extern "C" void xp_lane_destroy(void* h) {
   if (rt->trace_state_d != nullptr) cudaFree(rt->trace_state_d);
   for (auto* p : rt->layers_d)
     if (p != nullptr) cudaFree(p);
+  for (auto* p : rt->moe_d)
+    if (p != nullptr) cudaFree(p);
+  for (void* p : rt->moe_allocs) cudaFree(p);
+  if (rt->mws_d != nullptr) cudaFree(rt->mws_d);
+  if (rt->mmaps_d != nullptr) cudaFree(rt->mmaps_d);
   cudaFree(rt->ctl_d);
   cudaFree(rt->slots_d);
   cudaFree(rt->cur_d);

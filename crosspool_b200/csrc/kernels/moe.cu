@@ -14,6 +14,7 @@
 #include <math_constants.h>
 
 #include "xpool/api.h"
+#include "xpool/lane.cuh"
 #include "xpool/sm100.cuh"
 
 namespace xpool {
@@ -22,11 +23,7 @@ namespace moe {
 constexpr int kMaxPerLane = 8;  // up to 256 experts
 
 // One warp per token.
-__global__ void __launch_bounds__(128)
-router_topk_kernel(XpRouterArgs a) {
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= a.rows) return;
+__device__ __forceinline__ void router_topk_row(const XpRouterArgs& a, int row, int lane) {
   const int E = a.num_experts;
   float score[kMaxPerLane], sel[kMaxPerLane];
   float mx = -CUDART_INF_F;
@@ -112,6 +109,13 @@ router_topk_kernel(XpRouterArgs a) {
     a.topk_ids[static_cast<size_t>(row) * a.top_k + lane] = my_id;
     a.topk_weights[static_cast<size_t>(row) * a.top_k + lane] = w;
   }
+}
+
+__global__ void __launch_bounds__(128)
+router_topk_kernel(XpRouterArgs a) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  router_topk_row(a, row, threadIdx.x & 31);
 }
 
 // counts[e - lo] = routes naming expert e; one CTA per local expert.
@@ -217,10 +221,9 @@ gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ perm_tok
 
 // out[token] = sum over k (in order) of w[token, k] * y[route_pos[token, k]]; routes with
 // position < 0 (experts of other ranks, padding) contribute nothing.
-__global__ void __launch_bounds__(128)
-combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ route_pos, const float* __restrict__ weights,
-               __nv_bfloat16* __restrict__ out, int top_k, int hidden, int ld_out) {
-  const int token = blockIdx.x;
+__device__ __forceinline__ void combine_token(const __nv_bfloat16* __restrict__ y, const int* __restrict__ route_pos,
+                                              const float* __restrict__ weights, __nv_bfloat16* __restrict__ out, int top_k,
+                                              int hidden, int ld_out, int token) {
   for (int c = threadIdx.x * 8; c < hidden; c += 128 * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int k = 0; k < top_k; ++k) {
@@ -244,6 +247,154 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ rout
   }
 }
 
+__global__ void __launch_bounds__(128)
+combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ route_pos, const float* __restrict__ weights,
+               __nv_bfloat16* __restrict__ out, int top_k, int hidden, int ld_out) {
+  combine_token(y, route_pos, weights, out, top_k, hidden, ld_out, blockIdx.x);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Lane forms: the same steps with every parameter read from the Lane's current invocation, so
+// that one captured graph serves dense and MoE layers of every model. Each is a no-op unless the
+// invocation's layer is a mixture-of-experts layer.
+
+__device__ __forceinline__ const lane::MoeLayer* lane_moe_layer(const lane::InstanceSlot* slots, const lane::LaneCur* cur) {
+  if (cur->valid == 0 || cur->rows == 0) return nullptr;
+  return slots[cur->instance].layers[cur->layer].moe;
+}
+
+__global__ void __launch_bounds__(128)
+moe_lane_topk_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws) {
+  const lane::MoeLayer* m = lane_moe_layer(slots, cur);
+  if (m == nullptr) return;
+  XpRouterArgs a;
+  a.logits = ws->logits;
+  a.logit_bias = m->router_bias;
+  a.correction_bias = m->correction_bias;
+  a.topk_ids = ws->ids;
+  a.topk_weights = ws->weights;
+  a.rows = static_cast<int>(cur->rows);
+  a.num_experts = m->num_experts;
+  a.top_k = m->top_k;
+  a.ld_logits = m->e_pad;
+  a.logits_fp32 = 0;
+  a.sigmoid = m->sigmoid;
+  a.renormalize = m->renormalize;
+  a.round_weights_bf16 = 0;
+  a.scale = m->scale;
+  for (int row = blockIdx.x * 4 + (threadIdx.x >> 5); row < a.rows; row += gridDim.x * 4) router_topk_row(a, row, threadIdx.x & 31);
+}
+
+// Exclusive scan of one int per thread across a 1024-thread CTA; returns the prefix, *total the sum.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int* total) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) warp_sums[w] = inc;
+  __syncthreads();
+  if (w == 0) {
+    int ws = warp_sums[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, ws, o);
+      if (lane >= o) ws += t;
+    }
+    warp_sums[lane] = ws;
+  }
+  __syncthreads();
+  const int base = w > 0 ? warp_sums[w - 1] : 0;
+  *total = warp_sums[31];
+  __syncthreads();
+  return base + inc - v;
+}
+
+// One CTA orders the routes of this rank's experts and writes both tile tables. Positions inside
+// an expert's segment are handed out by an atomic cursor; expert outputs do not depend on the
+// position of a row, and the combine step sums a token's routes in top-k order, so results are
+// reproducible although the placement is not.
+__global__ void __launch_bounds__(1024)
+moe_lane_route_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws) {
+  const lane::MoeLayer* m = lane_moe_layer(slots, cur);
+  if (m == nullptr) return;
+  __shared__ int hist[1024], cursor[1024], warp_sums[32];
+  const lane::InstanceSlot& s = slots[cur->instance];
+  const lane::LayerEntry& le = s.layers[cur->layer];
+  const int lo = m->expert_lo, n_local = m->expert_hi - m->expert_lo;
+  const int n_routes = static_cast<int>(cur->rows) * m->top_k;
+  const int bn = lane::moe_tile_width(static_cast<int>(cur->rows), m->top_k, n_local);
+  const int tm_gu = le.inter_local / 128, tm_dn = s.hidden / 128;
+  const int e = threadIdx.x;
+  hist[e] = 0;
+  __syncthreads();
+  for (int i = e; i < n_routes; i += 1024) {
+    const int x = ws->ids[i] - lo;
+    if (x >= 0 && x < n_local) atomicAdd(&hist[x], 1);
+    else ws->route_pos[i] = -1;
+  }
+  __syncthreads();
+  const int c = e < n_local ? hist[e] : 0;
+  const int nb = (c + bn - 1) / bn;
+  int total_rows, total_gu, total_dn;
+  const int off = block_exclusive_scan(c, warp_sums, &total_rows);
+  const int t_gu = block_exclusive_scan(tm_gu * nb, warp_sums, &total_gu);
+  const int t_dn = block_exclusive_scan(tm_dn * nb, warp_sums, &total_dn);
+  cursor[e] = off;
+  if (e <= n_local) ws->offsets[e] = off;  // thread n_local sees the sum of all counts
+  if (e == 0) {
+    ws->n_tiles[0] = total_gu;
+    ws->n_tiles[1] = total_dn;
+    if (n_local == 1024) ws->offsets[1024] = total_rows;
+  }
+  __syncthreads();
+  for (int i = e; i < n_routes; i += 1024) {
+    const int x = ws->ids[i] - lo;
+    if (x >= 0 && x < n_local) {
+      const int pos = atomicAdd(&cursor[x], 1);
+      ws->perm_token[pos] = i / m->top_k;
+      ws->route_pos[i] = pos;
+    }
+  }
+  if (e < n_local) {
+    const int row0 = off, row1 = off + c;
+    int idx = t_gu;
+    for (int t = 0; t < tm_gu; ++t)
+      for (int r = row0; r < row1; r += bn) ws->tiles_gateup[idx++] = make_int4(e, t * 128, r, row1);
+    idx = t_dn;
+    for (int t = 0; t < tm_dn; ++t)
+      for (int r = row0; r < row1; r += bn) ws->tiles_down[idx++] = make_int4(e, t * 128, r, row1);
+  }
+}
+
+__global__ void __launch_bounds__(128)
+moe_lane_gather_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws) {
+  const lane::MoeLayer* m = lane_moe_layer(slots, cur);
+  if (m == nullptr) return;
+  const lane::InstanceSlot& s = slots[cur->instance];
+  const int n = ws->offsets[m->expert_hi - m->expert_lo];
+  const int hidden8 = s.hidden / 8;
+  const uint4* x = reinterpret_cast<const uint4*>(s.input);
+  uint4* out = reinterpret_cast<uint4*>(ws->xp);
+  for (int pos = blockIdx.x; pos < n; pos += gridDim.x) {
+    const uint4* src = x + static_cast<size_t>(ws->perm_token[pos]) * hidden8;
+    uint4* dst = out + static_cast<size_t>(pos) * hidden8;
+    for (int i = threadIdx.x; i < hidden8; i += 128) dst[i] = src[i];
+  }
+}
+
+__global__ void __launch_bounds__(128)
+moe_lane_combine_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws) {
+  const lane::MoeLayer* m = lane_moe_layer(slots, cur);
+  if (m == nullptr) return;
+  const lane::InstanceSlot& s = slots[cur->instance];
+  for (int token = blockIdx.x; token < static_cast<int>(cur->rows); token += gridDim.x)
+    combine_token(reinterpret_cast<const __nv_bfloat16*>(ws->yp), ws->route_pos, ws->weights,
+                  reinterpret_cast<__nv_bfloat16*>(s.out_peer), m->top_k, s.hidden, s.hidden, token);
+}
+
 }  // namespace moe
 }  // namespace xpool
 
@@ -264,7 +415,7 @@ extern "C" int xp_router_topk(const XpRouterArgs* a, void* stream) {
 extern "C" int xp_moe_route(const XpRouteArgs* a, void* stream) {
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int n_local = a->expert_hi - a->expert_lo;
-  if (n_local < 1 || n_local > 1024) return -10;
+  if (n_local < 1 || n_local > 1023) return -10;
   const int n_routes = a->rows * a->top_k;
   cudaMemsetAsync(a->route_pos, 0xff, sizeof(int) * n_routes, s);  // -1: not handled by this rank
   route_count_kernel<<<n_local, 256, 0, s>>>(a->topk_ids, n_routes, a->expert_lo, a->counts);

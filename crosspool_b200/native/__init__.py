@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 13
+EXPECTED_ABI = 14
 HERE = Path(__file__).resolve().parent
 
 
@@ -273,6 +273,17 @@ class LaneLayerDesc(C.Structure):
         ("gate_limit", C.c_float),
         ("up_add", C.c_float),
         ("act_alpha", C.c_float),
+        ("router", C.c_void_p),
+        ("correction_bias", C.c_void_p),
+        ("router_bias", C.c_void_p),
+        ("num_experts", C.c_int),
+        ("top_k", C.c_int),
+        ("expert_lo", C.c_int),
+        ("expert_hi", C.c_int),
+        ("sigmoid", C.c_int),
+        ("renormalize", C.c_int),
+        ("scale", C.c_float),
+        ("reserved", C.c_int),
     ]
 
 

@@ -91,10 +91,31 @@ class InstancePlacement:
     atn_rank: int
     ffn_ranks: tuple[int, ...]
     capacity_rows: int
+    moe_parallel: str = "ep"  # how MoE layers use the FFN ranks: "ep" (experts split) or "tp" (every expert split)
 
     @property
     def tp(self) -> int:
         return len(self.ffn_ranks)
+
+    @property
+    def expert_parallel(self) -> bool:
+        return self.cfg.is_moe and self.moe_parallel == "ep" and self.tp > 1
+
+    def expert_range(self, group_rank: int) -> tuple[int, int]:
+        """Experts owned by the ``group_rank``-th FFN rank (all of them unless expert parallel)."""
+        e = self.cfg.num_experts
+        if not self.expert_parallel:
+            return 0, e
+        if e % self.tp:
+            raise ValueError(f"{e} experts do not split evenly over {self.tp} ranks")
+        per = e // self.tp
+        return group_rank * per, (group_rank + 1) * per
+
+    def dense_inter_local(self) -> int:
+        """Widest dense-layer shard of this instance on one FFN rank (0 if every layer is MoE)."""
+        cfg = self.cfg
+        has_dense = not cfg.is_moe or cfg.first_k_dense > 0
+        return cfg.intermediate_size // self.tp if has_dense else 0
 
 
 @dataclass
@@ -116,8 +137,8 @@ class Topology:
 
 
 def ffn_slot_layout(p: InstancePlacement) -> rt.FfnSlotLayout:
-    inter = (p.cfg.moe_intermediate_size if p.cfg.is_moe else p.cfg.intermediate_size) // p.tp
-    return rt.plan_ffn_slot(p.capacity_rows, p.cfg.hidden_size, inter)
+    # the slot's activation scratch serves dense layers; MoE layers use the Lane's own scratch
+    return rt.plan_ffn_slot(p.capacity_rows, p.cfg.hidden_size, max(p.dense_inter_local(), 128))
 
 
 def atn_slot_layout(p: InstancePlacement) -> rt.AtnSlotLayout:
@@ -195,8 +216,14 @@ class FfnRankRuntime:
     def add_instance(self, place: InstancePlacement, tp_rank: int) -> FfnInstanceState:
         lay = ffn_slot_layout(place)
         slot = PeerBuffer(lay.total_bytes)
-        weights = [random_ffn_layer(place.cfg, l, place.seed, self.device, torch.bfloat16, tp_rank, place.tp)
-                   for l in range(place.cfg.num_layers)]
+        cfg = place.cfg
+        weights = []
+        for l in range(cfg.num_layers):
+            if cfg.layer_is_moe(l) and place.expert_parallel:
+                w = random_ffn_layer(cfg, l, place.seed, self.device, torch.bfloat16, expert_range=place.expert_range(tp_rank))
+            else:
+                w = random_ffn_layer(cfg, l, place.seed, self.device, torch.bfloat16, tp_rank, place.tp)
+            weights.append(w)
         st = FfnInstanceState(place, tp_rank, slot, weights)
         self.instances.append(st)
         return st
@@ -212,7 +239,7 @@ class FfnRankRuntime:
         self._keep = []
         for i, st in enumerate(self.instances):
             p, flay, alay = st.place, ffn_slot_layout(st.place), atn_slot_layout(st.place)
-            inter = st.weights[0].gate_up.shape[0] // 2
+            act_ld = max(p.dense_inter_local(), 128)
             d = native.LaneInstanceDesc()
             d.input = st.slot.ptr + flay.input_offset
             d.act = st.slot.ptr + flay.act_offset
@@ -220,18 +247,39 @@ class FfnRankRuntime:
             d.record = st.slot.ptr + flay.record_offset
             d.out_peer = st.atn_base + alay.output_offset + st.tp_rank * alay.output_stride
             d.done_record_peer = st.atn_base + alay.completion_offset + st.tp_rank * RECORD_BYTES
-            d.capacity_rows, d.hidden, d.num_layers, d.act_ld = p.capacity_rows, p.cfg.hidden_size, p.cfg.num_layers, inter
+            d.capacity_rows, d.hidden, d.num_layers, d.act_ld = p.capacity_rows, p.cfg.hidden_size, p.cfg.num_layers, act_ld
             native.check(lib.xp_lane_set_instance(self.handle, i, C.byref(d)), "xp_lane_set_instance", 0)
             for l, w in enumerate(st.weights):
                 gu, dn = w.gate_up, w.down
-                if self.tile_weights:
-                    gu, dn = gemm.tile_weight(gu), gemm.tile_weight(dn)
-                    self._keep.append((gu, dn))
                 ld = native.LaneLayerDesc()
+                if w.is_moe:
+                    from ..ops.moe import padded_router
+
+                    if w.shared_gate_up is not None:
+                        raise NotImplementedError("shared experts are served by ops.moe.moe_forward, not by Lanes yet")
+                    cfg = p.cfg
+                    router = padded_router(w.router)
+                    self._keep.append(router)
+                    lo, hi = p.expert_range(st.tp_rank)
+                    ld.router = router.data_ptr()
+                    cb, rb = w.extra.get("correction_bias"), w.extra.get("router_bias")
+                    ld.correction_bias = cb.data_ptr() if cb is not None else None
+                    ld.router_bias = rb.data_ptr() if rb is not None else None
+                    ld.num_experts, ld.top_k, ld.expert_lo, ld.expert_hi = cfg.num_experts, cfg.num_experts_per_tok, lo, hi
+                    ld.sigmoid, ld.renormalize = int(cfg.router_scoring == "sigmoid"), int(cfg.norm_topk_prob)
+                    ld.scale = cfg.routed_scaling_factor
+                    inter = gu.shape[1] // 2
+                    ld.w_tiled = 0
+                else:
+                    inter = gu.shape[0] // 2
+                    if self.tile_weights:
+                        gu, dn = gemm.tile_weight(gu), gemm.tile_weight(dn)
+                        self._keep.append((gu, dn))
+                    ld.w_tiled = int(self.tile_weights)
                 ld.w_gateup, ld.w_down = gu.data_ptr(), dn.data_ptr()
                 ld.bias_gateup = w.gate_up_bias.data_ptr() if w.gate_up_bias is not None else None
                 ld.bias_down = w.down_bias.data_ptr() if w.down_bias is not None else None
-                ld.inter_local, ld.gated, ld.w_tiled = inter, 1, int(self.tile_weights)
+                ld.inter_local, ld.gated = inter, 1
                 native.check(lib.xp_lane_set_layer(self.handle, i, l, C.byref(ld)), "xp_lane_set_layer", 0)
         native.check(lib.xp_lane_commit(self.handle), "xp_lane_commit", 0)
 
@@ -241,16 +289,20 @@ class FfnRankRuntime:
                      "xp_lane_launch", 4)
 
     # -- serving threads ---------------------------------------------------------------------
-    def _lane_loop(self, lane: int, lease_ms: float, depth: int) -> None:
+    def _capture_lane(self, lane: int, lease_ms: float):
+        stream = torch.cuda.Stream(self.device)
+        with torch.cuda.stream(stream):
+            self.launch_once(lane, min(lease_ms, 1.0), stream)  # eager once: set-up work outside capture
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+                self.launch_once(lane, lease_ms, stream)
+        return stream, graph
+
+    def _lane_loop(self, lane: int, stream, graph, depth: int) -> None:
         try:
             torch.cuda.set_device(self.device)
-            stream = torch.cuda.Stream(self.device)
             with torch.cuda.stream(stream):
-                self.launch_once(lane, lease_ms, stream)  # eager once: set-up work outside capture
-                stream.synchronize()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=stream):
-                    self.launch_once(lane, lease_ms, stream)
                 pending: deque[torch.cuda.Event] = deque()
                 while not self._stop.is_set():
                     graph.replay()
@@ -264,9 +316,15 @@ class FfnRankRuntime:
             self.errors.append(f"lane {lane}: {e!r}")
 
     def start(self, lease_ms: float = 20.0, depth: int = 3) -> None:
+        """Captures every Lane's graph on the calling thread, one after the other (stream capture
+        does not tolerate another thread of the process preparing its own capture), then starts one
+        replay thread per Lane."""
         self._stop.clear()
-        for lane in range(self.n_lanes):
-            t = threading.Thread(target=self._lane_loop, args=(lane, lease_ms, depth), daemon=True, name=f"lane{lane}")
+        torch.cuda.set_device(self.device)
+        captured = [self._capture_lane(lane, lease_ms) for lane in range(self.n_lanes)]
+        self._graphs = captured
+        for lane, (stream, graph) in enumerate(captured):
+            t = threading.Thread(target=self._lane_loop, args=(lane, stream, graph, depth), daemon=True, name=f"lane{lane}")
             t.start()
             self._threads.append(t)
 

@@ -135,7 +135,7 @@ def test_fabric_observer_records_lane_events_in_order_and_counts_overflow():
         ffn.launch_once(0, lease_ms=2)                      # idle
         x = (torch.randn(3, place.cfg.hidden_size, device="cuda") * 0.5).bfloat16()
         for seq in (1, 2):
-            _publish(F, st, place, x, seq - 1, seq)
+            _publish(F, st, place, x, 0, seq)
             ffn.launch_once(0, lease_ms=20)
             torch.cuda.synchronize()
         art = devkit.FabricObserver(ffn).collect()
@@ -146,3 +146,88 @@ def test_fabric_observer_records_lane_events_in_order_and_counts_overflow():
         assert ts == sorted(ts)
     finally:
         ffn.close()
+
+
+def _moe_cfg(E=8, k=2, hidden=256, inter=128, layers=1):
+    from crosspool_b200.models.config import ModelConfig
+
+    return ModelConfig(name="tmoe", architecture="Qwen3MoeForCausalLM", hidden_size=hidden, num_layers=layers, num_q_heads=4,
+                       num_kv_heads=2, head_dim=64, intermediate_size=inter, vocab_size=128, num_experts=E,
+                       num_experts_per_tok=k, moe_intermediate_size=inter)
+
+
+@pytest.mark.parametrize("E,k,hidden,inter,rows", [(8, 2, 256, 128, 7), (128, 8, 2048, 768, 64), (128, 8, 2048, 768, 1)])
+def test_lane_serves_a_moe_layer_and_a_dense_model_from_one_graph(E, k, hidden, inter, rows):
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.models.reference import moe_ffn
+    from crosspool_b200.parallel import fabric as F
+
+    ffn = F.FfnRankRuntime("cuda", n_lanes=1)
+    cfgs = [_moe_cfg(E, k, hidden, inter), mc.preset("Qwen/Qwen3-0.6B").with_layers(1)]
+    places, atn = [], []
+    for i, cfg in enumerate(cfgs):
+        p = F.InstancePlacement(f"m{i}", cfg, seed=i + 3, atn_rank=0, ffn_ranks=(1,), capacity_rows=128)
+        st = ffn.add_instance(p, 0)
+        buf = F.PeerBuffer(F.atn_slot_layout(p).total_bytes)
+        st.atn_base = buf.ptr
+        places.append(p)
+        atn.append(buf)
+    ffn.install()
+    try:
+        g = torch.Generator(device="cuda").manual_seed(rows)
+        xs = [(torch.randn(rows, c.hidden_size, device="cuda", generator=g) * 0.5).bfloat16() for c in cfgs]
+        for i in (0, 1):
+            _publish(F, ffn.instances[i], places[i], xs[i], 0, 1)
+        ffn.launch_once(0, lease_ms=20)
+        ffn.launch_once(0, lease_ms=20)
+        torch.cuda.synchronize()
+        assert ffn.stats()["status"] == 0 and ffn.stats()["served"] == [1, 1]
+        out, rc, nrows, seq = _result(F, atn[0], places[0], rows)
+        assert (rc, nrows, seq) == (0, rows, 1)
+        ref = moe_ffn(xs[0], ffn.instances[0].weights[0], cfgs[0]).float()
+        err = (out.float() - ref).abs()
+        assert (err.max() / ref.abs().max().clamp_min(1e-6)).item() < 0.05
+        assert (err.pow(2).mean().sqrt() / ref.pow(2).mean().sqrt().clamp_min(1e-9)).item() < 0.02
+        out1, rc1, _, _ = _result(F, atn[1], places[1], rows)
+        assert rc1 == 0
+        torch.testing.assert_close(out1.float(), _ref(xs[1], ffn.instances[1].weights[0]), atol=2e-2, rtol=2e-2)
+    finally:
+        ffn.close()
+
+
+def test_expert_parallel_lane_partials_fold_to_the_full_moe_output():
+    """Two FFN ranks' runtimes (run one after the other here; they never wait on each other) each own
+    half of the experts; the rank-order fp32 fold of their partials equals the full layer."""
+    from crosspool_b200.models.reference import moe_ffn
+    from crosspool_b200.models.weights import random_ffn_layer
+    from crosspool_b200.parallel import fabric as F
+
+    cfg = _moe_cfg(16, 4, 512, 256)
+    place = F.InstancePlacement("m", cfg, seed=9, atn_rank=0, ffn_ranks=(1, 2), capacity_rows=64)
+    assert place.expert_parallel and place.expert_range(1) == (8, 16)
+    buf = F.PeerBuffer(F.atn_slot_layout(place).total_bytes)
+    x = (torch.randn(33, cfg.hidden_size, device="cuda") * 0.5).bfloat16()
+    rts = []
+    try:
+        for r in (0, 1):
+            ffn = F.FfnRankRuntime("cuda", n_lanes=1)
+            rts.append(ffn)
+            st = ffn.add_instance(place, r)
+            st.atn_base = buf.ptr
+            ffn.install()
+            _publish(F, st, place, x, 0, 1)
+            ffn.launch_once(0, lease_ms=20)
+            torch.cuda.synchronize()
+            assert ffn.stats()["status"] == 0
+        alay = F.atn_slot_layout(place)
+        parts = [buf.tensor(alay.output_offset + r * alay.output_stride, (64, cfg.hidden_size), torch.bfloat16, "cuda")[:33]
+                 for r in (0, 1)]
+        full = random_ffn_layer(cfg, 0, 9, "cuda", torch.bfloat16)
+        ref = moe_ffn(x, full, cfg).float()
+        got = parts[0].float() + parts[1].float()
+        err = (got - ref).abs()
+        assert (err.max() / ref.abs().max()).item() < 0.05
+    finally:
+        for ffn in rts:
+            ffn.close()
+        buf.free()

@@ -10,11 +10,12 @@ import time
 import numpy as np
 import pytest
 
+from crosspool_b200 import native
 from crosspool_b200.native import runtime as rt
 
 
 def test_abi_and_record_sizes():
-    assert rt.lib().xr_abi_version() == 13
+    assert rt.lib().xr_abi_version() == native.EXPECTED_ABI
     assert rt.lib().xr_record_bytes(0) == 256  # InvocationRecord
     assert rt.lib().xr_record_bytes(1) == 256  # CompletionRecord
 
