@@ -1,0 +1,174 @@
+"""Kernel microbenchmarks with roofline fractions.
+
+``python -m crosspool_b200.bench.kernels gemm --rows 64 --n 3072 --k 1024 --dual 1``
+``python -m crosspool_b200.bench.kernels decode-attn --batch 64``
+``python -m crosspool_b200.bench.kernels norm --rows 256 --hidden 1024``
+``python -m crosspool_b200.bench.kernels moe --rows 64``
+
+Each case runs ``--warmup`` untimed iterations, then times ``--iters`` launches with CUDA events on
+the launching stream, writing a buffer larger than L2 between launches, and prints one JSON line:
+median microseconds, achieved GB/s and TFLOP/s, and the fractions of the measured copy bandwidth and
+cuBLAS bf16 throughput (``MEASURED_PEAKS.json`` at the repository root when present, else 6.65 TB/s
+and 1.59 PFLOP/s, reported as "fallback"). ``--iters 1 --warmup 1 --no-flush`` gives a small
+fixed-launch run suitable for a profiler.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import random
+import statistics
+from pathlib import Path
+
+import torch
+
+
+def peaks() -> dict:
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class Timer:
+    def __init__(self, iters: int, warmup: int, flush: bool):
+        self.iters, self.warmup = iters, warmup
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+
+    def __call__(self, fn) -> float:
+        for _ in range(self.warmup):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(self.iters):
+            if self.flush is not None:
+                self.flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(ts)
+
+
+def report(name: str, us: float, bytes_moved: float, flops: float, extra: dict) -> dict:
+    pk = peaks()
+    gbs, tfl = bytes_moved / us / 1e3, flops / us / 1e6
+    out = {"kernel": name, "us": round(us, 2), "gbs": round(gbs, 1), "tflops": round(tfl, 2),
+           f"frac_hbm_of_{pk['source']}": round(gbs / pk["hbm_gbs"], 3),
+           f"frac_bf16_of_{pk['source']}": round(tfl / pk["bf16_tflops"], 3), **extra}
+    print(json.dumps(out), flush=True)
+    return out
+
+
+def bench_gemm(ns, timer: Timer) -> dict:
+    from ..ops import gemm
+
+    dev = torch.device("cuda")
+    x = (torch.randn(ns.rows, ns.k, device=dev) * 0.5).bfloat16()
+    w = (torch.randn(ns.n * (2 if ns.dual else 1), ns.k, device=dev) * 0.05).bfloat16()
+    out = torch.empty(ns.rows, ns.n, dtype=torch.bfloat16, device=dev)
+    fn = (lambda: gemm.gateup_swiglu(x, w, out=out, splits=ns.splits, bn=ns.bn)) if ns.dual else \
+        (lambda: gemm.linear(x, w, out=out, splits=ns.splits, bn=ns.bn))
+    us = timer(fn)
+    gemm.check_status(dev)
+    plan = gemm.plan_shape(ns.n, ns.k, ns.rows, int(ns.dual))
+    byts = (w.numel() + x.numel() + out.numel()) * 2
+    return report("gemm_ws" + ("_swiglu" if ns.dual else ""), us, byts, 2.0 * ns.rows * w.shape[0] * ns.k,
+                  {"rows": ns.rows, "n": ns.n, "k": ns.k, "bn": ns.bn or plan["bn"], "splits": ns.splits or plan["splits"]})
+
+
+def bench_decode_attn(ns, timer: Timer) -> dict:
+    from ..ops import attention as A
+
+    B, hq, hkv, d, page = ns.batch, ns.q_heads, ns.kv_heads, ns.head_dim, 16
+    rnd = random.Random(0)
+    lens = [rnd.randint(ns.min_len, ns.max_len) for _ in range(B)]
+    maxb = (max(lens) + page - 1) // page
+    total = sum((l + page - 1) // page for l in lens) + 8
+    perm = torch.randperm(total, device="cuda").int()
+    table = torch.zeros(B, maxb, dtype=torch.int32, device="cuda")
+    c = 0
+    for b, l in enumerate(lens):
+        n = (l + page - 1) // page
+        table[b, :n] = perm[c:c + n]
+        c += n
+    kc = torch.randn(total, page, hkv, d, device="cuda").bfloat16()
+    vc = torch.randn(total, page, hkv, d, device="cuda").bfloat16()
+    q = torch.randn(B, hq, d, device="cuda").bfloat16()
+    sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    out = torch.empty_like(q)
+    splits, chunk = A.decode_plan(B, hkv, ns.max_len)
+    ws = torch.empty(B * hq * max(splits, 1) * (d + 2), dtype=torch.float32, device="cuda")
+    us = timer(lambda: A.paged_decode(q, kc, vc, table, sl, out=out, num_splits=splits, ws=ws, chunk_tokens=chunk))
+    kv_bytes = sum(lens) * hkv * d * 2 * 2
+    return report("paged_decode_attention", us, kv_bytes, 4.0 * sum(lens) * hq * d,
+                  {"batch": B, "tokens": sum(lens), "splits": splits, "chunk_tokens": chunk})
+
+
+def bench_norm(ns, timer: Timer) -> dict:
+    from ..ops import norm
+
+    h = torch.randn(ns.rows, ns.hidden, device="cuda").bfloat16()
+    part = torch.randn(ns.rows, ns.hidden, device="cuda").bfloat16()
+    w = torch.ones(ns.hidden, device="cuda").bfloat16()
+    out = torch.empty_like(h)
+    us = timer(lambda: norm.add_rmsnorm([part], w, 1e-6, resid=h, out=out))
+    return report("add_rmsnorm", us, 4 * h.numel() * 2, 0.0, {"rows": ns.rows, "hidden": ns.hidden})
+
+
+def bench_moe(ns, timer: Timer) -> dict:
+    from ..models.config import PRESETS
+    from ..models.weights import random_ffn_layer
+    from ..ops import gemm, moe
+
+    cfg = PRESETS["Qwen/Qwen3-30B-A3B"]
+    w = random_ffn_layer(cfg, 0, 1, "cuda", torch.bfloat16)
+    x = (torch.randn(ns.rows, cfg.hidden_size, device="cuda") * 0.5).bfloat16()
+    out = torch.empty_like(x)
+    ws = moe.workspace(x.device, ns.rows, cfg, cfg.moe_intermediate_size, cfg.num_experts)
+    us = timer(lambda: moe.moe_forward(x, w, cfg, out=out, ws=ws))
+    gemm.check_status(x.device)
+    routes = ns.rows * cfg.num_experts_per_tok
+    touched = min(cfg.num_experts, routes)  # upper bound on experts whose weights are read
+    byts = touched * 3 * cfg.hidden_size * cfg.moe_intermediate_size * 2
+    return report("moe_forward(Qwen3-30B-A3B layer)", us, byts, 6.0 * routes * cfg.hidden_size * cfg.moe_intermediate_size,
+                  {"rows": ns.rows, "routes": routes})
+
+
+def main(argv: list[str] | None = None) -> int:
+    ap = argparse.ArgumentParser(prog="python -m crosspool_b200.bench.kernels")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    sub = ap.add_subparsers(dest="case", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--rows", type=int, default=64)
+    g.add_argument("--n", type=int, default=3072)
+    g.add_argument("--k", type=int, default=1024)
+    g.add_argument("--dual", type=int, default=0)
+    g.add_argument("--splits", type=int, default=0)
+    g.add_argument("--bn", type=int, default=0)
+    a = sub.add_parser("decode-attn")
+    a.add_argument("--batch", type=int, default=256)
+    a.add_argument("--q-heads", type=int, default=16)
+    a.add_argument("--kv-heads", type=int, default=8)
+    a.add_argument("--head-dim", type=int, default=128)
+    a.add_argument("--min-len", type=int, default=128)
+    a.add_argument("--max-len", type=int, default=2048)
+    n = sub.add_parser("norm")
+    n.add_argument("--rows", type=int, default=256)
+    n.add_argument("--hidden", type=int, default=1024)
+    m = sub.add_parser("moe")
+    m.add_argument("--rows", type=int, default=64)
+    ns = ap.parse_args(argv)
+    timer = Timer(ns.iters, ns.warmup, not ns.no_flush)
+    {"gemm": bench_gemm, "decode-attn": bench_decode_attn, "norm": bench_norm, "moe": bench_moe}[ns.case](ns, timer)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

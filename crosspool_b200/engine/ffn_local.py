@@ -25,13 +25,20 @@ class LocalFfnPort(FfnPort):
         inter = max(w.gate_up.shape[-2] // 2 for w in self.weights)
         self.act = torch.zeros(engine.cap, inter, dtype=torch.bfloat16, device=engine.device)
         self.y = torch.zeros(engine.cap, self.cfg.hidden_size, dtype=torch.bfloat16, device=engine.device)
+        self.moe_ws = None
+        moe_layers = [w for w in self.weights if w.is_moe]
+        if moe_layers:
+            from ..ops import moe
+
+            w = moe_layers[0]  # one scratch set sized for the engine's row capacity serves every layer and bucket
+            self.moe_ws = moe.workspace(engine.device, engine.cap, self.cfg, w.gate_up.shape[1] // 2, w.gate_up.shape[0])
 
     def run(self, layer: int, x: torch.Tensor, rows: int, mode: int) -> list[torch.Tensor]:
         w = self.weights[layer]
         if w.is_moe:
             from ..ops import moe
 
-            return [moe.moe_forward(x, w, self.cfg, out=self.y[:rows])]
+            return [moe.moe_forward(x, w, self.cfg, out=self.y[:rows], ws=self.moe_ws)]
         inter = w.gate_up.shape[0] // 2
         act = self.act[:rows, :inter]
         gemm.gateup_swiglu(x, w.gate_up, out=act, bias=w.gate_up_bias)

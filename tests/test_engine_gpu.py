@@ -82,3 +82,22 @@ def test_pages_are_returned_and_batches_pad_to_buckets():
     assert [len(o) for o in out] == [5, 5, 5]
     assert eng.kv.allocator.free_pages == free0
     assert eng.stats["decode_steps"] >= 4 and eng.stats["prefill_steps"] >= 1
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_loopback_engine_serves_a_moe_model(graph):
+    cfg, eng, ref = _build("tiny-qwen3-moe", max_batch=8, prefill_chunk=128, max_seq_len=256, use_cuda_graph=graph)
+    eng.warmup()
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (7, 40)]
+    seqs = [eng.add_request(p, 5) for p in prompts]
+    first_logits = {}
+    while eng.has_work:
+        for i, (s, tok) in enumerate(eng.step()):
+            first_logits.setdefault(s.seq_id, eng.logits[i].clone())
+    from crosspool_b200.ops import gemm
+    gemm.check_status(eng.device)
+    for s, p in zip(seqs, prompts):
+        toks, ref_logits = ref.generate(torch.tensor(p, device="cuda"), 5)
+        assert len(s.generated) == 5
+        assert _kl(ref_logits[:1], first_logits[s.seq_id][None]).item() <= 0.05
