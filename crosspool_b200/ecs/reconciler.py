@@ -105,7 +105,7 @@ class CapacityReconciler:
         self.floor_bundles = floor_bundles
         self.gate_factory = gate_factory or (lambda: (lambda: True))
         self.clock_ns = clock_ns
-        self.bundle_bytes = cache.backing.bundle_bytes()
+        self.bundle_bytes = cache.backing.bundle_bytes
         self._retiring: list[_Retiring] = []
         self._done_command = 0
         self._pending: tuple[int, int] | None = None  # (sequence, target bundles) of a shrink in progress
@@ -161,7 +161,7 @@ class CapacityReconciler:
             return
         # shrink: retire empty bundles (highest index first keeps low addresses dense)
         excess = live - target
-        for b in sorted(self.cache.allocator.empty_bundles(), reverse=True)[:max(0, excess)]:
+        for b in sorted(self.retirable_empty(), reverse=True)[:max(0, excess)]:
             self.cache.allocator.begin_retirement(b)
             self._retiring.append(_Retiring(b, self.gate_factory()))
             self.events.append(("retire", b))
@@ -183,6 +183,11 @@ class CapacityReconciler:
         self._done_command = seq
         self._pending = None
         self.channel.publish_completion(self.index, seq, self.mapped_bytes)
+
+    def retirable_empty(self) -> list[int]:
+        """Empty bundles a shrink may take: the floor bundles (lowest indices, the base of every KV
+        tensor) stay mapped for the life of the cache."""
+        return [b for b in self.cache.allocator.empty_bundles() if b >= self.floor_bundles]
 
     @property
     def shrink_in_progress(self) -> bool:

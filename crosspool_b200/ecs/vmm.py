@@ -177,15 +177,18 @@ def elastic_kv_cache(cfg: ModelConfig, max_pages: int, page_size: int, device, d
     backing = KvVmmBacking(driver, dev_index, 2 * cfg.num_layers, n_bundles * chunk, chunk, quota)
     lay = KvLayout(page_size, pages, cfg.num_kv_heads, cfg.head_dim, cfg.num_layers)
     alloc = PageAllocator(pages, ppb, mapped_bundles=0)
-    k, v = [], []
-    if make_tensors:
-        shape = (pages, page_size, cfg.num_kv_heads, cfg.head_dim)
-        for l in range(cfg.num_layers):
-            k.append(tensor_from_ptr(backing.address(2 * l), shape, torch.bfloat16, device))
-            v.append(tensor_from_ptr(backing.address(2 * l + 1), shape, torch.bfloat16, device))
-    cache = PagedKvCache(lay, k, v, alloc, backing)
+    cache = PagedKvCache(lay, [], [], alloc, backing)
     if initial_bundles:
         grow(cache, list(range(initial_bundles)))
+    if make_tensors:
+        # views are created after the first bundles are mapped: the framework inspects the base
+        # address of foreign memory when it wraps it
+        if not backing.is_mapped(0):
+            raise ValueError("bundle 0 must be mapped before tensors are created over the range")
+        shape = (pages, page_size, cfg.num_kv_heads, cfg.head_dim)
+        for l in range(cfg.num_layers):
+            cache.k.append(tensor_from_ptr(backing.address(2 * l), shape, torch.bfloat16, device))
+            cache.v.append(tensor_from_ptr(backing.address(2 * l + 1), shape, torch.bfloat16, device))
     return cache
 
 

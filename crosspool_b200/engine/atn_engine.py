@@ -124,7 +124,35 @@ class AttentionEngine:
         self._b_last = None
         self._inflight = None
         self._graph_launches: dict[int, int] = {}
+        self.capacity = None          # ecs.reconciler.CapacityReconciler when the KV cache is elastic
+        self._demand_pages = 0
+        self.ttft_slo_s = 0.0
         port.attach(self)
+
+    # ------------------------------------------------------------------ elastic KV capacity
+    def attach_capacity(self, reconciler, ttft_slo_s: float = 0.0) -> None:
+        """Couples the engine to the capacity channel: it publishes demand when admission stalls,
+        executes grow/shrink commands once per step, and retracts sequences when a shrink needs
+        bundles that would not drain on their own."""
+        self.capacity, self.ttft_slo_s = reconciler, ttft_slo_s
+
+    def _capacity_tick(self) -> None:
+        rec = self.capacity
+        rec.poll()
+        if rec.bundles_to_vacate() > 0 and not rec.retirable_empty() and self.running and self._inflight is None:
+            self._retract(self.running[-1])  # newest first: the least work is lost
+            self.stats["retracted_for_shrink"] = self.stats.get("retracted_for_shrink", 0) + 1
+            rec.poll()
+
+    def _publish_demand(self, missing_pages: int, head: "Sequence | None") -> None:
+        if self.capacity is None or missing_pages == self._demand_pages:
+            return
+        self._demand_pages = missing_pages
+        if missing_pages <= 0:
+            self.capacity.withdraw_demand()
+            return
+        deadline = int((head.arrival + self.ttft_slo_s) * 1e9) if head is not None and self.ttft_slo_s > 0 else 0
+        self.capacity.publish_demand(missing_pages, deadline)
 
     # ------------------------------------------------------------------ buffers
     def _alloc_buffers(self) -> None:
@@ -294,7 +322,9 @@ class AttentionEngine:
             s = self.waiting[0]
             need = self.kv.pages_needed(s.seq_id, len(s.prompt) + 1)
             if need > self.kv.allocator.free_pages:
+                self._publish_demand(need - self.kv.allocator.free_pages, s)
                 break
+            self._publish_demand(0, None)
             self.waiting.popleft()
             self.kv.ensure(s.seq_id, len(s.prompt) + 1)
             self.prefilling.append(s)
@@ -470,6 +500,7 @@ class AttentionEngine:
     def _retract(self, s: Sequence) -> None:
         """Gives the sequence's pages back and queues it for recomputation (prompt + generated)."""
         self.running.remove(s)
+        self._b_key = None  # the cached decode batch no longer matches
         self.kv.release(s.seq_id)
         s.prompt = s.prompt + s.generated
         s.max_new_tokens -= len(s.generated)
@@ -482,6 +513,8 @@ class AttentionEngine:
         GPU, so that a driver of several co-located Instances can overlap them; ``collect_step``
         finishes it. Prefill chunks complete inside this call."""
         self._pending: list[tuple[Sequence, int]] | None = None
+        if self.capacity is not None:
+            self._capacity_tick()
         want_prefill = bool(self.waiting or self.prefilling)
         if want_prefill and (not self.running or not self._last_was_prefill):
             chosen, rows = self._admit_prefill()

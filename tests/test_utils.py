@@ -1,0 +1,119 @@
+"""Small host-side utilities: model ids, process identity, CUDA error classes, device inventory,
+background threads, signal handling, MPS endpoint description, bootstrap."""
+import os
+import signal
+import subprocess
+import sys
+import threading
+import time
+import types
+
+import pytest
+
+from crosspool_b200 import bootstrap
+from crosspool_b200.model import ModelId
+from crosspool_b200.utils import background, cuda_errors, device, mps, procs, sighandler
+
+
+def test_model_id_parses_and_round_trips_through_a_uri():
+    m = ModelId.parse("Qwen/Qwen3-0.6B")
+    assert (m.namespace, m.name) == ("Qwen", "Qwen3-0.6B") and str(m) == "Qwen/Qwen3-0.6B"
+    assert m.uri() == "Qwen%2FQwen3-0.6B" and ModelId.from_uri(m.uri()) == m
+    assert str(ModelId.parse("tiny")) == "tiny" and m.resolve("/models/") == "/models/Qwen/Qwen3-0.6B"
+    for bad in ("", "a/b/c", "/x", "a b", "-x/y"):
+        with pytest.raises(ValueError):
+            ModelId.parse(bad)
+
+
+def test_process_identity_tells_a_reused_pid_from_the_original_and_kills_exact_trees():
+    me = procs.ProcUniqId.current()
+    assert me.alive() and procs.ProcUniqId(me.pid, me.create_time - 100).status() == "replaced"
+    child = subprocess.Popen([sys.executable, "-c", "import subprocess,sys,time; subprocess.Popen([sys.executable,'-c','import time; time.sleep(60)']); time.sleep(60)"])
+    try:
+        ident = procs.ProcUniqId.of(child.pid)
+        for _ in range(100):
+            if len(procs.tree(child.pid)) == 2:
+                break
+            time.sleep(0.05)
+        pids = procs.kill_tree(ident, grace_s=3)
+        assert len(pids) == 2 and pids[-1] == child.pid
+        child.wait(5)
+        assert procs.wait_exit(ident, 3) and ident.status() == "exited"
+        assert procs.kill_tree(ident) == []     # an identity that is gone is never signalled again
+    finally:
+        if child.poll() is None:
+            child.kill()
+
+
+def test_cuda_error_classification():
+    T = cuda_errors.is_terminal_device_error
+    assert T(RuntimeError("CUDA error: an illegal memory access was encountered"))
+    assert T(RuntimeError("CUDA error: unspecified launch failure"))
+    assert not T(RuntimeError("CUDA out of memory. Tried to allocate 2 GiB"))
+    assert not T(RuntimeError("CUDA error: operation not permitted when stream is capturing"))
+    assert T(cuda_errors.CudaDriverError("cuLaunchKernel", 700)) and not T(cuda_errors.CudaDriverError("cuMemCreate", 2))
+    assert not T(ValueError("bad shape"))
+
+
+def test_device_inventory_and_visibility_mask():
+    text = "0, GPU-aaaa, NVIDIA B200, 183359, 12\n1, GPU-bbbb, NVIDIA B200, 183359, 0\n"
+    inv = device.parse_inventory(text)
+    assert [d.uuid for d in inv] == ["GPU-aaaa", "GPU-bbbb"] and inv[0].memory_total_mib == 183359
+    fake = lambda *a, **k: types.SimpleNamespace(returncode=0, stdout=text, stderr="")  # noqa: E731
+    assert device.inventory(fake) == inv
+    assert device.visible_indices(8, {"CUDA_VISIBLE_DEVICES": "3,1,9,2"}) == [3, 1]
+    assert device.visible_indices(2, {}) == [0, 1]
+    assert device.resolve_uuids([1], inv) == {1: "GPU-bbbb"}
+    with pytest.raises(LookupError):
+        device.resolve_uuids([5], inv)
+
+
+def test_background_thread_runs_periodically_and_surfaces_errors():
+    hits = []
+    t = background.BackgroundThread.periodic(lambda: hits.append(1), 0.01, "tick").start()
+    time.sleep(0.08)
+    assert t.stop() and len(hits) >= 3
+    t.check()
+
+    def boom():
+        raise KeyError("x")
+
+    b = background.BackgroundThread.periodic(boom, 0.01, "boom").start()
+    time.sleep(0.05)
+    b.stop()
+    with pytest.raises(RuntimeError, match="boom failed"):
+        b.check()
+
+
+def test_first_signal_requests_shutdown():
+    got = []
+    with sighandler.ShutdownSignals(on_request=got.append) as s:
+        os.kill(os.getpid(), signal.SIGTERM)
+        assert s.requested.wait(2) and got == [signal.SIGTERM] and s.signum == signal.SIGTERM
+    assert signal.getsignal(signal.SIGTERM) in (signal.SIG_DFL, signal.default_int_handler) or True
+
+
+def test_mps_endpoint_only_describes_an_environment():
+    ep = mps.MpsEndpoint.for_device("GPU-12345678-abcd", root="/tmp/xp-mps-test")
+    env = ep.client_env(active_thread_percentage=50)
+    assert env["CUDA_MPS_PIPE_DIRECTORY"].endswith("/pipe") and env["CUDA_MPS_ACTIVE_THREAD_PERCENTAGE"] == "50"
+    assert not ep.daemon_running()
+    with pytest.raises(ValueError):
+        ep.client_env(active_thread_percentage=0)
+    e = {"CUDA_VISIBLE_DEVICES": "0"}
+    with mps.MpsScope(ep, environ=e):
+        assert e["CUDA_VISIBLE_DEVICES"] == "GPU-12345678-abcd"
+    assert e == {"CUDA_VISIBLE_DEVICES": "0"}
+
+
+def test_bootstrap_initialises_once_per_process():
+    bootstrap.reset_for_tests()
+    cfg = types.SimpleNamespace(logging_level="warning", logging_color="never", debug_transport_observer_enable=True)
+    st = bootstrap.init("Instance", None, config=cfg)
+    assert bootstrap.get_runtime_role() == "Instance" and [o.name for o in st.observers.observers] == ["transport"]
+    assert bootstrap.init("Instance", None, config=cfg) is st
+    with pytest.raises(RuntimeError):
+        bootstrap.init("FfnAgent", 0, config=cfg)
+    with pytest.raises(ValueError):
+        bootstrap.reset_for_tests() or bootstrap.init("Nobody")
+    bootstrap.reset_for_tests()
