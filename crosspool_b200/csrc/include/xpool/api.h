@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 14
+#define XP_ABI_VERSION 15
 
 #ifdef __cplusplus
 extern "C" {
@@ -196,6 +196,10 @@ typedef struct XpDecodeAttnArgs {
   int batch, q_heads, kv_heads, head_dim, page_size, max_blocks, num_splits;
   float scale;
   int chunk_tokens;           /* > 0: slices of this many tokens (num_splits = ceil(max_len / chunk)) */
+  int num_pages;              /* pages in the cache (bound of the tensor maps); 0: SIMT kernel only */
+  uint32_t* status;           /* optional: set non-zero when a bounded wait ran out */
+  int force_simt;             /* testing: skip the tensor-core kernel */
+  int reserved;
 } XpDecodeAttnArgs;
 
 typedef struct XpPrefillAttnArgs {

@@ -54,6 +54,22 @@ inline int encode_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// Paged KV cache [tokens, kv_heads, head_dim] (bf16) as a 3-D map whose box is 16 tokens of one
+// head by 64 dims (128 bytes, 128-byte swizzle): one box is what a warp's ldmatrix/mma tile needs.
+inline int encode_kv_3d(CUtensorMap* out, const void* base, uint64_t tokens, uint32_t kv_heads, uint32_t head_dim) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || head_dim % 64 != 0) return -2;
+  cuuint64_t dims[3] = {head_dim, kv_heads, tokens};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 2, static_cast<cuuint64_t>(head_dim) * 2 * kv_heads};
+  cuuint32_t box[3] = {64, 1, 16};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 // Small cache: encoding costs a few microseconds and serving reuses the same
 // (pointer, shape) pairs on every step.
 class Cache {
@@ -70,6 +86,23 @@ class Cache {
     }
     CUtensorMap m;
     int rc = encode_2d(&m, base, rows, cols, pitch_bytes, box_rows, 128 / elem_bytes, elem_bytes);
+    if (rc != 0) return rc;
+    if (map_.size() > 8192) map_.clear();
+    map_.emplace(k, m);
+    *out = m;
+    return 0;
+  }
+
+  int get_kv(CUtensorMap* out, const void* base, uint64_t tokens, uint32_t kv_heads, uint32_t head_dim) {
+    Key k{base, tokens, kv_heads, head_dim, 0xffffffffu, 3};
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = map_.find(k);
+    if (it != map_.end()) {
+      *out = it->second;
+      return 0;
+    }
+    CUtensorMap m;
+    int rc = encode_kv_3d(&m, base, tokens, kv_heads, head_dim);
     if (rc != 0) return rc;
     if (map_.size() > 8192) map_.clear();
     map_.emplace(k, m);

@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 14
+EXPECTED_ABI = 15
 HERE = Path(__file__).resolve().parent
 
 
@@ -198,6 +198,10 @@ class DecodeAttnArgs(C.Structure):
         ("num_splits", C.c_int),
         ("scale", C.c_float),
         ("chunk_tokens", C.c_int),
+        ("num_pages", C.c_int),
+        ("status", C.c_void_p),
+        ("force_simt", C.c_int),
+        ("reserved", C.c_int),
     ]
 
 

@@ -52,8 +52,11 @@ def decode_plan(batch: int, kv_heads: int, max_len: int) -> tuple[int, int]:
 def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                  seq_lens: torch.Tensor, *, out: torch.Tensor | None = None, num_splits: int = 0,
                  ws: torch.Tensor | None = None, scale: float | None = None, max_len: int | None = None,
-                 chunk_tokens: int = 0) -> torch.Tensor:
-    """q ``[batch, q_heads, d]`` against caches ``[pages, page, kv_heads, d]``."""
+                 chunk_tokens: int = 0, force_simt: bool = False) -> torch.Tensor:
+    """q ``[batch, q_heads, d]`` against caches ``[pages, page, kv_heads, d]``.
+
+    Runs the tensor-core kernel (TMA-fed ``mma`` tiles) whenever pages hold a multiple of 16 tokens
+    and at most 16 query heads share a KV head; ``force_simt`` selects the plain kernel."""
     batch, q_heads, d = q.shape
     page_size, kv_heads = k_cache.shape[1], k_cache.shape[2]
     if out is None:
@@ -71,6 +74,11 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     a.page_size, a.max_blocks, a.num_splits = page_size, block_table.stride(0), num_splits
     a.scale = scale if scale is not None else d ** -0.5
     a.chunk_tokens = chunk_tokens
+    a.num_pages = k_cache.shape[0] if k_cache.is_contiguous() and v_cache.is_contiguous() else 0
+    a.force_simt = int(force_simt)
+    from .gemm import scratch
+
+    a.status = scratch(q.device).status.data_ptr()
     native.check(native.kernels().xp_decode_attn(C.byref(a), _stream(q.device)), "xp_decode_attn",
                  2 if num_splits > 1 else 1)
     return out

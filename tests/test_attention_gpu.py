@@ -75,7 +75,8 @@ def _gather(cache, table, b, n, page):
 
 @pytest.mark.parametrize("d,hq,hkv", [(128, 16, 8), (128, 32, 8), (128, 64, 8), (64, 4, 2), (128, 8, 8)])
 @pytest.mark.parametrize("splits", [0, 1, 3])
-def test_paged_decode(d, hq, hkv, splits):
+@pytest.mark.parametrize("simt", [False, True])
+def test_paged_decode(d, hq, hkv, splits, simt):
     from crosspool_b200.ops import attention as A
 
     torch.manual_seed(1)
@@ -84,7 +85,7 @@ def test_paged_decode(d, hq, hkv, splits):
     kc, vc, table = _paged(len(lens), lens, hkv, d, page)
     q = torch.randn(len(lens), hq, d, device="cuda").bfloat16()
     sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
-    out = A.paged_decode(q, kc, vc, table, sl, num_splits=splits)
+    out = A.paged_decode(q, kc, vc, table, sl, num_splits=splits, force_simt=simt)
     g = hq // hkv
     for b, n in enumerate(lens):
         k, v = _gather(kc, table, b, n, page), _gather(vc, table, b, n, page)
@@ -139,6 +140,35 @@ def test_embedding_and_argmax():
     assert int(got[3]) == 77
     lb = logits.bfloat16()
     assert torch.equal(A.argmax(lb).long(), lb.float().argmax(-1))
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(128, 32, 2), (64, 16, 1)])
+def test_tensor_core_decode_handles_sixteen_heads_per_group_and_ignores_stale_cache_slots(d, hq, hkv):
+    from crosspool_b200.ops import attention as A
+    from crosspool_b200.ops import gemm
+
+    torch.manual_seed(7)
+    lens = [5, 16, 37, 300, 513]
+    page = 32
+    kc, vc, table = _paged(len(lens), lens, hkv, d, page)
+    # slots past each sequence's end hold NaN (as stale or unscrubbed memory might)
+    for b, n in enumerate(lens):
+        last = int(table[b, (n - 1) // page])
+        kc[last, n % page or page:] = float("nan")
+        vc[last, n % page or page:] = float("nan")
+    q = torch.randn(len(lens), hq, d, device="cuda").bfloat16()
+    sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    out = A.paged_decode(q, kc, vc, table, sl, num_splits=2, chunk_tokens=256)
+    torch.cuda.synchronize()
+    gemm.check_status(q.device)
+    assert torch.isfinite(out.float()).all()
+    g = hq // hkv
+    for b, n in enumerate(lens):
+        k, v = _gather(kc, table, b, n, page), _gather(vc, table, b, n, page)
+        k, v = k.repeat_interleave(g, 1), v.repeat_interleave(g, 1)
+        s = torch.einsum("hd,nhd->hn", q[b].float(), k) * d ** -0.5
+        ref = torch.einsum("hn,nhd->hd", s.softmax(-1), v)
+        torch.testing.assert_close(out[b].float(), ref, atol=2e-2, rtol=2e-2)
 
 
 def test_paged_decode_fixed_chunks_balance_mixed_lengths():
