@@ -102,6 +102,8 @@ def bench_decode_attn(ns, timer: Timer) -> dict:
     sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
     out = torch.empty_like(q)
     splits, chunk = A.decode_plan(B, hkv, ns.max_len)
+    if ns.chunk > 0:
+        splits, chunk = (ns.max_len + ns.chunk - 1) // ns.chunk, ns.chunk
     ws = torch.empty(B * hq * max(splits, 1) * (d + 2), dtype=torch.float32, device="cuda")
     us = timer(lambda: A.paged_decode(q, kc, vc, table, sl, out=out, num_splits=splits, ws=ws, chunk_tokens=chunk))
     kv_bytes = sum(lens) * hkv * d * 2 * 2
@@ -139,6 +141,52 @@ def bench_moe(ns, timer: Timer) -> dict:
                   {"rows": ns.rows, "routes": routes})
 
 
+def bench_decode_step(ns, timer: Timer) -> dict:
+    """One Instance's decode step on the loopback engine, launched eagerly (no CUDA graph) over
+    sequences whose KV is taken as already cached -- the workload for a per-launch time list."""
+    from ..engine.atn_engine import AttentionEngine, EngineConfig, Sequence
+    from ..engine.ffn_local import LocalFfnPort
+    from ..models import config as mc
+    from ..models.weights import random_attention_weights, random_ffn_weights
+    from ..ops import gemm
+
+    cfg = mc.preset(ns.model)
+    aw = random_attention_weights(cfg, 0, "cuda", torch.bfloat16)
+    fw = random_ffn_weights(cfg, 0, "cuda", torch.bfloat16)
+    rnd = random.Random(0)
+    lens = [rnd.randint(ns.min_len, ns.max_len) for _ in range(ns.batch)]
+    steps = timer.iters + timer.warmup
+    pages = sum((l + steps + 32) // 16 + 1 for l in lens) + 64
+    eng = AttentionEngine(cfg, aw, LocalFfnPort(cfg, fw), EngineConfig(
+        max_batch=ns.batch, prefill_chunk=256, max_seq_len=ns.max_len + steps + 64, num_pages=pages,
+        decode_buckets=[ns.batch], use_cuda_graph=bool(ns.graph)))
+    eng.warmup()
+    for i, l in enumerate(lens):
+        s = Sequence(i, [1] * l, steps + 8)
+        s.computed, s.generated = l, [2]
+        eng.kv.ensure(s.seq_id, l + 1)
+        eng.running.append(s)
+    torch.cuda.synchronize()
+    for _ in range(timer.warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(timer.iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(eng.stream)
+        eng.step()
+        b.record(eng.stream)
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b) * 1e3)
+    gemm.check_status(torch.device("cuda"))
+    us = statistics.median(ts)
+    kv_bytes = sum(lens) * cfg.kv_bytes_per_token()
+    w_bytes = cfg.attention_param_bytes() - 2 * cfg.vocab_size * cfg.hidden_size * (0 if cfg.tie_word_embeddings else 1) + \
+        sum(cfg.ffn_param_bytes_per_layer(l) for l in range(cfg.num_layers))
+    return report(f"decode_step({ns.model})", us, kv_bytes + w_bytes, 0.0,
+                  {"batch": ns.batch, "tokens_cached": sum(lens), "graph": bool(ns.graph), "tok_per_s": round(ns.batch / us * 1e6)})
+
+
 def main(argv: list[str] | None = None) -> int:
     ap = argparse.ArgumentParser(prog="python -m crosspool_b200.bench.kernels")
     ap.add_argument("--iters", type=int, default=20)
@@ -159,14 +207,22 @@ def main(argv: list[str] | None = None) -> int:
     a.add_argument("--head-dim", type=int, default=128)
     a.add_argument("--min-len", type=int, default=128)
     a.add_argument("--max-len", type=int, default=2048)
+    a.add_argument("--chunk", type=int, default=-1, help="KV slice length (-1: the planner's choice, 0: even split)")
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=256)
     n.add_argument("--hidden", type=int, default=1024)
     m = sub.add_parser("moe")
     m.add_argument("--rows", type=int, default=64)
+    d = sub.add_parser("decode-step")
+    d.add_argument("--model", default="Qwen/Qwen3-0.6B")
+    d.add_argument("--batch", type=int, default=256)
+    d.add_argument("--min-len", type=int, default=128)
+    d.add_argument("--max-len", type=int, default=2048)
+    d.add_argument("--graph", type=int, default=0)
     ns = ap.parse_args(argv)
     timer = Timer(ns.iters, ns.warmup, not ns.no_flush)
-    {"gemm": bench_gemm, "decode-attn": bench_decode_attn, "norm": bench_norm, "moe": bench_moe}[ns.case](ns, timer)
+    {"gemm": bench_gemm, "decode-attn": bench_decode_attn, "norm": bench_norm, "moe": bench_moe,
+     "decode-step": bench_decode_step}[ns.case](ns, timer)
     return 0
 
 
