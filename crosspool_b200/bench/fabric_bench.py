@@ -1,9 +1,11 @@
 """Multi-GPU layout of the decode benchmark (``bench.py --gpus N`` under ``torch.distributed.run``).
 
-Ranks ``[0, N/2)`` are attention ranks, ranks ``[N/2, N)`` form the shared FFN tier. Every attention
-rank hosts ``--instances-per-atn`` co-located Instances; Instance ``j`` keeps its FFN on FFN rank(s)
-``(j .. j + tp - 1) mod N/2`` so that every attention GPU talks to several FFN GPUs and every FFN GPU
-serves Instances of several attention GPUs. Times are device times, maximum over ranks.
+The last ``max(1, N // 4)`` ranks (or ``--ffn-ranks``) form the shared FFN tier, the others are attention
+ranks: decode is bound by KV reads on the attention side, and one FFN GPU keeps up with the FFN
+invocations of about six co-located Instances of this size, so the pool is kept small (that is the
+point of pooling FFNs). Every attention rank hosts ``--instances-per-atn`` co-located Instances;
+Instance ``j`` keeps its FFN on FFN rank(s) ``(j .. j + tp - 1) mod n_ffn``, so every FFN GPU serves
+Instances of several attention GPUs. Times are device times, maximum over ranks.
 """
 
 from __future__ import annotations
@@ -34,8 +36,9 @@ def main(args) -> int:
     cfg = mc.load(args.model)
     if args.layers:
         cfg = cfg.with_layers(args.layers)
-    n_atn = world // 2
-    n_ffn = world - n_atn
+    n_ffn = getattr(args, "ffn_ranks", 0) or max(1, world // 4)
+    n_ffn = min(n_ffn, world - 1)
+    n_atn = world - n_ffn
     tp = max(1, min(args.ffn_tp, n_ffn))
     placements, workloads, ecfgs = [], {}, {}
     j = 0

@@ -34,7 +34,9 @@ def _parser() -> argparse.ArgumentParser:
     e.add_argument("argv", nargs=argparse.REMAINDER)
     c = sub.add_parser("config")
     c.add_subparsers(dest="config_command", required=True).add_parser("dump")
-    sub.add_parser("memory-profile")
+    mp = sub.add_parser("memory-profile")
+    mp.add_argument("--calibrate", action="store_true", help="measure a corpus of synthetic deployments on this GPU and fit the model")
+    mp.add_argument("--out", default="xpool-memory-profile.json")
     b = sub.add_parser("bench")
     b.add_argument("rest", nargs=argparse.REMAINDER)
     return p
@@ -108,6 +110,14 @@ def cmd_exec(ns) -> int:
 
 
 def cmd_memory_profile(ns) -> int:
+    if getattr(ns, "calibrate", False):
+        from ..runtime import memory_calibration as mcal
+
+        prof = mcal.calibrate()
+        prof.save(ns.out)
+        print(json.dumps({"saved": ns.out, "samples": prof.samples, "max_abs_error_bytes": prof.max_abs_error_bytes,
+                          "coefficients": vars(prof.coefficients)}, indent=2))
+        return 0
     from ..models import config as mc
     from ..service.daemon.placement import DeviceSupply, ModelDemand, place_ffn_models
 

@@ -76,3 +76,15 @@ def test_fp8_block_round_trip_and_quanta():
     assert torch.equal(q.dequantize(q.slice(st, 128, 256, 0, 256), torch.float32), back[128:, :256])
     with pytest.raises(ValueError):
         q.slice(st, 64, 256, 0, 128)
+
+
+def test_calibration_runner_fits_from_an_injected_measurement():
+    from crosspool_b200.runtime import memory_calibration as mcal
+
+    true = M.DeviceMemoryEstimator(M.FfnMemoryCalibrationCoefficients(650e6, 9e6, 3e6, 0.0))
+    env = M.MemoryCalibrationEnvironment("fake", "0", "12.9", "torch", "x")
+    prof = mcal.calibrate(measure=lambda e: true.estimate(mcal.features_of(e)).total, environment=env)
+    assert prof.samples == len(mcal.DEFAULT_CORPUS) and prof.max_abs_error_bytes < 4 << 20
+    assert abs(prof.coefficients.per_lane_bytes - 9e6) < 1e6
+    f = mcal.features_of(mcal.Experiment("Qwen/Qwen3-0.6B", 28, 1, 2))
+    assert f.weight_bytes == 28 * 3 * 1024 * 3072 * 2 and f.slot_bytes > 512 * 1024 * 2
