@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 15
+#define XP_ABI_VERSION 16
 
 #ifdef __cplusplus
 extern "C" {
@@ -44,6 +44,7 @@ typedef struct XpGemmArgs {
   const void* tile_table;
   const int* n_tiles;
   int w_rows_per_group;
+  int smem_limit;      /* > 0: cap on dynamic shared memory, so the CTA can share an SM with another stream's kernel */
 } XpGemmArgs;
 
 typedef struct XpGemmPlan {

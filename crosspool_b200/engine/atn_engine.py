@@ -179,9 +179,9 @@ class AttentionEngine:
         self._pre_words = 3 * P + 4 * S + S * self.max_blocks
         self.pre_meta = torch.zeros(self._pre_words, dtype=torch.int32, device=dev)
         self.pre_meta_host = torch.zeros(self._pre_words, dtype=torch.int32).pin_memory()
-        splits = max(A.decode_plan(b, cfg.num_kv_heads, e.max_seq_len)[0] for b in (1, B))
-        self.attn_ws = torch.zeros(B * cfg.num_q_heads * max(splits, 1) * (cfg.head_dim + 2), dtype=torch.float32,
-                                   device=dev)
+        buckets = e.decode_buckets or capacity_buckets(B)
+        ws_rows = max(b * A.decode_plan(b, cfg.num_kv_heads, e.max_seq_len)[0] for b in buckets)
+        self.attn_ws = torch.zeros(ws_rows * cfg.num_q_heads * (cfg.head_dim + 2), dtype=torch.float32, device=dev)
 
     def _dec_views(self, B: int):
         m, cap = self.dec_meta, self.ecfg.max_batch

@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 15
+EXPECTED_ABI = 16
 HERE = Path(__file__).resolve().parent
 
 
@@ -58,6 +58,7 @@ class GemmArgs(C.Structure):
         ("tile_table", C.c_void_p),
         ("n_tiles", C.c_void_p),
         ("w_rows_per_group", C.c_int),
+        ("smem_limit", C.c_int),
     ]
 
 

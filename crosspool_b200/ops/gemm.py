@@ -17,6 +17,10 @@ import torch
 
 from .. import native
 
+# Dynamic shared memory cap of decode-size GEMMs: 126 KB keeps three pipeline stages of the widest decode
+# tile and fits beside one 98 KB decode-attention CTA of another stream on the same SM (227 KB per SM).
+DECODE_SMEM_LIMIT = 126 * 1024
+DECODE_ROWS = 256
 EPI_STORE = 0
 EPI_SWIGLU = 1
 EPI_RESIDUAL = 2
@@ -126,6 +130,8 @@ def _args(x, w, out, *, n_out, rows, epilogue, dual=0, up_offset=0, bias=None, r
     a.gate_limit = gate_limit
     a.up_add = up_add
     a.act_alpha = act_alpha
+    # decode-size calls leave room for a second kernel on the SM (the co-located Instance's attention)
+    a.smem_limit = DECODE_SMEM_LIMIT if rows <= DECODE_ROWS else 0
     return a
 
 

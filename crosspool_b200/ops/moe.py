@@ -44,7 +44,6 @@ class MoeWorkspace:
 
 
 _ws_cache: dict[tuple, MoeWorkspace] = {}
-_router_pad: dict[int, torch.Tensor] = {}
 
 
 def workspace(device, cap_rows: int, cfg: ModelConfig, inter: int, n_local: int) -> MoeWorkspace:
@@ -67,16 +66,18 @@ def workspace(device, cap_rows: int, cfg: ModelConfig, inter: int, n_local: int)
     return ws
 
 
-def padded_router(router: torch.Tensor) -> torch.Tensor:
-    """Router weights with the expert dimension padded to a multiple of 128 rows (one UMMA tile)."""
+def padded_router(w: FfnLayerWeights) -> torch.Tensor:
+    """The layer's router weights with the expert dimension padded to a multiple of 128 rows (one UMMA
+    tile); built once and kept with the layer."""
+    router = w.router
     e = router.shape[0]
     if e % 128 == 0:
         return router
-    t = _router_pad.get(router.data_ptr())
-    if t is None:
+    t = w.extra.get("router_padded")
+    if t is None or t.shape[1] != router.shape[1] or t.device != router.device:
         t = torch.zeros((e + 127) // 128 * 128, router.shape[1], dtype=router.dtype, device=router.device)
         t[:e] = router
-        _router_pad[router.data_ptr()] = t
+        w.extra["router_padded"] = t
     return t
 
 
@@ -129,7 +130,7 @@ def moe_forward(x: torch.Tensor, w: FfnLayerWeights, cfg: ModelConfig, out: torc
     lib, s = native.kernels(), _stream(dev)
     # 1. router (payload precision: bf16 logits, fp32 scores)
     logits = ws.logits[:rows]
-    gemm.linear(x, padded_router(w.router), out=logits)
+    gemm.linear(x, padded_router(w), out=logits)
     router_topk(logits, e_total, k, out_ids=ws.ids[:rows], out_weights=ws.weights[:rows],
                 sigmoid=cfg.router_scoring == "sigmoid", renormalize=cfg.norm_topk_prob, scale=cfg.routed_scaling_factor,
                 correction_bias=w.extra.get("correction_bias"), logit_bias=w.extra.get("router_bias"))

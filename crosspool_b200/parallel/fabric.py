@@ -258,8 +258,7 @@ class FfnRankRuntime:
                     if w.shared_gate_up is not None:
                         raise NotImplementedError("shared experts are served by ops.moe.moe_forward, not by Lanes yet")
                     cfg = p.cfg
-                    router = padded_router(w.router)
-                    self._keep.append(router)
+                    router = padded_router(w)
                     lo, hi = p.expert_range(st.tp_rank)
                     ld.router = router.data_ptr()
                     cb, rb = w.extra.get("correction_bias"), w.extra.get("router_bias")

@@ -180,8 +180,9 @@ def test_paged_decode_fixed_chunks_balance_mixed_lengths():
     kc, vc, table = _paged(len(lens), lens, hkv, d, page)
     q = torch.randn(len(lens), hq, d, device="cuda").bfloat16()
     sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
-    splits, chunk = A.decode_plan(len(lens), hkv, 1520)
-    assert chunk == 256 and splits == 6, (splits, chunk)
+    assert A.decode_plan(len(lens), hkv, 1520) == (2, 1024)      # 336 (sequence, head) pairs: two long slices
+    assert A.decode_plan(256, hkv, 2048) == (1, 0) and A.decode_plan(4, hkv, 2048) == (8, 256)
+    splits, chunk = 6, 256
     out = A.paged_decode(q, kc, vc, table, sl, num_splits=splits, chunk_tokens=chunk)
     ref = A.paged_decode(q, kc, vc, table, sl, num_splits=1)
     torch.testing.assert_close(out.float(), ref.float(), atol=1e-2, rtol=1e-2)

@@ -28,3 +28,11 @@ def test_one_atn_one_ffn_matches_loopback_tokens():
 
 def test_one_atn_two_ffn_tensor_parallel():
     _run(3, ["--tp", "2"])
+
+
+def test_moe_model_through_lanes_on_one_ffn_rank():
+    _run(2, ["--tp", "1", "--model", "tiny-qwen3-moe", "--layers", "2"])
+
+
+def test_moe_expert_parallel_over_two_ffn_ranks():
+    _run(3, ["--tp", "2", "--model", "tiny-qwen3-moe", "--layers", "2"])
