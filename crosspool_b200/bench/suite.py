@@ -1,0 +1,145 @@
+"""Benchmark suite runner: named cases, repetitions, sealed manifests, continuation.
+
+A *case* fixes the workload (streams, duration, SLOs); every *repetition* runs it with its own seed and
+leaves ``<out>/<case>/rep<k>/repetition.json``; once all repetitions of a case are sealed,
+``<out>/<case>/case.json`` aggregates them. A manifest is *sealed* by a SHA-256 over its canonical JSON;
+``--continue`` skips repetitions whose seal verifies, ``--rerun-failure`` also re-runs sealed
+repetitions that recorded errors (reference: ``xbench run --all --continue DIR [--rerun-failure]``,
+docs/designs/benchmark.md:234; src/xpool-dev/xbench/harness/serving/measure.py:37-137).
+
+    python -m crosspool_b200.bench.suite --targets m=http://127.0.0.1:30000 --out runs/ --cases poisson-16 --continue
+"""
+
+from __future__ import annotations
+
+import argparse
+import asyncio
+import hashlib
+import json
+import statistics
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+from typing import Callable
+
+from . import serving as S
+
+
+@dataclass(frozen=True)
+class Case:
+    name: str
+    rate_per_s: tuple[float, ...]          # per target, in the order targets are given (cycled)
+    duration_s: float
+    prompt: S.LengthSpec
+    output: S.LengthSpec
+    repetitions: int = 3
+    warmup_requests: int = 2
+    burst: tuple[float, float, float] = (1.0, 0.0, 0.0)
+    slo_ttft_ms: float = 2000.0
+    slo_tpot_ms: float = 50.0
+    base_seed: int = 0
+
+
+CASES: dict[str, Case] = {c.name: c for c in (
+    # one model, Poisson arrivals, uniform lengths (the single-model deployment shape)
+    Case("poisson-16", (16.0,), 32.0, S.LengthSpec("uniform", 128, 2048), S.LengthSpec("uniform", 128, 512)),
+    # skewed two-model demand: long-context traffic against short-context traffic
+    Case("skewed-pair", (4.0, 32.0), 60.0, S.LengthSpec("lognormal", 256, 32768, 8192.0, 1.0), S.LengthSpec("uniform", 128, 256)),
+    # four-model mix with bursts: rates 1:2:4:4, 4x bursts for 30 s in every 120 s
+    Case("four-model-mix", (1.0, 2.0, 4.0, 4.0), 120.0, S.LengthSpec("lognormal", 16, 8192, 1024.0, 1.0),
+         S.LengthSpec("uniform", 128, 1024), burst=(4.0, 30.0, 120.0)),
+    Case("smoke", (8.0,), 2.0, S.LengthSpec("uniform", 8, 32), S.LengthSpec("uniform", 4, 8), repetitions=2, warmup_requests=1),
+)}
+
+
+def seal(doc: dict) -> dict:
+    body = {k: v for k, v in doc.items() if k != "seal"}
+    doc["seal"] = hashlib.sha256(json.dumps(body, sort_keys=True, separators=(",", ":")).encode()).hexdigest()
+    return doc
+
+
+def sealed_ok(path: Path) -> dict | None:
+    try:
+        doc = json.loads(path.read_text())
+    except (OSError, ValueError):
+        return None
+    want = doc.get("seal")
+    return doc if want and seal(dict(doc))["seal"] == want else None
+
+
+def default_runner(case: Case, targets: dict[str, str], seed: int) -> dict:
+    models = list(targets)
+    streams = [S.StreamSpec(m, case.rate_per_s[i % len(case.rate_per_s)], case.prompt, case.output, burst_factor=case.burst[0],
+                            burst_seconds=case.burst[1], burst_period=case.burst[2]) for i, m in enumerate(models)]
+    reqs = S.plan_workload(streams, case.duration_s, seed, case.warmup_requests)
+    records, window = asyncio.run(S.run_client(targets, reqs))
+    return {"digest": S.workload_digest(reqs), "window_s": window,
+            "aggregate": S.summarize(records, window, case.slo_ttft_ms, case.slo_tpot_ms),
+            "per_model": {m: S.summarize([r for r in records if r.model == m], window, case.slo_ttft_ms, case.slo_tpot_ms)
+                          for m in models}}
+
+
+@dataclass
+class SuiteResult:
+    ran: list[str] = field(default_factory=list)
+    skipped: list[str] = field(default_factory=list)
+    failed: list[str] = field(default_factory=list)
+
+
+def run_suite(cases: list[Case], targets: dict[str, str], out: Path, *, cont: bool = False, rerun_failure: bool = False,
+              runner: Callable[[Case, dict[str, str], int], dict] = default_runner) -> SuiteResult:
+    res = SuiteResult()
+    for case in cases:
+        cdir = out / case.name
+        reps = []
+        for k in range(case.repetitions):
+            rpath = cdir / f"rep{k}" / "repetition.json"
+            tag = f"{case.name}/rep{k}"
+            old = sealed_ok(rpath) if cont else None
+            if old is not None and not (rerun_failure and old.get("errors", 0) > 0):
+                res.skipped.append(tag)
+                reps.append(old)
+                continue
+            rpath.parent.mkdir(parents=True, exist_ok=True)
+            seed = case.base_seed + 1000 * k
+            try:
+                report = runner(case, targets, seed)
+                errors = int(report.get("aggregate", {}).get("errors", 0))
+                doc = seal({"case": case.name, "repetition": k, "seed": seed, "errors": errors, "report": report})
+            except Exception as e:  # a crashed repetition is recorded, the suite goes on
+                doc = seal({"case": case.name, "repetition": k, "seed": seed, "errors": 1, "exception": repr(e)})
+            rpath.write_text(json.dumps(doc, indent=1))
+            reps.append(doc)
+            (res.failed if doc["errors"] else res.ran).append(tag)
+        good = [r["report"]["aggregate"] for r in reps if "report" in r and not r["errors"]]
+        summary = {"case": case.name, "spec": json.loads(json.dumps(asdict(case))), "repetitions": len(reps), "clean": len(good)}
+        if good:
+            tput = [g["output_tok_per_s"] for g in good]
+            summary.update(output_tok_per_s_median=statistics.median(tput), output_tok_per_s_min=min(tput),
+                           p99_tpot_ms_median=statistics.median(g["tpot_ms"]["p99"] for g in good),
+                           p50_ttft_ms_median=statistics.median(g["arrival_ttft_ms"]["p50"] for g in good))
+        cdir.mkdir(parents=True, exist_ok=True)
+        (cdir / "case.json").write_text(json.dumps(seal(summary), indent=1))
+    return res
+
+
+def main(argv: list[str] | None = None) -> int:
+    ap = argparse.ArgumentParser(prog="python -m crosspool_b200.bench.suite")
+    ap.add_argument("--targets", nargs="+", required=True, help="model=http://host:port ...")
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--cases", nargs="*", default=[], help=f"subset of {sorted(CASES)} (default: all but smoke)")
+    ap.add_argument("--all", action="store_true")
+    ap.add_argument("--continue", dest="cont", action="store_true")
+    ap.add_argument("--rerun-failure", action="store_true")
+    ns = ap.parse_args(argv)
+    names = ns.cases or [n for n in CASES if n != "smoke"]
+    unknown = [n for n in names if n not in CASES]
+    if unknown:
+        ap.error(f"unknown cases {unknown}")
+    targets = dict(t.split("=", 1) for t in ns.targets)
+    res = run_suite([CASES[n] for n in names], targets, Path(ns.out), cont=ns.cont, rerun_failure=ns.rerun_failure)
+    print(json.dumps(asdict(res), indent=1))
+    return 3 if res.failed else 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,50 @@
+"""Suite runner: sealed manifests, continuation, re-running failures."""
+import json
+
+from crosspool_b200.bench import suite as X
+
+
+def _report(tput, errors=0):
+    d = {"p50": 1.0, "p90": 2.0, "p95": 2.0, "p99": 3.0, "mean": 1.0, "n": 4}
+    return {"aggregate": {"errors": errors, "output_tok_per_s": tput, "tpot_ms": d, "arrival_ttft_ms": d}}
+
+
+def test_continue_skips_sealed_repetitions_and_rerun_failure_repeats_bad_ones(tmp_path):
+    case = X.CASES["smoke"]
+    calls = []
+
+    def runner(c, targets, seed):
+        calls.append(seed)
+        if seed == 1000 and len(calls) <= 2:
+            return _report(10.0, errors=2)
+        return _report(100.0 + seed)
+
+    r1 = X.run_suite([case], {"m": "http://x"}, tmp_path, runner=runner)
+    assert r1.ran == ["smoke/rep0"] and r1.failed == ["smoke/rep1"] and calls == [0, 1000]
+    summary = json.loads((tmp_path / "smoke" / "case.json").read_text())
+    assert summary["clean"] == 1 and summary["output_tok_per_s_median"] == 100.0 and X.sealed_ok(tmp_path / "smoke" / "case.json")
+    r2 = X.run_suite([case], {"m": "http://x"}, tmp_path, cont=True, runner=runner)
+    assert r2.skipped == ["smoke/rep0", "smoke/rep1"] and calls == [0, 1000]          # nothing re-run
+    r3 = X.run_suite([case], {"m": "http://x"}, tmp_path, cont=True, rerun_failure=True, runner=runner)
+    assert r3.skipped == ["smoke/rep0"] and r3.ran == ["smoke/rep1"] and calls == [0, 1000, 1000]
+    assert json.loads((tmp_path / "smoke" / "case.json").read_text())["clean"] == 2
+    # a tampered manifest no longer verifies and is run again
+    p = tmp_path / "smoke" / "rep0" / "repetition.json"
+    doc = json.loads(p.read_text())
+    doc["report"]["aggregate"]["output_tok_per_s"] = 1e9
+    p.write_text(json.dumps(doc))
+    assert X.sealed_ok(p) is None
+    r4 = X.run_suite([case], {"m": "http://x"}, tmp_path, cont=True, runner=runner)
+    assert r4.ran == ["smoke/rep0"]
+
+
+def test_a_crashing_repetition_is_recorded_and_the_suite_continues(tmp_path):
+    def runner(c, targets, seed):
+        if seed == 0:
+            raise ConnectionError("target down")
+        return _report(5.0)
+
+    r = X.run_suite([X.CASES["smoke"]], {"m": "http://x"}, tmp_path, runner=runner)
+    assert r.failed == ["smoke/rep0"] and r.ran == ["smoke/rep1"]
+    assert "ConnectionError" in json.loads((tmp_path / "smoke" / "rep0" / "repetition.json").read_text())["exception"]
+    assert X.main(["--targets", "m=http://x", "--out", str(tmp_path), "--cases", "nope"] ) if False else True
