@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 16
+#define XP_ABI_VERSION 17
 
 #ifdef __cplusplus
 extern "C" {
@@ -45,6 +45,11 @@ typedef struct XpGemmArgs {
   const int* n_tiles;
   int w_rows_per_group;
   int smem_limit;      /* > 0: cap on dynamic shared memory, so the CTA can share an SM with another stream's kernel */
+  /* Block-scaled fp8: w and x are e4m3; w_scale [n_rows / 128][k / 128], x_scale [k / 128][ld_xscale] (fp32). */
+  int fp8;
+  const float* w_scale;
+  const float* x_scale;
+  int ld_xscale;
 } XpGemmArgs;
 
 typedef struct XpGemmPlan {
@@ -230,6 +235,7 @@ int xp_l2_flush(void* p, size_t bytes, void* stream);
 
 int xp_abi_version(void);
 int xp_gemm_plan(const XpGemmArgs* a, XpGemmPlan* plan);
+int xp_quant_act_fp8(const void* x, void* xq, float* scales, int rows, int k, int ldx, int ldq, int ld_scale, void* stream);
 int xp_gemm(const XpGemmArgs* a);
 int xp_encode_tmap_2d(void* out128, const void* base, uint64_t rows, uint64_t cols,
                       uint64_t pitch_bytes, uint32_t box_rows, uint32_t elem_bytes);

@@ -27,6 +27,7 @@ namespace gemm {
 
 constexpr int kTileM = 128;    // weight rows per tile (UMMA M)
 constexpr int kTileK = 64;     // bf16 elements per K block = one 128-byte swizzle row
+constexpr int kMaxBnF8 = 64;   // widest activation tile of the block-scaled fp8 path (accumulators live in registers)
 constexpr int kUmmaK = 16;     // K per tcgen05.mma for 16-bit inputs
 constexpr int kMaxStages = 8;
 constexpr int kThreads = 192;
@@ -80,6 +81,14 @@ struct Problem {
   const int4* tile_table;
   const int* n_tiles;
   int w_rows_per_group;
+  // Block-scaled fp8 (e4m3) operands: a K block is 128 elements (still one 128-byte swizzle row);
+  // weights carry one fp32 scale per 128 x 128 block ([rows / 128][k / 128]), activations one per
+  // row and K block, stored transposed ([k / 128][ld_xscale]) so that a tile's scales are contiguous.
+  int kblk;                // elements per K block: 64 (bf16) or 128 (fp8)
+  int fp8;
+  const float* w_scale;
+  const float* x_scale;
+  int ld_xscale;
 };
 
 struct SmemLayout {
@@ -178,7 +187,7 @@ __device__ __forceinline__ TileCoord tile_coord(const Problem& p, int t) {
     c.split = 0;
     c.mn = t;
     c.kb0 = 0;
-    c.kbn = p.k / kTileK;
+    c.kbn = p.k / p.kblk;
     return c;
   }
   int tm = tiles_m(p);
@@ -187,7 +196,7 @@ __device__ __forceinline__ TileCoord tile_coord(const Problem& p, int t) {
   c.mn = mn;
   c.m0 = (mn % tm) * kTileM;
   c.n0 = (mn / tm) * p.bn;
-  int kb_total = p.k / kTileK;
+  int kb_total = p.k / p.kblk;
   int per = (kb_total + p.splits - 1) / p.splits;
   c.kb0 = c.split * per;
   int end = c.kb0 + per;
@@ -222,7 +231,7 @@ __device__ __forceinline__ bool produce_tile(const Problem& p, const TileCoord& 
   const uint64_t tx_map = reinterpret_cast<uint64_t>(p.tmap_x);
   // Row-major weights: box at (k, row). Tiled weights: every 128x64 tile is one
   // contiguous 16 KB run, tile index = m_tile * k_tiles + k_tile.
-  const int kb_total = p.k / kTileK;
+  const int kb_total = p.k / p.kblk;
   int wc0, wc1, uc1, dwc0, dwc1;
   if (p.w_tiled) {
     wc0 = 0;
@@ -231,13 +240,13 @@ __device__ __forceinline__ bool produce_tile(const Problem& p, const TileCoord& 
     uc1 = (((p.up_offset + c.w_row0) / kTileM) * kb_total + c.kb0) * kTileM;
     dwc1 = kTileM;
   } else {
-    wc0 = c.kb0 * kTileK;
-    dwc0 = kTileK;
+    wc0 = c.kb0 * p.kblk;
+    dwc0 = p.kblk;
     wc1 = c.w_row0;
     uc1 = p.up_offset + c.w_row0;
     dwc1 = 0;
   }
-  int xc0 = c.kb0 * kTileK;
+  int xc0 = c.kb0 * p.kblk;
   uint32_t stage = st.stage, phase = st.phase;
   uint32_t a_addr = tiles_addr + stage * stage_bytes;
   const bool dual = p.dual != 0;
@@ -256,7 +265,7 @@ __device__ __forceinline__ bool produce_tile(const Problem& p, const TileCoord& 
     wc0 += dwc0;
     wc1 += dwc1;
     uc1 += dwc1;
-    xc0 += kTileK;
+    xc0 += p.kblk;
     a_addr += stage_bytes;
     if (++stage == stages) {
       stage = 0;
@@ -284,9 +293,13 @@ __device__ __forceinline__ void producer_drain(const SmemLayout& L, Barriers* ba
 
 // ---------------------------------------------------------------- MMA issuer
 
+__device__ __forceinline__ bool mma_tile_f8(const Problem& p, const TileCoord& c, const SmemLayout& L, uint8_t* tiles,
+                                            Barriers* bar, PipeState& st, int nacc, uint64_t deadline);
+
 __device__ __forceinline__ bool mma_tile(const Problem& p, const TileCoord& c, const SmemLayout& L,
                                          uint8_t* tiles, Barriers* bar, PipeState& st, int nacc,
                                          uint64_t deadline) {
+  if (p.fp8) return mma_tile_f8(p, c, L, tiles, bar, st, nacc, deadline);
   const uint32_t acc_w = static_cast<uint32_t>(p.bn * (p.dual ? 2 : 1));
   const uint32_t tmem_g = bar->tmem_base + st.acc * acc_w;
   const uint32_t tmem_u = tmem_g + p.bn;
@@ -343,6 +356,55 @@ __device__ __forceinline__ bool mma_tile(const Problem& p, const TileCoord& c, c
   return true;
 }
 
+// Block-scaled fp8: every K block (one scale block) is accumulated on its own into one of the two
+// TMEM buffers and handed to the epilogue warps, which scale it and keep the running sum in
+// registers; the buffers alternate per K block instead of per tile.
+__device__ __forceinline__ bool mma_tile_f8(const Problem& p, const TileCoord& c, const SmemLayout& L,
+                                            uint8_t* tiles, Barriers* bar, PipeState& st, int nacc,
+                                            uint64_t deadline) {
+  const uint32_t acc_w = static_cast<uint32_t>(p.bn);
+  const uint32_t idesc = sm100::umma_idesc_e4m3(kTileM, static_cast<uint32_t>(p.bn));
+  const uint32_t tiles_addr = sm100::smem_u32(tiles);
+  const uint32_t full0 = sm100::smem_u32(&bar->full[0]);
+  const uint32_t empty0 = sm100::smem_u32(&bar->empty[0]);
+  const uint32_t stages = static_cast<uint32_t>(L.stages);
+  const uint64_t da0 = sm100::umma_desc_sw128(tiles_addr);
+  const uint64_t db0 = sm100::umma_desc_sw128(tiles_addr + L.a_bytes);
+  const uint64_t dstage = static_cast<uint64_t>(L.stage_bytes >> 4);
+  uint32_t stage = st.stage, phase = st.phase;
+  uint64_t da = da0 + stage * dstage, db = db0 + stage * dstage;
+  for (int i = 0; i < c.kbn; ++i) {
+    if (!sm100::mbar_wait(&bar->acc_empty[st.acc], st.acc_phase ^ 1, deadline)) return false;
+    const uint32_t full = full0 + stage * 8;
+    if (!sm100::mbar_try_wait_addr(full, phase) && !sm100::mbar_wait_addr(full, phase, deadline)) {
+      st.stage = stage;
+      st.phase = phase;
+      return false;
+    }
+    sm100::tc_fence_after_sync();
+    const uint32_t tmem_d = bar->tmem_base + st.acc * acc_w;
+    // 32 fp8 elements = 32 bytes per UMMA K step: the same descriptor stride as bf16
+    sm100::umma_f8(tmem_d, da, db, idesc, 0u);
+    sm100::umma_f8(tmem_d, da + 2, db + 2, idesc, 1u);
+    sm100::umma_f8(tmem_d, da + 4, db + 4, idesc, 1u);
+    sm100::umma_f8(tmem_d, da + 6, db + 6, idesc, 1u);
+    sm100::umma_commit_addr(empty0 + stage * 8);
+    sm100::umma_commit(&bar->acc_full[st.acc]);
+    st.advance_acc(nacc);
+    da += dstage;
+    db += dstage;
+    if (++stage == stages) {
+      stage = 0;
+      phase ^= 1;
+      da = da0;
+      db = db0;
+    }
+  }
+  st.stage = stage;
+  st.phase = phase;
+  return true;
+}
+
 // ---------------------------------------------------------------- epilogue
 
 __device__ __forceinline__ void epi_bar_sync() {
@@ -396,7 +458,51 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
   sm100::tc_fence_after_sync();
 
   float g[16], u[16];
-  if (p.splits == 1) {
+  if (p.fp8) {
+    // scaled accumulation over the K blocks of this tile (bn <= 64: four chunks of 16 columns)
+    float acc[kMaxBnF8];
+#pragma unroll
+    for (int j = 0; j < kMaxBnF8; ++j) acc[j] = 0.f;
+    const int kb_total = p.k / p.kblk;
+    const float* wsc = p.w_scale + static_cast<size_t>(c.w_row0 >> 7) * kb_total + c.kb0;
+    for (int i = 0; i < c.kbn; ++i) {
+      if (i > 0) {
+        if (!__all_sync(0xffffffffu, sm100::mbar_wait(&bar->acc_full[st.acc], st.acc_phase, deadline))) return false;
+        sm100::tc_fence_after_sync();
+      }
+      const uint32_t tacc = bar->tmem_base + st.acc * acc_cols + (static_cast<uint32_t>(ew * 32) << 16);
+      const float sw = __ldg(wsc + i);
+      const float4* xs = reinterpret_cast<const float4*>(p.x_scale + static_cast<size_t>(c.kb0 + i) * p.ld_xscale + c.n0);
+#pragma unroll
+      for (int cc = 0; cc < kMaxBnF8 / 16; ++cc) {
+        if (cc * 16 < p.bn) {
+          sm100::tmem_ld16(tacc + cc * 16, g);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float4 sx = __ldg(xs + cc * 4 + q);
+            acc[cc * 16 + q * 4 + 0] += g[q * 4 + 0] * (sw * sx.x);
+            acc[cc * 16 + q * 4 + 1] += g[q * 4 + 1] * (sw * sx.y);
+            acc[cc * 16 + q * 4 + 2] += g[q * 4 + 2] * (sw * sx.z);
+            acc[cc * 16 + q * 4 + 3] += g[q * 4 + 3] * (sw * sx.w);
+          }
+        }
+      }
+      sm100::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&bar->acc_empty[st.acc]);
+      st.advance_acc(nacc);
+    }
+    if (p.splits == 1) {
+#pragma unroll
+      for (int cc = 0; cc < kMaxBnF8 / 16; ++cc)
+        if (cc * 16 < p.bn && c.n0 + cc * 16 < c.row_end) epilogue_store16(p, f, c.n0 + cc * 16, c.row_end, &acc[cc * 16], u);
+    } else {
+      float* ws = p.ws + (static_cast<size_t>(c.mn) * p.splits + c.split) * acc_cols * kTileM;
+#pragma unroll
+      for (int j = 0; j < kMaxBnF8; ++j)
+        if (j < p.bn) ws[static_cast<size_t>(j) * kTileM + lane_in_tile] = acc[j];
+    }
+  } else if (p.splits == 1) {
     for (int col = 0; col < p.bn; col += 16) {
       if (c.n0 + col >= c.row_end) break;
       sm100::tmem_ld16(tmem_acc + col, g);
@@ -412,11 +518,13 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
       for (int j = 0; j < 16; ++j) ws[static_cast<size_t>(col + j) * kTileM + lane_in_tile] = g[j];
     }
   }
-  // The accumulator buffer is free again once every epilogue warp has read it.
-  sm100::tc_fence_before_sync();
-  __syncwarp();
-  if (lane == 0) sm100::mbar_arrive(&bar->acc_empty[st.acc]);
-  st.advance_acc(nacc);
+  if (!p.fp8) {
+    // The accumulator buffer is free again once every epilogue warp has read it.
+    sm100::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) sm100::mbar_arrive(&bar->acc_empty[st.acc]);
+    st.advance_acc(nacc);
+  }
 
   if (p.splits > 1) {
     __threadfence();

@@ -88,6 +88,7 @@ gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int 
   int bucket = 0;
   while ((1 << bucket) < rows && bucket < lane::kRowBuckets - 1) ++bucket;
   Problem p{};
+  p.kblk = kTileK;
   p.rows = rows;
   p.ws = ws;
   p.counters = counters;
@@ -200,8 +201,8 @@ struct TileChoice {
 };
 
 static TileChoice choose_tiles(int tm, int rows, int kb, int dual, int sms, int fixed_bn, int fixed_splits,
-                               size_t ws_bytes_available) {
-  const int cap = dual ? 128 : 256;
+                               size_t ws_bytes_available, int max_bn = 256) {
+  const int cap = std::min(dual ? 128 : 256, max_bn);
   int top = 16;
   while (top < rows && top < cap) top <<= 1;
   TileChoice best{top, 1};
@@ -236,10 +237,14 @@ TileChoice choose_tiles_host(int tm, int rows, int kb, int dual, int sms, size_t
 
 using namespace xpool;
 
+static inline int kblk_of(const XpGemmArgs* a) { return a->fp8 ? 128 : gemm::kTileK; }
+
 extern "C" int xp_gemm_plan(const XpGemmArgs* a, XpGemmPlan* plan) {
-  if (a->n_out <= 0 || a->n_out % gemm::kTileM != 0 || a->k <= 0 || a->k % gemm::kTileK != 0 ||
-      a->rows <= 0)
-    return -10;
+  const int kblk = a->fp8 ? 128 : gemm::kTileK;
+  if (a->n_out <= 0 || a->n_out % gemm::kTileM != 0 || a->k <= 0 || a->k % kblk != 0 || a->rows <= 0) return -10;
+  if (a->fp8 && (a->dual || a->w_tiled || a->tile_table != nullptr || a->w_scale == nullptr || a->x_scale == nullptr ||
+                 a->ld_xscale % 4 != 0 || a->bn > gemm::kMaxBnF8))
+    return -14;
   int dev = 0;
   cudaGetDevice(&dev);
   static int sm_count_cache[64] = {0};
@@ -248,13 +253,14 @@ extern "C" int xp_gemm_plan(const XpGemmArgs* a, XpGemmPlan* plan) {
   int sms = a->num_sms > 0 ? a->num_sms : (dev < 64 ? sm_count_cache[dev] : 148);
   if (sms <= 0) sms = 148;
   const int tm = a->n_out / gemm::kTileM;
-  const int kb = a->k / gemm::kTileK;
+  const int kb = a->k / kblk;
   if (a->bn > 0 && a->bn != 16 && a->bn != 32 && a->bn != 64 && a->bn != 128 && a->bn != 256) return -11;
   int fixed_splits = a->splits;
   if (fixed_splits > kb) fixed_splits = kb;
   while (fixed_splits > 1 && (fixed_splits - 1) * ((kb + fixed_splits - 1) / fixed_splits) >= kb) --fixed_splits;
   const size_t ws_avail = (a->ws != nullptr && a->counters != nullptr) ? a->ws_bytes : 0;
-  const gemm::TileChoice ch = gemm::choose_tiles(tm, a->rows, kb, a->dual, sms, a->bn, fixed_splits, ws_avail);
+  const gemm::TileChoice ch = gemm::choose_tiles(tm, a->rows, kb, a->dual, sms, a->bn, fixed_splits, ws_avail,
+                                                 a->fp8 ? gemm::kMaxBnF8 : 256);
   const int bn = a->bn > 0 ? a->bn : ch.bn;
   int splits = fixed_splits > 0 ? fixed_splits : ch.splits;
   const int acc_cols = bn * (a->dual ? 2 : 1);
@@ -296,13 +302,17 @@ extern "C" int xp_gemm(const XpGemmArgs* a) {
     rc = tmap::cache().get(&tw, a->w, static_cast<uint64_t>(w_rows) * (a->k / gemm::kTileK), gemm::kTileK,
                            gemm::kTileK * 2, gemm::kTileM, 2);
   } else {
-    rc = tmap::cache().get(&tw, a->w, w_rows, a->k, static_cast<uint64_t>(a->ldw > 0 ? a->ldw : a->k) * 2,
-                           gemm::kTileM, 2);
+    const int eb = a->fp8 ? 1 : 2;
+    rc = tmap::cache().get(&tw, a->w, w_rows, a->k, static_cast<uint64_t>(a->ldw > 0 ? a->ldw : a->k) * eb,
+                           gemm::kTileM, eb);
   }
   if (rc != 0) return -20;
-  rc = tmap::cache().get(&tx, a->x, a->rows, a->k, static_cast<uint64_t>(a->ldx > 0 ? a->ldx : a->k) * 2,
-                         plan.bn, 2);
+  {
+    const int eb = a->fp8 ? 1 : 2;
+    rc = tmap::cache().get(&tx, a->x, a->rows, a->k, static_cast<uint64_t>(a->ldx > 0 ? a->ldx : a->k) * eb, plan.bn, eb);
+  }
   if (rc != 0) return -21;
+  if (a->fp8 && a->ld_xscale < (a->rows + plan.bn - 1) / plan.bn * plan.bn) return -15;  // scales padded to whole tiles
 
   gemm::Problem p{};
   p.out = a->out;
@@ -328,6 +338,11 @@ extern "C" int xp_gemm(const XpGemmArgs* a) {
   p.tile_table = reinterpret_cast<const int4*>(a->tile_table);
   p.n_tiles = a->n_tiles;
   p.w_rows_per_group = a->w_rows_per_group;
+  p.kblk = kblk_of(a);
+  p.fp8 = a->fp8;
+  p.w_scale = a->w_scale;
+  p.x_scale = a->x_scale;
+  p.ld_xscale = a->ld_xscale;
   if (a->tile_table != nullptr) {
     if (plan.splits != 1) return -13;
     plan.grid = plan.smem_bytes > 0 ? 148 : 148;

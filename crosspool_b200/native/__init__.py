@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 16
+EXPECTED_ABI = 17
 HERE = Path(__file__).resolve().parent
 
 
@@ -59,6 +59,10 @@ class GemmArgs(C.Structure):
         ("n_tiles", C.c_void_p),
         ("w_rows_per_group", C.c_int),
         ("smem_limit", C.c_int),
+        ("fp8", C.c_int),
+        ("w_scale", C.c_void_p),
+        ("x_scale", C.c_void_p),
+        ("ld_xscale", C.c_int),
     ]
 
 
@@ -348,6 +352,7 @@ def _declare_moe(lib: C.CDLL) -> None:
         "xp_moe_route": [C.POINTER(RouteArgs), C.c_void_p],
         "xp_moe_gather": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p],
         "xp_moe_combine": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p],
+        "xp_quant_act_fp8": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p],
     }
     for name, args in sig.items():
         fn = getattr(lib, name)

@@ -178,3 +178,52 @@ def gateup_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, *, out: torch.Tensor
               splits=splits, bn=bn, num_sms=num_sms, gate_limit=gate_limit, up_add=up_add, act_alpha=act_alpha)
     native.check(native.kernels().xp_gemm(C.byref(a)), "xp_gemm(swiglu)")
     return out
+
+
+# ---------------------------------------------------------------------------------------------- fp8
+
+def quantize_act_fp8(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16 ``[rows, k]`` -> (e4m3 ``[rows, k]``, fp32 scales ``[k / 128, rows padded to 256]``): one
+    scale per row and 128-element K block."""
+    rows, k = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and k % 128 == 0
+    xq = torch.empty(rows, k, dtype=torch.float8_e4m3fn, device=x.device)
+    ld = (rows + 255) // 256 * 256
+    scales = torch.ones(k // 128, ld, dtype=torch.float32, device=x.device)
+    native.check(native.kernels().xp_quant_act_fp8(x.data_ptr(), xq.data_ptr(), scales.data_ptr(), rows, k, x.stride(0), k, ld,
+                                                   torch.cuda.current_stream(x.device).cuda_stream), "xp_quant_act_fp8")
+    return xq, scales
+
+
+def linear_fp8(x: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor, *, out: torch.Tensor | None = None,
+               bias: torch.Tensor | None = None, resid: torch.Tensor | None = None, splits: int = 0, bn: int = 0) -> torch.Tensor:
+    """``x @ dequant(wq, w_scale).T`` with block-scaled e4m3 operands on ``tcgen05.mma.kind::f8f6f4``.
+
+    ``wq`` ``[n, k]`` e4m3 with ``w_scale`` ``[n / 128, k / 128]`` (:class:`~crosspool_b200.quantization.Fp8Block`);
+    ``x`` bf16, quantised here per row and 128-element K block. Every K block is accumulated in TMEM on its
+    own and folded into fp32 registers with ``w_scale * x_scale``, so the result equals the fp32 product of
+    the dequantised operands up to summation order."""
+    rows, k = x.shape
+    n = wq.shape[0]
+    assert wq.dtype == torch.float8_e4m3fn and wq.shape[1] == k and n % 128 == 0 and k % 128 == 0
+    assert w_scale.dtype == torch.float32 and tuple(w_scale.shape) == (n // 128, k // 128) and w_scale.is_contiguous()
+    xq, xs = quantize_act_fp8(x)
+    if out is None:
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=x.device)
+    s = scratch(x.device)
+    a = native.GemmArgs()
+    a.w, a.x, a.out = wq.data_ptr(), xq.data_ptr(), out.data_ptr()
+    a.resid = resid.data_ptr() if resid is not None else None
+    a.bias = bias.data_ptr() if bias is not None else None
+    a.ws, a.counters, a.status = s.ws.data_ptr(), s.counters.data_ptr(), s.status.data_ptr()
+    a.stream = torch.cuda.current_stream(x.device).cuda_stream
+    a.ws_bytes, a.counter_bytes = s.ws.numel() * 4, s.counters.numel() * 4
+    a.w_rows_total, a.n_out, a.k, a.rows = n, n, k, rows
+    a.ldw, a.ldx, a.ld_out = wq.stride(0), k, out.stride(0)
+    a.ld_resid = resid.stride(0) if resid is not None else 0
+    a.epilogue = EPI_STORE_F32 if out.dtype == torch.float32 else (EPI_RESIDUAL if resid is not None else EPI_STORE)
+    a.splits, a.bn = splits, bn
+    a.w_evict_first = int(rows <= 64)
+    a.fp8, a.w_scale, a.x_scale, a.ld_xscale = 1, w_scale.data_ptr(), xs.data_ptr(), xs.stride(0)
+    native.check(native.kernels().xp_gemm(C.byref(a)), "xp_gemm(fp8)")
+    return out
