@@ -202,7 +202,8 @@ struct TileChoice {
 
 static TileChoice choose_tiles(int tm, int rows, int kb, int dual, int sms, int fixed_bn, int fixed_splits,
                                size_t ws_bytes_available, int max_bn = 256) {
-  const int cap = std::min(dual ? 128 : 256, max_bn);
+  // 256-wide dual tiles use all 512 TMEM columns (one accumulator buffer): only on request
+  const int cap = std::min((dual && fixed_bn != 256) ? 128 : 256, max_bn);
   int top = 16;
   while (top < rows && top < cap) top <<= 1;
   TileChoice best{top, 1};

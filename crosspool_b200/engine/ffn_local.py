@@ -39,6 +39,8 @@ class LocalFfnPort(FfnPort):
             from ..ops import moe
 
             return [moe.moe_forward(x, w, self.cfg, out=self.y[:rows], ws=self.moe_ws)]
+        if "fp8" in w.extra:
+            return [gemm.ffn_fp8(x, w.extra["fp8"], out=self.y[:rows])]
         inter = w.gate_up.shape[0] // 2
         act = self.act[:rows, :inter]
         gemm.gateup_swiglu(x, w.gate_up, out=act, bias=w.gate_up_bias)

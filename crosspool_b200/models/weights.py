@@ -148,6 +148,20 @@ def random_ffn_layer(cfg: ModelConfig, layer: int, seed: int = 0, device="cpu", 
     return FfnLayerWeights(gate_up.to(device), down.to(device))
 
 
+def quantize_ffn_layer_fp8(w: FfnLayerWeights) -> FfnLayerWeights:
+    """Attaches block-scaled e4m3 copies of a dense layer's projections (128 x 128 weight blocks) under
+    ``w.extra["fp8"]``; ports that find them run the fp8 GEMM path."""
+    from ..quantization import Fp8Block
+
+    if w.is_moe:
+        raise NotImplementedError("fp8 expert weights are not supported")
+    fmt = Fp8Block()
+    gu, dn = fmt.quantize(w.gate_up), fmt.quantize(w.down)
+    w.extra["fp8"] = {"gate_up": gu["weight"], "gate_up_scale": gu["scale"].contiguous(), "down": dn["weight"],
+                      "down_scale": dn["scale"].contiguous()}
+    return w
+
+
 def random_ffn_weights(cfg: ModelConfig, seed: int = 0, device="cpu", dtype: torch.dtype | None = None,
                        tp_rank: int = 0, tp_size: int = 1) -> list[FfnLayerWeights]:
     return [random_ffn_layer(cfg, l, seed, device, dtype, tp_rank, tp_size) for l in range(cfg.num_layers)]

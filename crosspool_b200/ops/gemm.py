@@ -189,7 +189,7 @@ def quantize_act_fp8(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and k % 128 == 0
     xq = torch.empty(rows, k, dtype=torch.float8_e4m3fn, device=x.device)
     ld = (rows + 255) // 256 * 256
-    scales = torch.ones(k // 128, ld, dtype=torch.float32, device=x.device)
+    scales = torch.empty(k // 128, ld, dtype=torch.float32, device=x.device)  # padding columns are never stored
     native.check(native.kernels().xp_quant_act_fp8(x.data_ptr(), xq.data_ptr(), scales.data_ptr(), rows, k, x.stride(0), k, ld,
                                                    torch.cuda.current_stream(x.device).cuda_stream), "xp_quant_act_fp8")
     return xq, scales
@@ -227,3 +227,14 @@ def linear_fp8(x: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor, *, out:
     a.fp8, a.w_scale, a.x_scale, a.ld_xscale = 1, w_scale.data_ptr(), xs.data_ptr(), xs.stride(0)
     native.check(native.kernels().xp_gemm(C.byref(a)), "xp_gemm(fp8)")
     return out
+
+
+def ffn_fp8(x: torch.Tensor, q: dict, *, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Dense gated FFN with block-scaled fp8 weights: gate/up projection (one GEMM over the concatenated
+    rows), SiLU-gate in bf16, down projection. ``q`` holds ``gate_up``/``down`` e4m3 tensors and their
+    ``*_scale`` grids (see :func:`crosspool_b200.models.weights.quantize_ffn_layer_fp8`)."""
+    from . import norm
+
+    gu = linear_fp8(x, q["gate_up"], q["gate_up_scale"])
+    act = norm.swiglu(gu)
+    return linear_fp8(act, q["down"], q["down_scale"], out=out)

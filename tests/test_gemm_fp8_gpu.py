@@ -48,3 +48,31 @@ def test_fp8_linear_adds_the_residual_and_tracks_the_bf16_product():
     full = x.float() @ w.t() + resid.float()
     rel = ((out.float() - full).pow(2).mean().sqrt() / full.pow(2).mean().sqrt()).item()
     assert rel < 0.05, rel                     # two e4m3 roundings (about 3 % each) against exact bf16 math
+
+
+def test_engine_with_fp8_ffn_weights_stays_close_to_the_bf16_model():
+    from crosspool_b200.engine.atn_engine import AttentionEngine, EngineConfig
+    from crosspool_b200.engine.ffn_local import LocalFfnPort
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.models.reference import ReferenceModel
+    from crosspool_b200.models.weights import quantize_ffn_layer_fp8, random_attention_weights, random_ffn_weights
+    from crosspool_b200.ops import gemm
+
+    cfg = mc.preset("Qwen/Qwen3-0.6B").with_layers(2)
+    aw = random_attention_weights(cfg, 1, "cuda", torch.bfloat16)
+    fw = random_ffn_weights(cfg, 1, "cuda", torch.bfloat16)
+    ref = ReferenceModel(cfg, aw, fw)
+    fq = [quantize_ffn_layer_fp8(w) for w in random_ffn_weights(cfg, 1, "cuda", torch.bfloat16)]
+    eng = AttentionEngine(cfg, aw, LocalFfnPort(cfg, fq), EngineConfig(max_batch=4, prefill_chunk=128, max_seq_len=256))
+    eng.warmup()
+    prompt = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(0)).tolist()
+    s = eng.add_request(prompt, 3)
+    first = None
+    while eng.has_work:
+        for i, (sq, _) in enumerate(eng.step()):
+            first = eng.logits[i].float().clone() if first is None else first
+    gemm.check_status(eng.device)
+    _, rl = ref.generate(torch.tensor(prompt, device="cuda"), 1)
+    p, q = rl[0].float().log_softmax(-1), first.log_softmax(-1)
+    kl = (p.exp() * (p - q)).sum().item()
+    assert kl < 0.05, kl       # fp8 weights and activations in the FFNs only
