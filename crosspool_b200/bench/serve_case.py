@@ -1,0 +1,137 @@
+"""Brings up a local deployment (daemon + one agent per GPU, as ``xpool`` child processes), runs one
+serving benchmark case against it over HTTP and retires it in order.
+
+    python -m crosspool_b200.bench.serve_case --case poisson-16 --models Qwen/Qwen3-0.6B --atn 0 --ffn 1 \
+        --out gpurun_out/serve_poisson16.json
+
+The deployment is the one a user would start by hand with ``xpool daemon serve`` / ``xpool atnagent`` /
+``xpool ffnagent``; the load generator is ``bench.serving`` (open-loop Poisson arrivals, streaming
+``POST /generate``, client-side TTFT / TPOT / ITL).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import signal
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[2]
+
+
+def toml_for(models: list[str], atn: list[int], ffn: list[int], port: int, ffn_tp: int, lanes: int) -> str:
+    t = [f"[daemon]\nport = {port}", f"[atn]\ndevices = {atn}", f"[ffn]\ndevices = {ffn}",
+         f"[scheduler]\nffn_concurrency = {lanes}", "[scheduler.slo]\nttft_ms = 2000\ntbt_ms = 50"]
+    for m in models:
+        t.append(f'[[models]]\nid = "{m}"\nffn_tp_size = {ffn_tp}')
+    return "\n".join(t) + "\n"
+
+
+class LocalDeployment:
+    def __init__(self, toml_text: str, atn: list[int], ffn: list[int], port: int, env: dict[str, str] | None = None):
+        self.toml_text, self.atn, self.ffn, self.port = toml_text, atn, ffn, port
+        self.env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0", **(env or {}))
+        self.procs: list[subprocess.Popen] = []
+        self._dir = tempfile.TemporaryDirectory(prefix="xpool-deploy-")
+
+    def _xp(self, *args: str) -> subprocess.Popen:
+        p = subprocess.Popen([sys.executable, "-m", "crosspool_b200.cli.main", *args], env=self.env)
+        self.procs.append(p)
+        return p
+
+    def __enter__(self) -> "LocalDeployment":
+        import httpx
+
+        cfgp = Path(self._dir.name) / "xpool.toml"
+        cfgp.write_text(self.toml_text)
+        self.env["XPOOL_CONFIG"] = str(cfgp)
+        base = f"http://127.0.0.1:{self.port}"
+        self._xp("daemon", "serve")
+        for _ in range(150):
+            try:
+                if httpx.get(base + "/health", timeout=1).status_code == 200:
+                    break
+            except httpx.HTTPError:
+                time.sleep(0.2)
+        for d in self.ffn:
+            self._xp("ffnagent", "--device", str(d))
+        for d in self.atn:
+            self._xp("atnagent", "--device", str(d))
+        for _ in range(1200):
+            r = httpx.get(base + "/ready", timeout=5).json()
+            if r.get("failure"):
+                raise RuntimeError(f"deployment failed: {r['failure']}")
+            if r["system_ready"]:
+                return self
+            if any(p.poll() not in (None, 0) for p in self.procs):
+                raise RuntimeError("a deployment process exited early")
+            time.sleep(0.5)
+        raise TimeoutError("deployment did not become ready")
+
+    def targets(self, models: list[str]) -> dict[str, str]:
+        return {m: "http://127.0.0.1:30000" for m in models}   # all Instances of attention device 0 share one listener
+
+    def __exit__(self, *exc) -> None:
+        import httpx
+
+        try:
+            httpx.post(f"http://127.0.0.1:{self.port}/fabric/quiesce", json={"reason": "benchmark finished"}, timeout=5)
+            for p in self.procs[1:]:
+                try:
+                    p.wait(60)
+                except subprocess.TimeoutExpired:
+                    pass
+        except Exception:
+            pass
+        for p in self.procs:
+            if p.poll() is None:
+                p.send_signal(signal.SIGTERM)   # exact child PIDs only
+        for p in self.procs:
+            try:
+                p.wait(15)
+            except subprocess.TimeoutExpired:
+                p.kill()
+        self._dir.cleanup()
+
+
+def main(argv: list[str] | None = None) -> int:
+    from . import suite
+
+    ap = argparse.ArgumentParser(prog="python -m crosspool_b200.bench.serve_case")
+    ap.add_argument("--case", default="poisson-16", choices=sorted(suite.CASES))
+    ap.add_argument("--models", nargs="+", default=["Qwen/Qwen3-0.6B"])
+    ap.add_argument("--atn", type=int, nargs="+", default=[0])
+    ap.add_argument("--ffn", type=int, nargs="+", default=[1])
+    ap.add_argument("--ffn-tp", type=int, default=1)
+    ap.add_argument("--lanes", type=int, default=2)
+    ap.add_argument("--port", type=int, default=9841)
+    ap.add_argument("--max-batch", type=int, default=256)
+    ap.add_argument("--max-seq-len", type=int, default=2624)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--out", default="")
+    ns = ap.parse_args(argv)
+    case = suite.CASES[ns.case]
+    env = {"XPOOL_MAX_BATCH": str(ns.max_batch), "XPOOL_MAX_SEQ_LEN": str(ns.max_seq_len), "XPOOL_MAX_ROWS": "4096"}
+    text = toml_for(ns.models, ns.atn, ns.ffn, ns.port, ns.ffn_tp, ns.lanes)
+    with LocalDeployment(text, ns.atn, ns.ffn, ns.port, env) as dep:
+        report = suite.default_runner(case, dep.targets(ns.models), ns.seed)
+    report["case"] = ns.case
+    report["deployment"] = {"models": ns.models, "atn": ns.atn, "ffn": ns.ffn, "ffn_tp": ns.ffn_tp, "lanes": ns.lanes}
+    agg = report["aggregate"]
+    line = {"case": ns.case, "output_tok_per_s": round(agg["output_tok_per_s"], 1), "completed": agg["completed"],
+            "errors": agg["errors"], "tpot_p50_ms": round(agg["tpot_ms"]["p50"], 2), "tpot_p99_ms": round(agg["tpot_ms"]["p99"], 2),
+            "ttft_p50_ms": round(agg["arrival_ttft_ms"]["p50"], 1), "ttft_p99_ms": round(agg["arrival_ttft_ms"]["p99"], 1),
+            "slo": agg.get("slo")}
+    print(json.dumps(line), flush=True)
+    if ns.out:
+        Path(ns.out).write_text(json.dumps(report, indent=1))
+    return 0 if agg["errors"] == 0 else 3
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

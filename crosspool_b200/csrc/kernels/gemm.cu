@@ -175,11 +175,12 @@ gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int 
   run_tiles(p, nacc, smem_budget, status);
 }
 
-// Estimated duration (microseconds) of one launch for a tile width and split-K
-// factor. The constants come from measurements on B200: one SM ingests about
-// 55 GB/s through TMA, HBM delivers about 6 TB/s in total, a tcgen05.mma of
-// M=128 retires in max(45, N/2) cycles, and a launch costs about 3 us of set-up,
-// pipeline fill and epilogue. Only relative order matters.
+// Estimated duration (microseconds) of one launch for a tile width and split-K factor, fitted to
+// measurements on B200 (python -m crosspool_b200.bench.kernels gemm ...): a CTA streams its stages at
+// about 45 GB/s whatever the source (a 48-64 KB stage takes 1.0-1.4 us), HBM delivers about 6 TB/s in
+// total, a tcgen05.mma of M=128 retires in max(45, N/2) cycles, a launch costs about 3 us of set-up and
+// pipeline fill, and split-K pays for parking and re-reading fp32 partials (about 3 TB/s through L2:
+// two splits of a 4096 x 12288 gate/up projection at 256 rows cost +45 us). Only relative order matters.
 static double estimate_us(int tm, int rows, int kb, int dual, int bn, int splits, int sms) {
   const int tn = (rows + bn - 1) / bn;
   const int ctas = tm * tn * splits;
@@ -187,13 +188,16 @@ static double estimate_us(int tm, int rows, int kb, int dual, int bn, int splits
   const int kb_per = (kb + splits - 1) / splits;
   const double stage_kb = (kTileM * kTileK * 2 * (dual ? 2 : 1) + bn * kTileK * 2) / 1000.0;
   const int active = std::min(ctas, sms);
-  const double bw = std::min(55.0, 6000.0 / active);  // KB per us per SM
+  const double bw = std::min(45.0, 6000.0 / active);  // KB per us per SM
   const double t_mem = stage_kb / bw;
   const double t_mma = (dual ? 8 : 4) * std::max(45.0, bn / 2.0) / 1900.0;
   const int acc_cols = bn * (dual ? 2 : 1);
-  double t = 3.0 + kb_per * std::max(t_mem, t_mma) + (bn / 16) * 0.12;
-  if (splits > 1) t += 2.0 + splits * acc_cols * 0.512 / 55.0 + acc_cols * 0.004;
-  return waves * t;
+  double t = waves * (3.0 + kb_per * std::max(t_mem, t_mma) + (acc_cols / 16) * 0.12);
+  if (splits > 1) {
+    const double ws_mb = static_cast<double>(tm) * tn * splits * acc_cols * kTileM * 4 / 1e6;
+    t += 2.0 + ws_mb * 2.0 / 3.0 + splits * acc_cols * 0.512 / 55.0;
+  }
+  return t;
 }
 
 struct TileChoice {
@@ -202,8 +206,9 @@ struct TileChoice {
 
 static TileChoice choose_tiles(int tm, int rows, int kb, int dual, int sms, int fixed_bn, int fixed_splits,
                                size_t ws_bytes_available, int max_bn = 256) {
-  // 256-wide dual tiles use all 512 TMEM columns (one accumulator buffer): only on request
-  const int cap = std::min((dual && fixed_bn != 256) ? 128 : 256, max_bn);
+  // 256-wide dual tiles use all 512 TMEM columns (one accumulator buffer, no epilogue overlap): worth it
+  // only when they make the activation a single tile, so that every weight byte is fetched once
+  const int cap = std::min((dual && fixed_bn != 256 && !(rows > 128 && rows <= 256)) ? 128 : 256, max_bn);
   int top = 16;
   while (top < rows && top < cap) top <<= 1;
   TileChoice best{top, 1};
