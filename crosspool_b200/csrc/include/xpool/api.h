@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 17
+#define XP_ABI_VERSION 18
 
 #ifdef __cplusplus
 extern "C" {
@@ -91,6 +91,14 @@ typedef struct XpWaitArgs {
   int n;
 } XpWaitArgs;
 
+/* Producer half of a flag handshake: *seq_counter += 1, then every flag receives the new value (release). */
+typedef struct XpSignalArgs {
+  uint32_t* flags[8];
+  uint32_t* seq_counter;
+  int n;
+  int reserved;
+} XpSignalArgs;
+
 /* FFN device Lane runtime (see xpool/lane.cuh). */
 typedef struct XpLaneInstanceDesc {
   void* input;             /* local [capacity_rows, hidden] bf16 payload buffer */
@@ -130,6 +138,7 @@ int xp_lane_trace_enable(void* rt, uint32_t capacity);
 int64_t xp_lane_trace_read(void* rt, uint64_t* out, uint64_t max_events, uint64_t* dropped, void* stream);
 void xp_lane_destroy(void* rt);
 int xp_wait_flags(const XpWaitArgs* a, void* stream);
+int xp_signal_flags(const XpSignalArgs* a, void* stream);
 
 /* Mixture-of-experts helpers (csrc/kernels/moe.cu). */
 typedef struct XpRouterArgs {

@@ -133,6 +133,17 @@ __global__ void wait_flags_kernel(XpWaitArgs a) {
   if (rc != 0 && a.status != nullptr) atomicCAS(a.status, 0u, 4u);
 }
 
+// Bumps a device-resident sequence counter and releases the new value into up to 8 flag words
+// (typically one per peer GPU): the producer half of a flag handshake whose consumer half is
+// wait_flags_kernel with want_ptr on a counter that advances in step.
+__global__ void signal_flags_kernel(XpSignalArgs a) {
+  const uint32_t seq = *a.seq_counter + 1;
+  __threadfence_system();  // everything this stream wrote before is visible before the flags move
+  if (threadIdx.x < static_cast<unsigned>(a.n)) sm100::st_release_sys(a.flags[threadIdx.x], seq);
+  __syncthreads();
+  if (threadIdx.x == 0) *a.seq_counter = seq;
+}
+
 struct Runtime {
   int n_instances = 0, n_lanes = 0, sms = 148;
   size_t ws_bytes_per_lane = 0;
@@ -526,6 +537,13 @@ extern "C" void xp_lane_destroy(void* h) {
   cudaFree(rt->counters_d);
   cudaFree(rt->status_d);
   delete rt;
+}
+
+extern "C" int xp_signal_flags(const XpSignalArgs* a, void* stream) {
+  if (a->n < 1 || a->n > 8 || a->seq_counter == nullptr) return -1;
+  lane::signal_flags_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*a);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);
 }
 
 extern "C" int xp_wait_flags(const XpWaitArgs* a, void* stream) {

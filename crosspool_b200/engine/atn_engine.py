@@ -98,8 +98,12 @@ class FfnPort:
 
 class AttentionEngine:
     def __init__(self, cfg: ModelConfig, weights: AttentionWeights, port: FfnPort, ecfg: EngineConfig | None = None,
-                 device: str | torch.device = "cuda", kv: PagedKvCache | None = None):
+                 device: str | torch.device = "cuda", kv: PagedKvCache | None = None, tp=None):
+        """``tp``: a connected ``parallel.atn_tp.TpGroup`` when this engine is one attention TP rank;
+        ``cfg`` and ``weights`` are then the rank-local ones (``atn_tp.local_config`` /
+        ``shard_attention_weights``)."""
         self.cfg, self.w, self.port = cfg, weights, port
+        self.tp = tp
         self.ecfg = ecfg or EngineConfig()
         self.device = torch.device(device)
         e = self.ecfg
@@ -218,13 +222,20 @@ class AttentionEngine:
                 norm.add_rmsnorm(parts, lw.input_norm, cfg.rms_norm_eps, resid=resid, out=x, **self.port.wait_args())
             gemm.linear(x, lw.qkv, out=self.qkv[:rows], bias=lw.qkv_bias)
             attn_fn(l, lw, rows)
-            gemm.linear(self.attn_out[:rows].view(rows, cfg.q_size), lw.o, out=self.o[:rows])
             tgt = self.port.publish_targets(l, rows, mode)
-            if tgt is None:
-                norm.add_rmsnorm([self.o[:rows]], lw.post_attn_norm, cfg.rms_norm_eps, resid=resid, out=x2)
+            if self.tp is None:
+                gemm.linear(self.attn_out[:rows].view(rows, cfg.q_size), lw.o, out=self.o[:rows])
+                o_parts = dict(parts=[self.o[:rows]])
             else:
-                norm.add_rmsnorm([self.o[:rows]], lw.post_attn_norm, cfg.rms_norm_eps, resid=resid, out=x2,
-                                 want_local=False, **tgt)
+                # this rank's heads give a partial; all ranks' partials are folded by the norm below
+                gemm.linear(self.attn_out[:rows].view(rows, cfg.q_size), lw.o, out=self.tp.part(l)[:rows])
+                self.tp.exchange()
+                o_parts = dict(parts=[], part_ptrs=self.tp.part_ptrs(l), part_shape=(rows, cfg.hidden_size, cfg.hidden_size))
+            if tgt is None:
+                norm.add_rmsnorm(weight=lw.post_attn_norm, eps=cfg.rms_norm_eps, resid=resid, out=x2, **o_parts)
+            else:
+                norm.add_rmsnorm(weight=lw.post_attn_norm, eps=cfg.rms_norm_eps, resid=resid, out=x2,
+                                 want_local=False, **tgt, **o_parts)
             parts = self.port.run(l, x2, rows, mode)
         self._parts = parts
 

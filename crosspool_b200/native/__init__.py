@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 17
+EXPECTED_ABI = 18
 HERE = Path(__file__).resolve().parent
 
 
@@ -255,6 +255,10 @@ class WaitArgs(C.Structure):
     ]
 
 
+class SignalArgs(C.Structure):
+    _fields_ = [("flags", C.c_void_p * 8), ("seq_counter", C.c_void_p), ("n", C.c_int), ("reserved", C.c_int)]
+
+
 class LaneInstanceDesc(C.Structure):
     _fields_ = [
         ("input", C.c_void_p),
@@ -312,6 +316,7 @@ def _declare_lane(lib: C.CDLL) -> None:
         "xp_lane_shutdown": [C.c_void_p, C.c_void_p],
         "xp_lane_stats": [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.c_void_p],
         "xp_wait_flags": [C.POINTER(WaitArgs), C.c_void_p],
+        "xp_signal_flags": [C.POINTER(SignalArgs), C.c_void_p],
         "xp_dev_alloc": [C.POINTER(C.c_void_p), C.c_size_t],
         "xp_dev_free": [C.c_void_p],
         "xp_ipc_get_handle": [C.c_void_p, C.c_void_p],

@@ -34,23 +34,34 @@ def add_rmsnorm(parts: Sequence[torch.Tensor] | torch.Tensor, weight: torch.Tens
                 peer_ptrs: Sequence[int] = (), peer_flag_ptrs: Sequence[int] = (), peer_meta_ptrs: Sequence[int] = (),
                 publish_seq: int = 0, wait_flag_ptrs: Sequence[int] = (), wait_seq: int = 0,
                 wait_ns: int = 5_000_000_000, meta: tuple[int, int, int] = (0, 0, 0),
-                want_local: bool = True, seq_counter_ptr: int = 0) -> torch.Tensor | None:
+                want_local: bool = True, seq_counter_ptr: int = 0,
+                part_ptrs: Sequence[int] | None = None, part_shape: tuple[int, int, int] | None = None
+                ) -> torch.Tensor | None:
     """``y = rmsnorm(sum(parts) + resid) * weight``; ``resid`` is updated in place.
 
-    ``parts`` are bf16 ``[rows, hidden]`` tensors (or raw device pointers paired with an explicit
-    ``out`` for shape). With ``weight=None`` only the residual add happens.
+    ``parts`` are bf16 ``[rows, hidden]`` tensors summed in list order. Parts that live in another
+    GPU's memory are given as raw mapped pointers instead: ``part_ptrs`` with
+    ``part_shape = (rows, hidden, leading dimension)``; the device then comes from ``resid``/``out``.
+    With ``weight=None`` only the residual add happens.
     """
     if isinstance(parts, torch.Tensor):
         parts = [parts]
-    first = parts[0]
-    rows, hidden = first.shape
-    dev = first.device
+    a = native.NormArgs()
+    if part_ptrs is not None:
+        rows, hidden, ld_parts = part_shape
+        dev = (resid if resid is not None else out).device
+        for i, ptr in enumerate(part_ptrs):
+            a.parts[i] = ptr
+        parts = list(part_ptrs)
+    else:
+        first = parts[0]
+        rows, hidden = first.shape
+        dev, ld_parts = first.device, first.stride(0)
+        for i, p in enumerate(parts):
+            assert p.dtype == torch.bfloat16 and p.stride(1) == 1 and p.stride(0) == first.stride(0)
+            a.parts[i] = p.data_ptr()
     if want_local and out is None and weight is not None:
         out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
-    a = native.NormArgs()
-    for i, p in enumerate(parts):
-        assert p.dtype == torch.bfloat16 and p.stride(1) == 1 and p.stride(0) == first.stride(0)
-        a.parts[i] = p.data_ptr()
     for i, f in enumerate(wait_flag_ptrs):
         a.wait_flags[i] = f
     for i, p in enumerate(peer_ptrs):
@@ -65,7 +76,7 @@ def add_rmsnorm(parts: Sequence[torch.Tensor] | torch.Tensor, weight: torch.Tens
     a.cancel = None
     a.wait_ns = wait_ns
     a.rows, a.hidden = rows, hidden
-    a.ld_parts = first.stride(0)
+    a.ld_parts = ld_parts
     a.ld_out = out.stride(0) if out is not None else hidden
     a.nparts, a.npeers = len(parts), len(peer_ptrs)
     a.wait_seq, a.publish_seq = wait_seq, publish_seq
