@@ -50,6 +50,7 @@ class EngineConfig:
     max_prefill_seqs: int = 64
     use_cuda_graph: bool = True
     decode_buckets: list[int] | None = None
+    prefix_cache: bool = False  # keep full prompt pages and share them with later requests
 
 
 @dataclass
@@ -128,6 +129,11 @@ class AttentionEngine:
         self._b_last = None
         self._inflight = None
         self._graph_launches: dict[int, int] = {}
+        self.prefix = None
+        if e.prefix_cache:
+            from .prefix_cache import PrefixCache
+
+            self.prefix = PrefixCache(e.page_size)
         self.capacity = None          # ecs.reconciler.CapacityReconciler when the KV cache is elastic
         self._demand_pages = 0
         self.ttft_slo_s = 0.0
@@ -331,15 +337,25 @@ class AttentionEngine:
             if len(self.running) + len(self.prefilling) >= e.max_batch:
                 break
             s = self.waiting[0]
-            need = self.kv.pages_needed(s.seq_id, len(s.prompt) + 1)
+            shared = self.prefix.match(s.prompt) if self.prefix is not None else []
+            need = (len(s.prompt) + 1 + e.page_size - 1) // e.page_size - len(shared)
+            if need > self.kv.allocator.free_pages and self.prefix is not None:
+                freed = self.prefix.evict(need - self.kv.allocator.free_pages)
+                self.kv.allocator.free(freed)
             if need > self.kv.allocator.free_pages:
+                if self.prefix is not None:
+                    self.prefix.release(shared)
                 self._publish_demand(need - self.kv.allocator.free_pages, s)
                 break
             self._publish_demand(0, None)
             self.waiting.popleft()
+            if shared:
+                self.kv.tables[s.seq_id] = list(shared)   # read-only prefix pages come first
+                s.computed = len(shared) * e.page_size
+                s.shared_pages = list(shared)
             self.kv.ensure(s.seq_id, len(s.prompt) + 1)
             self.prefilling.append(s)
-            n = min(len(s.prompt), budget)
+            n = min(len(s.prompt) - s.computed, budget)
             chosen.append((s, n))
             budget -= n
         return chosen, e.prefill_chunk - budget
@@ -382,6 +398,10 @@ class AttentionEngine:
         for i, (s, n) in enumerate(chosen):
             s.computed += n
             if s.prefill_done:
+                if self.prefix is not None:
+                    # full prompt pages become shareable; the sequence keeps them pinned while it runs
+                    taken = self.prefix.insert(s.prompt, self.kv.tables[s.seq_id])
+                    s.shared_pages = list(getattr(s, "shared_pages", [])) + taken
                 tok = int(th[i])
                 s.generated.append(tok)
                 s.first_token_time = now
@@ -394,9 +414,21 @@ class AttentionEngine:
                     self.running.append(s)
         return out
 
+    def _release_pages(self, s: Sequence) -> None:
+        """Returns the sequence's private pages to the allocator; pages of the prefix cache are only unpinned."""
+        shared = getattr(s, "shared_pages", None)
+        if self.prefix is not None and shared:
+            keep = set(shared)
+            t = self.kv.tables.pop(s.seq_id, [])
+            self.kv.allocator.free([p for p in t if p not in keep])
+            self.prefix.release(shared)
+            s.shared_pages = []
+        else:
+            self.kv.release(s.seq_id)
+
     def _finish(self, s: Sequence, now: float) -> None:
         s.finish_time = now
-        self.kv.release(s.seq_id)
+        self._release_pages(s)
 
     def _decode_prepare(self) -> tuple[list[Sequence], int] | None:
         """Fills the pinned decode metadata for the next step. When the batch membership did not
@@ -512,7 +544,7 @@ class AttentionEngine:
         """Gives the sequence's pages back and queues it for recomputation (prompt + generated)."""
         self.running.remove(s)
         self._b_key = None  # the cached decode batch no longer matches
-        self.kv.release(s.seq_id)
+        self._release_pages(s)
         s.prompt = s.prompt + s.generated
         s.max_new_tokens -= len(s.generated)
         s.generated = []

@@ -101,3 +101,28 @@ def test_loopback_engine_serves_a_moe_model(graph):
         toks, ref_logits = ref.generate(torch.tensor(p, device="cuda"), 5)
         assert len(s.generated) == 5
         assert _kl(ref_logits[:1], first_logits[s.seq_id][None]).item() <= 0.05
+
+
+def test_prefix_cache_reuses_prompt_pages_and_keeps_results():
+    cfg, eng, ref = _build("Qwen/Qwen3-0.6B", layers=2, max_batch=8, prefill_chunk=256, max_seq_len=512, prefix_cache=True)
+    eng.warmup()
+    g = torch.Generator().manual_seed(5)
+    system = torch.randint(0, cfg.vocab_size, (70,), generator=g).tolist()      # 4 full pages + 6 tokens
+    tails = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 30)]
+    first = eng.generate([system + tails[0]], 4)[0]
+    free_after_first = eng.kv.allocator.free_pages
+    assert eng.prefix.stats()["pages"] == 4 and eng.prefix.stats()["hits"] == 0     # 79 tokens: 4 full pages
+    seq = eng.add_request(system + tails[1], 4)
+    logits = []
+    while eng.has_work:
+        for i, (s, _) in enumerate(eng.step()):
+            logits.append(eng.logits[i].float().clone())
+    st = eng.prefix.stats()
+    assert st["hits"] == 1 and st["hit_tokens"] == 64
+    toks, ref_logits = ref.generate(torch.tensor(system + tails[1], device="cuda"), 4)
+    assert _kl(ref_logits[:1], logits[0][None]).item() <= 0.05
+    assert seq.generated[0] == toks[0]
+    assert eng.generate([system + tails[0]], 4)[0] == first          # served from the cache, same tokens
+    assert eng.kv.allocator.free_pages <= free_after_first             # cached pages stay resident
+    from crosspool_b200.ops import gemm
+    gemm.check_status(eng.device)
