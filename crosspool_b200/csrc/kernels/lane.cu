@@ -540,7 +540,7 @@ extern "C" void xp_lane_destroy(void* h) {
 }
 
 extern "C" int xp_signal_flags(const XpSignalArgs* a, void* stream) {
-  if (a->n < 1 || a->n > 8 || a->seq_counter == nullptr) return -1;
+  if (a->n < 0 || a->n > 8 || a->seq_counter == nullptr) return -1;  // n == 0: advance the counter only
   lane::signal_flags_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*a);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);

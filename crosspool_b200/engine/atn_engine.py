@@ -97,6 +97,12 @@ class FfnPort:
         return {}
 
 
+def _parts_kw(parts) -> dict:
+    """FFN outputs as add-RMSNorm arguments: a list of local tensors, or (for a port whose result lives
+    in another GPU's memory) a dict with ``part_ptrs`` and ``part_shape``."""
+    return parts if isinstance(parts, dict) else dict(parts=parts)
+
+
 class AttentionEngine:
     def __init__(self, cfg: ModelConfig, weights: AttentionWeights, port: FfnPort, ecfg: EngineConfig | None = None,
                  device: str | torch.device = "cuda", kv: PagedKvCache | None = None, tp=None):
@@ -225,7 +231,8 @@ class AttentionEngine:
             if parts is None:
                 norm.add_rmsnorm([resid], lw.input_norm, cfg.rms_norm_eps, out=x)
             else:
-                norm.add_rmsnorm(parts, lw.input_norm, cfg.rms_norm_eps, resid=resid, out=x, **self.port.wait_args())
+                norm.add_rmsnorm(weight=lw.input_norm, eps=cfg.rms_norm_eps, resid=resid, out=x, **_parts_kw(parts),
+                                 **self.port.wait_args())
             gemm.linear(x, lw.qkv, out=self.qkv[:rows], bias=lw.qkv_bias)
             attn_fn(l, lw, rows)
             tgt = self.port.publish_targets(l, rows, mode)
@@ -248,7 +255,8 @@ class AttentionEngine:
     def _head(self, rows: int, n_sel: int, sel_idx: torch.Tensor | None) -> None:
         """Final norm, row selection, LM head, greedy sampling into ``self.tokens[:n_sel]``."""
         cfg = self.cfg
-        norm.add_rmsnorm(self._parts, self.w.final_norm, cfg.rms_norm_eps, resid=self.resid[:rows], out=self.x[:rows],
+        norm.add_rmsnorm(weight=self.w.final_norm, eps=cfg.rms_norm_eps, resid=self.resid[:rows], out=self.x[:rows],
+                         **_parts_kw(self._parts),
                          **self.port.wait_args())
         if sel_idx is None:
             hsel = self.x[:n_sel]

@@ -92,6 +92,11 @@ class InstancePlacement:
     ffn_ranks: tuple[int, ...]
     capacity_rows: int
     moe_parallel: str = "ep"  # how MoE layers use the FFN ranks: "ep" (experts split) or "tp" (every expert split)
+    atn_tp_followers: tuple[int, ...] = ()  # further ranks of the Instance's attention TP group (atn_rank is rank 0)
+
+    @property
+    def atn_tp_ranks(self) -> tuple[int, ...]:
+        return (self.atn_rank,) + tuple(self.atn_tp_followers)
 
     @property
     def tp(self) -> int:
@@ -124,7 +129,7 @@ class Topology:
     instances: list[InstancePlacement]
 
     def atn_ranks(self) -> list[int]:
-        return sorted({i.atn_rank for i in self.instances})
+        return sorted({r for i in self.instances for r in i.atn_tp_ranks})
 
     def ffn_ranks(self) -> list[int]:
         return sorted({r for i in self.instances for r in i.ffn_ranks})
@@ -186,6 +191,44 @@ class FabricFfnPort(FfnPort):
         native.check(native.kernels().xp_wait_flags(C.byref(self._wait), torch.cuda.current_stream(self.device).cuda_stream),
                      "xp_wait_flags")
         return [p[:rows] for p in self.parts]
+
+
+class FabricFfnFollowerPort(FfnPort):
+    """FFN port of an attention TP rank other than the first. Rank 0 of the TP group publishes the
+    hidden states (all ranks hold identical copies) and owns the completion records and partial
+    buffers; a follower keeps its own invocation counter in step, waits on rank 0's completion words
+    over NVLink and lets its add-RMSNorm read the partials from rank 0's memory."""
+
+    def __init__(self, place: InstancePlacement, atn0_base: int, device):
+        self.place, self.device = place, torch.device(device)
+        self.alay = atn_slot_layout(place)
+        tp = place.tp
+        self.part_ptrs = [atn0_base + self.alay.output_offset + r * self.alay.output_stride for r in range(tp)]
+        self.seq = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._bump = native.SignalArgs()
+        self._bump.n, self._bump.seq_counter = 0, self.seq.data_ptr()
+        self._wait = native.WaitArgs()
+        for r in range(tp):
+            self._wait.flags[r] = atn0_base + self.alay.completion_offset + r * RECORD_BYTES + COMPLETION_SEQ_OFFSET
+        self._wait.n, self._wait.want_ptr, self._wait.wait_ns = tp, self.seq.data_ptr(), 5_000_000_000
+
+    def attach(self, engine: AttentionEngine) -> None:
+        from ..ops.gemm import scratch
+
+        if engine.cap > self.place.capacity_rows:
+            raise ValueError("engine row capacity exceeds the fabric slot capacity")
+        self._wait.status = scratch(self.device).status.data_ptr()
+
+    def publish_targets(self, layer: int, rows: int, mode: int) -> dict | None:
+        return None
+
+    def run(self, layer: int, x: torch.Tensor, rows: int, mode: int) -> dict:
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        k = native.kernels()
+        native.check(k.xp_signal_flags(C.byref(self._bump), s), "xp_signal_flags")
+        native.check(k.xp_wait_flags(C.byref(self._wait), s), "xp_wait_flags")
+        h = self.place.cfg.hidden_size
+        return dict(parts=[], part_ptrs=self.part_ptrs, part_shape=(rows, h, h))
 
 
 # ------------------------------------------------------------------ FFN side
@@ -393,6 +436,7 @@ def build_rank(topo: Topology, rank: int, device, ecfg_for: dict[str, EngineConf
     ctx = RankContext(rank, role)
     mine: dict[str, bytes] = {}
     atn_local: dict[str, PeerBuffer] = {}
+    tp_groups: dict = {}
     if role == "ffn":
         ctx.ffn = FfnRankRuntime(device, n_lanes=n_lanes, policy=policy, tile_weights=tile_weights)
         for p in topo.instances:
@@ -400,12 +444,20 @@ def build_rank(topo: Topology, rank: int, device, ecfg_for: dict[str, EngineConf
                 st = ctx.ffn.add_instance(p, p.ffn_ranks.index(rank))
                 mine[f"ffn:{p.model_id}:{rank}"] = st.slot.handle()
     elif role == "atn":
+        from . import atn_tp
+
         for p in topo.instances:
             if p.atn_rank == rank:
                 buf = PeerBuffer(atn_slot_layout(p).total_bytes)
                 atn_local[p.model_id] = buf
                 ctx.buffers.append(buf)
                 mine[f"atn:{p.model_id}"] = buf.handle()
+            if rank in p.atn_tp_ranks and len(p.atn_tp_ranks) > 1:
+                e = ecfg_for[p.model_id]
+                g = atn_tp.TpGroup(p.atn_tp_ranks.index(rank), len(p.atn_tp_ranks), max(e.max_batch, e.prefill_chunk),
+                                   p.cfg.hidden_size, device)
+                tp_groups[p.model_id] = g
+                mine[f"tp:{p.model_id}:{g.rank}"] = g.handle()
     gathered: list[dict] = [None] * topo.world_size
     dist.all_gather_object(gathered, mine, group=group)
     handles = {k: v for d in gathered for k, v in d.items()}
@@ -414,12 +466,22 @@ def build_rank(topo: Topology, rank: int, device, ecfg_for: dict[str, EngineConf
             st.atn_base = PeerBuffer.open(handles[f"atn:{st.place.model_id}"])
         ctx.ffn.install()
     elif role == "atn":
+        from . import atn_tp
+
         for p in topo.instances:
-            if p.atn_rank != rank:
+            if rank not in p.atn_tp_ranks:
                 continue
-            bases = [PeerBuffer.open(handles[f"ffn:{p.model_id}:{r}"]) for r in p.ffn_ranks]
-            port = FabricFfnPort(p, atn_local[p.model_id], bases, device)
+            if p.atn_rank == rank:
+                bases = [PeerBuffer.open(handles[f"ffn:{p.model_id}:{r}"]) for r in p.ffn_ranks]
+                port = FabricFfnPort(p, atn_local[p.model_id], bases, device)
+            else:
+                port = FabricFfnFollowerPort(p, PeerBuffer.open(handles[f"atn:{p.model_id}"]), device)
             aw = random_attention_weights(p.cfg, p.seed, device, torch.bfloat16)
-            ctx.engines[p.model_id] = AttentionEngine(p.cfg, aw, port, ecfg_for[p.model_id], device)
+            cfg_local, tp = p.cfg, tp_groups.get(p.model_id)
+            if tp is not None:
+                tp.connect([handles[f"tp:{p.model_id}:{r}"] for r in range(tp.size)])
+                aw = atn_tp.shard_attention_weights(aw, p.cfg, tp.rank, tp.size)
+                cfg_local = atn_tp.local_config(p.cfg, tp.size)
+            ctx.engines[p.model_id] = AttentionEngine(cfg_local, aw, port, ecfg_for[p.model_id], device, tp=tp)
     dist.barrier(group=group)
     return ctx

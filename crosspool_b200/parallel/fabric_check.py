@@ -21,6 +21,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--model", default="Qwen/Qwen3-0.6B")
     ap.add_argument("--lanes", type=int, default=1)
+    ap.add_argument("--atn-tp", type=int, default=1, help="attention TP ranks (ranks 0 .. atn_tp - 1); FFN ranks follow")
     args = ap.parse_args()
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -36,10 +37,11 @@ def main() -> int:
     from crosspool_b200.ops import gemm
     from crosspool_b200.parallel import fabric as F
 
-    assert world >= 1 + args.tp
+    assert world >= args.atn_tp + args.tp
     cfg = mc.preset(args.model).with_layers(args.layers)
     ecfg = EngineConfig(max_batch=8, prefill_chunk=128, max_seq_len=256)
-    place = F.InstancePlacement("m0", cfg, seed=3, atn_rank=0, ffn_ranks=tuple(range(1, 1 + args.tp)), capacity_rows=128)
+    place = F.InstancePlacement("m0", cfg, seed=3, atn_rank=0, ffn_ranks=tuple(range(args.atn_tp, args.atn_tp + args.tp)),
+                                capacity_rows=128, atn_tp_followers=tuple(range(1, args.atn_tp)))
     topo = F.Topology(world, [place])
     ctx = F.build_rank(topo, rank, f"cuda:{local}", {"m0": ecfg}, group=ctl, n_lanes=args.lanes)
     ok = True

@@ -36,3 +36,7 @@ def test_moe_model_through_lanes_on_one_ffn_rank():
 
 def test_moe_expert_parallel_over_two_ffn_ranks():
     _run(3, ["--tp", "2", "--model", "tiny-qwen3-moe", "--layers", "2"])
+
+
+def test_attention_tp_pair_with_a_remote_ffn_rank():
+    _run(3, ["--atn-tp", "2", "--tp", "1"])
