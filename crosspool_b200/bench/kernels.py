@@ -111,6 +111,26 @@ def bench_decode_attn(ns, timer: Timer) -> dict:
                   {"batch": B, "tokens": sum(lens), "splits": splits, "chunk_tokens": chunk})
 
 
+def bench_prefill_attn(ns, timer: Timer) -> dict:
+    """Causal prefill attention of ``--seqs`` prompts of ``--len`` tokens each (no cached context)."""
+    from ..ops import attention as A
+
+    S, L, hq, hkv, d, page = ns.seqs, ns.len, ns.q_heads, ns.kv_heads, ns.head_dim, 16
+    blocks = (L + page - 1) // page
+    table = torch.arange(S * blocks, dtype=torch.int32, device="cuda").view(S, blocks)
+    kc = torch.randn(S * blocks, page, hkv, d, device="cuda").bfloat16()
+    vc = torch.randn(S * blocks, page, hkv, d, device="cuda").bfloat16()
+    q = torch.randn(S * L, hq, d, device="cuda").bfloat16()
+    q_starts = (torch.arange(S, device="cuda", dtype=torch.int32) * L).contiguous()
+    q_lens = torch.full((S,), L, dtype=torch.int32, device="cuda")
+    ctx = torch.zeros(S, dtype=torch.int32, device="cuda")
+    out = torch.empty_like(q)
+    us = timer(lambda: A.paged_prefill(q, kc, vc, table, q_starts, q_lens, ctx, L, out=out))
+    flops = 4.0 * S * (L * (L + 1) / 2) * hq * d          # QK^T and PV over the causal half
+    byts = (q.numel() + out.numel() + kc.numel() + vc.numel()) * 2
+    return report("paged_prefill_attention", us, byts, flops, {"seqs": S, "len": L, "q_heads": hq, "kv_heads": hkv})
+
+
 def bench_norm(ns, timer: Timer) -> dict:
     from ..ops import norm
 
@@ -208,6 +228,12 @@ def main(argv: list[str] | None = None) -> int:
     a.add_argument("--min-len", type=int, default=128)
     a.add_argument("--max-len", type=int, default=2048)
     a.add_argument("--chunk", type=int, default=-1, help="KV slice length (-1: the planner's choice, 0: even split)")
+    pa = sub.add_parser("prefill-attn")
+    pa.add_argument("--seqs", type=int, default=4)
+    pa.add_argument("--len", type=int, default=1024)
+    pa.add_argument("--q-heads", type=int, default=16)
+    pa.add_argument("--kv-heads", type=int, default=8)
+    pa.add_argument("--head-dim", type=int, default=128)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=256)
     n.add_argument("--hidden", type=int, default=1024)
@@ -222,7 +248,7 @@ def main(argv: list[str] | None = None) -> int:
     ns = ap.parse_args(argv)
     timer = Timer(ns.iters, ns.warmup, not ns.no_flush)
     {"gemm": bench_gemm, "decode-attn": bench_decode_attn, "norm": bench_norm, "moe": bench_moe,
-     "decode-step": bench_decode_step}[ns.case](ns, timer)
+     "decode-step": bench_decode_step, "prefill-attn": bench_prefill_attn}[ns.case](ns, timer)
     return 0
 
 
