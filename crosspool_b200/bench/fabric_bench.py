@@ -53,7 +53,11 @@ def main(args) -> int:
             placements.append(F.InstancePlacement(model_id, cfg, seed=j, atn_rank=a, ffn_ranks=ffn, capacity_rows=cap))
             j += 1
     topo = F.Topology(world, placements)
-    ctx = F.build_rank(topo, rank, f"cuda:{local}", ecfgs, group=ctl, n_lanes=args.lanes, policy=rt.POLICY_FIFO)
+    policy = {"fifo": rt.POLICY_FIFO, "random": rt.POLICY_RANDOM, "slo": rt.POLICY_SLO}[getattr(args, "policy", "fifo")]
+    ctx = F.build_rank(topo, rank, f"cuda:{local}", ecfgs, group=ctl, n_lanes=args.lanes, policy=policy)
+    if policy == rt.POLICY_SLO:
+        for eng in ctx.engines.values():
+            eng.port.slo_tbt_ms = 50.0
     if ctx.role == "ffn":
         ctx.ffn.start(lease_ms=20.0)
     dist.barrier(group=ctl)

@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 18
+#define XP_ABI_VERSION 19
 
 #ifdef __cplusplus
 extern "C" {
@@ -78,6 +78,7 @@ typedef struct XpNormArgs {
   uint32_t wait_seq, publish_seq, meta_layer, meta_mode, meta_deadline_us;
   float eps;
   uint32_t* seq_counter;       /* optional device word: publish value = *seq_counter + 1, stored back */
+  const uint32_t* meta_deadline_ptr; /* optional device word overriding meta_deadline_us (refreshed per step) */
 } XpNormArgs;
 
 /* Attention side: wait (bounded) until each flag reaches *want_ptr (or `want`). */

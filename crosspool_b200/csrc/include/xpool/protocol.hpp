@@ -23,7 +23,7 @@
 
 namespace xpool {
 
-constexpr uint32_t kAbiVersion = 18;
+constexpr uint32_t kAbiVersion = 19;
 constexpr uint64_t kAllocationAlignment = 256;  // every arena region
 constexpr uint64_t kPayloadAlignment = 16;      // every payload row
 
@@ -82,7 +82,7 @@ struct alignas(256) InvocationRecord {
   uint32_t rows;            // live payload rows
   uint32_t layer_ordinal;   // index into the instance's layer table
   uint32_t forward_mode;    // ForwardMode
-  uint32_t deadline_us;     // SLO deadline, microseconds on the device timer (mod 2^32)
+  uint32_t deadline_us;     // SLO deadline: microseconds of the host's monotonic clock mod 2^32; 0 = none
   uint32_t output_requirement;
   uint32_t dp_row_layout;
   uint32_t reserved[2];

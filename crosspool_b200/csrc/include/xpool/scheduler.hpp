@@ -97,13 +97,30 @@ class Scheduler {
     bool found = false;
     uint32_t best = 0;
     uint64_t best_key = 0, best_ticket = 0;
+    // Deadlines arrive as 32-bit microsecond stamps that wrap; they are ordered relative to the first
+    // queued entry (valid while all queued deadlines lie within 35 minutes of one another). A zero
+    // deadline means "none" and sorts last.
+    bool have_ref = false;
+    uint32_t ref = 0;
     for (uint32_t i = 0; i < n_; ++i) {
       const SchedulerEntry& e = entries_[i];
       if (e.state != static_cast<uint32_t>(EntryState::Queued)) continue;
       uint64_t key;
       switch (policy_.kind) {
         case SchedulerPolicyKind::Random: key = splitmix64(policy_.seed ^ e.ticket); break;
-        case SchedulerPolicyKind::Slo: key = e.deadline; break;
+        case SchedulerPolicyKind::Slo: {
+          const uint32_t dl = static_cast<uint32_t>(e.deadline);
+          if (dl == 0) {
+            key = ~0ull;
+          } else {
+            if (!have_ref) {
+              have_ref = true;
+              ref = dl;
+            }
+            key = static_cast<uint64_t>(static_cast<int64_t>(static_cast<int32_t>(dl - ref)) + (1ll << 32));
+          }
+          break;
+        }
         default: key = e.ticket; break;
       }
       if (!found || key < best_key || (key == best_key && e.ticket < best_ticket)) {

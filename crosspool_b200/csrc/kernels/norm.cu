@@ -163,7 +163,7 @@ norm_publish_kernel(XpNormArgs a) {
             a.peer_meta[d][0] = static_cast<uint32_t>(gridDim.x);
             a.peer_meta[d][1] = a.meta_layer;
             a.peer_meta[d][2] = a.meta_mode;
-            a.peer_meta[d][3] = a.meta_deadline_us;
+            a.peer_meta[d][3] = a.meta_deadline_ptr != nullptr ? *a.meta_deadline_ptr : a.meta_deadline_us;
           }
           sm100::st_release_sys(a.peer_flags[d], seq);
         }

@@ -566,6 +566,10 @@ class AttentionEngine:
         self._pending: list[tuple[Sequence, int]] | None = None
         if self.capacity is not None:
             self._capacity_tick()
+        begin = getattr(self.port, "begin_step", None)
+        if begin is not None:
+            with torch.cuda.stream(self.stream):
+                begin()
         want_prefill = bool(self.waiting or self.prefilling)
         if want_prefill and (not self.running or not self._last_was_prefill):
             chosen, rows = self._admit_prefill()

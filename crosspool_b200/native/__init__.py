@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 18
+EXPECTED_ABI = 19
 HERE = Path(__file__).resolve().parent
 
 
@@ -108,6 +108,7 @@ class NormArgs(C.Structure):
         ("meta_deadline_us", C.c_uint32),
         ("eps", C.c_float),
         ("seq_counter", C.c_void_p),
+        ("meta_deadline_ptr", C.c_void_p),
     ]
 
 

@@ -35,8 +35,8 @@ def add_rmsnorm(parts: Sequence[torch.Tensor] | torch.Tensor, weight: torch.Tens
                 publish_seq: int = 0, wait_flag_ptrs: Sequence[int] = (), wait_seq: int = 0,
                 wait_ns: int = 5_000_000_000, meta: tuple[int, int, int] = (0, 0, 0),
                 want_local: bool = True, seq_counter_ptr: int = 0,
-                part_ptrs: Sequence[int] | None = None, part_shape: tuple[int, int, int] | None = None
-                ) -> torch.Tensor | None:
+                part_ptrs: Sequence[int] | None = None, part_shape: tuple[int, int, int] | None = None,
+                deadline_ptr: int = 0) -> torch.Tensor | None:
     """``y = rmsnorm(sum(parts) + resid) * weight``; ``resid`` is updated in place.
 
     ``parts`` are bf16 ``[rows, hidden]`` tensors summed in list order. Parts that live in another
@@ -83,6 +83,7 @@ def add_rmsnorm(parts: Sequence[torch.Tensor] | torch.Tensor, weight: torch.Tens
     a.meta_layer, a.meta_mode, a.meta_deadline_us = meta
     a.eps = eps
     a.seq_counter = seq_counter_ptr or None
+    a.meta_deadline_ptr = deadline_ptr or None
     native.check(native.kernels().xp_norm_publish(C.byref(a), torch.cuda.current_stream(dev).cuda_stream),
                  "xp_norm_publish")
     return out

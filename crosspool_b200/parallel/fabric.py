@@ -166,6 +166,11 @@ class FabricFfnPort(FfnPort):
         self.done_flags = [local.ptr + self.alay.completion_offset + r * RECORD_BYTES + COMPLETION_SEQ_OFFSET
                            for r in range(tp)]
         self.seq = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # SLO deadline of the step in flight (microseconds of the monotonic host clock mod 2^32, 0 = none);
+        # the norm kernel copies it into every invocation record, the FFN Lanes' SLO policy orders by it
+        self.slo_tbt_ms = 0.0
+        self.deadline = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._deadline_host = torch.zeros(4, dtype=torch.int32).pin_memory()
         self.wait_ns = 5_000_000_000  # the reference's device wait limit (utils/wait.cuh:17-19)
         self._wait = native.WaitArgs()
         for r, f in enumerate(self.done_flags):
@@ -181,8 +186,20 @@ class FabricFfnPort(FfnPort):
             raise ValueError("engine row capacity exceeds the fabric slot capacity")
         self._wait.status = scratch(self.device).status.data_ptr()
 
+    def begin_step(self, now_s: float | None = None) -> None:
+        """Stamps the step's deadline (call before launching the step; a 16-byte pinned copy)."""
+        if self.slo_tbt_ms <= 0:
+            return
+        import time
+
+        now = time.monotonic() if now_s is None else now_s
+        us = int((now + self.slo_tbt_ms / 1e3) * 1e6) & 0xFFFFFFFF
+        self._deadline_host[0] = (us or 1) - (1 << 32) if (us or 1) >= (1 << 31) else (us or 1)
+        self.deadline.copy_(self._deadline_host, non_blocking=True)
+
     def publish_targets(self, layer: int, rows: int, mode: int) -> dict:
-        return dict(peer_ptrs=[b + self.flay.input_offset for b in self.ffn_bases],
+        return dict(deadline_ptr=self.deadline.data_ptr(),
+                    peer_ptrs=[b + self.flay.input_offset for b in self.ffn_bases],
                     peer_flag_ptrs=[b + self.flay.record_offset + RECORD_SEQ_OFFSET for b in self.ffn_bases],
                     peer_meta_ptrs=[b + self.flay.record_offset for b in self.ffn_bases],
                     seq_counter_ptr=self.seq.data_ptr(), meta=(layer, mode, 0))

@@ -131,6 +131,7 @@ class AtnBackend:
     def prepare_execution(self, plan: FabricPlan) -> None:
         for (model_id, rank), place in self.places.items():
             port = F.FabricFfnPort(place, self.buffers[(model_id, rank)], self._bases[(model_id, rank)], self.cuda)
+            port.slo_tbt_ms = self.cfg.slo_for(model_id).tbt_ms   # per-step deadline for the Lanes' SLO policy
             aw = random_attention_weights(place.cfg, place.seed, self.cuda, torch.bfloat16)
             self.engines[model_id] = AttentionEngine(place.cfg, aw, port, self.ecfg, self.cuda)
 

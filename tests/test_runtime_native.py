@@ -68,6 +68,18 @@ def test_scheduler_slo_earliest_deadline_first_and_random_is_seeded():
         order.append(i)
         s.release(i, lease)
     assert order == [1, 2, 0]
+    # 32-bit microsecond stamps that wrap are ordered relative to one another; zero means "no deadline"
+    w = rt.LaneScheduler(4, 1, rt.POLICY_SLO)
+    w.enqueue(0, 1, deadline=0)
+    w.enqueue(1, 1, deadline=50)               # wrapped: 150 us after instance 2's stamp
+    w.enqueue(2, 1, deadline=2**32 - 100)
+    w.enqueue(3, 1, deadline=2**32 - 5000)
+    order = []
+    for _ in range(4):
+        i, lane, lease = w.try_schedule()
+        order.append(i)
+        w.release(i, lease)
+    assert order == [3, 2, 1, 0]
 
     def run(seed):
         r = rt.LaneScheduler(8, 1, rt.POLICY_RANDOM, seed)
