@@ -27,12 +27,12 @@ def _make(cfgs, n_lanes=1, policy=0, tile=False, cap=128):
     return ffn, places, atn
 
 
-def _publish(F, st, place, x, layer, seq, mode=2):
+def _publish(F, st, place, x, layer, seq, mode=2, deadline=0):
     flay = F.ffn_slot_layout(place)
     rows = x.shape[0]
     st.slot.tensor(flay.input_offset, (place.capacity_rows, place.cfg.hidden_size), torch.bfloat16, "cuda")[:rows] = x
     rec = st.slot.tensor(flay.record_offset, (64,), torch.int32, "cuda")
-    rec[0], rec[1], rec[2], rec[3] = rows, layer, mode, 0
+    rec[0], rec[1], rec[2], rec[3] = rows, layer, mode, deadline
     rec[8] = seq  # InvocationRecord.sequence
     torch.cuda.synchronize()
 
@@ -231,3 +231,24 @@ def test_expert_parallel_lane_partials_fold_to_the_full_moe_output():
         for ffn in rts:
             ffn.close()
         buf.free()
+
+
+def test_slo_policy_serves_the_earliest_deadline_first():
+    from crosspool_b200 import devkit
+    from crosspool_b200.native import runtime as rt
+    from crosspool_b200.parallel import fabric as F
+
+    ffn, places, atn = _make([("Qwen/Qwen3-0.6B", 1)] * 3, policy=rt.POLICY_SLO)
+    try:
+        ffn.enable_trace(64)
+        for i, dl in enumerate((9000, 0, 100)):          # instance 1 carries no deadline: it goes last
+            x = (torch.randn(2, places[i].cfg.hidden_size, device="cuda") * 0.5).bfloat16()
+            _publish(F, ffn.instances[i], places[i], x, 0, 1, deadline=dl)
+        for _ in range(3):
+            ffn.launch_once(0, lease_ms=20)
+        torch.cuda.synchronize()
+        ev = devkit.FabricObserver(ffn).collect().events
+        assert [e["instance"] for e in ev if e["name"] == "admitted"] == [2, 0, 1]
+        assert ffn.stats()["served"] == [1, 1, 1] and ffn.stats()["status"] == 0
+    finally:
+        ffn.close()
