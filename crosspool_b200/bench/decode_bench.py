@@ -197,12 +197,15 @@ def result_json(args, cfg: ModelConfig, n_gpus: int, parallelism: str, n_instanc
                 dev_ms: float, e2e_s: float, e2e_tokens: int, step_ms: list[float], ttft_ms: list[float],
                 h2d: int, d2h: int, launches: int, clocks: dict, extra_config: dict | None = None) -> dict:
     K = args.steps
+    tpot_p99 = percentile(step_ms, 99)
     cfgd = {"model": f"{n_instances}x {args.model} co-located", "global_batch": tokens_per_step,
+            "phase": "steady-state decode, every Instance at its full running batch",
+            "slo": {"tpot_p99_ms_limit": 50.0, "tpot_p99_ms": tpot_p99, "met": bool(tpot_p99 <= 50.0)},
             "seq_len": f"prompt {args.min_prompt}-{args.max_prompt} + decode", "parallelism": parallelism,
             "layers": cfg.num_layers, "l2": "weights and KV streamed per step exceed the 126 MB L2 (no flush needed)"}
     cfgd.update(extra_config or {})
     return {
-        "metric": "aggregate output tok/s across co-located models (steady-state decode)",
+        "metric": "aggregate output tok/s across co-located models at p99 TPOT SLO; p50 TTFT",
         "value": tokens_per_step * K / (dev_ms / 1e3),
         "unit": "tok/s",
         "n_gpus": n_gpus,
