@@ -62,7 +62,20 @@ def cmd_daemon_serve(ns) -> int:
     cfg = _load(ns)
     init_logging("Daemon", cfg.logging_level, cfg.logging_color)
     cp = ControlPlane(cfg)
-    app = create_app(cfg, cp)
+    factory = None
+    if cfg.atn_elastic_kv:
+        from ..service.daemon.ecs_service import EcsService
+
+        holder = {}
+
+        def factory(control):
+            return EcsService(control, lambda ref: setattr(holder["app"].state, "ecs_channel_ref", ref) if "app" in holder else None,
+                              utilization=cfg.atn_device_memory_utilization)
+
+        app = create_app(cfg, cp, ecs_factory=factory)
+        holder["app"] = app
+    else:
+        app = create_app(cfg, cp)
     uvicorn.run(app, host=cfg.daemon_host, port=cfg.daemon_port, log_level="warning")
     return cp.exit_code
 

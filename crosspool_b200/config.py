@@ -160,6 +160,8 @@ CONFIG_REGISTRY: tuple[ConfigSetting, ...] = (
     ConfigSetting("vendor_model_base_uri", ("vendor", "model_base_uri"), str, ""),
     ConfigSetting("atn_devices", ("atn", "devices"), _devices, required=True),
     ConfigSetting("atn_device_memory_utilization", ("atn", "device_memory_utilization"), _float(0.05, 1.0), 0.95),
+    ConfigSetting("atn_elastic_kv", ("atn", "elastic_kv"), _bool, False, env_var="XPOOL_ATN_ELASTIC_KV",
+                  description="back the KV caches with VMM bundles lent between co-located Instances"),
     ConfigSetting("ffn_devices", ("ffn", "devices"), _devices, required=True),
     ConfigSetting("ffn_device_memory_calibration", ("ffn", "device_memory_calibration"), _bool, False,
                   env_var="XPOOL_FFN_DEVICE_MEMORY_CALIBRATION"),

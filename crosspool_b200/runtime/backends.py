@@ -111,6 +111,9 @@ class AtnBackend:
         self._server = None
         self._listen = listen
         self.listener: ServingListener | None = None
+        self.ecs_ref = None          # callable(generation) -> EcsChannelRef, set by the launcher when elastic KV is on
+        self._ecs_channel = None
+        self._reconcilers = []
 
     def prepare_join(self, plan: FabricPlan) -> dict[str, str]:
         torch.cuda.set_device(self.cuda)
@@ -133,7 +136,51 @@ class AtnBackend:
             port = F.FabricFfnPort(place, self.buffers[(model_id, rank)], self._bases[(model_id, rank)], self.cuda)
             port.slo_tbt_ms = self.cfg.slo_for(model_id).tbt_ms   # per-step deadline for the Lanes' SLO policy
             aw = random_attention_weights(place.cfg, place.seed, self.cuda, torch.bfloat16)
-            self.engines[model_id] = AttentionEngine(place.cfg, aw, port, self.ecfg, self.cuda)
+            kv = self._elastic_cache(plan, model_id, rank, place) if self.cfg.atn_elastic_kv and self.ecs_ref else None
+            eng = AttentionEngine(place.cfg, aw, port, self.ecfg, self.cuda, kv=kv)
+            if kv is not None:
+                self._attach_capacity(eng, model_id, rank)
+            self.engines[model_id] = eng
+        if self._ecs_channel is not None:
+            free, total = torch.cuda.mem_get_info(self.cuda)
+            self._ecs_channel.publish_report(self._ecs_ref.devices[str(self.device)], free, total, 1)
+
+    # ------------------------------------------------------------------ elastic KV
+    def _elastic_cache(self, plan: FabricPlan, model_id: str, rank: int, place):
+        """A KV cache over VMM bundles with one bundle mapped; the Instance rank describes its partition
+        (floor = one bundle, reservation = the whole range) in the daemon's control channel."""
+        import time
+
+        from ..ecs import vmm
+        from ..native.runtime import EcsChannel
+
+        if self._ecs_channel is None:
+            for _ in range(200):                      # the daemon opens the channel on its next policy tick
+                try:
+                    self._ecs_ref = self.ecs_ref(plan.generation)
+                    break
+                except Exception:
+                    time.sleep(0.05)
+            else:
+                raise RuntimeError("the daemon did not publish an ECS control channel")
+            self._ecs_channel = EcsChannel.attach(self._ecs_ref.name)
+            self._driver, self._quota = vmm.Driver.real(), vmm.MemoryQuota(1 << 62)
+        e = self.ecfg
+        max_blocks = (e.max_seq_len + e.page_size - 1) // e.page_size
+        pages = e.num_pages or e.max_batch * max_blocks
+        kv = vmm.elastic_kv_cache(place.cfg, pages, e.page_size, self.cuda, self._driver, self._quota, initial_bundles=1)
+        idx = self._ecs_ref.partitions[f"{model_id}:{rank}"]
+        bb = kv.backing.bundle_bytes
+        self._ecs_channel.set_partition(idx, self.device, 0, rank, bb, kv.backing.bundle_count * bb)
+        return kv
+
+    def _attach_capacity(self, eng, model_id: str, rank: int) -> None:
+        from ..ecs import reconciler as R
+
+        idx = self._ecs_ref.partitions[f"{model_id}:{rank}"]
+        rec = R.CapacityReconciler(eng.kv, self._ecs_channel, idx, gate_factory=lambda e=eng: R.cuda_event_gate(e.stream))
+        eng.attach_capacity(rec, ttft_slo_s=self.cfg.slo_for(model_id).ttft_ms / 1e3)
+        self._reconcilers.append(rec)
 
     def activate(self, plan: FabricPlan) -> None:
         pass  # engines warm up once the whole Fabric is executable (their graphs invoke the FFN tier)

@@ -51,6 +51,8 @@ def run_agent(cfg: XpoolConfig, role: str, device: int) -> int:
                             max_seq_len=int(os.environ.get("XPOOL_MAX_SEQ_LEN", "4096")))
         port = SERVING_BASE_PORT + cfg.atn_devices.index(device)
         backend = AtnBackend(cfg, device, insts, ecfg, capacity_rows=max_rows, local_index=local, listen=("127.0.0.1", port))
+        if cfg.atn_elastic_kv:
+            backend.ecs_ref = client.ecs_channel
         profs = [(m, r, InstanceFfnProfile(max_prefill_rows=ecfg.prefill_chunk, max_decode_rows=ecfg.max_batch,
                                            hidden_size=model_config_for(cfg, m).hidden_size)) for m, r in insts]
         agent = AtnAgent(client, device, backend, profs, owner=owner)

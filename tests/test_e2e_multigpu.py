@@ -33,11 +33,12 @@ ffn_tp_size = 1
 """
 
 
-def test_daemon_agents_serve_requests_and_retire(tmp_path):
+@pytest.mark.parametrize("elastic", [False, True])
+def test_daemon_agents_serve_requests_and_retire(tmp_path, elastic):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     cfgp = tmp_path / "xpool.toml"
-    cfgp.write_text(TOML)
+    cfgp.write_text(TOML.replace("devices = [0]", "devices = [0]\nelastic_kv = true") if elastic else TOML)
     env = dict(os.environ, XPOOL_CONFIG=str(cfgp), PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0", XPOOL_MAX_ROWS="512",
                XPOOL_MAX_BATCH="16", XPOOL_MAX_SEQ_LEN="512")
     xp = [sys.executable, "-m", "crosspool_b200.cli.main"]
