@@ -72,7 +72,8 @@ __global__ void lane_wait_kernel(LaneCtl* ctl, const InstanceSlot* slots, LaneCu
         const InvocationRecord* rec = s.record;
         uint32_t rows = rec->rows, layer = rec->layer_ordinal;
         uint32_t rc = 0;
-        if (rows > static_cast<uint32_t>(s.capacity_rows) || layer >= static_cast<uint32_t>(s.num_layers)) {
+        if (rows > static_cast<uint32_t>(s.capacity_rows) || layer >= static_cast<uint32_t>(s.num_layers) ||
+            s.layers[layer < static_cast<uint32_t>(s.num_layers) ? layer : 0].inter_local == 0) {  // not held here
           rc = static_cast<uint32_t>(ResultCode::ProtocolMismatch);
           rows = 0;
           layer = 0;

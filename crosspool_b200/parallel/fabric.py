@@ -93,14 +93,38 @@ class InstancePlacement:
     capacity_rows: int
     moe_parallel: str = "ep"  # how MoE layers use the FFN ranks: "ep" (experts split) or "tp" (every expert split)
     atn_tp_followers: tuple[int, ...] = ()  # further ranks of the Instance's attention TP group (atn_rank is rank 0)
+    # Layer-split placement: ((first layer, end layer, FFN ranks in TP order), ...) covering all layers, every
+    # group of the same TP size; ``ffn_ranks`` is then the union of the groups. Empty: one group of all layers.
+    layer_groups: tuple[tuple[int, int, tuple[int, ...]], ...] = ()
+
+    def __post_init__(self):
+        if self.layer_groups:
+            sizes = {len(g[2]) for g in self.layer_groups}
+            covered = sorted((g[0], g[1]) for g in self.layer_groups)
+            ok = len(sizes) == 1 and covered[0][0] == 0 and covered[-1][1] == self.cfg.num_layers and \
+                all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+            union = tuple(dict.fromkeys(r for g in self.layer_groups for r in g[2]))
+            if not ok or union != tuple(self.ffn_ranks) or len(union) != sum(len(g[2]) for g in self.layer_groups):
+                raise ValueError("layer groups must tile the layers, share one TP size, use every FFN rank once, "
+                                 "and ffn_ranks must list their ranks in group order")
 
     @property
     def atn_tp_ranks(self) -> tuple[int, ...]:
         return (self.atn_rank,) + tuple(self.atn_tp_followers)
 
+    def groups(self) -> tuple[tuple[int, int, tuple[int, ...]], ...]:
+        return self.layer_groups or ((0, self.cfg.num_layers, tuple(self.ffn_ranks)),)
+
     @property
     def tp(self) -> int:
-        return len(self.ffn_ranks)
+        return len(self.groups()[0][2])
+
+    def locate(self, ffn_rank: int) -> tuple[int, int, int]:
+        """(TP rank, first layer, end layer) of an FFN rank of this Instance."""
+        for lo, hi, ranks in self.groups():
+            if ffn_rank in ranks:
+                return ranks.index(ffn_rank), lo, hi
+        raise LookupError(f"rank {ffn_rank} holds no shard of {self.model_id}")
 
     @property
     def expert_parallel(self) -> bool:
@@ -158,7 +182,9 @@ class FabricFfnPort(FfnPort):
     def __init__(self, place: InstancePlacement, local: PeerBuffer, ffn_bases: list[int], device):
         self.place, self.local, self.device = place, local, torch.device(device)
         self.alay, self.flay = atn_slot_layout(place), ffn_slot_layout(place)
-        self.ffn_bases = ffn_bases  # mapped base pointer of this instance's slot on each TP rank
+        self.ffn_bases = ffn_bases  # mapped base pointer of this instance's slot on every rank of place.ffn_ranks
+        base_of = dict(zip(place.ffn_ranks, ffn_bases))
+        self._group_bases = [(lo, hi, [base_of[r] for r in ranks]) for lo, hi, ranks in place.groups()]
         tp = place.tp
         self.parts = [local.tensor(self.alay.output_offset + r * self.alay.output_stride,
                                    (place.capacity_rows, place.cfg.hidden_size), torch.bfloat16, self.device)
@@ -198,10 +224,11 @@ class FabricFfnPort(FfnPort):
         self.deadline.copy_(self._deadline_host, non_blocking=True)
 
     def publish_targets(self, layer: int, rows: int, mode: int) -> dict:
+        bases = next(b for lo, hi, b in self._group_bases if lo <= layer < hi)   # the TP group that holds this layer
         return dict(deadline_ptr=self.deadline.data_ptr(),
-                    peer_ptrs=[b + self.flay.input_offset for b in self.ffn_bases],
-                    peer_flag_ptrs=[b + self.flay.record_offset + RECORD_SEQ_OFFSET for b in self.ffn_bases],
-                    peer_meta_ptrs=[b + self.flay.record_offset for b in self.ffn_bases],
+                    peer_ptrs=[b + self.flay.input_offset for b in bases],
+                    peer_flag_ptrs=[b + self.flay.record_offset + RECORD_SEQ_OFFSET for b in bases],
+                    peer_meta_ptrs=[b + self.flay.record_offset for b in bases],
                     seq_counter_ptr=self.seq.data_ptr(), meta=(layer, mode, 0))
 
     def run(self, layer: int, x: torch.Tensor, rows: int, mode: int) -> list[torch.Tensor]:
@@ -273,12 +300,18 @@ class FfnRankRuntime:
         self._stop = threading.Event()
         self.errors: list[str] = []
 
-    def add_instance(self, place: InstancePlacement, tp_rank: int) -> FfnInstanceState:
+    def add_instance(self, place: InstancePlacement, tp_rank: int, layers: tuple[int, int] | None = None) -> FfnInstanceState:
+        """``layers``: the half-open layer range this rank holds (layer-split placements); other layers get no
+        weights and an invocation naming them is refused."""
         lay = ffn_slot_layout(place)
         slot = PeerBuffer(lay.total_bytes)
         cfg = place.cfg
+        lo, hi = layers or (0, cfg.num_layers)
         weights = []
         for l in range(cfg.num_layers):
+            if not lo <= l < hi:
+                weights.append(None)
+                continue
             if cfg.layer_is_moe(l) and place.expert_parallel:
                 w = random_ffn_layer(cfg, l, place.seed, self.device, torch.bfloat16, expert_range=place.expert_range(tp_rank))
             else:
@@ -310,6 +343,8 @@ class FfnRankRuntime:
             d.capacity_rows, d.hidden, d.num_layers, d.act_ld = p.capacity_rows, p.cfg.hidden_size, p.cfg.num_layers, act_ld
             native.check(lib.xp_lane_set_instance(self.handle, i, C.byref(d)), "xp_lane_set_instance", 0)
             for l, w in enumerate(st.weights):
+                if w is None:
+                    continue   # held by another layer group: the table entry stays empty
                 gu, dn = w.gate_up, w.down
                 ld = native.LaneLayerDesc()
                 if w.is_moe:
@@ -458,7 +493,8 @@ def build_rank(topo: Topology, rank: int, device, ecfg_for: dict[str, EngineConf
         ctx.ffn = FfnRankRuntime(device, n_lanes=n_lanes, policy=policy, tile_weights=tile_weights)
         for p in topo.instances:
             if rank in p.ffn_ranks:
-                st = ctx.ffn.add_instance(p, p.ffn_ranks.index(rank))
+                tp_rank, lo, hi = p.locate(rank)
+                st = ctx.ffn.add_instance(p, tp_rank, (lo, hi))
                 mine[f"ffn:{p.model_id}:{rank}"] = st.slot.handle()
     elif role == "atn":
         from . import atn_tp

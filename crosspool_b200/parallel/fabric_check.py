@@ -21,6 +21,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--model", default="Qwen/Qwen3-0.6B")
     ap.add_argument("--lanes", type=int, default=1)
+    ap.add_argument("--layer-split", type=int, default=0, help="split the layers over this many FFN groups of --tp ranks each")
     ap.add_argument("--atn-tp", type=int, default=1, help="attention TP ranks (ranks 0 .. atn_tp - 1); FFN ranks follow")
     args = ap.parse_args()
 
@@ -37,11 +38,18 @@ def main() -> int:
     from crosspool_b200.ops import gemm
     from crosspool_b200.parallel import fabric as F
 
-    assert world >= args.atn_tp + args.tp
+    n_groups = max(1, args.layer_split)
+    assert world >= args.atn_tp + args.tp * n_groups
     cfg = mc.preset(args.model).with_layers(args.layers)
     ecfg = EngineConfig(max_batch=8, prefill_chunk=128, max_seq_len=256)
-    place = F.InstancePlacement("m0", cfg, seed=3, atn_rank=0, ffn_ranks=tuple(range(args.atn_tp, args.atn_tp + args.tp)),
-                                capacity_rows=128, atn_tp_followers=tuple(range(1, args.atn_tp)))
+    ffn_ranks = tuple(range(args.atn_tp, args.atn_tp + args.tp * n_groups))
+    groups = ()
+    if n_groups > 1:
+        per = cfg.num_layers // n_groups
+        groups = tuple((g * per, cfg.num_layers if g == n_groups - 1 else (g + 1) * per,
+                        ffn_ranks[g * args.tp:(g + 1) * args.tp]) for g in range(n_groups))
+    place = F.InstancePlacement("m0", cfg, seed=3, atn_rank=0, ffn_ranks=ffn_ranks, capacity_rows=128,
+                                atn_tp_followers=tuple(range(1, args.atn_tp)), layer_groups=groups)
     topo = F.Topology(world, [place])
     ctx = F.build_rank(topo, rank, f"cuda:{local}", {"m0": ecfg}, group=ctl, n_lanes=args.lanes)
     ok = True

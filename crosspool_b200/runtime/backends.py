@@ -33,13 +33,15 @@ def model_config_for(cfg: XpoolConfig, model_id: str):
 
 
 def _placement(cfg: XpoolConfig, plan: FabricPlan, model_id: str, atn_rank: int, capacity_rows: int) -> F.InstancePlacement:
-    shards = sorted((s for s in plan.shards if s.model_id == model_id), key=lambda s: s.tp_rank)
-    if any(s.layer_begin != 0 or s.layer_end != shards[0].layer_end for s in shards):
-        raise NotImplementedError("layer-split placements are planned by the daemon but not routed per layer yet")
+    shards = [s for s in plan.shards if s.model_id == model_id]
+    ranges = sorted({(s.layer_begin, s.layer_end) for s in shards})
+    groups = tuple((lo, hi, tuple(s.pe for s in sorted((x for x in shards if (x.layer_begin, x.layer_end) == (lo, hi)),
+                                                        key=lambda x: x.tp_rank))) for lo, hi in ranges)
     rank = next(r for r in plan.instance_ranks if r.model_id == model_id and r.rank == atn_rank)
     seed = zlib.crc32(model_id.encode()) % 1000  # random-init deployments: same seed on every rank of a model
-    return F.InstancePlacement(model_id, model_config_for(cfg, model_id), seed, rank.pe, tuple(s.pe for s in shards),
-                               capacity_rows)
+    union = tuple(pe for g in groups for pe in g[2])
+    return F.InstancePlacement(model_id, model_config_for(cfg, model_id), seed, rank.pe, union, capacity_rows,
+                               layer_groups=groups if len(groups) > 1 else ())
 
 
 class FfnBackend:
@@ -59,7 +61,8 @@ class FfnBackend:
             place = _placement(self.cfg, plan, r.model_id, r.rank, self.capacity_rows)
             if my_pe not in place.ffn_ranks:
                 continue
-            st = self.rt.add_instance(place, place.ffn_ranks.index(my_pe))
+            tp_rank, lo, hi = place.locate(my_pe)
+            st = self.rt.add_instance(place, tp_rank, (lo, hi))
             self._keys.append((st, f"atn:{r.model_id}:{r.rank}"))
             handles[f"ffn:{r.model_id}:{r.rank}:{my_pe}"] = st.slot.handle().hex()
         return handles

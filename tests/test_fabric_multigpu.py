@@ -40,3 +40,7 @@ def test_moe_expert_parallel_over_two_ffn_ranks():
 
 def test_attention_tp_pair_with_a_remote_ffn_rank():
     _run(3, ["--atn-tp", "2", "--tp", "1"])
+
+
+def test_layer_split_placement_over_two_ffn_ranks():
+    _run(3, ["--tp", "1", "--layer-split", "2"])
