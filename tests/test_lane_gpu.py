@@ -252,3 +252,34 @@ def test_slo_policy_serves_the_earliest_deadline_first():
         assert ffn.stats()["served"] == [1, 1, 1] and ffn.stats()["status"] == 0
     finally:
         ffn.close()
+
+
+def test_a_rank_refuses_layers_of_another_layer_group():
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.parallel import fabric as F
+
+    cfg = mc.preset("Qwen/Qwen3-0.6B").with_layers(2)
+    place = F.InstancePlacement("m", cfg, seed=2, atn_rank=0, ffn_ranks=(1, 2), capacity_rows=64,
+                                layer_groups=((0, 1, (1,)), (1, 2, (2,))))
+    ffn = F.FfnRankRuntime("cuda", n_lanes=1)
+    st = ffn.add_instance(place, *place.locate(2)[:1], place.locate(2)[1:])      # this rank holds layer 1 only
+    buf = F.PeerBuffer(F.atn_slot_layout(place).total_bytes)
+    st.atn_base = buf.ptr
+    ffn.install()
+    try:
+        assert st.weights[0] is None and st.weights[1] is not None
+        x = (torch.randn(4, cfg.hidden_size, device="cuda") * 0.5).bfloat16()
+        _publish(F, st, place, x, 0, 1)
+        ffn.launch_once(0, lease_ms=20)
+        torch.cuda.synchronize()
+        _, rc, nrows, seq = _result(F, buf, place, 4)
+        assert (rc, nrows, seq) == (2, 0, 1)                      # ProtocolMismatch, nothing computed
+        _publish(F, st, place, x, 1, 5)                           # sequence numbers may jump: other groups served 2..4
+        ffn.launch_once(0, lease_ms=20)
+        torch.cuda.synchronize()
+        out, rc, nrows, seq = _result(F, buf, place, 4)
+        assert (rc, nrows, seq) == (0, 4, 5)
+        torch.testing.assert_close(out.float(), _ref(x, st.weights[1]), atol=2e-2, rtol=2e-2)
+    finally:
+        ffn.close()
+        buf.free()
