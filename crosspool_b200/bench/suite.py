@@ -51,6 +51,46 @@ CASES: dict[str, Case] = {c.name: c for c in (
 )}
 
 
+def _length(spec: dict | str) -> S.LengthSpec:
+    """``{kind="uniform", lo=, hi=}`` / ``{kind="lognormal", median=, sigma=, lo=, hi=}`` or the CLI string form."""
+    if isinstance(spec, str):
+        p = spec.split(":")
+        return S.LengthSpec("uniform", int(p[1]), int(p[2])) if p[0] == "uniform" else \
+            S.LengthSpec("lognormal", int(p[3]), int(p[4]), float(p[1]), float(p[2]))
+    if spec.get("kind", "uniform") == "uniform":
+        return S.LengthSpec("uniform", int(spec["lo"]), int(spec["hi"]))
+    return S.LengthSpec("lognormal", int(spec.get("lo", 1)), int(spec["hi"]), float(spec["median"]), float(spec.get("sigma", 1.0)))
+
+
+def load_catalogue(path: str | Path) -> dict[str, Case]:
+    """Cases from a TOML catalogue (the counterpart of the reference's ``benches/benches.toml``):
+
+        [defaults]                      # optional, merged into every case
+        duration_s = 60
+        [cases.small-pair-1rps]
+        rate_per_s = [1.0, 1.0]
+        prompt = {kind = "lognormal", median = 1024, sigma = 1.0, lo = 16, hi = 8192}
+        output = {kind = "uniform", lo = 128, hi = 512}
+    """
+    import tomllib
+
+    doc = tomllib.loads(Path(path).read_text())
+    defaults = doc.get("defaults", {})
+    out = {}
+    for name, raw in doc.get("cases", {}).items():
+        c = {**defaults, **raw}
+        unknown = set(c) - {"rate_per_s", "duration_s", "prompt", "output", "repetitions", "warmup_requests", "burst",
+                            "slo_ttft_ms", "slo_tpot_ms", "base_seed"}
+        if unknown:
+            raise ValueError(f"case {name}: unknown keys {sorted(unknown)}")
+        rates = c["rate_per_s"]
+        out[name] = Case(name, tuple(float(r) for r in (rates if isinstance(rates, list) else [rates])), float(c["duration_s"]),
+                         _length(c["prompt"]), _length(c["output"]), int(c.get("repetitions", 3)),
+                         int(c.get("warmup_requests", 2)), tuple(float(x) for x in c.get("burst", (1.0, 0.0, 0.0))),
+                         float(c.get("slo_ttft_ms", 2000.0)), float(c.get("slo_tpot_ms", 50.0)), int(c.get("base_seed", 0)))
+    return out
+
+
 def seal(doc: dict) -> dict:
     body = {k: v for k, v in doc.items() if k != "seal"}
     doc["seal"] = hashlib.sha256(json.dumps(body, sort_keys=True, separators=(",", ":")).encode()).hexdigest()
@@ -128,9 +168,12 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--out", required=True)
     ap.add_argument("--cases", nargs="*", default=[], help=f"subset of {sorted(CASES)} (default: all but smoke)")
     ap.add_argument("--all", action="store_true")
+    ap.add_argument("--catalogue", default="", help="TOML file with [cases.<name>] tables (adds to the built-in cases)")
     ap.add_argument("--continue", dest="cont", action="store_true")
     ap.add_argument("--rerun-failure", action="store_true")
     ns = ap.parse_args(argv)
+    if ns.catalogue:
+        CASES.update(load_catalogue(ns.catalogue))
     names = ns.cases or [n for n in CASES if n != "smoke"]
     unknown = [n for n in names if n not in CASES]
     if unknown:

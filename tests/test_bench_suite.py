@@ -48,3 +48,13 @@ def test_a_crashing_repetition_is_recorded_and_the_suite_continues(tmp_path):
     assert r.failed == ["smoke/rep0"] and r.ran == ["smoke/rep1"]
     assert "ConnectionError" in json.loads((tmp_path / "smoke" / "rep0" / "repetition.json").read_text())["exception"]
     assert X.main(["--targets", "m=http://x", "--out", str(tmp_path), "--cases", "nope"] ) if False else True
+
+
+def test_toml_catalogue_loads_cases_with_defaults():
+    from pathlib import Path
+
+    cases = X.load_catalogue(Path(__file__).resolve().parent.parent / "configs" / "benches.toml")
+    assert {"pair-1rps", "input-heavy", "bursty-mix"} <= set(cases)
+    c = cases["input-heavy"]
+    assert c.rate_per_s == (2.0, 2.0) and c.prompt.kind == "lognormal" and c.prompt.median == 4096 and c.output.hi == 128
+    assert cases["bursty-mix"].burst == (4.0, 30.0, 120.0) and cases["pair-1rps"].duration_s == 60 and cases["pair-1rps"].repetitions == 3
