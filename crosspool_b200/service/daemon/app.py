@@ -22,6 +22,7 @@ from ..wire import (AgentStartupAdmission, AtnAgentRegistration, ConfigCheckRequ
                     HeartbeatRequest, InstanceRankInitialized, InstanceRankRegistration, ParticipantReport,
                     QuiesceRequest, SlotHandlePublication, TransportArenaAcquire, TransportArenaUpsert,
                     TransportLeaseQuiesceResponse)
+from ..wire import ProcessRef
 from .control import ControlPlane
 
 WATCHDOG_SECONDS = 1.0
@@ -158,6 +159,11 @@ def create_app(config: XpoolConfig, control: ControlPlane | None = None, *, back
     @app.post("/instance/{model_id:path}/transport-arena/acquire")
     def instance_acquire(model_id: str, req: TransportArenaAcquire):
         return cp.acquire_arena(model_id, req.rank, req.owner, req.generation)
+
+    @app.post("/serving/terminate-owner")
+    @app.post("/serving/mps/terminate-client")   # the reference's route name, kept for its clients
+    def terminate_owner(owner: ProcessRef):
+        return {"signalled": cp.terminate_owner(owner)}
 
     @app.get("/ecs/control-channel/{generation}")
     def ecs_channel(generation: int):

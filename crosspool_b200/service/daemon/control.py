@@ -373,6 +373,24 @@ class ControlPlane:
         else:
             self._abort(f"{key} {reason.value}")
 
+    # ------------------------------------------------------------------ forced termination
+    def terminate_owner(self, owner: ProcessRef, terminate: Callable[[ProcessRef], list[int]] | None = None) -> list[int]:
+        """Ends a registered participant process (and its children) on an operator's or a peer's request, e.g. an
+        Instance host that stopped answering while it still holds GPU memory. Only an owner the daemon knows,
+        with a matching creation time, is ever signalled (the reference terminates an MPS client the same way,
+        ``POST /serving/mps/terminate-client``, src/xpool/utils/mps.py:514-588)."""
+        with self._lock:
+            known = [r.owner for t in (self.atnagents, self.ffnagents, self.instances) for r in t.values()]
+        if not any(o.pid == owner.pid and abs(o.create_time - owner.create_time) < 1.0 for o in known):
+            raise DaemonError("not_found", f"process {owner.pid} is not a registered participant")
+        if terminate is None:
+            from ...utils import procs
+
+            def terminate(ref: ProcessRef) -> list[int]:
+                return procs.kill_tree(procs.ProcUniqId(ref.pid, ref.create_time))
+
+        return terminate(owner)
+
     # ------------------------------------------------------------------ watchdog
     def watchdog(self) -> list[tuple[str, OwnerFailureReason]]:
         """Runs every second: classify lost owners, expire phases."""

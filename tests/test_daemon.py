@@ -249,3 +249,16 @@ def test_http_face_in_process():
         assert hb["fabric_phase"] == "preparing_join"
         ready = http.get("/ready").json()
         assert ready["fabric_executable"] is False and ready["phase"] == "preparing_join"
+
+
+def test_terminate_owner_only_signals_registered_participants():
+    w = World()
+    owner = w.ref(4242)
+    w.cp.register_atnagent(AtnAgentRegistration(owner=owner, device=0))
+    killed = []
+    assert w.cp.terminate_owner(owner, terminate=lambda ref: killed.append(ref.pid) or [ref.pid]) == [4242]
+    with pytest.raises(DaemonError):   # same PID, other creation time: a reused PID is never signalled
+        w.cp.terminate_owner(ProcessRef(abi_version=ABI_VERSION, pid=4242, create_time=900.0), terminate=lambda r: [r.pid])
+    with pytest.raises(DaemonError):
+        w.cp.terminate_owner(ProcessRef(abi_version=ABI_VERSION, pid=1, create_time=1.0), terminate=lambda r: [r.pid])
+    assert killed == [4242]
