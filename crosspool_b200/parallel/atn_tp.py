@@ -90,7 +90,7 @@ class TpGroup:
         w = native.WaitArgs()
         for i, r in enumerate(peers):
             w.flags[i] = self.buf.ptr + 4 * r                # the peer's word in my flag block
-        w.n, w.want_ptr, w.wait_ns = len(peers), self.seq.data_ptr(), 20_000_000_000  # tolerates graph-capture skew between ranks
+        w.n, w.want_ptr, w.wait_ns = len(peers), self.seq.data_ptr(), 5_000_000_000
         w.status = scratch(self.device).status.data_ptr()
         self._sig, self._wait = sig, w
 
