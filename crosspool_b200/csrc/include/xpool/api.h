@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 19
+#define XP_ABI_VERSION 20
 
 #ifdef __cplusplus
 extern "C" {
@@ -125,7 +125,9 @@ typedef struct XpLaneLayerDesc {
   const float* router_bias;      /* optional [num_experts] */
   int num_experts, top_k, expert_lo, expert_hi, sigmoid, renormalize;
   float scale;
-  int reserved;
+  int shared_inter_local;        /* > 0: shared experts as one dense gated FFN of this local width */
+  const void* w_shared_gateup;   /* [2 * shared_inter_local, hidden] */
+  const void* w_shared_down;     /* [hidden, shared_inter_local] */
 } XpLaneLayerDesc;
 
 void* xp_lane_create(int n_instances, int n_lanes, int policy, uint64_t seed, size_t ws_bytes_per_lane);

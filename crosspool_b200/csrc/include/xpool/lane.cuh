@@ -61,6 +61,13 @@ struct alignas(128) LayerEntry {
   float gate_limit, up_add, act_alpha;
   int reserved;
   const MoeLayer* moe;      // null for a dense layer
+  // shared experts of a MoE layer (one dense gated FFN added to the routed output); 0: none
+  int shared_inter_local;
+  int reserved2;
+  CUtensorMap tmap_shared_gateup;  // [2 * shared_inter_local, hidden]
+  CUtensorMap tmap_shared_down;    // [hidden, shared_inter_local]
+  uint8_t bn_sh_gateup[kRowBuckets], splits_sh_gateup[kRowBuckets];
+  uint8_t bn_sh_down[kRowBuckets], splits_sh_down[kRowBuckets];
   // tile width and split-K factor per row bucket, chosen on the host at install time
   uint8_t bn_gateup[kRowBuckets], splits_gateup[kRowBuckets];
   uint8_t bn_down[kRowBuckets], splits_down[kRowBuckets];
@@ -97,6 +104,7 @@ struct MoeLaneWs {
   void* xp;               // [routes, hidden] gathered rows
   void* act;              // [routes, inter_local]
   void* yp;               // [routes, hidden] expert outputs
+  void* comb;             // [capacity_rows, hidden] routed result when shared experts still have to be added
   int cap_routes;
   int reserved;
 };

@@ -84,6 +84,7 @@ gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int 
   const lane::LayerEntry& le = s.layers[cur->layer];
   const lane::MoeLayer* moe = le.moe;
   if (phase == 2 && moe == nullptr) return;       // router projection: MoE layers only
+  if (phase >= 3 && (moe == nullptr || le.shared_inter_local == 0)) return;  // shared experts of a MoE layer
   const int rows = static_cast<int>(cur->rows);
   int bucket = 0;
   while ((1 << bucket) < rows && bucket < lane::kRowBuckets - 1) ++bucket;
@@ -94,7 +95,34 @@ gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int 
   p.counters = counters;
   p.w_tiled = le.w_tiled;
   p.w_evict_first = rows <= 64;
-  if (phase == 2) {
+  if (phase == 3) {
+    // shared experts, gate/up + SwiGLU into the slot's activation scratch
+    p.bn = le.bn_sh_gateup[bucket] == 255 ? 256 : le.bn_sh_gateup[bucket];
+    p.splits = le.splits_sh_gateup[bucket];
+    p.tmap_w = &le.tmap_shared_gateup;
+    p.tmap_x = &s.tmap_x[lane::bn_index(p.bn)];
+    p.out = s.act;
+    p.n_out = le.shared_inter_local;
+    p.k = s.hidden;
+    p.ld_out = s.act_ld;
+    p.dual = 1;
+    p.up_offset = le.shared_inter_local;
+    p.epilogue = kEpiSwiglu;
+    p.w_tiled = 0;
+  } else if (phase == 4) {
+    // shared experts, down projection added to the routed result, stored to the attention device
+    p.bn = le.bn_sh_down[bucket] == 255 ? 256 : le.bn_sh_down[bucket];
+    p.splits = le.splits_sh_down[bucket];
+    p.tmap_w = &le.tmap_shared_down;
+    p.tmap_x = &s.tmap_act[lane::bn_index(p.bn)];
+    p.out = s.out_peer;
+    p.resid = mws->comb;
+    p.n_out = s.hidden;
+    p.k = le.shared_inter_local;
+    p.ld_out = s.hidden;
+    p.epilogue = kEpiResidual;
+    p.w_tiled = 0;
+  } else if (phase == 2) {
     p.bn = moe->bn_router[bucket] == 255 ? 256 : moe->bn_router[bucket];
     p.splits = moe->splits_router[bucket];
     p.tmap_w = &moe->tmap_router;
@@ -171,7 +199,7 @@ gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int 
   }
   p.ld_resid = p.ld_out;
   const int nacc = p.bn * (p.dual ? 2 : 1) * 2 <= 512 ? 2 : 1;
-  if (threadIdx.x == 0 && (phase == 0 || phase == 2)) sm100::fence_proxy_async();  // payload arrived through peer stores
+  if (threadIdx.x == 0 && (phase == 0 || phase == 2 || phase == 3)) sm100::fence_proxy_async();  // payload arrived through peer stores
   run_tiles(p, nacc, smem_budget, status);
 }
 

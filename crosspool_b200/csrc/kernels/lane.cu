@@ -300,6 +300,27 @@ extern "C" int xp_lane_set_layer(void* h, int inst, int layer, const XpLaneLayer
     rt->moe_n_local[inst] = std::max(rt->moe_n_local[inst], n_local);
     rt->moe_e_pad[inst] = std::max(rt->moe_e_pad[inst], m.e_pad);
     e.kind = 2;
+    if (d->shared_inter_local > 0) {
+      if (d->shared_inter_local % 128 != 0 || d->shared_inter_local > s.act_ld || d->w_shared_gateup == nullptr ||
+          d->w_shared_down == nullptr)
+        return -5;
+      if (rc == 0)
+        rc = tmap::encode_2d(&e.tmap_shared_gateup, d->w_shared_gateup, 2 * d->shared_inter_local, s.hidden,
+                             static_cast<uint64_t>(s.hidden) * 2, 128, 64, 2);
+      if (rc == 0)
+        rc = tmap::encode_2d(&e.tmap_shared_down, d->w_shared_down, s.hidden, d->shared_inter_local,
+                             static_cast<uint64_t>(d->shared_inter_local) * 2, 128, 64, 2);
+      e.shared_inter_local = d->shared_inter_local;
+      for (int b = 0; b < lane::kRowBuckets; ++b) {
+        const int rows = std::min(1 << b, s.capacity_rows);
+        gemm::TileChoice g = gemm::choose_tiles_host(d->shared_inter_local / 128, rows, s.hidden / 64, 1, rt->sms, rt->ws_bytes_per_lane);
+        gemm::TileChoice w = gemm::choose_tiles_host(s.hidden / 128, rows, d->shared_inter_local / 64, 0, rt->sms, rt->ws_bytes_per_lane);
+        e.bn_sh_gateup[b] = static_cast<uint8_t>(g.bn == 256 ? 255 : g.bn);
+        e.splits_sh_gateup[b] = static_cast<uint8_t>(g.splits);
+        e.bn_sh_down[b] = static_cast<uint8_t>(w.bn == 256 ? 255 : w.bn);
+        e.splits_sh_down[b] = static_cast<uint8_t>(w.splits);
+      }
+    }
   } else if (d->w_tiled) {
     rc = tmap::encode_2d(&e.tmap_gateup, d->w_gateup, static_cast<uint64_t>(gu_rows) * (s.hidden / 64), 64, 128, 128, 64, 2);
     if (rc == 0)
@@ -371,9 +392,10 @@ static int commit_moe(Runtime* rt) {
     w.xp = alloc(routes * hidden * 2);
     w.act = alloc(routes * inter * 2);
     w.yp = alloc(routes * hidden * 2);
+    w.comb = alloc(rows * hidden * 2);
     w.cap_routes = static_cast<int>(routes);
     if (!w.logits || !w.ids || !w.weights || !w.offsets || !w.perm_token || !w.route_pos || !w.tiles_gateup || !w.tiles_down ||
-        !w.n_tiles || !w.xp || !w.act || !w.yp)
+        !w.n_tiles || !w.xp || !w.act || !w.yp || !w.comb)
       return -5;
     for (int i = 0; i < rt->n_instances; ++i) {
       if (rt->moe_top_k[i] == 0) continue;
@@ -452,7 +474,14 @@ extern "C" int xp_lane_launch(void* h, int lane_index, uint64_t lease_ns, void* 
                                                                mmaps);
   gemm::gemm_lane_kernel<<<rt->sms, gemm::kThreads, smem, s>>>(rt->slots_d, cur, 1, ws, counters, smem_budget, rt->status_d, mws,
                                                                mmaps);
-  if (rt->has_moe) moe::moe_lane_combine_kernel<<<rt->sms * 4, 128, 0, s>>>(rt->slots_d, cur, mws);
+  if (rt->has_moe) {
+    moe::moe_lane_combine_kernel<<<rt->sms * 4, 128, 0, s>>>(rt->slots_d, cur, mws);
+    // shared experts (no-ops unless the layer has them)
+    gemm::gemm_lane_kernel<<<rt->sms, gemm::kThreads, smem, s>>>(rt->slots_d, cur, 3, ws, counters, smem_budget, rt->status_d,
+                                                                 mws, mmaps);
+    gemm::gemm_lane_kernel<<<rt->sms, gemm::kThreads, smem, s>>>(rt->slots_d, cur, 4, ws, counters, smem_budget, rt->status_d,
+                                                                 mws, mmaps);
+  }
   lane::lane_complete_kernel<<<1, 1, 0, s>>>(rt->ctl_d, rt->slots_d, cur, lane_index);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);

@@ -390,9 +390,11 @@ moe_lane_combine_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cu
   const lane::MoeLayer* m = lane_moe_layer(slots, cur);
   if (m == nullptr) return;
   const lane::InstanceSlot& s = slots[cur->instance];
+  // with shared experts the routed sum stays local: their down projection adds it and stores the total
+  void* dst = s.layers[cur->layer].shared_inter_local > 0 ? ws->comb : s.out_peer;
   for (int token = blockIdx.x; token < static_cast<int>(cur->rows); token += gridDim.x)
     combine_token(reinterpret_cast<const __nv_bfloat16*>(ws->yp), ws->route_pos, ws->weights,
-                  reinterpret_cast<__nv_bfloat16*>(s.out_peer), m->top_k, s.hidden, s.hidden, token);
+                  reinterpret_cast<__nv_bfloat16*>(dst), m->top_k, s.hidden, s.hidden, token);
 }
 
 }  // namespace moe

@@ -136,10 +136,21 @@ def random_ffn_layer(cfg: ModelConfig, layer: int, seed: int = 0, device="cpu", 
         down = _randn(gen, (e, h, inter), dt, device)
         if tp_size > 1:
             gate_up, down = shard_rows(gate_up, inter), shard_cols(down, inter)
+        shared_gu = shared_dn = None
+        if cfg.num_shared_experts > 0:
+            # the shared experts act as one dense gated FFN of width num_shared * moe_intermediate
+            si = cfg.num_shared_experts * inter
+            shared_gu = _randn(gen, (2 * si, h), dt, device)
+            shared_dn = _randn(gen, (h, si), dt, device)
+            if tp_size > 1:
+                shared_gu, shared_dn = shard_rows(shared_gu, si), shard_cols(shared_dn, si)
         if expert_range is not None:
             lo, hi = expert_range
             gate_up, down = gate_up[lo:hi].contiguous(), down[lo:hi].contiguous()
-        return FfnLayerWeights(gate_up.to(device), down.to(device), router=router.to(device))
+            if lo != 0:
+                shared_gu = shared_dn = None   # the rank owning expert 0 adds the shared experts
+        return FfnLayerWeights(gate_up.to(device), down.to(device), router=router.to(device), shared_gate_up=shared_gu,
+                               shared_down=shared_dn)
     inter = cfg.intermediate_size
     gate_up = _randn(gen, (2 * inter, h), dt, device)
     down = _randn(gen, (h, inter), dt, device)

@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 19
+EXPECTED_ABI = 20
 HERE = Path(__file__).resolve().parent
 
 
@@ -297,7 +297,9 @@ class LaneLayerDesc(C.Structure):
         ("sigmoid", C.c_int),
         ("renormalize", C.c_int),
         ("scale", C.c_float),
-        ("reserved", C.c_int),
+        ("shared_inter_local", C.c_int),
+        ("w_shared_gateup", C.c_void_p),
+        ("w_shared_down", C.c_void_p),
     ]
 
 

@@ -141,10 +141,15 @@ class InstancePlacement:
         return group_rank * per, (group_rank + 1) * per
 
     def dense_inter_local(self) -> int:
-        """Widest dense-layer shard of this instance on one FFN rank (0 if every layer is MoE)."""
+        """Widest dense projection of this instance on one FFN rank: dense layers and the shared experts of
+        MoE layers (0 if there is neither)."""
         cfg = self.cfg
         has_dense = not cfg.is_moe or cfg.first_k_dense > 0
-        return cfg.intermediate_size // self.tp if has_dense else 0
+        dense = cfg.intermediate_size // self.tp if has_dense else 0
+        shared = cfg.num_shared_experts * cfg.moe_intermediate_size if cfg.is_moe else 0
+        if shared and not self.expert_parallel:
+            shared //= self.tp
+        return max(dense, shared)
 
 
 @dataclass
@@ -351,7 +356,8 @@ class FfnRankRuntime:
                     from ..ops.moe import padded_router
 
                     if w.shared_gate_up is not None:
-                        raise NotImplementedError("shared experts are served by ops.moe.moe_forward, not by Lanes yet")
+                        ld.shared_inter_local = w.shared_gate_up.shape[0] // 2
+                        ld.w_shared_gateup, ld.w_shared_down = w.shared_gate_up.data_ptr(), w.shared_down.data_ptr()
                     cfg = p.cfg
                     router = padded_router(w)
                     lo, hi = p.expert_range(st.tp_rank)

@@ -148,12 +148,12 @@ def test_fabric_observer_records_lane_events_in_order_and_counts_overflow():
         ffn.close()
 
 
-def _moe_cfg(E=8, k=2, hidden=256, inter=128, layers=1):
+def _moe_cfg(E=8, k=2, hidden=256, inter=128, layers=1, shared=0):
     from crosspool_b200.models.config import ModelConfig
 
     return ModelConfig(name="tmoe", architecture="Qwen3MoeForCausalLM", hidden_size=hidden, num_layers=layers, num_q_heads=4,
                        num_kv_heads=2, head_dim=64, intermediate_size=inter, vocab_size=128, num_experts=E,
-                       num_experts_per_tok=k, moe_intermediate_size=inter)
+                       num_experts_per_tok=k, moe_intermediate_size=inter, num_shared_experts=shared)
 
 
 @pytest.mark.parametrize("E,k,hidden,inter,rows", [(8, 2, 256, 128, 7), (128, 8, 2048, 768, 64), (128, 8, 2048, 768, 1)])
@@ -280,6 +280,36 @@ def test_a_rank_refuses_layers_of_another_layer_group():
         out, rc, nrows, seq = _result(F, buf, place, 4)
         assert (rc, nrows, seq) == (0, 4, 5)
         torch.testing.assert_close(out.float(), _ref(x, st.weights[1]), atol=2e-2, rtol=2e-2)
+    finally:
+        ffn.close()
+        buf.free()
+
+
+@pytest.mark.parametrize("rows", [5, 70])
+def test_lane_adds_shared_experts_to_the_routed_output(rows):
+    from crosspool_b200.models.reference import moe_ffn
+    from crosspool_b200.parallel import fabric as F
+
+    cfg = _moe_cfg(16, 4, 512, 256, shared=2)
+    place = F.InstancePlacement("m", cfg, seed=11, atn_rank=0, ffn_ranks=(1,), capacity_rows=128)
+    ffn = F.FfnRankRuntime("cuda", n_lanes=1)
+    st = ffn.add_instance(place, 0)
+    buf = F.PeerBuffer(F.atn_slot_layout(place).total_bytes)
+    st.atn_base = buf.ptr
+    ffn.install()
+    try:
+        assert st.weights[0].shared_gate_up.shape == (2 * 2 * 256, 512)
+        x = (torch.randn(rows, cfg.hidden_size, device="cuda") * 0.5).bfloat16()
+        _publish(F, st, place, x, 0, 1)
+        ffn.launch_once(0, lease_ms=20)
+        torch.cuda.synchronize()
+        assert ffn.stats()["status"] == 0
+        out, rc, nrows, seq = _result(F, buf, place, rows)
+        assert (rc, nrows, seq) == (0, rows, 1)
+        ref = moe_ffn(x, st.weights[0], cfg).float()
+        err = (out.float() - ref).abs()
+        assert (err.max() / ref.abs().max().clamp_min(1e-6)).item() < 0.05
+        assert (err.pow(2).mean().sqrt() / ref.pow(2).mean().sqrt()).item() < 0.02
     finally:
         ffn.close()
         buf.free()
