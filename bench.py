@@ -46,6 +46,7 @@ def parse_args(argv=None):
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the result invalid)")
     ap.add_argument("--ffn-tp", type=int, default=1, help="FFN tensor-parallel degree (multi-GPU only)")
     ap.add_argument("--lanes", type=int, default=2, help="Executor Lanes per FFN device (multi-GPU only)")
+    ap.add_argument("--trace-dir", default="", help="multi-GPU only: write the FFN ranks' Lane timelines (chrome trace JSON) here")
     ap.add_argument("--policy", default="fifo", choices=["fifo", "random", "slo"], help="Lane scheduling policy (multi-GPU only)")
     ap.add_argument("--ffn-ranks", type=int, default=0, help="GPUs in the shared FFN tier (0: max(1, N // 4); multi-GPU only)")
     return ap.parse_args(argv)

@@ -58,7 +58,10 @@ def main(args) -> int:
     if policy == rt.POLICY_SLO:
         for eng in ctx.engines.values():
             eng.port.slo_tbt_ms = 50.0
+    trace_dir = getattr(args, "trace_dir", "")
     if ctx.role == "ffn":
+        if trace_dir:
+            ctx.ffn.enable_trace(1 << 18)   # fabric observer: Lane admissions / completions with device timestamps
         ctx.ffn.start(lease_ms=20.0)
     dist.barrier(group=ctl)
 
@@ -86,6 +89,16 @@ def main(args) -> int:
     if ctx.role == "ffn":
         lane_stats = ctx.ffn.stats()
         ctx.ffn.stop()
+        if trace_dir:
+            from .. import devkit
+
+            os.makedirs(trace_dir, exist_ok=True)
+            art = devkit.FabricObserver(ctx.ffn, role=f"FfnAgent-rank{rank}").collect()
+            tail = art.events[-20000:]      # the timed region is at the end of the run
+            art.events = tail
+            with open(os.path.join(trace_dir, f"lanes_rank{rank}.chrome.json"), "w") as f:
+                json.dump(devkit.chrome_trace([art]), f)
+            lane_stats["trace"] = {"events": len(tail), "dropped": art.dropped}
     gathered = [None] * world
     dist.all_gather_object(gathered, {"rank": rank, "role": ctx.role, "lanes": lane_stats,
                                       "step_ms": res.step_ms if res else None, "ttft_ms": res.ttft_ms if res else None,
