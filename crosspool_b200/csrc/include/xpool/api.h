@@ -8,7 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#define XP_ABI_VERSION 20
+#define XP_ABI_VERSION 21
 
 #ifdef __cplusplus
 extern "C" {
@@ -231,6 +231,9 @@ typedef struct XpPrefillAttnArgs {
   const int* ctx_lens;        /* [num_seqs] tokens cached before the chunk */
   int num_seqs, max_q_len, q_heads, kv_heads, head_dim, page_size, max_blocks;
   float scale;
+  int num_pages;              /* pages in the cache (bound of the tensor maps); 0: simple kernel only */
+  int force_simple;           /* testing: skip the pipelined kernel */
+  uint32_t* status;           /* optional: set non-zero when a bounded wait ran out */
 } XpPrefillAttnArgs;
 
 int xp_rope_kv(const XpRopeArgs* a, void* stream);

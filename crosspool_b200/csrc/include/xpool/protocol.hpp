@@ -23,7 +23,7 @@
 
 namespace xpool {
 
-constexpr uint32_t kAbiVersion = 20;
+constexpr uint32_t kAbiVersion = 21;
 constexpr uint64_t kAllocationAlignment = 256;  // every arena region
 constexpr uint64_t kPayloadAlignment = 16;      // every payload row
 

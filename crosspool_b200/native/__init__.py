@@ -15,7 +15,7 @@ import ctypes as C
 import functools
 from pathlib import Path
 
-EXPECTED_ABI = 20
+EXPECTED_ABI = 21
 HERE = Path(__file__).resolve().parent
 
 
@@ -229,6 +229,9 @@ class PrefillAttnArgs(C.Structure):
         ("page_size", C.c_int),
         ("max_blocks", C.c_int),
         ("scale", C.c_float),
+        ("num_pages", C.c_int),
+        ("force_simple", C.c_int),
+        ("status", C.c_void_p),
     ]
 
 

@@ -94,8 +94,11 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
 
 def paged_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                   q_starts: torch.Tensor, q_lens: torch.Tensor, ctx_lens: torch.Tensor, max_q_len: int, *,
-                  out: torch.Tensor | None = None, scale: float | None = None) -> torch.Tensor:
-    """Causal attention of packed chunk queries ``[total_q, q_heads, d]`` over the paged cache."""
+                  out: torch.Tensor | None = None, scale: float | None = None, force_simple: bool = False) -> torch.Tensor:
+    """Causal attention of packed chunk queries ``[total_q, q_heads, d]`` over the paged cache.
+
+    Runs the pipelined kernel (TMA-fed K/V ring, one CTA per KV head group) when pages hold a multiple of
+    16 tokens and 1, 2, 4 or 8 query heads share a KV head; ``force_simple`` selects the plain kernel."""
     _, q_heads, d = q.shape
     page_size, kv_heads = k_cache.shape[1], k_cache.shape[2]
     if out is None:
@@ -108,6 +111,11 @@ def paged_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     a.q_heads, a.kv_heads, a.head_dim = q_heads, kv_heads, d
     a.page_size, a.max_blocks = page_size, block_table.stride(0)
     a.scale = scale if scale is not None else d ** -0.5
+    a.num_pages = k_cache.shape[0] if k_cache.is_contiguous() and v_cache.is_contiguous() else 0
+    a.force_simple = int(force_simple)
+    from .gemm import scratch
+
+    a.status = scratch(q.device).status.data_ptr()
     native.check(native.kernels().xp_prefill_attn(C.byref(a), _stream(q.device)), "xp_prefill_attn")
     return out
 

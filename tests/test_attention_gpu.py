@@ -95,21 +95,31 @@ def test_paged_decode(d, hq, hkv, splits, simt):
         torch.testing.assert_close(out[b].float(), ref, atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("d,hq,hkv", [(128, 16, 8), (64, 4, 2), (128, 32, 4)])
-def test_paged_prefill_chunked_causal(d, hq, hkv):
+@pytest.mark.parametrize("d,hq,hkv", [(128, 16, 8), (64, 4, 2), (128, 32, 4), (128, 8, 8), (64, 8, 2)])
+@pytest.mark.parametrize("simple,page", [(False, 16), (False, 64), (True, 16)])
+def test_paged_prefill_chunked_causal(d, hq, hkv, simple, page):
     from crosspool_b200.ops import attention as A
+    from crosspool_b200.ops import gemm
 
     torch.manual_seed(2)
-    page = 16
     ctx = [0, 5, 128, 300, 0]
     qlen = [1, 70, 64, 130, 257]
     lens = [c + q for c, q in zip(ctx, qlen)]
     kc, vc, table = _paged(len(lens), lens, hkv, d, page)
+    # slots past each sequence's end hold NaN (stale or unscrubbed memory): they must not leak into the result
+    for b, n in enumerate(lens):
+        if n % page:
+            last = int(table[b, (n - 1) // page])
+            kc[last, n % page:] = float("nan")
+            vc[last, n % page:] = float("nan")
     total_q = sum(qlen)
     q = torch.randn(total_q, hq, d, device="cuda").bfloat16()
     starts = torch.tensor([sum(qlen[:i]) for i in range(len(qlen))], device="cuda", dtype=torch.int32)
     out = A.paged_prefill(q, kc, vc, table, starts, torch.tensor(qlen, device="cuda", dtype=torch.int32),
-                          torch.tensor(ctx, device="cuda", dtype=torch.int32), max(qlen))
+                          torch.tensor(ctx, device="cuda", dtype=torch.int32), max(qlen), force_simple=simple)
+    torch.cuda.synchronize()
+    gemm.check_status(q.device)
+    assert torch.isfinite(out.float()).all()
     g = hq // hkv
     for b in range(len(lens)):
         n = lens[b]
