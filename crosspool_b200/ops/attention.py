@@ -7,6 +7,7 @@ oracles are plain fp32 PyTorch restatements in ``tests/``.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import math
 
 import torch
@@ -38,6 +39,11 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
 
 def decode_splits(batch: int, kv_heads: int, max_len: int) -> int:
     return native.kernels().xp_decode_attn_splits(batch, kv_heads, max_len)
+
+
+# Which prefill kernel runs when the caller does not say: the pipelined one once it has been validated on
+# the deployment's hardware (XPOOL_PREFILL_PIPELINED=1), else the simple one.
+PREFILL_SIMPLE_DEFAULT = os.environ.get("XPOOL_PREFILL_PIPELINED", "0") != "1"
 
 
 def decode_plan(batch: int, kv_heads: int, max_len: int) -> tuple[int, int]:
@@ -94,7 +100,7 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
 
 def paged_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                   q_starts: torch.Tensor, q_lens: torch.Tensor, ctx_lens: torch.Tensor, max_q_len: int, *,
-                  out: torch.Tensor | None = None, scale: float | None = None, force_simple: bool = False) -> torch.Tensor:
+                  out: torch.Tensor | None = None, scale: float | None = None, force_simple: bool | None = None) -> torch.Tensor:
     """Causal attention of packed chunk queries ``[total_q, q_heads, d]`` over the paged cache.
 
     Runs the pipelined kernel (TMA-fed K/V ring, one CTA per KV head group) when pages hold a multiple of
@@ -112,7 +118,7 @@ def paged_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     a.page_size, a.max_blocks = page_size, block_table.stride(0)
     a.scale = scale if scale is not None else d ** -0.5
     a.num_pages = k_cache.shape[0] if k_cache.is_contiguous() and v_cache.is_contiguous() else 0
-    a.force_simple = int(force_simple)
+    a.force_simple = int(PREFILL_SIMPLE_DEFAULT if force_simple is None else force_simple)
     from .gemm import scratch
 
     a.status = scratch(q.device).status.data_ptr()
