@@ -245,6 +245,8 @@ int xp_prefill_attn(const XpPrefillAttnArgs* a, void* stream);
 int xp_embedding(const int* ids, const void* table, void* out, int rows, int hidden, int vocab,
                  void* stream);
 int xp_argmax(const void* logits, int is_fp32, int* out, int rows, int vocab, int ld, void* stream);
+int xp_sample(const void* logits, int is_fp32, const float* temps, const uint32_t* seeds, int* out, int rows, int vocab,
+              int ld, void* stream);
 int xp_fill_u32(void* p, uint32_t v, size_t n, void* stream);
 int xp_l2_flush(void* p, size_t bytes, void* stream);
 

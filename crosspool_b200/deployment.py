@@ -53,9 +53,10 @@ class Deployment:
         for i in self.instances:
             i.engine.warmup()
 
-    def add_request(self, model_id: str, prompt: list[int], max_new_tokens: int, arrival: float | None = None
-                    ) -> Sequence:
-        return self._by_id[model_id].engine.add_request(prompt, max_new_tokens, arrival)
+    def add_request(self, model_id: str, prompt: list[int], max_new_tokens: int, arrival: float | None = None,
+                    **sampling) -> Sequence:
+        """``sampling``: ``temperature`` and ``seed`` (engines built with ``EngineConfig(sampling=True)``)."""
+        return self._by_id[model_id].engine.add_request(prompt, max_new_tokens, arrival, **sampling)
 
     @property
     def has_work(self) -> bool:

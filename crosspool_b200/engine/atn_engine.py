@@ -51,6 +51,7 @@ class EngineConfig:
     use_cuda_graph: bool = True
     decode_buckets: list[int] | None = None
     prefix_cache: bool = False  # keep full prompt pages and share them with later requests
+    sampling: bool = False      # per-request temperature sampling (Gumbel-max kernel) instead of greedy argmax
 
 
 @dataclass
@@ -65,6 +66,8 @@ class Sequence:
     first_token_time: float | None = None
     finish_time: float | None = None
     token_times: list[float] = field(default_factory=list)
+    temperature: float = 0.0         # 0: greedy (needs EngineConfig.sampling for anything else)
+    seed: int = 0
 
     @property
     def total_len(self) -> int:
@@ -185,6 +188,11 @@ class AttentionEngine:
         self.sel = torch.zeros(max(B, e.max_prefill_seqs), cfg.hidden_size, dtype=bf, device=dev)
         self.logits = torch.zeros(max(B, e.max_prefill_seqs), cfg.vocab_size, dtype=bf, device=dev)
         self.tokens = torch.zeros(max(B, e.max_prefill_seqs), dtype=torch.int32, device=dev)
+        if e.sampling:
+            n = max(B, e.max_prefill_seqs)
+            self.samp_temps = torch.zeros(n, dtype=torch.float32, device=dev)
+            self.samp_seeds = torch.zeros(n, 2, dtype=torch.int32, device=dev)
+            self._samp_host = torch.zeros(n, 3, dtype=torch.float32).pin_memory()   # temperature | seed, step as int bits
         self.tokens_host = torch.zeros(max(B, e.max_prefill_seqs), dtype=torch.int32).pin_memory()
         # decode metadata: ids | positions | slots | seq_lens | block_table, one pinned mirror
         self._dec_words = 4 * B + B * self.max_blocks
@@ -206,11 +214,13 @@ class AttentionEngine:
 
     # ------------------------------------------------------------------ request API
     def add_request(self, prompt: list[int], max_new_tokens: int, arrival: float | None = None,
-                    deadline: float = 0.0) -> Sequence:
+                    deadline: float = 0.0, temperature: float = 0.0, seed: int = 0) -> Sequence:
         if len(prompt) + max_new_tokens > self.ecfg.max_seq_len:
             raise ValueError("request exceeds max_seq_len")
+        if temperature > 0 and not self.ecfg.sampling:
+            raise ValueError("temperature sampling needs EngineConfig(sampling=True)")
         s = Sequence(self._next_id, list(prompt), max_new_tokens, arrival if arrival is not None else time.monotonic(),
-                     deadline)
+                     deadline, temperature=float(temperature), seed=int(seed) & 0x7FFFFFFF)
         self._next_id += 1
         self.waiting.append(s)
         return s
@@ -218,6 +228,21 @@ class AttentionEngine:
     @property
     def has_work(self) -> bool:
         return bool(self.waiting or self.running or self.prefilling)
+
+    def _stage_sampling(self, seqs: list["Sequence"]) -> None:
+        """Copies the rows' temperatures and (seed, step) pairs to the device (on the engine stream, before the
+        forward that samples them)."""
+        if not self.ecfg.sampling:
+            return
+        h = self._samp_host
+        hi = h.view(torch.int32)
+        for i, s in enumerate(seqs):
+            h[i, 0] = s.temperature
+            hi[i, 1] = s.seed
+            hi[i, 2] = len(s.generated)
+        n = len(seqs)
+        self.samp_temps[:n].copy_(h[:n, 0], non_blocking=True)
+        self.samp_seeds[:n].copy_(hi[:n, 1:3], non_blocking=True)
 
     # ------------------------------------------------------------------ model forward
     def _layers(self, rows: int, mode: int, attn_fn) -> None:
@@ -263,7 +288,10 @@ class AttentionEngine:
         else:
             hsel = A.embedding(sel_idx, self.x[:rows], out=self.sel[:n_sel])
         gemm.linear(hsel, self.w.lm_head, out=self.logits[:n_sel])
-        A.argmax(self.logits[:n_sel], out=self.tokens[:n_sel])
+        if self.ecfg.sampling:
+            A.sample(self.logits[:n_sel], self.samp_temps[:n_sel], self.samp_seeds[:n_sel], out=self.tokens[:n_sel])
+        else:
+            A.argmax(self.logits[:n_sel], out=self.tokens[:n_sel])
 
     def _decode_forward(self, B: int) -> None:
         cfg = self.cfg
@@ -394,6 +422,7 @@ class AttentionEngine:
             r += n
         with torch.cuda.stream(self.stream):
             self.pre_meta.copy_(self.pre_meta_host, non_blocking=True)
+            self._stage_sampling([s for s, _ in chosen])
             self._prefill_forward(rows, len(chosen), max(n for _, n in chosen))
             self.tokens_host[:len(chosen)].copy_(self.tokens[:len(chosen)], non_blocking=True)
             self.stream.synchronize()
@@ -510,6 +539,7 @@ class AttentionEngine:
         n = len(batch)
         with torch.cuda.stream(self.stream):
             self.dec_meta.copy_(self.dec_meta_host, non_blocking=True)
+            self._stage_sampling(batch)
             g = self._graphs.get(B)
             if g is not None:
                 g.replay()

@@ -245,6 +245,8 @@ def _declare_attention(lib: C.CDLL) -> None:
     lib.xp_decode_attn_splits.argtypes = [C.c_int, C.c_int, C.c_int]
     lib.xp_embedding.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.xp_argmax.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.xp_sample.restype = C.c_int
+    lib.xp_sample.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
 
 
 class WaitArgs(C.Structure):

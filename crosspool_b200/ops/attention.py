@@ -142,3 +142,17 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     native.check(native.kernels().xp_argmax(logits.data_ptr(), int(logits.dtype == torch.float32), out.data_ptr(),
                                             rows, vocab, logits.stride(0), _stream(logits.device)), "xp_argmax")
     return out
+
+
+def sample(logits: torch.Tensor, temps: torch.Tensor, seeds: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row from ``softmax(logits / temperature)`` (Gumbel-max); rows with temperature 0 are
+    greedy. ``temps`` fp32 ``[rows]``; ``seeds`` int32 ``[rows, 2]`` = (request seed, step): the same pair
+    always gives the same token."""
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    assert temps.dtype == torch.float32 and seeds.dtype == torch.int32 and seeds.shape[-1] == 2
+    native.check(native.kernels().xp_sample(logits.data_ptr(), int(logits.dtype == torch.float32), temps.data_ptr(),
+                                            seeds.data_ptr(), out.data_ptr(), rows, vocab, logits.stride(0),
+                                            _stream(logits.device)), "xp_sample")
+    return out

@@ -34,6 +34,8 @@ class Pending:
     prompt: list[int]
     max_new_tokens: int
     arrival: float
+    temperature: float = 0.0
+    seed: int = 0
     out: "queue.Queue[tuple[int, bool] | Exception]" = field(default_factory=queue.Queue)
 
 
@@ -49,8 +51,8 @@ class EngineLoop:
         self.steps = 0
         self.tokens = 0
 
-    def submit(self, model_id: str, prompt: list[int], max_new_tokens: int) -> Pending:
-        p = Pending(model_id, prompt, max_new_tokens, time.monotonic())
+    def submit(self, model_id: str, prompt: list[int], max_new_tokens: int, temperature: float = 0.0, seed: int = 0) -> Pending:
+        p = Pending(model_id, prompt, max_new_tokens, time.monotonic(), temperature, seed)
         self._inbox.put(p)
         return p
 
@@ -61,7 +63,8 @@ class EngineLoop:
             except queue.Empty:
                 return
             try:
-                seq = self.dep.add_request(p.model_id, p.prompt, p.max_new_tokens, arrival=p.arrival)
+                kw = {"temperature": p.temperature, "seed": p.seed} if p.temperature > 0 else {}
+                seq = self.dep.add_request(p.model_id, p.prompt, p.max_new_tokens, arrival=p.arrival, **kw)
                 self._by_seq[(p.model_id, seq.seq_id)] = p
             except Exception as e:  # bad request: answer it, keep serving
                 p.out.put(e)
@@ -106,6 +109,8 @@ class GenerateRequest(BaseModel):
     text: Optional[str] = None
     max_new_tokens: int = 16
     stream: bool = False
+    temperature: float = 0.0
+    seed: int = 0
 
 
 def create_serving_app(loop: EngineLoop, models: list[str], tokenizer=None):
@@ -137,7 +142,7 @@ def create_serving_app(loop: EngineLoop, models: list[str], tokenizer=None):
             if req.text is None or tokenizer is None:
                 raise HTTPException(status_code=422, detail="input_ids required (no tokenizer configured)")
             ids = tokenizer.encode(req.text)
-        p = loop.submit(model, list(ids), req.max_new_tokens)
+        p = loop.submit(model, list(ids), req.max_new_tokens, req.temperature, req.seed)
         if req.stream:
             async def sse():
                 n = 0

@@ -196,3 +196,27 @@ def test_paged_decode_fixed_chunks_balance_mixed_lengths():
     out = A.paged_decode(q, kc, vc, table, sl, num_splits=splits, chunk_tokens=chunk)
     ref = A.paged_decode(q, kc, vc, table, sl, num_splits=1)
     torch.testing.assert_close(out.float(), ref.float(), atol=1e-2, rtol=1e-2)
+
+
+def test_gumbel_sampling_follows_the_softmax_and_is_reproducible():
+    from crosspool_b200.ops import attention as A
+
+    torch.manual_seed(11)
+    rows, vocab = 4096, 1000
+    base = torch.randn(vocab, device="cuda") * 2.0
+    logits = base[None].repeat(rows, 1).bfloat16()
+    temps = torch.full((rows,), 0.7, device="cuda")
+    temps[:8] = 0.0                                           # greedy rows
+    seeds = torch.stack([torch.arange(rows, device="cuda", dtype=torch.int32) + 17,
+                         torch.zeros(rows, device="cuda", dtype=torch.int32)], dim=1).contiguous()
+    tok = A.sample(logits, temps, seeds)
+    assert torch.equal(tok[:8].long(), logits[:8].float().argmax(-1))
+    assert torch.equal(tok, A.sample(logits, temps, seeds))   # same (seed, step) -> same token
+    seeds2 = seeds.clone()
+    seeds2[:, 1] = 1
+    assert (A.sample(logits, temps, seeds2)[8:] != tok[8:]).float().mean() > 0.5   # next step draws anew
+    p = (logits[0].float() / 0.7).softmax(-1)
+    freq = torch.bincount(tok[8:].long(), minlength=vocab).float() / (rows - 8)
+    top = p.topk(5).indices
+    assert ((freq[top] - p[top]).abs() < 4 * (p[top] * (1 - p[top]) / (rows - 8)).sqrt() + 0.005).all()
+    assert (freq - p).abs().sum().item() < 0.5                 # total variation distance well below a uniform draw's

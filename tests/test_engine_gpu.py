@@ -126,3 +126,25 @@ def test_prefix_cache_reuses_prompt_pages_and_keeps_results():
     assert eng.kv.allocator.free_pages <= free_after_first             # cached pages stay resident
     from crosspool_b200.ops import gemm
     gemm.check_status(eng.device)
+
+
+def test_temperature_sampling_is_seeded_and_greedy_requests_are_unaffected():
+    cfg, eng, ref = _build("Qwen/Qwen3-0.6B", layers=2, max_batch=8, prefill_chunk=128, max_seq_len=256, sampling=True)
+    eng.warmup()
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, cfg.vocab_size, (20,), generator=g).tolist()
+
+    def run(**kw):
+        s = eng.add_request(prompt, 8, **kw)
+        while eng.has_work:
+            eng.step()
+        return s.generated
+
+    greedy = run()
+    toks, _ = ref.generate(torch.tensor(prompt, device="cuda"), 8)
+    assert greedy[0] == toks[0]
+    a, b, c = run(temperature=1.5, seed=5), run(temperature=1.5, seed=5), run(temperature=1.5, seed=6)
+    assert a == b and a != c and a != greedy
+    cfg2, eng2, _ = _build("Qwen/Qwen3-0.6B", layers=2, max_batch=8, prefill_chunk=128, max_seq_len=256)
+    with pytest.raises(ValueError, match="sampling"):
+        eng2.add_request(prompt, 4, temperature=1.0)
