@@ -1,0 +1,71 @@
+"""Request replication for an Instance whose attention runs tensor-parallel over several processes.
+
+Every attention TP rank runs the same engine on its share of the heads and must see the same requests
+in the same order at the same step, or the ranks' schedules (and their peer-memory handshakes) diverge.
+The leader (TP rank 0) owns the HTTP front end; once per engine step it broadcasts the requests that
+arrived since the last step over a ``torch.distributed`` CPU group; followers add them to their own
+deployment before stepping. The broadcast also carries the stop signal, so all ranks leave together.
+(The reference relies on its serving engine's scheduler broadcast for the same purpose.)
+"""
+
+from __future__ import annotations
+
+import time
+
+from .serving import EngineLoop, Pending
+
+
+class TpEngineLoop(EngineLoop):
+    def __init__(self, deployment, group, leader: bool, idle_sleep: float = 0.0005):
+        super().__init__(deployment, idle_sleep)
+        self.group, self.leader = group, leader
+
+    def _exchange(self, batch: list[dict] | None, stop: bool) -> tuple[list[dict], bool]:
+        import torch.distributed as dist
+
+        box = [{"requests": batch or [], "stop": stop}] if self.leader else [None]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
+        return box[0]["requests"], box[0]["stop"]
+
+    def _run(self) -> None:
+        try:
+            while True:
+                mine: list[Pending] = []
+                if self.leader:
+                    while not self._inbox.empty():
+                        mine.append(self._inbox.get_nowait())
+                reqs, stop = self._exchange(
+                    [{"model": p.model_id, "prompt": p.prompt, "max_new_tokens": p.max_new_tokens, "temperature": p.temperature,
+                      "seed": p.seed} for p in mine] if self.leader else None, self._stop.is_set())
+                if stop:
+                    break
+                for i, r in enumerate(reqs):
+                    kw = {"temperature": r["temperature"], "seed": r["seed"]} if r["temperature"] > 0 else {}
+                    try:
+                        seq = self.dep.add_request(r["model"], r["prompt"], r["max_new_tokens"], **kw)
+                        if self.leader:
+                            self._by_seq[(r["model"], seq.seq_id)] = mine[i]
+                    except Exception as e:   # every rank refuses the same request the same way
+                        if self.leader:
+                            mine[i].out.put(e)
+                if not self.dep.has_work:
+                    time.sleep(self.idle_sleep)
+                    continue
+                res = self.dep.step()
+                self.steps += 1
+                if not self.leader:
+                    continue
+                for model_id, pairs in res.tokens.items():
+                    for seq, tok in pairs:
+                        p = self._by_seq.get((model_id, seq.seq_id))
+                        if p is None:
+                            continue
+                        done = seq.finished
+                        p.out.put((tok, done))
+                        self.tokens += 1
+                        if done:
+                            del self._by_seq[(model_id, seq.seq_id)]
+        except Exception as e:
+            self.error = e
+            for p in self._by_seq.values():
+                p.out.put(e)
