@@ -17,7 +17,8 @@ token). Two measurements are reported:
   loop, which per step copies the step's metadata (token ids, positions, KV slots, lengths, block
   table) from pinned host memory to the device and reads the sampled tokens back.
 
-``--impl reference`` reports why the reference cannot run here.
+``--impl reference`` reports why the reference cannot run here: its build needs a CUDA 13.2 toolkit,
+NVSHMEM and a serving engine that this image does not carry.
 """
 
 from __future__ import annotations
@@ -27,7 +28,7 @@ import json
 import os
 import sys
 
-BASELINE_PUBLISHED = None  # the reference publishes no number
+BASELINE_PUBLISHED = None  # the reference publishes no throughput or latency number
 REFERENCE_UNAVAILABLE = ("reference not installable offline: needs CUDA Toolkit >= 13.2 (image has 12.9), "
                          "NVSHMEM 3.7.2, cuda-bindings 13, sglang 0.5.20, torch 2.13")
 

@@ -2,7 +2,7 @@
 serving benchmark case against it over HTTP and retires it in order.
 
     python -m crosspool_b200.bench.serve_case --case poisson-16 --models Qwen/Qwen3-0.6B --atn 0 --ffn 1 \
-        --out gpurun_out/serve_poisson16.json
+        --out serve_poisson16.json
 
 The deployment is the one a user would start by hand with ``xpool daemon serve`` / ``xpool atnagent`` /
 ``xpool ffnagent``; the load generator is ``bench.serving`` (open-loop Poisson arrivals, streaming
