@@ -41,9 +41,9 @@ def decode_splits(batch: int, kv_heads: int, max_len: int) -> int:
     return native.kernels().xp_decode_attn_splits(batch, kv_heads, max_len)
 
 
-# Which prefill kernel runs when the caller does not say: the pipelined one once it has been validated on
-# the deployment's hardware (XPOOL_PREFILL_PIPELINED=1), else the simple one.
-PREFILL_SIMPLE_DEFAULT = os.environ.get("XPOOL_PREFILL_PIPELINED", "0") != "1"
+# Which prefill kernel runs when the caller does not say: the pipelined one (XPOOL_PREFILL_PIPELINED=0 selects
+# the simple kernel, e.g. to bisect a numerical difference).
+PREFILL_SIMPLE_DEFAULT = os.environ.get("XPOOL_PREFILL_PIPELINED", "1") == "0"
 
 
 def decode_plan(batch: int, kv_heads: int, max_len: int) -> tuple[int, int]:

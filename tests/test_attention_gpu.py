@@ -4,7 +4,6 @@ import math
 import pytest
 import torch
 
-from conftest import unvalidated
 
 pytestmark = pytest.mark.gpu
 
@@ -98,8 +97,7 @@ def test_paged_decode(d, hq, hkv, splits, simt):
 
 
 @pytest.mark.parametrize("d,hq,hkv", [(128, 16, 8), (64, 4, 2), (128, 32, 4), (128, 8, 8), (64, 8, 2)])
-@pytest.mark.parametrize("simple,page", [pytest.param(False, 16, marks=unvalidated), pytest.param(False, 64, marks=unvalidated),
-                                         (True, 16)])
+@pytest.mark.parametrize("simple,page", [(False, 16), (False, 64), (True, 16)])
 def test_paged_prefill_chunked_causal(d, hq, hkv, simple, page):
     from crosspool_b200.ops import attention as A
     from crosspool_b200.ops import gemm
@@ -201,7 +199,6 @@ def test_paged_decode_fixed_chunks_balance_mixed_lengths():
     torch.testing.assert_close(out.float(), ref.float(), atol=1e-2, rtol=1e-2)
 
 
-@unvalidated
 def test_gumbel_sampling_follows_the_softmax_and_is_reproducible():
     from crosspool_b200.ops import attention as A
 

@@ -2,7 +2,6 @@
 import pytest
 import torch
 
-from conftest import unvalidated
 
 pytestmark = pytest.mark.gpu
 
@@ -130,7 +129,6 @@ def test_prefix_cache_reuses_prompt_pages_and_keeps_results():
     gemm.check_status(eng.device)
 
 
-@unvalidated
 def test_temperature_sampling_is_seeded_and_greedy_requests_are_unaffected():
     cfg, eng, ref = _build("Qwen/Qwen3-0.6B", layers=2, max_batch=8, prefill_chunk=128, max_seq_len=256, sampling=True)
     eng.warmup()
