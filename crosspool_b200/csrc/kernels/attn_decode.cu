@@ -1,9 +1,9 @@
-// Paged decode attention for grouped-query heads with split-KV ("flash
-// decoding"). One CTA handles every query head that shares one KV head over one
-// slice of the sequence; a second small kernel merges the slices. The op is
-// bound by reading the KV cache once, so the layout aims at wide coalesced
-// loads: 8 lanes cooperate on one cached token (16 or 32 bytes each), 16 tokens
-// are in flight per CTA iteration.
+// Paged decode attention for grouped-query heads with optional split-KV ("flash decoding"). One CTA handles
+// every query head that shares one KV head over one slice of the sequence; a second small kernel merges the
+// slices. The op is bound by reading the KV cache once. Two kernels:
+//   decode_attn_tc_kernel  TMA-fed 16-token tiles, ldmatrix + mma.m16n8k16 (default; see its comment below);
+//   decode_attn_kernel     plain SIMT version: 8 lanes cooperate on one cached token, cp.async ring; kept for
+//                          page sizes below 16 tokens and as the numerical cross-check.
 //
 // The reference has no attention code of its own (SGLang/FlashInfer provide
 // it, pyproject.toml:17-35); the oracle is a plain fp32 softmax(QK^T)V.
