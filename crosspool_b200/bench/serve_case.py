@@ -113,9 +113,16 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--max-batch", type=int, default=256)
     ap.add_argument("--max-seq-len", type=int, default=2624)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--duration", type=float, default=0.0, help="override the case's duration (seconds)")
+    ap.add_argument("--rate", type=float, default=0.0, help="override the case's per-model request rate")
     ap.add_argument("--out", default="")
     ns = ap.parse_args(argv)
     case = suite.CASES[ns.case]
+    if ns.duration > 0 or ns.rate > 0:
+        import dataclasses
+
+        case = dataclasses.replace(case, duration_s=ns.duration or case.duration_s,
+                                   rate_per_s=(ns.rate,) if ns.rate > 0 else case.rate_per_s)
     env = {"XPOOL_MAX_BATCH": str(ns.max_batch), "XPOOL_MAX_SEQ_LEN": str(ns.max_seq_len), "XPOOL_MAX_ROWS": "4096"}
     text = toml_for(ns.models, ns.atn, ns.ffn, ns.port, ns.ffn_tp, ns.lanes)
     with LocalDeployment(text, ns.atn, ns.ffn, ns.port, env) as dep:

@@ -200,7 +200,8 @@ async def run_client(targets: dict[str, str], reqs: list[PlannedRequest], max_in
     import httpx
 
     sem = asyncio.Semaphore(max_inflight)
-    async with httpx.AsyncClient(timeout=600.0, transport=transport) as client:
+    limits = httpx.Limits(max_connections=max_inflight, max_keepalive_connections=max_inflight)
+    async with httpx.AsyncClient(timeout=httpx.Timeout(300.0, pool=None), transport=transport, limits=limits) as client:
         warm = [r for r in reqs if r.warmup]
         t0 = time.perf_counter()
         await asyncio.gather(*[_one(client, targets[r.model], r, RequestRecord(r.model, 0.0), t0) for r in warm])

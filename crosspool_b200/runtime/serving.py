@@ -37,6 +37,14 @@ class Pending:
     temperature: float = 0.0
     seed: int = 0
     out: "queue.Queue[tuple[int, bool] | Exception]" = field(default_factory=queue.Queue)
+    # set by an asyncio consumer: tokens are then also handed to its event loop, so that it never has to poll
+    aio_loop: object = None
+    aio_queue: object = None
+
+    def deliver(self, item) -> None:
+        self.out.put(item)
+        if self.aio_loop is not None:
+            self.aio_loop.call_soon_threadsafe(self.aio_queue.put_nowait, item)
 
 
 class EngineLoop:
@@ -51,8 +59,12 @@ class EngineLoop:
         self.steps = 0
         self.tokens = 0
 
-    def submit(self, model_id: str, prompt: list[int], max_new_tokens: int, temperature: float = 0.0, seed: int = 0) -> Pending:
+    def submit(self, model_id: str, prompt: list[int], max_new_tokens: int, temperature: float = 0.0, seed: int = 0,
+               aio: bool = False) -> Pending:
+        """``aio``: called from a running event loop that will ``await p.aio_queue.get()``."""
         p = Pending(model_id, prompt, max_new_tokens, time.monotonic(), temperature, seed)
+        if aio:
+            p.aio_loop, p.aio_queue = asyncio.get_running_loop(), asyncio.Queue()
         self._inbox.put(p)
         return p
 
@@ -67,7 +79,7 @@ class EngineLoop:
                 seq = self.dep.add_request(p.model_id, p.prompt, p.max_new_tokens, arrival=p.arrival, **kw)
                 self._by_seq[(p.model_id, seq.seq_id)] = p
             except Exception as e:  # bad request: answer it, keep serving
-                p.out.put(e)
+                p.deliver(e)
 
     def _run(self) -> None:
         try:
@@ -84,14 +96,14 @@ class EngineLoop:
                         if p is None:
                             continue
                         done = seq.finished
-                        p.out.put((tok, done))
+                        p.deliver((tok, done))
                         self.tokens += 1
                         if done:
                             del self._by_seq[(model_id, seq.seq_id)]
         except Exception as e:  # device failure: fail every waiting request, stop (fail-stop)
             self.error = e
             for p in self._by_seq.values():
-                p.out.put(e)
+                p.deliver(e)
 
     def start(self) -> None:
         self._thread = threading.Thread(target=self._run, daemon=True, name="engine-loop")
@@ -126,11 +138,7 @@ def create_serving_app(loop: EngineLoop, models: list[str], tokenizer=None):
         return {"status": "ok", "models": models, "steps": loop.steps, "tokens": loop.tokens}
 
     async def _next(p: Pending):
-        while True:
-            try:
-                return p.out.get_nowait()
-            except queue.Empty:
-                await asyncio.sleep(0.0005)
+        return await p.aio_queue.get()
 
     @app.post("/generate")
     async def generate(req: GenerateRequest):
@@ -142,7 +150,7 @@ def create_serving_app(loop: EngineLoop, models: list[str], tokenizer=None):
             if req.text is None or tokenizer is None:
                 raise HTTPException(status_code=422, detail="input_ids required (no tokenizer configured)")
             ids = tokenizer.encode(req.text)
-        p = loop.submit(model, list(ids), req.max_new_tokens, req.temperature, req.seed)
+        p = loop.submit(model, list(ids), req.max_new_tokens, req.temperature, req.seed, aio=True)
         if req.stream:
             async def sse():
                 n = 0

@@ -47,7 +47,7 @@ class TpEngineLoop(EngineLoop):
                             self._by_seq[(r["model"], seq.seq_id)] = mine[i]
                     except Exception as e:   # every rank refuses the same request the same way
                         if self.leader:
-                            mine[i].out.put(e)
+                            mine[i].deliver(e)
                 if not self.dep.has_work:
                     time.sleep(self.idle_sleep)
                     continue
@@ -61,11 +61,11 @@ class TpEngineLoop(EngineLoop):
                         if p is None:
                             continue
                         done = seq.finished
-                        p.out.put((tok, done))
+                        p.deliver((tok, done))
                         self.tokens += 1
                         if done:
                             del self._by_seq[(model_id, seq.seq_id)]
         except Exception as e:
             self.error = e
             for p in self._by_seq.values():
-                p.out.put(e)
+                p.deliver(e)
