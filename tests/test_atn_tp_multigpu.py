@@ -8,14 +8,12 @@ from pathlib import Path
 import pytest
 import torch
 
-from conftest import unvalidated
 
 gpu = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
 @gpu
-@unvalidated
 @pytest.mark.parametrize("graph", [0, 1])
 def test_two_attention_tp_ranks_match_the_unsharded_engine(graph):
     if torch.cuda.device_count() < 2:
