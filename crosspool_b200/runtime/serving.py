@@ -47,6 +47,22 @@ class Pending:
             self.aio_loop.call_soon_threadsafe(self.aio_queue.put_nowait, item)
 
 
+def deliver_batch(batch: list[tuple[Pending, object]]) -> None:
+    """Hands one engine step's tokens to their consumers: one wake-up of the event loop per step, not per token."""
+    by_loop: dict = {}
+    for p, item in batch:
+        p.out.put(item)
+        if p.aio_loop is not None:
+            by_loop.setdefault(p.aio_loop, []).append((p.aio_queue, item))
+    for loop, items in by_loop.items():
+        loop.call_soon_threadsafe(_fan_out, items)
+
+
+def _fan_out(items) -> None:
+    for q, item in items:
+        q.put_nowait(item)
+
+
 class EngineLoop:
     def __init__(self, deployment: SteppedDeployment, idle_sleep: float = 0.0005):
         self.dep = deployment
@@ -90,16 +106,18 @@ class EngineLoop:
                     continue
                 res = self.dep.step()
                 self.steps += 1
+                batch: list[tuple[Pending, tuple[int, bool]]] = []
                 for model_id, pairs in res.tokens.items():
                     for seq, tok in pairs:
                         p = self._by_seq.get((model_id, seq.seq_id))
                         if p is None:
                             continue
                         done = seq.finished
-                        p.deliver((tok, done))
+                        batch.append((p, (tok, done)))
                         self.tokens += 1
                         if done:
                             del self._by_seq[(model_id, seq.seq_id)]
+                deliver_batch(batch)
         except Exception as e:  # device failure: fail every waiting request, stop (fail-stop)
             self.error = e
             for p in self._by_seq.values():
