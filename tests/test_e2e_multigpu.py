@@ -12,7 +12,6 @@ import httpx
 import pytest
 import torch
 
-from conftest import unvalidated
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
@@ -35,7 +34,7 @@ ffn_tp_size = 1
 """
 
 
-@pytest.mark.parametrize("elastic", [False, pytest.param(True, marks=unvalidated)])
+@pytest.mark.parametrize("elastic", [False, True])
 def test_daemon_agents_serve_requests_and_retire(tmp_path, elastic):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
