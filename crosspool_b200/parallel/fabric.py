@@ -96,6 +96,9 @@ class InstancePlacement:
     # Layer-split placement: ((first layer, end layer, FFN ranks in TP order), ...) covering all layers, every
     # group of the same TP size; ``ffn_ranks`` is then the union of the groups. Empty: one group of all layers.
     layer_groups: tuple[tuple[int, int, tuple[int, ...]], ...] = ()
+    # Directory of a Hugging Face checkpoint (config.json + safetensors) to load the weights from; None: random
+    # init from ``seed`` (benchmarks and tests).
+    checkpoint: str | None = None
 
     def __post_init__(self):
         if self.layer_groups:
@@ -291,6 +294,36 @@ class FfnInstanceState:
     atn_base: int = 0
 
 
+class CheckpointFfnSource:
+    """FFN weights of one model read from its safetensors checkpoint: the architecture adapter compiles the
+    FFN description from ``config.json`` and the checkpoint's key list, coverage is validated once, and each
+    layer's local shard (TP rows/columns, or an expert range) goes through the pinned staging loader. The
+    reference prepares FFN shards the same way, src/xpool/runtime/ffnagent/preparation.py:164-334."""
+
+    def __init__(self, model_id: str, model_dir: str):
+        import json
+        from pathlib import Path
+
+        from ..engine import checkpoint as ck
+        from ..models import adapters
+
+        self.view = ck.read_checkpoint_key_view(model_dir)
+        hf = json.loads((Path(model_dir) / "config.json").read_text())
+        self.spec = adapters.compile_ffn_spec(model_id, hf, self.view.keys())
+        ck.validate_ffn_coverage(self.spec, self.view)
+
+    def layer(self, layer: int, device, *, tp_rank: int = 0, tp_size: int = 1,
+              expert_range: tuple[int, int] | None = None) -> FfnLayerWeights:
+        from ..engine import loader
+
+        w = loader.materialize_layer_weights(self.spec, self.view, layer, tp_rank=tp_rank, tp_size=tp_size, device=device,
+                                             dtype=torch.bfloat16,
+                                             experts=range(*expert_range) if expert_range is not None else None)
+        if expert_range is not None and expert_range[0] != 0:
+            w.shared_gate_up = w.shared_down = None   # the rank owning expert 0 adds the shared experts
+        return w
+
+
 class FfnRankRuntime:
     """Everything an FFN rank owns: shards, slots, the native Lane runtime and the Lane threads."""
 
@@ -313,11 +346,16 @@ class FfnRankRuntime:
         cfg = place.cfg
         lo, hi = layers or (0, cfg.num_layers)
         weights = []
+        source = CheckpointFfnSource(place.model_id, place.checkpoint) if place.checkpoint else None
         for l in range(cfg.num_layers):
             if not lo <= l < hi:
                 weights.append(None)
                 continue
-            if cfg.layer_is_moe(l) and place.expert_parallel:
+            if source is not None:
+                ep = cfg.layer_is_moe(l) and place.expert_parallel
+                w = source.layer(l, self.device, tp_rank=0 if ep else tp_rank, tp_size=1 if ep else place.tp,
+                                 expert_range=place.expert_range(tp_rank) if ep else None)
+            elif cfg.layer_is_moe(l) and place.expert_parallel:
                 w = random_ffn_layer(cfg, l, place.seed, self.device, torch.bfloat16, expert_range=place.expert_range(tp_rank))
             else:
                 w = random_ffn_layer(cfg, l, place.seed, self.device, torch.bfloat16, tp_rank, place.tp)

@@ -9,13 +9,14 @@ from __future__ import annotations
 
 import threading
 import zlib
+from pathlib import Path
 
 import torch
 
 from ..config import XpoolConfig
 from ..engine.atn_engine import AttentionEngine, EngineConfig
 from ..models import config as mc
-from ..models.weights import random_attention_weights
+from ..models.weights import load_attention_from_safetensors, random_attention_weights
 from ..native import runtime as rt
 from ..parallel import fabric as F
 from ..service.wire import FabricPlan, InvocationFailure, ServingListener
@@ -32,6 +33,15 @@ def model_config_for(cfg: XpoolConfig, model_id: str):
     return mc.load(m.path)
 
 
+def checkpoint_dir_for(cfg: XpoolConfig, model_id: str) -> str | None:
+    """The model's checkpoint directory when ``path`` names one (``config.json`` plus safetensors files); None
+    for presets, which run on random-init weights."""
+    p = Path(cfg.model(model_id).path or "")
+    if p.is_dir() and (p / "config.json").exists() and any(p.glob("*.safetensors")):
+        return str(p)
+    return None
+
+
 def _placement(cfg: XpoolConfig, plan: FabricPlan, model_id: str, atn_rank: int, capacity_rows: int) -> F.InstancePlacement:
     shards = [s for s in plan.shards if s.model_id == model_id]
     ranges = sorted({(s.layer_begin, s.layer_end) for s in shards})
@@ -41,7 +51,8 @@ def _placement(cfg: XpoolConfig, plan: FabricPlan, model_id: str, atn_rank: int,
     seed = zlib.crc32(model_id.encode()) % 1000  # random-init deployments: same seed on every rank of a model
     union = tuple(pe for g in groups for pe in g[2])
     return F.InstancePlacement(model_id, model_config_for(cfg, model_id), seed, rank.pe, union, capacity_rows,
-                               layer_groups=groups if len(groups) > 1 else ())
+                               layer_groups=groups if len(groups) > 1 else (),
+                               checkpoint=checkpoint_dir_for(cfg, model_id))
 
 
 class FfnBackend:
@@ -138,7 +149,10 @@ class AtnBackend:
         for (model_id, rank), place in self.places.items():
             port = F.FabricFfnPort(place, self.buffers[(model_id, rank)], self._bases[(model_id, rank)], self.cuda)
             port.slo_tbt_ms = self.cfg.slo_for(model_id).tbt_ms   # per-step deadline for the Lanes' SLO policy
-            aw = random_attention_weights(place.cfg, place.seed, self.cuda, torch.bfloat16)
+            if place.checkpoint:
+                aw = load_attention_from_safetensors(place.cfg, place.checkpoint, self.cuda, torch.bfloat16)
+            else:
+                aw = random_attention_weights(place.cfg, place.seed, self.cuda, torch.bfloat16)
             kv = self._elastic_cache(plan, model_id, rank, place) if self.cfg.atn_elastic_kv and self.ecs_ref else None
             eng = AttentionEngine(place.cfg, aw, port, self.ecfg, self.cuda, kv=kv)
             if kv is not None:

@@ -56,3 +56,59 @@ def assert_logits_close(ref_logits: torch.Tensor, got_logits: torch.Tensor, pref
         raise AssertionError(f"prefill KL {kl[:prefill_rows].max().item():.4f} nats exceeds {KL_PREFILL}")
     if kl.shape[0] > prefill_rows and kl[prefill_rows:].max().item() > KL_DECODE:
         raise AssertionError(f"decode KL {kl[prefill_rows:].max().item():.5f} nats exceeds {KL_DECODE}")
+
+
+def write_synthetic_checkpoint(model_dir, hf_config: dict, seed: int = 0, shards: int = 2, scale: float = 0.02) -> dict:
+    """Writes a random Hugging Face style checkpoint (``config.json``, sharded safetensors and their index) for a
+    Qwen3 / Qwen3-MoE shaped ``hf_config`` and returns the tensors by key. Lets loading paths run against files
+    of the real layout without model downloads."""
+    import json
+    from pathlib import Path
+
+    from safetensors.torch import save_file
+
+    d = Path(model_dir)
+    d.mkdir(parents=True, exist_ok=True)
+    g = torch.Generator().manual_seed(seed)
+    h, heads = int(hf_config["hidden_size"]), int(hf_config["num_attention_heads"])
+    kvh = int(hf_config.get("num_key_value_heads") or heads)
+    hd = int(hf_config.get("head_dim") or h // heads)
+    n_exp = int(hf_config.get("num_experts") or 0)
+
+    def rnd(*shape):
+        return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16)
+
+    def norm(n):
+        return (1.0 + 0.1 * torch.randn(n, generator=g)).to(torch.bfloat16)
+
+    t = {"model.embed_tokens.weight": rnd(int(hf_config["vocab_size"]), h), "model.norm.weight": norm(h)}
+    if not hf_config.get("tie_word_embeddings", False):
+        t["lm_head.weight"] = rnd(int(hf_config["vocab_size"]), h)
+    for i in range(int(hf_config["num_hidden_layers"])):
+        p = f"model.layers.{i}."
+        t[p + "input_layernorm.weight"], t[p + "post_attention_layernorm.weight"] = norm(h), norm(h)
+        t[p + "self_attn.q_proj.weight"] = rnd(heads * hd, h)
+        t[p + "self_attn.k_proj.weight"], t[p + "self_attn.v_proj.weight"] = rnd(kvh * hd, h), rnd(kvh * hd, h)
+        t[p + "self_attn.o_proj.weight"] = rnd(h, heads * hd)
+        if str(hf_config["architectures"][0]).startswith("Qwen3"):
+            t[p + "self_attn.q_norm.weight"], t[p + "self_attn.k_norm.weight"] = norm(hd), norm(hd)
+        if n_exp:
+            inter = int(hf_config["moe_intermediate_size"])
+            t[p + "mlp.gate.weight"] = rnd(n_exp, h)
+            for e in range(n_exp):
+                q = p + f"mlp.experts.{e}."
+                t[q + "gate_proj.weight"], t[q + "up_proj.weight"] = rnd(inter, h), rnd(inter, h)
+                t[q + "down_proj.weight"] = rnd(h, inter)
+        else:
+            inter = int(hf_config["intermediate_size"])
+            t[p + "mlp.gate_proj.weight"], t[p + "mlp.up_proj.weight"] = rnd(inter, h), rnd(inter, h)
+            t[p + "mlp.down_proj.weight"] = rnd(h, inter)
+    keys, wm = sorted(t), {}
+    for s in range(shards):
+        part = {k: t[k].contiguous() for k in keys[s::shards]}
+        name = f"model-{s + 1:05d}-of-{shards:05d}.safetensors"
+        save_file(part, str(d / name))
+        wm.update({k: name for k in part})
+    (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wm}))
+    (d / "config.json").write_text(json.dumps(hf_config))
+    return t
