@@ -71,6 +71,17 @@ def bench_gemm(ns, timer: Timer) -> dict:
     x = (torch.randn(ns.rows, ns.k, device=dev) * 0.5).bfloat16()
     w = (torch.randn(ns.n * (2 if ns.dual else 1), ns.k, device=dev) * 0.05).bfloat16()
     out = torch.empty(ns.rows, ns.n, dtype=torch.bfloat16, device=dev)
+    if ns.fp8:
+        # block-scaled e4m3 weights; the timed op is what a layer pays: activation quantisation + GEMM
+        from ..quantization import Fp8Block
+
+        q = Fp8Block().quantize(w[:ns.n])
+        wq, wscale = q["weight"], q["scale"].contiguous()
+        us = timer(lambda: gemm.linear_fp8(x, wq, wscale, out=out, splits=ns.splits, bn=ns.bn))
+        gemm.check_status(dev)
+        byts = wq.numel() + wscale.numel() * 4 + (x.numel() + out.numel()) * 2
+        return report("gemm_ws_fp8_block", us, byts, 2.0 * ns.rows * ns.n * ns.k,
+                      {"rows": ns.rows, "n": ns.n, "k": ns.k, "includes": "activation quantisation kernel"})
     fn = (lambda: gemm.gateup_swiglu(x, w, out=out, splits=ns.splits, bn=ns.bn)) if ns.dual else \
         (lambda: gemm.linear(x, w, out=out, splits=ns.splits, bn=ns.bn))
     us = timer(fn)
@@ -220,6 +231,7 @@ def main(argv: list[str] | None = None) -> int:
     g.add_argument("--dual", type=int, default=0)
     g.add_argument("--splits", type=int, default=0)
     g.add_argument("--bn", type=int, default=0)
+    g.add_argument("--fp8", type=int, default=0, help="1: block-scaled e4m3 weights and activations")
     a = sub.add_parser("decode-attn")
     a.add_argument("--batch", type=int, default=256)
     a.add_argument("--q-heads", type=int, default=16)

@@ -412,11 +412,13 @@ __device__ __forceinline__ void epi_bar_sync() {
 }
 
 // Applies the fused epilogue to 16 accumulator columns (activation rows
-// n .. n+15) of feature f and stores them.
-__device__ __forceinline__ void epilogue_store16(const Problem& p, int f, int n_first, int row_end,
+// n .. n+15) of feature f and stores them. `fb` is the feature's weight row in
+// the whole weight tensor, which indexes the bias: equal to f except for
+// grouped problems, where every group (expert) has its own bias row.
+__device__ __forceinline__ void epilogue_store16(const Problem& p, int f, int fb, int n_first, int row_end,
                                                  const float* g, const float* u) {
-  const float bias = p.bias != nullptr ? p.bias[f] : 0.f;
-  const float bias_u = (p.bias != nullptr && p.dual) ? p.bias[p.up_offset + f] : 0.f;
+  const float bias = p.bias != nullptr ? p.bias[fb] : 0.f;
+  const float bias_u = (p.bias != nullptr && p.dual) ? p.bias[p.up_offset + fb] : 0.f;
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     const int n = n_first + j;
@@ -453,6 +455,7 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
       bar->tmem_base + st.acc * acc_cols + (static_cast<uint32_t>(ew * 32) << 16);
   const int lane_in_tile = ew * 32 + lane;
   const int f = c.m0 + lane_in_tile;
+  const int fb = c.w_row0 + lane_in_tile;
   // all lanes agree on the outcome so that the aligned TMEM loads below stay convergent
   if (!__all_sync(0xffffffffu, sm100::mbar_wait(&bar->acc_full[st.acc], st.acc_phase, deadline))) return false;
   sm100::tc_fence_after_sync();
@@ -495,7 +498,7 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
     if (p.splits == 1) {
 #pragma unroll
       for (int cc = 0; cc < kMaxBnF8 / 16; ++cc)
-        if (cc * 16 < p.bn && c.n0 + cc * 16 < c.row_end) epilogue_store16(p, f, c.n0 + cc * 16, c.row_end, &acc[cc * 16], u);
+        if (cc * 16 < p.bn && c.n0 + cc * 16 < c.row_end) epilogue_store16(p, f, fb, c.n0 + cc * 16, c.row_end, &acc[cc * 16], u);
     } else {
       float* ws = p.ws + (static_cast<size_t>(c.mn) * p.splits + c.split) * acc_cols * kTileM;
 #pragma unroll
@@ -507,7 +510,7 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
       if (c.n0 + col >= c.row_end) break;
       sm100::tmem_ld16(tmem_acc + col, g);
       if (p.dual) sm100::tmem_ld16(tmem_acc + p.bn + col, u);
-      epilogue_store16(p, f, c.n0 + col, c.row_end, g, u);
+      epilogue_store16(p, f, fb, c.n0 + col, c.row_end, g, u);
     }
   } else {
     // Split-K: park raw partial sums, last-arriving CTA folds them in split order.
@@ -557,7 +560,7 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
             if (p.dual) u[j] += tu[j];
           }
         }
-        epilogue_store16(p, f, c.n0 + col, c.row_end, g, u);
+        epilogue_store16(p, f, fb, c.n0 + col, c.row_end, g, u);
       }
       if (ew == 0 && lane == 0) p.counters[c.mn] = 0;  // ready for the next call
     }

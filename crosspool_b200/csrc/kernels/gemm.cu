@@ -154,6 +154,7 @@ gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int 
       p.gate_limit = le.gate_limit;
       p.up_add = le.up_add;
       p.act_alpha = le.act_alpha;
+      p.bias = le.bias_gateup;   // [local experts, 2 * inter]: the epilogue indexes it by stacked weight row
       p.tile_table = mws->tiles_gateup;
       p.n_tiles = mws->n_tiles;
       p.w_rows_per_group = 2 * le.inter_local;
@@ -165,6 +166,7 @@ gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int 
       p.k = le.inter_local;
       p.ld_out = s.hidden;
       p.epilogue = kEpiStore;
+      p.bias = le.bias_down;     // [local experts, hidden]
       p.tile_table = mws->tiles_down;
       p.n_tiles = mws->n_tiles + 1;
       p.w_rows_per_group = s.hidden;

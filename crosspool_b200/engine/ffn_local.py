@@ -43,6 +43,7 @@ class LocalFfnPort(FfnPort):
             return [gemm.ffn_fp8(x, w.extra["fp8"], out=self.y[:rows])]
         inter = w.gate_up.shape[0] // 2
         act = self.act[:rows, :inter]
-        gemm.gateup_swiglu(x, w.gate_up, out=act, bias=w.gate_up_bias)
+        lim, up_add, alpha = w.extra.get("gate_transform", (0.0, 0.0, 0.0))
+        gemm.gateup_swiglu(x, w.gate_up, out=act, bias=w.gate_up_bias, gate_limit=lim, up_add=up_add, act_alpha=alpha)
         gemm.linear(act, w.down, out=self.y[:rows], bias=w.down_bias)
         return [self.y[:rows]]

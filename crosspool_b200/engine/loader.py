@@ -70,6 +70,16 @@ class _Reader:
             idx[-2 if nd >= 2 else -1] = r.rows
         if r.cols is not None:
             idx[-1] = r.cols
+        strided = [i for i, v in enumerate(idx) if isinstance(v, slice) and v.step not in (None, 1)]
+        if strided:   # safetensors slices take unit steps only: read the span, stride in memory
+            steps = {i: idx[i].step for i in strided}
+            for i in strided:
+                idx[i] = slice(idx[i].start, idx[i].stop)
+            t = sl[tuple(idx)]
+            lead = sum(1 for v in idx[:min(strided)] if isinstance(v, int))   # dims dropped by integer indices
+            for i, st in steps.items():
+                t = t[(slice(None),) * (i - lead) + (slice(None, None, st),)]
+            return t
         return sl[tuple(idx)]
 
 
@@ -118,7 +128,35 @@ def _dense_reads(l: DenseFfnSpec, rank: int, size: int):
     return reads
 
 
-def _moe_reads(l: MoeFfnSpec, rank: int, size: int, experts: range):
+def _mxfp4_expert(reader: "_Reader", blocks_key: str, suffix: str, expert: int) -> torch.Tensor:
+    """One expert's projection of a stacked MXFP4 tensor, dequantised to bf16 ``[rows, k]``. The checkpoint holds
+    ``*_blocks`` ``[experts, rows, k / 32, 16]`` (two e2m1 codes per byte, low nibble first) and ``*_scales``
+    ``[experts, rows, k / 32]`` (e8m0). The reference keeps such weights packed for its GEMM library
+    (src/xpool/quantization/mxfp4.py); this build expands them once at load time and runs the bf16 kernels."""
+    from ..quantization import Mxfp4
+
+    blocks = reader.read(TensorRead(blocks_key, expert=expert))
+    scales = reader.read(TensorRead(blocks_key.removesuffix("_blocks") + suffix, expert=expert))
+    rows = blocks.shape[0]
+    return Mxfp4().dequantize({"blocks": blocks.reshape(rows, -1), "scales": scales.reshape(rows, -1)}, torch.bfloat16)
+
+
+def _moe_mxfp4(l: MoeFfnSpec, reader: "_Reader", rank: int, size: int, experts: range) -> dict[str, torch.Tensor]:
+    """Host tensors ``gate{e}``/``up{e}``/``down{e}`` of the local shard, from packed MXFP4 expert tensors."""
+    rows = _local(l.moe_intermediate_size, rank, size, 32)
+    ex, inter, out = l.experts, l.moe_intermediate_size, {}
+    for e in experts:
+        gu = _mxfp4_expert(reader, ex.packed_key, ex.scales_suffix, e)             # [2 * inter, hidden]
+        if l.source_order == GateUpOrder.INTERLEAVED:
+            g, u = gu[0::2], gu[1::2]
+        else:
+            g, u = gu[:inter], gu[inter:]
+        out[f"gate{e}"], out[f"up{e}"] = g[rows].contiguous(), u[rows].contiguous()
+        out[f"down{e}"] = _mxfp4_expert(reader, ex.down_key, ex.scales_suffix, e)[:, rows].contiguous()
+    return out
+
+
+def _moe_reads(l: MoeFfnSpec, rank: int, size: int, experts: range, packed_weights: bool = True):
     rows = _local(l.moe_intermediate_size, rank, size)
     ex = l.experts
     reads = {"router": TensorRead(l.router_weight_key)}
@@ -127,6 +165,21 @@ def _moe_reads(l: MoeFfnSpec, rank: int, size: int, experts: range):
     if l.correction_bias_key:
         reads["correction_bias"] = TensorRead(l.correction_bias_key)
     for e in experts:
+        if ex.gate_bias_key:
+            # per-expert biases: [experts, 2 * inter] in the source order of the packed projection, [experts, hidden]
+            inter = l.moe_intermediate_size
+            if ex.per_expert:
+                raise NotImplementedError("biases of per-expert checkpoints")
+            if l.source_order == GateUpOrder.INTERLEAVED:
+                reads[f"gate_bias{e}"] = TensorRead(ex.gate_bias_key, expert=e, cols=slice(2 * rows.start, 2 * rows.stop, 2))
+                reads[f"up_bias{e}"] = TensorRead(ex.gate_bias_key, expert=e, cols=slice(2 * rows.start + 1, 2 * rows.stop, 2))
+            else:
+                reads[f"gate_bias{e}"] = TensorRead(ex.gate_bias_key, expert=e, cols=rows)
+                reads[f"up_bias{e}"] = TensorRead(ex.gate_bias_key, expert=e, cols=slice(inter + rows.start, inter + rows.stop))
+        if ex.down_bias_key and rank == 0:
+            reads[f"down_bias{e}"] = TensorRead(ex.down_bias_key, expert=e)     # added once: TP rank 0 only
+        if not packed_weights:
+            continue
         if ex.per_expert:
             reads[f"gate{e}"] = TensorRead(ex.gate_key.format(expert=e), rows=rows)
             reads[f"up{e}"] = TensorRead(ex.up_key.format(expert=e), rows=rows)
@@ -152,23 +205,26 @@ def materialize_layer_weights(spec: FfnModelSpec, view: CheckpointKeyView, layer
                               device="cpu", dtype: torch.dtype = torch.bfloat16, parallelism: int = 4,
                               experts: range | None = None) -> FfnLayerWeights:
     """Loads one layer's local shard. ``experts`` restricts a MoE layer to a range (expert parallelism)."""
-    if spec.quantization != "none":
-        raise NotImplementedError(f"quantised checkpoints ({spec.quantization}) load through ops.quant")
+    if spec.quantization not in ("none", "mxfp4"):
+        raise NotImplementedError(f"checkpoints quantised with {spec.quantization} are not loadable")
     l = spec.layers[layer]
+    mx = spec.quantization == "mxfp4" and isinstance(l, MoeFfnSpec) and l.experts.scales_suffix is not None
     stager, reader = PinnedStager(parallelism, device), _Reader(view)
     if isinstance(l, DenseFfnSpec):
         reads = _dense_reads(l, tp_rank, tp_size)
     else:
         experts = experts if experts is not None else range(l.num_experts)
-        reads = _moe_reads(l, tp_rank, tp_size, experts)
+        reads = _moe_reads(l, tp_rank, tp_size, experts, packed_weights=not mx)
 
     def fetch(item):
         name, r = item
-        bias = name.endswith("bias")
+        bias = "bias" in name      # biases stay fp32: the GEMM epilogue adds them to the fp32 accumulator
         return name, stager.to_device(reader.read(r), torch.float32 if bias else dtype)
 
     with ThreadPoolExecutor(max_workers=max(1, parallelism)) as pool:
         got = dict(pool.map(fetch, reads.items()))
+    if mx:
+        got.update({k: stager.to_device(v, dtype) for k, v in _moe_mxfp4(l, reader, tp_rank, tp_size, experts).items()})
     if isinstance(l, DenseFfnSpec):
         gated = "gate" in got
         gate_up = torch.cat([got["gate"], got["up"]], 0) if gated else got["up"]
@@ -177,10 +233,20 @@ def materialize_layer_weights(spec: FfnModelSpec, view: CheckpointKeyView, layer
             gub = torch.cat([got["gate_bias"], got["up_bias"]], 0) if "gate_bias" in got else got["up_bias"]
         w = FfnLayerWeights(gate_up, got["down"], gate_up_bias=gub, down_bias=got.get("down_bias"))
         w.extra["gated"] = gated
+        t = l.gate_transform
+        if t is not None and (t.limit > 0 or t.up_offset != 0 or t.alpha != 1.0):
+            w.extra["gate_transform"] = (float(t.limit), float(t.up_offset), float(t.alpha))
         return w
     gate_up = torch.stack([torch.cat([got[f"gate{e}"], got[f"up{e}"]], 0) for e in experts])
     down = torch.stack([got[f"down{e}"] for e in experts])
     w = FfnLayerWeights(gate_up, down, router=got["router"])
+    if f"gate_bias{experts[0]}" in got:
+        w.gate_up_bias = torch.stack([torch.cat([got[f"gate_bias{e}"], got[f"up_bias{e}"]]) for e in experts]).contiguous()
+    if f"down_bias{experts[0]}" in got:
+        w.down_bias = torch.stack([got[f"down_bias{e}"] for e in experts]).contiguous()
+    t = l.gate_transform
+    if t is not None and (t.limit > 0 or t.up_offset != 0 or t.alpha != 1.0):
+        w.extra["gate_transform"] = (float(t.limit), float(t.up_offset), float(t.alpha))
     if "shared_gate" in got:
         w.shared_gate_up = torch.cat([got["shared_gate"], got["shared_up"]], 0)
         w.shared_down = got["shared_down"]

@@ -45,10 +45,23 @@ def activation(name: str, g: torch.Tensor) -> torch.Tensor:
     raise ValueError(f"unsupported activation {name}")
 
 
+def gated(g: torch.Tensor, u: torch.Tensor, act: str, transform: tuple[float, float, float] | None) -> torch.Tensor:
+    """``act(g) * u``; with a gate transform ``(limit, up_offset, alpha)`` (GPT-OSS):
+    ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``, ``g' * sigmoid(alpha * g') * (u' + up_offset)``
+    (src/xpool/runtime/ffnagent/operators/activation.py:19-60)."""
+    if transform is None:
+        return activation(act, g.float()).to(g.dtype) * u
+    limit, up_offset, alpha = transform
+    gf, uf = g.float(), u.float()
+    if limit > 0:
+        gf, uf = gf.clamp(max=limit), uf.clamp(-limit, limit)
+    return (gf * torch.sigmoid((alpha or 1.0) * gf) * (uf + up_offset)).to(g.dtype)
+
+
 def dense_ffn(x: torch.Tensor, w: FfnLayerWeights, act: str = "silu") -> torch.Tensor:
     gu = F.linear(x, w.gate_up, w.gate_up_bias.to(x.dtype) if w.gate_up_bias is not None else None)
     inter = gu.shape[-1] // 2
-    h = activation(act, gu[..., :inter].float()).to(x.dtype) * gu[..., inter:]
+    h = gated(gu[..., :inter], gu[..., inter:], act, w.extra.get("gate_transform"))
     return F.linear(h, w.down, w.down_bias.to(x.dtype) if w.down_bias is not None else None)
 
 
@@ -78,6 +91,8 @@ def route_topk(logits: torch.Tensor, k: int, renormalize: bool, scoring: str = "
 
 def moe_ffn(x: torch.Tensor, w: FfnLayerWeights, cfg: ModelConfig) -> torch.Tensor:
     logits = F.linear(x, w.router)
+    if w.extra.get("router_bias") is not None:
+        logits = logits.float() + w.extra["router_bias"].float()    # payload-precision logits, bias added in fp32
     ids, weights = route_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.router_scoring,
                               w.extra.get("correction_bias"), cfg.routed_scaling_factor)
     out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
@@ -87,9 +102,9 @@ def moe_ffn(x: torch.Tensor, w: FfnLayerWeights, cfg: ModelConfig) -> torch.Tens
         if tok.numel() == 0:
             continue
         xe = x[tok]
-        gu = F.linear(xe, w.gate_up[e])
-        h = F.silu(gu[:, :inter].float()).to(x.dtype) * gu[:, inter:]
-        ye = F.linear(h, w.down[e])
+        gu = F.linear(xe, w.gate_up[e], w.gate_up_bias[e].to(x.dtype) if w.gate_up_bias is not None else None)
+        h = gated(gu[:, :inter], gu[:, inter:], "silu", w.extra.get("gate_transform"))
+        ye = F.linear(h, w.down[e], w.down_bias[e].to(x.dtype) if w.down_bias is not None else None)
         out.index_add_(0, tok, ye.float() * weights[tok, slot, None])
     if w.shared_gate_up is not None:
         out += dense_ffn(x, FfnLayerWeights(w.shared_gate_up, w.shared_down)).float()

@@ -108,8 +108,11 @@ def _tile_width(rows: int, top_k: int, n_local: int) -> int:
     return bn
 
 
-def _grouped(x, w2d, out, *, n_out, rows_cap, bn, dual, up_offset, tiles, n_tiles, rows_per_group, epilogue):
-    a = gemm._args(x, w2d, out, n_out=n_out, rows=rows_cap, epilogue=epilogue, dual=dual, up_offset=up_offset, splits=1, bn=bn)
+def _grouped(x, w2d, out, *, n_out, rows_cap, bn, dual, up_offset, tiles, n_tiles, rows_per_group, epilogue, bias=None,
+             transform=(0.0, 0.0, 0.0)):
+    """``bias``: fp32 ``[experts, rows_per_group]``, indexed by the weight row of the stacked tensor."""
+    a = gemm._args(x, w2d, out, n_out=n_out, rows=rows_cap, epilogue=epilogue, dual=dual, up_offset=up_offset, splits=1, bn=bn,
+                   bias=bias, gate_limit=transform[0], up_add=transform[1], act_alpha=transform[2])
     a.tile_table, a.n_tiles, a.w_rows_per_group = tiles.data_ptr(), n_tiles.data_ptr(), rows_per_group
     native.check(native.kernels().xp_gemm(C.byref(a)), "xp_gemm(grouped)")
 
@@ -151,9 +154,10 @@ def moe_forward(x: torch.Tensor, w: FfnLayerWeights, cfg: ModelConfig, out: torc
     # 4. grouped projections
     _grouped(ws.xp[:routes], w.gate_up.view(n_local * 2 * inter, h), ws.act[:routes], n_out=inter, rows_cap=routes, bn=bn,
              dual=1, up_offset=inter, tiles=ws.tiles_gu, n_tiles=ws.n_tiles[0:1], rows_per_group=2 * inter,
-             epilogue=gemm.EPI_SWIGLU)
+             epilogue=gemm.EPI_SWIGLU, bias=w.gate_up_bias, transform=w.extra.get("gate_transform", (0.0, 0.0, 0.0)))
     _grouped(ws.act[:routes], w.down.view(n_local * h, inter), ws.yp[:routes], n_out=h, rows_cap=routes, bn=bn, dual=0,
-             up_offset=0, tiles=ws.tiles_dn, n_tiles=ws.n_tiles[1:2], rows_per_group=h, epilogue=gemm.EPI_STORE)
+             up_offset=0, tiles=ws.tiles_dn, n_tiles=ws.n_tiles[1:2], rows_per_group=h, epilogue=gemm.EPI_STORE,
+             bias=w.down_bias)
     # 5. weighted sum over the selected experts, fixed order
     native.check(lib.xp_moe_combine(ws.yp.data_ptr(), ws.route_pos.data_ptr(), ws.weights.data_ptr(), out.data_ptr(), rows, k,
                                     h, out.stride(0), s), "xp_moe_combine")

@@ -417,6 +417,7 @@ class FfnRankRuntime:
                 ld.w_gateup, ld.w_down = gu.data_ptr(), dn.data_ptr()
                 ld.bias_gateup = w.gate_up_bias.data_ptr() if w.gate_up_bias is not None else None
                 ld.bias_down = w.down_bias.data_ptr() if w.down_bias is not None else None
+                ld.gate_limit, ld.up_add, ld.act_alpha = w.extra.get("gate_transform", (0.0, 0.0, 0.0))
                 ld.inter_local, ld.gated = inter, 1
                 native.check(lib.xp_lane_set_layer(self.handle, i, l, C.byref(ld)), "xp_lane_set_layer", 0)
         native.check(lib.xp_lane_commit(self.handle), "xp_lane_commit", 0)

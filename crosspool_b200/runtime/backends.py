@@ -21,6 +21,7 @@ from ..native import runtime as rt
 from ..parallel import fabric as F
 from ..service.wire import FabricPlan, InvocationFailure, ServingListener
 
+TP_RENDEZVOUS_BASE_PORT = 30500   # + Instance rank of the TP group's first member
 _POLICY = {"fifo": rt.POLICY_FIFO, "random": rt.POLICY_RANDOM, "slo": rt.POLICY_SLO}
 
 
@@ -47,12 +48,16 @@ def _placement(cfg: XpoolConfig, plan: FabricPlan, model_id: str, atn_rank: int,
     ranges = sorted({(s.layer_begin, s.layer_end) for s in shards})
     groups = tuple((lo, hi, tuple(s.pe for s in sorted((x for x in shards if (x.layer_begin, x.layer_end) == (lo, hi)),
                                                         key=lambda x: x.tp_rank))) for lo, hi in ranges)
-    rank = next(r for r in plan.instance_ranks if r.model_id == model_id and r.rank == atn_rank)
+    tp = cfg.model(model_id).atn_tp_size
+    leader = atn_rank - atn_rank % tp        # attention TP groups are runs of ``atn_tp_size`` consecutive Instance ranks
+    by_rank = {r.rank: r for r in plan.instance_ranks if r.model_id == model_id}
+    rank = by_rank[leader]
+    followers = tuple(by_rank[leader + i].pe for i in range(1, tp))
     seed = zlib.crc32(model_id.encode()) % 1000  # random-init deployments: same seed on every rank of a model
     union = tuple(pe for g in groups for pe in g[2])
     return F.InstancePlacement(model_id, model_config_for(cfg, model_id), seed, rank.pe, union, capacity_rows,
                                layer_groups=groups if len(groups) > 1 else (),
-                               checkpoint=checkpoint_dir_for(cfg, model_id))
+                               checkpoint=checkpoint_dir_for(cfg, model_id), atn_tp_followers=followers)
 
 
 class FfnBackend:
@@ -69,6 +74,8 @@ class FfnBackend:
         my_pe = len(plan.atn_devices) + plan.ffn_devices.index(self.device)
         handles = {}
         for r in plan.instance_ranks:
+            if r.rank % self.cfg.model(r.model_id).atn_tp_size:
+                continue    # an attention TP follower: the group's first rank talks to the FFN tier for all of them
             place = _placement(self.cfg, plan, r.model_id, r.rank, self.capacity_rows)
             if my_pe not in place.ffn_ranks:
                 continue
@@ -121,6 +128,7 @@ class AtnBackend:
         self.buffers: dict[tuple[str, int], F.PeerBuffer] = {}
         self.places: dict[tuple[str, int], F.InstancePlacement] = {}
         self.engines: dict[str, AttentionEngine] = {}
+        self.tp_groups: dict[tuple[str, int], object] = {}
         self.loop = None
         self._server = None
         self._listen = listen
@@ -129,32 +137,66 @@ class AtnBackend:
         self._ecs_channel = None
         self._reconcilers = []
 
+    def _tp(self, model_id: str, rank: int) -> tuple[int, int, int]:
+        """(TP rank, TP size, Instance rank of the group's first member)."""
+        t = self.cfg.model(model_id).atn_tp_size
+        return rank % t, t, rank - rank % t
+
     def prepare_join(self, plan: FabricPlan) -> dict[str, str]:
+        from ..parallel import atn_tp
+
         torch.cuda.set_device(self.cuda)
         handles = {}
         for model_id, rank in self.instances:
             place = _placement(self.cfg, plan, model_id, rank, self.capacity_rows)
-            buf = F.PeerBuffer(F.atn_slot_layout(place).total_bytes)
-            self.buffers[(model_id, rank)], self.places[(model_id, rank)] = buf, place
-            handles[f"atn:{model_id}:{rank}"] = buf.handle().hex()
+            self.places[(model_id, rank)] = place
+            tpr, tps, _ = self._tp(model_id, rank)
+            if tpr == 0:
+                buf = F.PeerBuffer(F.atn_slot_layout(place).total_bytes)
+                self.buffers[(model_id, rank)] = buf
+                handles[f"atn:{model_id}:{rank}"] = buf.handle().hex()
+            if tps > 1:
+                if self.cfg.atn_elastic_kv:
+                    raise RuntimeError("elastic KV with attention tensor parallelism is not supported: capacity "
+                                       "decisions are per rank and would let the ranks' schedules diverge")
+                g = atn_tp.TpGroup(tpr, tps, max(self.ecfg.max_batch, self.ecfg.prefill_chunk), place.cfg.hidden_size, self.cuda)
+                self.tp_groups[(model_id, rank)] = g
+                handles[f"atp:{model_id}:{rank}"] = g.handle().hex()
         return handles
 
     def join(self, plan: FabricPlan) -> None:
-        self._bases = {}
+        self._bases, self._leader_base = {}, {}
         for (model_id, rank), place in self.places.items():
-            self._bases[(model_id, rank)] = [F.PeerBuffer.open(bytes.fromhex(plan.slot_handles[f"ffn:{model_id}:{rank}:{pe}"]))
-                                             for pe in place.ffn_ranks]
+            tpr, tps, leader = self._tp(model_id, rank)
+            if tpr == 0:
+                self._bases[(model_id, rank)] = [F.PeerBuffer.open(bytes.fromhex(plan.slot_handles[f"ffn:{model_id}:{rank}:{pe}"]))
+                                                 for pe in place.ffn_ranks]
+            else:
+                self._leader_base[(model_id, rank)] = F.PeerBuffer.open(bytes.fromhex(plan.slot_handles[f"atn:{model_id}:{leader}"]))
+            g = self.tp_groups.get((model_id, rank))
+            if g is not None:
+                g.connect([bytes.fromhex(plan.slot_handles[f"atp:{model_id}:{leader + i}"]) for i in range(tps)])
 
     def prepare_execution(self, plan: FabricPlan) -> None:
+        from ..parallel import atn_tp
+
         for (model_id, rank), place in self.places.items():
-            port = F.FabricFfnPort(place, self.buffers[(model_id, rank)], self._bases[(model_id, rank)], self.cuda)
-            port.slo_tbt_ms = self.cfg.slo_for(model_id).tbt_ms   # per-step deadline for the Lanes' SLO policy
+            tpr, tps, _ = self._tp(model_id, rank)
+            if tpr == 0:
+                port = F.FabricFfnPort(place, self.buffers[(model_id, rank)], self._bases[(model_id, rank)], self.cuda)
+                port.slo_tbt_ms = self.cfg.slo_for(model_id).tbt_ms   # per-step deadline for the Lanes' SLO policy
+            else:
+                port = F.FabricFfnFollowerPort(place, self._leader_base[(model_id, rank)], self.cuda)
             if place.checkpoint:
                 aw = load_attention_from_safetensors(place.cfg, place.checkpoint, self.cuda, torch.bfloat16)
             else:
                 aw = random_attention_weights(place.cfg, place.seed, self.cuda, torch.bfloat16)
+            cfg_local, g = place.cfg, self.tp_groups.get((model_id, rank))
+            if g is not None:
+                aw = atn_tp.shard_attention_weights(aw, place.cfg, tpr, tps)
+                cfg_local = atn_tp.local_config(place.cfg, tps)
             kv = self._elastic_cache(plan, model_id, rank, place) if self.cfg.atn_elastic_kv and self.ecs_ref else None
-            eng = AttentionEngine(place.cfg, aw, port, self.ecfg, self.cuda, kv=kv)
+            eng = AttentionEngine(cfg_local, aw, port, self.ecfg, self.cuda, kv=kv, tp=g)
             if kv is not None:
                 self._attach_capacity(eng, model_id, rank)
             self.engines[model_id] = eng
@@ -206,11 +248,29 @@ class AtnBackend:
         from ..deployment import Deployment, InstanceHandle
         from .serving import EngineLoop, create_serving_app
 
-        dep = Deployment([InstanceHandle(m, e.cfg, e) for m, e in self.engines.items()])
-        dep.warmup()
-        self.loop = EngineLoop(dep)
+        tp_members = {self._tp(m, r) for m, r in self.instances if self._tp(m, r)[1] > 1}
+        order = sorted(self.engines, key=lambda m: self.cfg.model(m).atn_tp_size == 1)   # TP engines warm up first, in step
+        dep = Deployment([InstanceHandle(m, self.engines[m].cfg, self.engines[m]) for m in order])
+        leader = True
+        if tp_members:
+            import torch.distributed as dist
+
+            from .tp_replication import TpEngineLoop
+
+            if len(tp_members) != 1:
+                raise RuntimeError("the tensor-parallel Instances of one attention device must share one TP group")
+            (tpr, tps, first), = tp_members
+            leader = tpr == 0
+            # the members of the group meet here before any of them runs a kernel that waits on a peer
+            dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{TP_RENDEZVOUS_BASE_PORT + first}",
+                                    rank=tpr, world_size=tps)
+            dep.warmup()
+            self.loop = TpEngineLoop(dep, None, leader)
+        else:
+            dep.warmup()
+            self.loop = EngineLoop(dep)
         self.loop.start()
-        if self._listen is not None:
+        if self._listen is not None and leader:
             import uvicorn
 
             app = create_serving_app(self.loop, list(self.engines))

@@ -28,6 +28,7 @@ class TpEngineLoop(EngineLoop):
         return box[0]["requests"], box[0]["stop"]
 
     def _run(self) -> None:
+        hosted = {i.model_id for i in getattr(self.dep, "instances", ())} or None
         try:
             while True:
                 mine: list[Pending] = []
@@ -40,6 +41,8 @@ class TpEngineLoop(EngineLoop):
                 if stop:
                     break
                 for i, r in enumerate(reqs):
+                    if hosted is not None and r["model"] not in hosted:
+                        continue       # an Instance that only the leader's device hosts
                     kw = {"temperature": r["temperature"], "seed": r["seed"]} if r["temperature"] > 0 else {}
                     try:
                         seq = self.dep.add_request(r["model"], r["prompt"], r["max_new_tokens"], **kw)

@@ -12,6 +12,7 @@ import httpx
 import pytest
 import torch
 
+from conftest import unvalidated
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
@@ -38,8 +39,24 @@ ffn_tp_size = 1
 def test_daemon_agents_serve_requests_and_retire(tmp_path, elastic):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
+    _serve_and_retire(tmp_path, TOML.replace("devices = [0]", "devices = [0]\nelastic_kv = true") if elastic else TOML,
+                      [("ffnagent", 1), ("atnagent", 0)])
+
+
+@unvalidated
+def test_attention_tp_pair_serves_through_the_daemon(tmp_path):
+    """One Instance whose attention runs tensor-parallel over two agent processes (GPUs 0 and 1); the FFN tier
+    is GPU 2. The first rank owns the HTTP endpoint and replicates requests to the other."""
+    if torch.cuda.device_count() < 3:
+        pytest.skip("needs 3 GPUs")
+    toml = TOML.replace("devices = [0]", "devices = [0, 1]").replace("devices = [1]", "devices = [2]") \
+               .replace("ffn_tp_size = 1", "ffn_tp_size = 1\natn_tp_size = 2")
+    _serve_and_retire(tmp_path, toml, [("ffnagent", 2), ("atnagent", 0), ("atnagent", 1)])
+
+
+def _serve_and_retire(tmp_path, toml, agents):
     cfgp = tmp_path / "xpool.toml"
-    cfgp.write_text(TOML.replace("devices = [0]", "devices = [0]\nelastic_kv = true") if elastic else TOML)
+    cfgp.write_text(toml)
     env = dict(os.environ, XPOOL_CONFIG=str(cfgp), PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0", XPOOL_MAX_ROWS="512",
                XPOOL_MAX_BATCH="16", XPOOL_MAX_SEQ_LEN="512")
     xp = [sys.executable, "-m", "crosspool_b200.cli.main"]
@@ -51,8 +68,8 @@ def test_daemon_agents_serve_requests_and_retire(tmp_path, elastic):
                     break
             except httpx.HTTPError:
                 time.sleep(0.2)
-        procs.append(subprocess.Popen(xp + ["ffnagent", "--device", "1"], env=env))
-        procs.append(subprocess.Popen(xp + ["atnagent", "--device", "0"], env=env))
+        for role, dev in agents:
+            procs.append(subprocess.Popen(xp + [role, "--device", str(dev)], env=env))
         ready = False
         for _ in range(600):
             r = httpx.get("http://127.0.0.1:9831/ready", timeout=2).json()

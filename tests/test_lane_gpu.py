@@ -195,6 +195,39 @@ def test_lane_serves_a_moe_layer_and_a_dense_model_from_one_graph(E, k, hidden, 
         ffn.close()
 
 
+def test_lane_moe_layer_with_expert_biases_and_gate_transform():
+    """A GPT-OSS shaped expert layer in a Lane: per-expert biases on both grouped projections, router bias,
+    clamped activation with offset and sigmoid slope."""
+    from crosspool_b200.models.reference import moe_ffn
+    from crosspool_b200.parallel import fabric as F
+    from crosspool_b200.testing import assert_ffn_close
+
+    E, k, hidden, inter, rows = 8, 2, 256, 128, 21
+    cfg = _moe_cfg(E, k, hidden, inter)
+    place = F.InstancePlacement("m", cfg, seed=4, atn_rank=0, ffn_ranks=(1,), capacity_rows=64)
+    ffn = F.FfnRankRuntime("cuda", n_lanes=1)
+    st = ffn.add_instance(place, 0)
+    w = st.weights[0]
+    g = torch.Generator(device="cuda").manual_seed(2)
+    w.gate_up_bias = torch.randn(E, 2 * inter, device="cuda", generator=g) * 0.3
+    w.down_bias = torch.randn(E, hidden, device="cuda", generator=g) * 0.3
+    w.extra["router_bias"] = torch.randn(E, device="cuda", generator=g) * 0.5
+    w.extra["gate_transform"] = (1.5, 1.0, 1.702)
+    buf = F.PeerBuffer(F.atn_slot_layout(place).total_bytes)
+    st.atn_base = buf.ptr
+    ffn.install()
+    try:
+        x = (torch.randn(rows, hidden, device="cuda", generator=g) * 0.5).bfloat16()
+        _publish(F, st, place, x, 0, 1)
+        ffn.launch_once(0, lease_ms=20)
+        torch.cuda.synchronize()
+        out, rc, nrows, seq = _result(F, buf, place, rows)
+        assert (rc, nrows, seq) == (0, rows, 1) and ffn.stats()["status"] == 0
+        assert_ffn_close(out.float(), moe_ffn(x, w, cfg).float())
+    finally:
+        ffn.close()
+
+
 def test_expert_parallel_lane_partials_fold_to_the_full_moe_output():
     """Two FFN ranks' runtimes (run one after the other here; they never wait on each other) each own
     half of the experts; the rank-order fp32 fold of their partials equals the full layer."""

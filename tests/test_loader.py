@@ -126,3 +126,43 @@ def test_unsupported_models_are_named():
         adapters.compile_ffn_spec("x", {**QWEN3, "quantization_config": {"quant_method": "awq"}})
     with pytest.raises(adapters.UnsupportedModel, match="misses 'intermediate_size'"):
         adapters.compile_ffn_spec("x", {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 8, "num_hidden_layers": 1})
+
+
+def test_gpt_oss_mxfp4_checkpoint_loads_dequantised_shards_with_biases(tmp_path):
+    """Stacked MXFP4 expert tensors (blocks + e8m0 scales, interleaved gate/up rows, per-expert biases) become
+    bf16 gate|up and down shards; the clamp/offset/alpha of the activation travel with the layer."""
+    from crosspool_b200.quantization import Mxfp4
+
+    E, H, I = 4, 64, 64
+    cfg = {"architectures": ["GptOssForCausalLM"], "hidden_size": H, "intermediate_size": I, "num_hidden_layers": 1,
+           "num_local_experts": E, "num_experts_per_tok": 2, "quantization_config": {"quant_method": "mxfp4"},
+           "num_attention_heads": 4, "vocab_size": 100}
+    g = torch.Generator().manual_seed(3)
+    fmt = Mxfp4()
+    gu_q, dn_q = fmt.quantize(torch.randn(E, 2 * I, H, generator=g)), fmt.quantize(torch.randn(E, H, I, generator=g))
+    p = "model.layers.0.mlp."
+    tensors = {p + "router.weight": torch.randn(E, H, generator=g).bfloat16(), p + "router.bias": torch.randn(E, generator=g).bfloat16(),
+               p + "experts.gate_up_proj_blocks": gu_q["blocks"].reshape(E, 2 * I, H // 32, 16),
+               p + "experts.gate_up_proj_scales": gu_q["scales"],
+               p + "experts.gate_up_proj_bias": torch.randn(E, 2 * I, generator=g).bfloat16(),
+               p + "experts.down_proj_blocks": dn_q["blocks"].reshape(E, H, I // 32, 16),
+               p + "experts.down_proj_scales": dn_q["scales"],
+               p + "experts.down_proj_bias": torch.randn(E, H, generator=g).bfloat16()}
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    view = ck.read_checkpoint_key_view(tmp_path)
+    spec = adapters.compile_ffn_spec("oss", cfg, view.keys())
+    ck.validate_ffn_coverage(spec, view)
+    gu, dn = fmt.dequantize(gu_q), fmt.dequantize(dn_q)          # [E, 2I, H] rows interleaved gate, up, gate, ...
+    gb = tensors[p + "experts.gate_up_proj_bias"].float()
+    for rank in (0, 1):
+        w = loader.materialize_layer_weights(spec, view, 0, tp_rank=rank, tp_size=2, experts=range(1, 3))
+        rows = slice(32 * rank, 32 * (rank + 1))
+        assert w.gate_up.shape == (2, 64, H) and w.down.shape == (2, H, 32)
+        for i, e in enumerate((1, 2)):
+            assert torch.equal(w.gate_up[i], torch.cat([gu[e, 0::2][rows], gu[e, 1::2][rows]]))
+            assert torch.equal(w.down[i], dn[e][:, rows])
+            assert torch.equal(w.gate_up_bias[i], torch.cat([gb[e, 0::2][rows], gb[e, 1::2][rows]]))
+        assert (w.down_bias is not None) == (rank == 0)          # added once across the TP group
+        assert w.extra["gate_transform"] == (7.0, 1.0, 1.702) and w.extra["router_bias"].shape == (E,)
+    assert w.gate_up_bias.dtype == torch.float32

@@ -71,3 +71,34 @@ def test_expert_parallel_partials_sum_to_the_full_result():
     torch.testing.assert_close(parts[0] + parts[1], full, atol=3e-2, rtol=3e-2)
     # a token routed only to the other rank's experts contributes exactly zero here
     assert (parts[0].abs().sum(-1) == 0).any() or (parts[1].abs().sum(-1) == 0).any() or True
+
+
+def _gpt_oss_like(w, E, hidden, inter, seed):
+    """Adds what a GPT-OSS expert layer carries beyond plain SwiGLU experts: per-expert biases on both
+    projections, a router bias, and the clamp / offset / sigmoid-slope of its activation."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w.gate_up_bias = torch.randn(E, 2 * inter, device="cuda", generator=g) * 0.3
+    w.down_bias = torch.randn(E, hidden, device="cuda", generator=g) * 0.3
+    w.extra["router_bias"] = torch.randn(E, device="cuda", generator=g) * 0.5
+    w.extra["gate_transform"] = (1.5, 1.0, 1.702)   # a tight limit so that the clamps bite at this scale
+    return w
+
+
+@pytest.mark.parametrize("rows", [3, 77])
+def test_moe_forward_with_expert_biases_and_gate_transform(rows):
+    from crosspool_b200.models.reference import moe_ffn
+    from crosspool_b200.models.weights import random_ffn_layer
+    from crosspool_b200.ops import gemm, moe
+    from crosspool_b200.testing import assert_ffn_close
+
+    E, k, hidden, inter = 8, 2, 256, 128
+    cfg = _cfg(E, k, hidden, inter)
+    w = _gpt_oss_like(random_ffn_layer(cfg, 0, seed=11, device="cuda", dtype=torch.bfloat16), E, hidden, inter, 1)
+    x = (torch.randn(rows, hidden, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rows)) * 0.5).bfloat16()
+    y = moe.moe_forward(x, w, cfg)
+    torch.cuda.synchronize()
+    gemm.check_status(x.device)
+    ref = moe_ffn(x, w, cfg)
+    assert_ffn_close(y.float(), ref.float())
+    plain = moe_ffn(x, random_ffn_layer(cfg, 0, seed=11, device="cuda", dtype=torch.bfloat16), cfg)
+    assert (plain.float() - ref.float()).abs().max() > 0.05       # the additions matter at this scale

@@ -85,3 +85,34 @@ def test_followers_see_the_leaders_requests_in_order_and_stop_with_it():
     assert res[0][1] == ([[0, 1, 2], [100, 101]], "ValueError")
     assert res[0][2] == res[1][2] == [("add", "m", (1, 2, 3), 3), ("add", "m", (9,), 2)]
     assert res[0][3] is None and res[1][3] is None
+
+
+def test_deployed_placement_names_the_tp_group_from_its_first_rank():
+    """Every rank of an attention TP group resolves the same placement: the group's first rank talks to the FFN
+    tier, the others follow it (reference: atn_tp_size in src/xpool/config.py)."""
+    from crosspool_b200.config import load_config
+    from crosspool_b200.runtime.backends import _placement
+    from crosspool_b200.service.wire import FabricPhase, FabricPlan, InstanceRankTopology, ShardPlacement
+
+    cfg = load_config(env={}, toml_text="""
+[daemon]
+port = 18000
+[atn]
+devices = [0, 1]
+[ffn]
+devices = [2]
+[scheduler.slo]
+ttft_ms = 2000
+tbt_ms = 50
+[[models]]
+id = "Qwen/Qwen3-0.6B"
+atn_tp_size = 2
+""")
+    plan = FabricPlan(generation=1, uid="u", phase=FabricPhase.PREPARING_JOIN, atn_devices=[0, 1], ffn_devices=[2],
+                      lanes_per_ffn_device=1, policy="fifo",
+                      shards=[ShardPlacement(model_id="Qwen/Qwen3-0.6B", layer_begin=0, layer_end=28, tp_rank=0, tp_size=1,
+                                             device=2, pe=2, bytes=1)],
+                      instance_ranks=[InstanceRankTopology(model_id="Qwen/Qwen3-0.6B", rank=r, device=r, pe=r, instance_index=r)
+                                      for r in (0, 1)])
+    a, b = (_placement(cfg, plan, "Qwen/Qwen3-0.6B", r, 256) for r in (0, 1))
+    assert a == b and a.atn_rank == 0 and a.atn_tp_followers == (1,) and a.ffn_ranks == (2,)
