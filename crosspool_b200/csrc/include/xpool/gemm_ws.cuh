@@ -29,7 +29,7 @@ constexpr int kTileM = 128;    // weight rows per tile (UMMA M)
 constexpr int kTileK = 64;     // bf16 elements per K block = one 128-byte swizzle row
 constexpr int kMaxBnF8 = 64;   // widest activation tile of the block-scaled fp8 path (accumulators live in registers)
 constexpr int kUmmaK = 16;     // K per tcgen05.mma for 16-bit inputs
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 12;
 constexpr int kThreads = 192;
 constexpr int kEpilogueThreads = 128;
 
@@ -127,11 +127,6 @@ struct Barriers {
 
 __device__ __forceinline__ void record_status(uint32_t* status, uint32_t code) {
   if (status != nullptr) atomicCAS(status, 0u, code);
-}
-
-__device__ __forceinline__ float silu_like(float g, float alpha) {
-  float a = alpha == 0.f ? 1.f : alpha;
-  return g / (1.f + __expf(-a * g));
 }
 
 __device__ __forceinline__ float round_bf16(float v) {
@@ -415,34 +410,48 @@ __device__ __forceinline__ void epi_bar_sync() {
 // n .. n+15) of feature f and stores them. `fb` is the feature's weight row in
 // the whole weight tensor, which indexes the bias: equal to f except for
 // grouped problems, where every group (expert) has its own bias row.
+//
+// One warp per scheduler runs this, so nothing hides an instruction's latency
+// but the warp's own independent work: the 16 values are computed as 16
+// independent chains (fully unrolled, no early exit) and stored with
+// predicates, the epilogue kind is tested once per call.
 __device__ __forceinline__ void epilogue_store16(const Problem& p, int f, int fb, int n_first, int row_end,
                                                  const float* g, const float* u) {
   const float bias = p.bias != nullptr ? p.bias[fb] : 0.f;
-  const float bias_u = (p.bias != nullptr && p.dual) ? p.bias[p.up_offset + fb] : 0.f;
+  const int valid = row_end - n_first;  // > 0 by the callers' checks
+  const size_t o0 = static_cast<size_t>(n_first) * p.ld_out + f;
+  float v[16];
+  if (p.epilogue == kEpiSwiglu) {
+    const float bias_u = (p.bias != nullptr && p.dual) ? p.bias[p.up_offset + fb] : 0.f;
+    const float lim = p.gate_limit > 0.f ? p.gate_limit : 3.0e38f;
+    const float a = p.act_alpha == 0.f ? 1.f : p.act_alpha;
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const int n = n_first + j;
-    if (n >= row_end) break;
-    float v = g[j] + bias;
-    const size_t o = static_cast<size_t>(n) * p.ld_out + f;
-    if (p.epilogue == kEpiSwiglu) {
-      float gg = round_bf16(v);
-      float uu = round_bf16(u[j] + bias_u);
-      if (p.gate_limit > 0.f) {
-        gg = fminf(gg, p.gate_limit);
-        uu = fminf(fmaxf(uu, -p.gate_limit), p.gate_limit);
-      }
-      v = silu_like(gg, p.act_alpha) * (uu + p.up_add);
-      reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
-    } else if (p.epilogue == kEpiResidual) {
-      const __nv_bfloat16* r = reinterpret_cast<const __nv_bfloat16*>(p.resid);
-      v = round_bf16(v) + __bfloat162float(r[static_cast<size_t>(n) * p.ld_resid + f]);
-      reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
-    } else if (p.epilogue == kEpiStoreF32) {
-      reinterpret_cast<float*>(p.out)[o] = v;
-    } else {
-      reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
+    for (int j = 0; j < 16; ++j) {
+      const float gg = fminf(round_bf16(g[j] + bias), lim);
+      const float uu = fminf(fmaxf(round_bf16(u[j] + bias_u), -lim), lim);
+      v[j] = __fdividef(gg, 1.f + __expf(-a * gg)) * (uu + p.up_add);
     }
+  } else if (p.epilogue == kEpiResidual) {
+    const __nv_bfloat16* r = reinterpret_cast<const __nv_bfloat16*>(p.resid) + static_cast<size_t>(n_first) * p.ld_resid + f;
+    float rr[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) rr[j] = j < valid ? __bfloat162float(r[static_cast<size_t>(j) * p.ld_resid]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = round_bf16(g[j] + bias) + rr[j];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = g[j] + bias;
+  }
+  if (p.epilogue == kEpiStoreF32) {
+    float* o = reinterpret_cast<float*>(p.out) + o0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      if (j < valid) o[static_cast<size_t>(j) * p.ld_out] = v[j];
+  } else {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + o0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      if (j < valid) o[static_cast<size_t>(j) * p.ld_out] = __float2bfloat16_rn(v[j]);
   }
 }
 
@@ -506,11 +515,41 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
         if (j < p.bn) ws[static_cast<size_t>(j) * kTileM + lane_in_tile] = acc[j];
     }
   } else if (p.splits == 1) {
-    for (int col = 0; col < p.bn; col += 16) {
-      if (c.n0 + col >= c.row_end) break;
-      sm100::tmem_ld16(tmem_acc + col, g);
-      if (p.dual) sm100::tmem_ld16(tmem_acc + p.bn + col, u);
+    // Two register buffers: the TMEM read of the next 16 columns is in flight while the current
+    // ones go through the epilogue math and their stores. All conditions are warp-uniform.
+    const int ncol = min(p.bn, c.row_end - c.n0);  // columns that hold rows to store (> 0)
+    const uint32_t up = tmem_acc + static_cast<uint32_t>(p.bn);
+    uint32_t ga[16], ua[16], gb[16], ub[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) ua[j] = ub[j] = 0u;
+    sm100::tmem_ld16_issue(tmem_acc, ga);
+    if (p.dual) sm100::tmem_ld16_issue(up, ua);
+    for (int col = 0; col < ncol; col += 32) {
+      sm100::tmem_ld_wait32(ga, ua);
+      const bool more = col + 16 < ncol;
+      if (more) {
+        sm100::tmem_ld16_issue(tmem_acc + col + 16, gb);
+        if (p.dual) sm100::tmem_ld16_issue(up + col + 16, ub);
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        g[j] = __uint_as_float(ga[j]);
+        u[j] = __uint_as_float(ua[j]);
+      }
       epilogue_store16(p, f, fb, c.n0 + col, c.row_end, g, u);
+      if (more) {
+        sm100::tmem_ld_wait32(gb, ub);
+        if (col + 32 < ncol) {
+          sm100::tmem_ld16_issue(tmem_acc + col + 32, ga);
+          if (p.dual) sm100::tmem_ld16_issue(up + col + 32, ua);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          g[j] = __uint_as_float(gb[j]);
+          u[j] = __uint_as_float(ub[j]);
+        }
+        epilogue_store16(p, f, fb, c.n0 + col + 16, c.row_end, g, u);
+      }
     }
   } else {
     // Split-K: park raw partial sums, last-arriving CTA folds them in split order.

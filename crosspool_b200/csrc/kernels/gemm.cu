@@ -309,7 +309,7 @@ extern "C" int xp_gemm_plan(const XpGemmArgs* a, XpGemmPlan* plan) {
   plan->grid = std::min(plan->tiles, sms);
   plan->ws_bytes = splits > 1 ? static_cast<size_t>(tm) * tn * splits * acc_cols * gemm::kTileM * 4 : 0;
   plan->counter_bytes = splits > 1 ? static_cast<size_t>(tm) * tn * 4 : 0;
-  plan->smem_budget = 200 * 1024;
+  plan->smem_budget = 220 * 1024;
   if (a->smem_limit > 0 && a->smem_limit < plan->smem_budget) plan->smem_budget = std::max(a->smem_limit, 48 * 1024);
   gemm::SmemLayout L = gemm::smem_layout(bn, a->dual, plan->smem_budget);
   plan->smem_bytes = L.total_bytes;

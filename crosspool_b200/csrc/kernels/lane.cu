@@ -457,7 +457,7 @@ extern "C" int xp_lane_launch(void* h, int lane_index, uint64_t lease_ns, void* 
   lane::LaneCur* cur = rt->cur_d + lane_index;
   float* ws = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(rt->ws_d) + rt->ws_bytes_per_lane * lane_index);
   uint32_t* counters = rt->counters_d + lane::kCounterWords * lane_index;
-  const int smem_budget = 200 * 1024;
+  const int smem_budget = 220 * 1024;
   const int smem = smem_budget + 2048;
   const lane::MoeLaneWs* mws = rt->has_moe ? rt->mws_d + lane_index : nullptr;
   const lane::MoeLaneMaps* mmaps = rt->has_moe ? rt->mmaps_d + static_cast<size_t>(lane_index) * rt->n_instances : nullptr;

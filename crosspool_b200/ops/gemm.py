@@ -21,6 +21,10 @@ from .. import native
 # tile and fits beside one 98 KB decode-attention CTA of another stream on the same SM (227 KB per SM).
 DECODE_SMEM_LIMIT = 126 * 1024
 DECODE_ROWS = 256
+# ... but only for weight matrices this small: streaming a larger one is bound by the bytes a CTA keeps in
+# flight (measured: 5 stages of 24 KB per CTA reach 0.40 of the copy bandwidth on a 100 MB matrix), so it
+# takes every stage the SM can hold.
+DECODE_SMALL_WEIGHT_BYTES = 16 << 20
 EPI_STORE = 0
 EPI_SWIGLU = 1
 EPI_RESIDUAL = 2
@@ -131,7 +135,8 @@ def _args(x, w, out, *, n_out, rows, epilogue, dual=0, up_offset=0, bias=None, r
     a.up_add = up_add
     a.act_alpha = act_alpha
     # decode-size calls leave room for a second kernel on the SM (the co-located Instance's attention)
-    a.smem_limit = DECODE_SMEM_LIMIT if rows <= DECODE_ROWS else 0
+    small = w.shape[0] * k * 2 <= DECODE_SMALL_WEIGHT_BYTES
+    a.smem_limit = DECODE_SMEM_LIMIT if rows <= DECODE_ROWS and small else 0
     return a
 
 

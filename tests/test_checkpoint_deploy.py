@@ -108,7 +108,7 @@ def test_lane_runs_a_layer_loaded_from_a_checkpoint(tmp_path):
         torch.cuda.synchronize()
         out = buf.tensor(alay.output_offset, (place.capacity_rows, cfg.hidden_size), torch.bfloat16, "cuda")[:17].float()
         done = buf.tensor(alay.completion_offset, (64,), torch.int32, "cuda")
-        assert int(done[0]) == 1
+        assert (int(done[0]), int(done[1]), int(done[4])) == (0, 17, 1)      # result code, rows, sequence
         g, u, d = (t[f"model.layers.1.mlp.{n}_proj.weight"].cuda().float() for n in ("gate", "up", "down"))
         xf = x.float()
         ref = (torch.nn.functional.silu(xf @ g.t()) * (xf @ u.t())) @ d.t()
