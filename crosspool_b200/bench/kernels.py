@@ -82,14 +82,16 @@ def bench_gemm(ns, timer: Timer) -> dict:
         byts = wq.numel() + wscale.numel() * 4 + (x.numel() + out.numel()) * 2
         return report("gemm_ws_fp8_block", us, byts, 2.0 * ns.rows * ns.n * ns.k,
                       {"rows": ns.rows, "n": ns.n, "k": ns.k, "includes": "activation quantisation kernel"})
-    fn = (lambda: gemm.gateup_swiglu(x, w, out=out, splits=ns.splits, bn=ns.bn)) if ns.dual else \
-        (lambda: gemm.linear(x, w, out=out, splits=ns.splits, bn=ns.bn))
+    wk = gemm.tile_weight(w) if ns.tiled else w      # 128 x 64 blocks stored contiguously (one 16 KB run per TMA box)
+    fn = (lambda: gemm.gateup_swiglu(x, wk, out=out, splits=ns.splits, bn=ns.bn)) if ns.dual else \
+        (lambda: gemm.linear(x, wk, out=out, splits=ns.splits, bn=ns.bn))
     us = timer(fn)
     gemm.check_status(dev)
     plan = gemm.plan_shape(ns.n, ns.k, ns.rows, int(ns.dual))
     byts = (w.numel() + x.numel() + out.numel()) * 2
     return report("gemm_ws" + ("_swiglu" if ns.dual else ""), us, byts, 2.0 * ns.rows * w.shape[0] * ns.k,
-                  {"rows": ns.rows, "n": ns.n, "k": ns.k, "bn": ns.bn or plan["bn"], "splits": ns.splits or plan["splits"]})
+                  {"rows": ns.rows, "n": ns.n, "k": ns.k, "bn": ns.bn or plan["bn"], "splits": ns.splits or plan["splits"],
+                   "tiled": int(ns.tiled)})
 
 
 def bench_decode_attn(ns, timer: Timer) -> dict:
@@ -231,6 +233,7 @@ def main(argv: list[str] | None = None) -> int:
     g.add_argument("--dual", type=int, default=0)
     g.add_argument("--splits", type=int, default=0)
     g.add_argument("--bn", type=int, default=0)
+    g.add_argument("--tiled", type=int, default=0, help="1: weights pre-tiled into contiguous 128 x 64 blocks")
     g.add_argument("--fp8", type=int, default=0, help="1: block-scaled e4m3 weights and activations")
     a = sub.add_parser("decode-attn")
     a.add_argument("--batch", type=int, default=256)
