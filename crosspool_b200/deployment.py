@@ -65,12 +65,20 @@ class Deployment:
     def step(self) -> StepResult:
         """One iteration of every Instance that has work."""
         active = [i for i in self.instances if i.engine.has_work]
+        self.idle_tick()
         for i in active:
             i.engine.launch_step()
         res = StepResult()
         for i in active:
             res.tokens[i.model_id] = i.engine.collect_step()
         return res
+
+    def idle_tick(self) -> None:
+        """Lets Instances without work serve their elastic-KV capacity commands."""
+        for i in self.instances:
+            tick = getattr(i.engine, "idle_tick", None)
+            if tick is not None:
+                tick()
 
     def run_until_idle(self, max_steps: int = 1 << 30) -> int:
         n = 0

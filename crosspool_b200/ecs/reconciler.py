@@ -208,3 +208,103 @@ def cuda_event_gate(stream=None) -> Callable[[], bool]:
     ev = torch.cuda.Event()
     ev.record(stream or torch.cuda.current_stream())
     return ev.query
+
+
+class TpAgreedReconciler(CapacityReconciler):
+    """Capacity reconciler of one rank of an attention tensor-parallel group.
+
+    The ranks of a TP group run the same schedule without exchanging it, so everything the scheduler can see
+    of the KV capacity (which bundles hand out pages) has to change in the same engine step on every rank,
+    although each rank has its own partition, its own commands from the daemon and its own device memory.
+    ``agree(values)`` is an all-gather over the group (every rank calls it once per :meth:`poll`, in step order;
+    it returns every rank's list). With it the ranks act on a command only in a step in which *all* of them hold
+    an unserved command and none still has bundles in retirement, on the smallest of their targets; a growth is
+    kept only if every rank's mapping succeeded. What the scheduler cannot see stays local: unmapping behind
+    the retirement gate and the completion message. A rank whose peers get no command for ``patience`` steps
+    answers its own command without changing capacity, so that the daemon's policy never waits on it forever.
+
+    The reference agrees the same decisions over a gloo group of the TP ranks
+    (src/xpool/integrations/sglang/ecs/capacity.py:183-207).
+    """
+
+    def __init__(self, *args, agree: Callable[[list[int]], list[list[int]]], patience: int = 2000, **kw):
+        super().__init__(*args, **kw)
+        self.agree, self.patience = agree, patience
+        self._agreed: tuple[int, int] | None = None   # (own command sequence, agreed target) once acted on
+        self._waited = 0
+
+    def poll(self) -> None:
+        self._finish_retirements()
+        seq, target_bytes = self.channel.read_command(self.index)
+        if seq != self._done_command and (self._pending is None or self._pending[0] != seq):
+            self._pending = (seq, max(self.floor_bundles, target_bytes // self.bundle_bytes))
+            self._agreed = None
+        unserved = self._pending is not None and self._agreed is None
+        votes = self.agree([int(unserved), self._pending[1] if unserved else 0, len(self._retiring)])
+        if unserved:
+            if all(v[0] for v in votes) and not any(v[2] for v in votes):
+                self._agreed = (self._pending[0], min(v[1] for v in votes))
+                self._waited = 0
+                self._act_on_agreement()
+            else:
+                self._waited += 1
+                if self._waited > self.patience:     # the peers were given no command: answer, capacity unchanged
+                    self.events.append(("unanswered", self._pending[0]))
+                    self._waited = 0
+                    self._complete(self._pending[0])
+            return
+        if self._agreed is not None:
+            self._continue_shrink()
+
+    def _act_on_agreement(self) -> None:
+        seq, target = self._agreed
+        live = len(self.cache.allocator.mapped_bundles())
+        if target > live:
+            take = self.cache.allocator.unmapped_bundles()[: target - live]   # nothing is retiring on any rank
+            rc = self.cache.backing.try_map(take) if take else 0
+            ok = all(v[0] for v in self.agree([int(rc == 0), 0, 0]))
+            if ok:
+                for b in take:
+                    self.cache.allocator.publish_bundle(b)
+                self.events.append(("grow", len(take)))
+            elif rc == 0 and take:
+                self.cache.backing.unmap(take)     # a peer could not map: nobody grows
+            self._finish(seq)
+            return
+        self._continue_shrink()
+
+    def _continue_shrink(self) -> None:
+        seq, target = self._agreed
+        excess = len(self.cache.allocator.mapped_bundles()) - target
+        for b in sorted(self.retirable_empty(), reverse=True)[:max(0, excess)]:
+            self.cache.allocator.begin_retirement(b)
+            self._retiring.append(_Retiring(b, self.gate_factory()))
+            self.events.append(("retire", b))
+        self._finish_retirements()
+        if len(self.cache.allocator.mapped_bundles()) <= target and not self._retiring:
+            self._finish(seq)
+
+    def _finish(self, seq: int) -> None:
+        self._agreed = None
+        self._complete(seq)
+
+    def bundles_to_vacate(self) -> int:
+        if self._agreed is None:
+            return 0
+        return max(0, len(self.cache.allocator.mapped_bundles()) - self._agreed[1])
+
+
+def gloo_agreement(group=None) -> Callable[[list[int]], list[list[int]]]:
+    """``agree`` for :class:`TpAgreedReconciler` over a ``torch.distributed`` CPU group (three integers per rank)."""
+    import torch
+    import torch.distributed as dist
+
+    n = dist.get_world_size(group)
+
+    def agree(values: list[int]) -> list[list[int]]:
+        mine = torch.tensor(values, dtype=torch.int64)
+        out = [torch.empty_like(mine) for _ in range(n)]
+        dist.all_gather(out, mine, group=group)
+        return [t.tolist() for t in out]
+
+    return agree

@@ -163,6 +163,12 @@ class AttentionEngine:
             self.stats["retracted_for_shrink"] = self.stats.get("retracted_for_shrink", 0) + 1
             rec.poll()
 
+    def idle_tick(self) -> None:
+        """Serves capacity commands while there is nothing to run: an idle Instance is the usual donor of a
+        shrink, and nothing else would look at its command."""
+        if self.capacity is not None and not self.has_work:
+            self._capacity_tick()
+
     def _publish_demand(self, missing_pages: int, head: "Sequence | None") -> None:
         if self.capacity is None or missing_pages == self._demand_pages:
             return

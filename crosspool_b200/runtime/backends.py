@@ -129,6 +129,7 @@ class AtnBackend:
         self.places: dict[tuple[str, int], F.InstancePlacement] = {}
         self.engines: dict[str, AttentionEngine] = {}
         self.tp_groups: dict[tuple[str, int], object] = {}
+        self._agree = None
         self.loop = None
         self._server = None
         self._listen = listen
@@ -156,9 +157,6 @@ class AtnBackend:
                 self.buffers[(model_id, rank)] = buf
                 handles[f"atn:{model_id}:{rank}"] = buf.handle().hex()
             if tps > 1:
-                if self.cfg.atn_elastic_kv:
-                    raise RuntimeError("elastic KV with attention tensor parallelism is not supported: capacity "
-                                       "decisions are per rank and would let the ranks' schedules diverge")
                 g = atn_tp.TpGroup(tpr, tps, max(self.ecfg.max_batch, self.ecfg.prefill_chunk), place.cfg.hidden_size, self.cuda)
                 self.tp_groups[(model_id, rank)] = g
                 handles[f"atp:{model_id}:{rank}"] = g.handle().hex()
@@ -195,17 +193,17 @@ class AtnBackend:
             if g is not None:
                 aw = atn_tp.shard_attention_weights(aw, place.cfg, tpr, tps)
                 cfg_local = atn_tp.local_config(place.cfg, tps)
-            kv = self._elastic_cache(plan, model_id, rank, place) if self.cfg.atn_elastic_kv and self.ecs_ref else None
+            kv = self._elastic_cache(plan, model_id, rank, cfg_local) if self.cfg.atn_elastic_kv and self.ecs_ref else None
             eng = AttentionEngine(cfg_local, aw, port, self.ecfg, self.cuda, kv=kv, tp=g)
             if kv is not None:
-                self._attach_capacity(eng, model_id, rank)
+                self._attach_capacity(eng, model_id, rank, tp=g is not None)
             self.engines[model_id] = eng
         if self._ecs_channel is not None:
             free, total = torch.cuda.mem_get_info(self.cuda)
             self._ecs_channel.publish_report(self._ecs_ref.devices[str(self.device)], free, total, 1)
 
     # ------------------------------------------------------------------ elastic KV
-    def _elastic_cache(self, plan: FabricPlan, model_id: str, rank: int, place):
+    def _elastic_cache(self, plan: FabricPlan, model_id: str, rank: int, model_cfg):
         """A KV cache over VMM bundles with one bundle mapped; the Instance rank describes its partition
         (floor = one bundle, reservation = the whole range) in the daemon's control channel."""
         import time
@@ -227,17 +225,23 @@ class AtnBackend:
         e = self.ecfg
         max_blocks = (e.max_seq_len + e.page_size - 1) // e.page_size
         pages = e.num_pages or e.max_batch * max_blocks
-        kv = vmm.elastic_kv_cache(place.cfg, pages, e.page_size, self.cuda, self._driver, self._quota, initial_bundles=1)
+        kv = vmm.elastic_kv_cache(model_cfg, pages, e.page_size, self.cuda, self._driver, self._quota, initial_bundles=1)
         idx = self._ecs_ref.partitions[f"{model_id}:{rank}"]
         bb = kv.backing.bundle_bytes
         self._ecs_channel.set_partition(idx, self.device, 0, rank, bb, kv.backing.bundle_count * bb)
         return kv
 
-    def _attach_capacity(self, eng, model_id: str, rank: int) -> None:
+    def _attach_capacity(self, eng, model_id: str, rank: int, tp: bool = False) -> None:
         from ..ecs import reconciler as R
 
         idx = self._ecs_ref.partitions[f"{model_id}:{rank}"]
-        rec = R.CapacityReconciler(eng.kv, self._ecs_channel, idx, gate_factory=lambda e=eng: R.cuda_event_gate(e.stream))
+        gate = lambda e=eng: R.cuda_event_gate(e.stream)
+        if tp:
+            # the ranks of the TP group agree every capacity change over their gloo group, which exists from
+            # warm_and_serve on (before the first engine step)
+            rec = R.TpAgreedReconciler(eng.kv, self._ecs_channel, idx, gate_factory=gate, agree=lambda v: self._agree(v))
+        else:
+            rec = R.CapacityReconciler(eng.kv, self._ecs_channel, idx, gate_factory=gate)
         eng.attach_capacity(rec, ttft_slo_s=self.cfg.slo_for(model_id).ttft_ms / 1e3)
         self._reconcilers.append(rec)
 
@@ -264,6 +268,9 @@ class AtnBackend:
             # the members of the group meet here before any of them runs a kernel that waits on a peer
             dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{TP_RENDEZVOUS_BASE_PORT + first}",
                                     rank=tpr, world_size=tps)
+            from ..ecs.reconciler import gloo_agreement
+
+            self._agree = gloo_agreement(None)
             dep.warmup()
             self.loop = TpEngineLoop(dep, None, leader)
         else:

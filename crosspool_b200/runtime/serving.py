@@ -97,12 +97,18 @@ class EngineLoop:
             except Exception as e:  # bad request: answer it, keep serving
                 p.deliver(e)
 
+    def _idle(self) -> None:
+        tick = getattr(self.dep, "idle_tick", None)
+        if tick is not None:
+            tick()          # idle Instances still answer elastic-KV capacity commands
+        time.sleep(self.idle_sleep)
+
     def _run(self) -> None:
         try:
             while not self._stop.is_set():
                 self._admit()
                 if not self.dep.has_work:
-                    time.sleep(self.idle_sleep)
+                    self._idle()
                     continue
                 res = self.dep.step()
                 self.steps += 1

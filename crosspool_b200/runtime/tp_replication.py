@@ -52,7 +52,7 @@ class TpEngineLoop(EngineLoop):
                         if self.leader:
                             mine[i].deliver(e)
                 if not self.dep.has_work:
-                    time.sleep(self.idle_sleep)
+                    self._idle()       # the same number of idle ticks on every rank: one per exchange
                     continue
                 res = self.dep.step()
                 self.steps += 1

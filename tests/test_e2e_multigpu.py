@@ -44,13 +44,16 @@ def test_daemon_agents_serve_requests_and_retire(tmp_path, elastic):
 
 
 @unvalidated
-def test_attention_tp_pair_serves_through_the_daemon(tmp_path):
+@pytest.mark.parametrize("elastic", [False, True])
+def test_attention_tp_pair_serves_through_the_daemon(tmp_path, elastic):
     """One Instance whose attention runs tensor-parallel over two agent processes (GPUs 0 and 1); the FFN tier
     is GPU 2. The first rank owns the HTTP endpoint and replicates requests to the other."""
     if torch.cuda.device_count() < 3:
         pytest.skip("needs 3 GPUs")
     toml = TOML.replace("devices = [0]", "devices = [0, 1]").replace("devices = [1]", "devices = [2]") \
                .replace("ffn_tp_size = 1", "ffn_tp_size = 1\natn_tp_size = 2")
+    if elastic:      # capacity changes are agreed between the two ranks over their gloo group
+        toml = toml.replace("devices = [0, 1]", "devices = [0, 1]\nelastic_kv = true")
     _serve_and_retire(tmp_path, toml, [("ffnagent", 2), ("atnagent", 0), ("atnagent", 1)])
 
 

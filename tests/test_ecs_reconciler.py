@@ -136,3 +136,71 @@ def test_policy_and_two_reconcilers_move_memory_from_the_idle_partition_to_the_b
     kinds = [e.kind for e in pol.events]
     assert "grow" in kinds and "shrink" in kinds
     assert q.charged == 7 * bb
+
+
+class _LockstepAgreement:
+    """All-gather between reconcilers driven from one thread each (stands in for the gloo group)."""
+
+    def __init__(self, n):
+        import threading
+
+        self.n, self.slots, self.barrier = n, [None] * n, threading.Barrier(n)
+
+    def for_rank(self, r):
+        def agree(values):
+            self.slots[r] = list(values)
+            self.barrier.wait(10)
+            out = [list(v) for v in self.slots]
+            self.barrier.wait(10)
+            return out
+        return agree
+
+
+def test_tp_ranks_change_capacity_in_the_same_step_on_the_smallest_target():
+    import threading
+
+    ch = EcsChannel.create(f"/xp-test-recon-tp-{os.getpid()}", 1, 2, 1)
+    try:
+        ag = _LockstepAgreement(2)
+        caches = [_cache(initial=1) for _ in range(2)]
+        recs = [R.TpAgreedReconciler(c[0], ch, i, agree=ag.for_rank(i), patience=3) for i, c in enumerate(caches)]
+        bb, ppb = recs[0].bundle_bytes, caches[0][1]
+        history = [[], []]
+
+        def steps(n):
+            def run(i):
+                for _ in range(n):
+                    recs[i].poll()
+                    history[i].append(len(caches[i][0].allocator.mapped_bundles()))
+            ts = [threading.Thread(target=run, args=(i,)) for i in range(2)]
+            for t in ts:
+                t.start()
+            for t in ts:
+                t.join(20)
+                assert not t.is_alive()
+
+        ch.publish_command(0, 1, 4 * bb)                 # only rank 0 has its command yet
+        steps(2)
+        assert history == [[1, 1], [1, 1]]
+        ch.publish_command(1, 1, 3 * bb)                 # rank 1 is granted less: both grow to 3, in the same step
+        steps(1)
+        assert history[0][-1] == history[1][-1] == 3
+        assert ch.read_completion(0) == (1, 3 * bb) and ch.read_completion(1) == (1, 3 * bb)
+        for c, _, _ in caches:                            # identical allocations on both ranks
+            assert R.admit(c, [(1, 16 * ppb), (2, 16 * ppb)]).admitted
+        ch.publish_command(0, 2, 1 * bb)
+        ch.publish_command(1, 2, 2 * bb)                 # shrink: the smaller target (1) on both, one bundle is free now
+        steps(1)
+        assert history[0][-1] == history[1][-1] == 2 and all(r.bundles_to_vacate() == 1 for r in recs)
+        for c, _, _ in caches:
+            c.release(2)
+        steps(2)
+        assert history[0][-1] == history[1][-1] == 1
+        assert ch.read_completion(0) == (2, bb) and ch.read_completion(1) == (2, bb)
+        ch.publish_command(0, 3, 2 * bb)                 # a command that the peer never receives is answered unchanged
+        steps(5)
+        assert history[0][-1] == history[1][-1] == 1 and ch.read_completion(0) == (3, bb)
+        assert ("unanswered", 3) in recs[0].events
+        assert history[0] == history[1]
+    finally:
+        ch.close()
