@@ -114,7 +114,13 @@ def stage_bytes(weights: int, slots: int, n_models: int, n_layers: int, lanes: i
 
 
 def place_ffn_models(models: list[ModelDemand], devices: list[DeviceSupply], *, margin_bytes: int = 0, lanes: int = 1,
-                     ws_per_lane: int = 64 << 20, timeout_seconds: float = 60.0) -> PlacementResult:
+                     ws_per_lane: int = 64 << 20, timeout_seconds: float = 60.0,
+                     stagnation_nodes: int | None = None) -> PlacementResult:
+    """Depth-first search over whole-model placements (then greedy layer splits) with the lexicographic objective
+    (fewest materialisations, largest minimum headroom, smallest total peak). Small deployments are searched
+    exhaustively; the search also stops when ``stagnation_nodes`` options were explored since the incumbent last
+    improved (default ``max(4000, 40 * models)``), which keeps planning of deployments with hundreds of
+    co-located models to a few seconds: the first leaf already takes the most-headroom choice at every step."""
     if not devices:
         raise PlacementError("no FFN devices")
     ids = [d.device for d in devices]
@@ -124,8 +130,9 @@ def place_ffn_models(models: list[ModelDemand], devices: list[DeviceSupply], *, 
             raise PlacementError(f"model {m.model_id}: ffn_tp_size {m.tp_size} exceeds {len(ids)} FFN devices")
     order = sorted(range(len(models)), key=lambda i: (-sum(models[i].layer_bytes), models[i].model_id))
     t0 = time.monotonic()
-    best: dict = {"score": None, "groups": None}
+    best: dict = {"score": None, "groups": None, "at": 0}
     explored = 0
+    stagnation = stagnation_nodes if stagnation_nodes is not None else max(4000, 40 * len(models))
 
     def peak(st: _State, d: int) -> int:
         return stage_bytes(st.weights[d], st.slots[d], len(st.models_on[d]), st.layers_on[d], lanes, ws_per_lane).peak
@@ -184,12 +191,12 @@ def place_ffn_models(models: list[ModelDemand], devices: list[DeviceSupply], *, 
 
     def dfs(k: int, st: _State, acc: list[LayerGroupPlacement]) -> None:
         nonlocal explored
-        if time.monotonic() - t0 > timeout_seconds and best["groups"] is not None:
+        if best["groups"] is not None and (explored - best["at"] > stagnation or time.monotonic() - t0 > timeout_seconds):
             return
         if k == len(order):
             sc = score(st)
             if best["score"] is None or sc < best["score"]:
-                best["score"], best["groups"], best["state"] = sc, list(acc), st
+                best["score"], best["groups"], best["state"], best["at"] = sc, list(acc), st, explored
             return
         if best["score"] is not None and sum(len(s) for s in st.models_on.values()) > best["score"][0]:
             return  # already more materialisations than the incumbent

@@ -262,3 +262,54 @@ def test_terminate_owner_only_signals_registered_participants():
     with pytest.raises(DaemonError):
         w.cp.terminate_owner(ProcessRef(abi_version=ABI_VERSION, pid=1, create_time=1.0), terminate=lambda r: [r.pid])
     assert killed == [4242]
+
+
+def test_thousand_instance_rank_leases_plan_join_and_become_ready():
+    """Topology scale of the reference's qualification plan (docs/designs/qualification.md:134-147): 1,000 Transport
+    arena leases (125 co-located models x 8 data-parallel ranks over 8 attention and 4 FFN devices) go through
+    planning, the generation barrier, arena brokering and readiness in bounded time."""
+    import time
+
+    n_models, dp, atn, ffn = 125, 8, list(range(8)), [8, 9, 10, 11]
+    toml = (f"[atn]\ndevices = {atn}\n[ffn]\ndevices = {ffn}\n[scheduler]\nffn_concurrency = 2\n"
+            "[scheduler.slo]\nttft_ms = 1000\ntbt_ms = 50\n")
+    for i in range(n_models):
+        toml += f'[[models]]\nid = "org/m{i}"\npath = "Qwen/Qwen3-0.6B"\nffn_tp_size = 1\natn_dp_size = {dp}\n'
+    alive = set()
+
+    def ref(pid):
+        alive.add(pid)
+        return ProcessRef(abi_version=ABI_VERSION, pid=pid, create_time=1.0)
+
+    cp = ControlPlane(C.load_config(env={}, toml_text=toml), clock=FakeClock(), process_alive=lambda r: r.pid in alive)
+    t0 = time.monotonic()
+    for d in atn:
+        cp.register_atnagent(AtnAgentRegistration(owner=ref(10 + d), device=d))
+    for d in ffn:
+        cp.register_ffnagent(FfnAgentRegistration(owner=ref(10 + d), device=d, device_free_memory_bytes=170 << 30,
+                                                  device_total_memory_bytes=180 << 30))
+    prof = InstanceFfnProfile(max_prefill_rows=256, max_decode_rows=32, hidden_size=1024)
+    owners = {}
+    for i in range(n_models):
+        for r in range(dp):
+            owners[(f"org/m{i}", r)] = ref(1000 + i * dp + r)
+            cp.register_instance(InstanceRankRegistration(owner=owners[(f"org/m{i}", r)], model_id=f"org/m{i}", rank=r,
+                                                          device=r, ffn_profile=prof))
+    g = cp.generation
+    assert g is not None and len(g.plan.instance_ranks) == 1000 and len(g.plan.shards) == n_models
+    per_device = {d: sum(1 for s in g.plan.shards if s.device == d) for d in ffn}
+    assert max(per_device.values()) - min(per_device.values()) <= 1          # headroom objective balances the tier
+    for ph in (ParticipantPhase.JOIN_READY, ParticipantPhase.JOINED, ParticipantPhase.EXECUTION_READY, ParticipantPhase.ACTIVE):
+        for pe, key in g.participants.items():
+            cp.report_participant(ParticipantReport(owner=ref(10 + int(key.split(":")[1])), generation=g.number, pe=pe, phase=ph))
+    assert g.phase == FabricPhase.EXECUTABLE
+    for d in atn:
+        cp.upsert_arenas(d, ref(10 + d), g.number, [TransportArenaBinding(model_id=f"org/m{i}", rank=d, handle_hex=f"{i:04x}", nbytes=64)
+                                                    for i in range(n_models)])
+    for (mid, r), owner in owners.items():
+        assert cp.acquire_arena(mid, r, owner, g.number).handle_hex == f"{int(mid[5:]):04x}"
+        cp.instance_initialized(mid, InstanceRankInitialized(owner=owner, rank=r, generation=g.number))
+    rd = cp.readiness()
+    assert rd.system_ready and len(rd.instance_ranks) == 1000
+    assert sorted(len(cp.quiesce_leases(d, ref(10 + d))) for d in atn) == [n_models] * 8
+    assert time.monotonic() - t0 < 30.0
