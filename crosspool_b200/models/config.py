@@ -93,6 +93,11 @@ PRESETS: dict[str, ModelConfig] = {
     "tiny-qwen3": ModelConfig(name="tiny-qwen3", architecture="Qwen3ForCausalLM", hidden_size=256, num_layers=2,
                               num_q_heads=4, num_kv_heads=2, head_dim=64, intermediate_size=768, vocab_size=4096,
                               dtype="float32"),
+    # the partner of Qwen3-0.6B in the reference's small benchmark pair (benches/benches.toml): 14 query / 2 KV heads
+    # of 64, q/k/v biases, no q/k norm, rope theta 1e6
+    "Qwen/Qwen2.5-0.5B": ModelConfig(name="Qwen/Qwen2.5-0.5B", architecture="Qwen2ForCausalLM", hidden_size=896, num_layers=24,
+                                     num_q_heads=14, num_kv_heads=2, head_dim=64, intermediate_size=4864, vocab_size=151936,
+                                     rope_theta=1e6, qk_norm=False, attention_bias=True, tie_word_embeddings=True),
     "Qwen/Qwen3-0.6B": _qwen3("Qwen/Qwen3-0.6B", 28, 1024, 16, 8, 3072, tie_word_embeddings=True),
     "Qwen/Qwen3-1.7B": _qwen3("Qwen/Qwen3-1.7B", 28, 2048, 16, 8, 6144, tie_word_embeddings=True),
     "Qwen/Qwen3-8B": _qwen3("Qwen/Qwen3-8B", 36, 4096, 32, 8, 12288),

@@ -99,6 +99,7 @@ def random_attention_weights(cfg: ModelConfig, seed: int = 0, device="cpu", dtyp
             o=_randn(gen, (cfg.hidden_size, cfg.q_size), dt, device),
             q_norm=torch.ones(cfg.head_dim, dtype=dt, device=device) if cfg.qk_norm else None,
             k_norm=torch.ones(cfg.head_dim, dtype=dt, device=device) if cfg.qk_norm else None,
+            qkv_bias=(_randn(gen, (cfg.q_size + 2 * cfg.kv_size,), torch.float32, device) * 5.0) if cfg.attention_bias else None,
         ))
     final_norm = torch.ones(cfg.hidden_size, dtype=dt, device=device)
     lm_head = embed if cfg.tie_word_embeddings else _randn(gen, (cfg.vocab_size, cfg.hidden_size), dt, device)

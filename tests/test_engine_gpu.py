@@ -61,6 +61,26 @@ def test_loopback_engine_matches_reference_logits(graph):
             assert kl[1:].max().item() <= 0.005
 
 
+def test_qwen2_shape_with_qkv_bias_and_seven_query_heads_per_kv_head():
+    """Qwen2.5-0.5B: 14 query / 2 KV heads of 64 (7 per group, the padded tensor-core decode path and the plain
+    prefill kernel), q/k/v biases, no q/k norm, hidden 896."""
+    cfg, eng, ref = _build("Qwen/Qwen2.5-0.5B", layers=2, max_batch=8, prefill_chunk=256, max_seq_len=512)
+    eng.warmup()
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 40, 150)]
+    seqs = [eng.add_request(p, 4) for p in prompts]
+    first = {}
+    while eng.has_work:
+        for i, (s, tok) in enumerate(eng.step()):
+            first.setdefault(s.seq_id, eng.logits[i].clone())
+    from crosspool_b200.ops import gemm
+    gemm.check_status(eng.device)
+    for s, p in zip(seqs, prompts):
+        toks, ref_logits = ref.generate(torch.tensor(p, device="cuda"), 4)
+        assert _kl(ref_logits[:1], first[s.seq_id][None]).item() <= 0.05
+        assert s.generated[0] == toks[0]
+
+
 def test_chunked_prefill_equals_single_chunk():
     cfg, eng_small, _ = _build("Qwen/Qwen3-0.6B", layers=2, max_batch=4, prefill_chunk=64, max_seq_len=512,
                                use_cuda_graph=False)
