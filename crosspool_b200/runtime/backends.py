@@ -265,7 +265,11 @@ class AtnBackend:
                 raise RuntimeError("the tensor-parallel Instances of one attention device must share one TP group")
             (tpr, tps, first), = tp_members
             leader = tpr == 0
-            # the members of the group meet here before any of them runs a kernel that waits on a peer
+            # the members of the group meet here before any of them runs a kernel that waits on a peer; they
+            # share the host, so the loopback interface carries the group (the host name may not resolve)
+            import os
+
+            os.environ.setdefault("GLOO_SOCKET_IFNAME", "lo")
             dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{TP_RENDEZVOUS_BASE_PORT + first}",
                                     rank=tpr, world_size=tps)
             from ..ecs.reconciler import gloo_agreement
@@ -306,3 +310,6 @@ class AtnBackend:
         for b in self.buffers.values():
             b.free()
         self.buffers.clear()
+        for g in self.tp_groups.values():
+            g.close()
+        self.tp_groups.clear()
