@@ -103,7 +103,8 @@ def main(argv: list[str] | None = None) -> int:
     from . import suite
 
     ap = argparse.ArgumentParser(prog="python -m crosspool_b200.bench.serve_case")
-    ap.add_argument("--case", default="poisson-16", choices=sorted(suite.CASES))
+    ap.add_argument("--case", default="poisson-16", help=f"one of {sorted(suite.CASES)} or a case of --catalogue")
+    ap.add_argument("--catalogue", default="", help="TOML catalogue with further cases (configs/benches.toml)")
     ap.add_argument("--models", nargs="+", default=["Qwen/Qwen3-0.6B"])
     ap.add_argument("--atn", type=int, nargs="+", default=[0])
     ap.add_argument("--ffn", type=int, nargs="+", default=[1])
@@ -118,7 +119,12 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--rate", type=float, default=0.0, help="override the case's per-model request rate")
     ap.add_argument("--out", default="")
     ns = ap.parse_args(argv)
-    case = suite.CASES[ns.case]
+    cases = dict(suite.CASES)
+    if ns.catalogue:
+        cases.update(suite.load_catalogue(ns.catalogue))
+    if ns.case not in cases:
+        ap.error(f"unknown case {ns.case!r}; known: {sorted(cases)}")
+    case = cases[ns.case]
     if ns.duration > 0 or ns.rate > 0:
         import dataclasses
 
