@@ -478,24 +478,39 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
     const int kb_total = p.k / p.kblk;
     const float* wsc = p.w_scale + static_cast<size_t>(c.w_row0 >> 7) * kb_total + c.kb0;
     for (int i = 0; i < c.kbn; ++i) {
+      // The scales of this K block do not depend on its MMAs: their loads are issued before the wait
+      // for the accumulator so that the L2 round trip overlaps it.
+      const float sw = __ldg(wsc + i);
+      const float4* xs = reinterpret_cast<const float4*>(p.x_scale + static_cast<size_t>(c.kb0 + i) * p.ld_xscale + c.n0);
+      float4 sx[kMaxBnF8 / 4];
+#pragma unroll
+      for (int q = 0; q < kMaxBnF8 / 4; ++q) sx[q] = q * 4 < p.bn ? __ldg(xs + q) : make_float4(0.f, 0.f, 0.f, 0.f);
       if (i > 0) {
         if (!__all_sync(0xffffffffu, sm100::mbar_wait(&bar->acc_full[st.acc], st.acc_phase, deadline))) return false;
         sm100::tc_fence_after_sync();
       }
       const uint32_t tacc = bar->tmem_base + st.acc * acc_cols + (static_cast<uint32_t>(ew * 32) << 16);
-      const float sw = __ldg(wsc + i);
-      const float4* xs = reinterpret_cast<const float4*>(p.x_scale + static_cast<size_t>(c.kb0 + i) * p.ld_xscale + c.n0);
+      // two halves of 32 columns: both TMEM reads of a half in flight, one wait
 #pragma unroll
-      for (int cc = 0; cc < kMaxBnF8 / 16; ++cc) {
-        if (cc * 16 < p.bn) {
-          sm100::tmem_ld16(tacc + cc * 16, g);
+      for (int h = 0; h < kMaxBnF8 / 32; ++h) {
+        if (h * 32 < p.bn) {
+          uint32_t ra[16], rb[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) rb[j] = 0u;
+          sm100::tmem_ld16_issue(tacc + h * 32, ra);
+          if (h * 32 + 16 < p.bn) sm100::tmem_ld16_issue(tacc + h * 32 + 16, rb);
+          sm100::tmem_ld_wait32(ra, rb);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const float4 sx = __ldg(xs + cc * 4 + q);
-            acc[cc * 16 + q * 4 + 0] += g[q * 4 + 0] * (sw * sx.x);
-            acc[cc * 16 + q * 4 + 1] += g[q * 4 + 1] * (sw * sx.y);
-            acc[cc * 16 + q * 4 + 2] += g[q * 4 + 2] * (sw * sx.z);
-            acc[cc * 16 + q * 4 + 3] += g[q * 4 + 3] * (sw * sx.w);
+            const float4 sa = sx[h * 8 + q], sb = sx[h * 8 + 4 + q];
+            acc[h * 32 + q * 4 + 0] += __uint_as_float(ra[q * 4 + 0]) * (sw * sa.x);
+            acc[h * 32 + q * 4 + 1] += __uint_as_float(ra[q * 4 + 1]) * (sw * sa.y);
+            acc[h * 32 + q * 4 + 2] += __uint_as_float(ra[q * 4 + 2]) * (sw * sa.z);
+            acc[h * 32 + q * 4 + 3] += __uint_as_float(ra[q * 4 + 3]) * (sw * sa.w);
+            acc[h * 32 + 16 + q * 4 + 0] += __uint_as_float(rb[q * 4 + 0]) * (sw * sb.x);
+            acc[h * 32 + 16 + q * 4 + 1] += __uint_as_float(rb[q * 4 + 1]) * (sw * sb.y);
+            acc[h * 32 + 16 + q * 4 + 2] += __uint_as_float(rb[q * 4 + 2]) * (sw * sb.z);
+            acc[h * 32 + 16 + q * 4 + 3] += __uint_as_float(rb[q * 4 + 3]) * (sw * sb.w);
           }
         }
       }

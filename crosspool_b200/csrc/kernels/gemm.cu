@@ -62,10 +62,10 @@ __device__ __forceinline__ void run_tiles(const Problem& p, int nacc, int smem_b
   cta_teardown(bar, tmem_cols, warp);
 }
 
-// At most 200 registers: 192 threads x 200 leave room on the SM for one decode-attention CTA of another
+// At most 208 registers: 192 threads x 208 leave room on the SM for one decode-attention CTA of another
 // stream (128 threads x 192 registers), which is how decode GEMMs hide behind the co-located Instance's
 // attention.
-__global__ void __maxnreg__(200)
+__global__ void __maxnreg__(208)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap tmap_w,
                const __grid_constant__ CUtensorMap tmap_x, Problem p, int nacc, int smem_budget,
                uint32_t* status) {
