@@ -24,8 +24,9 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parents[2]
 
 
-def toml_for(models: list[str], atn: list[int], ffn: list[int], port: int, ffn_tp: int, lanes: int, atn_tp: int = 1) -> str:
-    t = [f"[daemon]\nport = {port}", f"[atn]\ndevices = {atn}", f"[ffn]\ndevices = {ffn}",
+def toml_for(models: list[str], atn: list[int], ffn: list[int], port: int, ffn_tp: int, lanes: int, atn_tp: int = 1,
+             elastic: bool = False) -> str:
+    t = [f"[daemon]\nport = {port}", f"[atn]\ndevices = {atn}" + ("\nelastic_kv = true" if elastic else ""), f"[ffn]\ndevices = {ffn}",
          f"[scheduler]\nffn_concurrency = {lanes}", "[scheduler.slo]\nttft_ms = 2000\ntbt_ms = 50"]
     for m in models:
         t.append(f'[[models]]\nid = "{m}"\nffn_tp_size = {ffn_tp}\natn_tp_size = {atn_tp}')
@@ -110,6 +111,7 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--ffn", type=int, nargs="+", default=[1])
     ap.add_argument("--ffn-tp", type=int, default=1)
     ap.add_argument("--atn-tp", type=int, default=1, help="attention tensor-parallel degree (= number of --atn devices)")
+    ap.add_argument("--elastic", action="store_true", help="elastic KV: co-located Instances lend physical KV memory")
     ap.add_argument("--lanes", type=int, default=2)
     ap.add_argument("--port", type=int, default=9841)
     ap.add_argument("--max-batch", type=int, default=256)
@@ -131,11 +133,11 @@ def main(argv: list[str] | None = None) -> int:
         case = dataclasses.replace(case, duration_s=ns.duration or case.duration_s,
                                    rate_per_s=(ns.rate,) if ns.rate > 0 else case.rate_per_s)
     env = {"XPOOL_MAX_BATCH": str(ns.max_batch), "XPOOL_MAX_SEQ_LEN": str(ns.max_seq_len), "XPOOL_MAX_ROWS": "4096"}
-    text = toml_for(ns.models, ns.atn, ns.ffn, ns.port, ns.ffn_tp, ns.lanes, ns.atn_tp)
+    text = toml_for(ns.models, ns.atn, ns.ffn, ns.port, ns.ffn_tp, ns.lanes, ns.atn_tp, ns.elastic)
     with LocalDeployment(text, ns.atn, ns.ffn, ns.port, env) as dep:
         report = suite.default_runner(case, dep.targets(ns.models), ns.seed)
     report["case"] = ns.case
-    report["deployment"] = {"models": ns.models, "atn": ns.atn, "ffn": ns.ffn, "ffn_tp": ns.ffn_tp, "atn_tp": ns.atn_tp, "lanes": ns.lanes}
+    report["deployment"] = {"models": ns.models, "atn": ns.atn, "ffn": ns.ffn, "ffn_tp": ns.ffn_tp, "atn_tp": ns.atn_tp, "lanes": ns.lanes, "elastic_kv": ns.elastic}
     agg = report["aggregate"]
     line = {"case": ns.case, "output_tok_per_s": round(agg["output_tok_per_s"], 1), "completed": agg["completed"],
             "errors": agg["errors"], "tpot_p50_ms": round(agg["tpot_ms"]["p50"], 2), "tpot_p99_ms": round(agg["tpot_ms"]["p99"], 2),
