@@ -174,6 +174,54 @@ def bench_moe(ns, timer: Timer) -> dict:
                   {"rows": ns.rows, "routes": routes})
 
 
+def bench_kv_vmm(ns, timer: Timer) -> dict:
+    """Elastic KV: time to map and to unmap one KV Page Bundle (one physical chunk per layer and K/V buffer behind
+    stable addresses) of a model, and the ECS seqlock channel's command/completion round trip on the host."""
+    import time
+
+    from ..ecs import vmm
+    from ..models import config as mc
+    from ..native.runtime import EcsChannel
+
+    cfg = mc.preset(ns.model)
+    drv, quota = vmm.Driver.real(), vmm.MemoryQuota(1 << 62)
+    ppb, chunk = vmm.bundle_geometry(cfg, 16)
+    cache = vmm.elastic_kv_cache(cfg, ns.bundles * ppb, 16, "cuda", drv, quota, initial_bundles=1)
+    base = cache.k_cache[0].data_ptr()
+    grow_us, shrink_us = [], []
+    for _ in range(timer.iters):
+        take = cache.allocator.unmapped_bundles()[: ns.bundles - 1]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        assert vmm.grow(cache, take) == 0
+        t1 = time.perf_counter()
+        for b in take:
+            cache.allocator.begin_retirement(b)
+        cache.backing.unmap(take)
+        t2 = time.perf_counter()
+        grow_us.append((t1 - t0) * 1e6 / len(take))
+        shrink_us.append((t2 - t1) * 1e6 / len(take))
+    assert cache.k_cache[0].data_ptr() == base            # addresses never move
+    ch = EcsChannel.create(f"/xp-bench-ecs-{time.time_ns() & 0xffffff}", 1, 2, 1)
+    try:
+        t0 = time.perf_counter()
+        n = 20000
+        for i in range(1, n + 1):
+            ch.publish_command(0, i, i << 20)
+            seq, _ = ch.read_command(0)
+            ch.publish_completion(0, seq, i << 20)
+            ch.read_completion(0)
+        ecs_us = (time.perf_counter() - t0) * 1e6 / n
+    finally:
+        ch.close()
+    out = {"kernel": "kv_vmm_bundle", "model": ns.model, "bundle_mib": round(chunk * 2 * cfg.num_layers / 2 ** 20, 1),
+           "chunks_per_bundle": 2 * cfg.num_layers, "pages_per_bundle": ppb,
+           "map_us_per_bundle": round(statistics.median(grow_us), 1), "unmap_us_per_bundle": round(statistics.median(shrink_us), 1),
+           "ecs_command_completion_round_trip_us": round(ecs_us, 2)}
+    print(json.dumps(out), flush=True)
+    return out
+
+
 def bench_decode_step(ns, timer: Timer) -> dict:
     """One Instance's decode step on the loopback engine, launched eagerly (no CUDA graph) over
     sequences whose KV is taken as already cached -- the workload for a per-launch time list."""
@@ -254,6 +302,9 @@ def main(argv: list[str] | None = None) -> int:
     n.add_argument("--hidden", type=int, default=1024)
     m = sub.add_parser("moe")
     m.add_argument("--rows", type=int, default=64)
+    v = sub.add_parser("kv-vmm")
+    v.add_argument("--model", default="Qwen/Qwen3-0.6B")
+    v.add_argument("--bundles", type=int, default=9)
     d = sub.add_parser("decode-step")
     d.add_argument("--model", default="Qwen/Qwen3-0.6B")
     d.add_argument("--batch", type=int, default=256)
@@ -263,7 +314,7 @@ def main(argv: list[str] | None = None) -> int:
     ns = ap.parse_args(argv)
     timer = Timer(ns.iters, ns.warmup, not ns.no_flush)
     {"gemm": bench_gemm, "decode-attn": bench_decode_attn, "norm": bench_norm, "moe": bench_moe,
-     "decode-step": bench_decode_step, "prefill-attn": bench_prefill_attn}[ns.case](ns, timer)
+     "decode-step": bench_decode_step, "prefill-attn": bench_prefill_attn, "kv-vmm": bench_kv_vmm}[ns.case](ns, timer)
     return 0
 
 
