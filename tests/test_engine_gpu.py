@@ -81,6 +81,28 @@ def test_qwen2_shape_with_qkv_bias_and_seven_query_heads_per_kv_head():
         assert s.generated[0] == toks[0]
 
 
+def test_long_context_chunked_prefill_and_decode_match_reference():
+    """A 9,000-token prompt goes through five prefill chunks over the paged cache, then decodes with a split KV
+    range: long context here is chunked prefill plus paged (optionally elastic) KV, there is no sequence or
+    context parallelism (neither has the reference: src/xpool/integrations/sglang/server_args.py:65,97-99)."""
+    cfg, eng, ref = _build("Qwen/Qwen3-0.6B", layers=2, max_batch=4, prefill_chunk=2048, max_seq_len=16384)
+    eng.warmup()
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, cfg.vocab_size, (9000,), generator=g).tolist()
+    s = eng.add_request(prompt, 3)
+    logits = []
+    while eng.has_work:
+        for i, (q, tok) in enumerate(eng.step()):
+            logits.append(eng.logits[i].clone())
+    from crosspool_b200.ops import gemm
+    gemm.check_status(eng.device)
+    toks, ref_logits = ref.generate(torch.tensor(prompt, device="cuda"), 3)
+    assert eng.stats["prefill_steps"] >= 5
+    assert _kl(ref_logits[:1], logits[0][None]).item() <= 0.05
+    if s.generated[0] == toks[0]:
+        assert _kl(ref_logits[1:2], logits[1][None]).item() <= 0.005
+
+
 def test_chunked_prefill_equals_single_chunk():
     cfg, eng_small, _ = _build("Qwen/Qwen3-0.6B", layers=2, max_batch=4, prefill_chunk=64, max_seq_len=512,
                                use_cuda_graph=False)
