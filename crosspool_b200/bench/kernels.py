@@ -187,7 +187,7 @@ def bench_kv_vmm(ns, timer: Timer) -> dict:
     drv, quota = vmm.Driver.real(), vmm.MemoryQuota(1 << 62)
     ppb, chunk = vmm.bundle_geometry(cfg, 16)
     cache = vmm.elastic_kv_cache(cfg, ns.bundles * ppb, 16, "cuda", drv, quota, initial_bundles=1)
-    base = cache.k_cache[0].data_ptr()
+    base = cache.k[0].data_ptr()
     grow_us, shrink_us = [], []
     for _ in range(timer.iters):
         take = cache.allocator.unmapped_bundles()[: ns.bundles - 1]
@@ -201,7 +201,7 @@ def bench_kv_vmm(ns, timer: Timer) -> dict:
         t2 = time.perf_counter()
         grow_us.append((t1 - t0) * 1e6 / len(take))
         shrink_us.append((t2 - t1) * 1e6 / len(take))
-    assert cache.k_cache[0].data_ptr() == base            # addresses never move
+    assert cache.k[0].data_ptr() == base            # addresses never move
     ch = EcsChannel.create(f"/xp-bench-ecs-{time.time_ns() & 0xffffff}", 1, 2, 1)
     try:
         t0 = time.perf_counter()
