@@ -116,3 +116,29 @@ atn_tp_size = 2
                                       for r in (0, 1)])
     a, b = (_placement(cfg, plan, "Qwen/Qwen3-0.6B", r, 256) for r in (0, 1))
     assert a == b and a.atn_rank == 0 and a.atn_tp_followers == (1,) and a.ffn_ranks == (2,)
+
+
+def _agree_rank(rank, port, q):
+    import torch.distributed as dist
+
+    from crosspool_b200.ecs.reconciler import gloo_agreement
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=2)
+    agree = gloo_agreement(None)
+    out = [agree([rank, 10 + rank, 7]), agree([1, 3 - rank, 0])]
+    q.put((rank, out))
+    dist.destroy_process_group()
+
+
+def test_gloo_agreement_gathers_every_ranks_vote():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29400 + os.getpid() % 200
+    ps = [ctx.Process(target=_agree_rank, args=(r, port, q)) for r in (0, 1)]
+    for p in ps:
+        p.start()
+    res = dict(q.get(timeout=60) for _ in ps)
+    for p in ps:
+        p.join(30)
+    assert res[0] == res[1] == [[[0, 10, 7], [1, 11, 7]], [[1, 3, 0], [1, 2, 0]]]
