@@ -116,6 +116,7 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--port", type=int, default=9841)
     ap.add_argument("--max-batch", type=int, default=256)
     ap.add_argument("--max-seq-len", type=int, default=2624)
+    ap.add_argument("--prefill-chunk", type=int, default=2048, help="tokens per prefill step of the attention engines")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--duration", type=float, default=0.0, help="override the case's duration (seconds)")
     ap.add_argument("--rate", type=float, default=0.0, help="override the case's per-model request rate")
@@ -132,7 +133,8 @@ def main(argv: list[str] | None = None) -> int:
 
         case = dataclasses.replace(case, duration_s=ns.duration or case.duration_s,
                                    rate_per_s=(ns.rate,) if ns.rate > 0 else case.rate_per_s)
-    env = {"XPOOL_MAX_BATCH": str(ns.max_batch), "XPOOL_MAX_SEQ_LEN": str(ns.max_seq_len), "XPOOL_MAX_ROWS": "4096"}
+    env = {"XPOOL_MAX_BATCH": str(ns.max_batch), "XPOOL_MAX_SEQ_LEN": str(ns.max_seq_len), "XPOOL_MAX_ROWS": "4096",
+           "XPOOL_PREFILL_CHUNK": str(ns.prefill_chunk)}
     text = toml_for(ns.models, ns.atn, ns.ffn, ns.port, ns.ffn_tp, ns.lanes, ns.atn_tp, ns.elastic)
     with LocalDeployment(text, ns.atn, ns.ffn, ns.port, env) as dep:
         report = suite.default_runner(case, dep.targets(ns.models), ns.seed)
