@@ -174,6 +174,44 @@ def bench_moe(ns, timer: Timer) -> dict:
                   {"rows": ns.rows, "routes": routes})
 
 
+def bench_prefill_step(ns, timer: Timer) -> dict:
+    """Prefill chunks of one Instance on the loopback engine: a prompt of ``chunks`` x ``chunk`` tokens goes through
+    the engine chunk by chunk (launched eagerly), each step timed on the device."""
+    from ..engine.atn_engine import AttentionEngine, EngineConfig
+    from ..engine.ffn_local import LocalFfnPort
+    from ..models import config as mc
+    from ..models.weights import random_attention_weights, random_ffn_weights
+    from ..ops import gemm
+
+    cfg = mc.preset(ns.model)
+    aw = random_attention_weights(cfg, 0, "cuda", torch.bfloat16)
+    fw = random_ffn_weights(cfg, 0, "cuda", torch.bfloat16)
+    total = ns.chunk * ns.chunks
+    eng = AttentionEngine(cfg, aw, LocalFfnPort(cfg, fw), EngineConfig(
+        max_batch=8, prefill_chunk=ns.chunk, max_seq_len=total + 64, decode_buckets=[8], use_cuda_graph=False))
+    eng.warmup()
+    rnd = random.Random(0)
+    ts = []
+    for rep in range(timer.warmup + timer.iters):
+        eng.add_request([rnd.randrange(cfg.vocab_size) for _ in range(total)], 1)
+        per = []
+        while eng.has_work:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(eng.stream)
+            eng.step()
+            b.record(eng.stream)
+            torch.cuda.synchronize()
+            per.append(a.elapsed_time(b))
+        if rep >= timer.warmup:
+            ts.append(per[:ns.chunks])
+    gemm.check_status(eng.device)
+    med = [statistics.median(t[i] for t in ts) for i in range(ns.chunks)]
+    out = {"kernel": "prefill_step", "model": ns.model, "chunk_tokens": ns.chunk, "ms_per_chunk_by_position": [round(m, 3) for m in med],
+           "prompt_tokens_per_s": round(total / (sum(med) / 1e3))}
+    print(json.dumps(out), flush=True)
+    return out
+
+
 def bench_kv_vmm(ns, timer: Timer) -> dict:
     """Elastic KV: time to map and to unmap one KV Page Bundle (one physical chunk per layer and K/V buffer behind
     stable addresses) of a model, and the ECS seqlock channel's command/completion round trip on the host."""
@@ -302,6 +340,10 @@ def main(argv: list[str] | None = None) -> int:
     n.add_argument("--hidden", type=int, default=1024)
     m = sub.add_parser("moe")
     m.add_argument("--rows", type=int, default=64)
+    ps = sub.add_parser("prefill-step")
+    ps.add_argument("--model", default="Qwen/Qwen3-0.6B")
+    ps.add_argument("--chunk", type=int, default=2048)
+    ps.add_argument("--chunks", type=int, default=4)
     v = sub.add_parser("kv-vmm")
     v.add_argument("--model", default="Qwen/Qwen3-0.6B")
     v.add_argument("--bundles", type=int, default=9)
@@ -314,7 +356,8 @@ def main(argv: list[str] | None = None) -> int:
     ns = ap.parse_args(argv)
     timer = Timer(ns.iters, ns.warmup, not ns.no_flush)
     {"gemm": bench_gemm, "decode-attn": bench_decode_attn, "norm": bench_norm, "moe": bench_moe,
-     "decode-step": bench_decode_step, "prefill-attn": bench_prefill_attn, "kv-vmm": bench_kv_vmm}[ns.case](ns, timer)
+     "decode-step": bench_decode_step, "prefill-attn": bench_prefill_attn, "kv-vmm": bench_kv_vmm,
+     "prefill-step": bench_prefill_step}[ns.case](ns, timer)
     return 0
 
 

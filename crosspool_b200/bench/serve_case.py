@@ -116,7 +116,7 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--port", type=int, default=9841)
     ap.add_argument("--max-batch", type=int, default=256)
     ap.add_argument("--max-seq-len", type=int, default=2624)
-    ap.add_argument("--prefill-chunk", type=int, default=2048, help="tokens per prefill step of the attention engines")
+    ap.add_argument("--prefill-chunk", type=int, default=4096, help="tokens per prefill step of the attention engines")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--duration", type=float, default=0.0, help="override the case's duration (seconds)")
     ap.add_argument("--rate", type=float, default=0.0, help="override the case's per-model request rate")

@@ -47,7 +47,7 @@ def run_agent(cfg: XpoolConfig, role: str, device: int) -> int:
                          owner=owner)
     else:
         insts = hosted_instances(cfg, device)
-        chunk = min(max_rows, int(os.environ.get("XPOOL_PREFILL_CHUNK", "2048")))   # tokens per prefill step
+        chunk = min(max_rows, int(os.environ.get("XPOOL_PREFILL_CHUNK", "4096")))   # tokens per prefill step
         ecfg = EngineConfig(max_batch=int(os.environ.get("XPOOL_MAX_BATCH", "256")), prefill_chunk=chunk,
                             max_seq_len=int(os.environ.get("XPOOL_MAX_SEQ_LEN", "4096")))
         port = SERVING_BASE_PORT + cfg.atn_devices.index(device)
