@@ -264,7 +264,10 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t full[kPfStages];
 
-  const int seq = blockIdx.z, hk = blockIdx.y, qt = blockIdx.x;
+  // Query tiles are taken from the end of the sequence first: under the causal mask the last tile reads the
+  // most K/V, and CTAs are dispatched in index order, so the longest ones start first and the short ones fill
+  // the tail (longest-processing-time-first) instead of one 32-tile CTA running alone at the end.
+  const int seq = blockIdx.z, hk = blockIdx.y, qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
   const int q_len = a.q_lens[seq];
   const int q0 = qt * rows_per_cta;
   if (q0 >= q_len) return;
