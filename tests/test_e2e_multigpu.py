@@ -12,7 +12,6 @@ import httpx
 import pytest
 import torch
 
-from conftest import unvalidated
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
@@ -43,7 +42,6 @@ def test_daemon_agents_serve_requests_and_retire(tmp_path, elastic):
                       [("ffnagent", 1), ("atnagent", 0)])
 
 
-@unvalidated
 @pytest.mark.parametrize("elastic", [False, True])
 def test_attention_tp_pair_serves_through_the_daemon(tmp_path, elastic):
     """One Instance whose attention runs tensor-parallel over two agent processes (GPUs 0 and 1); the FFN tier

@@ -7,7 +7,6 @@ from pathlib import Path
 import pytest
 import torch
 
-from conftest import unvalidated
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
@@ -40,11 +39,9 @@ def test_moe_expert_parallel_over_two_ffn_ranks():
     _run(3, ["--tp", "2", "--model", "tiny-qwen3-moe", "--layers", "2"])
 
 
-@unvalidated
 def test_attention_tp_pair_with_a_remote_ffn_rank():
     _run(3, ["--atn-tp", "2", "--tp", "1"])
 
 
-@unvalidated
 def test_layer_split_placement_over_two_ffn_ranks():
     _run(3, ["--tp", "1", "--layer-split", "2"])
