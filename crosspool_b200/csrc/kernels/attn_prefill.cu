@@ -343,11 +343,9 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   for (int t = 0; t < n_tiles; ++t) {
     const int s = t % kPfStages;
     const uint32_t ks_base = ring + s * kStage, vs_base = ks_base + kTile;
+    // No CTA barrier here: a warp starts on the tile as soon as it has seen it land. A wait that ran out is
+    // reported at the barrier that ends the tile, which every thread reaches whatever it saw.
     const bool landed = sm100::mbar_wait(&full[s], (t / kPfStages) & 1, sm100::global_timer_ns() + sm100::kPipelineWaitNs);
-    if (__syncthreads_or(!landed)) {   // CTA-uniform: the barriers below name every thread
-      timed_out = true;
-      break;
-    }
     const int t0 = t * kBN;
     if (t0 + kBN > kv_end) {
       // cache slots past the sequence end may hold anything: zero those V rows (probability 0 x NaN)
@@ -358,7 +356,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       }
       __syncthreads();
     }
-    if (t0 < warp_kv_end) {
+    if (landed && t0 < warp_kv_end) {
       // S = Q K^T for 16 rows x 64 tokens
       float sacc[NB][4];
 #pragma unroll
@@ -438,7 +436,10 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         }
       }
     }
-    __syncthreads();   // every warp is done with the stage
+    if (__syncthreads_or(!landed)) {   // every warp is done with the stage; CTA-uniform outcome of the waits
+      timed_out = true;
+      break;
+    }
     if (threadIdx.x == 0 && t + kPfStages < n_tiles) {
       sm100::fence_proxy_async_smem();
       issue(t + kPfStages);
