@@ -97,6 +97,10 @@ class LocalDeployment:
                 p.wait(15)
             except subprocess.TimeoutExpired:
                 p.kill()
+        # the daemon is ended by SIGTERM; an agent that did not retire with exit code 0 is worth a line
+        for p in self.procs[1:]:
+            if p.returncode not in (0, None):
+                print(f"deployment process {' '.join(p.args[3:])} exited with code {p.returncode}", file=sys.stderr, flush=True)
         self._dir.cleanup()
 
 
