@@ -68,6 +68,18 @@ class Sequence:
     token_times: list[float] = field(default_factory=list)
     temperature: float = 0.0         # 0: greedy (needs EngineConfig.sampling for anything else)
     seed: int = 0
+    refill_len: int = 0              # > 0 after a retraction: prompt + generated tokens to recompute before decoding on
+
+    @property
+    def fill_len(self) -> int:
+        """Tokens the prefill phase has to cache: the prompt, or after a retraction everything emitted so far."""
+        return self.refill_len or len(self.prompt)
+
+    def fill_tokens(self, start: int, n: int) -> list[int]:
+        """Tokens ``start .. start + n`` of the prefill stream (prompt, then already generated tokens)."""
+        if start + n <= len(self.prompt):
+            return self.prompt[start:start + n]
+        return (self.prompt + self.generated)[start:start + n]
 
     @property
     def total_len(self) -> int:
@@ -75,7 +87,7 @@ class Sequence:
 
     @property
     def prefill_done(self) -> bool:
-        return self.computed >= len(self.prompt)
+        return self.computed >= self.fill_len
 
     @property
     def finished(self) -> bool:
@@ -221,8 +233,14 @@ class AttentionEngine:
     # ------------------------------------------------------------------ request API
     def add_request(self, prompt: list[int], max_new_tokens: int, arrival: float | None = None,
                     deadline: float = 0.0, temperature: float = 0.0, seed: int = 0) -> Sequence:
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        if max_new_tokens < 1:
+            raise ValueError("max_new_tokens must be at least 1")
         if len(prompt) + max_new_tokens > self.ecfg.max_seq_len:
             raise ValueError("request exceeds max_seq_len")
+        if min(prompt) < 0 or max(prompt) >= self.cfg.vocab_size:
+            raise ValueError(f"token id outside [0, {self.cfg.vocab_size})")
         if temperature > 0 and not self.ecfg.sampling:
             raise ValueError("temperature sampling needs EngineConfig(sampling=True)")
         s = Sequence(self._next_id, list(prompt), max_new_tokens, arrival if arrival is not None else time.monotonic(),
@@ -372,7 +390,9 @@ class AttentionEngine:
         for s in list(self.prefilling):
             if budget <= 0 or len(chosen) >= e.max_prefill_seqs:
                 break
-            n = min(len(s.prompt) - s.computed, budget)
+            n = min(s.fill_len - s.computed, budget)
+            if n <= 0:
+                continue
             chosen.append((s, n))
             budget -= n
         while self.waiting and budget > 0 and len(chosen) < e.max_prefill_seqs:
@@ -380,7 +400,7 @@ class AttentionEngine:
                 break
             s = self.waiting[0]
             shared = self.prefix.match(s.prompt) if self.prefix is not None else []
-            need = (len(s.prompt) + 1 + e.page_size - 1) // e.page_size - len(shared)
+            need = (s.fill_len + 1 + e.page_size - 1) // e.page_size - len(shared)
             if need > self.kv.allocator.free_pages and self.prefix is not None:
                 freed = self.prefix.evict(need - self.kv.allocator.free_pages)
                 self.kv.allocator.free(freed)
@@ -395,9 +415,9 @@ class AttentionEngine:
                 self.kv.tables[s.seq_id] = list(shared)   # read-only prefix pages come first
                 s.computed = len(shared) * e.page_size
                 s.shared_pages = list(shared)
-            self.kv.ensure(s.seq_id, len(s.prompt) + 1)
+            self.kv.ensure(s.seq_id, s.fill_len + 1)
             self.prefilling.append(s)
-            n = min(len(s.prompt) - s.computed, budget)
+            n = min(s.fill_len - s.computed, budget)
             chosen.append((s, n))
             budget -= n
         return chosen, e.prefill_chunk - budget
@@ -409,7 +429,7 @@ class AttentionEngine:
         r = 0
         ps = e.page_size
         for i, (s, n) in enumerate(chosen):
-            toks = s.prompt[s.computed:s.computed + n]
+            toks = s.fill_tokens(s.computed, n)
             hv[r:r + n] = toks
             for j in range(n):
                 p = s.computed + j
@@ -447,7 +467,8 @@ class AttentionEngine:
                     s.shared_pages = list(getattr(s, "shared_pages", [])) + taken
                 tok = int(th[i])
                 s.generated.append(tok)
-                s.first_token_time = now
+                if s.first_token_time is None:
+                    s.first_token_time = now   # a re-prefill after a retraction is not a first token
                 s.token_times.append(now)
                 self.prefilling.remove(s)
                 out.append((s, tok))
@@ -585,13 +606,13 @@ class AttentionEngine:
         return self._decode_collect() if self._decode_launch() else []
 
     def _retract(self, s: Sequence) -> None:
-        """Gives the sequence's pages back and queues it for recomputation (prompt + generated)."""
+        """Gives the sequence's pages back and queues it for recomputation. The emitted tokens stay in
+        ``generated`` (readers of the sequence keep seeing all of them); the prefill phase recomputes the KV of
+        prompt + generated and its sampled token continues the same output stream."""
         self.running.remove(s)
         self._b_key = None  # the cached decode batch no longer matches
         self._release_pages(s)
-        s.prompt = s.prompt + s.generated
-        s.max_new_tokens -= len(s.generated)
-        s.generated = []
+        s.refill_len = s.total_len
         s.computed = 0
         self.waiting.appendleft(s)
 

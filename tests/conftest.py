@@ -1,4 +1,3 @@
-import os
 import sys
 from pathlib import Path
 
@@ -7,12 +6,6 @@ import pytest
 ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
-
-
-# Multi-GPU tests that have not yet completed a run on real hardware (GPU slots were unavailable when they
-# were written) only run on request, so that a first-run surprise cannot stop the rest of the suite.
-unvalidated = pytest.mark.skipif(not os.environ.get("XPOOL_RUN_UNVALIDATED"),
-                                 reason="not yet validated on a multi-GPU box; set XPOOL_RUN_UNVALIDATED=1 to run")
 
 
 def pytest_configure(config):

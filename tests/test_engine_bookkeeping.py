@@ -1,0 +1,101 @@
+"""Host-side bookkeeping of the attention engine that needs no GPU: request validation, the prefill
+stream of a retracted sequence, and an engine loop that keeps serving after a bad request."""
+import time
+from collections import deque
+
+import pytest
+
+from crosspool_b200.engine.atn_engine import AttentionEngine, EngineConfig, Sequence
+from crosspool_b200.models import config as mc
+from crosspool_b200.runtime.serving import EngineLoop
+
+
+class _Kv:
+    def __init__(self):
+        self.released = []
+        self.tables = {}
+
+    def release(self, seq_id):
+        self.released.append(seq_id)
+
+
+def bare_engine() -> AttentionEngine:
+    """An engine object with the host-side state only (no device buffers)."""
+    eng = AttentionEngine.__new__(AttentionEngine)
+    eng.cfg = mc.preset("Qwen/Qwen3-0.6B").with_layers(1)
+    eng.ecfg = EngineConfig(max_batch=4, prefill_chunk=64, max_seq_len=128)
+    eng.waiting, eng.running, eng.prefilling = deque(), [], []
+    eng._next_id, eng._b_key, eng.prefix, eng.kv = 0, None, None, _Kv()
+    return eng
+
+
+@pytest.mark.parametrize("prompt,new,match", [([], 4, "empty prompt"), ([1, 2], 0, "max_new_tokens"),
+                                              ([1, -3], 4, "token id"), ([1, 10 ** 9], 4, "token id"),
+                                              (list(range(100)), 64, "max_seq_len")])
+def test_add_request_rejects_bad_requests(prompt, new, match):
+    eng = bare_engine()
+    with pytest.raises(ValueError, match=match):
+        eng.add_request(prompt, new)
+    assert not eng.waiting
+
+
+def test_retraction_keeps_emitted_tokens_and_recomputes_them():
+    eng = bare_engine()
+    s = eng.add_request([5, 6, 7], 8)
+    eng.waiting.clear()
+    s.generated, s.computed, s.first_token_time = [11, 12, 13], 5, 1.0
+    eng.running.append(s)
+    eng._retract(s)
+    assert s.generated == [11, 12, 13] and s.max_new_tokens == 8 and s.prompt == [5, 6, 7]
+    assert s.computed == 0 and not s.prefill_done and s.fill_len == 6
+    assert s.fill_tokens(0, 6) == [5, 6, 7, 11, 12, 13] and s.fill_tokens(2, 3) == [7, 11, 12]
+    assert list(eng.waiting) == [s] and eng.kv.released == [s.seq_id]
+    # the token sampled by the re-prefill continues the same stream; the request is not finished early
+    s.computed = 6
+    s.generated.append(14)
+    assert s.prefill_done and s.total_len == 7 and not s.finished
+
+
+def test_fill_stream_of_a_fresh_sequence_is_its_prompt():
+    s = Sequence(0, [1, 2, 3, 4], 2)
+    assert s.fill_len == 4 and s.fill_tokens(1, 2) == [2, 3]
+
+
+class _Dep:
+    """Deployment whose add_request is the real engine's (validation included) and whose step emits one token."""
+
+    def __init__(self):
+        self.eng = bare_engine()
+
+    def add_request(self, model_id, prompt, max_new_tokens, arrival=None):
+        return self.eng.add_request(prompt, max_new_tokens, arrival)
+
+    @property
+    def has_work(self):
+        return bool(self.eng.waiting)
+
+    def step(self):
+        class R:
+            tokens = {}
+        out = []
+        for s in list(self.eng.waiting):
+            s.generated.append(1)
+            out.append((s, 1))
+            if s.finished:
+                self.eng.waiting.remove(s)
+        R.tokens = {"m": out}
+        return R
+
+
+def test_engine_loop_survives_an_empty_prompt():
+    loop = EngineLoop(_Dep())
+    loop.start()
+    try:
+        bad = loop.submit("m", [], 4)
+        item = bad.out.get(timeout=5)
+        assert isinstance(item, ValueError)
+        good = loop.submit("m", [3, 4], 2)
+        assert good.out.get(timeout=5) == (1, False) and good.out.get(timeout=5) == (1, True)
+        assert loop.error is None
+    finally:
+        loop.stop()
