@@ -14,6 +14,9 @@ import sys
 import torch
 import torch.distributed as dist
 
+sys.path.insert(0, os.path.abspath(os.path.join(os.path.dirname(__file__), "..", "..")))
+from crosspool_b200.testing import compare_generations  # noqa: E402
+
 
 def main() -> int:
     ap = argparse.ArgumentParser()
@@ -78,14 +81,9 @@ def main() -> int:
             for i, (s, _) in enumerate(ref.step()):
                 rlogits[s.seq_id].append(ref.logits[i].float().clone())
         for s, r in zip(seqs, rseqs):
-            a, b = torch.stack(logits[s.seq_id]), torch.stack(rlogits[r.seq_id])
-            n = 0
-            while n < len(s.generated) and s.generated[n] == r.generated[n]:
-                n += 1
-            p, q = a[:max(n, 1)].log_softmax(-1), b[:max(n, 1)].log_softmax(-1)
-            kl = (p.exp() * (p - q)).sum(-1).max().item()
-            print(f"[fabric_check] seq {s.seq_id}: tokens agree {n}/{len(s.generated)} max KL {kl:.2e}", flush=True)
-            ok = ok and n >= 1 and kl < 0.02
+            good, n, kl = compare_generations(s.generated, r.generated, logits[s.seq_id], rlogits[r.seq_id])
+            print(f"[fabric_check] seq {s.seq_id}: tokens agree {n}/{len(s.generated)} max KL {kl:.2e} ok {good}", flush=True)
+            ok = ok and good
     dist.barrier(group=ctl)
     if ctx.role == "ffn":
         st = ctx.ffn.stats()

@@ -20,7 +20,7 @@ def test_two_attention_tp_ranks_match_the_unsharded_engine(graph):
         pytest.skip("needs 2 GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29561", str(ROOT / "crosspool_b200/parallel/atn_tp_check.py"), "--graph", str(graph)]
+           "--master-port", "29561", str(ROOT / "tests/multigpu/atn_tp_check.py"), "--graph", str(graph)]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "ATN_TP_CHECK_OK" in r.stdout

@@ -17,7 +17,7 @@ def _run(nproc, extra):
         pytest.skip(f"needs {nproc} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-           "--master-addr", "127.0.0.1", "--master-port", "29541", str(ROOT / "crosspool_b200/parallel/fabric_check.py")] + extra
+           "--master-addr", "127.0.0.1", "--master-port", "29541", str(ROOT / "tests/multigpu/fabric_check.py")] + extra
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "FABRIC_CHECK_OK" in r.stdout
