@@ -1,24 +1,31 @@
 #!/usr/bin/env python
-"""Headline benchmark: aggregate output tok/s across co-located models in steady-state decode.
+"""Headline benchmark: aggregate output tok/s across co-located models served under open-loop traffic, with the
+p99 TPOT / p99 TTFT service-level objectives checked, and p50 TTFT.
 
-``python bench.py --gpus N --steps K --warmup W`` (under ``torch.distributed.run`` for N > 1, one rank
-per GPU). The workload is acceptance configuration (b) of BASELINE.json scaled by N: Instances of the
-Qwen3-0.6B architecture in bf16 with random-init weights, two co-located Instances per attention GPU,
-each with ``--batch`` in-flight requests whose prompt lengths are uniform in [128, 2048] (uniform random
-token ids, outputs forced with ignore-eos semantics). N = 1 runs every role on one GPU (loopback);
-N >= 2 puts attention on N/2 GPUs and the shared FFN tier on the other N/2.
+``python bench.py --gpus N --steps K --warmup W`` (under ``torch.distributed.run`` for N > 1, one rank per GPU).
+The served path is measured: admission, chunked prefill and decode interleaved by each Instance's engine loop,
+Poisson arrivals generated in-process and submitted through ``EngineLoop.submit`` (what ``POST /generate`` calls),
+synthetic prompts of the named length distributions, random-init weights of the named architectures, bf16.
 
-A *step* is one decode iteration of every co-located Instance (every in-flight request gains one
-token). Two measurements are reported:
+The model mix follows the acceptance configurations by GPU count (``--mix`` overrides):
 
-* ``value``: K steps device-timed with CUDA events around back-to-back replays of the Instances' full
-  decode-step graphs (all layers, LM head, sampling) — the kernel-only number;
-* ``e2e``: the same K steps driven through the public API (``Deployment.step``), timed around the whole
-  loop, which per step copies the step's metadata (token ids, positions, KV slots, lengths, block
-  table) from pinned host memory to the device and reads the sampled tokens back.
+* N = 1: Qwen3-0.6B, every role on one GPU (loopback: the FFN runs in-stream);
+* N = 2: Qwen3-0.6B on 1 attention GPU + 1 FFN GPU over NVLink peer memory;
+* N = 4: Qwen3-8B + Qwen3-0.6B sharing each of 2 attention GPUs with elastic KV lending, FFN on a shared 2-GPU
+  tier (8B tensor-parallel over both), the two models trading long- and short-context traffic every window;
+* N = 8: Qwen3-32B (FFN TP4) + Qwen3-8B (FFN TP2) + 2 x Qwen3-1.7B, attention on 2 GPUs with elastic KV, FFN tier
+  on 6 GPUs, bursty Poisson streams with rates 1:2:4:4.
 
-``--impl reference`` reports why the reference cannot run here: its build needs a CUDA 13.2 toolkit,
-NVSHMEM and a serving engine that this image does not carry.
+A *step* is one ``--step-seconds`` (0.5 s) scheduling interval of offered traffic. After W warm-up intervals,
+three windows of exactly K intervals are measured back to back; ``value`` is the median window's output tokens
+divided by its device time (CUDA events at the window boundaries, maximum over attention ranks); ``e2e`` is the
+same windows seen by the request producer on the host clock, with TTFT and TPOT percentiles. ``valid`` is false
+when an SLO is missed or the correctness gate (logits against an oracle engine) fails.
+
+``--impl baseline`` runs the same deployment and workload with the FFN tier built from library calls (NCCL
+broadcast / reduce, cuBLAS GEMMs, unfused SwiGLU). ``--impl reference`` reports why the reference itself cannot
+run here. ``--decode-only`` runs the steady-state decode replay benchmark instead (every Instance at a full
+running batch, no arrivals), a kernel-level figure.
 """
 
 from __future__ import annotations
@@ -28,7 +35,6 @@ import json
 import os
 import sys
 
-BASELINE_PUBLISHED = None  # the reference publishes no throughput or latency number
 REFERENCE_UNAVAILABLE = ("reference not installable offline: needs CUDA Toolkit >= 13.2 (image has 12.9), "
                          "NVSHMEM 3.7.2, cuda-bindings 13, sglang 0.5.20, torch 2.13")
 
@@ -36,25 +42,30 @@ REFERENCE_UNAVAILABLE = ("reference not installable offline: needs CUDA Toolkit 
 def parse_args(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="xpool", choices=["xpool", "reference"])
-    ap.add_argument("--batch", type=int, default=256, help="in-flight requests per Instance")
-    ap.add_argument("--model", default="Qwen/Qwen3-0.6B")
+    ap.add_argument("--steps", type=int, default=20, help="scheduling intervals per measured window")
+    ap.add_argument("--warmup", type=int, default=5, help="untimed intervals of traffic before the first window")
+    ap.add_argument("--impl", default="xpool", choices=["xpool", "baseline", "reference"])
+    ap.add_argument("--step-seconds", type=float, default=0.5)
+    ap.add_argument("--mix", default="", choices=["", "b", "c", "e"], help="model mix (default: by GPU count)")
+    ap.add_argument("--rate-scale", type=float, default=1.0, help="multiplies every arrival rate of the mix")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the models (marks the result invalid)")
+    ap.add_argument("--lanes", type=int, default=2, help="Executor Lanes per FFN device (multi-GPU only)")
+    ap.add_argument("--policy", default="fifo", choices=["fifo", "random", "slo"], help="Lane scheduling policy")
+    # steady-state decode replay (kernel-level)
+    ap.add_argument("--decode-only", action="store_true")
+    ap.add_argument("--batch", type=int, default=256, help="decode-only: in-flight requests per Instance")
+    ap.add_argument("--model", default="Qwen/Qwen3-0.6B", help="decode-only: model preset")
     ap.add_argument("--instances-per-atn", type=int, default=2)
     ap.add_argument("--min-prompt", type=int, default=128)
     ap.add_argument("--max-prompt", type=int, default=2048)
-    ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the result invalid)")
-    ap.add_argument("--ffn-tp", type=int, default=1, help="FFN tensor-parallel degree (multi-GPU only)")
-    ap.add_argument("--lanes", type=int, default=2, help="Executor Lanes per FFN device (multi-GPU only)")
-    ap.add_argument("--trace-dir", default="", help="multi-GPU only: write the FFN ranks' Lane timelines (chrome trace JSON) here")
-    ap.add_argument("--policy", default="fifo", choices=["fifo", "random", "slo"], help="Lane scheduling policy (multi-GPU only)")
-    ap.add_argument("--ffn-ranks", type=int, default=0, help="GPUs in the shared FFN tier (0: max(1, N // 4); multi-GPU only)")
+    ap.add_argument("--ffn-tp", type=int, default=1)
+    ap.add_argument("--trace-dir", default="")
+    ap.add_argument("--ffn-ranks", type=int, default=0)
     return ap.parse_args(argv)
 
 
-def run_single_gpu(args) -> dict:
-    """Loopback: every role on GPU 0, FFNs in-stream."""
+def run_decode_only_single_gpu(args) -> dict:
     import torch
 
     from crosspool_b200.bench import decode_bench as db
@@ -89,13 +100,19 @@ def main(argv=None) -> int:
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.gpus == 1 and world == 1:
-        res = run_single_gpu(args)
-        print(json.dumps(res))
-        return 0
-    from crosspool_b200.bench import fabric_bench
+    if args.decode_only:
+        if args.gpus == 1 and world == 1:
+            print(json.dumps(run_decode_only_single_gpu(args)))
+            return 0
+        from crosspool_b200.bench import fabric_bench
 
-    return fabric_bench.main(args)
+        return fabric_bench.main(args)
+    from crosspool_b200.bench import served
+
+    if args.gpus == 1 and world == 1:
+        print(json.dumps(served.run_single_gpu(args)))
+        return 0
+    return served.run_multi_gpu(args)
 
 
 if __name__ == "__main__":

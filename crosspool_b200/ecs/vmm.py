@@ -165,13 +165,16 @@ def bundle_geometry(cfg: ModelConfig, page_size: int, granularity: int = 2 << 20
 
 
 def elastic_kv_cache(cfg: ModelConfig, max_pages: int, page_size: int, device, driver: Driver,
-                     quota: MemoryQuota | None, initial_bundles: int = 0, make_tensors: bool = True) -> PagedKvCache:
+                     quota: MemoryQuota | None, initial_bundles: int = 0, make_tensors: bool = True,
+                     granularity: int = 2 << 20) -> PagedKvCache:
     """A paged KV cache over VMM ranges. ``make_tensors=False`` (CPU tests with the fake driver) leaves
-    the tensor lists empty; addresses are still reserved and mapped."""
+    the tensor lists empty; addresses are still reserved and mapped. ``granularity``: bytes of one physical
+    allocation per buffer and bundle (a multiple of the driver's 2 MiB granule); larger values move memory with
+    fewer driver calls per byte at the price of coarser lending."""
     from ..parallel.fabric import tensor_from_ptr
 
     dev_index = torch.device(device).index or 0
-    ppb, chunk = bundle_geometry(cfg, page_size)
+    ppb, chunk = bundle_geometry(cfg, page_size, granularity)
     n_bundles = (max_pages + ppb - 1) // ppb
     pages = n_bundles * ppb
     backing = KvVmmBacking(driver, dev_index, 2 * cfg.num_layers, n_bundles * chunk, chunk, quota)

@@ -47,3 +47,46 @@ class LocalFfnPort(FfnPort):
         gemm.gateup_swiglu(x, w.gate_up, out=act, bias=w.gate_up_bias, gate_limit=lim, up_add=up_add, act_alpha=alpha)
         gemm.linear(act, w.down, out=self.y[:rows], bias=w.down_bias)
         return [self.y[:rows]]
+
+
+class UnfusedFfnPort(FfnPort):
+    """Baseline arm of the benchmarks: the layer's FFN as library calls -- cuBLAS GEMMs through ``torch.matmul``
+    and a separate elementwise SwiGLU -- on the attention GPU's own memory. None of this repository's FFN kernels
+    run on this path (MoE layers excepted, for which there is no library restatement here)."""
+
+    def __init__(self, cfg: ModelConfig, weights: list[FfnLayerWeights]):
+        self.cfg, self.weights = cfg, weights
+        self._moe = LocalFfnPort(cfg, weights) if any(w.is_moe for w in weights) else None
+
+    def attach(self, engine) -> None:
+        dense = [w for w in self.weights if not w.is_moe]
+        inter2 = max((w.gate_up.shape[0] for w in dense), default=2)
+        dev, bf = engine.device, torch.bfloat16
+        self.gu = torch.zeros(engine.cap, inter2, dtype=bf, device=dev)
+        self.act = torch.zeros(engine.cap, inter2 // 2, dtype=bf, device=dev)
+        self.y = torch.zeros(engine.cap, self.cfg.hidden_size, dtype=bf, device=dev)
+        if self._moe is not None:
+            self._moe.attach(engine)
+
+    def run(self, layer: int, x: torch.Tensor, rows: int, mode: int) -> list[torch.Tensor]:
+        w = self.weights[layer]
+        if w.is_moe:
+            return self._moe.run(layer, x, rows, mode)
+        return [unfused_dense_ffn(x, w, self.gu, self.act, self.y)]
+
+
+def unfused_dense_ffn(x: torch.Tensor, w: FfnLayerWeights, gu: torch.Tensor, act: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """``down(silu(gate) * up)`` as library launches: two cuBLAS GEMMs, an elementwise SwiGLU, bias adds. The gate
+    rows of ``gate_up`` come first, then the up rows."""
+    rows, inter2 = x.shape[0], w.gate_up.shape[0]
+    g = gu[:rows, :inter2]
+    torch.matmul(x, w.gate_up.t(), out=g)
+    if w.gate_up_bias is not None:
+        g += w.gate_up_bias.to(g.dtype)
+    a = act[:rows, :inter2 // 2]
+    torch.mul(torch.nn.functional.silu(g[:, :inter2 // 2]), g[:, inter2 // 2:], out=a)
+    out = y[:rows]
+    torch.matmul(a, w.down.t(), out=out)
+    if w.down_bias is not None:
+        out += w.down_bias.to(out.dtype)
+    return out

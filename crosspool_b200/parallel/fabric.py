@@ -524,9 +524,10 @@ class RankContext:
 
 
 def build_rank(topo: Topology, rank: int, device, ecfg_for: dict[str, EngineConfig], group=None, n_lanes: int = 1,
-               policy: int = rt.POLICY_FIFO, tile_weights: bool = False) -> RankContext:
+               policy: int = rt.POLICY_FIFO, tile_weights: bool = False, kv_for=None) -> RankContext:
     """Creates this rank's side of every Instance and exchanges arena handles with its peers.
-    Collective over ``group`` (any backend that supports object collectives)."""
+    Collective over ``group`` (any backend that supports object collectives). ``kv_for(placement)`` may return
+    the KV cache an attention engine should use (an elastic one, say); None keeps the engine's fixed cache."""
     import torch.distributed as dist
 
     role = topo.role(rank)
@@ -580,6 +581,7 @@ def build_rank(topo: Topology, rank: int, device, ecfg_for: dict[str, EngineConf
                 tp.connect([handles[f"tp:{p.model_id}:{r}"] for r in range(tp.size)])
                 aw = atn_tp.shard_attention_weights(aw, p.cfg, tp.rank, tp.size)
                 cfg_local = atn_tp.local_config(p.cfg, tp.size)
-            ctx.engines[p.model_id] = AttentionEngine(cfg_local, aw, port, ecfg_for[p.model_id], device, tp=tp)
+            kv = kv_for(p) if kv_for is not None else None
+            ctx.engines[p.model_id] = AttentionEngine(cfg_local, aw, port, ecfg_for[p.model_id], device, kv=kv, tp=tp)
     dist.barrier(group=group)
     return ctx

@@ -36,13 +36,15 @@ class Pending:
     arrival: float
     temperature: float = 0.0
     seed: int = 0
-    out: "queue.Queue[tuple[int, bool] | Exception]" = field(default_factory=queue.Queue)
+    out: "queue.Queue[tuple[int, bool] | Exception] | None" = field(default_factory=queue.Queue)
     # set by an asyncio consumer: tokens are then also handed to its event loop, so that it never has to poll
     aio_loop: object = None
     aio_queue: object = None
+    tag: object = None   # opaque to the loop; an in-process consumer (``EngineLoop.sink``) finds its own record here
 
     def deliver(self, item) -> None:
-        self.out.put(item)
+        if self.out is not None:
+            self.out.put(item)
         if self.aio_loop is not None:
             self.aio_loop.call_soon_threadsafe(self.aio_queue.put_nowait, item)
 
@@ -51,7 +53,8 @@ def deliver_batch(batch: list[tuple[Pending, object]]) -> None:
     """Hands one engine step's tokens to their consumers: one wake-up of the event loop per step, not per token."""
     by_loop: dict = {}
     for p, item in batch:
-        p.out.put(item)
+        if p.out is not None:
+            p.out.put(item)
         if p.aio_loop is not None:
             by_loop.setdefault(p.aio_loop, []).append((p.aio_queue, item))
     for loop, items in by_loop.items():
@@ -64,8 +67,14 @@ def _fan_out(items) -> None:
 
 
 class EngineLoop:
-    def __init__(self, deployment: SteppedDeployment, idle_sleep: float = 0.0005):
+    """``sink``: an in-process consumer called on the loop thread once per engine step with that step's
+    ``[(Pending, (token, finished))]`` and a ``time.perf_counter()`` stamp taken after the step's tokens reached the
+    host; requests submitted with ``queued=False`` are delivered to it alone (no per-request queue)."""
+
+    def __init__(self, deployment: SteppedDeployment, idle_sleep: float = 0.0005, sink=None):
         self.dep = deployment
+        self.sink = sink
+        self._calls: "queue.Queue" = queue.Queue()
         self._inbox: "queue.Queue[Pending]" = queue.Queue()
         self._by_seq: dict[int, Pending] = {}
         self._stop = threading.Event()
@@ -76,9 +85,11 @@ class EngineLoop:
         self.tokens = 0
 
     def submit(self, model_id: str, prompt: list[int], max_new_tokens: int, temperature: float = 0.0, seed: int = 0,
-               aio: bool = False) -> Pending:
+               aio: bool = False, queued: bool = True, tag: object = None) -> Pending:
         """``aio``: called from a running event loop that will ``await p.aio_queue.get()``."""
-        p = Pending(model_id, prompt, max_new_tokens, time.monotonic(), temperature, seed)
+        p = Pending(model_id, prompt, max_new_tokens, time.monotonic(), temperature, seed, tag=tag)
+        if not queued:
+            p.out = None
         if aio:
             p.aio_loop, p.aio_queue = asyncio.get_running_loop(), asyncio.Queue()
         self._inbox.put(p)
@@ -97,6 +108,19 @@ class EngineLoop:
             except Exception as e:  # bad request: answer it, keep serving
                 p.deliver(e)
 
+    def call_between_steps(self, fn) -> None:
+        """Runs ``fn()`` on the loop thread before its next step, when no engine step is in flight (a benchmark
+        records its window boundaries this way)."""
+        self._calls.put(fn)
+
+    def _run_calls(self) -> None:
+        while True:
+            try:
+                fn = self._calls.get_nowait()
+            except queue.Empty:
+                return
+            fn()
+
     def _idle(self) -> None:
         tick = getattr(self.dep, "idle_tick", None)
         if tick is not None:
@@ -106,6 +130,7 @@ class EngineLoop:
     def _run(self) -> None:
         try:
             while not self._stop.is_set():
+                self._run_calls()
                 self._admit()
                 if not self.dep.has_work:
                     self._idle()
@@ -123,6 +148,8 @@ class EngineLoop:
                         self.tokens += 1
                         if done:
                             del self._by_seq[(model_id, seq.seq_id)]
+                if self.sink is not None:
+                    self.sink(batch, time.perf_counter())
                 deliver_batch(batch)
         except Exception as e:  # device failure: fail every waiting request, stop (fail-stop)
             self.error = e
