@@ -48,6 +48,8 @@ def parse_args(argv=None):
     ap.add_argument("--step-seconds", type=float, default=0.5)
     ap.add_argument("--mix", default="", choices=["", "b", "c", "e"], help="model mix (default: by GPU count)")
     ap.add_argument("--rate-scale", type=float, default=1.0, help="multiplies every arrival rate of the mix")
+    ap.add_argument("--max-batch", type=int, default=0, help="override the running-request limit of every Instance")
+    ap.add_argument("--kv-tokens", type=int, default=0, help="override the KV capacity (tokens) of every Instance")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the models (marks the result invalid)")
     ap.add_argument("--lanes", type=int, default=2, help="Executor Lanes per FFN device (multi-GPU only)")

@@ -138,10 +138,11 @@ def bench_prefill_attn(ns, timer: Timer) -> dict:
     q_lens = torch.full((S,), L, dtype=torch.int32, device="cuda")
     ctx = torch.zeros(S, dtype=torch.int32, device="cuda")
     out = torch.empty_like(q)
-    us = timer(lambda: A.paged_prefill(q, kc, vc, table, q_starts, q_lens, ctx, L, out=out))
+    us = timer(lambda: A.paged_prefill(q, kc, vc, table, q_starts, q_lens, ctx, L, out=out, force_simple=ns.kernel))
     flops = 4.0 * S * (L * (L + 1) / 2) * hq * d          # QK^T and PV over the causal half
     byts = (q.numel() + out.numel() + kc.numel() + vc.numel()) * 2
-    return report("paged_prefill_attention", us, byts, flops, {"seqs": S, "len": L, "q_heads": hq, "kv_heads": hkv})
+    return report("paged_prefill_attention", us, byts, flops, {"seqs": S, "len": L, "q_heads": hq, "kv_heads": hkv,
+                                                               "kernel": ns.kernel})
 
 
 def bench_norm(ns, timer: Timer) -> dict:
@@ -335,6 +336,8 @@ def main(argv: list[str] | None = None) -> int:
     pa.add_argument("--q-heads", type=int, default=16)
     pa.add_argument("--kv-heads", type=int, default=8)
     pa.add_argument("--head-dim", type=int, default=128)
+    pa.add_argument("--kernel", default="umma", choices=["umma", "mma", "simple"],
+                    help="umma: tcgen05 kernel; mma: TMA-fed mma.sync kernel; simple: plain mma.sync kernel")
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=256)
     n.add_argument("--hidden", type=int, default=1024)

@@ -85,8 +85,17 @@ def _lognormal(median, lo, hi, sigma=1.0):
     return LengthSpec("lognormal", lo, hi, float(median), sigma)
 
 
-def build_mix(name: str, world: int, scale: float) -> tuple[list[ModelStream], dict]:
-    """The Instances and traffic of a named mix on ``world`` GPUs. ``scale`` multiplies every arrival rate."""
+def build_mix(name: str, world: int, scale: float, max_batch: int = 0, kv_tokens: int = 0) -> tuple[list[ModelStream], dict]:
+    """The Instances and traffic of a named mix on ``world`` GPUs. ``scale`` multiplies every arrival rate;
+    ``max_batch`` / ``kv_tokens`` override every Instance's running-request limit and KV capacity (0: the mix's own)."""
+    streams, info = _build_mix(name, world, scale)
+    for s in streams:
+        s.max_batch = max_batch or s.max_batch
+        s.kv_tokens = kv_tokens or s.kv_tokens
+    return streams, info
+
+
+def _build_mix(name: str, world: int, scale: float) -> tuple[list[ModelStream], dict]:
     b_prompt, b_out = _uniform(128, 2048), _uniform(128, 512)
     if name == "b":
         # Qwen3-0.6B, prompts uniform 128-2048, outputs uniform 128-512 (ignore-eos), Poisson arrivals;
@@ -96,8 +105,8 @@ def build_mix(name: str, world: int, scale: float) -> tuple[list[ModelStream], d
         out = []
         for a in range(n_atn):
             ffn = (n_atn + a % n_ffn,) if n_ffn else ()
-            out.append(ModelStream(f"Qwen/Qwen3-0.6B#{a}", "Qwen/Qwen3-0.6B", a, a, ffn, 56.0 * scale, b_prompt, b_out,
-                                   max_batch=384, max_seq_len=2048 + 512 + PAGE, kv_tokens=704 * 1024))
+            out.append(ModelStream(f"Qwen/Qwen3-0.6B#{a}", "Qwen/Qwen3-0.6B", a, a, ffn, 72.0 * scale, b_prompt, b_out,
+                                   max_batch=768, max_seq_len=2048 + 512 + PAGE, kv_tokens=1152 * 1024))
         return out, {"name": "b", "layout": f"atn{n_atn}+ffn{n_ffn}" if n_ffn else "loopback",
                      "slo": {"ttft_ms": SLO_TTFT_MS, "tpot_ms": SLO_TPOT_MS}}
     if name == "c":
@@ -532,7 +541,7 @@ def run_single_gpu(args) -> dict:
 
     torch.cuda.set_device(0)
     dev = torch.device("cuda:0")
-    streams, info = build_mix(args.mix or "b", 1, args.rate_scale)
+    streams, info = build_mix(args.mix or "b", 1, args.rate_scale, args.max_batch, args.kv_tokens)
     bounds, end_s, window_s = timeline(args)
     reqs = plan_streams(streams, end_s, window_s, args.seed)
     insts, first = [], None
@@ -579,7 +588,7 @@ def run_multi_gpu(args) -> int:
     dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
     ctl = dist.new_group(backend="gloo")
 
-    streams, info = build_mix(args.mix or default_mix(world), world, args.rate_scale)
+    streams, info = build_mix(args.mix or default_mix(world), world, args.rate_scale, args.max_batch, args.kv_tokens)
     bounds, end_s, window_s = timeline(args)
     mine = [s for s in streams if s.atn_rank == rank]
     reqs = plan_streams(mine, end_s, window_s, args.seed) if mine else []

@@ -135,6 +135,9 @@ int xp_lane_set_instance(void* rt, int idx, const XpLaneInstanceDesc* d);
 int xp_lane_set_layer(void* rt, int inst, int layer, const XpLaneLayerDesc* d);
 int xp_lane_commit(void* rt);
 int xp_lane_launch(void* rt, int lane_index, uint64_t lease_ns, void* stream);
+int xp_lane_threads_start(void* rt, uint64_t lease_ns, int depth);
+int xp_lane_threads_stop(void* rt);
+int xp_lane_threads_state(void* rt, uint64_t* replays);
 int xp_lane_shutdown(void* rt, void* stream);
 int xp_lane_stats(void* rt, uint64_t* served, uint32_t* idle, uint32_t* status, void* stream);
 int xp_lane_trace_enable(void* rt, uint32_t capacity);
@@ -232,14 +235,17 @@ typedef struct XpPrefillAttnArgs {
   int num_seqs, max_q_len, q_heads, kv_heads, head_dim, page_size, max_blocks;
   float scale;
   int num_pages;              /* pages in the cache (bound of the tensor maps); 0: simple kernel only */
-  int force_simple;           /* testing: skip the pipelined kernel */
+  int force_simple;           /* kernel choice: 0 tcgen05 kernel (falls back when the shape is outside it),
+                                 1 plain mma.sync kernel, 2 TMA-fed mma.sync kernel */
   uint32_t* status;           /* optional: set non-zero when a bounded wait ran out */
+  int total_q;                /* rows of q / out (bound of the query tensor map); 0: no tcgen05 kernel */
 } XpPrefillAttnArgs;
 
 int xp_rope_kv(const XpRopeArgs* a, void* stream);
 int xp_decode_attn_splits(int batch, int kv_heads, int max_len);
 int xp_decode_attn(const XpDecodeAttnArgs* a, void* stream);
 int xp_prefill_attn(const XpPrefillAttnArgs* a, void* stream);
+int xp_prefill_attn_umma(const XpPrefillAttnArgs* a, void* stream);
 
 /* Small row-wise helpers. */
 int xp_embedding(const int* ids, const void* table, void* out, int rows, int hidden, int vocab,

@@ -70,6 +70,25 @@ inline int encode_kv_3d(CUtensorMap* out, const void* base, uint64_t tokens, uin
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// Packed queries [rows, q_heads, head_dim] (bf16) as a 3-D map whose box is 64 dims x `heads` heads x
+// `positions` rows (128-byte swizzle): the box lands in shared memory as heads * positions rows of 128 bytes,
+// row index = position * heads + head. Out-of-range rows read as zero.
+inline int encode_q_3d(CUtensorMap* out, const void* base, uint64_t rows, uint32_t q_heads, uint32_t head_dim,
+                       uint32_t heads, uint32_t positions) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || head_dim % 64 != 0) return -2;
+  if (heads == 0 || positions == 0 || heads > 256 || positions > 256) return -3;
+  cuuint64_t dims[3] = {head_dim, q_heads, rows};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 2, static_cast<cuuint64_t>(head_dim) * 2 * q_heads};
+  cuuint32_t box[3] = {64, heads, positions};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 // Small cache: encoding costs a few microseconds and serving reuses the same
 // (pointer, shape) pairs on every step.
 class Cache {
@@ -103,6 +122,24 @@ class Cache {
     }
     CUtensorMap m;
     int rc = encode_kv_3d(&m, base, tokens, kv_heads, head_dim);
+    if (rc != 0) return rc;
+    if (map_.size() > 8192) map_.clear();
+    map_.emplace(k, m);
+    *out = m;
+    return 0;
+  }
+
+  int get_q(CUtensorMap* out, const void* base, uint64_t rows, uint32_t q_heads, uint32_t head_dim, uint32_t heads,
+            uint32_t positions) {
+    Key k{base, rows, (static_cast<uint64_t>(q_heads) << 32) | head_dim, heads, positions, 4};
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = map_.find(k);
+    if (it != map_.end()) {
+      *out = it->second;
+      return 0;
+    }
+    CUtensorMap m;
+    int rc = encode_q_3d(&m, base, rows, q_heads, head_dim, heads, positions);
     if (rc != 0) return rc;
     if (map_.size() > 8192) map_.clear();
     map_.emplace(k, m);

@@ -495,9 +495,13 @@ extern "C" int xp_prefill_attn(const XpPrefillAttnArgs* a, void* stream) {
   using namespace xpool::attn;
   if (a->num_seqs <= 0 || a->max_q_len <= 0) return 0;
   if (a->q_heads % a->kv_heads != 0) return -11;
+  if ((a->force_simple & 0xff) == 0) {
+    const int rc = xp_prefill_attn_umma(a, stream);
+    if (rc <= 0) return rc;   // launched (0) or failed (< 0); 1: shape outside the tcgen05 kernel
+  }
   {
     const int G = a->q_heads / a->kv_heads;
-    const bool tc_ok = !a->force_simple && a->num_pages > 0 && a->page_size >= 16 && (a->page_size & (a->page_size - 1)) == 0 &&
+    const bool tc_ok = (a->force_simple & 0xff) != 1 && a->num_pages > 0 && a->page_size >= 16 && (a->page_size & (a->page_size - 1)) == 0 &&
                        (G == 1 || G == 2 || G == 4 || G == 8) && (reinterpret_cast<uintptr_t>(a->q) & 3) == 0;
     if (tc_ok && a->head_dim == 128) return launch_prefill_tc<128>(*a, G, reinterpret_cast<cudaStream_t>(stream));
     if (tc_ok && a->head_dim == 64) return launch_prefill_tc<64>(*a, G, reinterpret_cast<cudaStream_t>(stream));

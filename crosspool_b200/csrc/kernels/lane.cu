@@ -3,6 +3,10 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
+#include <deque>
+#include <string>
+#include <thread>
 #include <vector>
 
 #include "xpool/api.h"
@@ -169,6 +173,15 @@ struct Runtime {
   MoeLaneMaps* mmaps_d = nullptr;  // [n_lanes][n_instances]
   std::vector<void*> moe_allocs;
   bool has_moe = false;
+  // replay threads (xp_lane_threads_start): one host thread, stream and instantiated graph per Lane
+  int device = 0;
+  std::vector<std::thread> threads;
+  std::vector<cudaStream_t> lane_streams;
+  std::vector<cudaGraph_t> lane_graphs;
+  std::vector<cudaGraphExec_t> lane_execs;
+  std::atomic<bool> stop_threads{false};
+  std::atomic<int> thread_error{0};      // first CUDA error code a replay thread met (0: none)
+  std::atomic<uint64_t> replays{0};
 };
 
 constexpr size_t kCounterWords = 1 << 14;
@@ -187,6 +200,7 @@ extern "C" void* xp_lane_create(int n_instances, int n_lanes, int policy, uint64
   rt->ws_bytes_per_lane = ws_bytes_per_lane;
   int dev = 0;
   cudaGetDevice(&dev);
+  rt->device = dev;
   cudaDeviceGetAttribute(&rt->sms, cudaDevAttrMultiProcessorCount, dev);
   rt->slots_h.resize(n_instances);
   rt->layers_h.resize(n_instances);
@@ -487,6 +501,93 @@ extern "C" int xp_lane_launch(void* h, int lane_index, uint64_t lease_ns, void* 
   return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);
 }
 
+// Replays every Lane's graph from a host thread of this library, so that no interpreter lock and no other host
+// work of the process sits between two Lane iterations. The reference launches each Lane's persistent graph once
+// and lets it loop on the device (src/cext/ffnagent/runtime.cu:1041-1047); here a Lane iteration is a short graph
+// with a lease, and `depth` replays are kept enqueued so the device never waits for the host.
+// Captures happen on the calling thread, one Lane after the other; the threads only replay.
+extern "C" int xp_lane_threads_start(void* h, uint64_t lease_ns, int depth) {
+  auto* rt = static_cast<Runtime*>(h);
+  if (!rt->committed || !rt->threads.empty() || depth < 1 || depth > 16) return -1;
+  cudaSetDevice(rt->device);
+  rt->stop_threads.store(false);
+  rt->thread_error.store(0);
+  for (int lane = 0; lane < rt->n_lanes; ++lane) {
+    cudaStream_t s = nullptr;
+    cudaGraph_t g = nullptr;
+    cudaGraphExec_t x = nullptr;
+    if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) return -2;
+    // one eager iteration with a short lease: first-use set-up stays outside the capture
+    if (xp_lane_launch(h, lane, 1000000ull, s) != 0 || cudaStreamSynchronize(s) != cudaSuccess) return -3;
+    if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) != cudaSuccess) return -4;
+    const int rc = xp_lane_launch(h, lane, lease_ns, s);
+    if (cudaStreamEndCapture(s, &g) != cudaSuccess || rc != 0) return -5;
+    if (cudaGraphInstantiate(&x, g, 0) != cudaSuccess) return -6;
+    rt->lane_streams.push_back(s);
+    rt->lane_graphs.push_back(g);
+    rt->lane_execs.push_back(x);
+  }
+  for (int lane = 0; lane < rt->n_lanes; ++lane) {
+    rt->threads.emplace_back([rt, lane, depth]() {
+      cudaSetDevice(rt->device);
+      cudaStream_t s = rt->lane_streams[lane];
+      std::vector<cudaEvent_t> ev(depth);
+      for (auto& e : ev) cudaEventCreateWithFlags(&e, cudaEventDisableTiming | cudaEventBlockingSync);
+      std::deque<int> pending;
+      int next = 0;
+      while (!rt->stop_threads.load(std::memory_order_acquire)) {
+        cudaError_t e = cudaGraphLaunch(rt->lane_execs[lane], s);
+        if (e == cudaSuccess) e = cudaEventRecord(ev[next], s);
+        if (e != cudaSuccess) {
+          int zero = 0;
+          rt->thread_error.compare_exchange_strong(zero, static_cast<int>(e));
+          break;
+        }
+        rt->replays.fetch_add(1, std::memory_order_relaxed);
+        pending.push_back(next);
+        next = (next + 1) % depth;
+        if (static_cast<int>(pending.size()) >= depth) {
+          e = cudaEventSynchronize(ev[pending.front()]);
+          pending.pop_front();
+          if (e != cudaSuccess) {
+            int zero = 0;
+            rt->thread_error.compare_exchange_strong(zero, static_cast<int>(e));
+            break;
+          }
+        }
+      }
+      cudaStreamSynchronize(s);
+      for (auto& e : ev) cudaEventDestroy(e);
+    });
+  }
+  return 0;
+}
+
+// Ends the replay threads: the caller first sets the device-side shutdown word (xp_lane_shutdown) so that leases in
+// flight end at once. Returns the first CUDA error a thread met, as -100 - code, or 0.
+extern "C" int xp_lane_threads_stop(void* h) {
+  auto* rt = static_cast<Runtime*>(h);
+  rt->stop_threads.store(true, std::memory_order_release);
+  for (auto& t : rt->threads)
+    if (t.joinable()) t.join();
+  rt->threads.clear();
+  for (auto x : rt->lane_execs) cudaGraphExecDestroy(x);
+  for (auto g : rt->lane_graphs) cudaGraphDestroy(g);
+  for (auto s : rt->lane_streams) cudaStreamDestroy(s);
+  rt->lane_execs.clear();
+  rt->lane_graphs.clear();
+  rt->lane_streams.clear();
+  const int e = rt->thread_error.load();
+  return e == 0 ? 0 : -100 - e;
+}
+
+// (replays issued so far, first error code of a replay thread or 0)
+extern "C" int xp_lane_threads_state(void* h, uint64_t* replays) {
+  auto* rt = static_cast<Runtime*>(h);
+  if (replays != nullptr) *replays = rt->replays.load();
+  return rt->thread_error.load();
+}
+
 extern "C" int xp_lane_shutdown(void* h, void* stream) {
   auto* rt = static_cast<Runtime*>(h);
   static const uint32_t one = 1;
@@ -551,6 +652,7 @@ extern "C" int64_t xp_lane_trace_read(void* h, uint64_t* out, uint64_t max_event
 extern "C" void xp_lane_destroy(void* h) {
   auto* rt = static_cast<Runtime*>(h);
   if (rt == nullptr) return;
+  if (!rt->threads.empty()) xp_lane_threads_stop(h);
   if (rt->trace_events_d != nullptr) cudaFree(rt->trace_events_d);
   if (rt->trace_state_d != nullptr) cudaFree(rt->trace_state_d);
   for (auto* p : rt->layers_d)

@@ -232,6 +232,7 @@ class PrefillAttnArgs(C.Structure):
         ("num_pages", C.c_int),
         ("force_simple", C.c_int),
         ("status", C.c_void_p),
+        ("total_q", C.c_int),
     ]
 
 
@@ -322,6 +323,9 @@ def _declare_lane(lib: C.CDLL) -> None:
         "xp_lane_commit": [C.c_void_p],
         "xp_lane_launch": [C.c_void_p, C.c_int, C.c_uint64, C.c_void_p],
         "xp_lane_shutdown": [C.c_void_p, C.c_void_p],
+        "xp_lane_threads_start": [C.c_void_p, C.c_uint64, C.c_int],
+        "xp_lane_threads_stop": [C.c_void_p],
+        "xp_lane_threads_state": [C.c_void_p, C.POINTER(C.c_uint64)],
         "xp_lane_stats": [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.c_void_p],
         "xp_wait_flags": [C.POINTER(WaitArgs), C.c_void_p],
         "xp_signal_flags": [C.POINTER(SignalArgs), C.c_void_p],

@@ -41,9 +41,11 @@ def decode_splits(batch: int, kv_heads: int, max_len: int) -> int:
     return native.kernels().xp_decode_attn_splits(batch, kv_heads, max_len)
 
 
-# Which prefill kernel runs when the caller does not say: the pipelined one (XPOOL_PREFILL_PIPELINED=0 selects
-# the simple kernel, e.g. to bisect a numerical difference).
-PREFILL_SIMPLE_DEFAULT = os.environ.get("XPOOL_PREFILL_PIPELINED", "1") == "0"
+# Which prefill kernel runs when the caller does not say: "umma" (tcgen05 tensor cores, TMEM accumulators; shapes it
+# does not cover fall back to "mma"), "mma" (TMA-fed mma.sync kernel) or "simple" (plain mma.sync kernel).
+# XPOOL_PREFILL_KERNEL selects one, e.g. to bisect a numerical difference.
+PREFILL_KERNELS = {"umma": 0, "simple": 1, "mma": 2, "umma-swapped-v": 0x100}
+PREFILL_KERNEL_DEFAULT = os.environ.get("XPOOL_PREFILL_KERNEL", "umma")
 
 
 def decode_plan(batch: int, kv_heads: int, max_len: int) -> tuple[int, int]:
@@ -100,11 +102,13 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
 
 def paged_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                   q_starts: torch.Tensor, q_lens: torch.Tensor, ctx_lens: torch.Tensor, max_q_len: int, *,
-                  out: torch.Tensor | None = None, scale: float | None = None, force_simple: bool | None = None) -> torch.Tensor:
+                  out: torch.Tensor | None = None, scale: float | None = None,
+                  force_simple: bool | str | None = None) -> torch.Tensor:
     """Causal attention of packed chunk queries ``[total_q, q_heads, d]`` over the paged cache.
 
-    Runs the pipelined kernel (TMA-fed K/V ring, one CTA per KV head group) when pages hold a multiple of
-    16 tokens and 1, 2, 4 or 8 query heads share a KV head; ``force_simple`` selects the plain kernel."""
+    Runs the tcgen05 kernel (S and O in tensor memory, TMA-fed Q/K/V, the heads of a KV group packed into 128-row
+    tiles) when pages hold a power-of-two number of at least 16 tokens and 1, 2, 4, 8 or 16 query heads share a KV
+    head. ``force_simple``: True or ``"simple"`` selects the plain kernel, ``"mma"`` the TMA-fed mma.sync kernel."""
     _, q_heads, d = q.shape
     page_size, kv_heads = k_cache.shape[1], k_cache.shape[2]
     if out is None:
@@ -118,7 +122,9 @@ def paged_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     a.page_size, a.max_blocks = page_size, block_table.stride(0)
     a.scale = scale if scale is not None else d ** -0.5
     a.num_pages = k_cache.shape[0] if k_cache.is_contiguous() and v_cache.is_contiguous() else 0
-    a.force_simple = int(PREFILL_SIMPLE_DEFAULT if force_simple is None else force_simple)
+    which = PREFILL_KERNEL_DEFAULT if force_simple in (None, False) else ("simple" if force_simple is True else force_simple)
+    a.force_simple = PREFILL_KERNELS[which]
+    a.total_q = q.shape[0]
     from .gemm import scratch
 
     a.status = scratch(q.device).status.data_ptr()

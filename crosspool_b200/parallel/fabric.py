@@ -20,8 +20,6 @@ for Transport arenas (src/xpool/service/daemon/transport.py).
 from __future__ import annotations
 
 import ctypes as C
-import threading
-from collections import deque
 from dataclasses import dataclass, field
 
 import torch
@@ -334,8 +332,7 @@ class FfnRankRuntime:
         self.tile_weights = tile_weights
         self.instances: list[FfnInstanceState] = []
         self.handle = None
-        self._threads: list[threading.Thread] = []
-        self._stop = threading.Event()
+        self._running = False
         self.errors: list[str] = []
 
     def add_instance(self, place: InstancePlacement, tp_rank: int, layers: tuple[int, int] | None = None) -> FfnInstanceState:
@@ -428,54 +425,30 @@ class FfnRankRuntime:
                      "xp_lane_launch", 4)
 
     # -- serving threads ---------------------------------------------------------------------
-    def _capture_lane(self, lane: int, lease_ms: float):
-        stream = torch.cuda.Stream(self.device)
-        with torch.cuda.stream(stream):
-            self.launch_once(lane, min(lease_ms, 1.0), stream)  # eager once: set-up work outside capture
-            stream.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
-                self.launch_once(lane, lease_ms, stream)
-        return stream, graph
-
-    def _lane_loop(self, lane: int, stream, graph, depth: int) -> None:
-        try:
-            torch.cuda.set_device(self.device)
-            with torch.cuda.stream(stream):
-                pending: deque[torch.cuda.Event] = deque()
-                while not self._stop.is_set():
-                    graph.replay()
-                    ev = torch.cuda.Event()
-                    ev.record(stream)
-                    pending.append(ev)
-                    if len(pending) > depth:
-                        pending.popleft().synchronize()
-                stream.synchronize()
-        except Exception as e:  # pragma: no cover - surfaced through .errors
-            self.errors.append(f"lane {lane}: {e!r}")
-
     def start(self, lease_ms: float = 20.0, depth: int = 3) -> None:
-        """Captures every Lane's graph on the calling thread, one after the other (stream capture
-        does not tolerate another thread of the process preparing its own capture), then starts one
-        replay thread per Lane."""
-        self._stop.clear()
-        torch.cuda.set_device(self.device)
-        captured = [self._capture_lane(lane, lease_ms) for lane in range(self.n_lanes)]
-        self._graphs = captured
-        for lane, (stream, graph) in enumerate(captured):
-            t = threading.Thread(target=self._lane_loop, args=(lane, stream, graph, depth), daemon=True, name=f"lane{lane}")
-            t.start()
-            self._threads.append(t)
+        """Starts one replay thread per Lane inside the native library: each captures nothing itself (the graphs
+        are captured here, on the calling thread, one Lane after the other) and keeps ``depth`` replays of its
+        Lane's graph enqueued. No Python thread and no interpreter lock is on the path between two Lane iterations."""
+        if self.device.index is not None:
+            torch.cuda.set_device(self.device)
+        native.check(native.kernels().xp_lane_threads_start(self.handle, int(lease_ms * 1e6), depth),
+                     "xp_lane_threads_start", 0)
+        self._running = True
+
+    def _thread_state(self) -> tuple[int, int]:
+        n = C.c_uint64()
+        err = native.kernels().xp_lane_threads_state(self.handle, C.byref(n))
+        return n.value, err
 
     def stop(self) -> None:
-        self._stop.set()
-        if self.handle:
+        if self.handle and getattr(self, "_running", False):
             side = torch.cuda.Stream(self.device)
-            native.kernels().xp_lane_shutdown(self.handle, side.cuda_stream)
+            native.kernels().xp_lane_shutdown(self.handle, side.cuda_stream)   # leases in flight end at once
             side.synchronize()
-        for t in self._threads:
-            t.join(30)
-        self._threads.clear()
+            rc = native.kernels().xp_lane_threads_stop(self.handle)
+            self._running = False
+            if rc != 0:
+                self.errors.append(f"lane replay thread failed with CUDA error {-100 - rc}")
 
     def stats(self) -> dict:
         served = (C.c_uint64 * len(self.instances))()
@@ -484,7 +457,10 @@ class FfnRankRuntime:
         side = torch.cuda.Stream(self.device)
         native.check(native.kernels().xp_lane_stats(self.handle, served, idle, C.byref(status), side.cuda_stream),
                      "xp_lane_stats", 0)
-        return {"served": list(served), "idle_replays": list(idle), "status": status.value}
+        replays, err = self._thread_state()
+        if err and not self.errors:
+            self.errors.append(f"lane replay thread failed with CUDA error {err}")
+        return {"served": list(served), "idle_replays": list(idle), "status": status.value, "replays": replays}
 
     def enable_trace(self, capacity: int = 1 << 16) -> None:
         """Turns the fabric observer on (after ``install``, before ``start``)."""

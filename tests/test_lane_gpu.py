@@ -346,3 +346,51 @@ def test_lane_adds_shared_experts_to_the_routed_output(rows):
     finally:
         ffn.close()
         buf.free()
+
+
+def test_native_replay_threads_serve_invocations_without_a_python_thread():
+    """The library's own replay threads keep Lane iterations enqueued (2 ms leases, so no iteration outlives the test
+    step); the host publishes invocations with plain copies and polls the completion record. No kernel here needs
+    another launch to run at the same time: an idle iteration simply ends with its lease."""
+    import time
+
+    from crosspool_b200.ops import gemm
+    from crosspool_b200.parallel import fabric as F
+
+    ffn, places, atn = _make([("Qwen/Qwen3-0.6B", 2)], n_lanes=2)
+    try:
+        st, place = ffn.instances[0], places[0]
+        flay, alay = F.ffn_slot_layout(place), F.atn_slot_layout(place)
+        ffn.start(lease_ms=2.0, depth=3)
+        side = torch.cuda.Stream()
+        inp = st.slot.tensor(flay.input_offset, (place.capacity_rows, place.cfg.hidden_size), torch.bfloat16, "cuda")
+        rec = st.slot.tensor(flay.record_offset, (64,), torch.int32, "cuda")
+        done = atn[0].tensor(alay.completion_offset, (64,), torch.int32, "cuda")
+        out = atn[0].tensor(alay.output_offset, (place.capacity_rows, place.cfg.hidden_size), torch.bfloat16, "cuda")
+        done_host = torch.zeros(64, dtype=torch.int32).pin_memory()
+        for seq, (layer, rows) in enumerate([(0, 5), (1, 64), (0, 1)], start=1):
+            x = (torch.randn(rows, place.cfg.hidden_size) * 0.5).bfloat16().pin_memory()
+            rec_host = torch.zeros(64, dtype=torch.int32).pin_memory()
+            rec_host[0], rec_host[1], rec_host[2], rec_host[8] = rows, layer, 2, seq
+            with torch.cuda.stream(side):
+                inp[:rows].copy_(x, non_blocking=True)      # payload first, then the record that names it
+                side.synchronize()
+                rec.copy_(rec_host, non_blocking=True)
+                side.synchronize()
+                t0 = time.monotonic()
+                while True:
+                    done_host.copy_(done, non_blocking=True)
+                    side.synchronize()
+                    if int(done_host[4]) == seq or time.monotonic() - t0 > 10:
+                        break
+                    time.sleep(0.001)
+                assert (int(done_host[0]), int(done_host[1]), int(done_host[4])) == (0, rows, seq)
+                got = out[:rows].float().cpu()
+            torch.testing.assert_close(got, _ref(x.cuda(), st.weights[layer]).cpu(), atol=2e-2, rtol=2e-2)
+        s = ffn.stats()
+        assert s["served"] == [3] and s["status"] == 0 and s["replays"] >= 3
+        ffn.stop()
+        assert not ffn.errors
+        gemm.check_status(torch.device("cuda"))
+    finally:
+        ffn.close()

@@ -60,7 +60,7 @@ class FakeDep:
 
 
 def _args(**kw):
-    d = dict(steps=4, warmup=2, step_seconds=0.05, layers=0, impl="xpool")
+    d = dict(steps=4, warmup=2, step_seconds=0.05, layers=0, impl="xpool", max_batch=0, kv_tokens=0)
     d.update(kw)
     return argparse.Namespace(**d)
 
