@@ -128,7 +128,7 @@ def bench_prefill_attn(ns, timer: Timer) -> dict:
     """Causal prefill attention of ``--seqs`` prompts of ``--len`` tokens each (no cached context)."""
     from ..ops import attention as A
 
-    S, L, hq, hkv, d, page = ns.seqs, ns.len, ns.q_heads, ns.kv_heads, ns.head_dim, 16
+    S, L, hq, hkv, d, page = ns.seqs, ns.len, ns.q_heads, ns.kv_heads, ns.head_dim, ns.page
     blocks = (L + page - 1) // page
     table = torch.arange(S * blocks, dtype=torch.int32, device="cuda").view(S, blocks)
     kc = torch.randn(S * blocks, page, hkv, d, device="cuda").bfloat16()
@@ -142,7 +142,7 @@ def bench_prefill_attn(ns, timer: Timer) -> dict:
     flops = 4.0 * S * (L * (L + 1) / 2) * hq * d          # QK^T and PV over the causal half
     byts = (q.numel() + out.numel() + kc.numel() + vc.numel()) * 2
     return report("paged_prefill_attention", us, byts, flops, {"seqs": S, "len": L, "q_heads": hq, "kv_heads": hkv,
-                                                               "kernel": ns.kernel})
+                                                               "kernel": ns.kernel, "page": page})
 
 
 def bench_norm(ns, timer: Timer) -> dict:
@@ -336,6 +336,7 @@ def main(argv: list[str] | None = None) -> int:
     pa.add_argument("--q-heads", type=int, default=16)
     pa.add_argument("--kv-heads", type=int, default=8)
     pa.add_argument("--head-dim", type=int, default=128)
+    pa.add_argument("--page", type=int, default=16, help="tokens per KV page")
     pa.add_argument("--kernel", default="umma", choices=["umma", "mma", "simple"],
                     help="umma: tcgen05 kernel; mma: TMA-fed mma.sync kernel; simple: plain mma.sync kernel")
     n = sub.add_parser("norm")

@@ -44,7 +44,7 @@ from ..models import config as mc
 from .decode_bench import ClockSampler
 from .serving import LengthSpec, PlannedRequest, StreamSpec, plan_workload, workload_digest
 
-PAGE = 16
+PAGE = 64   # tokens per KV page: one TMA copy brings a whole 64-token K (or V) tile of the prefill attention
 METRIC = "aggregate output tok/s across co-located models at p99 TPOT SLO; p50 TTFT"
 SLO_TTFT_MS, SLO_TPOT_MS = 2000.0, 50.0
 WINDOWS = 3
@@ -153,12 +153,39 @@ def default_mix(world: int) -> str:
     return {1: "b", 2: "b", 4: "c", 8: "e"}.get(world, "b")
 
 
-def plan_streams(streams: list[ModelStream], total_s: float, window_s: float, seed: int) -> list[PlannedRequest]:
+def _mean(spec: LengthSpec) -> float:
+    if spec.kind == "uniform":
+        return (spec.lo + spec.hi) / 2
+    return min(spec.hi, spec.median * 1.65)     # log-normal with sigma 1: mean = median * e^0.5
+
+
+def preload_requests(s: ModelStream, seed: int, tpot_estimate_s: float = 0.02, fraction: float = 0.8) -> list[PlannedRequest]:
+    """Requests released at time 0 so that the warm-up intervals start near the steady state instead of an empty
+    deployment: about ``fraction`` of the concurrency that Little's law gives for the stream (arrival rate x output
+    length x time per token), each with a uniformly drawn share of its output still to produce, as requests caught
+    mid-flight would have. They arrive before the first measured window, so they never enter the latency statistics."""
+    from .serving import derive_rng
+
+    rng = derive_rng(seed, s.model_id, "preload")
+    vocab = mc.load(s.preset).vocab_size
+    n = min(s.max_batch, int(fraction * s.rate * _mean(s.output) * tpot_estimate_s))
+    out = []
+    for _ in range(n):
+        n_in = s.prompt.sample(rng)
+        n_out = max(1, int(s.output.sample(rng) * rng.uniform(0.05, 1.0)))
+        out.append(PlannedRequest(s.model_id, 0.0, [rng.randrange(vocab) for _ in range(n_in)], n_out, warmup=True))
+    return out
+
+
+def plan_streams(streams: list[ModelStream], total_s: float, window_s: float, seed: int, preload: bool = False
+                 ) -> list[PlannedRequest]:
     """Planned arrivals for every Instance over ``total_s`` seconds. Bursts repeat every window; Instances with an
-    alternate shape swap shapes every window."""
+    alternate shape swap shapes every window. ``preload`` adds each stream's time-0 backlog (``preload_requests``)."""
     reqs: list[PlannedRequest] = []
     for s in streams:
         vocab = mc.load(s.preset).vocab_size
+        if preload:
+            reqs += preload_requests(s, seed)
         if s.alt_prompt is None:
             bf, bs, bp = s.burst
             if bf > 1.0 and bp <= 0:
@@ -543,7 +570,7 @@ def run_single_gpu(args) -> dict:
     dev = torch.device("cuda:0")
     streams, info = build_mix(args.mix or "b", 1, args.rate_scale, args.max_batch, args.kv_tokens)
     bounds, end_s, window_s = timeline(args)
-    reqs = plan_streams(streams, end_s, window_s, args.seed)
+    reqs = plan_streams(streams, end_s, window_s, args.seed, preload=True)
     insts, first = [], None
     for s in streams:
         cfg = model_cfg(s, args.layers)
@@ -591,7 +618,7 @@ def run_multi_gpu(args) -> int:
     streams, info = build_mix(args.mix or default_mix(world), world, args.rate_scale, args.max_batch, args.kv_tokens)
     bounds, end_s, window_s = timeline(args)
     mine = [s for s in streams if s.atn_rank == rank]
-    reqs = plan_streams(mine, end_s, window_s, args.seed) if mine else []
+    reqs = plan_streams(mine, end_s, window_s, args.seed, preload=True) if mine else []
     cfgs = {s.model_id: model_cfg(s, args.layers) for s in streams}
     ecfgs = {s.model_id: engine_config(s) for s in streams}
     placements = [F.InstancePlacement(s.model_id, cfgs[s.model_id], seed=s.seed, atn_rank=s.atn_rank, ffn_ranks=s.ffn_ranks,

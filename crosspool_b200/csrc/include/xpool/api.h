@@ -79,17 +79,33 @@ typedef struct XpNormArgs {
   float eps;
   uint32_t* seq_counter;       /* optional device word: publish value = *seq_counter + 1, stored back */
   const uint32_t* meta_deadline_ptr; /* optional device word overriding meta_deadline_us (refreshed per step) */
+  /* observer (all null / 0: off) */
+  void* trace_events;
+  void* trace_state;
+  uint32_t trace_capacity;
+  uint32_t reserved;
 } XpNormArgs;
 
 /* Attention side: wait (bounded) until each flag reaches *want_ptr (or `want`). */
 typedef struct XpWaitArgs {
   const uint32_t* flags[8];
   const uint32_t* want_ptr;
-  const uint32_t* cancel;
+  const uint32_t* cancel;      /* usually the claim word of `failure`: non-zero ends the wait (status 5) */
   uint32_t* status;
   uint64_t wait_ns;
   uint32_t want;
   int n;
+  /* Canonical failure: a wait that runs out claims `failure` (first failure wins) and copies it into the
+     peers' slots so that every kernel waiting anywhere in the generation leaves at once. All optional. */
+  void* failure;               /* local FailureSlot */
+  void* peer_failures[8];      /* FailureSlots in the FFN ranks' memory */
+  int n_peer_failures;
+  uint32_t origin_pe, instance;
+  /* observer (all null / 0: off) */
+  void* trace_events;
+  void* trace_state;
+  uint32_t trace_capacity;
+  uint32_t reserved;
 } XpWaitArgs;
 
 /* Producer half of a flag handshake: *seq_counter += 1, then every flag receives the new value (release). */
@@ -109,6 +125,9 @@ typedef struct XpLaneInstanceDesc {
   void* out_peer;          /* attention device: [capacity_rows, hidden] partial of this TP rank */
   void* done_record_peer;  /* attention device: CompletionRecord of this TP rank */
   int capacity_rows, hidden, num_layers, act_ld;
+  void* failure_peer;      /* attention device: the Instance's failure slot (may be null) */
+  int pe;                  /* this FFN device's PE number */
+  int reserved;
 } XpLaneInstanceDesc;
 
 typedef struct XpLaneLayerDesc {
@@ -139,6 +158,11 @@ int xp_lane_threads_start(void* rt, uint64_t lease_ns, int depth);
 int xp_lane_threads_stop(void* rt);
 int xp_lane_threads_state(void* rt, uint64_t* replays);
 int xp_lane_shutdown(void* rt, void* stream);
+int xp_lane_failure(void* rt, uint32_t out6[6], void* stream);   /* {claim, result, origin, instance, sequence, layer} */
+/* Stand-alone event buffers for the attention-side observers (device memory). */
+int xp_trace_create(uint32_t capacity, void** events, void** state);
+int64_t xp_trace_read(void* events, void* state, uint32_t capacity, uint64_t* out, uint64_t max_events, uint64_t* dropped, void* stream);
+void xp_trace_destroy(void* events, void* state);
 int xp_lane_stats(void* rt, uint64_t* served, uint32_t* idle, uint32_t* status, void* stream);
 int xp_lane_trace_enable(void* rt, uint32_t capacity);
 int64_t xp_lane_trace_read(void* rt, uint64_t* out, uint64_t max_events, uint64_t* dropped, void* stream);

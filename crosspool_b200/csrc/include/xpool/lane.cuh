@@ -24,6 +24,7 @@
 #include "xpool/gemm_ws.cuh"
 #include "xpool/protocol.hpp"
 #include "xpool/scheduler.hpp"
+#include "xpool/hooks.cuh"
 #include "xpool/trace.cuh"
 
 namespace xpool {
@@ -83,6 +84,8 @@ struct alignas(128) InstanceSlot {
   void* act;                          // local scratch between the two GEMMs
   void* out_peer;                     // attention device: partial buffer of this TP rank
   uint32_t* done_flag_peer;           // attention device: completion sequence word
+  FailureSlot* failure_local;         // this slot's failure word (the attention side writes it when its wait ran out)
+  FailureSlot* failure_peer;          // attention device: the Instance's canonical failure slot
   const LayerEntry* layers;           // this instance's layer table
   int capacity_rows;
   int hidden;
@@ -135,6 +138,8 @@ struct alignas(128) LaneCtl {
   uint64_t next_ticket;
   uint64_t served[kMaxInstances];  // invocations completed per instance (statistics)
   trace::BufferView trace;         // fabric observer (null events pointer: off)
+  FailureSlot failure;             // first failure met on this device (canonical for the generation once reported)
+  uint32_t pe;                     // this device's PE number (origin of the failures it claims)
   SchedulerEntry entries[kMaxInstances];
   LaneState lanes[kMaxLanes];
 };

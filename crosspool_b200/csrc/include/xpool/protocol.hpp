@@ -97,15 +97,23 @@ struct alignas(256) CompletionRecord {
 };
 
 // First failure wins (the reference's canonical generation failure,
-// fabric/protocol.hpp:236-270).
+// fabric/protocol.hpp:236-270): whoever moves `claim` from 0 owns the slot, fills the payload and
+// releases claim = kFailureClaimed; everybody else only reads. Waiting kernels poll `claim` as their
+// cancel word, so one failure ends every wait of the generation within microseconds.
 struct alignas(64) FailureSlot {
-  uint32_t claim;  // 0 free, 1 claimed
+  uint32_t claim;  // 0 free, kFailureWriting while the owner fills the payload, kFailureClaimed after
   uint32_t result_code;
-  uint32_t origin;
+  uint32_t origin;  // PE that met the failure
   uint32_t instance_index;
   uint32_t invocation_sequence;
   uint32_t layer_ordinal;
 };
+constexpr uint32_t kFailureWriting = 2;
+constexpr uint32_t kFailureClaimed = 1;
+// Both 256-byte record blocks have room behind their fields: the failure slot of an FFN-side Instance slot
+// sits this many bytes into its InvocationRecord block, the failure slot of an attention-side slot this many
+// bytes into the block of its first CompletionRecord.
+constexpr uint64_t kFailureSlotOffset = 64;
 
 // ---------------------------------------------------------------- checked arithmetic
 

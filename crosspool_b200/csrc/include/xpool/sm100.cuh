@@ -316,6 +316,15 @@ __device__ __forceinline__ void tma_load_3d_addr(uint32_t smem_dst, const CUtens
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d_addr(uint32_t smem_dst, const CUtensorMap* m, uint32_t bar, int32_t c0,
+                                                 int32_t c1, int32_t c2, int32_t c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

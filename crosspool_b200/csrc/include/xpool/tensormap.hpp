@@ -70,6 +70,25 @@ inline int encode_kv_3d(CUtensorMap* out, const void* base, uint64_t tokens, uin
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// Paged KV cache [tokens, kv_heads, head_dim] (bf16) as a 4-D map (64 dims, tokens, 64-dim blocks of the head, heads)
+// whose box is `box_tokens` tokens of one head over the whole head dim: it lands in shared memory as one
+// [box_tokens][128 bytes] block per 64 dims, the blocks one after the other -- the operand layout of the tensor
+// cores -- with one copy instead of one per 64-dim block. box_tokens must not cross a page.
+inline int encode_kv_4d(CUtensorMap* out, const void* base, uint64_t tokens, uint32_t kv_heads, uint32_t head_dim,
+                        uint32_t box_tokens) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || head_dim % 64 != 0 || box_tokens == 0 || box_tokens > 256) return -2;
+  cuuint64_t dims[4] = {64, tokens, head_dim / 64, kv_heads};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(head_dim) * 2 * kv_heads, 128, static_cast<cuuint64_t>(head_dim) * 2};
+  cuuint32_t box[4] = {64, box_tokens, head_dim / 64, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 // Packed queries [rows, q_heads, head_dim] (bf16) as a 3-D map whose box is 64 dims x `heads` heads x
 // `positions` rows (128-byte swizzle): the box lands in shared memory as heads * positions rows of 128 bytes,
 // row index = position * heads + head. Out-of-range rows read as zero.
@@ -122,6 +141,23 @@ class Cache {
     }
     CUtensorMap m;
     int rc = encode_kv_3d(&m, base, tokens, kv_heads, head_dim);
+    if (rc != 0) return rc;
+    if (map_.size() > 8192) map_.clear();
+    map_.emplace(k, m);
+    *out = m;
+    return 0;
+  }
+
+  int get_kv4(CUtensorMap* out, const void* base, uint64_t tokens, uint32_t kv_heads, uint32_t head_dim, uint32_t box_tokens) {
+    Key k{base, tokens, kv_heads, head_dim, box_tokens, 5};
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = map_.find(k);
+    if (it != map_.end()) {
+      *out = it->second;
+      return 0;
+    }
+    CUtensorMap m;
+    int rc = encode_kv_4d(&m, base, tokens, kv_heads, head_dim, box_tokens);
     if (rc != 0) return rc;
     if (map_.size() > 8192) map_.clear();
     map_.emplace(k, m);

@@ -18,14 +18,7 @@ struct BufferView {
   uint32_t reserved;
 };
 
-// Event kinds written by the Lane kernels (fabric observer, FFN side).
-enum LaneEvent : uint32_t {
-  kLaneAdmitted = 1,   // a = instance, b = layer << 16 | rows (saturated)
-  kLaneCompleted = 2,  // a = instance, b = invocation sequence
-  kLaneIdle = 3,       // a = lane, b = idle replays so far
-  kLaneShutdown = 4,   // a = lane
-  kLaneRejected = 5,   // a = instance, b = result code
-};
+// Event kinds are listed in xpool/hooks.cuh (hooks::Kind), beside the hook points that write them.
 
 __device__ __forceinline__ void record(const BufferView& v, uint32_t kind, uint32_t a, uint32_t b) {
   if (v.events == nullptr) return;

@@ -12,8 +12,10 @@
 //               2^8 (the accumulated sum carries the same stale maximum, so the quotient is exact), and at the
 //               end normalises O and stores it.
 //   warps 4-7   the same for tile B.
-//   warp 8      TMA producer: Q tiles once, then a 3-stage ring of K/V tiles (16-token boxes through the page
-//               table, 128-byte swizzle).
+//   warp 8      TMA producer: Q tiles once, then a 3-stage ring of K/V tiles through the page table (128-byte
+//               swizzle). With pages of at least 64 tokens one 4-D copy brings a whole K (or V) tile; with smaller
+//               pages every 16 tokens and 64 dims are one copy. The lanes of the warp issue a stage's copies side
+//               by side: a single thread issuing sixteen small copies per stage was what bounded the kernel.
 //   warp 9      allocates tensor memory and issues every tcgen05.mma from one thread. S is double-buffered per
 //               tile and issued one K/V tile ahead, in the order S_A(t+1), PV_A(t), S_B(t+1), PV_B(t).
 //
@@ -72,7 +74,9 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                         const __grid_constant__ CUtensorMap tmap_v, XpPrefillAttnArgs a, int G, int g_shift) {
+                         const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_k3,
+                         const __grid_constant__ CUtensorMap tmap_v3, XpPrefillAttnArgs a, int G, int g_shift,
+                         int box_tokens) {
   const bool swap_v_offsets = (a.force_simple >> 8) & 1;   // diagnostic: exchange the two byte offsets of V's descriptor
   constexpr int kHalves = D / 64;                 // 64-dim (128-byte) column blocks of a row
   constexpr int kQHalf = kRows * 128;             // one 64-dim block of a query tile
@@ -112,7 +116,7 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         sm100::mbar_init(&bars.s_full[x][bf], 1);
         sm100::mbar_init(&bars.s_empty[x][bf], 4);
       }
-      sm100::mbar_init(&bars.p_full[x], kRows);
+      sm100::mbar_init(&bars.p_full[x], 4);
       sm100::mbar_init(&bars.pv_done[x], 1);
     }
     bars.abort_flag = 0;
@@ -130,35 +134,45 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
+    // One copy per (K or V, box of box_tokens tokens); the lanes of the warp issue a stage's copies side by side,
+    // each after its own page-table lookup.
     if (lane == 0) {
       sm100::tma_prefetch_desc(&tmap_q);
       sm100::tma_prefetch_desc(&tmap_k);
       sm100::tma_prefetch_desc(&tmap_v);
-      const uint32_t qbar = sm100::smem_u32(&bars.q_full);
       sm100::mbar_arrive_expect_tx(&bars.q_full, 2 * kQTile);
-      for (int x = 0; x < 2; ++x)
-        for (int h = 0; h < kHalves; ++h)
-          sm100::tma_load_3d_addr(q_s + x * kQTile + h * kQHalf, &tmap_q, qbar, h * 64, hk * G, q_base + q0 + x * np);
-      const int page_shift = 31 - __clz(a.page_size);
-      const int page_mask = a.page_size - 1;
-      const int* table = a.block_table + static_cast<size_t>(seq) * a.max_blocks;
-      for (int t = 0; t < n_tiles; ++t) {
-        const int s = t % kStages;
-        if (t >= kStages && !wait_bar(&bars.kv_empty[s], ((t / kStages) - 1) & 1, &bars)) break;
-        const uint32_t bar = sm100::smem_u32(&bars.kv_full[s]);
-        const uint32_t dst = kv_s + s * kStage;
-        sm100::mbar_arrive_expect_tx(&bars.kv_full[s], kStage);
-#pragma unroll
-        for (int j = 0; j < kBN / 16; ++j) {
-          int tk = t * kBN + j * 16;
-          if (tk >= kv_end) tk = (kv_end - 1) & ~15;     // boxes past the end repeat the last valid one (masked)
+    }
+    __syncwarp();
+    if (lane < 2 * kHalves) {
+      const int x = lane / kHalves, h = lane % kHalves;
+      sm100::tma_load_3d_addr(q_s + x * kQTile + h * kQHalf, &tmap_q, sm100::smem_u32(&bars.q_full), h * 64, hk * G,
+                              q_base + q0 + x * np);
+    }
+    const int page_shift = 31 - __clz(a.page_size);
+    const int page_mask = a.page_size - 1;
+    const int* table = a.block_table + static_cast<size_t>(seq) * a.max_blocks;
+    const int boxes = kBN / box_tokens;            // boxes per tile and tensor
+    const int box_bytes = box_tokens * 128;        // one 64-dim block of a box
+    for (int t = 0; t < n_tiles; ++t) {
+      const int s = t % kStages;
+      if (t >= kStages && !__all_sync(0xffffffffu, wait_bar(&bars.kv_empty[s], ((t / kStages) - 1) & 1, &bars))) break;
+      if (lane == 0) sm100::mbar_arrive_expect_tx(&bars.kv_full[s], kStage);
+      __syncwarp();
+      if (boxes == 1) {
+        if (lane < 2) {
+          int tk = t * kBN;
+          if (tk >= kv_end) tk = (kv_end - 1) & ~(kBN - 1);
           const int tok = (table[tk >> page_shift] << page_shift) + (tk & page_mask);
-#pragma unroll
-          for (int h = 0; h < kHalves; ++h) {
-            sm100::tma_load_3d_addr(dst + h * kKVHalf + j * 2048, &tmap_k, bar, h * 64, hk, tok);
-            sm100::tma_load_3d_addr(dst + kKVTile + h * kKVHalf + j * 2048, &tmap_v, bar, h * 64, hk, tok);
-          }
+          sm100::tma_load_4d_addr(kv_s + s * kStage + lane * kKVTile, lane ? &tmap_v : &tmap_k,
+                                  sm100::smem_u32(&bars.kv_full[s]), 0, tok, 0, hk);
         }
+      } else if (lane < 2 * boxes * kHalves) {
+        const int h = lane % kHalves, is_v = (lane / kHalves) & 1, j = lane / (2 * kHalves);
+        int tk = t * kBN + j * box_tokens;
+        if (tk >= kv_end) tk = (kv_end - 1) & ~(box_tokens - 1);   // boxes past the end repeat the last valid one (masked)
+        const int tok = (table[tk >> page_shift] << page_shift) + (tk & page_mask);
+        sm100::tma_load_3d_addr(kv_s + s * kStage + is_v * kKVTile + h * kKVHalf + j * box_bytes, is_v ? &tmap_v3 : &tmap_k3,
+                                sm100::smem_u32(&bars.kv_full[s]), h * 64, hk, tok);
       }
     }
   } else if (warp == 9) {
@@ -333,8 +347,9 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(v_s + off), "r"(0u) : "memory");
           }
         }
-        sm100::fence_proxy_async_smem();
-        sm100::mbar_arrive(&bars.p_full[x]);
+        sm100::fence_proxy_async_smem();   // this thread's P (and V) stores, for the tensor core's reads
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive(&bars.p_full[x]);
       }
       if (ok && my_tiles > 0) ok = __all_sync(0xffffffffu, wait_bar(&bars.pv_done[x], (my_tiles - 1) & 1, &bars));
       if (ok) {
@@ -376,13 +391,17 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 
 template <int D>
 static int launch(const XpPrefillAttnArgs& a, int G, cudaStream_t s) {
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mk3, mv3;
   const uint64_t tokens = static_cast<uint64_t>(a.num_pages) * a.page_size;
   int g_shift = 0;
   while ((1 << g_shift) < G) ++g_shift;
   const int np = kRows >> g_shift;
-  if (tmap::cache().get_kv(&mk, a.k_cache, tokens, a.kv_heads, D) != 0) return -20;
-  if (tmap::cache().get_kv(&mv, a.v_cache, tokens, a.kv_heads, D) != 0) return -20;
+  // pages of 64 tokens or more: one copy brings a whole K (or V) tile; smaller pages: one copy per page and 64 dims
+  const int box_tokens = a.page_size >= kBN ? kBN : 16;
+  if (tmap::cache().get_kv4(&mk, a.k_cache, tokens, a.kv_heads, D, kBN) != 0) return -20;
+  if (tmap::cache().get_kv4(&mv, a.v_cache, tokens, a.kv_heads, D, kBN) != 0) return -20;
+  if (tmap::cache().get_kv(&mk3, a.k_cache, tokens, a.kv_heads, D) != 0) return -20;
+  if (tmap::cache().get_kv(&mv3, a.v_cache, tokens, a.kv_heads, D) != 0) return -20;
   if (tmap::cache().get_q(&mq, a.q, static_cast<uint64_t>(a.total_q), a.q_heads, D, G, np) != 0) return -20;
   constexpr int kSmem = 2 * (D / 64) * kRows * 128 + kStages * 2 * (D / 64) * kBN * 128 + 2 * kRows * 128 + 1024;
   static bool attr_set = false;
@@ -392,7 +411,7 @@ static int launch(const XpPrefillAttnArgs& a, int G, cudaStream_t s) {
     attr_set = true;
   }
   dim3 grid((a.max_q_len + 2 * np - 1) / (2 * np), a.kv_heads, a.num_seqs);
-  prefill_attn_umma_kernel<D><<<grid, kThreads, kSmem, s>>>(mq, mk, mv, a, G, g_shift);
+  prefill_attn_umma_kernel<D><<<grid, kThreads, kSmem, s>>>(mq, mk, mv, mk3, mv3, a, G, g_shift, box_tokens);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);
 }

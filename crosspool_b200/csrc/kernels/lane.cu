@@ -34,6 +34,17 @@ __global__ void moe_lane_combine_kernel(const lane::InstanceSlot* slots, const l
 
 namespace lane {
 
+// First failure wins on this device; the winner copies it into the failure slot of every Instance's attention
+// rank (first wins there as well), so that every kernel waiting for this device leaves with the same payload
+// (the reference's converge_failure + publish_to_all, src/cext/fabric/atnagent.cu:101-119, coordinator.cu:403-410).
+__device__ void converge_failure(LaneCtl* ctl, const InstanceSlot* slots, uint32_t result_code, uint32_t instance,
+                                 uint32_t sequence, uint32_t layer) {
+  if (!failure::claim(&ctl->failure, result_code, ctl->pe, instance, sequence, layer)) return;
+  hooks::Point<hooks::LaneFailureClaimed>::hooks({ctl->trace, instance, result_code});
+  for (uint32_t i = 0; i < ctl->n_instances; ++i)
+    failure::claim(slots[i].failure_peer, result_code, ctl->pe, instance, sequence, layer);
+}
+
 // One thread: find work for this Lane or give up when the lease runs out.
 __global__ void lane_wait_kernel(LaneCtl* ctl, const InstanceSlot* slots, LaneCur* cur, uint32_t lane_index,
                                  uint64_t lease_ns) {
@@ -47,8 +58,20 @@ __global__ void lane_wait_kernel(LaneCtl* ctl, const InstanceSlot* slots, LaneCu
   while (true) {
     if (sm100::ld_relaxed_sys(&ctl->shutdown) != 0) {
       cur->result_code = static_cast<uint32_t>(ResultCode::Shutdown);
-      trace::record(ctl->trace, trace::kLaneShutdown, lane_index, 0);
+      hooks::Point<hooks::LaneShutdown>::hooks({ctl->trace, lane_index});
       return;
+    }
+    // A failed generation serves nothing more: a failure claimed on this device, or one that an attention rank
+    // wrote into the slot of one of its Instances, ends the iteration (the slot's failure becomes this device's).
+    if (failure::claimed(&ctl->failure)) {
+      cur->result_code = static_cast<uint32_t>(ResultCode::Shutdown);
+      hooks::Point<hooks::LaneFailureObserved>::hooks({ctl->trace, lane_index, ctl->failure.origin});
+      return;
+    }
+    for (uint32_t i = 0; i < n; ++i) {
+      const FailureSlot* f = slots[i].failure_local;
+      if (f != nullptr && sm100::ld_acquire_sys(&f->claim) == kFailureClaimed)
+        failure::claim(&ctl->failure, f->result_code, f->origin, i, f->invocation_sequence, f->layer_ordinal);
     }
     // cheap look before taking the lock: is any slot ahead of its completed sequence?
     bool any = false;
@@ -67,7 +90,10 @@ __global__ void lane_wait_kernel(LaneCtl* ctl, const InstanceSlot* slots, LaneCu
         const uint32_t seq = sm100::ld_acquire_sys(slots[i].in_flag);
         const uint32_t done = static_cast<uint32_t>(e.completed_sequence);
         const int32_t ahead = static_cast<int32_t>(seq - done);
-        if (ahead > 0) sched.enqueue(i, e.completed_sequence + static_cast<uint64_t>(ahead), slots[i].record->deadline_us);
+        if (ahead > 0) {
+          sched.enqueue(i, e.completed_sequence + static_cast<uint64_t>(ahead), slots[i].record->deadline_us);
+          hooks::Point<hooks::LaneDiscovered>::hooks({ctl->trace, i, seq});
+        }
       }
       const Decision d = sched.try_schedule_on(lane_index);
       lock_release(&ctl->lock);
@@ -93,14 +119,17 @@ __global__ void lane_wait_kernel(LaneCtl* ctl, const InstanceSlot* slots, LaneCu
         cur->result_code = rc;
         __threadfence();
         cur->valid = 1;
-        if (rc != 0) trace::record(ctl->trace, trace::kLaneRejected, d.instance, rc);
-        trace::record(ctl->trace, trace::kLaneAdmitted, d.instance, (layer << 16) | (rows > 0xffffu ? 0xffffu : rows));
+        if (rc != 0) {
+          hooks::Point<hooks::LaneRejected>::hooks({ctl->trace, d.instance, rc});
+          converge_failure(ctl, slots, rc, d.instance, cur->sequence, rec->layer_ordinal);
+        }
+        hooks::Point<hooks::LaneAdmitted>::hooks({ctl->trace, d.instance, layer, rows});
         return;
       }
     }
     if ((++spins & 0xfu) == 0 && sm100::global_timer_ns() > deadline) {
       cur->idle_replays += 1;
-      trace::record(ctl->trace, trace::kLaneIdle, lane_index, cur->idle_replays);
+      hooks::Point<hooks::LaneIdle>::hooks({ctl->trace, lane_index, cur->idle_replays});
       return;
     }
     __nanosleep(200);
@@ -108,34 +137,63 @@ __global__ void lane_wait_kernel(LaneCtl* ctl, const InstanceSlot* slots, LaneCu
 }
 
 // One thread: publish the completion on the attention device, free the Lane.
-__global__ void lane_complete_kernel(LaneCtl* ctl, const InstanceSlot* slots, LaneCur* cur, uint32_t lane_index) {
+__global__ void lane_complete_kernel(LaneCtl* ctl, const InstanceSlot* slots, LaneCur* cur, uint32_t lane_index,
+                                     const uint32_t* status) {
   if (cur->valid == 0) return;
   const InstanceSlot& s = slots[cur->instance];
+  // a bounded wait inside the Lane's GEMMs ran out: the output is not trustworthy
+  if (cur->result_code == 0 && status != nullptr && *status != 0) {
+    cur->result_code = static_cast<uint32_t>(ResultCode::Timeout);
+    converge_failure(ctl, slots, cur->result_code, cur->instance, cur->sequence, cur->layer);
+  }
   CompletionRecord* done = reinterpret_cast<CompletionRecord*>(s.done_flag_peer);
   done->result_code = cur->result_code;
   done->rows = cur->rows;
   __threadfence_system();
   sm100::st_release_sys(&done->sequence, cur->sequence);
-  if (lock_acquire(&ctl->lock, sm100::global_timer_ns() + 1000000ull)) {
-    Scheduler sched(ctl->entries, ctl->n_instances, ctl->lanes, ctl->n_lanes,
-                    SchedulerPolicy{static_cast<SchedulerPolicyKind>(ctl->policy), ctl->seed}, &ctl->next_ticket);
-    sched.release(cur->instance, cur->lease);
-    ctl->served[cur->instance] += 1;
-    lock_release(&ctl->lock);
+  // The Lane must go back to the scheduler or the Instance stays Running for ever: keep trying for the
+  // data-plane limit, and make a failure of it if even that runs out.
+  bool released = false;
+  for (int attempt = 0; attempt < 5000 && !released; ++attempt) {
+    if (lock_acquire(&ctl->lock, sm100::global_timer_ns() + 1000000ull)) {
+      Scheduler sched(ctl->entries, ctl->n_instances, ctl->lanes, ctl->n_lanes,
+                      SchedulerPolicy{static_cast<SchedulerPolicyKind>(ctl->policy), ctl->seed}, &ctl->next_ticket);
+      sched.release(cur->instance, cur->lease);
+      ctl->served[cur->instance] += 1;
+      lock_release(&ctl->lock);
+      released = true;
+    }
   }
-  trace::record(ctl->trace, trace::kLaneCompleted, cur->instance, cur->sequence);
+  if (!released) {
+    hooks::Point<hooks::LaneLockTimeout>::hooks({ctl->trace, lane_index, 1});
+    converge_failure(ctl, slots, static_cast<uint32_t>(ResultCode::Timeout), cur->instance, cur->sequence, cur->layer);
+  }
+  hooks::Point<hooks::LaneCompleted>::hooks({ctl->trace, cur->instance, cur->sequence});
   cur->valid = 0;
-  (void)lane_index;
 }
 
 // Attention side: up to 8 threads each wait until their flag reaches *want.
 __global__ void wait_flags_kernel(XpWaitArgs a) {
   const int i = threadIdx.x;
   if (i >= a.n) return;
+  const trace::BufferView tv{static_cast<trace::Event*>(a.trace_events), static_cast<trace::BufferState*>(a.trace_state),
+                             a.trace_capacity, 0};
   const uint32_t want = a.want_ptr != nullptr ? *a.want_ptr : a.want;
+  hooks::Point<hooks::AtnWaitBegin>::hooks({tv, static_cast<uint32_t>(i), want});
   const uint64_t deadline = sm100::global_timer_ns() + a.wait_ns;
   const int rc = sm100::wait_flag_ge(a.flags[i], want, deadline, a.cancel);
-  if (rc != 0 && a.status != nullptr) atomicCAS(a.status, 0u, 4u);
+  hooks::Point<hooks::AtnWaitEnd>::hooks({tv, static_cast<uint32_t>(i), want, static_cast<uint32_t>(rc)});
+  if (rc == 0) return;
+  if (a.status != nullptr) atomicCAS(a.status, 0u, rc == 2 ? 5u /*cancelled by a failure elsewhere*/ : 4u /*timed out*/);
+  if (rc == 1) {
+    // our own wait ran out and nobody reported a failure: this rank claims it and tells the FFN ranks
+    FailureSlot* f = static_cast<FailureSlot*>(a.failure);
+    if (failure::claim(f, static_cast<uint32_t>(ResultCode::Timeout), a.origin_pe, a.instance, want, 0xffffffffu)) {
+      for (int d = 0; d < a.n_peer_failures && d < 8; ++d)
+        failure::claim(static_cast<FailureSlot*>(a.peer_failures[d]), static_cast<uint32_t>(ResultCode::Timeout), a.origin_pe,
+                       a.instance, want, 0xffffffffu);
+    }
+  }
 }
 
 // Bumps a device-resident sequence counter and releases the new value into up to 8 flag words
@@ -173,6 +231,7 @@ struct Runtime {
   MoeLaneMaps* mmaps_d = nullptr;  // [n_lanes][n_instances]
   std::vector<void*> moe_allocs;
   bool has_moe = false;
+  int pe = 0;
   // replay threads (xp_lane_threads_start): one host thread, stream and instantiated graph per Lane
   int device = 0;
   std::vector<std::thread> threads;
@@ -257,6 +316,9 @@ extern "C" int xp_lane_set_instance(void* h, int idx, const XpLaneInstanceDesc* 
   s.act = d->act;
   s.out_peer = d->out_peer;
   s.done_flag_peer = reinterpret_cast<uint32_t*>(d->done_record_peer);
+  s.failure_local = reinterpret_cast<FailureSlot*>(reinterpret_cast<uint8_t*>(const_cast<void*>(d->record)) + kFailureSlotOffset);
+  s.failure_peer = reinterpret_cast<FailureSlot*>(d->failure_peer);
+  rt->pe = d->pe;
   s.capacity_rows = d->capacity_rows;
   s.hidden = d->hidden;
   s.num_layers = d->num_layers;
@@ -452,6 +514,8 @@ extern "C" int xp_lane_commit(void* h) {
     rt->slots_h[i].layers = rt->layers_d[i];
   }
   cudaMemcpy(rt->slots_d, rt->slots_h.data(), sizeof(lane::InstanceSlot) * rt->n_instances, cudaMemcpyHostToDevice);
+  const uint32_t pe = static_cast<uint32_t>(rt->pe);
+  cudaMemcpy(&rt->ctl_d->pe, &pe, sizeof(pe), cudaMemcpyHostToDevice);
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm::gemm_lane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
@@ -496,7 +560,7 @@ extern "C" int xp_lane_launch(void* h, int lane_index, uint64_t lease_ns, void* 
     gemm::gemm_lane_kernel<<<rt->sms, gemm::kThreads, smem, s>>>(rt->slots_d, cur, 4, ws, counters, smem_budget, rt->status_d,
                                                                  mws, mmaps);
   }
-  lane::lane_complete_kernel<<<1, 1, 0, s>>>(rt->ctl_d, rt->slots_d, cur, lane_index);
+  lane::lane_complete_kernel<<<1, 1, 0, s>>>(rt->ctl_d, rt->slots_d, cur, lane_index, rt->status_d);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);
 }
@@ -595,6 +659,55 @@ extern "C" int xp_lane_shutdown(void* h, void* stream) {
                  cudaSuccess
              ? 0
              : -1;
+}
+
+// The first failure this device met, as {claim, result code, origin PE, instance, sequence, layer}; claim 0: none.
+extern "C" int xp_lane_failure(void* h, uint32_t out6[6], void* stream) {
+  auto* rt = static_cast<Runtime*>(h);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  FailureSlot f;
+  if (cudaMemcpyAsync(&f, &rt->ctl_d->failure, sizeof(f), cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return -2;
+  out6[0] = f.claim;
+  out6[1] = f.result_code;
+  out6[2] = f.origin;
+  out6[3] = f.instance_index;
+  out6[4] = f.invocation_sequence;
+  out6[5] = f.layer_ordinal;
+  return 0;
+}
+
+extern "C" int xp_trace_create(uint32_t capacity, void** events, void** state) {
+  if (capacity == 0 || events == nullptr || state == nullptr) return -1;
+  if (cudaMalloc(events, sizeof(trace::Event) * capacity) != cudaSuccess) return -2;
+  if (cudaMalloc(state, sizeof(trace::BufferState)) != cudaSuccess) return -2;
+  return cudaMemset(*state, 0, sizeof(trace::BufferState)) == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int64_t xp_trace_read(void* events, void* state, uint32_t capacity, uint64_t* out, uint64_t max_events,
+                                 uint64_t* dropped, void* stream) {
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  trace::BufferState st;
+  if (cudaMemcpyAsync(&st, state, sizeof(st), cudaMemcpyDeviceToHost, s) != cudaSuccess) return -2;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return -2;
+  const uint64_t n = std::min<uint64_t>(std::min<uint64_t>(st.sequence, capacity), max_events);
+  std::vector<trace::Event> ev(n);
+  if (n > 0) {
+    cudaMemcpyAsync(ev.data(), events, sizeof(trace::Event) * n, cudaMemcpyDeviceToHost, s);
+    if (cudaStreamSynchronize(s) != cudaSuccess) return -2;
+  }
+  for (uint64_t i = 0; i < n; ++i) {
+    out[3 * i] = (static_cast<uint64_t>(ev[i].kind) << 32) | ev[i].a;
+    out[3 * i + 1] = ev[i].b;
+    out[3 * i + 2] = ev[i].timestamp_ns;
+  }
+  if (dropped != nullptr) *dropped = st.dropped;
+  return static_cast<int64_t>(n);
+}
+
+extern "C" void xp_trace_destroy(void* events, void* state) {
+  if (events != nullptr) cudaFree(events);
+  if (state != nullptr) cudaFree(state);
 }
 
 // served[n_instances], idle[n_lanes], status[1]; synchronous copies on `stream`.

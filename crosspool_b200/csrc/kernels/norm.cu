@@ -11,6 +11,7 @@
 // straight into each FFN rank's own memory with ordinary peer stores, followed
 // by a system-scope release of a sequence word.
 #include "xpool/api.h"
+#include "xpool/hooks.cuh"
 #include "xpool/sm100.cuh"
 
 namespace xpool {
@@ -56,7 +57,12 @@ norm_publish_kernel(XpNormArgs a) {
   if (a.wait_seq != 0 && threadIdx.x < a.nparts && a.wait_flags[threadIdx.x] != nullptr) {
     const uint64_t deadline = sm100::global_timer_ns() + a.wait_ns;
     int rc = sm100::wait_flag_ge(a.wait_flags[threadIdx.x], a.wait_seq, deadline, a.cancel);
-    if (rc != 0) s_fail = 1;
+    if (rc != 0) {
+      s_fail = 1;
+      const trace::BufferView tv{static_cast<trace::Event*>(a.trace_events), static_cast<trace::BufferState*>(a.trace_state),
+                                 a.trace_capacity, 0};
+      hooks::Point<hooks::AtnFoldWaitTimedOut>::hooks({tv, static_cast<uint32_t>(row), a.wait_seq});
+    }
   }
   __syncthreads();
   const bool failed = s_fail != 0;
@@ -167,6 +173,9 @@ norm_publish_kernel(XpNormArgs a) {
           }
           sm100::st_release_sys(a.peer_flags[d], seq);
         }
+        const trace::BufferView tv{static_cast<trace::Event*>(a.trace_events), static_cast<trace::BufferState*>(a.trace_state),
+                                   a.trace_capacity, 0};
+        hooks::Point<hooks::AtnPublished>::hooks({tv, a.meta_layer, static_cast<uint32_t>(gridDim.x), seq});
       }
     }
   }

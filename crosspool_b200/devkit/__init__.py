@@ -2,8 +2,8 @@
 into one chrome-trace file. Every observer is off unless its ``debug.*_observer_enabled`` setting
 (or ``XPOOL_DEBUG_*_OBSERVER_ENABLED``) is on, and an un-observed run allocates nothing."""
 
-from .observers import (FabricObserver, GraphObserver, ObserverSet, RoutingObserver, TransportObserver, chrome_trace,
+from .observers import (AtnFabricObserver, FabricObserver, GraphObserver, ObserverSet, RoutingObserver, TransportObserver, chrome_trace,
                         observers_for_role)
 
-__all__ = ["FabricObserver", "GraphObserver", "ObserverSet", "RoutingObserver", "TransportObserver", "chrome_trace",
+__all__ = ["AtnFabricObserver", "FabricObserver", "GraphObserver", "ObserverSet", "RoutingObserver", "TransportObserver", "chrome_trace",
            "observers_for_role"]

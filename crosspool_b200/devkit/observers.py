@@ -23,7 +23,10 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any, Iterable
 
-LANE_EVENT_NAMES = {1: "admitted", 2: "completed", 3: "idle", 4: "shutdown", 5: "rejected"}
+LANE_EVENT_NAMES = {1: "admitted", 2: "completed", 3: "idle", 4: "shutdown", 5: "rejected", 6: "discovered", 7: "lock_timeout",
+                    8: "failure_claimed", 9: "failure_observed"}
+ATN_EVENT_NAMES = {16: "published", 17: "fold_wait_timed_out", 18: "wait_begin", 19: "wait_end", 20: "wait_timed_out",
+                   21: "wait_cancelled"}
 TRANSPORT_EVENT_NAMES = {1: "publish", 2: "wait_begin", 3: "wait_end", 4: "timeout", 5: "cancelled", 6: "host_submit",
                          7: "host_collect"}
 
@@ -79,12 +82,47 @@ class FabricObserver(_Base):
                 e.update(instance=a, layer=b >> 16, rows=b & 0xFFFF)
             elif kind == 2:
                 e.update(instance=a, sequence=b)
-            elif kind == 5:
+            elif kind in (5, 8):
                 e.update(instance=a, result_code=b)
+            elif kind == 6:
+                e.update(instance=a, sequence=b)
+            elif kind == 9:
+                e.update(lane=a, origin_pe=b)
             else:
                 e.update(lane=a, count=b)
             ev.append(e)
         return TraceArtifact(self.name, self.role, os.getpid(), ev, dropped)
+
+
+class AtnFabricObserver(_Base):
+    """Drains the device event buffer of an attention-side Fabric port (``FabricFfnPort.enable_trace``) and groups the
+    events of each invocation into a timeline: published -> wait_begin -> wait_end | wait_timed_out | wait_cancelled,
+    keyed by the invocation sequence (the reference keeps a ``Timeline<Event>`` per invocation,
+    src/cext/devkit/fabric_observer.cu)."""
+
+    name = "fabric"
+
+    def __init__(self, port, role: str = "AtnAgent", out_dir=None):
+        super().__init__(role, out_dir)
+        self.port = port
+
+    def collect(self) -> TraceArtifact:
+        raw, dropped = self.port.trace.read()
+        ev, timelines = [], {}
+        for kind, a, b, ts in raw:
+            name = ATN_EVENT_NAMES.get(kind, str(kind))
+            e = {"name": name, "ts_ns": ts, "sequence": b}
+            if kind == 16:
+                e.update(layer=a >> 16, rows=a & 0xFFFF)
+            else:
+                e.update(flag=a)
+            ev.append(e)
+            t = timelines.setdefault(b, {"sequence": b})
+            t.setdefault(name, ts)
+        done = [t for t in timelines.values() if "published" in t and "wait_end" in t]
+        for t in done:
+            t["round_trip_ns"] = t["wait_end"] - t["published"]
+        return TraceArtifact(self.name, self.role, os.getpid(), ev, dropped, {"timelines": sorted(timelines.values(), key=lambda t: t["sequence"])})
 
 
 class TransportObserver(_Base):

@@ -109,6 +109,10 @@ class NormArgs(C.Structure):
         ("eps", C.c_float),
         ("seq_counter", C.c_void_p),
         ("meta_deadline_ptr", C.c_void_p),
+        ("trace_events", C.c_void_p),
+        ("trace_state", C.c_void_p),
+        ("trace_capacity", C.c_uint32),
+        ("reserved", C.c_uint32),
     ]
 
 
@@ -259,6 +263,15 @@ class WaitArgs(C.Structure):
         ("wait_ns", C.c_uint64),
         ("want", C.c_uint32),
         ("n", C.c_int),
+        ("failure", C.c_void_p),
+        ("peer_failures", C.c_void_p * 8),
+        ("n_peer_failures", C.c_int),
+        ("origin_pe", C.c_uint32),
+        ("instance", C.c_uint32),
+        ("trace_events", C.c_void_p),
+        ("trace_state", C.c_void_p),
+        ("trace_capacity", C.c_uint32),
+        ("reserved", C.c_uint32),
     ]
 
 
@@ -278,6 +291,9 @@ class LaneInstanceDesc(C.Structure):
         ("hidden", C.c_int),
         ("num_layers", C.c_int),
         ("act_ld", C.c_int),
+        ("failure_peer", C.c_void_p),
+        ("pe", C.c_int),
+        ("reserved", C.c_int),
     ]
 
 
@@ -314,6 +330,11 @@ def _declare_lane(lib: C.CDLL) -> None:
     lib.xp_lane_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_size_t]
     lib.xp_lane_destroy.restype = None
     lib.xp_lane_destroy.argtypes = [C.c_void_p]
+    lib.xp_trace_read.restype = C.c_int64
+    lib.xp_trace_read.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(C.c_uint64), C.c_uint64, C.POINTER(C.c_uint64),
+                                  C.c_void_p]
+    lib.xp_trace_destroy.restype = None
+    lib.xp_trace_destroy.argtypes = [C.c_void_p, C.c_void_p]
     lib.xp_lane_trace_read.restype = C.c_int64
     lib.xp_lane_trace_read.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.c_uint64, C.POINTER(C.c_uint64), C.c_void_p]
     sig = {
@@ -323,6 +344,8 @@ def _declare_lane(lib: C.CDLL) -> None:
         "xp_lane_commit": [C.c_void_p],
         "xp_lane_launch": [C.c_void_p, C.c_int, C.c_uint64, C.c_void_p],
         "xp_lane_shutdown": [C.c_void_p, C.c_void_p],
+        "xp_lane_failure": [C.c_void_p, C.POINTER(C.c_uint32), C.c_void_p],
+        "xp_trace_create": [C.c_uint32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)],
         "xp_lane_threads_start": [C.c_void_p, C.c_uint64, C.c_int],
         "xp_lane_threads_stop": [C.c_void_p],
         "xp_lane_threads_state": [C.c_void_p, C.POINTER(C.c_uint64)],

@@ -36,13 +36,15 @@ def add_rmsnorm(parts: Sequence[torch.Tensor] | torch.Tensor, weight: torch.Tens
                 wait_ns: int = 5_000_000_000, meta: tuple[int, int, int] = (0, 0, 0),
                 want_local: bool = True, seq_counter_ptr: int = 0,
                 part_ptrs: Sequence[int] | None = None, part_shape: tuple[int, int, int] | None = None,
-                deadline_ptr: int = 0) -> torch.Tensor | None:
+                deadline_ptr: int = 0, cancel_ptr: int = 0, trace: tuple[int, int, int] | None = None) -> torch.Tensor | None:
     """``y = rmsnorm(sum(parts) + resid) * weight``; ``resid`` is updated in place.
 
     ``parts`` are bf16 ``[rows, hidden]`` tensors summed in list order. Parts that live in another
     GPU's memory are given as raw mapped pointers instead: ``part_ptrs`` with
     ``part_shape = (rows, hidden, leading dimension)``; the device then comes from ``resid``/``out``.
-    With ``weight=None`` only the residual add happens.
+    With ``weight=None`` only the residual add happens. ``cancel_ptr``: a device word that ends the waits when it
+    turns non-zero (the claim word of the Instance's failure slot). ``trace``: (events, state, capacity) of a device
+    event buffer the kernel's hook points record into.
     """
     if isinstance(parts, torch.Tensor):
         parts = [parts]
@@ -73,7 +75,9 @@ def add_rmsnorm(parts: Sequence[torch.Tensor] | torch.Tensor, weight: torch.Tens
     a.out_local = out.data_ptr() if (out is not None and want_local) else None
     a.done_counter = _done_counter(dev).data_ptr()
     a.status = scratch(dev).status.data_ptr()
-    a.cancel = None
+    a.cancel = cancel_ptr or None
+    if trace is not None:
+        a.trace_events, a.trace_state, a.trace_capacity = trace
     a.wait_ns = wait_ns
     a.rows, a.hidden = rows, hidden
     a.ld_parts = ld_parts

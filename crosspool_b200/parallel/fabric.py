@@ -33,6 +33,47 @@ from ..native import runtime as rt
 RECORD_SEQ_OFFSET = 32      # InvocationRecord.sequence
 COMPLETION_SEQ_OFFSET = 16  # CompletionRecord.sequence
 RECORD_BYTES = 256
+FAILURE_SLOT_OFFSET = 64    # failure slot inside the first 256-byte record block of a slot (protocol.hpp)
+RESULT_NAMES = {0: "ok", 1: "shutdown", 2: "protocol_mismatch", 3: "timeout"}
+
+
+@dataclass
+class FabricFailure:
+    """The canonical failure of a generation as one slot recorded it (first failure wins)."""
+
+    result_code: int
+    origin_pe: int
+    instance_index: int
+    invocation_sequence: int
+    layer_ordinal: int
+
+    @classmethod
+    def from_words(cls, w) -> "FabricFailure | None":
+        return cls(int(w[1]), int(w[2]), int(w[3]), int(w[4]), int(w[5])) if int(w[0]) == 1 else None
+
+
+class DeviceTrace:
+    """A device event buffer for the attention-side hook points (publish, wait begin / end)."""
+
+    def __init__(self, capacity: int = 1 << 16):
+        ev, st = C.c_void_p(), C.c_void_p()
+        native.check(native.kernels().xp_trace_create(capacity, C.byref(ev), C.byref(st)), "xp_trace_create", 0)
+        self.events, self.state, self.capacity = ev.value, st.value, capacity
+
+    def args(self) -> tuple[int, int, int]:
+        return self.events, self.state, self.capacity
+
+    def read(self, stream: int = 0) -> tuple[list[tuple[int, int, int, int]], int]:
+        out, dropped = (C.c_uint64 * (3 * self.capacity))(), C.c_uint64()
+        n = native.kernels().xp_trace_read(self.events, self.state, self.capacity, out, self.capacity, C.byref(dropped), stream)
+        if n < 0:
+            raise RuntimeError(f"xp_trace_read failed with {n}")
+        return [(out[3 * i] >> 32, out[3 * i] & 0xFFFFFFFF, out[3 * i + 1], out[3 * i + 2]) for i in range(n)], dropped.value
+
+    def close(self) -> None:
+        if self.events:
+            native.kernels().xp_trace_destroy(self.events, self.state)
+            self.events = self.state = 0
 
 
 class PeerBuffer:
@@ -210,6 +251,17 @@ class FabricFfnPort(FfnPort):
         self._wait.n = tp
         self._wait.want_ptr = self.seq.data_ptr()
         self._wait.wait_ns = self.wait_ns
+        # canonical failure: this Instance's slot lives behind the first completion record; its claim word cancels
+        # every wait of the Instance, and a wait of ours that runs out claims it and tells the FFN ranks
+        self.failure_ptr = local.ptr + self.alay.completion_offset + FAILURE_SLOT_OFFSET
+        self._failure_words = local.tensor(self.alay.completion_offset + FAILURE_SLOT_OFFSET, (8,), torch.int32, self.device)
+        self._wait.cancel = self.failure_ptr
+        self._wait.failure = self.failure_ptr
+        for i, b in enumerate(ffn_bases[:8]):
+            self._wait.peer_failures[i] = b + self.flay.record_offset + FAILURE_SLOT_OFFSET
+        self._wait.n_peer_failures = min(8, len(ffn_bases))
+        self._wait.origin_pe, self._wait.instance = place.atn_rank, 0
+        self.trace: DeviceTrace | None = None
 
     def attach(self, engine: AttentionEngine) -> None:
         from ..ops.gemm import scratch
@@ -217,6 +269,23 @@ class FabricFfnPort(FfnPort):
         if engine.cap > self.place.capacity_rows:
             raise ValueError("engine row capacity exceeds the fabric slot capacity")
         self._wait.status = scratch(self.device).status.data_ptr()
+
+    def set_wait_limit(self, wait_ns: int) -> None:
+        self.wait_ns = self._wait.wait_ns = int(wait_ns)
+
+    def wait_args(self) -> dict:
+        return dict(cancel_ptr=self.failure_ptr)
+
+    def enable_trace(self, capacity: int = 1 << 16) -> DeviceTrace:
+        """Attaches a device event buffer to this port's publish and wait kernels (the transport observer of the
+        attention side)."""
+        self.trace = DeviceTrace(capacity)
+        self._wait.trace_events, self._wait.trace_state, self._wait.trace_capacity = self.trace.args()
+        return self.trace
+
+    def failure(self) -> FabricFailure | None:
+        """The failure recorded in this Instance's slot, if any (reads six words from the device)."""
+        return FabricFailure.from_words(self._failure_words.cpu().tolist())
 
     def begin_step(self, now_s: float | None = None) -> None:
         """Stamps the step's deadline (call before launching the step; a 16-byte pinned copy)."""
@@ -231,7 +300,7 @@ class FabricFfnPort(FfnPort):
 
     def publish_targets(self, layer: int, rows: int, mode: int) -> dict:
         bases = next(b for lo, hi, b in self._group_bases if lo <= layer < hi)   # the TP group that holds this layer
-        return dict(deadline_ptr=self.deadline.data_ptr(),
+        return dict(deadline_ptr=self.deadline.data_ptr(), trace=self.trace.args() if self.trace is not None else None,
                     peer_ptrs=[b + self.flay.input_offset for b in bases],
                     peer_flag_ptrs=[b + self.flay.record_offset + RECORD_SEQ_OFFSET for b in bases],
                     peer_meta_ptrs=[b + self.flay.record_offset for b in bases],
@@ -326,8 +395,9 @@ class FfnRankRuntime:
     """Everything an FFN rank owns: shards, slots, the native Lane runtime and the Lane threads."""
 
     def __init__(self, device, n_lanes: int = 1, policy: int = rt.POLICY_FIFO, seed: int = 0,
-                 ws_bytes_per_lane: int = 64 << 20, tile_weights: bool = False):
+                 ws_bytes_per_lane: int = 64 << 20, tile_weights: bool = False, pe: int = 0):
         self.device = torch.device(device)
+        self.pe = pe   # this device's PE number: the origin written into failures it claims
         self.n_lanes, self.policy, self.seed, self.ws_bytes = n_lanes, policy, seed, ws_bytes_per_lane
         self.tile_weights = tile_weights
         self.instances: list[FfnInstanceState] = []
@@ -380,6 +450,8 @@ class FfnRankRuntime:
             d.record = st.slot.ptr + flay.record_offset
             d.out_peer = st.atn_base + alay.output_offset + st.tp_rank * alay.output_stride
             d.done_record_peer = st.atn_base + alay.completion_offset + st.tp_rank * RECORD_BYTES
+            d.failure_peer = st.atn_base + alay.completion_offset + FAILURE_SLOT_OFFSET
+            d.pe = self.pe
             d.capacity_rows, d.hidden, d.num_layers, d.act_ld = p.capacity_rows, p.cfg.hidden_size, p.cfg.num_layers, act_ld
             native.check(lib.xp_lane_set_instance(self.handle, i, C.byref(d)), "xp_lane_set_instance", 0)
             for l, w in enumerate(st.weights):
@@ -462,6 +534,13 @@ class FfnRankRuntime:
             self.errors.append(f"lane replay thread failed with CUDA error {err}")
         return {"served": list(served), "idle_replays": list(idle), "status": status.value, "replays": replays}
 
+    def failure(self) -> FabricFailure | None:
+        """The first failure this device met (claimed here, or written into a slot by an attention rank)."""
+        w = (C.c_uint32 * 6)()
+        side = torch.cuda.Stream(self.device)
+        native.check(native.kernels().xp_lane_failure(self.handle, w, side.cuda_stream), "xp_lane_failure", 0)
+        return FabricFailure.from_words(list(w))
+
     def enable_trace(self, capacity: int = 1 << 16) -> None:
         """Turns the fabric observer on (after ``install``, before ``start``)."""
         native.check(native.kernels().xp_lane_trace_enable(self.handle, capacity), "xp_lane_trace_enable", 0)
@@ -512,7 +591,7 @@ def build_rank(topo: Topology, rank: int, device, ecfg_for: dict[str, EngineConf
     atn_local: dict[str, PeerBuffer] = {}
     tp_groups: dict = {}
     if role == "ffn":
-        ctx.ffn = FfnRankRuntime(device, n_lanes=n_lanes, policy=policy, tile_weights=tile_weights)
+        ctx.ffn = FfnRankRuntime(device, n_lanes=n_lanes, policy=policy, tile_weights=tile_weights, pe=rank)
         for p in topo.instances:
             if rank in p.ffn_ranks:
                 tp_rank, lo, hi = p.locate(rank)

@@ -69,9 +69,9 @@ class FfnBackend:
 
     def prepare_join(self, plan: FabricPlan) -> dict[str, str]:
         torch.cuda.set_device(self.cuda)
-        self.rt = F.FfnRankRuntime(self.cuda, n_lanes=plan.lanes_per_ffn_device, policy=_POLICY[plan.policy],
-                                   seed=self.cfg.scheduler_ffn_random_seed or 0)
         my_pe = len(plan.atn_devices) + plan.ffn_devices.index(self.device)
+        self.rt = F.FfnRankRuntime(self.cuda, n_lanes=plan.lanes_per_ffn_device, policy=_POLICY[plan.policy],
+                                   seed=self.cfg.scheduler_ffn_random_seed or 0, pe=my_pe)
         handles = {}
         for r in plan.instance_ranks:
             if r.rank % self.cfg.model(r.model_id).atn_tp_size:
@@ -100,9 +100,13 @@ class FfnBackend:
             return None
         if self.rt.errors:
             raise RuntimeError("; ".join(self.rt.errors))
+        f = self.rt.failure()     # the canonical failure: who met it, for which Instance, sequence and layer
+        if f is not None:
+            return InvocationFailure(result_code=f.result_code, origin_pe=f.origin_pe, instance_index=f.instance_index,
+                                     invocation_sequence=f.invocation_sequence, layer_ordinal=f.layer_ordinal)
         st = self.rt.stats()
-        if st["status"] != 0:
-            return InvocationFailure(result_code=3, origin_pe=-1, instance_index=0, invocation_sequence=0, layer_ordinal=0)
+        if st["status"] != 0:   # a kernel status outside any invocation (no slot to blame)
+            return InvocationFailure(result_code=3, origin_pe=self.rt.pe, instance_index=0, invocation_sequence=0, layer_ordinal=0)
         return None
 
     def quiesce(self) -> None:
@@ -291,6 +295,12 @@ class AtnBackend:
             self.listener = ServingListener(host=self._listen[0], port=self._listen[1])
 
     def poll_health(self) -> InvocationFailure | None:
+        for eng in self.engines.values():
+            probe = getattr(eng.port, "failure", None)
+            f = probe() if probe is not None else None
+            if f is not None:   # claimed by an FFN rank, or by this rank when its own wait ran out
+                return InvocationFailure(result_code=f.result_code, origin_pe=f.origin_pe, instance_index=f.instance_index,
+                                         invocation_sequence=f.invocation_sequence, layer_ordinal=f.layer_ordinal)
         if self.loop is not None and self.loop.error is not None:
             raise RuntimeError(f"engine loop failed: {self.loop.error!r}")
         return None

@@ -103,6 +103,32 @@ def test_long_context_chunked_prefill_and_decode_match_reference():
         assert _kl(ref_logits[1:2], logits[1][None]).item() <= 0.005
 
 
+def test_32k_token_prompt_with_64_token_pages_matches_reference():
+    """The longest prompt of the elastic two-model acceptance configuration (32,768 tokens) through eight 4096-token
+    prefill chunks over 64-token pages (whole-tile TMA copies in the prefill attention), then split-KV decode. The
+    oracle consumes the prompt in 2048-token pieces so that its score matrix fits."""
+    cfg, eng, ref = _build("Qwen/Qwen3-0.6B", layers=2, max_batch=4, prefill_chunk=4096, max_seq_len=32768 + 64,
+                           page_size=64)
+    eng.warmup()
+    g = torch.Generator().manual_seed(9)
+    prompt = torch.randint(0, cfg.vocab_size, (32768,), generator=g).tolist()
+    s = eng.add_request(prompt, 2)
+    logits = []
+    while eng.has_work:
+        for i, (q, tok) in enumerate(eng.step()):
+            logits.append(eng.logits[i].clone())
+    from crosspool_b200.ops import gemm
+    gemm.check_status(eng.device)
+    assert eng.stats["prefill_steps"] == 8 and len(s.generated) == 2
+    cache = ref.new_cache()
+    ids = torch.tensor(prompt, device="cuda")
+    with torch.no_grad():
+        for lo in range(0, len(prompt), 2048):
+            last = ref.forward(ids[lo:lo + 2048], torch.arange(lo, lo + 2048, device="cuda"), cache)[-1:]
+    assert _kl(last, logits[0][None]).item() <= 0.05
+    assert torch.isfinite(logits[1].float()).all()
+
+
 def test_chunked_prefill_equals_single_chunk():
     cfg, eng_small, _ = _build("Qwen/Qwen3-0.6B", layers=2, max_batch=4, prefill_chunk=64, max_seq_len=512,
                                use_cuda_graph=False)

@@ -130,7 +130,7 @@ def test_fabric_observer_records_lane_events_in_order_and_counts_overflow():
 
     ffn, places, atn = _make([("Qwen/Qwen3-0.6B", 1)])
     try:
-        ffn.enable_trace(4)
+        ffn.enable_trace(6)
         st, place = ffn.instances[0], places[0]
         ffn.launch_once(0, lease_ms=2)                      # idle
         x = (torch.randn(3, place.cfg.hidden_size, device="cuda") * 0.5).bfloat16()
@@ -140,8 +140,9 @@ def test_fabric_observer_records_lane_events_in_order_and_counts_overflow():
             torch.cuda.synchronize()
         art = devkit.FabricObserver(ffn).collect()
         names = [e["name"] for e in art.events]
-        assert names == ["idle", "admitted", "completed", "admitted"] and art.dropped == 1   # capacity 4, never wraps
-        assert art.events[1]["rows"] == 3 and art.events[1]["layer"] == 0 and art.events[2]["sequence"] == 1
+        # capacity 6, never wraps: the second invocation's completion does not fit
+        assert names == ["idle", "discovered", "admitted", "completed", "discovered", "admitted"] and art.dropped == 1
+        assert art.events[2]["rows"] == 3 and art.events[2]["layer"] == 0 and art.events[3]["sequence"] == 1
         ts = [e["ts_ns"] for e in art.events]
         assert ts == sorted(ts)
     finally:
@@ -392,5 +393,58 @@ def test_native_replay_threads_serve_invocations_without_a_python_thread():
         ffn.stop()
         assert not ffn.errors
         gemm.check_status(torch.device("cuda"))
+    finally:
+        ffn.close()
+
+
+def test_a_rejected_invocation_becomes_the_canonical_failure_and_cancels_waits_at_once():
+    """First failure wins: the Lane that refuses a bad record claims the device's failure slot and copies it into the
+    attention-side slot; a wait that polls that slot as its cancel word returns at once instead of running into its
+    limit, the hook points record both sides, and later Lane iterations serve nothing more."""
+    import time
+
+    from crosspool_b200 import devkit, native
+    from crosspool_b200.ops import gemm
+    from crosspool_b200.parallel import fabric as F
+
+    ffn, places, atn = _make([("Qwen/Qwen3-0.6B", 2)])
+    try:
+        ffn.enable_trace(64)
+        st, place = ffn.instances[0], places[0]
+        alay = F.atn_slot_layout(place)
+        assert ffn.failure() is None
+        x = (torch.randn(3, place.cfg.hidden_size, device="cuda") * 0.5).bfloat16()
+        _publish(F, st, place, x, 77, 1)                      # no such layer
+        ffn.launch_once(0, lease_ms=20)
+        torch.cuda.synchronize()
+        f = ffn.failure()
+        assert f is not None and (f.result_code, f.origin_pe, f.instance_index, f.invocation_sequence, f.layer_ordinal) == (2, 0, 0, 1, 77)
+        words = atn[0].tensor(alay.completion_offset + F.FAILURE_SLOT_OFFSET, (8,), torch.int32, "cuda").cpu().tolist()
+        assert F.FabricFailure.from_words(words) == f         # the attention side holds the same payload
+        # a wait for a completion that will never come: cancelled by the failure word, far inside its 2 s limit
+        w = native.WaitArgs()
+        w.flags[0] = atn[0].ptr + alay.completion_offset + F.COMPLETION_SEQ_OFFSET
+        w.n, w.want, w.wait_ns = 1, 9, 2_000_000_000
+        w.cancel = atn[0].ptr + alay.completion_offset + F.FAILURE_SLOT_OFFSET
+        status = gemm.scratch(torch.device("cuda")).status
+        status.zero_()
+        w.status = status.data_ptr()
+        trace = F.DeviceTrace(16)
+        w.trace_events, w.trace_state, w.trace_capacity = trace.args()
+        t0 = time.monotonic()
+        native.check(native.kernels().xp_wait_flags(C.byref(w), torch.cuda.current_stream().cuda_stream), "xp_wait_flags")
+        torch.cuda.synchronize()
+        assert time.monotonic() - t0 < 0.5 and int(status[0]) == 5
+        status.zero_()
+        kinds = [k for k, _, _, _ in trace.read()[0]]
+        assert kinds == [18, 21]                              # wait_begin, wait_cancelled
+        trace.close()
+        # the generation is failed: a valid invocation published afterwards is not served
+        _publish(F, st, place, x, 0, 2)
+        ffn.launch_once(0, lease_ms=5)
+        torch.cuda.synchronize()
+        assert ffn.stats()["served"] == [1]
+        names = [e["name"] for e in devkit.FabricObserver(ffn).collect().events]
+        assert names[:4] == ["discovered", "rejected", "failure_claimed", "admitted"] and "failure_observed" in names
     finally:
         ffn.close()
