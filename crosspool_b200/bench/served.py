@@ -32,6 +32,7 @@ import heapq
 import json
 import os
 import statistics
+import sys
 import threading
 import time
 from dataclasses import dataclass, field
@@ -730,9 +731,22 @@ def _kv_bytes_per_token(cfg) -> int:
     return 2 * cfg.num_layers * cfg.num_kv_heads * cfg.head_dim * 2
 
 
+def _exit_watchdog(seconds: float, code: int = 0) -> None:
+    """Ends the process if teardown has not finished after ``seconds`` (the result line is already printed): a
+    library communicator that does not come down must not keep a GPU box busy."""
+    def fire():
+        sys.stdout.flush()
+        os._exit(code)
+
+    t = threading.Timer(seconds, fire)
+    t.daemon = True
+    t.start()
+
+
 def _shutdown(ctx, ctl, pools) -> None:
     import torch.distributed as dist
 
+    _exit_watchdog(45.0)
     dist.barrier(group=ctl)
     for port in getattr(ctx, "ports", []):      # baseline arm: a zero-row header ends each FFN service thread
         port.shutdown()
@@ -742,4 +756,8 @@ def _shutdown(ctx, ctl, pools) -> None:
         ctx.ffn.stop()
         ctx.ffn.close()
     dist.barrier(group=ctl)
+    if getattr(ctx, "ports", None) is not None:
+        # baseline arm: its NCCL communicators were captured into CUDA graphs; leave them to process exit
+        sys.stdout.flush()
+        os._exit(0)
     dist.destroy_process_group()

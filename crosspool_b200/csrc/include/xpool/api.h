@@ -116,6 +116,27 @@ typedef struct XpSignalArgs {
   int reserved;
 } XpSignalArgs;
 
+/* Transport of one Instance rank of an external serving engine (see kernels/instance.cu). */
+typedef struct XpInstanceBinding {
+  void* peer_inputs[8];      /* FFN ranks: [capacity_rows, hidden] bf16 input buffers of the Instance's slots */
+  void* peer_records[8];     /* FFN ranks: InvocationRecord of the slot */
+  void* peer_flags[8];       /* FFN ranks: the record's sequence word */
+  void* peer_failures[8];    /* FFN ranks: failure slot of the Instance's slot */
+  const void* parts[8];      /* local: partial outputs of the FFN TP ranks, [capacity_rows, hidden] bf16 each */
+  const void* done_flags[8]; /* local: completion sequence words, one per FFN TP rank */
+  void* failure;             /* local failure slot (its claim word cancels the wait) */
+  void* status;              /* device status word (4 timed out, 5 cancelled) */
+  uint64_t wait_ns;          /* completion wait limit; 0: 5 s */
+  int n_peers, n_parts, hidden, capacity_rows;
+  uint32_t origin_pe, reserved;
+} XpInstanceBinding;
+int xp_instance_create(const XpInstanceBinding* b);
+int xp_instance_set_current(int handle);
+int xp_instance_current(void);
+int xp_instance_submit(int handle, const void* hidden, int rows, int ld, void* out, int ld_out, int layer, int mode,
+                       int requirement, int dp_layout, void* stream);
+void xp_instance_destroy(int handle);
+
 /* FFN device Lane runtime (see xpool/lane.cuh). */
 typedef struct XpLaneInstanceDesc {
   void* input;             /* local [capacity_rows, hidden] bf16 payload buffer */

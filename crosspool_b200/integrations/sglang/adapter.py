@@ -24,11 +24,41 @@ def filter_decoder_ffn_weights(weights: Iterable[tuple[str, Any]]) -> Iterator[t
             yield name, tensor
 
 
+_filter_depth = 0
+
+
+class weight_filter_scope:
+    """While active, every ``load_weights`` hook drops decoder-FFN tensors (the lifecycle hook opens it around the
+    engine's ``load_model``; outside it the engine's own loaders are untouched)."""
+
+    def __enter__(self):
+        global _filter_depth
+        _filter_depth += 1
+        return self
+
+    def __exit__(self, *exc):
+        global _filter_depth
+        _filter_depth -= 1
+        return False
+
+
+def filtering_active() -> bool:
+    return _filter_depth > 0
+
+
+def layer_ordinal_from_prefix(prefix: str, default: int = -1) -> int:
+    """``model.layers.17.mlp`` -> 17 (engine modules are constructed with their parameter prefix)."""
+    m = re.search(r"layers\.(\d+)", prefix or "")
+    return int(m.group(1)) if m else default
+
+
 @dataclass(frozen=True)
 class Hook:
     target: str          # dotted path of the engine symbol
     handler: Any
     kind: str            # "replace" | "around" | "after"
+    required: bool = True   # install fails when a required hook cannot be applied; the hooks of architecture adapters
+                            # are optional there (an engine build need not ship every model) and checked at load time
 
 
 @dataclass(frozen=True)
@@ -59,6 +89,9 @@ class ShimAdapter(ABC):
 
     @abstractmethod
     def hooks(self) -> list[Hook]: ...
+
+    def validate_after_load(self, model: Any, expected_layers: int) -> list[Any]:
+        raise NotImplementedError
 
     def validate_before_load(self, model_runner: Any, binding: InstanceRankBinding) -> None:
         if binding.dp_size > 1 and not self.supports_dp_attention:
@@ -93,42 +126,95 @@ class ShimAdapter(ABC):
             raise RuntimeError(f"attention side still holds FFN parameters, e.g. {left[:3]}")
 
 
-class _Dense(ShimAdapter):
+class _ModuleAdapter(ShimAdapter):
+    """An architecture described by where its classes live in the engine: the module, the model class whose
+    ``load_weights`` is filtered, and the MLP / MoE-block classes that become shims. ``hooks()`` replaces each of those
+    classes with a factory that builds an :class:`FfnShimModule` for the layer named by the ``prefix`` the engine passes,
+    and wraps ``load_weights`` so that decoder-FFN tensors are never read on the attention side
+    (reference: src/xpool/integrations/sglang/models/qwen2.py:28-137, qwen3_moe.py:24-109)."""
+
+    module: str = ""
+    model_class: str = ""
+    mlp_classes: tuple[str, ...] = ()
+    dense_prefix_layers: int = 0       # DeepSeek-style: this many leading layers are dense, the rest MoE blocks
+
+    def shim_factory(self, class_name: str):
+        from .shim import FfnShimModule
+
+        def make(*args, prefix: str = "", layer_id: int | None = None, **kw):
+            ordinal = layer_id if layer_id is not None else layer_ordinal_from_prefix(prefix)
+            if ordinal < 0:
+                raise ValueError(f"{class_name}: cannot tell the layer ordinal from prefix {prefix!r}")
+            return FfnShimModule(ordinal)
+
+        make.__name__ = f"{class_name}Shim"
+        return make
+
+    @staticmethod
+    def load_weights_around(original, model, weights, *a, **kw):
+        if filtering_active():
+            weights = filter_decoder_ffn_weights(weights)
+        return original(model, weights, *a, **kw)
+
     def hooks(self) -> list[Hook]:
-        return []
+        base = f"sglang.srt.models.{self.module}."
+        out = [Hook(base + c, self.shim_factory(c), "replace", required=False) for c in self.mlp_classes]
+        out.append(Hook(base + self.model_class + ".load_weights", self.load_weights_around, "around", required=False))
+        return out
+
+    def validate_after_load(self, model: Any, expected_layers: int) -> list[Any]:
+        from .shim import FfnShimModule
+
+        shims = self.require_ffn_shims(model, expected_layers, FfnShimModule)
+        self.require_no_ffn_parameters(model)
+        for i, sh in enumerate(shims):
+            if sh.layer_ordinal != i:
+                raise RuntimeError(f"decoder layer {i} carries the shim of layer {sh.layer_ordinal}")
+        return shims
 
 
-class Qwen2Adapter(_Dense):
+class Qwen2Adapter(_ModuleAdapter):
     name, architectures = "qwen2", ("Qwen2ForCausalLM",)
+    module, model_class, mlp_classes = "qwen2", "Qwen2ForCausalLM", ("Qwen2MLP",)
 
 
-class Qwen3Adapter(_Dense):
+class Qwen3Adapter(_ModuleAdapter):
     name, architectures = "qwen3", ("Qwen3ForCausalLM",)
+    module, model_class, mlp_classes = "qwen3", "Qwen3ForCausalLM", ("Qwen3MLP",)
 
 
-class LlamaAdapter(_Dense):
+class LlamaAdapter(_ModuleAdapter):
     name, architectures = "llama", ("LlamaForCausalLM", "MistralForCausalLM")
+    module, model_class, mlp_classes = "llama", "LlamaForCausalLM", ("LlamaMLP",)
 
 
-class OptAdapter(_Dense):
+class OptAdapter(_ModuleAdapter):
+    """OPT keeps ``fc1`` / ``fc2`` directly on the decoder layer; the engine-side layer class is replaced by one whose
+    two projections and activation are a single ``ffn`` shim."""
+
     name, architectures = "opt", ("OPTForCausalLM",)
+    module, model_class, mlp_classes = "opt", "OPTForCausalLM", ("OPTDecoderMLP",)
     mlp_attribute = "ffn"
 
 
-class Qwen3MoeAdapter(_Dense):
+class Qwen3MoeAdapter(_ModuleAdapter):
     name, architectures, supports_dp_attention = "qwen3_moe", ("Qwen3MoeForCausalLM",), True
+    module, model_class, mlp_classes = "qwen3_moe", "Qwen3MoeForCausalLM", ("Qwen3MoeSparseMoeBlock", "Qwen3MoeMLP")
 
 
-class DeepseekV2Adapter(_Dense):
+class DeepseekV2Adapter(_ModuleAdapter):
     name, architectures = "deepseek_v2", ("DeepseekV2ForCausalLM",)
+    module, model_class, mlp_classes = "deepseek_v2", "DeepseekV2ForCausalLM", ("DeepseekV2MoE", "DeepseekV2MLP")
 
 
-class Glm4MoeLiteAdapter(_Dense):
+class Glm4MoeLiteAdapter(_ModuleAdapter):
     name, architectures = "glm4_moe_lite", ("Glm4MoeLiteForCausalLM",)
+    module, model_class, mlp_classes = "glm4_moe_lite", "Glm4MoeLiteForCausalLM", ("Glm4MoeLiteSparseMoeBlock", "Glm4MoeLiteMLP")
 
 
-class GptOssAdapter(_Dense):
+class GptOssAdapter(_ModuleAdapter):
     name, architectures = "gpt_oss", ("GptOssForCausalLM",)
+    module, model_class, mlp_classes = "gpt_oss", "GptOssForCausalLM", ("GptOssSparseMoeBlock",)
 
 
 ADAPTERS: tuple[ShimAdapter, ...] = (Qwen2Adapter(), Qwen3Adapter(), LlamaAdapter(), OptAdapter(), Qwen3MoeAdapter(),

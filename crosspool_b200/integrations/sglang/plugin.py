@@ -22,24 +22,18 @@ ENGINE_ENV = {
 _applied: list[Hook] = []
 
 
-def lifecycle_hooks() -> list[Hook]:
-    """Engine lifecycle seams the Instance runtime attaches to."""
-    names = [("sglang.srt.managers.scheduler.Scheduler.__init__", "around"),
-             ("sglang.srt.managers.scheduler.Scheduler.run_event_loop", "around"),
-             ("sglang.srt.model_executor.model_runner.ModelRunner.load_model", "around"),
-             ("sglang.srt.model_executor.model_runner.ModelRunner.alloc_memory_pool", "after"),
-             ("sglang.srt.managers.scheduler.Scheduler.get_init_info", "after"),
-             ("sglang.srt.managers.scheduler.Scheduler.release_host_resources", "around")]
-    return [Hook(t, _passthrough, k) for t, k in names]
+def install(registry: Any = None, check_config: Callable[[], None] | None = None, environ=os.environ, *, config: Any = None,
+            runtime_factory: Callable | None = None, context_state_factory: Callable | None = None,
+            hf_config_of: Callable | None = None) -> list[Hook]:
+    """Registers every hook of the integration with the engine's hook registry and returns them.
 
+    ``registry`` must offer ``register(target, handler, kind)``; without one the engine's own registry is imported.
+    ``config`` is the resolved deployment configuration and ``runtime_factory(binding, rank, profile, device)`` builds the
+    worker's :class:`~crosspool_b200.runtime.instance.InstanceRankRuntime` (default: one that talks to the configured
+    daemon and binds the native transport); ``context_state_factory`` turns elastic KV on."""
+    from .ecs_hooks import ElasticHooks
+    from .lifecycle import LifecycleHooks
 
-def _passthrough(original: Callable | None = None, *a, **kw):
-    return original(*a, **kw) if callable(original) else None
-
-
-def install(registry: Any = None, check_config: Callable[[], None] | None = None, environ=os.environ) -> list[Hook]:
-    """``registry`` must offer ``register(target, handler, kind)``; without one the engine's own
-    registry is imported. Returns the hooks that were applied."""
     for k, v in ENGINE_ENV.items():
         environ.setdefault(k, v)
     if check_config is not None:
@@ -51,21 +45,57 @@ def install(registry: Any = None, check_config: Callable[[], None] | None = None
             registry = HookRegistry
         except Exception as e:
             raise RuntimeError("no serving engine hook registry available; pass one explicitly") from e
-    hooks = lifecycle_hooks()
+    if config is None:
+        try:
+            from ...config import init_global_config
+
+            config = init_global_config()
+        except Exception:          # no deployment configuration in this process: hooks still register, binding fails later
+            import types
+
+            config = types.SimpleNamespace(models=())
+    life = LifecycleHooks(config, runtime_factory or default_runtime_factory(config), context_state_factory, hf_config_of)
+    hooks = life.hooks()
     for a in ADAPTERS:
         hooks.extend(a.hooks())
+    if context_state_factory is not None:
+        hooks.extend(ElasticHooks(lambda: life.scope.context_state).hooks())
     _applied.clear()
     for h in hooks:
         registry.register(h.target, h.handler, h.kind)
         _applied.append(h)
     verify_required_hooks_applied(registry, hooks)
+    install.lifecycle = life
     return list(_applied)
+
+
+def default_runtime_factory(config: Any) -> Callable:
+    """Instance runtimes that reach the daemon named in ``config`` and bind the native transport from the handles
+    the daemon brokers (the attention-side arena through the lease, the FFN slots through the plan)."""
+    def make(binding, rank, profile, device):
+        from ...runtime.backends import _placement
+        from ...runtime.instance import InstanceRankRuntime
+        from ...service.client import XpoolClient
+        from .transport import FabricInstanceTransport
+
+        client = XpoolClient(getattr(config, "daemon_host", "127.0.0.1"), getattr(config, "daemon_port", 9810))
+
+        def attach(arena, plan):
+            place = _placement(config, plan, binding.model_id, rank, max(profile.max_prefill_rows, profile.max_decode_rows))
+            ffn = [plan.slot_handles[f"ffn:{binding.model_id}:{rank}:{pe}"] for pe in place.ffn_ranks]
+            tr = FabricInstanceTransport.from_handles(place, arena.handle_hex, ffn, f"cuda:{device}")
+            tr.make_current()
+            return tr
+
+        return InstanceRankRuntime(client, binding.model_id, rank, device, profile, attach=attach)
+
+    return make
 
 
 def verify_required_hooks_applied(registry: Any, hooks: list[Hook]) -> None:
     applied = getattr(registry, "applied_targets", None)
     if applied is None:
         return
-    missing = [h.target for h in hooks if h.target not in applied()]
+    missing = [h.target for h in hooks if h.required and h.target not in applied()]
     if missing:
         raise RuntimeError(f"required hooks were not applied: {missing[:3]}")

@@ -27,20 +27,42 @@ def bind_submit(fn: Callable | None) -> None:
     _submit = fn
 
 
-try:
-    _lib = torch.library.Library("xpool", "FRAGMENT")
-    _lib.define("ffn_shim(Tensor hidden_states, Tensor? dp_rank_payload_rows, Tensor(a!) output, int layer_ordinal, "
-                "int forward_mode, int output_requirement, int dp_row_layout) -> ()")
+def _ffn_shim_host(hidden_states, dp_rank_payload_rows, output, layer_ordinal, forward_mode, output_requirement, dp_row_layout):
+    if _submit is None:
+        raise RuntimeError("xpool::ffn_shim called before an Instance runtime was bound")
+    _submit(hidden_states, dp_rank_payload_rows, output, layer_ordinal, forward_mode, output_requirement, dp_row_layout)
 
-    def _ffn_shim_impl(hidden_states, dp_rank_payload_rows, output, layer_ordinal, forward_mode, output_requirement,
-                       dp_row_layout):
-        if _submit is None:
-            raise RuntimeError("xpool::ffn_shim called before an Instance runtime was bound")
-        _submit(hidden_states, dp_rank_payload_rows, output, layer_ordinal, forward_mode, output_requirement, dp_row_layout)
 
-    _lib.impl("ffn_shim", _ffn_shim_impl, "CompositeExplicitAutograd")
-except Exception:  # pragma: no cover - already defined in this process
-    pass
+def _register_op() -> str:
+    """Makes ``torch.ops.xpool.ffn_shim`` available. The native library (``csrc/bindings/torch_ops.cpp``) defines the
+    schema and the CUDA implementation, which submits to the Instance transport on the current stream; Python adds
+    the CPU key, which calls the function installed with :func:`bind_submit` (engine-less tests). Without the native
+    library the whole operator is defined here and every device goes through ``bind_submit``."""
+    from pathlib import Path
+
+    native_lib = Path(__file__).resolve().parents[2] / "native" / "libxpool_torch_ops.so"
+    try:
+        if native_lib.exists():
+            torch.ops.load_library(str(native_lib))
+            lib = torch.library.Library("xpool", "IMPL")
+            lib.impl("ffn_shim", _ffn_shim_host, "CPU")
+            _keep.append(lib)
+            return "native"
+    except Exception:  # pragma: no cover - fall through to the Python definition
+        pass
+    try:
+        lib = torch.library.Library("xpool", "FRAGMENT")
+        lib.define("ffn_shim(Tensor hidden_states, Tensor? dp_rank_payload_rows, Tensor(a!) output, int layer_ordinal, "
+                   "int forward_mode, int output_requirement, int dp_row_layout) -> ()")
+        lib.impl("ffn_shim", _ffn_shim_host, "CompositeExplicitAutograd")
+        _keep.append(lib)
+        return "python"
+    except Exception:  # pragma: no cover - already defined in this process
+        return "existing"
+
+
+_keep: list = []
+OP_BACKEND = _register_op()
 
 
 @dataclass(frozen=True)

@@ -126,8 +126,36 @@ def build_runtime(force: bool = False) -> Path:
     return out
 
 
+def build_torch_ops(force: bool = False) -> Path:
+    """``libxpool_torch_ops.so``: the ``xpool::ffn_shim`` operator (``csrc/bindings/torch_ops.cpp``) compiled against
+    this interpreter's PyTorch headers and linked to ``libxpool_kernels.so`` beside it."""
+    from torch.utils import cpp_extension as ce
+
+    OBJ.mkdir(exist_ok=True)
+    out = HERE / "libxpool_torch_ops.so"
+    src = CSRC / "bindings" / "torch_ops.cpp"
+    import torch
+
+    stamp = _headers_digest() + torch.__version__
+    obj = OBJ / "torch_ops.o"
+    if force or _needs(obj, src, stamp) or not out.exists():
+        cxx = shutil.which("g++") or "g++"
+        inc = [f"-I{p}" for p in ce.include_paths("cuda")]
+        cuda_inc = Path(_nvcc()).resolve().parent.parent / "include"
+        abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+        _run([cxx, "-O2", "-std=c++17", "-fPIC", "-Wall", f"-D_GLIBCXX_USE_CXX11_ABI={abi}", f"-I{CSRC / 'include'}", f"-I{cuda_inc}",
+              *inc, "-c", str(src), "-o", str(obj)])
+        libdir = Path(torch.__file__).resolve().parent / "lib"
+        _run([cxx, "-shared", "-o", str(out), str(obj), f"-L{HERE}", "-lxpool_kernels", f"-L{libdir}", "-ltorch", "-ltorch_cpu",
+              "-lc10", "-ltorch_cuda", "-lc10_cuda", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{libdir}"])
+        _mark(obj, src, stamp)
+    return out
+
+
 def build_all(force: bool = False, verbose: bool = False) -> dict[str, Path]:
-    return {"runtime": build_runtime(force), "kernels": build_kernels(force, verbose)}
+    out = {"runtime": build_runtime(force), "kernels": build_kernels(force, verbose)}
+    out["torch_ops"] = build_torch_ops(force)
+    return out
 
 
 if __name__ == "__main__":

@@ -154,7 +154,7 @@ class NcclFfnRank:
     def stop(self) -> None:
         for sv in self.served:
             if sv.thread is not None:
-                sv.thread.join(90)
+                sv.thread.join(20)
 
     def close(self) -> None:
         self.served.clear()

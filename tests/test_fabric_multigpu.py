@@ -45,3 +45,25 @@ def test_attention_tp_pair_with_a_remote_ffn_rank():
 
 def test_layer_split_placement_over_two_ffn_ranks():
     _run(3, ["--tp", "1", "--layer-split", "2"])
+
+
+def test_a_failure_on_the_ffn_rank_cancels_the_attention_ranks_wait_in_the_same_call():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29547", str(ROOT / "tests/multigpu/failure_check.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "FAILURE_CHECK_OK" in r.stdout
+
+
+def test_native_ffn_shim_operator_reaches_the_ffn_tier_eagerly_and_from_a_graph():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29549", str(ROOT / "tests/multigpu/shim_check.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "SHIM_CHECK_OK" in r.stdout
