@@ -14,6 +14,7 @@
 #include <stdint.h>
 
 #include <atomic>
+#include <thread>
 
 namespace xpool {
 namespace ecs {
@@ -105,10 +106,13 @@ inline void seq_publish(SeqRecord<T>* r, const T& v) {
   r->revision.store(rev + 2, std::memory_order_seq_cst);
 }
 
-// Returns false if no stable snapshot could be taken within `attempts`.
+// Returns false if no stable snapshot could be taken within `attempts`. A reader that keeps colliding with the
+// writer gives its time slice away every 64 tries, so a writer that was descheduled in the middle of a publication
+// (odd revision) gets to finish it even on a loaded host.
 template <typename T>
-inline bool seq_read(const SeqRecord<T>* r, T* out, uint64_t* revision, int attempts = 1000) {
+inline bool seq_read(const SeqRecord<T>* r, T* out, uint64_t* revision, int attempts = 20000) {
   for (int i = 0; i < attempts; ++i) {
+    if ((i & 63) == 63) std::this_thread::yield();
     uint64_t a = r->revision.load(std::memory_order_seq_cst);
     if (a & 1) continue;
     T v;
