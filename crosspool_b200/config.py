@@ -75,6 +75,19 @@ def _choice(*allowed: str) -> Callable[[Any], str]:
     return parse
 
 
+def _int_choice(*allowed: int) -> Callable[[Any], int]:
+    def parse(v: Any) -> int:
+        try:
+            n = int(v)
+        except (TypeError, ValueError):
+            raise ConfigError(f"{v!r} is not an integer") from None
+        if n not in allowed:
+            raise ConfigError(f"{v!r} not one of {allowed}")
+        return n
+
+    return parse
+
+
 def _devices(v: Any) -> tuple[int, ...]:
     if isinstance(v, str):
         v = [p for p in v.replace(",", " ").split() if p]
@@ -179,6 +192,23 @@ CONFIG_REGISTRY: tuple[ConfigSetting, ...] = (
                   cli="--ffn-policy"),
     ConfigSetting("scheduler_ffn_random_seed", ("scheduler", "ffn_random_seed"), _int(0), 0),
     ConfigSetting("scheduler_slo", ("scheduler", "slo"), _slo, required=True),
+    # engine sizing of the attention ranks this repository hosts itself (covered by the configuration digest: every
+    # process of a deployment must agree on the row capacities the slots are sized for)
+    ConfigSetting("engine_max_rows", ("engine", "max_rows"), _int(1, 1 << 20), 4096, env_var="XPOOL_MAX_ROWS",
+                  description="row capacity of an FFN invocation (prefill chunk and decode batch fit in it)"),
+    ConfigSetting("engine_max_batch", ("engine", "max_batch"), _int(1, 1 << 16), 256, env_var="XPOOL_MAX_BATCH",
+                  description="running requests per Instance"),
+    ConfigSetting("engine_prefill_chunk", ("engine", "prefill_chunk"), _int(16, 1 << 20), 4096, env_var="XPOOL_PREFILL_CHUNK",
+                  description="tokens per prefill step"),
+    ConfigSetting("engine_max_seq_len", ("engine", "max_seq_len"), _int(16, 1 << 22), 4096, env_var="XPOOL_MAX_SEQ_LEN",
+                  description="longest prompt plus output of a request"),
+    ConfigSetting("engine_page_size", ("engine", "page_size"), _int_choice(16, 32, 64, 128), 16, env_var="XPOOL_PAGE_SIZE",
+                  description="tokens per KV page"),
+    ConfigSetting("serving_base_port", ("serving", "base_port"), _int(1, 65535), 30000, env_var="XPOOL_SERVING_BASE_PORT",
+                  description="HTTP port of the first attention device's Instances; device i listens on base + i"),
+    ConfigSetting("serving_tp_rendezvous_base_port", ("serving", "tp_rendezvous_base_port"), _int(1, 65535), 30500,
+                  env_var="XPOOL_TP_RENDEZVOUS_BASE_PORT",
+                  description="loopback port at which the ranks of an attention TP group meet (+ first rank of the group)"),
 )
 
 _BY_NAME = {s.name: s for s in CONFIG_REGISTRY}

@@ -21,7 +21,6 @@ from ..native import runtime as rt
 from ..parallel import fabric as F
 from ..service.wire import FabricPlan, InvocationFailure, ServingListener
 
-TP_RENDEZVOUS_BASE_PORT = 30500   # + Instance rank of the TP group's first member
 _POLICY = {"fifo": rt.POLICY_FIFO, "random": rt.POLICY_RANDOM, "slo": rt.POLICY_SLO}
 
 
@@ -274,7 +273,7 @@ class AtnBackend:
             import os
 
             os.environ.setdefault("GLOO_SOCKET_IFNAME", "lo")
-            dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{TP_RENDEZVOUS_BASE_PORT + first}",
+            dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{self.cfg.serving_tp_rendezvous_base_port + first}",
                                     rank=tpr, world_size=tps)
             from ..ecs.reconciler import gloo_agreement
 

@@ -9,7 +9,6 @@ from ..logging import get_logger, init_logging, kv
 from ..service.client import XpoolClient
 from ..service.wire import InstanceFfnProfile, Role
 
-SERVING_BASE_PORT = 30000
 
 
 def hosted_instances(cfg: XpoolConfig, device: int) -> list[tuple[str, int]]:
@@ -40,17 +39,17 @@ def run_agent(cfg: XpoolConfig, role: str, device: int) -> int:
     visible = os.environ.get("CUDA_VISIBLE_DEVICES")
     local = [int(x) for x in visible.split(",")].index(device) if visible else device
     torch.cuda.set_device(local)
-    max_rows = int(os.environ.get("XPOOL_MAX_ROWS", "4096"))
+    max_rows = cfg.engine_max_rows
     if role == "ffnagent":
         free, total = torch.cuda.mem_get_info(local)
         agent = FfnAgent(client, device, FfnBackend(cfg, device, capacity_rows=max_rows, local_index=local), free, total,
                          owner=owner)
     else:
         insts = hosted_instances(cfg, device)
-        chunk = min(max_rows, int(os.environ.get("XPOOL_PREFILL_CHUNK", "4096")))   # tokens per prefill step
-        ecfg = EngineConfig(max_batch=int(os.environ.get("XPOOL_MAX_BATCH", "256")), prefill_chunk=chunk,
-                            max_seq_len=int(os.environ.get("XPOOL_MAX_SEQ_LEN", "4096")))
-        port = SERVING_BASE_PORT + cfg.atn_devices.index(device)
+        chunk = min(max_rows, cfg.engine_prefill_chunk)   # tokens per prefill step
+        ecfg = EngineConfig(max_batch=cfg.engine_max_batch, prefill_chunk=chunk, max_seq_len=cfg.engine_max_seq_len,
+                            page_size=cfg.engine_page_size)
+        port = cfg.serving_base_port + cfg.atn_devices.index(device)
         backend = AtnBackend(cfg, device, insts, ecfg, capacity_rows=max_rows, local_index=local, listen=("127.0.0.1", port))
         if cfg.atn_elastic_kv:
             backend.ecs_ref = client.ecs_channel

@@ -77,3 +77,16 @@ def test_observer_env_switches():
                              "XPOOL_DEBUG_FABRIC_OBSERVER_RECORD_CAPACITY": "128"}, toml_text=TOML)
     assert cfg.debug_fabric_observer_enable is True and cfg.debug_fabric_observer_record_capacity == 128
     assert cfg.debug_graph_observer_enable is False
+
+
+def test_engine_knobs_and_ports_are_registry_settings_covered_by_the_digest():
+    base = "[atn]\ndevices=[0]\n[ffn]\ndevices=[1]\n[scheduler.slo]\nttft_ms=1000\ntbt_ms=50\n"
+    a = C.load_config(toml_text=base, env={})
+    assert (a.engine_max_rows, a.engine_max_batch, a.engine_prefill_chunk, a.engine_page_size) == (4096, 256, 4096, 16)
+    assert (a.serving_base_port, a.serving_tp_rendezvous_base_port) == (30000, 30500)
+    b = C.load_config(toml_text=base + "[engine]\nmax_batch=64\npage_size=64\n[serving]\nbase_port=31000\n", env={"XPOOL_MAX_ROWS": "512"})
+    assert (b.engine_max_rows, b.engine_max_batch, b.engine_page_size, b.serving_base_port) == (512, 64, 64, 31000)
+    assert b.sources["engine_max_rows"] == "env" and b.sources["engine_max_batch"] == "toml"
+    assert a.digest() != b.digest()      # two processes that disagree on slot sizing fail the config check
+    with pytest.raises(C.ConfigError, match="page_size"):
+        C.load_config(toml_text=base + "[engine]\npage_size=48\n", env={})
