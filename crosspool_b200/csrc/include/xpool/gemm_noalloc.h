@@ -15,12 +15,13 @@
  *
  * Limits and sharp edges:
  *  - The scratch is XP_NOALLOC_WS_BYTES of workspace plus XP_NOALLOC_COUNTER_BYTES
- *    of counters per GPU; every GPU that loads the library holds that memory
+ *    of counters (plus one 256-byte block for a status word) per GPU; every GPU that loads the library holds that memory
  *    until the process exits. A problem whose plan needs more is refused with
  *    XP_NOALLOC_E_TOO_LARGE (see xp_gemm_noalloc_strerror); nothing is launched.
  *  - The first call on a device looks up the device address of the array
  *    (cudaGetSymbolAddress, with that device current). Make that first call
- *    before starting any stream capture.
+ *    before starting any stream capture. Two host threads may make it at the
+ *    same time: both find the same address.
  *  - All calls on a device share the one array, and it keeps the previous
  *    call's contents. The counters are cleared on the caller's stream before
  *    each launch; the workspace needs no clearing (every word read was written
@@ -40,9 +41,12 @@ extern "C" {
 #define XP_NOALLOC_WS_BYTES (8u << 20)
 #define XP_NOALLOC_COUNTER_BYTES (16u << 10)
 
-#define XP_NOALLOC_E_TOO_LARGE (-200)   /* plan needs more scratch than the fixed array holds */
-#define XP_NOALLOC_E_SYMBOL (-201)      /* the array's device address could not be obtained */
-#define XP_NOALLOC_E_ARGUMENT (-202)    /* null pointer or unsupported shape */
+/* Codes of this entry point sit below -1000: xp_gemm reports a CUDA launch error e as -100 - e, and those must
+ * not be mistaken for these. */
+#define XP_NOALLOC_E_TOO_LARGE (-1000)  /* plan needs more scratch than the fixed array holds */
+#define XP_NOALLOC_E_SYMBOL (-1001)     /* the array's device address could not be obtained */
+#define XP_NOALLOC_E_ARGUMENT (-1002)   /* null pointer or unsupported shape */
+#define XP_NOALLOC_E_CLEAR (-1003)      /* clearing or reading the counters / status word failed */
 
 /* w [n_out, k] and x [rows, k] are dense row-major bf16 device pointers, out is [rows, n_out] bf16.
  * n_out % 128 == 0, k % 64 == 0, splits >= 1 (1 = no split-K, the scratch is then unused).
@@ -51,6 +55,11 @@ int xp_gemm_noalloc(const void* w, const void* x, void* out, int n_out, int k, i
 
 /* Bytes of workspace the given problem would need (0 for splits == 1), or a negative code. */
 long long xp_gemm_noalloc_required_bytes(int n_out, int k, int rows, int splits);
+
+/* The kernel's bounded waits report through a status word that lives in the same fixed array and is cleared with
+ * the counters before every launch: 0 = the last call on this device ran to completion, non-zero = one of its
+ * pipeline waits gave up (the output is then not valid). Synchronises `stream`. Returns 0 or a code above. */
+int xp_gemm_noalloc_status(unsigned int* out, void* stream);
 
 const char* xp_gemm_noalloc_strerror(int code);
 

@@ -14,7 +14,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-TOO_LARGE = -200
+TOO_LARGE, BAD_ARGUMENT = -1000, -1002
 
 
 def _lib():
@@ -25,6 +25,8 @@ def _lib():
     lib.xp_gemm_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.xp_gemm_noalloc_required_bytes.restype = C.c_longlong
     lib.xp_gemm_noalloc_required_bytes.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int]
+    lib.xp_gemm_noalloc_status.restype = C.c_int
+    lib.xp_gemm_noalloc_status.argtypes = [C.POINTER(C.c_uint), C.c_void_p]
     lib.xp_gemm_noalloc_strerror.restype = C.c_char_p
     lib.xp_gemm_noalloc_strerror.argtypes = [C.c_int]
     return lib
@@ -45,7 +47,9 @@ def test_matches_the_allocating_entry_point_twice_in_a_row(rows, n, k, splits):
         rc = lib.xp_gemm_noalloc(w.data_ptr(), x.data_ptr(), got.data_ptr(), n, k, rows, splits, stream)
         assert rc == 0, lib.xp_gemm_noalloc_strerror(rc)
         torch.cuda.synchronize()
-        gemm.check_status(x.device)
+        gemm.check_status(x.device)                      # the allocating call's status word
+        st = C.c_uint(99)
+        assert lib.xp_gemm_noalloc_status(C.byref(st), stream) == 0 and st.value == 0   # and this entry point's own
         torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
         ref = x.float() @ w.float().t()
         torch.testing.assert_close(got.float(), ref, atol=2e-2, rtol=2e-2)
@@ -64,4 +68,4 @@ def test_refuses_problems_beyond_the_fixed_scratch_without_launching():
     assert b"scratch" in lib.xp_gemm_noalloc_strerror(rc)
     torch.cuda.synchronize()
     assert bool((out == 7.0).all())  # nothing ran
-    assert lib.xp_gemm_noalloc(None, x.data_ptr(), out.data_ptr(), n, k, rows, 1, None) == -202
+    assert lib.xp_gemm_noalloc(None, x.data_ptr(), out.data_ptr(), n, k, rows, 1, None) == BAD_ARGUMENT
