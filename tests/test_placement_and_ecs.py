@@ -3,7 +3,8 @@ channel, fake clock)."""
 import pytest
 
 from crosspool_b200.service.daemon.ecs import CapacityPolicy, Partition
-from crosspool_b200.service.daemon.placement import (DeviceSupply, ModelDemand, PlacementError, place_ffn_models,
+from crosspool_b200.service.daemon.placement import (DeviceSupply, ModelDemand, PlacementError, StageOverheads,
+                                                     decompose_into_tp_groups, place_ffn_models,
                                                      stage_bytes)
 
 GB = 1 << 30
@@ -147,3 +148,57 @@ def test_command_is_rejected_when_the_demand_witness_changed():
     ch.read_demand = flaky
     ev = pol.tick()
     assert ev.kind == "reject" and parts[0].target_bytes == 60
+
+
+def test_reference_objective_order_packs_equal_signatures_and_reuses_tp_groups():
+    devs = [DeviceSupply(d, 100 * GB) for d in (2, 3, 4, 5)]
+    models = [_model("a", 10, 2.0, 2), _model("b", 10, 2.0, 2)]
+    ref = place_ffn_models(models, devs, ws_per_lane=1 << 20, objectives="reference")
+    # same Signature: both models on one TP group -> 2 signature materialisations instead of 4, one group reused
+    assert ref.signature_materializations == 2 and ref.group_reuse == 1 and ref.objectives[0] == 2
+    assert {g.devices for g in ref.groups} == {(2, 3)}
+    bal = place_ffn_models(models, devs, ws_per_lane=1 << 20)
+    assert bal.signature_materializations == 4 and bal.group_reuse == 0 and min(bal.headroom.values()) > min(ref.headroom.values())
+
+
+def test_layer_classes_group_layers_by_signature_and_bytes():
+    m = ModelDemand("ds", tuple([int(1 * GB)] * 2 + [int(3 * GB)] * 6), 2, 2048, 256, max_intermediate=8192,
+                    layer_kinds=("dense",) * 2 + ("moe",) * 6, experts=64, top_k=6)
+    cls = m.layer_classes()
+    assert [(c.signature.kind, len(c.layers)) for c in cls] == [("dense", 2), ("moe", 6)]
+    assert cls[1].signature.experts == 64 and cls[0].signature.experts == 0 and cls[0].signature.local_width == 4096
+    r = place_ffn_models([m], [DeviceSupply(d, 100 * GB) for d in (0, 1)], ws_per_lane=1 << 20)
+    assert r.signature_materializations == 4          # two Signatures on each of the two TP ranks' devices
+
+
+def test_calibrated_stage_overheads_enter_admission():
+    devs = [DeviceSupply(0, 24 * GB)]
+    m = [_model("a", 10, 2.0, 1)]
+    ok = place_ffn_models(m, devs, ws_per_lane=1 << 20)
+    assert ok.headroom[0] > 3 * GB
+    over = StageOverheads(base_bytes=0.6 * GB, per_storage_mib=0.05 * (1 << 20), per_lane=8e6, per_dense_signature=64e6, joined_bytes=0.5 * GB)
+    tight = place_ffn_models(m, devs, ws_per_lane=1 << 20, overheads=over)
+    assert tight.stages[0].fabric_join - ok.stages[0].fabric_join >= int(0.6 * GB + 1.0 * GB + 0.5 * GB)   # base + 5 % of 20 GiB + joined
+    assert tight.stages[0].weight_materialization - ok.stages[0].weight_materialization < tight.stages[0].fabric_join - ok.stages[0].fabric_join
+    with pytest.raises(PlacementError):
+        place_ffn_models(m, [DeviceSupply(0, 22 * GB)], ws_per_lane=1 << 20, overheads=over)
+
+
+def test_rank_counts_decompose_into_tp_groups_of_distinct_devices():
+    # rank 0 shards: 6 layers on device 0, 4 on device 1; rank 1 shards: 4 on device 1 ... no wait: a device may not
+    # hold both ranks of a layer, so the 4 layers whose rank 0 is on device 1 need rank 1 elsewhere
+    counts = [{0: 6, 1: 4}, {1: 6, 2: 4}]
+    groups = decompose_into_tp_groups(counts)
+    assert groups == [((0, 1), 6), ((1, 2), 4)]
+    assert all(len(set(g)) == len(g) for g, _ in groups) and sum(n for _, n in groups) == 10
+    # the lexicographically first group must leave the rest decomposable: (0, 1) can only take 2 layers here
+    counts = [{0: 5, 1: 5}, {0: 3, 1: 2, 2: 5}]
+    groups = decompose_into_tp_groups(counts)
+    assert sum(n for _, n in groups) == 10 and all(g[0] != g[1] for g, _ in groups)
+    back = [{}, {}]
+    for g, n in groups:
+        for r in (0, 1):
+            back[r][g[r]] = back[r].get(g[r], 0) + n
+    assert back == counts
+    with pytest.raises(PlacementError, match="distinct devices"):
+        decompose_into_tp_groups([{0: 4}, {0: 4}])
