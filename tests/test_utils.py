@@ -117,3 +117,45 @@ def test_bootstrap_initialises_once_per_process():
     with pytest.raises(ValueError):
         bootstrap.reset_for_tests() or bootstrap.init("Nobody")
     bootstrap.reset_for_tests()
+
+
+def test_owned_mps_scope_against_a_stand_in_control_binary(tmp_path):
+    """The MPS control protocol without an MPS daemon: a stand-in for the control binary keeps server / client lists in
+    memory and logs every invocation, so start-up, client termination with confirmation and shutdown are checked
+    without touching how any GPU is shared."""
+    import types
+
+    log, state = [], {"servers": {4242: [111, 222]}, "sticky": set()}
+
+    def fake_run(argv, input=None, env=None, **kw):
+        assert env["CUDA_MPS_PIPE_DIRECTORY"].endswith("/pipe") and env["CUDA_VISIBLE_DEVICES"] == "GPU-abc"
+        cmd = "-d" if "-d" in argv else (input or "").strip()
+        log.append(cmd)
+        out = ""
+        if cmd == "get_server_list":
+            out = "\n".join(str(s) for s in state["servers"])
+        elif cmd.startswith("get_client_list"):
+            out = "\n".join(str(c) for c in state["servers"].get(int(cmd.split()[1]), []))
+        elif cmd.startswith("terminate_client"):
+            _, s, c = cmd.split()
+            if int(c) not in state["sticky"]:
+                state["servers"][int(s)].remove(int(c))
+        return types.SimpleNamespace(returncode=0, stdout=out, stderr="")
+
+    ep = mps.MpsEndpoint.for_device("GPU-abc", root=tmp_path)
+    scope = mps.OwnedMpsScope(ep, mps.MpsControl(ep, run=fake_run))
+    scope.start()
+    scope.start()                                   # idempotent
+    assert log == ["-d"] and ep.pipe_dir.is_dir() and ep.log_dir.is_dir()
+    assert scope.clients() == {4242: [111, 222]}
+    assert scope.terminate_client(111) and scope.clients() == {4242: [222]}
+    assert scope.terminate_client(999)              # not a client: nothing to do
+    state["sticky"].add(222)
+    assert not scope.terminate_client(222)          # still listed afterwards: not confirmed, the caller retains
+    scope.stop()
+    assert log[-1] == "quit" and not scope.started
+
+    def failing(argv, **kw):
+        return types.SimpleNamespace(returncode=1, stdout="", stderr="cannot create pipe")
+    with pytest.raises(mps.MpsControlError, match="cannot create pipe"):
+        mps.OwnedMpsScope(ep, mps.MpsControl(ep, run=failing)).start()
