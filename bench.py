@@ -46,7 +46,7 @@ def parse_args(argv=None):
     ap.add_argument("--warmup", type=int, default=5, help="untimed intervals of traffic before the first window")
     ap.add_argument("--impl", default="xpool", choices=["xpool", "baseline", "reference"])
     ap.add_argument("--step-seconds", type=float, default=0.5)
-    ap.add_argument("--mix", default="", choices=["", "b", "c", "e"], help="model mix (default: by GPU count)")
+    ap.add_argument("--mix", default="", choices=["", "b", "c", "d", "e"], help="model mix (default: by GPU count)")
     ap.add_argument("--rate-scale", type=float, default=1.0, help="multiplies every arrival rate of the mix")
     ap.add_argument("--max-batch", type=int, default=0, help="override the running-request limit of every Instance")
     ap.add_argument("--kv-tokens", type=int, default=0, help="override the KV capacity (tokens) of every Instance")

@@ -76,6 +76,7 @@ class ModelStream:
     alt_prompt: LengthSpec | None = None
     alt_output: LengthSpec | None = None
     swap_phase: int = 0                 # 0: starts with the primary shape, 1: starts with the alternate
+    weights_key: str | None = None      # Instances with the same key share one copy of the FFN weights per FFN rank
 
 
 def _uniform(lo, hi):
@@ -131,6 +132,19 @@ def _build_mix(name: str, world: int, scale: float) -> tuple[list[ModelStream], 
                                    alt_rate=32.0 * scale, alt_prompt=short_p, alt_output=short_o, swap_phase=1, **common))
         return out, {"name": "c", "layout": f"atn{n_atn} (8B + 0.6B each, elastic KV) + ffn2 (8B TP2)",
                      "slo": {"ttft_ms": SLO_TTFT_MS, "tpot_ms": SLO_TPOT_MS}}
+    if name == "d":
+        # Qwen3-30B-A3B: attention data-parallel over half of the GPUs (one Instance rank each, requests spread evenly:
+        # every rank has its own Poisson stream of a quarter of the load), experts expert-parallel over the other half
+        # (one copy of the expert weights serves every data-parallel rank). Prompts uniform 512-4096, outputs 256-1024.
+        if world < 2 or world % 2:
+            raise SystemExit("mix d needs an even number of GPUs (half attention DP ranks, half expert-parallel FFN ranks)")
+        n_atn = world // 2
+        ffn = tuple(range(n_atn, world))
+        out = [ModelStream(f"Qwen/Qwen3-30B-A3B#dp{a}", "Qwen/Qwen3-30B-A3B", 40, a, ffn, 6.0 * scale, _uniform(512, 4096),
+                           _uniform(256, 1024), max_batch=256, max_seq_len=4096 + 1024 + PAGE, kv_tokens=768 * 1024,
+                           weights_key="Qwen/Qwen3-30B-A3B") for a in range(n_atn)]
+        return out, {"name": "d", "layout": f"attention DP{n_atn} + experts EP{n_atn} (128 experts, top-8)",
+                     "slo": {"ttft_ms": SLO_TTFT_MS, "tpot_ms": SLO_TPOT_MS}}
     if name == "e":
         # Four models on 8 GPUs: attention on ranks 0-1 (elastic KV per GPU), FFN tier on ranks 2-7:
         # Qwen3-32B TP4 on 2-5, Qwen3-8B TP2 on 6-7, the two Qwen3-1.7B on 6 and 7. Rates 1:2:4:4, 4x bursts.
@@ -147,7 +161,7 @@ def _build_mix(name: str, world: int, scale: float) -> tuple[list[ModelStream], 
         ]
         return out, {"name": "e", "layout": "atn2 (32B + 1.7B | 8B + 1.7B, elastic KV) + ffn6 (32B TP4, 8B TP2, 1.7B x2)",
                      "burst": "4x for a quarter of every window", "slo": {"ttft_ms": SLO_TTFT_MS, "tpot_ms": SLO_TPOT_MS}}
-    raise SystemExit(f"unknown mix {name!r} (b, c, e)")
+    raise SystemExit(f"unknown mix {name!r} (b, c, d, e)")
 
 
 def default_mix(world: int) -> str:
@@ -623,7 +637,7 @@ def run_multi_gpu(args) -> int:
     cfgs = {s.model_id: model_cfg(s, args.layers) for s in streams}
     ecfgs = {s.model_id: engine_config(s) for s in streams}
     placements = [F.InstancePlacement(s.model_id, cfgs[s.model_id], seed=s.seed, atn_rank=s.atn_rank, ffn_ranks=s.ffn_ranks,
-                                      capacity_rows=max(s.max_batch, s.prefill_chunk)) for s in streams]
+                                      capacity_rows=max(s.max_batch, s.prefill_chunk), weights_key=s.weights_key) for s in streams]
     topo = F.Topology(world, placements)
 
     pools: list[ElasticPool] = []

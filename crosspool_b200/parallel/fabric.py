@@ -138,6 +138,9 @@ class InstancePlacement:
     # Directory of a Hugging Face checkpoint (config.json + safetensors) to load the weights from; None: random
     # init from ``seed`` (benchmarks and tests).
     checkpoint: str | None = None
+    # Instances that carry the same key (and seed / checkpoint) are ranks or replicas of one model: an FFN rank keeps
+    # one copy of the FFN shard for all of them. None: private weights.
+    weights_key: str | None = None
 
     def __post_init__(self):
         if self.layer_groups:
@@ -403,6 +406,7 @@ class FfnRankRuntime:
         self.instances: list[FfnInstanceState] = []
         self.handle = None
         self._running = False
+        self._shared_weights: dict = {}
         self.errors: list[str] = []
 
     def add_instance(self, place: InstancePlacement, tp_rank: int, layers: tuple[int, int] | None = None) -> FfnInstanceState:
@@ -412,6 +416,13 @@ class FfnRankRuntime:
         slot = PeerBuffer(lay.total_bytes)
         cfg = place.cfg
         lo, hi = layers or (0, cfg.num_layers)
+        # The attention data-parallel ranks of one model (and replicas that name the same weights) are separate
+        # Instances with their own slots, but they execute the same FFN: one copy of the shard serves them all.
+        share_key = (place.weights_key, cfg.name, place.checkpoint, place.seed, tp_rank, place.tp, lo, hi, place.moe_parallel)
+        if place.weights_key is not None and share_key in self._shared_weights:
+            st = FfnInstanceState(place, tp_rank, slot, self._shared_weights[share_key])
+            self.instances.append(st)
+            return st
         weights = []
         source = CheckpointFfnSource(place.model_id, place.checkpoint) if place.checkpoint else None
         for l in range(cfg.num_layers):
@@ -427,6 +438,8 @@ class FfnRankRuntime:
             else:
                 w = random_ffn_layer(cfg, l, place.seed, self.device, torch.bfloat16, tp_rank, place.tp)
             weights.append(w)
+        if place.weights_key is not None:
+            self._shared_weights[share_key] = weights
         st = FfnInstanceState(place, tp_rank, slot, weights)
         self.instances.append(st)
         return st
