@@ -110,16 +110,16 @@ def main(argv: list[str] | None = None) -> int:
     ap = argparse.ArgumentParser(prog="python -m crosspool_b200.bench.serve_case")
     ap.add_argument("--case", default="poisson-16", help=f"one of {sorted(suite.CASES)} or a case of --catalogue")
     ap.add_argument("--catalogue", default="", help="TOML catalogue with further cases (configs/benches.toml)")
-    ap.add_argument("--models", nargs="+", default=["Qwen/Qwen3-0.6B"])
-    ap.add_argument("--atn", type=int, nargs="+", default=[0])
-    ap.add_argument("--ffn", type=int, nargs="+", default=[1])
-    ap.add_argument("--ffn-tp", type=int, default=1)
-    ap.add_argument("--atn-tp", type=int, default=1, help="attention tensor-parallel degree (= number of --atn devices)")
-    ap.add_argument("--elastic", action="store_true", help="elastic KV: co-located Instances lend physical KV memory")
-    ap.add_argument("--lanes", type=int, default=2)
+    ap.add_argument("--models", nargs="+", default=None, help="default: the case's deployment, else Qwen/Qwen3-0.6B")
+    ap.add_argument("--atn", type=int, nargs="+", default=None)
+    ap.add_argument("--ffn", type=int, nargs="+", default=None)
+    ap.add_argument("--ffn-tp", type=int, default=None)
+    ap.add_argument("--atn-tp", type=int, default=None, help="attention tensor-parallel degree (= number of --atn devices)")
+    ap.add_argument("--elastic", action="store_true", default=None, help="elastic KV: co-located Instances lend physical KV memory")
+    ap.add_argument("--lanes", type=int, default=None)
     ap.add_argument("--port", type=int, default=9841)
-    ap.add_argument("--max-batch", type=int, default=256)
-    ap.add_argument("--max-seq-len", type=int, default=2624)
+    ap.add_argument("--max-batch", type=int, default=None)
+    ap.add_argument("--max-seq-len", type=int, default=None)
     ap.add_argument("--prefill-chunk", type=int, default=4096, help="tokens per prefill step of the attention engines")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--duration", type=float, default=0.0, help="override the case's duration (seconds)")
@@ -132,6 +132,12 @@ def main(argv: list[str] | None = None) -> int:
     if ns.case not in cases:
         ap.error(f"unknown case {ns.case!r}; known: {sorted(cases)}")
     case = cases[ns.case]
+    dep_defaults = {"models": ["Qwen/Qwen3-0.6B"], "atn": [0], "ffn": [1], "ffn_tp": 1, "atn_tp": 1, "elastic": False, "lanes": 2,
+                    "max_batch": 256, "max_seq_len": 2624}
+    dep_defaults.update({k: list(v) if isinstance(v, tuple) else v for k, v in case.deployment_dict().items()})
+    for k, v in dep_defaults.items():          # command line > the case's deployment > defaults
+        if getattr(ns, k) is None:
+            setattr(ns, k, v)
     if ns.duration > 0 or ns.rate > 0:
         import dataclasses
 

@@ -37,6 +37,11 @@ class Case:
     slo_ttft_ms: float = 2000.0
     slo_tpot_ms: float = 50.0
     base_seed: int = 0
+    # where the case is meant to run (catalogue cases): models, atn / ffn devices, lanes, ffn_tp, atn_tp, elastic
+    deployment: tuple = ()
+
+    def deployment_dict(self) -> dict:
+        return dict(self.deployment)
 
 
 CASES: dict[str, Case] = {c.name: c for c in (
@@ -62,6 +67,19 @@ def _length(spec: dict | str) -> S.LengthSpec:
     return S.LengthSpec("lognormal", int(spec.get("lo", 1)), int(spec["hi"]), float(spec["median"]), float(spec.get("sigma", 1.0)))
 
 
+def _deployment(case: str, named: dict, ref) -> tuple:
+    """A case names its deployment (``deployment = "small-pair"`` -> ``[deployments.small-pair]``) or spells it out."""
+    if ref is None:
+        return ()
+    d = named.get(ref) if isinstance(ref, str) else ref
+    if not isinstance(d, dict):
+        raise ValueError(f"case {case}: unknown deployment {ref!r}")
+    unknown = set(d) - {"models", "atn", "ffn", "lanes", "ffn_tp", "atn_tp", "elastic", "max_batch", "max_seq_len"}
+    if unknown:
+        raise ValueError(f"case {case}: unknown deployment keys {sorted(unknown)}")
+    return tuple(sorted((k, tuple(v) if isinstance(v, list) else v) for k, v in d.items()))
+
+
 def load_catalogue(path: str | Path) -> dict[str, Case]:
     """Cases from a TOML catalogue (the counterpart of the reference's ``benches/benches.toml``):
 
@@ -80,14 +98,15 @@ def load_catalogue(path: str | Path) -> dict[str, Case]:
     for name, raw in doc.get("cases", {}).items():
         c = {**defaults, **raw}
         unknown = set(c) - {"rate_per_s", "duration_s", "prompt", "output", "repetitions", "warmup_requests", "burst",
-                            "slo_ttft_ms", "slo_tpot_ms", "base_seed"}
+                            "slo_ttft_ms", "slo_tpot_ms", "base_seed", "deployment"}
         if unknown:
             raise ValueError(f"case {name}: unknown keys {sorted(unknown)}")
         rates = c["rate_per_s"]
         out[name] = Case(name, tuple(float(r) for r in (rates if isinstance(rates, list) else [rates])), float(c["duration_s"]),
                          _length(c["prompt"]), _length(c["output"]), int(c.get("repetitions", 3)),
                          int(c.get("warmup_requests", 2)), tuple(float(x) for x in c.get("burst", (1.0, 0.0, 0.0))),
-                         float(c.get("slo_ttft_ms", 2000.0)), float(c.get("slo_tpot_ms", 50.0)), int(c.get("base_seed", 0)))
+                         float(c.get("slo_ttft_ms", 2000.0)), float(c.get("slo_tpot_ms", 50.0)), int(c.get("base_seed", 0)),
+                         _deployment(name, doc.get("deployments", {}), c.get("deployment")))
     return out
 
 

@@ -50,11 +50,19 @@ def test_a_crashing_repetition_is_recorded_and_the_suite_continues(tmp_path):
     assert X.main(["--targets", "m=http://x", "--out", str(tmp_path), "--cases", "nope"] ) if False else True
 
 
-def test_toml_catalogue_loads_cases_with_defaults():
+def test_toml_catalogue_loads_the_sixty_one_cases_with_defaults_and_deployments():
     from pathlib import Path
 
     cases = X.load_catalogue(Path(__file__).resolve().parent.parent / "configs" / "benches.toml")
-    assert {"pair-1rps", "input-heavy", "bursty-mix"} <= set(cases)
-    c = cases["input-heavy"]
+    assert len(cases) == 61
+    assert {"small-pair-1rps", "medium-input-heavy", "four-model-bursty", "large-isolated-b-4rps", "small-pair-atn-tp2-2rps"} <= set(cases)
+    c = cases["medium-input-heavy"]
     assert c.rate_per_s == (2.0, 2.0) and c.prompt.kind == "lognormal" and c.prompt.median == 4096 and c.output.hi == 128
-    assert cases["bursty-mix"].burst == (4.0, 30.0, 120.0) and cases["pair-1rps"].duration_s == 60 and cases["pair-1rps"].repetitions == 3
+    assert cases["four-model-bursty"].burst == (4.0, 30.0, 120.0) and cases["small-pair-1rps"].duration_s == 60
+    assert cases["small-pair-1rps"].repetitions == 3
+    d = cases["medium-pair-tp2-2rps"].deployment_dict()
+    assert d["ffn"] == (1, 2) and d["ffn_tp"] == 2 and d["models"] == ("Qwen/Qwen3-14B", "Qwen/Qwen3-8B") and d["lanes"] == 2
+    assert cases["small-pair-lanes1-1rps"].deployment_dict()["lanes"] == 1
+    assert cases["small-pair-atn-tp2-4rps"].deployment_dict()["atn_tp"] == 2
+    assert cases["large-pair-elastic-1rps"].deployment_dict()["elastic"] is True
+    assert sum(1 for n in cases if "isolated" in n) == 18 and sum(1 for n in cases if n.endswith("rps") and "-pair-" in n and "lanes1" not in n and "tp2" not in n and "elastic" not in n) == 18
