@@ -126,7 +126,8 @@ def cmd_memory_profile(ns) -> int:
     if getattr(ns, "calibrate", False):
         from ..runtime import memory_calibration as mcal
 
-        prof = mcal.calibrate()
+        cfg = _load(ns, require=False)
+        prof = mcal.calibrate(evidence_root=cfg.cache_root)     # evidence persists under the cache root; re-runs resume
         prof.save(ns.out)
         print(json.dumps({"saved": ns.out, "samples": prof.samples, "max_abs_error_bytes": prof.max_abs_error_bytes,
                           "coefficients": vars(prof.coefficients)}, indent=2))

@@ -11,7 +11,8 @@ measuring function is injectable so that the fit and the bookkeeping are testabl
 from __future__ import annotations
 
 import hashlib
-from dataclasses import dataclass
+import json
+from dataclasses import asdict, dataclass
 from pathlib import Path
 from typing import Callable
 
@@ -101,8 +102,66 @@ def current_environment() -> M.MemoryCalibrationEnvironment:
     return M.MemoryCalibrationEnvironment(name, drv, torch.version.cuda or "", f"torch {torch.__version__}", digest)
 
 
+def experiment_key(exp: Experiment) -> str:
+    return hashlib.sha256(repr(exp).encode()).hexdigest()[:12]
+
+
+class EvidenceStore:
+    """Measured peaks kept on disk, one JSON file per (environment, experiment): a calibration run that was interrupted
+    -- or a corpus that grew -- only measures what is missing, and a profile can be re-fitted without a GPU
+    (reference: memory_profile/evidence.py and experiment.py persist every experiment's evidence before fitting)."""
+
+    def __init__(self, root: str | Path, environment: M.MemoryCalibrationEnvironment):
+        self.dir = Path(root) / "memory-calibration" / environment.key()
+        self.environment = environment
+
+    def path(self, exp: Experiment) -> Path:
+        return self.dir / f"{experiment_key(exp)}.json"
+
+    def load(self, exp: Experiment) -> int | None:
+        p = self.path(exp)
+        if not p.exists():
+            return None
+        try:
+            d = json.loads(p.read_text())
+        except ValueError:
+            return None
+        return int(d["measured_bytes"]) if d.get("experiment") == asdict(exp) else None
+
+    def save(self, exp: Experiment, measured_bytes: int) -> None:
+        self.dir.mkdir(parents=True, exist_ok=True)
+        f = features_of(exp)
+        self.path(exp).write_text(json.dumps({"experiment": asdict(exp), "measured_bytes": int(measured_bytes),
+                                              "features": asdict(f), "environment": asdict(self.environment)}, indent=1))
+
+    def all(self) -> list[tuple[Experiment, int]]:
+        out = []
+        for p in sorted(self.dir.glob("*.json")) if self.dir.exists() else []:
+            try:
+                d = json.loads(p.read_text())
+                out.append((Experiment(**d["experiment"]), int(d["measured_bytes"])))
+            except (ValueError, KeyError, TypeError):
+                continue
+        return out
+
+
 def calibrate(corpus=DEFAULT_CORPUS, measure: Callable[[Experiment], int] = measure_on_gpu,
-              environment: M.MemoryCalibrationEnvironment | None = None) -> M.XpoolMemoryCalibrationProfile:
-    samples = [(features_of(e), measure(e)) for e in corpus]
+              environment: M.MemoryCalibrationEnvironment | None = None, evidence_root: str | Path | None = None
+              ) -> M.XpoolMemoryCalibrationProfile:
+    """Measures the corpus (skipping experiments whose evidence is already stored under ``evidence_root``), fits the
+    overhead coefficients to all stored evidence of this environment and returns the profile."""
+    env = environment or current_environment()
+    store = EvidenceStore(evidence_root, env) if evidence_root is not None else None
+    samples = []
+    for e in corpus:
+        got = store.load(e) if store is not None else None
+        if got is None:
+            got = measure(e)
+            if store is not None:
+                store.save(e, got)
+        samples.append((features_of(e), got))
+    if store is not None:                      # evidence of earlier runs with other experiments counts too
+        known = {experiment_key(e) for e in corpus}
+        samples += [(features_of(e), b) for e, b in store.all() if experiment_key(e) not in known]
     coef, resid = M.fit_coefficients(samples)
-    return M.XpoolMemoryCalibrationProfile(environment or current_environment(), coef, len(samples), resid)
+    return M.XpoolMemoryCalibrationProfile(env, coef, len(samples), resid)

@@ -88,3 +88,28 @@ def test_calibration_runner_fits_from_an_injected_measurement():
     assert abs(prof.coefficients.per_lane_bytes - 9e6) < 1e6
     f = mcal.features_of(mcal.Experiment("Qwen/Qwen3-0.6B", 28, 1, 2))
     assert f.weight_bytes == 28 * 3 * 1024 * 3072 * 2 and f.slot_bytes > 512 * 1024 * 2
+
+
+def test_calibration_evidence_persists_and_a_rerun_only_measures_what_is_missing(tmp_path):
+    from crosspool_b200.runtime import memory_calibration as mcal
+
+    env = M.MemoryCalibrationEnvironment("B200", "580", "12.9", "torch", "abc")
+    measured = []
+
+    def fake_measure(exp):
+        measured.append(exp)
+        f = mcal.features_of(exp)
+        return M.DeviceMemoryEstimator().analytic(f).total + int(500e6 + 6e6 * f.lanes + 2e6 * f.n_instances)
+
+    corpus = mcal.DEFAULT_CORPUS[:5]
+    p1 = mcal.calibrate(corpus, fake_measure, env, evidence_root=tmp_path)
+    assert len(measured) == 5 and p1.samples == 5
+    store = mcal.EvidenceStore(tmp_path, env)
+    assert len(store.all()) == 5 and store.load(corpus[0]) is not None
+    # a second run with a larger corpus measures only the new experiments and fits on everything stored
+    p2 = mcal.calibrate(mcal.DEFAULT_CORPUS[:7], fake_measure, env, evidence_root=tmp_path)
+    assert len(measured) == 7 and p2.samples == 7
+    assert abs(p2.coefficients.context_bytes - 500e6) < 5e6 and abs(p2.coefficients.per_lane_bytes - 6e6) < 1e6
+    # another environment has its own evidence
+    other = M.MemoryCalibrationEnvironment("B200", "999", "12.9", "torch", "abc")
+    assert mcal.EvidenceStore(tmp_path, other).all() == []
