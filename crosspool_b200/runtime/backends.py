@@ -315,6 +315,16 @@ class AtnBackend:
         return True
 
     def finalize(self) -> None:
+        if self._agree is not None:
+            # the TP group's gloo process group owns worker threads; leaving them to interpreter shutdown ends the
+            # process with "terminate called without an active exception" (joinable threads destroyed at exit)
+            import torch.distributed as dist
+
+            if dist.is_initialized():
+                dist.destroy_process_group()
+            self._agree = None
+        if self._server is not None:
+            self._server.should_exit = True
         self.engines.clear()
         for b in self.buffers.values():
             b.free()
