@@ -168,6 +168,9 @@ typedef struct XpLaneLayerDesc {
   int shared_inter_local;        /* > 0: shared experts as one dense gated FFN of this local width */
   const void* w_shared_gateup;   /* [2 * shared_inter_local, hidden] */
   const void* w_shared_down;     /* [hidden, shared_inter_local] */
+  const void* router_raw;        /* [num_experts, hidden] weights of an fp32 router projection (bf16; fp32 if precision 2) */
+  int router_precision;          /* 0 payload, 1 fp32 accumulate and logits from payload weights, 2 fp32 weights */
+  int reserved;
 } XpLaneLayerDesc;
 
 void* xp_lane_create(int n_instances, int n_lanes, int policy, uint64_t seed, size_t ws_bytes_per_lane);
@@ -218,6 +221,9 @@ typedef struct XpRouteArgs {
 } XpRouteArgs;
 
 int xp_router_topk(const XpRouterArgs* a, void* stream);
+/* Router projection with IEEE fp32 accumulation: x bf16 [rows, ldx], w [experts, hidden] bf16 (w_fp32 = 0) or fp32. */
+int xp_router_fp32(const void* x, int ldx, const void* w, int w_fp32, float* logits, int ld_logits, int rows, int hidden,
+                   int num_experts, void* stream);
 int xp_moe_route(const XpRouteArgs* a, void* stream);
 int xp_moe_gather(const void* x, const int* perm_token, const int* n_rows_ptr, void* out, int max_rows,
                   int hidden, int ldx, void* stream);

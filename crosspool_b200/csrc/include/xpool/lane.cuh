@@ -47,6 +47,9 @@ struct alignas(128) MoeLayer {
   float scale;
   int e_pad;
   uint8_t bn_router[kRowBuckets], splits_router[kRowBuckets];
+  int router_precision;         // 0 payload (tensor-core GEMM, bf16 logits), 1 fp32 logits from payload weights, 2 fp32 weights
+  int reserved;
+  const void* router_raw;       // [num_experts, hidden] router weights for the fp32 projection (bf16, or fp32 for precision 2)
 };
 
 // Per (instance, layer): weight tensor maps and epilogue parameters.
@@ -96,6 +99,7 @@ struct alignas(128) InstanceSlot {
 // Scratch of one Lane for mixture-of-experts layers (sized for the largest MoE instance).
 struct MoeLaneWs {
   __nv_bfloat16* logits;  // [capacity_rows, e_pad of the layer]
+  float* logits32;        // the same in fp32, for routers that ask for fp32 logits
   int* ids;               // [capacity_rows, top_k]
   float* weights;         // [capacity_rows, top_k]
   int* offsets;           // [n_local + 1] first route position of every local expert

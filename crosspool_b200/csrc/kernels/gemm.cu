@@ -86,7 +86,7 @@ gemm_lane_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, int 
   const lane::InstanceSlot& s = slots[cur->instance];
   const lane::LayerEntry& le = s.layers[cur->layer];
   const lane::MoeLayer* moe = le.moe;
-  if (phase == 2 && moe == nullptr) return;       // router projection: MoE layers only
+  if (phase == 2 && (moe == nullptr || moe->router_precision != 0)) return;  // payload-precision router projection only
   if (phase >= 3 && (moe == nullptr || le.shared_inter_local == 0)) return;  // shared experts of a MoE layer
   const int rows = static_cast<int>(cur->rows);
   int bucket = 0;

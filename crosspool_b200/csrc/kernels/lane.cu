@@ -30,6 +30,7 @@ __global__ void moe_lane_topk_kernel(const lane::InstanceSlot* slots, const lane
 __global__ void moe_lane_route_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws);
 __global__ void moe_lane_gather_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws);
 __global__ void moe_lane_combine_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws);
+__global__ void moe_lane_router_fp32_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws);
 }  // namespace moe
 
 namespace lane {
@@ -231,6 +232,8 @@ struct Runtime {
   MoeLaneMaps* mmaps_d = nullptr;  // [n_lanes][n_instances]
   std::vector<void*> moe_allocs;
   bool has_moe = false;
+  bool has_fp32_router = false;
+  int max_hidden = 0;
   int pe = 0;
   // replay threads (xp_lane_threads_start): one host thread, stream and instantiated graph per Lane
   int device = 0;
@@ -357,6 +360,11 @@ extern "C" int xp_lane_set_layer(void* h, int inst, int layer, const XpLaneLayer
       rc = tmap::encode_2d(&m.tmap_router, d->router, m.e_pad, s.hidden, static_cast<uint64_t>(s.hidden) * 2, 128, 64, 2);
     m.correction_bias = d->correction_bias;
     m.router_bias = d->router_bias;
+    m.router_precision = d->router_precision;
+    m.router_raw = d->router_raw;
+    if (d->router_precision != 0 && d->router_raw == nullptr) return -5;
+    if (d->router_precision != 0) rt->has_fp32_router = true;
+    rt->max_hidden = std::max(rt->max_hidden, s.hidden);
     m.num_experts = d->num_experts;
     m.top_k = d->top_k;
     m.expert_lo = d->expert_lo;
@@ -457,6 +465,7 @@ static int commit_moe(Runtime* rt) {
   for (int l = 0; l < rt->n_lanes; ++l) {
     lane::MoeLaneWs& w = ws[l];
     w.logits = static_cast<__nv_bfloat16*>(alloc(rows * e_pad * 2));
+    w.logits32 = rt->has_fp32_router ? static_cast<float*>(alloc(rows * e_pad * 4)) : nullptr;
     w.ids = static_cast<int*>(alloc(routes * 4));
     w.weights = static_cast<float*>(alloc(routes * 4));
     w.offsets = static_cast<int*>(alloc((n_local + 1) * 4));
@@ -544,6 +553,8 @@ extern "C" int xp_lane_launch(void* h, int lane_index, uint64_t lease_ns, void* 
     // MoE prologue; every kernel returns at once when the invocation's layer is dense
     gemm::gemm_lane_kernel<<<rt->sms, gemm::kThreads, smem, s>>>(rt->slots_d, cur, 2, ws, counters, smem_budget, rt->status_d,
                                                                  mws, mmaps);
+    if (rt->has_fp32_router)   // routers that ask for fp32 logits: exact SIMT projection (a no-op for the other layers)
+      moe::moe_lane_router_fp32_kernel<<<rt->sms * 2, 256, rt->max_hidden * sizeof(float), s>>>(rt->slots_d, cur, mws);
     moe::moe_lane_topk_kernel<<<rt->sms, 128, 0, s>>>(rt->slots_d, cur, mws);
     moe::moe_lane_route_kernel<<<1, 1024, 0, s>>>(rt->slots_d, cur, mws);
     moe::moe_lane_gather_kernel<<<rt->sms * 4, 128, 0, s>>>(rt->slots_d, cur, mws);

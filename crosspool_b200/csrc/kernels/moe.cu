@@ -268,7 +268,7 @@ moe_lane_topk_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, 
   const lane::MoeLayer* m = lane_moe_layer(slots, cur);
   if (m == nullptr) return;
   XpRouterArgs a;
-  a.logits = ws->logits;
+  a.logits = m->router_precision != 0 ? static_cast<const void*>(ws->logits32) : static_cast<const void*>(ws->logits);
   a.logit_bias = m->router_bias;
   a.correction_bias = m->correction_bias;
   a.topk_ids = ws->ids;
@@ -277,7 +277,7 @@ moe_lane_topk_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, 
   a.num_experts = m->num_experts;
   a.top_k = m->top_k;
   a.ld_logits = m->e_pad;
-  a.logits_fp32 = 0;
+  a.logits_fp32 = m->router_precision != 0;
   a.sigmoid = m->sigmoid;
   a.renormalize = m->renormalize;
   a.round_weights_bf16 = 0;
@@ -397,6 +397,62 @@ moe_lane_combine_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cu
                   reinterpret_cast<__nv_bfloat16*>(dst), m->top_k, s.hidden, s.hidden, token);
 }
 
+// Router projection with IEEE fp32 accumulation: logits[r, e] = sum_k x[r, k] * w[e, k] in fp32, the products
+// summed per lane in index order and the lanes folded by a fixed butterfly, so results are reproducible. The
+// reference keeps two router precisions beside the payload one (docs/designs/ffn-execution.md:165-173): fp32 weights
+// and fp32 inputs (GLM, sigmoid routers) and payload-dtype weights with fp32 accumulate and fp32 logits
+// (DeepSeek-V2); both run on its SIMT fp32 GEMMs (operators/simt.py:80-240), never on TF32. The tensor cores
+// accumulate bf16 products in fp32 too, but round the logits to bf16 on the way out and sum in hardware order;
+// a router is a few hundred MFLOP at most, so the exact form costs microseconds.
+template <typename WT>
+__device__ __forceinline__ void router_fp32_rows(const __nv_bfloat16* __restrict__ x, int ldx, const WT* __restrict__ w,
+                                                 float* __restrict__ logits, int ld_logits, int rows, int hidden, int E,
+                                                 float* xs) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    __syncthreads();
+    for (int k = threadIdx.x; k < hidden; k += blockDim.x) xs[k] = __bfloat162float(x[static_cast<size_t>(row) * ldx + k]);
+    __syncthreads();
+    for (int e = warp; e < E; e += nwarps) {
+      const WT* wr = w + static_cast<size_t>(e) * hidden;
+      float acc = 0.f;
+      for (int k = lane; k < hidden; k += 32) {
+        float wv;
+        if constexpr (sizeof(WT) == 4) wv = wr[k];
+        else wv = __bfloat162float(wr[k]);
+        acc = fmaf(xs[k], wv, acc);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) logits[static_cast<size_t>(row) * ld_logits + e] = acc;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+router_fp32_kernel(const __nv_bfloat16* x, int ldx, const void* w, int w_fp32, float* logits, int ld_logits, int rows, int hidden, int E) {
+  extern __shared__ float xs_dyn[];
+  if (w_fp32) router_fp32_rows(x, ldx, static_cast<const float*>(w), logits, ld_logits, rows, hidden, E, xs_dyn);
+  else router_fp32_rows(x, ldx, static_cast<const __nv_bfloat16*>(w), logits, ld_logits, rows, hidden, E, xs_dyn);
+}
+
+// Lane node: the same projection for the invocation the Lane holds; returns at once unless the layer's router asks
+// for fp32 logits (the payload-precision router runs as a tensor-core GEMM node instead).
+__global__ void __launch_bounds__(256)
+moe_lane_router_fp32_kernel(const lane::InstanceSlot* slots, const lane::LaneCur* cur, const lane::MoeLaneWs* ws) {
+  extern __shared__ float xs_dyn[];
+  const lane::MoeLayer* m = lane_moe_layer(slots, cur);
+  if (m == nullptr || m->router_precision == 0) return;
+  const lane::InstanceSlot& s = slots[cur->instance];
+  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(s.input);
+  if (m->router_precision == 2)
+    router_fp32_rows(x, s.hidden, static_cast<const float*>(m->router_raw), ws->logits32, m->e_pad, static_cast<int>(cur->rows), s.hidden,
+                     m->num_experts, xs_dyn);
+  else
+    router_fp32_rows(x, s.hidden, static_cast<const __nv_bfloat16*>(m->router_raw), ws->logits32, m->e_pad, static_cast<int>(cur->rows),
+                     s.hidden, m->num_experts, xs_dyn);
+}
+
 }  // namespace moe
 }  // namespace xpool
 
@@ -405,6 +461,16 @@ using namespace xpool::moe;
 static int last_error() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);
+}
+
+extern "C" int xp_router_fp32(const void* x, int ldx, const void* w, int w_fp32, float* logits, int ld_logits, int rows, int hidden,
+                              int num_experts, void* stream) {
+  if (rows <= 0) return 0;
+  if (hidden <= 0 || hidden > 16384 || num_experts <= 0) return -10;
+  const int grid = rows < 148 * 4 ? rows : 148 * 4;
+  router_fp32_kernel<<<grid, 256, hidden * sizeof(float), reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, w, w_fp32, logits, ld_logits, rows, hidden, num_experts);
+  return last_error();
 }
 
 extern "C" int xp_router_topk(const XpRouterArgs* a, void* stream) {

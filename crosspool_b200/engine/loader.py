@@ -18,7 +18,7 @@ from dataclasses import dataclass
 
 import torch
 
-from ..ffn import DenseFfnSpec, FfnModelSpec, GateUpOrder, MoeFfnSpec
+from ..ffn import DenseFfnSpec, FfnModelSpec, GateUpOrder, MoeFfnSpec, RouterProjectionPrecision
 from ..models.weights import FfnLayerWeights
 from .checkpoint import CheckpointKeyView
 
@@ -160,6 +160,8 @@ def _moe_reads(l: MoeFfnSpec, rank: int, size: int, experts: range, packed_weigh
     rows = _local(l.moe_intermediate_size, rank, size)
     ex = l.experts
     reads = {"router": TensorRead(l.router_weight_key)}
+    if l.router_precision == RouterProjectionPrecision.FP32:
+        reads["router_fp32"] = TensorRead(l.router_weight_key)     # kept at fp32 for the exact projection
     if l.router_bias_key:
         reads["router_bias"] = TensorRead(l.router_bias_key)
     if l.correction_bias_key:
@@ -218,8 +220,8 @@ def materialize_layer_weights(spec: FfnModelSpec, view: CheckpointKeyView, layer
 
     def fetch(item):
         name, r = item
-        bias = "bias" in name      # biases stay fp32: the GEMM epilogue adds them to the fp32 accumulator
-        return name, stager.to_device(reader.read(r), torch.float32 if bias else dtype)
+        wide = "bias" in name or name == "router_fp32"   # biases stay fp32: the GEMM epilogue adds them to the fp32 accumulator
+        return name, stager.to_device(reader.read(r), torch.float32 if wide else dtype)
 
     with ThreadPoolExecutor(max_workers=max(1, parallelism)) as pool:
         got = dict(pool.map(fetch, reads.items()))
@@ -254,6 +256,9 @@ def materialize_layer_weights(spec: FfnModelSpec, view: CheckpointKeyView, layer
         if k in got:
             w.extra[k] = got[k]
     w.extra["experts"] = (experts.start, experts.stop)
+    w.extra["router_precision"] = l.router_precision.value
+    if "router_fp32" in got:
+        w.extra["router_fp32"] = got["router_fp32"].contiguous()
     return w
 
 

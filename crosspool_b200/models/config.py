@@ -43,6 +43,7 @@ class ModelConfig:
     first_k_dense: int = 0
     routed_scaling_factor: float = 1.0
     router_scoring: str = "softmax"  # or "sigmoid"
+    router_precision: str = "payload"  # "fp32_logits" (payload weights, fp32 logits) or "fp32" (fp32 weights too)
     dtype: str = "bfloat16"
     extra: dict[str, Any] = field(default_factory=dict, compare=False, hash=False)
 
@@ -154,6 +155,7 @@ def from_hf_config(cfg: dict[str, Any], name: str = "") -> ModelConfig:
         first_k_dense=int(cfg.get("first_k_dense_replace", 0) or 0),
         routed_scaling_factor=float(cfg.get("routed_scaling_factor", 1.0) or 1.0),
         router_scoring=str(cfg.get("scoring_func", "softmax")),
+        router_precision={"DeepseekV2ForCausalLM": "fp32_logits", "Glm4MoeLiteForCausalLM": "fp32"}.get(arch, "payload"),
         dtype=str(cfg.get("torch_dtype", cfg.get("dtype", "bfloat16"))),
         extra={k: v for k, v in cfg.items() if k in ("swiglu_limit", "sliding_window", "quantization_config")},
     )

@@ -90,7 +90,11 @@ def route_topk(logits: torch.Tensor, k: int, renormalize: bool, scoring: str = "
 
 
 def moe_ffn(x: torch.Tensor, w: FfnLayerWeights, cfg: ModelConfig) -> torch.Tensor:
-    logits = F.linear(x, w.router)
+    prec = getattr(w.extra.get("router_precision", "payload"), "value", w.extra.get("router_precision", "payload"))
+    if prec == "payload":
+        logits = F.linear(x, w.router)
+    else:   # fp32 accumulation and fp32 logits; "fp32" also keeps the router weights in fp32
+        logits = F.linear(x.float(), w.extra["router_fp32"].float() if prec == "fp32" else w.router.float())
     if w.extra.get("router_bias") is not None:
         logits = logits.float() + w.extra["router_bias"].float()    # payload-precision logits, bias added in fp32
     ids, weights = route_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.router_scoring,

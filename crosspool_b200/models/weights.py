@@ -150,8 +150,15 @@ def random_ffn_layer(cfg: ModelConfig, layer: int, seed: int = 0, device="cpu", 
             gate_up, down = gate_up[lo:hi].contiguous(), down[lo:hi].contiguous()
             if lo != 0:
                 shared_gu = shared_dn = None   # the rank owning expert 0 adds the shared experts
-        return FfnLayerWeights(gate_up.to(device), down.to(device), router=router.to(device), shared_gate_up=shared_gu,
-                               shared_down=shared_dn)
+        w = FfnLayerWeights(gate_up.to(device), down.to(device), router=router.to(device), shared_gate_up=shared_gu,
+                            shared_down=shared_dn)
+        if cfg.router_precision != "payload":
+            w.extra["router_precision"] = cfg.router_precision
+            if cfg.router_precision == "fp32":   # fp32 router weights; the payload copy is their rounding
+                w.extra["router_fp32"] = (w.router.float() + _randn(gen, (e, h), torch.float32, device).to(device) * 2.0 ** -10
+                                          ).contiguous()
+                w.router = w.extra["router_fp32"].to(dt)
+        return w
     inter = cfg.intermediate_size
     gate_up = _randn(gen, (2 * inter, h), dt, device)
     down = _randn(gen, (h, inter), dt, device)

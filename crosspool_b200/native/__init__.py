@@ -322,6 +322,9 @@ class LaneLayerDesc(C.Structure):
         ("shared_inter_local", C.c_int),
         ("w_shared_gateup", C.c_void_p),
         ("w_shared_down", C.c_void_p),
+        ("router_raw", C.c_void_p),
+        ("router_precision", C.c_int),
+        ("reserved", C.c_int),
     ]
 
 
@@ -389,6 +392,7 @@ class RouteArgs(C.Structure):
 def _declare_moe(lib: C.CDLL) -> None:
     sig = {
         "xp_router_topk": [C.POINTER(RouterArgs), C.c_void_p],
+        "xp_router_fp32": [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p],
         "xp_moe_route": [C.POINTER(RouteArgs), C.c_void_p],
         "xp_moe_gather": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p],
         "xp_moe_combine": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p],

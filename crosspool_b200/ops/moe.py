@@ -41,6 +41,35 @@ class MoeWorkspace:
     xp: torch.Tensor
     act: torch.Tensor
     yp: torch.Tensor
+    logits32: torch.Tensor | None = None   # fp32 router logits, allocated on first use by an fp32 router projection
+
+
+ROUTER_PRECISIONS = {"payload": 0, "fp32_logits": 1, "fp32": 2}
+
+
+def router_precision_code(w: FfnLayerWeights) -> int:
+    """0: bf16 tensor-core projection with bf16 logits; 1: payload weights, fp32 accumulation and fp32 logits; 2: fp32
+    weights (``w.extra["router_fp32"]``), fp32 accumulation and logits. Reference: ``RouterProjectionPrecision`` in
+    src/xpool/ffn.py and its use in src/xpool/runtime/ffnagent/operators/routing.py."""
+    p = w.extra.get("router_precision", "payload")
+    p = getattr(p, "value", p)
+    if p not in ROUTER_PRECISIONS:
+        raise ValueError(f"unknown router projection precision {p!r}")
+    if p == "fp32" and w.extra.get("router_fp32") is None:
+        raise ValueError("router precision 'fp32' needs the fp32 router weights in extra['router_fp32']")
+    return ROUTER_PRECISIONS[p]
+
+
+def router_project_fp32(x: torch.Tensor, w: FfnLayerWeights, out: torch.Tensor) -> torch.Tensor:
+    """``out[:, :num_experts] = x @ router^T`` accumulated and stored in fp32 (exact SIMT projection)."""
+    code = router_precision_code(w)
+    rw = w.extra["router_fp32"] if code == 2 else w.router
+    assert rw.is_contiguous() and out.dtype == torch.float32 and x.stride(1) == 1
+    assert rw.dtype == (torch.float32 if code == 2 else torch.bfloat16)
+    native.check(native.kernels().xp_router_fp32(x.data_ptr(), x.stride(0), rw.data_ptr(), int(code == 2), out.data_ptr(),
+                                                 out.stride(0), x.shape[0], x.shape[1], rw.shape[0], _stream(x.device)),
+                 "xp_router_fp32")
+    return out
 
 
 _ws_cache: dict[tuple, MoeWorkspace] = {}
@@ -131,9 +160,14 @@ def moe_forward(x: torch.Tensor, w: FfnLayerWeights, cfg: ModelConfig, out: torc
     if out is None:
         out = torch.empty(rows, h, dtype=torch.bfloat16, device=dev)
     lib, s = native.kernels(), _stream(dev)
-    # 1. router (payload precision: bf16 logits, fp32 scores)
-    logits = ws.logits[:rows]
-    gemm.linear(x, padded_router(w), out=logits)
+    # 1. router (payload precision: bf16 logits; fp32 precisions: exact fp32 logits; scores always fp32)
+    if router_precision_code(w) == 0:
+        logits = ws.logits[:rows]
+        gemm.linear(x, padded_router(w), out=logits)
+    else:
+        if ws.logits32 is None:
+            ws.logits32 = torch.zeros(ws.cap_rows, ws.logits.shape[1], dtype=torch.float32, device=dev)
+        logits = router_project_fp32(x, w, ws.logits32[:rows])
     router_topk(logits, e_total, k, out_ids=ws.ids[:rows], out_weights=ws.weights[:rows],
                 sigmoid=cfg.router_scoring == "sigmoid", renormalize=cfg.norm_topk_prob, scale=cfg.routed_scaling_factor,
                 correction_bias=w.extra.get("correction_bias"), logit_bias=w.extra.get("router_bias"))

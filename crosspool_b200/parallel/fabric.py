@@ -473,7 +473,7 @@ class FfnRankRuntime:
                 gu, dn = w.gate_up, w.down
                 ld = native.LaneLayerDesc()
                 if w.is_moe:
-                    from ..ops.moe import padded_router
+                    from ..ops.moe import padded_router, router_precision_code
 
                     if w.shared_gate_up is not None:
                         ld.shared_inter_local = w.shared_gate_up.shape[0] // 2
@@ -482,6 +482,11 @@ class FfnRankRuntime:
                     router = padded_router(w)
                     lo, hi = p.expert_range(st.tp_rank)
                     ld.router = router.data_ptr()
+                    ld.router_precision = router_precision_code(w)
+                    if ld.router_precision:
+                        raw = w.extra["router_fp32"] if ld.router_precision == 2 else w.router
+                        assert raw.is_contiguous()
+                        ld.router_raw = raw.data_ptr()
                     cb, rb = w.extra.get("correction_bias"), w.extra.get("router_bias")
                     ld.correction_bias = cb.data_ptr() if cb is not None else None
                     ld.router_bias = rb.data_ptr() if rb is not None else None

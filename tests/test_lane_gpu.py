@@ -149,12 +149,50 @@ def test_fabric_observer_records_lane_events_in_order_and_counts_overflow():
         ffn.close()
 
 
-def _moe_cfg(E=8, k=2, hidden=256, inter=128, layers=1, shared=0):
+def _moe_cfg(E=8, k=2, hidden=256, inter=128, layers=1, shared=0, **kw):
     from crosspool_b200.models.config import ModelConfig
 
     return ModelConfig(name="tmoe", architecture="Qwen3MoeForCausalLM", hidden_size=hidden, num_layers=layers, num_q_heads=4,
                        num_kv_heads=2, head_dim=64, intermediate_size=inter, vocab_size=128, num_experts=E,
-                       num_experts_per_tok=k, moe_intermediate_size=inter, num_shared_experts=shared)
+                       num_experts_per_tok=k, moe_intermediate_size=inter, num_shared_experts=shared, **kw)
+
+
+@pytest.mark.parametrize("precision,scoring", [("fp32_logits", "softmax"), ("fp32", "sigmoid")])
+def test_lane_routes_with_an_fp32_router_projection(precision, scoring):
+    """A layer whose router asks for fp32 logits is served by the Lane's SIMT projection node; a payload-precision
+    layer of a second model keeps the tensor-core projection in the same graph."""
+    from crosspool_b200.models.reference import moe_ffn
+    from crosspool_b200.parallel import fabric as F
+
+    rows = 37
+    ffn = F.FfnRankRuntime("cuda", n_lanes=1)
+    cfgs = [_moe_cfg(64, 4, 1024, 256, router_precision=precision, router_scoring=scoring), _moe_cfg(8, 2, 256, 128)]
+    places, atn = [], []
+    for i, cfg in enumerate(cfgs):
+        p = F.InstancePlacement(f"m{i}", cfg, seed=i + 11, atn_rank=0, ffn_ranks=(1,), capacity_rows=128)
+        st = ffn.add_instance(p, 0)
+        buf = F.PeerBuffer(F.atn_slot_layout(p).total_bytes)
+        st.atn_base = buf.ptr
+        places.append(p)
+        atn.append(buf)
+    ffn.install()
+    try:
+        g = torch.Generator(device="cuda").manual_seed(rows)
+        xs = [(torch.randn(rows, c.hidden_size, device="cuda", generator=g) * 0.5).bfloat16() for c in cfgs]
+        for i in (0, 1):
+            _publish(F, ffn.instances[i], places[i], xs[i], 0, 1)
+        ffn.launch_once(0, lease_ms=20)
+        ffn.launch_once(0, lease_ms=20)
+        torch.cuda.synchronize()
+        assert ffn.stats()["status"] == 0 and ffn.stats()["served"] == [1, 1]
+        for i in (0, 1):
+            out, rc, nrows, _ = _result(F, atn[i], places[i], rows)
+            assert (rc, nrows) == (0, rows)
+            ref = moe_ffn(xs[i], ffn.instances[i].weights[0], cfgs[i]).float()
+            err = (out.float() - ref).abs()
+            assert (err.pow(2).mean().sqrt() / ref.pow(2).mean().sqrt().clamp_min(1e-9)).item() < 0.03, i
+    finally:
+        ffn.close()
 
 
 @pytest.mark.parametrize("E,k,hidden,inter,rows", [(8, 2, 256, 128, 7), (128, 8, 2048, 768, 64), (128, 8, 2048, 768, 1)])
@@ -303,17 +341,19 @@ def test_a_rank_refuses_layers_of_another_layer_group():
     try:
         assert st.weights[0] is None and st.weights[1] is not None
         x = (torch.randn(4, cfg.hidden_size, device="cuda") * 0.5).bfloat16()
-        _publish(F, st, place, x, 0, 1)
-        ffn.launch_once(0, lease_ms=20)
-        torch.cuda.synchronize()
-        _, rc, nrows, seq = _result(F, buf, place, 4)
-        assert (rc, nrows, seq) == (2, 0, 1)                      # ProtocolMismatch, nothing computed
-        _publish(F, st, place, x, 1, 5)                           # sequence numbers may jump: other groups served 2..4
+        _publish(F, st, place, x, 1, 4)                           # sequence numbers may jump: other groups served 1..3
         ffn.launch_once(0, lease_ms=20)
         torch.cuda.synchronize()
         out, rc, nrows, seq = _result(F, buf, place, 4)
-        assert (rc, nrows, seq) == (0, 4, 5)
+        assert (rc, nrows, seq) == (0, 4, 4)
         torch.testing.assert_close(out.float(), _ref(x, st.weights[1]), atol=2e-2, rtol=2e-2)
+        _publish(F, st, place, x, 0, 5)                           # a layer of the other group
+        ffn.launch_once(0, lease_ms=20)
+        torch.cuda.synchronize()
+        _, rc, nrows, seq = _result(F, buf, place, 4)
+        assert (rc, nrows, seq) == (2, 0, 5)                      # ProtocolMismatch, nothing computed
+        f = ffn.failure()                                         # ... and the generation's canonical failure
+        assert f is not None and (f.result_code, f.invocation_sequence, f.layer_ordinal) == (2, 5, 0)
     finally:
         ffn.close()
         buf.free()

@@ -166,3 +166,29 @@ def test_gpt_oss_mxfp4_checkpoint_loads_dequantised_shards_with_biases(tmp_path)
         assert (w.down_bias is not None) == (rank == 0)          # added once across the TP group
         assert w.extra["gate_transform"] == (7.0, 1.0, 1.702) and w.extra["router_bias"].shape == (E,)
     assert w.gate_up_bias.dtype == torch.float32
+
+
+def test_an_fp32_router_checkpoint_keeps_its_router_weights_in_fp32(tmp_path):
+    """A sigmoid-scored (GLM-style) router is projected in fp32: the loader keeps an fp32 copy of the router weights
+    beside the payload copy and names the precision on the layer; a DeepSeek-V2 router keeps payload weights."""
+    H, I, E = 64, 32, 4
+    base = {"hidden_size": H, "intermediate_size": 128, "moe_intermediate_size": I, "num_hidden_layers": 1, "n_routed_experts": E,
+            "num_experts_per_tok": 2, "first_k_dense_replace": 0, "num_attention_heads": 4, "vocab_size": 100}
+    g = torch.Generator().manual_seed(5)
+    p = "model.layers.0.mlp."
+    router = torch.randn(E, H, generator=g)       # fp32 in the checkpoint
+    tensors = {p + "gate.weight": router, p + "gate.e_score_correction_bias": torch.randn(E, generator=g)}
+    for e in range(E):
+        tensors[f"{p}experts.{e}.gate_proj.weight"] = torch.randn(I, H, generator=g).bfloat16()
+        tensors[f"{p}experts.{e}.up_proj.weight"] = torch.randn(I, H, generator=g).bfloat16()
+        tensors[f"{p}experts.{e}.down_proj.weight"] = torch.randn(H, I, generator=g).bfloat16()
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(tmp_path / "model.safetensors"))
+    view = ck.read_checkpoint_key_view(tmp_path)
+    for arch, prec in (("Glm4MoeLiteForCausalLM", "fp32"), ("DeepseekV2ForCausalLM", "fp32_logits")):
+        spec = adapters.compile_ffn_spec("m", {"architectures": [arch], **base}, view.keys())
+        w = loader.materialize_layer_weights(spec, view, 0)
+        assert w.extra["router_precision"] == prec and w.router.dtype == torch.bfloat16
+        if prec == "fp32":
+            assert torch.equal(w.extra["router_fp32"], router) and torch.equal(w.router, router.bfloat16())
+        else:
+            assert "router_fp32" not in w.extra

@@ -109,3 +109,37 @@ def test_moe_forward_with_expert_biases_and_gate_transform(rows):
     assert_ffn_close(y.float(), ref.float())
     plain = moe_ffn(x, random_ffn_layer(cfg, 0, seed=11, device="cuda", dtype=torch.bfloat16), cfg)
     assert (plain.float() - ref.float()).abs().max() > 0.05       # the additions matter at this scale
+
+
+@pytest.mark.parametrize("precision,scoring", [("fp32_logits", "softmax"), ("fp32", "sigmoid")])
+@pytest.mark.parametrize("rows,E,hidden", [(5, 8, 256), (130, 64, 2048), (33, 160, 1536)])
+def test_fp32_router_projection_matches_an_fp32_matmul(rows, E, hidden, precision, scoring):
+    """The projection itself (fp32 accumulate, fp32 logits) within the reference's routing tolerances, and the routing
+    decision of the whole layer equal to the oracle's."""
+    from crosspool_b200.models.reference import moe_ffn, route_topk
+    from crosspool_b200.models.weights import random_ffn_layer
+    from crosspool_b200.ops import gemm, moe
+
+    cfg = _cfg(E, min(4, E), hidden, 128, router_precision=precision, router_scoring=scoring)
+    w = random_ffn_layer(cfg, 0, seed=9, device="cuda", dtype=torch.bfloat16)
+    assert w.extra["router_precision"] == precision and (precision != "fp32" or w.extra["router_fp32"].dtype == torch.float32)
+    g = torch.Generator(device="cuda").manual_seed(rows + E)
+    x = (torch.randn(rows, hidden, device="cuda", generator=g) * 0.5).bfloat16()
+    out = torch.full((rows, (E + 127) // 128 * 128), float("nan"), device="cuda")
+    moe.router_project_fp32(x, w, out)
+    rw = w.extra["router_fp32"] if precision == "fp32" else w.router.float()
+    ref = x.double() @ rw.double().t()
+    torch.testing.assert_close(out[:, :E].double(), ref, atol=1e-4, rtol=1e-3)
+    ids = torch.zeros(rows, cfg.num_experts_per_tok, dtype=torch.int32, device="cuda")
+    wt = torch.zeros(rows, cfg.num_experts_per_tok, device="cuda")
+    moe.router_topk(out[:, :E] if E % 128 == 0 else out, E, cfg.num_experts_per_tok, out_ids=ids, out_weights=wt,
+                    sigmoid=scoring == "sigmoid", renormalize=True)
+    rid, rwt = route_topk(ref.float(), cfg.num_experts_per_tok, True, scoring)
+    same = (ids.long().sort(-1).values == rid.sort(-1).values).all(-1).float().mean().item()
+    assert same >= 0.97, same      # a near-tie may flip between fp32 and fp64 accumulation; nothing else may
+    y = moe.moe_forward(x, w, cfg)
+    torch.cuda.synchronize()
+    gemm.check_status(x.device)
+    r = moe_ffn(x, w, cfg).float()
+    err = (y.float() - r).abs()
+    assert (err.pow(2).mean().sqrt() / r.pow(2).mean().sqrt().clamp_min(1e-9)).item() < 0.03
