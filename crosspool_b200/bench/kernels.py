@@ -337,7 +337,7 @@ def main(argv: list[str] | None = None) -> int:
     pa.add_argument("--kv-heads", type=int, default=8)
     pa.add_argument("--head-dim", type=int, default=128)
     pa.add_argument("--page", type=int, default=16, help="tokens per KV page")
-    pa.add_argument("--kernel", default="umma", choices=["umma", "mma", "simple"],
+    pa.add_argument("--kernel", default="umma", choices=["umma", "umma-alt", "mma", "simple"],
                     help="umma: tcgen05 kernel; mma: TMA-fed mma.sync kernel; simple: plain mma.sync kernel")
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=256)

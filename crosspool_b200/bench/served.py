@@ -114,17 +114,17 @@ def _build_mix(name: str, world: int, scale: float) -> tuple[list[ModelStream], 
     if name == "c":
         # Qwen3-8B + Qwen3-0.6B sharing each attention GPU with elastic KV; FFN of the 8B tensor-parallel over the
         # 2-GPU FFN tier, the 0.6B on one rank of it. The two models trade long-context and short-context traffic
-        # every window.
-        if world < 3:
-            raise SystemExit("mix c needs at least 3 GPUs (1 attention + 2 FFN)")
+        # every window. On 2 GPUs the FFN tier is the one other GPU (8B untiled), a reduced form for bring-up.
+        if world < 2:
+            raise SystemExit("mix c needs at least 2 GPUs (1 attention + 1 FFN; 2 FFN from 3 GPUs on)")
         n_atn = max(1, world - 2)
-        f0, f1 = n_atn, n_atn + 1
+        f0, f1 = n_atn, min(n_atn + 1, world - 1)
         long_p, long_o = _lognormal(8192, 256, 32768), _uniform(256, 256)
         short_p, short_o = _uniform(256, 256), _uniform(128, 128)
         out = []
         for a in range(n_atn):
             common = dict(max_seq_len=32768 + 256 + PAGE, prefill_chunk=4096, elastic=True)
-            out.append(ModelStream(f"Qwen/Qwen3-8B#{a}", "Qwen/Qwen3-8B", 10 + a, a, (f0, f1), 4.0 * scale, long_p, long_o,
+            out.append(ModelStream(f"Qwen/Qwen3-8B#{a}", "Qwen/Qwen3-8B", 10 + a, a, (f0, f1) if f1 != f0 else (f0,), 4.0 * scale, long_p, long_o,
                                    max_batch=128, kv_tokens=512 * 1024, alt_rate=32.0 * scale, alt_prompt=short_p,
                                    alt_output=short_o, swap_phase=0, **common))
             out.append(ModelStream(f"Qwen/Qwen3-0.6B#{a}", "Qwen/Qwen3-0.6B", 20 + a, a, (f0 if a % 2 == 0 else f1,),

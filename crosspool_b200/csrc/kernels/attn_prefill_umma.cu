@@ -37,6 +37,7 @@ constexpr int kBN = 64;          // cached tokens per K/V tile
 constexpr int kStages = 3;
 constexpr int kThreads = 320;
 constexpr float kRescaleStep = 8.0f;   // log2 units
+constexpr int kDefaultTS = 0;          // 1: P through tensor memory unless bit 8 of force_simple asks for shared memory
 
 struct __align__(8) Bars {
   uint64_t q_full;
@@ -66,18 +67,23 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, Bars* b
   return true;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int D>
+template <int D, bool kTS>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_k3,
                          const __grid_constant__ CUtensorMap tmap_v3, XpPrefillAttnArgs a, int G, int g_shift,
                          int box_tokens) {
-  const bool swap_v_offsets = (a.force_simple >> 8) & 1;   // diagnostic: exchange the two byte offsets of V's descriptor
   constexpr int kHalves = D / 64;                 // 64-dim (128-byte) column blocks of a row
   constexpr int kQHalf = kRows * 128;             // one 64-dim block of a query tile
   constexpr int kQTile = kHalves * kQHalf;
@@ -91,7 +97,9 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   __shared__ Bars bars;
 
   const int np = kRows >> g_shift;                // query positions per tile
-  const int seq = blockIdx.z, hk = blockIdx.y, qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  // blocks are dispatched x-fastest: (head, sequence) vary fastest and the query tile slowest, so that the tiles with
+  // the longest key range of every head and sequence start first and the short ones fill the tail
+  const int hk = blockIdx.x, seq = blockIdx.y, qt = static_cast<int>(gridDim.z) - 1 - static_cast<int>(blockIdx.z);
   const int q_len = a.q_lens[seq];
   const int q0 = qt * 2 * np;                     // first position of the CTA (longest tiles are dispatched first)
   if (q0 >= q_len) return;
@@ -197,10 +205,14 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk) {
           const uint64_t da = sm100::umma_desc_sw128(p_s + x * kPTile) + kk * 2;
-          const uint64_t db = swap_v_offsets
-                                  ? sm100::umma_desc_mn_sw128(kv_s + s * kStage + kKVTile + kk * 2048, 1024, kKVHalf)
-                                  : sm100::umma_desc_mn_sw128(kv_s + s * kStage + kKVTile + kk * 2048, kKVHalf, 1024);
-          sm100::umma_bf16(d, da, db, idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+          const uint64_t db = sm100::umma_desc_mn_sw128(kv_s + s * kStage + kKVTile + kk * 2048, kKVHalf, 1024);
+          if constexpr (kTS) {
+            // P(t) sits in the first 32 columns of the S buffer it was computed from, 8 columns per K step
+            sm100::umma_bf16_ts(d, tmem + static_cast<uint32_t>((x * 2 + (t & 1)) * kBN + kk * 8), db, idesc_o,
+                                (t > 0 || kk > 0) ? 1u : 0u);
+          } else {
+            sm100::umma_bf16(d, da, db, idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+          }
         }
         sm100::umma_commit(&bars.pv_done[x]);
       };
@@ -216,7 +228,7 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         if (next) ok = wait_bar(&bars.kv_full[t1 % kStages], (t1 / kStages) & 1, &bars);
         // tile A
         if (ok && next && t1 < n_a) {
-          if (t1 >= 2) ok = wait_bar(&bars.s_empty[0][t1 & 1], ((t1 >> 1) - 1) & 1, &bars);
+          if (!kTS && t1 >= 2) ok = wait_bar(&bars.s_empty[0][t1 & 1], ((t1 >> 1) - 1) & 1, &bars);
           if (ok) {
             sm100::tc_fence_after_sync();
             issue_s(0, t1);
@@ -232,7 +244,7 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         // tile B
         if (ok && act_b) {
           if (next) {
-            if (t1 >= 2) ok = wait_bar(&bars.s_empty[1][t1 & 1], ((t1 >> 1) - 1) & 1, &bars);
+            if (!kTS && t1 >= 2) ok = wait_bar(&bars.s_empty[1][t1 & 1], ((t1 >> 1) - 1) & 1, &bars);
             if (ok) {
               sm100::tc_fence_after_sync();
               issue_s(1, t1);
@@ -274,22 +286,26 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         sm100::tmem_ld32_issue(s_t + 32, sv + 32);
         sm100::tmem_ld_wait_all(sv);
         sm100::tmem_ld_wait_all(sv + 32);
-        sm100::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) sm100::mbar_arrive(&bars.s_empty[x][bf]);
+        if constexpr (!kTS) {       // with P in tensor memory the buffer is free only after the PV product (issue order)
+          sm100::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) sm100::mbar_arrive(&bars.s_empty[x][bf]);
+        }
 
         const int nvis = min(kBN, max(0, limit - t * kBN + 1));   // visible tokens of this tile for this row
-        float mx = -CUDART_INF_F;
-        if (nvis == kBN) {
+        if (nvis < kBN) {
 #pragma unroll
-          for (int j = 0; j < kBN; ++j) mx = fmaxf(mx, __uint_as_float(sv[j]));
-        } else {
-#pragma unroll
-          for (int j = 0; j < kBN; ++j) {
+          for (int j = 0; j < kBN; ++j)
             if (j >= nvis) sv[j] = 0xff800000u;       // -inf: selected, never computed with (the slot may hold NaN)
-            mx = fmaxf(mx, __uint_as_float(sv[j]));
-          }
         }
+        // four independent chains of three-input maxima: a serial chain over 64 values costs its latency 64 times
+        float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+        for (int j = 0; j < kBN; j += 8) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) mx4[c] = max3(mx4[c], __uint_as_float(sv[j + 2 * c]), __uint_as_float(sv[j + 2 * c + 1]));
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         const float m_new = mx * sc2;
         float factor = 1.f;
         if (m_new > m_used + kRescaleStep || m_used == -CUDART_INF_F) {
@@ -299,21 +315,22 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           }
         }
         const float m_sub = m_used == -CUDART_INF_F ? 0.f : m_used;
-        float sum = 0.f;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[kBN / 2];
 #pragma unroll
         for (int j = 0; j < kBN; j += 2) {
           const float p0 = sm100::ex2_approx(fmaf(__uint_as_float(sv[j]), sc2, -m_sub));
           const float p1 = sm100::ex2_approx(fmaf(__uint_as_float(sv[j + 1]), sc2, -m_sub));
-          sum += p0 + p1;
+          sum4[(j >> 1) & 3] += p0 + p1;
           pk[j >> 1] = pack2(p0, p1);
         }
-        l = l * factor + sum;
-        if (t > 0) {
-          // the previous PV product must have retired: it reads the P buffer and accumulates into O
+        l = l * factor + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        const bool rescale = __any_sync(0xffffffffu, factor != 1.f);
+        if (t > 0 && (!kTS || rescale)) {
+          // the previous PV product must have retired: it accumulates into O (and reads the shared-memory P buffer)
           ok = __all_sync(0xffffffffu, wait_bar(&bars.pv_done[x], (t - 1) & 1, &bars));
           if (!ok) break;
-          if (__any_sync(0xffffffffu, factor != 1.f)) {
+          if (rescale) {
             sm100::tc_fence_after_sync();
 #pragma unroll 1
             for (int c = 0; c < D; c += 32) {
@@ -328,14 +345,19 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             sm100::tc_fence_before_sync();
           }
         }
+        if constexpr (kTS) {
+          // P row as the tensor core's A operand: 32 columns of two bf16 each, over the start of the S buffer
+          sm100::tmem_st32(s_t, pk);
+        }
         // P row: 8 chunks of 8 tokens, 16-byte chunks XOR-swizzled by the row like a TMA-written tile
 #pragma unroll
-        for (int c = 0; c < kBN / 8; ++c) {
+        for (int c = 0; c < (kTS ? 0 : kBN / 8); ++c) {
           asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (((c ^ (row & 7))) << 4)), "r"(pk[c * 4]),
                        "r"(pk[c * 4 + 1]), "r"(pk[c * 4 + 2]), "r"(pk[c * 4 + 3])
                        : "memory");
         }
-        if ((x == 0 || t >= n_a) && t * kBN + kBN > kv_end) {
+        const bool v_tail = (x == 0 || t >= n_a) && t * kBN + kBN > kv_end;
+        if (v_tail) {
           // cache slots past the sequence end may hold anything: zero those V rows (probability 0 x NaN).
           // Tile A's PV product is issued before tile B's and both read this stage, so tile A's threads do it
           // on the tiles that tile A visits, tile B's on the rest.
@@ -347,7 +369,11 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(v_s + off), "r"(0u) : "memory");
           }
         }
-        sm100::fence_proxy_async_smem();   // this thread's P (and V) stores, for the tensor core's reads
+        if (!kTS || v_tail) sm100::fence_proxy_async_smem();   // this thread's P (and V) stores, for the tensor core's reads
+        if constexpr (kTS) {
+          sm100::tmem_st_wait();
+          sm100::tc_fence_before_sync();
+        }
         __syncwarp();
         if (lane == 0) sm100::mbar_arrive(&bars.p_full[x]);
       }
@@ -389,7 +415,7 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   }
 }
 
-template <int D>
+template <int D, bool kTS>
 static int launch(const XpPrefillAttnArgs& a, int G, cudaStream_t s) {
   CUtensorMap mq, mk, mv, mk3, mv3;
   const uint64_t tokens = static_cast<uint64_t>(a.num_pages) * a.page_size;
@@ -406,12 +432,12 @@ static int launch(const XpPrefillAttnArgs& a, int G, cudaStream_t s) {
   constexpr int kSmem = 2 * (D / 64) * kRows * 128 + kStages * 2 * (D / 64) * kBN * 128 + 2 * kRows * 128 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(prefill_attn_umma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
+    if (cudaFuncSetAttribute(prefill_attn_umma_kernel<D, kTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
       return -21;
     attr_set = true;
   }
-  dim3 grid((a.max_q_len + 2 * np - 1) / (2 * np), a.kv_heads, a.num_seqs);
-  prefill_attn_umma_kernel<D><<<grid, kThreads, kSmem, s>>>(mq, mk, mv, mk3, mv3, a, G, g_shift, box_tokens);
+  dim3 grid(a.kv_heads, a.num_seqs, (a.max_q_len + 2 * np - 1) / (2 * np));
+  prefill_attn_umma_kernel<D, kTS><<<grid, kThreads, kSmem, s>>>(mq, mk, mv, mk3, mv3, a, G, g_shift, box_tokens);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);
 }
@@ -430,7 +456,11 @@ extern "C" int xp_prefill_attn_umma(const XpPrefillAttnArgs* a, void* stream) {
                   (G == 1 || G == 2 || G == 4 || G == 8 || G == 16) && (reinterpret_cast<uintptr_t>(a->q) & 15) == 0 &&
                   (reinterpret_cast<uintptr_t>(a->out) & 15) == 0;
   if (!ok) return 1;
-  if (a->head_dim == 128) return launch<128>(*a, G, reinterpret_cast<cudaStream_t>(stream));
-  if (a->head_dim == 64) return launch<64>(*a, G, reinterpret_cast<cudaStream_t>(stream));
+  // P (the probabilities) reaches the second product through tensor memory; bit 8 of force_simple selects the
+  // form that stages P in shared memory instead
+  const bool ts = ((a->force_simple >> 8) & 1) != kDefaultTS;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (a->head_dim == 128) return ts ? launch<128, true>(*a, G, s) : launch<128, false>(*a, G, s);
+  if (a->head_dim == 64) return ts ? launch<64, true>(*a, G, s) : launch<64, false>(*a, G, s);
   return 1;
 }

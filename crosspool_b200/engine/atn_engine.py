@@ -24,6 +24,7 @@ from ..models.config import ModelConfig
 from ..models.weights import AttentionWeights
 from ..ops import attention as A
 from ..ops import gemm, norm
+from ..utils import nvtx
 from .kv_cache import OutOfPages, PagedKvCache
 
 MODE_PREFILL, MODE_DECODE = 1, 2
@@ -372,16 +373,28 @@ class AttentionEngine:
             self.stream.synchronize()
             gemm.check_status(self.device)
             if self.ecfg.use_cuda_graph:
-                from .. import native
-
                 for B in self._buckets:
-                    g = torch.cuda.CUDAGraph()
-                    before = native.launch_count()
-                    with torch.cuda.graph(g, stream=self.stream):
-                        self._decode_forward(B)
-                    self._graph_launches[B] = native.launch_count() - before
-                    self._graphs[B] = g
+                    self._capture_decode(B)
             self.stream.synchronize()
+
+    def _capture_decode(self, B: int) -> None:
+        """Captures the decode step of one row bucket (on ``self.stream``, which is current)."""
+        from .. import native
+
+        g = torch.cuda.CUDAGraph()
+        before = native.launch_count()
+        with torch.cuda.graph(g, stream=self.stream):
+            self._decode_forward(B)
+        self._graph_launches[B] = native.launch_count() - before
+        self._graphs[B] = g
+
+    def _replay_decode(self, B: int) -> None:
+        """One decode step of bucket ``B``: the captured graph, or the eager launches when graphs are off."""
+        g = self._graphs.get(B)
+        if g is not None:
+            g.replay()
+        else:
+            self._decode_forward(B)
 
     def _admit_prefill(self) -> tuple[list[tuple[Sequence, int]], int]:
         """Chooses the sequences (and token counts) of the next prefill chunk."""
@@ -567,11 +580,7 @@ class AttentionEngine:
         with torch.cuda.stream(self.stream):
             self.dec_meta.copy_(self.dec_meta_host, non_blocking=True)
             self._stage_sampling(batch)
-            g = self._graphs.get(B)
-            if g is not None:
-                g.replay()
-            else:
-                self._decode_forward(B)
+            self._replay_decode(B)
             self.tokens_host[:n].copy_(self.tokens[:n], non_blocking=True)
         self._inflight = (batch, n)
         self.stats["decode_steps"] += 1
@@ -633,11 +642,14 @@ class AttentionEngine:
             if chosen:
                 self._last_was_prefill = True
                 self._b_key = None
-                self._pending = self._step_prefill(chosen, rows)
+                with nvtx.range(f"{self.cfg.name} prefill {rows}"):
+                    self._pending = self._step_prefill(chosen, rows)
                 return
         self._last_was_prefill = False
-        if self.running and not self._decode_launch():
-            self._pending = []
+        if self.running:
+            with nvtx.range(f"{self.cfg.name} decode {len(self.running)}"):
+                if not self._decode_launch():
+                    self._pending = []
 
     def collect_step(self) -> list[tuple[Sequence, int]]:
         if self._pending is not None:

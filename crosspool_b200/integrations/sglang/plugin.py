@@ -24,13 +24,15 @@ _applied: list[Hook] = []
 
 def install(registry: Any = None, check_config: Callable[[], None] | None = None, environ=os.environ, *, config: Any = None,
             runtime_factory: Callable | None = None, context_state_factory: Callable | None = None,
-            hf_config_of: Callable | None = None) -> list[Hook]:
+            hf_config_of: Callable | None = None, graph_runners: dict[str, type] | None = None) -> list[Hook]:
     """Registers every hook of the integration with the engine's hook registry and returns them.
 
     ``registry`` must offer ``register(target, handler, kind)``; without one the engine's own registry is imported.
     ``config`` is the resolved deployment configuration and ``runtime_factory(binding, rank, profile, device)`` builds the
     worker's :class:`~crosspool_b200.runtime.instance.InstanceRankRuntime` (default: one that talks to the configured
-    daemon and binds the native transport); ``context_state_factory`` turns elastic KV on."""
+    daemon and binds the native transport); ``context_state_factory`` turns elastic KV on. ``graph_runners`` (forward
+    phase -> graph runner class; default: the engine's decode and prefill runners when importable) are observed when
+    ``debug.graph_observer.enable`` is set."""
     from .ecs_hooks import ElasticHooks
     from .lifecycle import LifecycleHooks
 
@@ -66,7 +68,32 @@ def install(registry: Any = None, check_config: Callable[[], None] | None = None
         _applied.append(h)
     verify_required_hooks_applied(registry, hooks)
     install.lifecycle = life
+    install.graph_observer = _install_graph_observer(config, graph_runners)
     return list(_applied)
+
+
+def _install_graph_observer(config: Any, runners: dict[str, type] | None):
+    if not getattr(config, "debug_graph_observer_enable", False):
+        return None
+    from . import devkit
+
+    if runners is None:
+        try:
+            from sglang.srt.model_executor.runner.decode_cuda_graph_runner import DecodeCudaGraphRunner  # type: ignore
+            from sglang.srt.model_executor.runner.prefill_cuda_graph_runner import PrefillCudaGraphRunner  # type: ignore
+
+            runners = {"decode": DecodeCudaGraphRunner, "prefill": PrefillCudaGraphRunner}
+        except Exception:
+            return None
+
+    def model_id_of(runner):
+        path = getattr(getattr(getattr(runner, "model_runner", None), "model_config", None), "model_path", None)
+        for m in getattr(config, "models", ()):
+            if path is not None and str(getattr(m, "path", "")) == str(path):
+                return m.id
+        return str(getattr(runner, "model_id", path or ""))
+
+    return devkit.install_from_config(config, runners, model_id_of)
 
 
 def default_runtime_factory(config: Any) -> Callable:

@@ -43,8 +43,9 @@ def decode_splits(batch: int, kv_heads: int, max_len: int) -> int:
 
 # Which prefill kernel runs when the caller does not say: "umma" (tcgen05 tensor cores, TMEM accumulators; shapes it
 # does not cover fall back to "mma"), "mma" (TMA-fed mma.sync kernel) or "simple" (plain mma.sync kernel).
+# "umma-alt" is the tcgen05 kernel with the other route for the probabilities (tensor memory <-> shared memory).
 # XPOOL_PREFILL_KERNEL selects one, e.g. to bisect a numerical difference.
-PREFILL_KERNELS = {"umma": 0, "simple": 1, "mma": 2, "umma-swapped-v": 0x100}
+PREFILL_KERNELS = {"umma": 0, "simple": 1, "mma": 2, "umma-alt": 0x100}
 PREFILL_KERNEL_DEFAULT = os.environ.get("XPOOL_PREFILL_KERNEL", "umma")
 
 

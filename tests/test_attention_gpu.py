@@ -97,7 +97,7 @@ def test_paged_decode(d, hq, hkv, splits, simt):
 
 
 @pytest.mark.parametrize("d,hq,hkv", [(128, 16, 8), (64, 4, 2), (128, 32, 4), (128, 8, 8), (64, 8, 2)])
-@pytest.mark.parametrize("simple,page", [(False, 16), (False, 64), (True, 16), ("mma", 16), ("mma", 64)])
+@pytest.mark.parametrize("simple,page", [(False, 16), (False, 64), ("umma-alt", 16), ("umma-alt", 64), (True, 16), ("mma", 16), ("mma", 64)])
 def test_paged_prefill_chunked_causal(d, hq, hkv, simple, page):
     from crosspool_b200.ops import attention as A
     from crosspool_b200.ops import gemm

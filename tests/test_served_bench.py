@@ -66,7 +66,7 @@ def _args(**kw):
 
 
 def test_mixes_place_every_instance_and_plan_deterministically():
-    for mix, world in (("b", 1), ("b", 2), ("c", 4), ("e", 8), ("b", 8), ("d", 8), ("d", 4)):
+    for mix, world in (("b", 1), ("b", 2), ("c", 2), ("c", 4), ("e", 8), ("b", 8), ("d", 8), ("d", 4)):
         streams, info = served.build_mix(mix, world, 1.0)
         assert info["name"] == mix
         atn = {s.atn_rank for s in streams}
