@@ -171,10 +171,28 @@ class AttentionEngine:
     def _capacity_tick(self) -> None:
         rec = self.capacity
         rec.poll()
-        if rec.bundles_to_vacate() > 0 and not rec.retirable_empty() and self.running and self._inflight is None:
-            self._retract(self.running[-1])  # newest first: the least work is lost
-            self.stats["retracted_for_shrink"] = self.stats.get("retracted_for_shrink", 0) + 1
-            rec.poll()
+        if rec.bundles_to_vacate() > 0 and not rec.retirable_empty() and self._inflight is None:
+            if self._vacate_by_eviction(rec):        # cached prefixes go before running work does
+                rec.poll()
+            elif self.running:
+                self._retract(self.running[-1])  # newest first: the least work is lost
+                self.stats["retracted_for_shrink"] = self.stats.get("retracted_for_shrink", 0) + 1
+                rec.poll()
+
+    def _vacate_by_eviction(self, rec) -> bool:
+        """Empties one memory bundle by evicting cached prefix pages, if some bundle above the floor holds nothing but
+        unpinned cached pages. Returns whether a bundle became empty."""
+        if self.prefix is None or len(self.prefix) == 0:
+            return False
+        alloc = self.kv.allocator
+        cands = [b for b in alloc.mapped_bundles() if b >= rec.floor_bundles and alloc.used_in_bundle(b) > 0]
+        for b in sorted(cands, key=lambda b: (alloc.used_in_bundle(b), -b)):
+            pages = alloc.bundle_pages(b)
+            if self.prefix.evictable_among(pages) == alloc.used_in_bundle(b):
+                alloc.free(self.prefix.evict_pages(pages))
+                self.stats["evicted_for_shrink"] = self.stats.get("evicted_for_shrink", 0) + 1
+                return True
+        return False
 
     def idle_tick(self) -> None:
         """Serves capacity commands while there is nothing to run: an idle Instance is the usual donor of a

@@ -62,6 +62,9 @@ class PageAllocator:
     def mapped_bundles(self) -> list[int]:
         return [b for b in range(self.num_bundles) if self._mapped[b]]
 
+    def used_in_bundle(self, b: int) -> int:
+        return self._used_in_bundle[b]
+
     def unmapped_bundles(self) -> list[int]:
         return [b for b in range(self.num_bundles) if not self._mapped[b]]
 

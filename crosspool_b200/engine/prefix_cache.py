@@ -32,6 +32,7 @@ class PrefixCache:
         self._clock = itertools.count(1)
         self._by_page: dict[int, _Node] = {}
         self.hits = self.lookups = self.hit_tokens = 0
+        self.evicted_for_retirement = 0
 
     def __len__(self) -> int:
         return len(self._by_page)
@@ -104,5 +105,31 @@ class PrefixCache:
                 out.append(n.page)
         return out
 
+    def evictable_among(self, pages) -> int:
+        """How many of ``pages`` are cached and unpinned (a pin on a page pins its whole path, so an unpinned cached
+        page has no pinned descendant)."""
+        return sum(1 for p in pages if (n := self._by_page.get(p)) is not None and n.refs == 0)
+
+    def evict_pages(self, pages) -> list[int]:
+        """Evicts the unpinned cached pages among ``pages`` together with everything cached behind them (a prefix
+        without its head is unreachable). Used to vacate the pages of a memory bundle that is about to be retired:
+        the reference couples its radix tree to bundle retirement the same way (src/xpool/integrations/sglang/ecs/
+        state.py:470-541, ecs/radix.py). Returns every page freed, in or outside ``pages``."""
+        out: list[int] = []
+        for p in list(pages):
+            n = self._by_page.get(p)
+            if n is None or n.refs != 0:
+                continue
+            del n.parent.children[n.key]
+            stack = [n]
+            while stack:
+                cur = stack.pop()
+                stack.extend(cur.children.values())
+                del self._by_page[cur.page]
+                out.append(cur.page)
+        self.evicted_for_retirement += len(out)
+        return out
+
     def stats(self) -> dict:
-        return {"pages": len(self), "lookups": self.lookups, "hits": self.hits, "hit_tokens": self.hit_tokens}
+        return {"pages": len(self), "lookups": self.lookups, "hits": self.hits, "hit_tokens": self.hit_tokens,
+                "evicted_for_retirement": self.evicted_for_retirement}

@@ -32,3 +32,69 @@ def test_identical_prompts_prefilled_concurrently_keep_their_own_pages():
     assert c.insert(t, [30, 31, 32]) == []            # same tokens, other pages: stay private
     assert c.insert([1, 2, 9, 9, 9], [10, 40, 41]) == [40]   # shares page 10, adds its own second page
     assert len(c) == 3
+
+
+def test_evicting_the_cached_pages_of_a_bundle_takes_their_subtrees_and_spares_pinned_paths():
+    pc = PrefixCache(2)
+    a = [1, 2, 3, 4, 5, 6, 0]
+    assert pc.insert(a, [10, 11, 12]) == [10, 11, 12]
+    pc.release([10, 11, 12])
+    b = [1, 2, 9, 9, 8, 8, 0]
+    assert pc.insert(b, [10, 20, 21]) == [20, 21]     # shares page 10, branches behind it
+    pc.release([10, 20, 21])
+    pinned = pc.match(b)                              # pins 10, 20, 21
+    assert pinned == [10, 20, 21]
+    assert pc.evictable_among(range(10, 13)) == 2     # 11 and 12; 10 is on a pinned path
+    freed = pc.evict_pages([11])                      # evicting 11 takes 12 (cached behind it) too
+    assert sorted(freed) == [11, 12] and not pc.owns(12) and pc.owns(10)
+    assert pc.evict_pages([10, 20]) == []             # pinned: nothing happens
+    pc.release(pinned)
+    assert sorted(pc.evict_pages([10])) == [10, 20, 21] and len(pc) == 0
+    assert pc.stats()["evicted_for_retirement"] == 5
+
+
+def test_engine_vacates_a_bundle_by_eviction_before_it_retracts_running_work():
+    """A pending shrink with no empty bundle: a bundle holding only unpinned cached pages is emptied by eviction; a
+    bundle with a running sequence's page is not touched, and the engine then falls back to retraction."""
+    from collections import deque
+
+    from crosspool_b200.engine.atn_engine import AttentionEngine
+    from crosspool_b200.engine.kv_cache import PageAllocator
+
+    class Rec:
+        floor_bundles = 1
+
+        def __init__(self, alloc):
+            self.alloc, self.polls, self.target = alloc, 0, 2
+
+        def poll(self):
+            self.polls += 1
+
+        def bundles_to_vacate(self):
+            return max(0, len(self.alloc.mapped_bundles()) - self.target)
+
+        def retirable_empty(self):
+            return [b for b in self.alloc.empty_bundles() if b >= self.floor_bundles]
+
+    alloc = PageAllocator(12, pages_per_bundle=4)     # bundles 0, 1, 2
+    first = alloc.alloc(4)                            # bundle 0 (fullest-first fill)
+    cached = alloc.alloc(3)                           # bundle 1
+    running_page = alloc.alloc(1)                     # bundle 1's last page
+    more = alloc.alloc(2)                             # bundle 2
+    assert {p // 4 for p in cached} == {1} and {p // 4 for p in more} == {2}
+    pc = PrefixCache(2)
+    pc.insert([1, 2, 3, 4, 0], more)                  # bundle 2 holds cached pages only
+    pc.release(more)
+    eng = AttentionEngine.__new__(AttentionEngine)
+    eng.prefix, eng.stats, eng._inflight, eng.running, eng.waiting = pc, {}, None, [], deque()
+    eng.kv = type("Kv", (), {"allocator": alloc})()
+    eng.capacity = rec = Rec(alloc)
+    eng._capacity_tick()
+    assert alloc.used_in_bundle(2) == 0 and rec.retirable_empty() == [2] and eng.stats["evicted_for_shrink"] == 1
+    assert rec.polls == 2 and len(pc) == 0
+    # nothing evictable is left: with no running sequence the tick does nothing more
+    alloc.begin_retirement(2)
+    rec.target = 1
+    eng._capacity_tick()
+    assert eng.stats["evicted_for_shrink"] == 1 and alloc.used_in_bundle(1) == 4
+    del first, running_page
