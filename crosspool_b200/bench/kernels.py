@@ -156,6 +156,73 @@ def bench_norm(ns, timer: Timer) -> dict:
     return report("add_rmsnorm", us, 4 * h.numel() * 2, 0.0, {"rows": ns.rows, "hidden": ns.hidden})
 
 
+def bench_norm_publish(ns, timer: Timer) -> dict:
+    """The transport producer on one GPU: fold ``parts`` partials and the residual, RMSNorm, store the rows into
+    ``dests`` destination buffers (local memory standing in for the FFN ranks' slots) and release their sequence words."""
+    from ..ops import norm
+
+    rows, hidden = ns.rows, ns.hidden
+    h = torch.randn(rows, hidden, device="cuda").bfloat16()
+    parts = [torch.randn(rows, hidden, device="cuda").bfloat16() for _ in range(ns.parts)]
+    w = torch.ones(hidden, device="cuda").bfloat16()
+    out = torch.empty_like(h)
+    dst = [torch.zeros(rows, hidden, device="cuda", dtype=torch.bfloat16) for _ in range(ns.dests)]
+    flags = torch.zeros(ns.dests, 8, device="cuda", dtype=torch.int32)
+    meta = torch.zeros(ns.dests, 4, device="cuda", dtype=torch.int32)
+    seq = [0]
+
+    def run():
+        seq[0] += 1
+        norm.add_rmsnorm(parts, w, 1e-6, resid=h, out=out, peer_ptrs=[d.data_ptr() for d in dst],
+                         peer_flag_ptrs=[flags[i].data_ptr() for i in range(ns.dests)],
+                         peer_meta_ptrs=[meta[i].data_ptr() for i in range(ns.dests)], publish_seq=seq[0], meta=(0, 2, 0))
+
+    us = timer(run)
+    byts = (ns.parts + 2 + 1 + ns.dests) * h.numel() * 2     # partials + residual read/write + normed output + pushes
+    return report("norm_publish", us, byts, 0.0, {"rows": rows, "hidden": hidden, "parts": ns.parts, "dests": ns.dests})
+
+
+def bench_lane(ns, timer: Timer) -> dict:
+    """One Executor-Lane iteration of a dense layer on one GPU: the invocation is published before the iteration is
+    enqueued (nothing waits for another launch), then lane_wait, gate/up + SwiGLU, down, lane_complete run from the
+    descriptor table. Weight bytes are the roofline at decode sizes, FLOPs at prefill sizes."""
+    from ..models import config as mc
+    from ..parallel import fabric as F
+
+    cfg = mc.preset(ns.model).with_layers(ns.layers)
+    ffn = F.FfnRankRuntime("cuda", n_lanes=1, tile_weights=bool(ns.tiled))
+    cap = max(128, ns.rows)
+    place = F.InstancePlacement("m0", cfg, seed=1, atn_rank=0, ffn_ranks=(1,), capacity_rows=cap)
+    st = ffn.add_instance(place, 0)
+    buf = F.PeerBuffer(F.atn_slot_layout(place).total_bytes)
+    st.atn_base = buf.ptr
+    ffn.install()
+    try:
+        flay = F.ffn_slot_layout(place)
+        x = (torch.randn(ns.rows, cfg.hidden_size, device="cuda") * 0.5).bfloat16()
+        st.slot.tensor(flay.input_offset, (cap, cfg.hidden_size), torch.bfloat16, "cuda")[:ns.rows] = x
+        rec = st.slot.tensor(flay.record_offset, (64,), torch.int32, "cuda")
+        host = torch.zeros(64, dtype=torch.int32).pin_memory()
+        seq = [0]
+
+        def run():
+            seq[0] += 1
+            host[0], host[1], host[2], host[3], host[8] = ns.rows, (seq[0] - 1) % ns.layers, 2, 0, seq[0]
+            rec.copy_(host, non_blocking=True)        # the invocation record, as the attention side would publish it
+            ffn.launch_once(0, lease_ms=50)
+
+        us = timer(run)
+        stats = ffn.stats()
+        if stats["status"] != 0 or stats["served"][0] != seq[0]:
+            raise RuntimeError(f"lane iteration failed: {stats}")
+    finally:
+        ffn.close()
+    inter = cfg.intermediate_size
+    byts = 3 * cfg.hidden_size * inter * 2 + 2 * ns.rows * cfg.hidden_size * 2
+    return report(f"lane_iteration({ns.model})", us, byts, 6.0 * ns.rows * cfg.hidden_size * inter,
+                  {"rows": ns.rows, "note": "includes one 256-byte host-to-device copy of the invocation record"})
+
+
 def bench_moe(ns, timer: Timer) -> dict:
     from ..models.config import PRESETS
     from ..models.weights import random_ffn_layer
@@ -342,6 +409,16 @@ def main(argv: list[str] | None = None) -> int:
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=256)
     n.add_argument("--hidden", type=int, default=1024)
+    npub = sub.add_parser("norm-publish")
+    npub.add_argument("--rows", type=int, default=4096)
+    npub.add_argument("--hidden", type=int, default=4096)
+    npub.add_argument("--parts", type=int, default=2)
+    npub.add_argument("--dests", type=int, default=2)
+    ln = sub.add_parser("lane")
+    ln.add_argument("--model", default="Qwen/Qwen3-8B")
+    ln.add_argument("--rows", type=int, default=64)
+    ln.add_argument("--layers", type=int, default=4)
+    ln.add_argument("--tiled", type=int, default=0)
     m = sub.add_parser("moe")
     m.add_argument("--rows", type=int, default=64)
     ps = sub.add_parser("prefill-step")
@@ -361,7 +438,7 @@ def main(argv: list[str] | None = None) -> int:
     timer = Timer(ns.iters, ns.warmup, not ns.no_flush)
     {"gemm": bench_gemm, "decode-attn": bench_decode_attn, "norm": bench_norm, "moe": bench_moe,
      "decode-step": bench_decode_step, "prefill-attn": bench_prefill_attn, "kv-vmm": bench_kv_vmm,
-     "prefill-step": bench_prefill_step}[ns.case](ns, timer)
+     "prefill-step": bench_prefill_step, "norm-publish": bench_norm_publish, "lane": bench_lane}[ns.case](ns, timer)
     return 0
 
 

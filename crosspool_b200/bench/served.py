@@ -77,6 +77,7 @@ class ModelStream:
     alt_output: LengthSpec | None = None
     swap_phase: int = 0                 # 0: starts with the primary shape, 1: starts with the alternate
     weights_key: str | None = None      # Instances with the same key share one copy of the FFN weights per FFN rank
+    preload_tokens: int = 0             # cap on the prompt tokens of the time-0 backlog (0: no cap)
 
 
 def _uniform(lo, hi):
@@ -122,14 +123,16 @@ def _build_mix(name: str, world: int, scale: float) -> tuple[list[ModelStream], 
         long_p, long_o = _lognormal(8192, 256, 32768), _uniform(256, 256)
         short_p, short_o = _uniform(256, 256), _uniform(128, 128)
         out = []
+        # 4 req/s of long-context and 32 req/s of short-context traffic for the whole deployment: every attention GPU
+        # (each hosts its own pair of Instances) receives an equal share of both
+        r_long, r_short = 4.0 * scale / n_atn, 32.0 * scale / n_atn
         for a in range(n_atn):
-            common = dict(max_seq_len=32768 + 256 + PAGE, prefill_chunk=4096, elastic=True)
-            out.append(ModelStream(f"Qwen/Qwen3-8B#{a}", "Qwen/Qwen3-8B", 10 + a, a, (f0, f1) if f1 != f0 else (f0,), 4.0 * scale, long_p, long_o,
-                                   max_batch=128, kv_tokens=512 * 1024, alt_rate=32.0 * scale, alt_prompt=short_p,
-                                   alt_output=short_o, swap_phase=0, **common))
-            out.append(ModelStream(f"Qwen/Qwen3-0.6B#{a}", "Qwen/Qwen3-0.6B", 20 + a, a, (f0 if a % 2 == 0 else f1,),
-                                   4.0 * scale, long_p, long_o, max_batch=128, kv_tokens=512 * 1024,
-                                   alt_rate=32.0 * scale, alt_prompt=short_p, alt_output=short_o, swap_phase=1, **common))
+            common = dict(max_seq_len=32768 + 256 + PAGE, prefill_chunk=4096, elastic=True, alt_rate=r_short, alt_prompt=short_p,
+                          alt_output=short_o, max_batch=128, kv_tokens=512 * 1024)
+            out.append(ModelStream(f"Qwen/Qwen3-8B#{a}", "Qwen/Qwen3-8B", 10 + a, a, (f0, f1) if f1 != f0 else (f0,), r_long,
+                                   long_p, long_o, swap_phase=0, preload_tokens=24 * 1024, **common))
+            out.append(ModelStream(f"Qwen/Qwen3-0.6B#{a}", "Qwen/Qwen3-0.6B", 20 + a, a, (f0 if a % 2 == 0 else f1,), r_long,
+                                   long_p, long_o, swap_phase=1, preload_tokens=96 * 1024, **common))
         return out, {"name": "c", "layout": f"atn{n_atn} (8B + 0.6B each, elastic KV) + ffn2 (8B TP2)",
                      "slo": {"ttft_ms": SLO_TTFT_MS, "tpot_ms": SLO_TPOT_MS}}
     if name == "d":
@@ -142,7 +145,7 @@ def _build_mix(name: str, world: int, scale: float) -> tuple[list[ModelStream], 
         ffn = tuple(range(n_atn, world))
         out = [ModelStream(f"Qwen/Qwen3-30B-A3B#dp{a}", "Qwen/Qwen3-30B-A3B", 40, a, ffn, 6.0 * scale, _uniform(512, 4096),
                            _uniform(256, 1024), max_batch=256, max_seq_len=4096 + 1024 + PAGE, kv_tokens=768 * 1024,
-                           weights_key="Qwen/Qwen3-30B-A3B") for a in range(n_atn)]
+                           weights_key="Qwen/Qwen3-30B-A3B", preload_tokens=64 * 1024) for a in range(n_atn)]
         return out, {"name": "d", "layout": f"attention DP{n_atn} + experts EP{n_atn} (128 experts, top-8)",
                      "slo": {"ttft_ms": SLO_TTFT_MS, "tpot_ms": SLO_TPOT_MS}}
     if name == "e":
@@ -154,10 +157,13 @@ def _build_mix(name: str, world: int, scale: float) -> tuple[list[ModelStream], 
         common = dict(prompt=p, output=o, max_seq_len=8192 + 1024 + PAGE, elastic=True, burst=(4.0, 0.0, 0.0))
         r = 2.0 * scale
         out = [
-            ModelStream("Qwen/Qwen3-32B#0", "Qwen/Qwen3-32B", 30, 0, (2, 3, 4, 5), r, max_batch=192, kv_tokens=320 * 1024, **common),
-            ModelStream("Qwen/Qwen3-1.7B#0", "Qwen/Qwen3-1.7B", 31, 0, (6,), 4 * r, max_batch=256, kv_tokens=448 * 1024, **common),
-            ModelStream("Qwen/Qwen3-8B#0", "Qwen/Qwen3-8B", 32, 1, (6, 7), 2 * r, max_batch=256, kv_tokens=448 * 1024, **common),
-            ModelStream("Qwen/Qwen3-1.7B#1", "Qwen/Qwen3-1.7B", 33, 1, (7,), 4 * r, max_batch=256, kv_tokens=448 * 1024, **common),
+            ModelStream("Qwen/Qwen3-32B#0", "Qwen/Qwen3-32B", 30, 0, (2, 3, 4, 5), r, max_batch=192, kv_tokens=320 * 1024, preload_tokens=16 * 1024, **common),
+            ModelStream("Qwen/Qwen3-1.7B#0", "Qwen/Qwen3-1.7B", 31, 0, (6,), 4 * r, max_batch=256, kv_tokens=448 * 1024,
+                        preload_tokens=96 * 1024, **common),
+            ModelStream("Qwen/Qwen3-8B#0", "Qwen/Qwen3-8B", 32, 1, (6, 7), 2 * r, max_batch=256, kv_tokens=448 * 1024,
+                        preload_tokens=32 * 1024, **common),
+            ModelStream("Qwen/Qwen3-1.7B#1", "Qwen/Qwen3-1.7B", 33, 1, (7,), 4 * r, max_batch=256, kv_tokens=448 * 1024,
+                        preload_tokens=96 * 1024, **common),
         ]
         return out, {"name": "e", "layout": "atn2 (32B + 1.7B | 8B + 1.7B, elastic KV) + ffn6 (32B TP4, 8B TP2, 1.7B x2)",
                      "burst": "4x for a quarter of every window", "slo": {"ttft_ms": SLO_TTFT_MS, "tpot_ms": SLO_TPOT_MS}}
@@ -184,9 +190,12 @@ def preload_requests(s: ModelStream, seed: int, tpot_estimate_s: float = 0.02, f
     rng = derive_rng(seed, s.model_id, "preload")
     vocab = mc.load(s.preset).vocab_size
     n = min(s.max_batch, int(fraction * s.rate * _mean(s.output) * tpot_estimate_s))
-    out = []
+    out, tokens = [], 0
     for _ in range(n):
         n_in = s.prompt.sample(rng)
+        if s.preload_tokens and tokens + n_in > s.preload_tokens:
+            break       # a backlog that takes longer to prefill than the warm-up lasts would delay the measured arrivals
+        tokens += n_in
         n_out = max(1, int(s.output.sample(rng) * rng.uniform(0.05, 1.0)))
         out.append(PlannedRequest(s.model_id, 0.0, [rng.randrange(vocab) for _ in range(n_in)], n_out, warmup=True))
     return out
@@ -419,10 +428,12 @@ def result_json(args, world: int, impl: str, mix_info: dict, streams: list[Model
             "per_model": agg["per_model"], "workload_digest": digest,
             "l2": "weights and KV streamed per engine iteration exceed the 126 MB L2 (no flush needed)"}
     cfgd.update(extra or {})
+    base = recorded_baseline(mix_info["name"], world, args) if impl == "xpool" else None
+    vs = round(w["tok_per_s"] / base["value"], 4) if base and base.get("value") else None
     return {
         "metric": METRIC, "impl": impl, "value": w["tok_per_s"], "unit": "tok/s", "n_gpus": world, "steps": K,
         "warmup": args.warmup, "ms_per_step": w["dev_ms"] / K, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16",
+        "vs_baseline": vs, "baseline_arm": base, "dtype": "bf16",
         "data": "synthetic: uniform random token ids, Poisson arrivals, lengths as listed under config.seq_len, random-init weights",
         "config": cfgd, "clocks": clocks,
         "e2e": {"value": e2e_med, "unit": "tok/s", "h2d_bytes_per_step": w["h2d"] // K, "d2h_bytes_per_step": w["d2h"] // K,
@@ -432,6 +443,22 @@ def result_json(args, world: int, impl: str, mix_info: dict, streams: list[Model
         "gpu_launches": w["launches"],
         "valid": bool(lat["slo_met"]) and args.layers == 0 and (extra or {}).get("correctness", {}).get("ok", True),
     }
+
+
+def recorded_baseline(mix: str, world: int, args) -> dict | None:
+    """The library-collective arm's (``--impl baseline``) measurement of the same mix, GPU count and offered load, as
+    recorded in ``baseline_arm.json`` beside this file (value, latencies, whether it met the SLO, the command). The
+    reference publishes no figure and does not build on this image, so this arm is the comparison the bench can print;
+    a changed rate, batch limit or layer count has no recorded counterpart (None)."""
+    if getattr(args, "rate_scale", 1.0) != 1.0 or getattr(args, "max_batch", 0) or getattr(args, "kv_tokens", 0) or args.layers:
+        return None
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline_arm.json")
+    try:
+        with open(path, encoding="utf-8") as f:
+            table = json.load(f)
+    except (OSError, ValueError):
+        return None
+    return table.get(f"{mix}@{world}")
 
 
 # ------------------------------------------------------------------------------------------- engine sizing

@@ -287,8 +287,10 @@ typedef struct XpPrefillAttnArgs {
   float scale;
   int num_pages;              /* pages in the cache (bound of the tensor maps); 0: simple kernel only */
   int force_simple;           /* kernel choice: 0 tcgen05 kernel (falls back when the shape is outside it),
-                                 1 plain mma.sync kernel, 2 TMA-fed mma.sync kernel */
-  uint32_t* status;           /* optional: set non-zero when a bounded wait ran out */
+                                 1 plain mma.sync kernel, 2 TMA-fed mma.sync kernel; bit 8: the tcgen05 kernel stages
+                                 the probabilities in shared memory instead of tensor memory */
+  uint32_t* status;           /* optional, FOUR words: [0] set non-zero when a bounded wait ran out (7: tcgen05 kernel),
+                                 [1..3] detail of the first such CTA (wait site, block, tiles) */
   int total_q;                /* rows of q / out (bound of the query tensor map); 0: no tcgen05 kernel */
 } XpPrefillAttnArgs;
 

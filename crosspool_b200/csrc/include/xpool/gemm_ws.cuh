@@ -466,7 +466,15 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
   const int f = c.m0 + lane_in_tile;
   const int fb = c.w_row0 + lane_in_tile;
   // all lanes agree on the outcome so that the aligned TMEM loads below stay convergent
-  if (!__all_sync(0xffffffffu, sm100::mbar_wait(&bar->acc_full[st.acc], st.acc_phase, deadline))) return false;
+  bool acc_ok = __all_sync(0xffffffffu, sm100::mbar_wait(&bar->acc_full[st.acc], st.acc_phase, deadline));
+  if (p.splits > 1) {
+    // Split-K tiles meet at named barriers further down: the four warps agree on the verdict first, so that a wait
+    // that ran out in one warp cannot leave the others blocked at a barrier it never reaches.
+    if (!acc_ok) *reinterpret_cast<volatile uint32_t*>(&bar->abort_flag) = 1u;
+    epi_bar_sync();
+    acc_ok = *reinterpret_cast<volatile uint32_t*>(&bar->abort_flag) == 0u;
+  }
+  if (!acc_ok) return false;
   sm100::tc_fence_after_sync();
 
   float g[16], u[16];

@@ -37,7 +37,7 @@ constexpr int kBN = 64;          // cached tokens per K/V tile
 constexpr int kStages = 3;
 constexpr int kThreads = 320;
 constexpr float kRescaleStep = 8.0f;   // log2 units
-constexpr int kDefaultTS = 0;          // 1: P through tensor memory unless bit 8 of force_simple asks for shared memory
+constexpr int kDefaultTS = 1;          // P through tensor memory unless bit 8 of force_simple asks for shared memory
 
 struct __align__(8) Bars {
   uint64_t q_full;
@@ -52,14 +52,16 @@ struct __align__(8) Bars {
 };
 
 // Bounded wait that also gives up when another role of the CTA has aborted.
-__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, Bars* b) {
+// `site` (1..255) names the wait in the status detail word when it is the one that runs out.
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, Bars* b, uint32_t site) {
   if (sm100::mbar_try_wait(bar, parity)) return true;
   const uint64_t deadline = sm100::global_timer_ns() + sm100::kPipelineWaitNs;
   uint32_t spins = 0;
   while (!sm100::mbar_try_wait(bar, parity)) {
     if ((++spins & 0xffu) == 0) {
-      if (b->abort_flag != 0 || sm100::global_timer_ns() > deadline) {
-        b->abort_flag = 1;
+      if (b->abort_flag != 0) return false;
+      if (sm100::global_timer_ns() > deadline) {
+        b->abort_flag = site;
         return false;
       }
     }
@@ -163,7 +165,7 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     const int box_bytes = box_tokens * 128;        // one 64-dim block of a box
     for (int t = 0; t < n_tiles; ++t) {
       const int s = t % kStages;
-      if (t >= kStages && !__all_sync(0xffffffffu, wait_bar(&bars.kv_empty[s], ((t / kStages) - 1) & 1, &bars))) break;
+      if (t >= kStages && !__all_sync(0xffffffffu, wait_bar(&bars.kv_empty[s], ((t / kStages) - 1) & 1, &bars, 1))) break;
       if (lane == 0) sm100::mbar_arrive_expect_tx(&bars.kv_full[s], kStage);
       __syncwarp();
       if (boxes == 1) {
@@ -216,7 +218,7 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         }
         sm100::umma_commit(&bars.pv_done[x]);
       };
-      bool ok = wait_bar(&bars.q_full, 0, &bars) && wait_bar(&bars.kv_full[0], 0, &bars);
+      bool ok = wait_bar(&bars.q_full, 0, &bars, 2) && wait_bar(&bars.kv_full[0], 0, &bars, 3);
       if (ok) {
         sm100::tc_fence_after_sync();
         issue_s(0, 0);
@@ -225,17 +227,17 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       for (int t = 0; ok && t < n_tiles; ++t) {
         const int t1 = t + 1;
         const bool next = t1 < n_tiles;
-        if (next) ok = wait_bar(&bars.kv_full[t1 % kStages], (t1 / kStages) & 1, &bars);
+        if (next) ok = wait_bar(&bars.kv_full[t1 % kStages], (t1 / kStages) & 1, &bars, 4);
         // tile A
         if (ok && next && t1 < n_a) {
-          if (!kTS && t1 >= 2) ok = wait_bar(&bars.s_empty[0][t1 & 1], ((t1 >> 1) - 1) & 1, &bars);
+          if (!kTS && t1 >= 2) ok = wait_bar(&bars.s_empty[0][t1 & 1], ((t1 >> 1) - 1) & 1, &bars, 5);
           if (ok) {
             sm100::tc_fence_after_sync();
             issue_s(0, t1);
           }
         }
         if (ok && t < n_a) {
-          ok = wait_bar(&bars.p_full[0], t & 1, &bars);
+          ok = wait_bar(&bars.p_full[0], t & 1, &bars, 6);
           if (ok) {
             sm100::tc_fence_after_sync();
             issue_pv(0, t);
@@ -244,13 +246,13 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         // tile B
         if (ok && act_b) {
           if (next) {
-            if (!kTS && t1 >= 2) ok = wait_bar(&bars.s_empty[1][t1 & 1], ((t1 >> 1) - 1) & 1, &bars);
+            if (!kTS && t1 >= 2) ok = wait_bar(&bars.s_empty[1][t1 & 1], ((t1 >> 1) - 1) & 1, &bars, 7);
             if (ok) {
               sm100::tc_fence_after_sync();
               issue_s(1, t1);
             }
           }
-          if (ok) ok = wait_bar(&bars.p_full[1], t & 1, &bars);
+          if (ok) ok = wait_bar(&bars.p_full[1], t & 1, &bars, 8);
           if (ok) {
             sm100::tc_fence_after_sync();
             issue_pv(1, t);
@@ -277,7 +279,7 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     if (tile_on) {
       for (int t = 0; t < my_tiles; ++t) {
         const int bf = t & 1;
-        ok = __all_sync(0xffffffffu, wait_bar(&bars.s_full[x][bf], (t >> 1) & 1, &bars));
+        ok = __all_sync(0xffffffffu, wait_bar(&bars.s_full[x][bf], (t >> 1) & 1, &bars, 9));
         if (!ok) break;
         sm100::tc_fence_after_sync();
         uint32_t sv[kBN];
@@ -328,7 +330,7 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         const bool rescale = __any_sync(0xffffffffu, factor != 1.f);
         if (t > 0 && (!kTS || rescale)) {
           // the previous PV product must have retired: it accumulates into O (and reads the shared-memory P buffer)
-          ok = __all_sync(0xffffffffu, wait_bar(&bars.pv_done[x], (t - 1) & 1, &bars));
+          ok = __all_sync(0xffffffffu, wait_bar(&bars.pv_done[x], (t - 1) & 1, &bars, 10));
           if (!ok) break;
           if (rescale) {
             sm100::tc_fence_after_sync();
@@ -373,11 +375,18 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         if constexpr (kTS) {
           sm100::tmem_st_wait();
           sm100::tc_fence_before_sync();
+          // Every phase of pv_done is consumed in order, also when no rescale needed it: a parity wait tells phase
+          // t - 1 from phase t + 1 only if none is skipped. PV(t-1) was issued a whole tile ago, so this returns at
+          // once; it must come before the arrive below, after which PV(t) may complete and flip the parity again.
+          if (t > 0 && !rescale) {
+            ok = __all_sync(0xffffffffu, wait_bar(&bars.pv_done[x], (t - 1) & 1, &bars, 12));
+            if (!ok) break;
+          }
         }
         __syncwarp();
         if (lane == 0) sm100::mbar_arrive(&bars.p_full[x]);
       }
-      if (ok && my_tiles > 0) ok = __all_sync(0xffffffffu, wait_bar(&bars.pv_done[x], (my_tiles - 1) & 1, &bars));
+      if (ok && my_tiles > 0) ok = __all_sync(0xffffffffu, wait_bar(&bars.pv_done[x], (my_tiles - 1) & 1, &bars, 11));
       if (ok) {
         sm100::tc_fence_after_sync();
         const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -406,7 +415,12 @@ prefill_attn_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   sm100::tc_fence_before_sync();
   __syncthreads();
   if (bars.abort_flag != 0) {
-    if (threadIdx.x == 0 && a.status != nullptr) atomicCAS(a.status, 0u, 7u);
+    if (threadIdx.x == 0 && a.status != nullptr && atomicCAS(a.status, 0u, 7u) == 0u) {
+      // detail words of the first CTA that gave up: the wait that ran out, and where the CTA was
+      a.status[1] = bars.abort_flag;
+      a.status[2] = (blockIdx.z << 20) | (blockIdx.y << 8) | blockIdx.x;
+      a.status[3] = static_cast<uint32_t>(n_tiles);
+    }
     __nanosleep(1000000);   // copies still in flight get a bounded chance to land before the CTA retires
   }
   if (warp == 9) {

@@ -61,10 +61,13 @@ def scratch(device: torch.device) -> _Scratch:
 def check_status(device: torch.device) -> None:
     """Raises if a kernel recorded a bounded-wait timeout since the last check (synchronises)."""
     s = scratch(device)
-    code = int(s.status[0].item())
+    words = s.status.tolist()
+    code = words[0]
     if code != 0:
         s.status.zero_()
-        raise RuntimeError(f"xpool kernel reported device status {code}")
+        s.counters.zero_()     # a split-K call that gave up leaves tile counters behind: later calls must not fold stale partials
+        detail = f" (detail {words[1]}, {words[2]:#x}, {words[3]})" if any(words[1:]) else ""
+        raise RuntimeError(f"xpool kernel reported device status {code}{detail}")
 
 
 class TiledWeight:

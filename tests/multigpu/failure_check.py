@@ -19,6 +19,48 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.abspath(os.path.join(os.path.dirname(__file__), "..", "..")))
 
 
+def _attention_side(ctx, cfg, devkit, gemm, norm) -> bool:
+    ok = True
+    port = ctx.engines["m0"].port
+    port.enable_trace(256)
+    dev = port.device
+    rows, h = 4, cfg.hidden_size
+    w = torch.ones(h, dtype=torch.bfloat16, device=dev)
+    o = (torch.randn(rows, h, device=dev) * 0.1).bfloat16()
+    resid = torch.zeros(rows, h, dtype=torch.bfloat16, device=dev)
+    x2 = torch.empty(rows, h, dtype=torch.bfloat16, device=dev)
+
+    def call(layer):
+        norm.add_rmsnorm([o], w, 1e-6, resid=resid, out=x2, want_local=False, **port.publish_targets(layer, rows, 2))
+        port.run(layer, x2, rows, 2)
+        torch.cuda.synchronize(dev)
+
+    call(0)                                     # a good invocation first
+    status = gemm.scratch(dev).status
+    assert int(status[0]) == 0 and port.failure() is None
+    # the completion of the refused invocation still arrives, so make the wait look for the one after it: only
+    # the failure word can end it before its 5 s limit
+    t0 = time.monotonic()
+    bad = dict(port.publish_targets(0, rows, 2), meta=(999, 2, 0))    # layer 0's FFN rank, but a layer nobody holds
+    norm.add_rmsnorm([o], w, 1e-6, resid=resid, out=x2, want_local=False, **bad)
+    torch.cuda.synchronize(dev)
+    port.seq += 1                               # wait for sequence 3, which nobody will ever publish
+    port.run(999, x2, rows, 2)
+    torch.cuda.synchronize(dev)
+    elapsed = time.monotonic() - t0
+    f = port.failure()
+    code = int(status[0])
+    status.zero_()
+    print(f"[failure_check] rank 0: wait ended after {elapsed * 1e3:.1f} ms with status {code}, failure {f}", flush=True)
+    ok = ok and code == 5 and elapsed < 2.0 and f is not None
+    ok = ok and (f.result_code, f.origin_pe, f.invocation_sequence, f.layer_ordinal) == (2, 1, 2, 999)
+    tl = devkit.AtnFabricObserver(port).collect()
+    names = [e["name"] for e in tl.events]
+    ok = ok and names.count("published") == 2 and "wait_cancelled" in names
+    print(f"[failure_check] rank 0 events {names}", flush=True)
+    return ok
+
+
 def main() -> int:
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -43,42 +85,13 @@ def main() -> int:
         ctx.ffn.start(lease_ms=5.0)
     dist.barrier()
     if ctx.role == "atn":
-        port = ctx.engines["m0"].port
-        port.enable_trace(256)
-        dev = port.device
-        rows, h = 4, cfg.hidden_size
-        w = torch.ones(h, dtype=torch.bfloat16, device=dev)
-        o = (torch.randn(rows, h, device=dev) * 0.1).bfloat16()
-        resid = torch.zeros(rows, h, dtype=torch.bfloat16, device=dev)
-        x2 = torch.empty(rows, h, dtype=torch.bfloat16, device=dev)
+        try:
+            ok = _attention_side(ctx, cfg, devkit, gemm, norm)
+        except Exception:           # reported below; both ranks still leave together
+            import traceback
 
-        def call(layer):
-            norm.add_rmsnorm([o], w, 1e-6, resid=resid, out=x2, want_local=False, **port.publish_targets(layer, rows, 2))
-            port.run(layer, x2, rows, 2)
-            torch.cuda.synchronize(dev)
-
-        call(0)                                     # a good invocation first
-        status = gemm.scratch(dev).status
-        assert int(status[0]) == 0 and port.failure() is None
-        # the completion of the refused invocation still arrives, so make the wait look for the one after it: only
-        # the failure word can end it before its 5 s limit
-        t0 = time.monotonic()
-        norm.add_rmsnorm([o], w, 1e-6, resid=resid, out=x2, want_local=False, **port.publish_targets(999, rows, 2))
-        torch.cuda.synchronize(dev)
-        port.seq += 1                               # wait for sequence 3, which nobody will ever publish
-        port.run(999, x2, rows, 2)
-        torch.cuda.synchronize(dev)
-        elapsed = time.monotonic() - t0
-        f = port.failure()
-        code = int(status[0])
-        status.zero_()
-        print(f"[failure_check] rank 0: wait ended after {elapsed * 1e3:.1f} ms with status {code}, failure {f}", flush=True)
-        ok = ok and code == 5 and elapsed < 2.0 and f is not None
-        ok = ok and (f.result_code, f.origin_pe, f.invocation_sequence, f.layer_ordinal) == (2, 1, 2, 999)
-        tl = devkit.AtnFabricObserver(port).collect()
-        names = [e["name"] for e in tl.events]
-        ok = ok and names.count("published") == 2 and "wait_cancelled" in names
-        print(f"[failure_check] rank 0 events {names}", flush=True)
+            print("[failure_check] rank 0 raised:\n" + traceback.format_exc(), flush=True)
+            ok = False
     dist.barrier()
     if ctx.role == "ffn":
         f = ctx.ffn.failure()
