@@ -652,6 +652,11 @@ def run_multi_gpu(args) -> int:
     if world != args.gpus or world < 2:
         raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE == {args.gpus} >= 2 (got {world})")
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    if args.impl == "baseline":
+        # the library arm runs one communicator and stream per Instance: give every stream a hardware queue of its own
+        os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+    watchdog = _ProgressWatchdog(args.impl, rank)
+    watchdog.phase("setup", 420.0)
     torch.cuda.set_device(local)
     dev = torch.device(f"cuda:{local}")
     dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
@@ -721,11 +726,13 @@ def run_multi_gpu(args) -> int:
     if any(flags):
         if rank == 0:
             print(json.dumps({"metric": METRIC, "impl": args.impl, "error": [f for f in flags if f]}), flush=True)
+        watchdog.cancel()
         _shutdown(ctx, ctl, pools)
         return 1
 
     # common start: every rank's producer counts from its own clock right after this barrier
     dist.barrier(group=ctl)
+    watchdog.phase("measured run", end_s + 90.0)
     t0 = time.perf_counter() + 0.1
     try:
         if ctx.role == "atn":
@@ -741,6 +748,7 @@ def run_multi_gpu(args) -> int:
     except Exception as e:
         failure = repr(e)
     dist.barrier(group=ctl)
+    watchdog.phase("gathering results", 60.0)
     if pools:
         ecs_events = pools[0].close()
     lane_stats = ctx.ffn.stats() if ctx.role == "ffn" else None
@@ -764,12 +772,42 @@ def run_multi_gpu(args) -> int:
             served = sum(sum(l["served"]) for l in lanes) if args.impl == "xpool" else 0
             out["gpu_launches"] += 0 if not lanes else int(served * 4 * args.steps * args.step_seconds / max(1e-9, end_s))
             print(json.dumps(out), flush=True)
+    watchdog.cancel()
     _shutdown(ctx, ctl, pools)
     return rc
 
 
 def _kv_bytes_per_token(cfg) -> int:
     return 2 * cfg.num_layers * cfg.num_kv_heads * cfg.head_dim * 2
+
+
+class _ProgressWatchdog:
+    """Ends a multi-GPU run that makes no progress: if the phase in force lasts longer than its allowance, rank 0's
+    process prints an error line in the benchmark's format and every process that notices exits with code 3. A stuck
+    communicator or a generation that never becomes ready must not hold a machine of GPUs until an outer limit."""
+
+    def __init__(self, impl: str, rank: int):
+        self.impl, self.rank = impl, rank
+        self._timer: threading.Timer | None = None
+
+    def phase(self, name: str, seconds: float) -> None:
+        self.cancel()
+
+        def fire():
+            if self.rank == 0:
+                print(json.dumps({"metric": METRIC, "impl": self.impl,
+                                  "error": [f"no progress: phase '{name}' exceeded {seconds:.0f} s"]}), flush=True)
+            sys.stdout.flush()
+            os._exit(3)
+
+        self._timer = threading.Timer(seconds, fire)
+        self._timer.daemon = True
+        self._timer.start()
+
+    def cancel(self) -> None:
+        if self._timer is not None:
+            self._timer.cancel()
+            self._timer = None
 
 
 def _exit_watchdog(seconds: float, code: int = 0) -> None:

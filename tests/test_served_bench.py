@@ -1,5 +1,6 @@
 """The served-throughput benchmark's planning, producer loop and aggregation against a CPU fake deployment."""
 import argparse
+import json
 import time
 
 import pytest
@@ -130,3 +131,35 @@ def test_slo_violation_marks_the_result_invalid():
     # a request that never got a token and has waited longer than the limit counts against the TTFT percentile
     recs.append({"model": "m", "arrival": 0.1, "n_prompt": 3, "n_out": 4, "done": False, "first": None, "last": None, "n": 0, "times": []})
     assert served.latency_summary(recs, 0.0, 5.0)["ttft_ms"]["n"] == 2
+
+
+def test_vs_baseline_comes_from_the_recorded_library_arm_of_the_same_mix_and_load():
+    import argparse
+
+    base = argparse.Namespace(rate_scale=1.0, max_batch=0, kv_tokens=0, layers=0)
+    rec = served.recorded_baseline("b", 1, base)
+    assert rec is not None and rec["value"] > 0 and rec["slo_met"] is True and "--impl baseline" in rec["command"]
+    assert served.recorded_baseline("b", 3, base) is None                               # never measured: no ratio
+    assert served.recorded_baseline("b", 1, argparse.Namespace(rate_scale=1.5, max_batch=0, kv_tokens=0, layers=0)) is None
+    assert served.recorded_baseline("b", 1, argparse.Namespace(rate_scale=1.0, max_batch=0, kv_tokens=0, layers=2)) is None
+
+
+def test_progress_watchdog_ends_a_stuck_run_with_an_error_line_and_stays_quiet_when_cancelled():
+    import subprocess
+    import sys
+
+    code = ("import time, json\n"
+            "from crosspool_b200.bench.served import _ProgressWatchdog\n"
+            "w = _ProgressWatchdog('baseline', 0)\n"
+            "w.phase('a', 30.0); w.phase('b', 0.2)\n"
+            "time.sleep(5)\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 3
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "baseline" and "phase 'b'" in line["error"][0]
+    ok = ("import time\n"
+          "from crosspool_b200.bench.served import _ProgressWatchdog\n"
+          "w = _ProgressWatchdog('xpool', 1)\n"
+          "w.phase('a', 0.2); w.cancel(); time.sleep(0.6); print('done')\n")
+    r = subprocess.run([sys.executable, "-c", ok], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and r.stdout.strip() == "done"
