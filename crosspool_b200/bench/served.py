@@ -698,11 +698,17 @@ def run_multi_gpu(args) -> int:
 
     summary, clocks, correctness, ecs_events = None, None, None, None
     failure = None
+    stage = "start"
     try:
         if ctx.role == "atn":
             insts = [InstanceHandle(s.model_id, cfgs[s.model_id], ctx.engines[s.model_id]) for s in mine]
             dep = Deployment(insts)
-            dep.warmup()
+            for i in insts:          # one Instance at a time, so that a failed bring-up names it
+                stage = f"warm-up of {i.model_id}"
+                i.engine.warmup()
+                torch.cuda.synchronize(dev)
+                gemm.check_status(dev)
+            stage = "correctness check"
             if pools:
                 pools[0].attach([i.engine for i in insts], SLO_TTFT_MS / 1e3)
             if rank == 0:
@@ -720,12 +726,28 @@ def run_multi_gpu(args) -> int:
                 correctness["instance"] = s.model_id
             gemm.check_status(dev)
     except Exception as e:  # report, then let every rank leave together
-        failure = repr(e)
+        failure = f"{stage}: {e!r}"
     flags = [None] * world
     dist.all_gather_object(flags, failure, group=ctl)
     if any(flags):
+        # what every rank knows about the failed bring-up: the attention ranks' exceptions, the FFN ranks' Lane
+        # statistics, replay-thread errors and canonical failure record
+        note = {"rank": rank, "role": ctx.role, "failure": failure}
+        try:
+            if ctx.role == "ffn" and args.impl == "xpool":
+                f = ctx.ffn.failure()
+                note.update(lanes=ctx.ffn.stats(), errors=list(getattr(ctx.ffn, "errors", [])),
+                            canonical=None if f is None else [f.result_code, f.origin_pe, f.invocation_sequence, f.layer_ordinal])
+            elif ctx.role == "atn" and args.impl == "xpool":
+                note["instances"] = {m: (None if (f := e.port.failure()) is None else
+                                         [f.result_code, f.origin_pe, f.invocation_sequence, f.layer_ordinal])
+                                     for m, e in ctx.engines.items() if hasattr(e.port, "failure")}
+        except Exception as e:
+            note["diagnostics_failed"] = repr(e)
+        notes = [None] * world
+        dist.all_gather_object(notes, note, group=ctl)
         if rank == 0:
-            print(json.dumps({"metric": METRIC, "impl": args.impl, "error": [f for f in flags if f]}), flush=True)
+            print(json.dumps({"metric": METRIC, "impl": args.impl, "error": [f for f in flags if f], "ranks": notes}), flush=True)
         watchdog.cancel()
         _shutdown(ctx, ctl, pools)
         return 1
