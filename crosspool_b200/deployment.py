@@ -73,6 +73,37 @@ class Deployment:
             res.tokens[i.model_id] = i.engine.collect_step()
         return res
 
+    def step_async(self, poll_s: float = 5e-5) -> StepResult:
+        """Event-driven iteration for a serving loop: collects every Instance whose step has finished on the GPU and
+        starts that Instance's next step at once; Instances whose step is still running are left alone. A 170 ms
+        prefill chunk of a large model then no longer holds back the decode steps of the small model it shares the GPU
+        with (``step`` runs the Instances in lockstep: every call lasts as long as the slowest of them). Returns the
+        tokens of the steps collected in this call, possibly none."""
+        res = StepResult()
+        self.idle_tick()
+        progressed = False
+        waiting = []
+        for i in self.instances:
+            e = i.engine
+            if e.step_in_flight:
+                if not e.step_ready():
+                    waiting.append(i)
+                    continue
+                res.tokens[i.model_id] = e.collect_step()
+                progressed = True
+            if e.has_work:
+                e.launch_step()
+                progressed = True
+        if not progressed and waiting:
+            if len(waiting) == 1:       # nothing else to overlap with: wait for it (releases the interpreter lock)
+                i = waiting[0]
+                res.tokens[i.model_id] = i.engine.collect_step()
+                if i.engine.has_work:
+                    i.engine.launch_step()
+            else:
+                time.sleep(poll_s)
+        return res
+
     def idle_tick(self) -> None:
         """Lets Instances without work serve their elastic-KV capacity commands."""
         for i in self.instances:

@@ -41,6 +41,9 @@ def capacity_buckets(max_rows: int) -> list[int]:
     return out
 
 
+FIRST_CONTACT_WAIT_NS = 30_000_000_000   # wait limit of an Instance's very first FFN invocation (warm-up)
+
+
 @dataclass
 class EngineConfig:
     max_batch: int = 256
@@ -150,6 +153,8 @@ class AttentionEngine:
         self._b_pos = None
         self._b_last = None
         self._inflight = None
+        self._pre_inflight: list[tuple[Sequence, int]] | None = None
+        self._step_event = torch.cuda.Event() if torch.cuda.is_available() else None
         self._graph_launches: dict[int, int] = {}
         self.prefix = None
         if e.prefix_cache:
@@ -386,6 +391,16 @@ class AttentionEngine:
             hv = self.dec_meta_host.numpy()
             hv[2 * self.ecfg.max_batch:3 * self.ecfg.max_batch] = -1  # no KV writes for padding rows
             self.dec_meta.copy_(self.dec_meta_host, non_blocking=True)
+            # First contact with the FFN ranks (kernel loading on both sides, first touch of peer mappings, Lane
+            # threads reaching their first replay) gets a generous wait limit; every later wait keeps the normal one.
+            relax = getattr(self.port, "set_wait_limit", None)
+            normal = getattr(self.port, "wait_ns", None)
+            if relax is not None and normal is not None:
+                relax(max(normal, FIRST_CONTACT_WAIT_NS))
+            self._decode_forward(self._buckets[0])
+            self.stream.synchronize()
+            if relax is not None and normal is not None:
+                relax(normal)
             for B in self._buckets:
                 self._decode_forward(B)
             self.stream.synchronize()
@@ -454,6 +469,11 @@ class AttentionEngine:
         return chosen, e.prefill_chunk - budget
 
     def _step_prefill(self, chosen: list[tuple[Sequence, int]], rows: int) -> list[tuple[Sequence, int]]:
+        self._launch_prefill(chosen, rows)
+        return self._collect_prefill()
+
+    def _launch_prefill(self, chosen: list[tuple[Sequence, int]], rows: int) -> None:
+        """Fills the chunk's pinned metadata and enqueues the chunk; ``_collect_prefill`` finishes it."""
         e, P, S = self.ecfg, self.ecfg.prefill_chunk, self.ecfg.max_prefill_seqs
         hv = self.pre_meta_host.numpy()
         b = 3 * P
@@ -482,10 +502,16 @@ class AttentionEngine:
             self._stage_sampling([s for s, _ in chosen])
             self._prefill_forward(rows, len(chosen), max(n for _, n in chosen))
             self.tokens_host[:len(chosen)].copy_(self.tokens[:len(chosen)], non_blocking=True)
-            self.stream.synchronize()
+            self._step_event.record(self.stream)
+        self._pre_inflight = chosen
         self.stats["prefill_steps"] += 1
         self.stats["h2d_bytes"] += self._pre_words * 4
         self.stats["d2h_bytes"] += len(chosen) * 4
+
+    def _collect_prefill(self) -> list[tuple[Sequence, int]]:
+        """Finishes the prefill chunk in flight: waits for its sampled tokens and does the bookkeeping."""
+        chosen, self._pre_inflight = self._pre_inflight, None
+        self._step_event.synchronize()
         now = time.monotonic()
         out = []
         th = self.tokens_host.numpy()
@@ -600,6 +626,7 @@ class AttentionEngine:
             self._stage_sampling(batch)
             self._replay_decode(B)
             self.tokens_host[:n].copy_(self.tokens[:n], non_blocking=True)
+            self._step_event.record(self.stream)
         self._inflight = (batch, n)
         self.stats["decode_steps"] += 1
         self.stats["h2d_bytes"] += self._dec_words * 4
@@ -646,7 +673,7 @@ class AttentionEngine:
     def launch_step(self) -> None:
         """Starts one engine iteration (a prefill chunk or a decode step) without waiting for the
         GPU, so that a driver of several co-located Instances can overlap them; ``collect_step``
-        finishes it. Prefill chunks complete inside this call."""
+        finishes it and ``step_ready`` tells whether it would block."""
         self._pending: list[tuple[Sequence, int]] | None = None
         if self.capacity is not None:
             self._capacity_tick()
@@ -661,7 +688,7 @@ class AttentionEngine:
                 self._last_was_prefill = True
                 self._b_key = None
                 with nvtx.range(f"{self.cfg.name} prefill {rows}"):
-                    self._pending = self._step_prefill(chosen, rows)
+                    self._launch_prefill(chosen, rows)
                 return
         self._last_was_prefill = False
         if self.running:
@@ -669,10 +696,25 @@ class AttentionEngine:
                 if not self._decode_launch():
                     self._pending = []
 
+    @property
+    def step_in_flight(self) -> bool:
+        return self._pending is not None or self._pre_inflight is not None or self._inflight is not None
+
+    def step_ready(self) -> bool:
+        """Whether ``collect_step`` would return without waiting for the GPU (a driver of several co-located
+        Instances polls this so that a long prefill chunk of one does not hold back the steps of the others)."""
+        if self._pending is not None:
+            return True
+        if self._pre_inflight is not None or self._inflight is not None:
+            return self._step_event.query()
+        return True
+
     def collect_step(self) -> list[tuple[Sequence, int]]:
         if self._pending is not None:
             out, self._pending = self._pending, None
             return out
+        if self._pre_inflight is not None:
+            return self._collect_prefill()
         if self._inflight is not None:
             return self._decode_collect()
         return []

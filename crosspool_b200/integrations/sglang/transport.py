@@ -49,7 +49,7 @@ class FabricInstanceTransport:
 
     def __init__(self, place: F.InstancePlacement, atn_base: int, ffn_bases: list[int], device, wait_ns: int = 5_000_000_000,
                  keep=()):
-        from ...ops.gemm import scratch
+        from ...ops.gemm import status_words
 
         self.place, self.device, self._keep = place, torch.device(device), list(keep)
         alay, flay = F.atn_slot_layout(place), F.ffn_slot_layout(place)
@@ -63,7 +63,7 @@ class FabricInstanceTransport:
             b.parts[r] = atn_base + alay.output_offset + r * alay.output_stride
             b.done_flags[r] = atn_base + alay.completion_offset + r * F.RECORD_BYTES + F.COMPLETION_SEQ_OFFSET
         b.failure = atn_base + alay.completion_offset + F.FAILURE_SLOT_OFFSET
-        self.status = scratch(self.device).status
+        self.status = status_words(self.device)
         b.status, b.wait_ns = self.status.data_ptr(), wait_ns
         b.n_peers, b.n_parts, b.hidden, b.capacity_rows = len(ffn_bases), place.tp, place.cfg.hidden_size, place.capacity_rows
         b.origin_pe = place.atn_rank

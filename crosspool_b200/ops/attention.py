@@ -93,9 +93,9 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     a.chunk_tokens = chunk_tokens
     a.num_pages = k_cache.shape[0] if k_cache.is_contiguous() and v_cache.is_contiguous() else 0
     a.force_simt = int(force_simt)
-    from .gemm import scratch
+    from .gemm import status_words
 
-    a.status = scratch(q.device).status.data_ptr()
+    a.status = status_words(q.device).data_ptr()
     native.check(native.kernels().xp_decode_attn(C.byref(a), _stream(q.device)), "xp_decode_attn",
                  2 if num_splits > 1 else 1)
     return out
@@ -126,9 +126,9 @@ def paged_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     which = PREFILL_KERNEL_DEFAULT if force_simple in (None, False) else ("simple" if force_simple is True else force_simple)
     a.force_simple = PREFILL_KERNELS[which]
     a.total_q = q.shape[0]
-    from .gemm import scratch
+    from .gemm import status_words
 
-    a.status = scratch(q.device).status.data_ptr()
+    a.status = status_words(q.device).data_ptr()
     native.check(native.kernels().xp_prefill_attn(C.byref(a), _stream(q.device)), "xp_prefill_attn")
     return out
 

@@ -41,31 +41,53 @@ class _Scratch:
     status: torch.Tensor
 
 
-_scratch: dict[int, _Scratch] = {}
+_status: dict[int, torch.Tensor] = {}
+_scratch: dict[tuple[int, int], _Scratch] = {}
+
+
+def _device_index(device: torch.device) -> int:
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
+def status_words(device: torch.device) -> torch.Tensor:
+    """The device's four error words (one set per device, shared by every stream and kernel family)."""
+    idx = _device_index(device)
+    st = _status.get(idx)
+    if st is None:
+        st = _status[idx] = torch.zeros(4, dtype=torch.int32, device=device)
+    return st
 
 
 def scratch(device: torch.device) -> _Scratch:
-    """Per-device split-K workspace, tile counters and the error word of the GEMM kernels."""
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    s = _scratch.get(idx)
+    """Split-K workspace and tile counters of the GEMM kernels for the *current stream* of ``device``, and the
+    device's error words. Workspace and counters are per stream: two engines of one GPU run their decode GEMMs
+    concurrently on their own streams, and split-K calls that shared one workspace would fold each other's partial
+    sums. The status words (``status[0]`` code, ``[1..3]`` detail) are one set per device, read by ``check_status``."""
+    idx = _device_index(device)
+    st = status_words(device)
+    key = (idx, torch.cuda.current_stream(device).cuda_stream)
+    s = _scratch.get(key)
     if s is None:
         s = _Scratch(
             ws=torch.empty(_WS_BYTES // 4, dtype=torch.float32, device=device),
             counters=torch.zeros(_COUNTER_WORDS, dtype=torch.int32, device=device),
-            status=torch.zeros(4, dtype=torch.int32, device=device),
+            status=st,
         )
-        _scratch[idx] = s
+        _scratch[key] = s
     return s
 
 
 def check_status(device: torch.device) -> None:
     """Raises if a kernel recorded a bounded-wait timeout since the last check (synchronises)."""
-    s = scratch(device)
-    words = s.status.tolist()
+    status = status_words(device)
+    words = status.tolist()
     code = words[0]
     if code != 0:
-        s.status.zero_()
-        s.counters.zero_()     # a split-K call that gave up leaves tile counters behind: later calls must not fold stale partials
+        status.zero_()
+        idx = _device_index(device)
+        for (d, _), sc in _scratch.items():
+            if d == idx:
+                sc.counters.zero_()   # a split-K call that gave up leaves tile counters behind: later calls must not fold stale partials
         detail = f" (detail {words[1]}, {words[2]:#x}, {words[3]})" if any(words[1:]) else ""
         raise RuntimeError(f"xpool kernel reported device status {code}{detail}")
 

@@ -76,7 +76,9 @@ _ws_cache: dict[tuple, MoeWorkspace] = {}
 
 
 def workspace(device, cap_rows: int, cfg: ModelConfig, inter: int, n_local: int) -> MoeWorkspace:
-    key = (str(device), cap_rows, cfg.hidden_size, inter, cfg.num_experts_per_tok, n_local, cfg.num_experts)
+    # one workspace per stream: Instances of one GPU that run concurrently must not share routing tables and scratch rows
+    key = (str(device), torch.cuda.current_stream(device).cuda_stream if torch.device(device).type == "cuda" else 0,
+           cap_rows, cfg.hidden_size, inter, cfg.num_experts_per_tok, n_local, cfg.num_experts)
     ws = _ws_cache.get(key)
     if ws is None:
         k, h = cfg.num_experts_per_tok, cfg.hidden_size

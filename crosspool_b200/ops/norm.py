@@ -15,7 +15,7 @@ from typing import Sequence
 import torch
 
 from .. import native
-from .gemm import scratch
+from .gemm import status_words
 
 _counters: dict[int, torch.Tensor] = {}
 
@@ -74,7 +74,7 @@ def add_rmsnorm(parts: Sequence[torch.Tensor] | torch.Tensor, weight: torch.Tens
     a.weight = weight.data_ptr() if weight is not None else None
     a.out_local = out.data_ptr() if (out is not None and want_local) else None
     a.done_counter = _done_counter(dev).data_ptr()
-    a.status = scratch(dev).status.data_ptr()
+    a.status = status_words(dev).data_ptr()
     a.cancel = cancel_ptr or None
     if trace is not None:
         a.trace_events, a.trace_state, a.trace_capacity = trace

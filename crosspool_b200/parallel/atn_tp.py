@@ -80,7 +80,7 @@ class TpGroup:
         for r, h in enumerate(handles):
             if r != self.rank:
                 self.bases[r] = PeerBuffer.open(h)
-        from ..ops.gemm import scratch
+        from ..ops.gemm import status_words
 
         sig = native.SignalArgs()
         peers = [r for r in range(self.size) if r != self.rank]
@@ -91,7 +91,7 @@ class TpGroup:
         for i, r in enumerate(peers):
             w.flags[i] = self.buf.ptr + 4 * r                # the peer's word in my flag block
         w.n, w.want_ptr, w.wait_ns = len(peers), self.seq.data_ptr(), 5_000_000_000
-        w.status = scratch(self.device).status.data_ptr()
+        w.status = status_words(self.device).data_ptr()
         self._sig, self._wait = sig, w
 
     def part(self, layer: int) -> torch.Tensor:

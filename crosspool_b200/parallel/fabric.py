@@ -267,11 +267,11 @@ class FabricFfnPort(FfnPort):
         self.trace: DeviceTrace | None = None
 
     def attach(self, engine: AttentionEngine) -> None:
-        from ..ops.gemm import scratch
+        from ..ops.gemm import status_words
 
         if engine.cap > self.place.capacity_rows:
             raise ValueError("engine row capacity exceeds the fabric slot capacity")
-        self._wait.status = scratch(self.device).status.data_ptr()
+        self._wait.status = status_words(self.device).data_ptr()
 
     def set_wait_limit(self, wait_ns: int) -> None:
         self.wait_ns = self._wait.wait_ns = int(wait_ns)
@@ -335,11 +335,11 @@ class FabricFfnFollowerPort(FfnPort):
         self._wait.n, self._wait.want_ptr, self._wait.wait_ns = tp, self.seq.data_ptr(), 5_000_000_000
 
     def attach(self, engine: AttentionEngine) -> None:
-        from ..ops.gemm import scratch
+        from ..ops.gemm import status_words
 
         if engine.cap > self.place.capacity_rows:
             raise ValueError("engine row capacity exceeds the fabric slot capacity")
-        self._wait.status = scratch(self.device).status.data_ptr()
+        self._wait.status = status_words(self.device).data_ptr()
 
     def publish_targets(self, layer: int, rows: int, mode: int) -> dict | None:
         return None

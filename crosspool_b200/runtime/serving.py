@@ -80,6 +80,9 @@ class EngineLoop:
         self._stop = threading.Event()
         self._thread: threading.Thread | None = None
         self.idle_sleep = idle_sleep
+        # a deployment of several co-located Instances is stepped event-driven (each Instance as soon as its own step
+        # has finished) when it offers that; otherwise in lockstep
+        self._step = getattr(deployment, "step_async", None) or deployment.step
         self.error: Exception | None = None
         self.steps = 0
         self.tokens = 0
@@ -109,8 +112,9 @@ class EngineLoop:
                 p.deliver(e)
 
     def call_between_steps(self, fn) -> None:
-        """Runs ``fn()`` on the loop thread before its next step, when no engine step is in flight (a benchmark
-        records its window boundaries this way)."""
+        """Runs ``fn()`` on the loop thread between two of its iterations (a benchmark records its window boundaries
+        this way). With event-driven stepping an Instance's step may be in flight at that moment; its tokens count
+        when they are collected."""
         self._calls.put(fn)
 
     def _run_calls(self) -> None:
@@ -135,7 +139,7 @@ class EngineLoop:
                 if not self.dep.has_work:
                     self._idle()
                     continue
-                res = self.dep.step()
+                res = self._step()
                 self.steps += 1
                 batch: list[tuple[Pending, tuple[int, bool]]] = []
                 for model_id, pairs in res.tokens.items():

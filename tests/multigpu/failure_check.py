@@ -36,7 +36,7 @@ def _attention_side(ctx, cfg, devkit, gemm, norm) -> bool:
         torch.cuda.synchronize(dev)
 
     call(0)                                     # a good invocation first
-    status = gemm.scratch(dev).status
+    status = gemm.status_words(dev)
     assert int(status[0]) == 0 and port.failure() is None
     # the completion of the refused invocation still arrives, so make the wait look for the one after it: only
     # the failure word can end it before its 5 s limit

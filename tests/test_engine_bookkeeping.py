@@ -99,3 +99,61 @@ def test_engine_loop_survives_an_empty_prompt():
         assert loop.error is None
     finally:
         loop.stop()
+
+
+class _FakeEngine:
+    """Engine whose steps finish after a set number of readiness polls."""
+
+    def __init__(self, name, work, polls_per_step):
+        self.name, self.work, self.polls_per_step = name, work, polls_per_step
+        self.step_in_flight, self._polls, self.launched, self.collected, self.blocking_collects = False, 0, 0, 0, 0
+
+    @property
+    def has_work(self):
+        return self.work > 0
+
+    def launch_step(self):
+        assert not self.step_in_flight
+        self.step_in_flight, self._polls = True, 0
+        self.launched += 1
+
+    def step_ready(self):
+        self._polls += 1
+        return self._polls > self.polls_per_step
+
+    def collect_step(self):
+        if self._polls <= self.polls_per_step:
+            self.blocking_collects += 1
+        self.step_in_flight = False
+        self.work -= 1
+        self.collected += 1
+        return [(self.name, self.collected)]
+
+
+def test_event_driven_stepping_lets_a_fast_instance_run_while_a_slow_step_is_in_flight():
+    from crosspool_b200.deployment import Deployment, InstanceHandle
+
+    slow, fast = _FakeEngine("slow", 2, polls_per_step=6), _FakeEngine("fast", 10, polls_per_step=0)
+    dep = Deployment([InstanceHandle("slow", None, slow), InstanceHandle("fast", None, fast)])
+    tokens = {"slow": [], "fast": []}
+    calls = 0
+    while dep.has_work and calls < 200:
+        for m, pairs in dep.step_async(poll_s=0.0).tokens.items():
+            tokens[m] += pairs
+        calls += 1
+    assert slow.collected == 2 and fast.collected == 10 and not dep.has_work
+    # the fast Instance finished several steps before the slow one's first step came back
+    first_slow = 6
+    assert fast.launched >= 5 and calls < 40
+    assert [n for _, n in tokens["fast"]] == list(range(1, 11)) and [n for _, n in tokens["slow"]] == [1, 2]
+    # once only the slow Instance is left, the driver waits for it instead of polling
+    assert slow.blocking_collects >= 1 and fast.blocking_collects == 0
+    del first_slow
+
+
+def test_lockstep_step_still_runs_every_instance_once_per_call():
+    from crosspool_b200.deployment import Deployment, InstanceHandle
+
+    a, b = _FakeEngine("a", 3, 0), _FakeEngine("b", 1, 0)
+    dep = Deployment([InstanceHandle("a", None, a), InstanceHandle("b", None, b)])
+    assert set(dep.step().tokens) == {"a", "b"} and set(dep.step().tokens) == {"a"}

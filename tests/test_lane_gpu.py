@@ -466,7 +466,7 @@ def test_a_rejected_invocation_becomes_the_canonical_failure_and_cancels_waits_a
         w.flags[0] = atn[0].ptr + alay.completion_offset + F.COMPLETION_SEQ_OFFSET
         w.n, w.want, w.wait_ns = 1, 9, 2_000_000_000
         w.cancel = atn[0].ptr + alay.completion_offset + F.FAILURE_SLOT_OFFSET
-        status = gemm.scratch(torch.device("cuda")).status
+        status = gemm.status_words(torch.device("cuda"))
         status.zero_()
         w.status = status.data_ptr()
         trace = F.DeviceTrace(16)
