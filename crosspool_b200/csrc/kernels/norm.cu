@@ -151,9 +151,11 @@ norm_publish_kernel(XpNormArgs a) {
 
   // 4. last CTA releases the sequence word on every destination.
   if (a.npeers > 0 && (a.publish_seq != 0 || a.seq_counter != nullptr)) {
-    __threadfence_system();
+    // The CTA barrier orders every thread's row stores before thread 0; its system-scope fence is cumulative, so one
+    // fence per CTA (not one per thread: 256 x rows membar.sys were the kernel's top stall) publishes the whole row.
     __syncthreads();
     if (threadIdx.x == 0) {
+      __threadfence_system();
       const uint32_t prev = atomicAdd(a.done_counter, 1u);
       if (prev == gridDim.x - 1) {
         *a.done_counter = 0;

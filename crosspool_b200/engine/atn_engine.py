@@ -153,6 +153,7 @@ class AttentionEngine:
         self._b_pos = None
         self._b_last = None
         self._inflight = None
+        self._pending: list[tuple[Sequence, int]] | None = None
         self._pre_inflight: list[tuple[Sequence, int]] | None = None
         self._step_event = torch.cuda.Event() if torch.cuda.is_available() else None
         self._graph_launches: dict[int, int] = {}

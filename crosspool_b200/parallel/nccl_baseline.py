@@ -182,6 +182,13 @@ def build_rank(topo: Topology, rank: int, device, ecfg_for: dict[str, EngineConf
             raise ValueError("the baseline arm covers one attention rank and one FFN TP group per Instance")
         members = [p.atn_rank, *p.ffn_ranks]
         g = dist.new_group(ranks=members, backend="nccl", timeout=timedelta(seconds=timeout_s))
+        if rank in members:
+            # Communicators are created on first use, and creation is itself a collective. Doing it here, on one thread
+            # and in the same order on every rank, keeps the service threads of an FFN rank that serves several
+            # Instances from creating theirs in different orders on different ranks (which never completes).
+            t = torch.zeros(1, device=device)
+            dist.all_reduce(t, group=g)
+            torch.cuda.synchronize(device)
         if rank == p.atn_rank:
             port = NcclFfnPort(p, g, device)
             aw = random_attention_weights(p.cfg, p.seed, device, torch.bfloat16)
