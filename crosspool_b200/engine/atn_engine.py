@@ -115,6 +115,10 @@ class FfnPort:
     def wait_args(self) -> dict:
         return {}
 
+    # Optional: ``announce_forward(rows, mode)`` is called on the host right before a forward pass of ``rows`` rows is
+    # enqueued (eagerly or as a graph replay; not while a graph is being captured). A port whose FFN side must be
+    # told on the host that work is coming (the library-collective arm) implements it.
+
 
 def _parts_kw(parts) -> dict:
     """FFN outputs as add-RMSNorm arguments: a list of local tensors, or (for a port whose result lives
@@ -398,11 +402,13 @@ class AttentionEngine:
             normal = getattr(self.port, "wait_ns", None)
             if relax is not None and normal is not None:
                 relax(max(normal, FIRST_CONTACT_WAIT_NS))
+            self._announce(self._buckets[0], MODE_DECODE)
             self._decode_forward(self._buckets[0])
             self.stream.synchronize()
             if relax is not None and normal is not None:
                 relax(normal)
             for B in self._buckets:
+                self._announce(B, MODE_DECODE)
                 self._decode_forward(B)
             self.stream.synchronize()
             gemm.check_status(self.device)
@@ -410,6 +416,11 @@ class AttentionEngine:
                 for B in self._buckets:
                     self._capture_decode(B)
             self.stream.synchronize()
+
+    def _announce(self, rows: int, mode: int) -> None:
+        hook = getattr(self.port, "announce_forward", None)
+        if hook is not None:
+            hook(rows, mode)
 
     def _capture_decode(self, B: int) -> None:
         """Captures the decode step of one row bucket (on ``self.stream``, which is current)."""
@@ -424,6 +435,7 @@ class AttentionEngine:
 
     def _replay_decode(self, B: int) -> None:
         """One decode step of bucket ``B``: the captured graph, or the eager launches when graphs are off."""
+        self._announce(B, MODE_DECODE)
         g = self._graphs.get(B)
         if g is not None:
             g.replay()
@@ -501,6 +513,7 @@ class AttentionEngine:
         with torch.cuda.stream(self.stream):
             self.pre_meta.copy_(self.pre_meta_host, non_blocking=True)
             self._stage_sampling([s for s, _ in chosen])
+            self._announce(rows, MODE_PREFILL)
             self._prefill_forward(rows, len(chosen), max(n for _, n in chosen))
             self.tokens_host[:len(chosen)].copy_(self.tokens[:len(chosen)], non_blocking=True)
             self._step_event.record(self.stream)

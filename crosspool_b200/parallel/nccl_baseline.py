@@ -7,10 +7,13 @@ the attention rank, whose next add-RMSNorm adds them to the residual stream. The
 (kernels that store into peer memory, ``parallel/fabric.py``) against this arm on the same deployment and
 workload. None of this repository's FFN kernels, Lanes or flag protocol run here.
 
-One NCCL communicator per Instance holds its attention rank and its FFN ranks. Per engine iteration the attention
-rank first broadcasts a one-word header with the row count; the FFN rank's service thread reads it on the host
-(one stream synchronisation per iteration) and then enqueues all layers' receive -> GEMMs -> reduce without
-further host synchronisation. A header of 0 rows ends the service thread.
+One NCCL communicator per Instance holds its attention rank and its FFN ranks, beside a gloo group of the same
+members. Per engine iteration the attention rank first announces the row count on the host (a gloo broadcast, made
+right before the iteration's kernels are enqueued); the FFN rank's service thread waits for that announcement on the
+host and then enqueues all layers' receive -> GEMMs -> reduce without further host synchronisation. An announcement
+of 0 rows ends the service thread. No collective kernel therefore sits on an FFN GPU waiting for work that has not
+been decided yet: a library kernel that waits indefinitely blocks every CUDA call of the process that synchronises
+the device (an allocation, a handle creation), which is how an FFN rank serving several Instances stops for good.
 """
 
 from __future__ import annotations
@@ -29,29 +32,21 @@ from .fabric import InstancePlacement, Topology
 
 
 class NcclFfnPort(FfnPort):
-    def __init__(self, place: InstancePlacement, group, device):
-        self.place, self.group, self.device = place, group, torch.device(device)
+    def __init__(self, place: InstancePlacement, group, host_group, device):
+        self.place, self.group, self.host_group, self.device = place, group, host_group, torch.device(device)
         self.me = place.atn_rank
-        self._hdr: dict[int, torch.Tensor] = {}
-        self._hdr_dyn = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self._hdr_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self._hdr_host = torch.zeros(4, dtype=torch.int64)
         self.y = None
 
     def attach(self, engine: AttentionEngine) -> None:
         self.y = torch.zeros(engine.cap, self.place.cfg.hidden_size, dtype=torch.bfloat16, device=self.device)
-        for b in engine.ecfg.decode_buckets or _buckets(engine.ecfg.max_batch):
-            self._hdr[b] = torch.full((4,), b, dtype=torch.int32, device=self.device)   # constant inside the bucket's graph
 
-    def _header(self, rows: int, mode: int) -> torch.Tensor:
-        if mode == 2 and rows in self._hdr:
-            return self._hdr[rows]
-        self._hdr_host[:] = rows
-        self._hdr_dyn.copy_(self._hdr_host, non_blocking=True)
-        return self._hdr_dyn
+    def announce_forward(self, rows: int, mode: int) -> None:
+        """Host side, before the iteration's kernels are enqueued: tells the FFN ranks how many rows are coming."""
+        self._hdr_host[0], self._hdr_host[1] = rows, mode
+        dist.broadcast(self._hdr_host, src=self.me, group=self.host_group)
 
     def run(self, layer: int, x: torch.Tensor, rows: int, mode: int) -> list[torch.Tensor]:
-        if layer == 0:
-            dist.broadcast(self._header(rows, mode), src=self.me, group=self.group)
         dist.broadcast(x[:rows], src=self.me, group=self.group)
         y = self.y[:rows]
         y.zero_()                                  # the attention rank contributes nothing to the sum
@@ -59,21 +54,15 @@ class NcclFfnPort(FfnPort):
         return [y]
 
     def shutdown(self) -> None:
-        self._hdr_host[:] = 0
-        self._hdr_dyn.copy_(self._hdr_host, non_blocking=True)
-        dist.broadcast(self._hdr_dyn, src=self.me, group=self.group)
-
-
-def _buckets(max_rows: int) -> list[int]:
-    from ..engine.atn_engine import capacity_buckets
-
-    return capacity_buckets(max_rows)
+        self._hdr_host[0] = 0
+        dist.broadcast(self._hdr_host, src=self.me, group=self.host_group)
 
 
 @dataclass
 class _Served:
     place: InstancePlacement
     group: object
+    host_group: object
     tp_rank: int
     weights: list
     thread: threading.Thread | None = None
@@ -88,7 +77,7 @@ class NcclFfnRank:
         self.served: list[_Served] = []
         self.errors: list[str] = []
 
-    def add_instance(self, place: InstancePlacement, group, tp_rank: int) -> None:
+    def add_instance(self, place: InstancePlacement, group, host_group, tp_rank: int) -> None:
         cfg = place.cfg
         weights = []
         for l in range(cfg.num_layers):
@@ -97,7 +86,7 @@ class NcclFfnRank:
                                                 expert_range=place.expert_range(tp_rank)))
             else:
                 weights.append(random_ffn_layer(cfg, l, place.seed, self.device, torch.bfloat16, tp_rank, place.tp))
-        self.served.append(_Served(place, group, tp_rank, weights))
+        self.served.append(_Served(place, group, host_group, tp_rank, weights))
 
     def _serve(self, sv: _Served) -> None:
         try:
@@ -109,8 +98,7 @@ class NcclFfnRank:
             inter2 = max((w.gate_up.shape[0] for w in dense), default=2)
             moe_ws = None
             with torch.cuda.stream(stream):
-                hdr = torch.zeros(4, dtype=torch.int32, device=dev)
-                hdr_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+                hdr_host = torch.zeros(4, dtype=torch.int64)
                 x = torch.zeros(cap, cfg.hidden_size, dtype=bf, device=dev)
                 gu = torch.zeros(cap, inter2, dtype=bf, device=dev)
                 act = torch.zeros(cap, inter2 // 2, dtype=bf, device=dev)
@@ -121,9 +109,7 @@ class NcclFfnRank:
                     w0 = next(w for w in sv.weights if w.is_moe)
                     moe_ws = moe.workspace(dev, cap, cfg, w0.gate_up.shape[1] // 2, w0.gate_up.shape[0])
                 while True:
-                    dist.broadcast(hdr, src=src, group=sv.group)
-                    hdr_host.copy_(hdr, non_blocking=True)
-                    stream.synchronize()
+                    dist.broadcast(hdr_host, src=src, group=sv.host_group)   # host-side wait for the announcement
                     rows = int(hdr_host[0])
                     if rows <= 0:
                         return
@@ -182,6 +168,7 @@ def build_rank(topo: Topology, rank: int, device, ecfg_for: dict[str, EngineConf
             raise ValueError("the baseline arm covers one attention rank and one FFN TP group per Instance")
         members = [p.atn_rank, *p.ffn_ranks]
         g = dist.new_group(ranks=members, backend="nccl", timeout=timedelta(seconds=timeout_s))
+        hg = dist.new_group(ranks=members, backend="gloo", timeout=timedelta(seconds=max(timeout_s, 600.0)))
         if rank in members:
             # Communicators are created on first use, and creation is itself a collective. Doing it here, on one thread
             # and in the same order on every rank, keeps the service threads of an FFN rank that serves several
@@ -190,12 +177,12 @@ def build_rank(topo: Topology, rank: int, device, ecfg_for: dict[str, EngineConf
             dist.all_reduce(t, group=g)
             torch.cuda.synchronize(device)
         if rank == p.atn_rank:
-            port = NcclFfnPort(p, g, device)
+            port = NcclFfnPort(p, g, hg, device)
             aw = random_attention_weights(p.cfg, p.seed, device, torch.bfloat16)
             kv = kv_for(p) if kv_for is not None else None
             ctx.engines[p.model_id] = AttentionEngine(p.cfg, aw, port, ecfg_for[p.model_id], device, kv=kv)
             ctx.ports.append(port)
         elif rank in p.ffn_ranks:
-            ctx.ffn.add_instance(p, g, p.ffn_ranks.index(rank))
+            ctx.ffn.add_instance(p, g, hg, p.ffn_ranks.index(rank))
     dist.barrier(group=ctl_group)
     return ctx
