@@ -39,6 +39,8 @@ def _parser() -> argparse.ArgumentParser:
     mp.add_argument("--out", default="xpool-memory-profile.json")
     b = sub.add_parser("bench")
     b.add_argument("rest", nargs=argparse.REMAINDER)
+    q = sub.add_parser("qualify", help="check an architecture's FFN path against its checkpoint description")
+    q.add_argument("rest", nargs=argparse.REMAINDER)
     return p
 
 
@@ -164,7 +166,17 @@ def cmd_bench(ns) -> int:
 
 
 def main(argv: list[str] | None = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    # `bench` and `qualify` hand everything behind them to their own parsers (option-like words included, which
+    # argparse's REMAINDER does not accept as the first word)
+    passthrough = None
+    for i, word in enumerate(argv):
+        if word in ("bench", "qualify"):
+            argv, passthrough = argv[: i + 1], argv[i + 1:]
+            break
     ns = _parser().parse_args(argv)
+    if passthrough is not None:
+        ns.rest = passthrough
     try:
         if ns.command == "config":
             return cmd_config_dump(ns)
@@ -178,6 +190,10 @@ def main(argv: list[str] | None = None) -> int:
             return cmd_agent(ns, ns.command)
         if ns.command == "bench":
             return cmd_bench(ns)
+        if ns.command == "qualify":
+            from ..devtools import qualification
+
+            return qualification.main(ns.rest)
     except C.ConfigError as e:
         print(f"xpool: configuration error: {e}", file=sys.stderr)
         return 2

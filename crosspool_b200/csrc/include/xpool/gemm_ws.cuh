@@ -468,7 +468,7 @@ __device__ __forceinline__ bool epilogue_tile(const Problem& p, const TileCoord&
   // all lanes agree on the outcome so that the aligned TMEM loads below stay convergent
   bool acc_ok = __all_sync(0xffffffffu, sm100::mbar_wait(&bar->acc_full[st.acc], st.acc_phase, deadline));
   if (p.splits > 1) {
-    // Split-K tiles meet at named barriers further down: the four warps agree on the verdict first, so that a wait
+    // Split-K tiles meet at named barriers further down: the four warps agree on the outcome first, so that a wait
     // that ran out in one warp cannot leave the others blocked at a barrier it never reaches.
     if (!acc_ok) *reinterpret_cast<volatile uint32_t*>(&bar->abort_flag) = 1u;
     epi_bar_sync();

@@ -115,6 +115,84 @@ constexpr uint32_t kFailureClaimed = 1;
 // bytes into the block of its first CompletionRecord.
 constexpr uint64_t kFailureSlotOffset = 64;
 
+// ---------------------------------------------------------------- record expectations
+//
+// What a consumer checks before it acts on a record (the reference validates every publication against the
+// expected key and bounds, fabric/protocol.hpp `validate_expected`). Each returns ResultCode::Ok or
+// ProtocolMismatch; nothing traps.
+
+XP_HD inline bool valid_forward_mode(uint32_t m) {
+  return m == static_cast<uint32_t>(ForwardMode::Prefill) || m == static_cast<uint32_t>(ForwardMode::Decode) ||
+         m == static_cast<uint32_t>(ForwardMode::Idle);
+}
+
+// An invocation read from a slot whose previous completed sequence is `completed`: the next sequence, a layer the
+// Instance has, a known mode and requirement, rows within capacity (0 rows only for an idle step).
+XP_HD inline ResultCode validate_expected(const InvocationRecord& r, uint32_t completed, uint32_t capacity_rows,
+                                          uint32_t num_layers) {
+  const bool ok = r.sequence == completed + 1u && r.layer_ordinal < num_layers && valid_forward_mode(r.forward_mode) &&
+                  r.rows <= capacity_rows &&
+                  (r.rows > 0u || r.forward_mode == static_cast<uint32_t>(ForwardMode::Idle)) &&
+                  (r.output_requirement == 0u ||   // 0: the publisher predates the field (treated as per-rank complete)
+                   r.output_requirement == static_cast<uint32_t>(OutputRequirement::PerRankComplete) ||
+                   r.output_requirement == static_cast<uint32_t>(OutputRequirement::GroupSumComplete)) &&
+                  r.dp_row_layout <= static_cast<uint32_t>(DpRowLayout::PackedByRank);
+  return ok ? ResultCode::Ok : ResultCode::ProtocolMismatch;
+}
+
+// A completion read by the attention side for the invocation (`sequence`, `rows`) it published.
+XP_HD inline ResultCode validate_expected(const CompletionRecord& c, uint32_t sequence, uint32_t rows) {
+  if (c.sequence != sequence) return ResultCode::ProtocolMismatch;
+  if (c.result_code != static_cast<uint32_t>(ResultCode::Ok)) return static_cast<ResultCode>(c.result_code);
+  return c.rows == rows ? ResultCode::Ok : ResultCode::ProtocolMismatch;
+}
+
+// ---------------------------------------------------------------- attention-DP row tables
+//
+// The rows that the data-parallel attention ranks of one Instance contribute to one merged invocation
+// (the reference's Coordinator checks the same before it admits a rendezvous, fabric/coordinator.cu:55-117).
+//   None:          one rank (dp_size 1); its rows are the payload.
+//   UniformByRank: every rank holds the same number of (padded) rows; payload = dp_size x that number.
+//   PackedByRank:  ranks hold their own counts back to back; an idle rank holds none; the counts sum to the payload.
+// `modes[r]` / `rank_rows[r]` are rank r's forward mode and row count. Returns the merged forward mode (Prefill if
+// any rank prefills, else Decode) or 0 when the table is inconsistent.
+XP_HD inline uint32_t dp_inspect_rows(DpRowLayout layout, uint32_t dp_size, uint32_t payload_rows, const uint32_t* modes,
+                                      const uint32_t* rank_rows) {
+  if (dp_size == 0 || (dp_size == 1) != (layout == DpRowLayout::None)) return 0;
+  const uint32_t idle = static_cast<uint32_t>(ForwardMode::Idle);
+  bool any_prefill = false, any_non_idle = false;
+  uint64_t packed = 0;
+  uint32_t uniform = 0;
+  for (uint32_t r = 0; r < dp_size; ++r) {
+    const uint32_t mode = modes[r], rows = rank_rows[r];
+    if (!valid_forward_mode(mode)) return 0;
+    if (layout == DpRowLayout::None && (mode == idle || rows != payload_rows)) return 0;
+    if (layout == DpRowLayout::PackedByRank && ((mode == idle) != (rows == 0))) return 0;
+    if (layout == DpRowLayout::UniformByRank && (rows == 0 || (r != 0 && rows != uniform))) return 0;
+    any_prefill = any_prefill || mode == static_cast<uint32_t>(ForwardMode::Prefill);
+    any_non_idle = any_non_idle || mode != idle;
+    if (layout == DpRowLayout::PackedByRank) {
+      if (rows > payload_rows - packed) return 0;
+      packed += rows;
+    } else if (layout == DpRowLayout::UniformByRank && r == 0) {
+      uniform = rows;
+    }
+  }
+  if (!any_non_idle) return 0;
+  if (layout == DpRowLayout::PackedByRank && packed != payload_rows) return 0;
+  if (layout == DpRowLayout::UniformByRank && (payload_rows % dp_size != 0 || payload_rows / dp_size != uniform)) return 0;
+  return static_cast<uint32_t>(any_prefill ? ForwardMode::Prefill : ForwardMode::Decode);
+}
+
+// First payload row of rank `r` in the merged invocation (valid tables only).
+XP_HD inline uint32_t dp_row_offset(DpRowLayout layout, uint32_t r, const uint32_t* rank_rows) {
+  if (layout == DpRowLayout::UniformByRank) return r * rank_rows[0];
+  uint32_t off = 0;
+  if (layout == DpRowLayout::PackedByRank)
+    for (uint32_t i = 0; i < r; ++i) off += rank_rows[i];
+  return off;
+}
+
 // ---------------------------------------------------------------- checked arithmetic
 
 struct Checked {

@@ -43,6 +43,34 @@ int xr_plan_atn_slot(uint64_t capacity_rows, uint64_t hidden, uint64_t tp, uint6
   return 0;
 }
 
+// 0 when the table is inconsistent, else the merged forward mode; offsets_out (may be null) receives every rank's
+// first row in the merged payload.
+uint32_t xr_dp_inspect_rows(uint32_t layout, uint32_t dp_size, uint32_t payload_rows, const uint32_t* modes,
+                            const uint32_t* rank_rows, uint32_t* offsets_out) {
+  if (layout > static_cast<uint32_t>(DpRowLayout::PackedByRank)) return 0;
+  const DpRowLayout l = static_cast<DpRowLayout>(layout);
+  const uint32_t merged = dp_inspect_rows(l, dp_size, payload_rows, modes, rank_rows);
+  if (merged != 0 && offsets_out != nullptr)
+    for (uint32_t r = 0; r < dp_size; ++r) offsets_out[r] = dp_row_offset(l, r, rank_rows);
+  return merged;
+}
+
+// Invocation record fields -> ResultCode of validate_expected.
+uint32_t xr_validate_invocation(uint32_t rows, uint32_t layer, uint32_t mode, uint32_t requirement, uint32_t dp_layout,
+                                uint32_t sequence, uint32_t completed, uint32_t capacity_rows, uint32_t num_layers) {
+  InvocationRecord r{};
+  r.rows = rows, r.layer_ordinal = layer, r.forward_mode = mode, r.output_requirement = requirement;
+  r.dp_row_layout = dp_layout, r.sequence = sequence;
+  return static_cast<uint32_t>(validate_expected(r, completed, capacity_rows, num_layers));
+}
+
+uint32_t xr_validate_completion(uint32_t result_code, uint32_t rows, uint32_t sequence, uint32_t want_sequence,
+                                uint32_t want_rows) {
+  CompletionRecord c{};
+  c.result_code = result_code, c.rows = rows, c.sequence = sequence;
+  return static_cast<uint32_t>(validate_expected(c, want_sequence, want_rows));
+}
+
 uint64_t xr_record_bytes(int which) {
   switch (which) {
     case 0: return sizeof(InvocationRecord);

@@ -18,7 +18,7 @@ from dataclasses import dataclass
 
 import torch
 
-from ..ffn import DenseFfnSpec, FfnModelSpec, GateUpOrder, MoeFfnSpec, RouterProjectionPrecision
+from ..ffn import DenseFfnSpec, FfnModelSpec, GateUpOrder, MoeFfnSpec, RouterProjectionPrecision, TopKWeightRounding
 from ..models.weights import FfnLayerWeights
 from .checkpoint import CheckpointKeyView
 
@@ -257,6 +257,8 @@ def materialize_layer_weights(spec: FfnModelSpec, view: CheckpointKeyView, layer
             w.extra[k] = got[k]
     w.extra["experts"] = (experts.start, experts.stop)
     w.extra["router_precision"] = l.router_precision.value
+    if l.topk_weight_rounding == TopKWeightRounding.LOGITS_DTYPE:
+        w.extra["round_topk_weights"] = True      # combine weights rounded to the logits' dtype (GPT-OSS)
     if "router_fp32" in got:
         w.extra["router_fp32"] = got["router_fp32"].contiguous()
     return w

@@ -60,6 +60,9 @@ def gated(g: torch.Tensor, u: torch.Tensor, act: str, transform: tuple[float, fl
 
 def dense_ffn(x: torch.Tensor, w: FfnLayerWeights, act: str = "silu") -> torch.Tensor:
     gu = F.linear(x, w.gate_up, w.gate_up_bias.to(x.dtype) if w.gate_up_bias is not None else None)
+    if not w.extra.get("gated", True):       # a single up projection (OPT): act(x W1 + b1) W2 + b2
+        h = activation(act, gu.float()).to(gu.dtype)
+        return F.linear(h, w.down, w.down_bias.to(x.dtype) if w.down_bias is not None else None)
     inter = gu.shape[-1] // 2
     h = gated(gu[..., :inter], gu[..., inter:], act, w.extra.get("gate_transform"))
     return F.linear(h, w.down, w.down_bias.to(x.dtype) if w.down_bias is not None else None)
@@ -99,6 +102,8 @@ def moe_ffn(x: torch.Tensor, w: FfnLayerWeights, cfg: ModelConfig) -> torch.Tens
         logits = logits.float() + w.extra["router_bias"].float()    # payload-precision logits, bias added in fp32
     ids, weights = route_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.router_scoring,
                               w.extra.get("correction_bias"), cfg.routed_scaling_factor)
+    if w.extra.get("round_topk_weights"):
+        weights = weights.to(x.dtype).float()
     out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
     inter = w.gate_up.shape[1] // 2
     for e in range(w.gate_up.shape[0]):

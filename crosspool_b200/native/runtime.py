@@ -26,6 +26,10 @@ def lib() -> C.CDLL:
     sig = {
         "xr_plan_ffn_slot": (C.c_int, [u64, u64, u64, u64, C.POINTER(u64)]),
         "xr_plan_atn_slot": (C.c_int, [u64, u64, u64, u64, C.POINTER(u64)]),
+        "xr_dp_inspect_rows": (C.c_uint32, [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
+                                            C.POINTER(C.c_uint32)]),
+        "xr_validate_invocation": (C.c_uint32, [C.c_uint32] * 9),
+        "xr_validate_completion": (C.c_uint32, [C.c_uint32] * 5),
         "xr_record_bytes": (u64, [C.c_int]),
         "xr_mailbox_transition_allowed": (C.c_int, [u32, u32]),
         "xr_sched_create": (vp, [u32, u32, u32, u64]),
@@ -122,6 +126,28 @@ def plan_atn_slot(capacity_rows: int, hidden: int, tp: int, elem_bytes: int = 2)
     if lib().xr_plan_atn_slot(capacity_rows, hidden, tp, elem_bytes, out) != 0:
         raise ValueError("atn slot layout overflows")
     return AtnSlotLayout(*out)
+
+
+def dp_inspect_rows(layout: int, payload_rows: int, modes: list[int], rank_rows: list[int]) -> tuple[int, list[int]] | None:
+    """Checks the row table of an Instance's data-parallel attention ranks for one merged invocation (the native
+    ``dp_inspect_rows``, also compiled for the device). Returns ``(merged forward mode, first row of every rank)`` or
+    ``None`` when the table is inconsistent. Reference: src/cext/fabric/coordinator.cu:55-117."""
+    n = len(modes)
+    if n == 0 or n != len(rank_rows):
+        return None
+    m, r, off = (C.c_uint32 * n)(*modes), (C.c_uint32 * n)(*rank_rows), (C.c_uint32 * n)()
+    merged = lib().xr_dp_inspect_rows(layout, n, payload_rows, m, r, off)
+    return (int(merged), list(off)) if merged else None
+
+
+def validate_invocation(rows: int, layer: int, mode: int, sequence: int, *, completed: int, capacity_rows: int, num_layers: int,
+                        requirement: int = 1, dp_layout: int = 0) -> int:
+    """ResultCode (0 ok, 2 protocol mismatch) of an invocation record against what its consumer expects."""
+    return int(lib().xr_validate_invocation(rows, layer, mode, requirement, dp_layout, sequence, completed, capacity_rows, num_layers))
+
+
+def validate_completion(result_code: int, rows: int, sequence: int, *, want_sequence: int, want_rows: int) -> int:
+    return int(lib().xr_validate_completion(result_code, rows, sequence, want_sequence, want_rows))
 
 
 class LaneScheduler:

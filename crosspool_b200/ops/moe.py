@@ -172,7 +172,8 @@ def moe_forward(x: torch.Tensor, w: FfnLayerWeights, cfg: ModelConfig, out: torc
         logits = router_project_fp32(x, w, ws.logits32[:rows])
     router_topk(logits, e_total, k, out_ids=ws.ids[:rows], out_weights=ws.weights[:rows],
                 sigmoid=cfg.router_scoring == "sigmoid", renormalize=cfg.norm_topk_prob, scale=cfg.routed_scaling_factor,
-                correction_bias=w.extra.get("correction_bias"), logit_bias=w.extra.get("router_bias"))
+                correction_bias=w.extra.get("correction_bias"), logit_bias=w.extra.get("router_bias"),
+                round_weights_bf16=bool(w.extra.get("round_topk_weights")))
     # 2. order the routes of the local experts, build the tile tables
     bn = _tile_width(rows, k, n_local)
     r = native.RouteArgs()

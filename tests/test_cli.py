@@ -30,3 +30,10 @@ def test_missing_required_settings_exit_2(capsys, monkeypatch):
     monkeypatch.delenv("XPOOL_CONFIG", raising=False)
     assert cli.main(["memory-profile"]) == 2
     assert "configuration error" in capsys.readouterr().err
+
+
+def test_qualify_subcommand_passes_option_like_arguments_through(capsys):
+    from crosspool_b200.cli import main as cli
+
+    assert cli.main(["qualify", "--arch", "Qwen2ForCausalLM"]) == 0
+    assert "Qwen2ForCausalLM: PASS" in capsys.readouterr().out

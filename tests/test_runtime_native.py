@@ -212,3 +212,48 @@ def test_trace_buffer_drops_when_full_and_never_wraps():
     n, dropped = t.counts()
     assert (n, dropped) == (4, 2)
     assert t.events() == [(1, i, i * 2, 1000 + i) for i in range(4)]
+
+
+def test_dp_row_tables_follow_the_coordinators_admission_rules():
+    """Scenarios of the reference's rendezvous inspection (src/cext/fabric/coordinator.cu:55-117) on the function
+    that host and device share."""
+    from crosspool_b200.native import runtime as rt
+
+    P, D, I = rt.MODE_PREFILL, rt.MODE_DECODE, rt.MODE_IDLE
+    # one rank: layout None, its rows are the payload, never idle
+    assert rt.dp_inspect_rows(rt.DP_NONE, 7, [D], [7]) == (D, [0])
+    assert rt.dp_inspect_rows(rt.DP_NONE, 7, [D], [6]) is None and rt.dp_inspect_rows(rt.DP_NONE, 7, [I], [7]) is None
+    assert rt.dp_inspect_rows(rt.DP_UNIFORM_BY_RANK, 7, [D], [7]) is None        # a layout needs more than one rank
+    assert rt.dp_inspect_rows(rt.DP_NONE, 8, [D, D], [4, 4]) is None             # ... and several ranks need a layout
+    # uniform: equal (padded) counts, payload = ranks x count; an idle rank still holds its padded rows
+    assert rt.dp_inspect_rows(rt.DP_UNIFORM_BY_RANK, 12, [D, P, I], [4, 4, 4]) == (P, [0, 4, 8])
+    assert rt.dp_inspect_rows(rt.DP_UNIFORM_BY_RANK, 12, [D, D, D], [4, 4, 4]) == (D, [0, 4, 8])
+    assert rt.dp_inspect_rows(rt.DP_UNIFORM_BY_RANK, 12, [D, D, D], [4, 5, 3]) is None
+    assert rt.dp_inspect_rows(rt.DP_UNIFORM_BY_RANK, 13, [D, D, D], [4, 4, 4]) is None
+    assert rt.dp_inspect_rows(rt.DP_UNIFORM_BY_RANK, 0, [D, D], [0, 0]) is None
+    # packed: own counts back to back; idle exactly when a rank holds nothing; the counts sum to the payload
+    assert rt.dp_inspect_rows(rt.DP_PACKED_BY_RANK, 9, [P, I, D], [6, 0, 3]) == (P, [0, 6, 6])
+    assert rt.dp_inspect_rows(rt.DP_PACKED_BY_RANK, 9, [P, D, D], [6, 0, 3]) is None    # active rank without rows
+    assert rt.dp_inspect_rows(rt.DP_PACKED_BY_RANK, 9, [P, I, D], [6, 1, 2]) is None    # idle rank with rows
+    assert rt.dp_inspect_rows(rt.DP_PACKED_BY_RANK, 9, [P, D], [6, 4]) is None          # more rows than the payload
+    assert rt.dp_inspect_rows(rt.DP_PACKED_BY_RANK, 9, [P, D], [6, 2]) is None          # fewer
+    assert rt.dp_inspect_rows(rt.DP_PACKED_BY_RANK, 0, [I, I], [0, 0]) is None          # nobody has work
+    assert rt.dp_inspect_rows(rt.DP_PACKED_BY_RANK, 4, [D, 3], [2, 2]) is None          # unknown forward mode
+
+
+def test_records_are_checked_against_what_the_consumer_expects():
+    from crosspool_b200.native import runtime as rt
+
+    ok = dict(completed=4, capacity_rows=128, num_layers=28)
+    assert rt.validate_invocation(16, 3, rt.MODE_DECODE, 5, **ok) == 0
+    assert rt.validate_invocation(0, 3, rt.MODE_IDLE, 5, **ok) == 0                       # an idle step carries no rows
+    for bad in (dict(rows=129), dict(rows=0), dict(layer=28), dict(mode=3), dict(sequence=6), dict(sequence=4)):
+        a = dict(rows=16, layer=3, mode=rt.MODE_DECODE, sequence=5)
+        a.update(bad)
+        assert rt.validate_invocation(a["rows"], a["layer"], a["mode"], a["sequence"], **ok) == 2, bad
+    assert rt.validate_invocation(16, 3, rt.MODE_DECODE, 5, requirement=7, **ok) == 2
+    assert rt.validate_invocation(16, 3, rt.MODE_DECODE, 5, dp_layout=3, **ok) == 2
+    assert rt.validate_completion(0, 16, 5, want_sequence=5, want_rows=16) == 0
+    assert rt.validate_completion(0, 15, 5, want_sequence=5, want_rows=16) == 2           # rows differ
+    assert rt.validate_completion(0, 16, 4, want_sequence=5, want_rows=16) == 2           # stale record
+    assert rt.validate_completion(3, 0, 5, want_sequence=5, want_rows=16) == 3            # the producer's own failure code
