@@ -32,14 +32,16 @@ def init(role: str, device: int | None = None, config=None, argv_overrides: dict
 
     cfg = config if config is not None else cfgmod.init_global_config(argv_overrides or {})
     xlog.init_logging(role, getattr(cfg, "logging_level", "info"), getattr(cfg, "logging_color", "auto"))
+    options = {n: bool(getattr(cfg, f"debug_{n}_enable", False)) for n in native_runtime.DEBUG_OPTION_NAMES}
     if role != "Daemon":
         native_runtime.lib()  # loads the host library and checks its ABI number
+        native_runtime.runtime_initialize(role, device, options)   # the native library's own record of role / device / options
         if device is not None:
             import torch
 
             if torch.cuda.is_available():
                 torch.cuda.set_device(device)
-                native.kernels()
+                native.set_debug_options(options)                   # ... and their mirror in device constant memory
     obs = devkit.observers_for_role(role, cfg)
     _state = RuntimeState(role, device, cfg, obs)
     return _state
@@ -52,3 +54,9 @@ def get_runtime_role() -> str | None:
 def reset_for_tests() -> None:
     global _state
     _state = None
+    try:
+        from .native import runtime as native_runtime
+
+        native_runtime.runtime_reset_for_tests()
+    except Exception:
+        pass

@@ -310,6 +310,9 @@ int xp_fill_u32(void* p, uint32_t v, size_t n, void* stream);
 int xp_l2_flush(void* p, size_t bytes, void* stream);
 
 int xp_abi_version(void);
+/* device mirror of the process's debug options: transport, fabric, graph, routing observer switches */
+int xp_debug_options_set(const uint32_t* four);
+int xp_debug_options_get(uint32_t* four);
 int xp_gemm_plan(const XpGemmArgs* a, XpGemmPlan* plan);
 int xp_quant_act_fp8(const void* x, void* xq, float* scales, int rows, int k, int ldx, int ldq, int ld_scale, void* stream);
 int xp_gemm(const XpGemmArgs* a);

@@ -35,6 +35,25 @@ enum class ResultCode : uint32_t { Ok = 0, Shutdown = 1, ProtocolMismatch = 2, T
 enum class LayerKind : uint32_t { Dense = 1, Moe = 2 };
 enum class PayloadDtype : uint32_t { BF16 = 1, FP16 = 2 };
 
+// ---------------------------------------------------------------- runtime state and debug options
+//
+// One per process: which role the process plays, on which device, and which observers are switched on
+// (the reference's RuntimeState and debug Options, runtime.hpp:17-22 and debug/options.hpp). The options are
+// mirrored into constant memory of the kernel library (`xp_debug_options_set`) so that device code can read them.
+struct DebugOptions {
+  uint32_t transport_observer;
+  uint32_t fabric_observer;
+  uint32_t graph_observer;
+  uint32_t ffn_routing_observer;
+};
+
+struct RuntimeState {
+  uint32_t initialized;
+  uint32_t role;     // RuntimeRole
+  int32_t device;    // -1: none (the daemon)
+  DebugOptions options;
+};
+
 // ---------------------------------------------------------------- mailbox
 
 // Single-producer single-consumer mailbox between an Instance rank and the

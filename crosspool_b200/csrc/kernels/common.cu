@@ -1,9 +1,28 @@
 // ABI version and small device utilities shared by every kernel file.
 #include "xpool/api.h"
+#include "xpool/protocol.hpp"
 
 #include <cuda_runtime.h>
 
 extern "C" int xp_abi_version(void) { return XP_ABI_VERSION; }
+
+// Device mirror of the process's debug options (see xpool::DebugOptions): set once at bootstrap, readable by device
+// code of this library as `xpool::g_debug_options_d`.
+namespace xpool {
+__constant__ DebugOptions g_debug_options_d;
+}
+
+extern "C" int xp_debug_options_set(const uint32_t* four) {
+  xpool::DebugOptions o{four[0], four[1], four[2], four[3]};
+  return cudaMemcpyToSymbol(xpool::g_debug_options_d, &o, sizeof(o)) == cudaSuccess ? 0 : -100;
+}
+
+extern "C" int xp_debug_options_get(uint32_t* four) {
+  xpool::DebugOptions o{};
+  if (cudaMemcpyFromSymbol(&o, xpool::g_debug_options_d, sizeof(o)) != cudaSuccess) return -100;
+  four[0] = o.transport_observer, four[1] = o.fabric_observer, four[2] = o.graph_observer, four[3] = o.ffn_routing_observer;
+  return 0;
+}
 
 namespace {
 __global__ void fill_u32_kernel(uint32_t* p, uint32_t v, size_t n) {

@@ -1,6 +1,7 @@
 // C ABI of libxpool_runtime.so (host-only): layouts, Lane scheduler, shared
 // memory, the ECS control channel, the CPU transport mailbox and trace buffers.
 // Loaded with ctypes from crosspool_b200/native/runtime.py.
+#include <mutex>
 #include <string.h>
 
 #include <memory>
@@ -69,6 +70,40 @@ uint32_t xr_validate_completion(uint32_t result_code, uint32_t rows, uint32_t se
   CompletionRecord c{};
   c.result_code = result_code, c.rows = rows, c.sequence = sequence;
   return static_cast<uint32_t>(validate_expected(c, want_sequence, want_rows));
+}
+
+// Process-wide runtime state. Initialising twice with the same role and device is a no-op (options are replaced);
+// a different role or device is refused (-1); an unknown role is -2.
+static RuntimeState g_runtime_state{0u, 0u, -1, DebugOptions{}};
+static std::mutex g_runtime_mu;
+
+int xr_runtime_initialize(uint32_t role, int32_t device, const uint32_t* options4) {
+  if (role < static_cast<uint32_t>(RuntimeRole::Daemon) || role > static_cast<uint32_t>(RuntimeRole::FfnAgent)) return -2;
+  std::lock_guard<std::mutex> g(g_runtime_mu);
+  if (g_runtime_state.initialized != 0 && (g_runtime_state.role != role || g_runtime_state.device != device)) return -1;
+  g_runtime_state.initialized = 1;
+  g_runtime_state.role = role;
+  g_runtime_state.device = device;
+  if (options4 != nullptr)
+    g_runtime_state.options = DebugOptions{options4[0], options4[1], options4[2], options4[3]};
+  return 0;
+}
+
+// out7: initialized, role, device (as two's complement), four option words
+void xr_runtime_state(uint32_t* out7) {
+  std::lock_guard<std::mutex> g(g_runtime_mu);
+  out7[0] = g_runtime_state.initialized;
+  out7[1] = g_runtime_state.role;
+  out7[2] = static_cast<uint32_t>(g_runtime_state.device);
+  out7[3] = g_runtime_state.options.transport_observer;
+  out7[4] = g_runtime_state.options.fabric_observer;
+  out7[5] = g_runtime_state.options.graph_observer;
+  out7[6] = g_runtime_state.options.ffn_routing_observer;
+}
+
+void xr_runtime_reset_for_tests(void) {
+  std::lock_guard<std::mutex> g(g_runtime_mu);
+  g_runtime_state = RuntimeState{0u, 0u, -1, DebugOptions{}};
 }
 
 uint64_t xr_record_bytes(int which) {

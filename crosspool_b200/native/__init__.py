@@ -391,6 +391,8 @@ class RouteArgs(C.Structure):
 
 def _declare_moe(lib: C.CDLL) -> None:
     sig = {
+        "xp_debug_options_set": [C.POINTER(C.c_uint32)],
+        "xp_debug_options_get": [C.POINTER(C.c_uint32)],
         "xp_router_topk": [C.POINTER(RouterArgs), C.c_void_p],
         "xp_router_fp32": [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p],
         "xp_moe_route": [C.POINTER(RouteArgs), C.c_void_p],
@@ -402,3 +404,18 @@ def _declare_moe(lib: C.CDLL) -> None:
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = args
+
+
+DEBUG_OPTION_NAMES = ("transport_observer", "fabric_observer", "graph_observer", "ffn_routing_observer")
+
+
+def set_debug_options(options: dict) -> None:
+    """Uploads the process's debug options to the kernel library's constant memory on the current device."""
+    four = (C.c_uint32 * 4)(*[int(bool(options.get(n, False))) for n in DEBUG_OPTION_NAMES])
+    check(kernels().xp_debug_options_set(four), "xp_debug_options_set", 0)
+
+
+def get_debug_options() -> dict:
+    four = (C.c_uint32 * 4)()
+    check(kernels().xp_debug_options_get(four), "xp_debug_options_get", 0)
+    return {n: bool(four[i]) for i, n in enumerate(DEBUG_OPTION_NAMES)}

@@ -26,6 +26,9 @@ def lib() -> C.CDLL:
     sig = {
         "xr_plan_ffn_slot": (C.c_int, [u64, u64, u64, u64, C.POINTER(u64)]),
         "xr_plan_atn_slot": (C.c_int, [u64, u64, u64, u64, C.POINTER(u64)]),
+        "xr_runtime_initialize": (C.c_int, [C.c_uint32, C.c_int32, C.POINTER(C.c_uint32)]),
+        "xr_runtime_state": (None, [C.POINTER(C.c_uint32)]),
+        "xr_runtime_reset_for_tests": (None, []),
         "xr_dp_inspect_rows": (C.c_uint32, [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
                                             C.POINTER(C.c_uint32)]),
         "xr_validate_invocation": (C.c_uint32, [C.c_uint32] * 9),
@@ -126,6 +129,46 @@ def plan_atn_slot(capacity_rows: int, hidden: int, tp: int, elem_bytes: int = 2)
     if lib().xr_plan_atn_slot(capacity_rows, hidden, tp, elem_bytes, out) != 0:
         raise ValueError("atn slot layout overflows")
     return AtnSlotLayout(*out)
+
+
+ROLE_IDS = {"Daemon": 1, "Instance": 2, "AtnAgent": 3, "FfnAgent": 4}
+DEBUG_OPTION_NAMES = ("transport_observer", "fabric_observer", "graph_observer", "ffn_routing_observer")
+
+
+@dataclass(frozen=True)
+class NativeRuntimeState:
+    initialized: bool
+    role: str | None
+    device: int | None
+    options: dict
+
+
+def runtime_initialize(role: str, device: int | None, options: dict | None = None) -> None:
+    """Records the process's role, device and debug options in the native library (one per process: the same role and
+    device again only replaces the options, anything else is refused). Reference: ``native.initialize(role, device,
+    debug_options)``, src/cext/runtime.cpp."""
+    if role not in ROLE_IDS:
+        raise ValueError(f"unknown role {role!r}")
+    opts = (C.c_uint32 * 4)(*[int(bool((options or {}).get(n, False))) for n in DEBUG_OPTION_NAMES])
+    rc = lib().xr_runtime_initialize(ROLE_IDS[role], -1 if device is None else int(device), opts)
+    if rc == -1:
+        st = runtime_state()
+        raise RuntimeError(f"process already initialised as {st.role} on device {st.device}")
+    if rc != 0:
+        raise ValueError(f"xr_runtime_initialize failed ({rc})")
+
+
+def runtime_state() -> NativeRuntimeState:
+    out = (C.c_uint32 * 7)()
+    lib().xr_runtime_state(out)
+    names = {v: k for k, v in ROLE_IDS.items()}
+    dev = C.c_int32(out[2]).value
+    return NativeRuntimeState(bool(out[0]), names.get(out[1]), None if dev < 0 else dev,
+                              {n: bool(out[3 + i]) for i, n in enumerate(DEBUG_OPTION_NAMES)})
+
+
+def runtime_reset_for_tests() -> None:
+    lib().xr_runtime_reset_for_tests()
 
 
 def dp_inspect_rows(layout: int, payload_rows: int, modes: list[int], rank_rows: list[int]) -> tuple[int, list[int]] | None:

@@ -86,3 +86,15 @@ def test_swiglu_unfused():
     y = norm.swiglu(gu)
     ref = torch.nn.functional.silu(gu[:, :256].float()) * gu[:, 256:].float()
     torch.testing.assert_close(y.float(), ref, atol=2e-2, rtol=2e-2)
+
+
+def test_debug_options_round_trip_through_device_constant_memory():
+    from crosspool_b200 import native
+
+    before = native.get_debug_options()
+    try:
+        native.set_debug_options({"fabric_observer": True, "ffn_routing_observer": True})
+        assert native.get_debug_options() == {"transport_observer": False, "fabric_observer": True, "graph_observer": False,
+                                              "ffn_routing_observer": True}
+    finally:
+        native.set_debug_options(before)

@@ -257,3 +257,47 @@ def test_records_are_checked_against_what_the_consumer_expects():
     assert rt.validate_completion(0, 15, 5, want_sequence=5, want_rows=16) == 2           # rows differ
     assert rt.validate_completion(0, 16, 4, want_sequence=5, want_rows=16) == 2           # stale record
     assert rt.validate_completion(3, 0, 5, want_sequence=5, want_rows=16) == 3            # the producer's own failure code
+
+
+def test_native_runtime_state_is_one_per_process():
+    from crosspool_b200.native import runtime as rt
+
+    rt.runtime_reset_for_tests()
+    try:
+        assert rt.runtime_state() == rt.NativeRuntimeState(False, None, None, {n: False for n in rt.DEBUG_OPTION_NAMES})
+        rt.runtime_initialize("FfnAgent", 3, {"fabric_observer": True})
+        st = rt.runtime_state()
+        assert (st.initialized, st.role, st.device) == (True, "FfnAgent", 3)
+        assert st.options == {"transport_observer": False, "fabric_observer": True, "graph_observer": False,
+                              "ffn_routing_observer": False}
+        rt.runtime_initialize("FfnAgent", 3, {"graph_observer": True})          # same identity: options replaced
+        assert rt.runtime_state().options["graph_observer"] and not rt.runtime_state().options["fabric_observer"]
+        with pytest.raises(RuntimeError, match="already initialised as FfnAgent on device 3"):
+            rt.runtime_initialize("AtnAgent", 3)
+        with pytest.raises(RuntimeError):
+            rt.runtime_initialize("FfnAgent", 4)
+        with pytest.raises(ValueError):
+            rt.runtime_initialize("Scheduler", 0)
+        rt.runtime_reset_for_tests()
+        rt.runtime_initialize("Daemon", None)
+        assert rt.runtime_state().device is None and rt.runtime_state().role == "Daemon"
+    finally:
+        rt.runtime_reset_for_tests()
+
+
+def test_bootstrap_records_role_device_and_observer_switches_natively():
+    from crosspool_b200 import bootstrap
+    from crosspool_b200.config import load_config
+    from crosspool_b200.native import runtime as rt
+
+    bootstrap.reset_for_tests()
+    try:
+        cfg = load_config(env={"XPOOL_DEBUG_FABRIC_OBSERVER_ENABLE": "1"}, toml_text="[atn]\ndevices = [0]\n[ffn]\ndevices = [1]\n",
+                          require=False)
+        bootstrap.init("Instance", None, config=cfg)
+        st = rt.runtime_state()
+        assert st.role == "Instance" and st.device is None and st.options["fabric_observer"] and not st.options["graph_observer"]
+        with pytest.raises(RuntimeError):
+            bootstrap.init("FfnAgent", None, config=cfg)
+    finally:
+        bootstrap.reset_for_tests()
