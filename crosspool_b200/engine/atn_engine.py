@@ -485,6 +485,20 @@ class AttentionEngine:
         self._launch_prefill(chosen, rows)
         return self._collect_prefill()
 
+    @staticmethod
+    def _fill_chunk_rows(hv, P: int, r: int, s: Sequence, n: int, table: list[int], ps: int) -> None:
+        """Token ids, positions and KV slots of ``n`` chunk rows of sequence ``s`` starting at row ``r`` of the pinned
+        prefill metadata (three regions of ``P`` words). Vectorised: a 4096-token chunk is three array operations, not
+        8192 interpreter iterations."""
+        import numpy as np
+
+        hv[r:r + n] = s.fill_tokens(s.computed, n)
+        pos = np.arange(s.computed, s.computed + n, dtype=np.int64)
+        hv[P + r:P + r + n] = pos
+        first, last = s.computed // ps, (s.computed + n - 1) // ps
+        pages = np.asarray(table[first:last + 1], dtype=np.int64)
+        hv[2 * P + r:2 * P + r + n] = pages[pos // ps - first] * ps + pos % ps
+
     def _launch_prefill(self, chosen: list[tuple[Sequence, int]], rows: int) -> None:
         """Fills the chunk's pinned metadata and enqueues the chunk; ``_collect_prefill`` finishes it."""
         e, P, S = self.ecfg, self.ecfg.prefill_chunk, self.ecfg.max_prefill_seqs
@@ -493,16 +507,8 @@ class AttentionEngine:
         r = 0
         ps = e.page_size
         for i, (s, n) in enumerate(chosen):
-            toks = s.fill_tokens(s.computed, n)
-            hv[r:r + n] = toks
-            for j in range(n):
-                p = s.computed + j
-                hv[P + r + j] = p
+            self._fill_chunk_rows(hv, P, r, s, n, self.kv.tables[s.seq_id], ps)
             t = self.kv.tables[s.seq_id]
-            base = s.computed
-            for j in range(n):
-                p = base + j
-                hv[2 * P + r + j] = t[p // ps] * ps + p % ps
             hv[b + i] = r
             hv[b + S + i] = n
             hv[b + 2 * S + i] = s.computed

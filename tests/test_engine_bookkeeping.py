@@ -157,3 +157,29 @@ def test_lockstep_step_still_runs_every_instance_once_per_call():
     a, b = _FakeEngine("a", 3, 0), _FakeEngine("b", 1, 0)
     dep = Deployment([InstanceHandle("a", None, a), InstanceHandle("b", None, b)])
     assert set(dep.step().tokens) == {"a", "b"} and set(dep.step().tokens) == {"a"}
+
+
+def test_vectorised_chunk_metadata_equals_the_per_token_definition():
+    import numpy as np
+
+    rnd = __import__("random").Random(4)
+    for ps in (16, 64):
+        for _ in range(20):
+            P = 512
+            prompt = [rnd.randrange(1000) for _ in range(rnd.randrange(1, 400))]
+            s = Sequence(0, prompt, 8)
+            s.generated = [rnd.randrange(1000) for _ in range(rnd.randrange(0, 5))]
+            s.refill_len = s.total_len if s.generated else 0
+            fill = s.fill_len
+            s.computed = rnd.randrange(0, fill)
+            n = rnd.randrange(1, min(P, fill - s.computed) + 1)
+            r = rnd.randrange(0, P - n + 1)
+            table = rnd.sample(range(5000), (fill + ps) // ps + 1)
+            hv = np.full(3 * P, -7, dtype=np.int32)
+            AttentionEngine._fill_chunk_rows(hv, P, r, s, n, table, ps)
+            want = np.full(3 * P, -7, dtype=np.int32)
+            toks = s.fill_tokens(s.computed, n)
+            for j in range(n):
+                p = s.computed + j
+                want[r + j], want[P + r + j], want[2 * P + r + j] = toks[j], p, table[p // ps] * ps + p % ps
+            assert np.array_equal(hv, want)
