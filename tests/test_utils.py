@@ -87,10 +87,12 @@ def test_background_thread_runs_periodically_and_surfaces_errors():
 
 def test_first_signal_requests_shutdown():
     got = []
+    before = signal.getsignal(signal.SIGTERM)
     with sighandler.ShutdownSignals(on_request=got.append) as s:
+        assert signal.getsignal(signal.SIGTERM) is not before          # the scope installs its own handler
         os.kill(os.getpid(), signal.SIGTERM)
         assert s.requested.wait(2) and got == [signal.SIGTERM] and s.signum == signal.SIGTERM
-    assert signal.getsignal(signal.SIGTERM) in (signal.SIG_DFL, signal.default_int_handler) or True
+    assert signal.getsignal(signal.SIGTERM) == before                   # and puts the previous one back
 
 
 def test_mps_endpoint_only_describes_an_environment():
