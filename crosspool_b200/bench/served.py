@@ -687,6 +687,8 @@ def run_multi_gpu(args) -> int:
         policy = {"fifo": rt.POLICY_FIFO, "random": rt.POLICY_RANDOM, "slo": rt.POLICY_SLO}[args.policy]
         ctx = F.build_rank(topo, rank, dev, ecfgs, group=ctl, n_lanes=args.lanes, policy=policy, kv_for=kv_for)
         if ctx.role == "ffn":
+            if getattr(args, "trace_dir", ""):
+                ctx.ffn.enable_trace(1 << 21)      # Lane events of the whole run (24 bytes each)
             ctx.ffn.start(lease_ms=20.0)
     else:
         from ..parallel import nccl_baseline as NB
@@ -774,6 +776,15 @@ def run_multi_gpu(args) -> int:
     if pools:
         ecs_events = pools[0].close()
     lane_stats = ctx.ffn.stats() if ctx.role == "ffn" else None
+    if lane_stats is not None and getattr(args, "trace_dir", "") and args.impl == "xpool":
+        from ..devkit.observers import FabricObserver, lane_busy_summary
+
+        art = FabricObserver(ctx.ffn).collect()
+        lane_stats["busy"] = lane_busy_summary(art.events, args.lanes)
+        lane_stats["trace_dropped"] = art.dropped
+        os.makedirs(args.trace_dir, exist_ok=True)
+        with open(os.path.join(args.trace_dir, f"fabric.rank{rank}.json"), "w", encoding="utf-8") as f:
+            json.dump({"rank": rank, "summary": lane_stats["busy"], "dropped": art.dropped, "events": art.events[:20000]}, f)
     gathered = [None] * world
     dist.all_gather_object(gathered, {"rank": rank, "role": ctx.role, "summary": summary, "clocks": clocks, "lanes": lane_stats,
                                       "correctness": correctness, "ecs": ecs_events, "failure": failure}, group=ctl)

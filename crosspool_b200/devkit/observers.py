@@ -94,6 +94,38 @@ class FabricObserver(_Base):
         return TraceArtifact(self.name, self.role, os.getpid(), ev, dropped)
 
 
+def lane_busy_summary(events: list[dict], lanes: int) -> dict:
+    """How busy the Lanes of one FFN GPU were, from its fabric observer's events: an invocation occupies a Lane from
+    ``admitted`` to ``completed`` (device timestamps); the busy fraction is the sum of those spans over the observed
+    interval times the number of Lanes. Also the service-time distribution and the rows served."""
+    open_at: dict[int, list[int]] = {}
+    spans: list[int] = []
+    rows = 0
+    first = last = None
+    for e in events:
+        ts = e["ts_ns"]
+        first = ts if first is None else min(first, ts)
+        last = ts if last is None else max(last, ts)
+        if e["name"] == "admitted":
+            open_at.setdefault(e["instance"], []).append(ts)
+            rows += e.get("rows", 0)
+        elif e["name"] == "completed":
+            q = open_at.get(e["instance"])
+            if q:
+                spans.append(ts - q.pop(0))
+    if not spans or first is None or last <= first:
+        return {"invocations": len(spans), "busy_fraction": 0.0}
+    spans.sort()
+    busy = sum(spans)
+
+    def pct(p):
+        return spans[min(len(spans) - 1, int(p * (len(spans) - 1)))] / 1e3
+
+    return {"invocations": len(spans), "rows": rows, "observed_s": round((last - first) / 1e9, 3),
+            "busy_fraction": round(busy / ((last - first) * max(1, lanes)), 4),
+            "service_us": {"mean": round(busy / len(spans) / 1e3, 1), "p50": round(pct(0.5), 1), "p99": round(pct(0.99), 1)}}
+
+
 class AtnFabricObserver(_Base):
     """Drains the device event buffer of an attention-side Fabric port (``FabricFfnPort.enable_trace``) and groups the
     events of each invocation into a timeline: published -> wait_begin -> wait_end | wait_timed_out | wait_cancelled,

@@ -79,3 +79,19 @@ def test_routing_observer_keeps_a_bounded_number_of_samples(tmp_path):
 
     t = load_file(str(p.with_suffix(".safetensors")))
     assert set(t) == {"sample0.layer0.ids", "sample0.layer0.weights", "sample1.layer1.ids", "sample1.layer1.weights"}
+
+
+def test_lane_busy_summary_pairs_admissions_with_completions_per_instance():
+    from crosspool_b200.devkit.observers import lane_busy_summary
+
+    ev = [{"name": "discovered", "ts_ns": 1000, "instance": 0, "sequence": 1},
+          {"name": "admitted", "ts_ns": 2000, "instance": 0, "layer": 0, "rows": 8},
+          {"name": "admitted", "ts_ns": 2500, "instance": 1, "layer": 3, "rows": 4},
+          {"name": "completed", "ts_ns": 42000, "instance": 0, "sequence": 1},
+          {"name": "completed", "ts_ns": 62500, "instance": 1, "sequence": 1},
+          {"name": "idle", "ts_ns": 101000, "lane": 0, "count": 1}]
+    s = lane_busy_summary(ev, lanes=2)
+    assert s["invocations"] == 2 and s["rows"] == 12
+    assert s["busy_fraction"] == round((40000 + 60000) / (100000 * 2), 4)
+    assert s["service_us"] == {"mean": 50.0, "p50": 40.0, "p99": 40.0}
+    assert lane_busy_summary([], 2) == {"invocations": 0, "busy_fraction": 0.0}
