@@ -11,7 +11,6 @@ rank 0 only so that the reduction adds it once.
 
 from __future__ import annotations
 
-import queue
 import threading
 from concurrent.futures import ThreadPoolExecutor
 from dataclasses import dataclass

@@ -1,5 +1,4 @@
 """Attention-side kernels against fp32 PyTorch restatements."""
-import math
 
 import pytest
 import torch
