@@ -89,12 +89,14 @@ class Deployment:
                 if not e.step_ready():
                     waiting.append(i)
                     continue
+                progressed = progressed or getattr(e, "step_is_device_work", True)
                 res.tokens[i.model_id] = e.collect_step()
-                progressed = True
             if e.has_work:
                 e.launch_step()
-                progressed = True
-        if not progressed and waiting:
+                progressed = progressed or getattr(e, "step_is_device_work", True)
+        if not progressed and not waiting:
+            time.sleep(poll_s)          # every Instance with work is waiting for something on the host (KV capacity)
+        elif not progressed and waiting:
             if len(waiting) == 1:       # nothing else to overlap with: wait for it (releases the interpreter lock)
                 i = waiting[0]
                 res.tokens[i.model_id] = i.engine.collect_step()

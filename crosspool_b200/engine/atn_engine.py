@@ -720,6 +720,12 @@ class AttentionEngine:
     def step_in_flight(self) -> bool:
         return self._pending is not None or self._pre_inflight is not None or self._inflight is not None
 
+    @property
+    def step_is_device_work(self) -> bool:
+        """False when the step in flight put nothing on the GPU (nothing could be admitted, e.g. while the Instance
+        waits for KV capacity): a driver should not spin on such steps."""
+        return self._pre_inflight is not None or self._inflight is not None or bool(self._pending)
+
     def step_ready(self) -> bool:
         """Whether ``collect_step`` would return without waiting for the GPU (a driver of several co-located
         Instances polls this so that a long prefill chunk of one does not hold back the steps of the others)."""

@@ -183,3 +183,28 @@ def test_vectorised_chunk_metadata_equals_the_per_token_definition():
                 p = s.computed + j
                 want[r + j], want[P + r + j], want[2 * P + r + j] = toks[j], p, table[p // ps] * ps + p % ps
             assert np.array_equal(hv, want)
+
+
+def test_event_driven_stepping_sleeps_while_every_instance_waits_on_the_host():
+    """An Instance that cannot admit anything (no KV capacity yet) produces empty steps; the driver must not spin."""
+    from crosspool_b200 import deployment as D
+
+    class Starved(_FakeEngine):
+        step_is_device_work = False
+
+        def collect_step(self):
+            self.step_in_flight = False
+            self.collected += 1
+            return []
+
+    e = Starved("starved", 1, polls_per_step=0)
+    dep = D.Deployment([D.InstanceHandle("starved", None, e)])
+    slept = []
+    real_sleep = D.time.sleep
+    D.time.sleep = slept.append
+    try:
+        for _ in range(5):
+            assert dep.step_async(poll_s=0.123).tokens.get("starved", []) == []
+    finally:
+        D.time.sleep = real_sleep
+    assert slept == [0.123] * 5 and e.launched == 5
