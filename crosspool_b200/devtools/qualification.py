@@ -384,7 +384,7 @@ def qualify(hf_config: dict, workdir: str | Path | None = None, *, tp_sizes=(1, 
                             wr = loader.materialize_layer_weights(spec, view, l.layer, experts=range(r * per, (r + 1) * per))
                             if r != 0:
                                 wr.shared_gate_up = wr.shared_down = None      # the rank of expert 0 adds the shared experts
-                            parts.append(_ep_partial(reference, x, wr, cfg).float())
+                            parts.append(reference.moe_ffn(x, wr, cfg).float())   # the oracle restricts itself to the shard's range
                         ok, d = _close(sum(parts), want)
                         rep.checks.append(Check(f"{tag}: EP{ep} range outputs sum to the whole, {n} rows", ok, d))
                 if device != "cpu":
@@ -406,32 +406,6 @@ def _oracle_logits(reference, x, w):
     if w.extra.get("router_bias") is not None:
         logits = logits.float() + w.extra["router_bias"].float()
     return logits
-
-
-def _ep_partial(reference, x, w, cfg) -> torch.Tensor:
-    """The oracle's MoE forward restricted to the expert range ``w`` holds (ids outside the range contribute nothing)."""
-    lo, hi = w.extra["experts"]
-    logits = _oracle_logits(reference, x, w)
-    ids, weights = reference.route_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.router_scoring,
-                                        w.extra.get("correction_bias"), cfg.routed_scaling_factor)
-    out = torch.zeros(x.shape, dtype=torch.float32)
-    inter = w.gate_up.shape[1] // 2
-    import torch.nn.functional as F
-
-    for e in range(lo, hi):
-        tok, slot = (ids == e).nonzero(as_tuple=True)
-        if tok.numel() == 0:
-            continue
-        i = e - lo
-        gu = F.linear(x[tok], w.gate_up[i], w.gate_up_bias[i].to(x.dtype) if w.gate_up_bias is not None else None)
-        hcur = reference.gated(gu[:, :inter], gu[:, inter:], "silu", w.extra.get("gate_transform"))
-        ye = F.linear(hcur, w.down[i], w.down_bias[i].to(x.dtype) if w.down_bias is not None else None)
-        out.index_add_(0, tok, ye.float() * weights[tok, slot, None])
-    if w.shared_gate_up is not None:
-        from ..models.weights import FfnLayerWeights
-
-        out += reference.dense_ffn(x, FfnLayerWeights(w.shared_gate_up, w.shared_down)).float()
-    return out
 
 
 def _native_check(tag, spec, view, l, x, want, cfg, device) -> Check:

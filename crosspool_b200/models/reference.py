@@ -106,14 +106,16 @@ def moe_ffn(x: torch.Tensor, w: FfnLayerWeights, cfg: ModelConfig) -> torch.Tens
         weights = weights.to(x.dtype).float()
     out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
     inter = w.gate_up.shape[1] // 2
-    for e in range(w.gate_up.shape[0]):
+    lo = (w.extra.get("experts") or (0, 0))[0]     # an expert-parallel shard holds experts lo .. lo + n: a partial sum
+    for i in range(w.gate_up.shape[0]):
+        e = lo + i
         tok, slot = (ids == e).nonzero(as_tuple=True)
         if tok.numel() == 0:
             continue
         xe = x[tok]
-        gu = F.linear(xe, w.gate_up[e], w.gate_up_bias[e].to(x.dtype) if w.gate_up_bias is not None else None)
+        gu = F.linear(xe, w.gate_up[i], w.gate_up_bias[i].to(x.dtype) if w.gate_up_bias is not None else None)
         h = gated(gu[:, :inter], gu[:, inter:], "silu", w.extra.get("gate_transform"))
-        ye = F.linear(h, w.down[e], w.down_bias[e].to(x.dtype) if w.down_bias is not None else None)
+        ye = F.linear(h, w.down[i], w.down_bias[i].to(x.dtype) if w.down_bias is not None else None)
         out.index_add_(0, tok, ye.float() * weights[tok, slot, None])
     if w.shared_gate_up is not None:
         out += dense_ffn(x, FfnLayerWeights(w.shared_gate_up, w.shared_down)).float()

@@ -152,6 +152,8 @@ def random_ffn_layer(cfg: ModelConfig, layer: int, seed: int = 0, device="cpu", 
                 shared_gu = shared_dn = None   # the rank owning expert 0 adds the shared experts
         w = FfnLayerWeights(gate_up.to(device), down.to(device), router=router.to(device), shared_gate_up=shared_gu,
                             shared_down=shared_dn)
+        if expert_range is not None:
+            w.extra["experts"] = tuple(expert_range)
         if cfg.router_precision != "payload":
             w.extra["router_precision"] = cfg.router_precision
             if cfg.router_precision == "fp32":   # fp32 router weights; the payload copy is their rounding

@@ -22,3 +22,25 @@ def test_moe_model_through_the_same_plumbing():
     assert got.tokens == want.tokens
     for a, b in zip(got.logits, want.logits):
         assert (a - b).abs().max().item() <= 1e-4
+
+
+import pytest
+
+
+@pytest.mark.parametrize("preset,ranks,moe_parallel", [("tiny-qwen3", 2, "tp"), ("tiny-qwen3-moe", 2, "tp"),
+                                                       ("tiny-qwen3-moe", 4, "ep")])
+def test_ffn_tier_of_several_processes_folds_rank_partials_to_the_monolithic_logits(preset, ranks, moe_parallel):
+    """One process per FFN rank, each with its tensor-parallel shard or its expert range only; the attention side
+    folds the partials in rank order. fp32 sums of shards differ from the unsharded sum by rounding only."""
+    got = cpu_plumbing.run_topology(preset, ffn_ranks=ranks, moe_parallel=moe_parallel, seed=5, requests=2, prompt_len=12,
+                                    new_tokens=4)
+    want = cpu_plumbing.run_monolithic(preset, seed=5, requests=2, prompt_len=12, new_tokens=4)
+    assert got.tokens == want.tokens
+    for a, b in zip(got.logits, want.logits):
+        assert (a - b).abs().max().item() <= 2e-4
+    assert got.invocations == 2 * 4 * 2          # layers x forwards x requests, whatever the number of ranks
+
+
+def test_expert_parallel_topology_refuses_a_dense_model():
+    with pytest.raises(ValueError, match="expert parallelism"):
+        cpu_plumbing.run_topology("tiny-qwen3", ffn_ranks=2, moe_parallel="ep")
