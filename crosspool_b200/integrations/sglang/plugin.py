@@ -62,12 +62,17 @@ def install(registry: Any = None, check_config: Callable[[], None] | None = None
         hooks.extend(a.hooks())
     if context_state_factory is not None:
         hooks.extend(ElasticHooks(lambda: life.scope.context_state).hooks())
+    from .shutdown import ProcessTreeRetirement
+
+    retirement = ProcessTreeRetirement()      # sealed creation and ordered retirement of the engine's child processes
+    hooks.extend(retirement.hooks())
     _applied.clear()
     for h in hooks:
         registry.register(h.target, h.handler, h.kind)
         _applied.append(h)
     verify_required_hooks_applied(registry, hooks)
     install.lifecycle = life
+    install.retirement = retirement
     install.graph_observer = _install_graph_observer(config, graph_runners)
     return list(_applied)
 
