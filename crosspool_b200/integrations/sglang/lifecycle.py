@@ -41,18 +41,86 @@ LIFECYCLE_TARGETS = [
 ]
 
 
-def derive_instance_ffn_profile(model_runner: Any, hidden_size: int) -> InstanceFfnProfile:
-    """Row capacities the Instance will ever submit: a prefill invocation carries at most one chunk, a decode
-    invocation at most the largest captured batch (src/xpool/integrations/sglang/hooks/lifecycle.py:402-467)."""
+class ProfileError(RuntimeError):
+    pass
+
+
+def _positive_int(v: Any, what: str) -> int:
+    if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
+        raise ProfileError(f"cannot derive {what}: got {v!r}")
+    return v
+
+
+def resolved_graph_capacity(eager_capacity: int, *, enabled: bool, buckets: Any = None, max_bs: Any = None, label: str) -> int:
+    """Rows one invocation of a phase may carry: the eager capacity, or the largest captured bucket if graphs are on
+    and capture more (a disabled graph path contributes nothing).
+    Reference: src/xpool/integrations/sglang/hooks/lifecycle.py:470-505."""
+    if not enabled:
+        return eager_capacity
+    candidates = [eager_capacity]
+    if buckets is not None:
+        if not isinstance(buckets, (list, tuple)):
+            raise ProfileError(f"cannot derive {label} buckets from {buckets!r}")
+        candidates += [_positive_int(b, f"a {label} bucket") for b in buckets]
+    if max_bs is not None:
+        candidates.append(_positive_int(max_bs, f"the {label} maximum"))
+    return max(candidates)
+
+
+def derive_instance_ffn_profile(model_runner: Any, hidden_size: int, shims: list | None = None, dp_size: int = 1
+                                ) -> InstanceFfnProfile:
+    """The profile registered with the daemon, from the *resolved* state of the serving process: payload dtype bf16
+    or fp16; at least one installed FFN shim, all of one hidden size; row capacities from the eager limits
+    (``max_running_requests`` for decode, the prefill chunk for prefill) widened by the captured graph buckets; with
+    attention DP one invocation carries every data-parallel rank's rows and may ask for the group sum.
+    Reference: src/xpool/integrations/sglang/hooks/lifecycle.py:402-467."""
+    import torch
+
+    dtype = getattr(getattr(model_runner, "model_config", None), "dtype", torch.bfloat16)
+    names = {torch.bfloat16: "bfloat16", torch.float16: "float16", "bfloat16": "bfloat16", "float16": "float16"}
+    if dtype not in names:
+        raise ProfileError(f"the FFN payload does not support the serving dtype {dtype!r}")
+    kinds: list[str] = []
+    if shims is not None:
+        if not shims:
+            raise ProfileError("no FFN shim is installed in the loaded model")
+        widths = {int(getattr(s, "hidden_size", hidden_size) or hidden_size) for s in shims}
+        if len(widths) != 1 or widths != {hidden_size}:
+            raise ProfileError(f"FFN shims disagree on the hidden size: {sorted(widths)} against {hidden_size}")
+        kinds = [str(getattr(s, "layer_kind", "dense")) for s in sorted(shims, key=lambda s: s.layer_ordinal)]
     sa = getattr(model_runner, "server_args", None)
-    chunk = int(getattr(sa, "chunked_prefill_size", 0) or 0)
-    if chunk <= 0:
-        chunk = int(getattr(sa, "max_prefill_tokens", 0) or 8192)
-    decode = int(getattr(sa, "cuda_graph_max_bs", 0) or getattr(sa, "max_running_requests", 0) or 256)
-    dp = max(1, int(getattr(sa, "dp_size", 1) or 1))
-    if getattr(sa, "enable_dp_attention", False) and dp > 1:
-        chunk, decode = chunk * dp, decode * dp      # one invocation carries every data-parallel rank's rows
-    return InstanceFfnProfile(max_prefill_rows=chunk, max_decode_rows=decode, hidden_size=hidden_size)
+    eager_decode = getattr(model_runner, "max_running_requests", None) or getattr(sa, "max_running_requests", None) or 256
+    chunk = getattr(sa, "chunked_prefill_size", None)
+    eager_prefill = chunk if isinstance(chunk, int) and chunk > 0 else (getattr(sa, "max_prefill_tokens", None) or 8192)
+    graphs_off = bool(getattr(sa, "disable_cuda_graph", False))
+    decode = resolved_graph_capacity(_positive_int(eager_decode, "eager decode rows"), enabled=not graphs_off,
+                                     buckets=getattr(sa, "cuda_graph_bs", None), max_bs=getattr(sa, "cuda_graph_max_bs", None),
+                                     label="decode graph")
+    prefill = resolved_graph_capacity(_positive_int(eager_prefill, "eager prefill rows"),
+                                      enabled=bool(getattr(sa, "enable_prefill_cuda_graph", False)),
+                                      buckets=getattr(sa, "prefill_cuda_graph_bs", None), label="prefill graph")
+    dp = max(1, int(dp_size or getattr(sa, "dp_size", 1) or 1)) if getattr(sa, "enable_dp_attention", False) else 1
+    return InstanceFfnProfile(max_prefill_rows=prefill * dp, max_decode_rows=decode * dp, hidden_size=hidden_size,
+                              payload_dtype=names[dtype], layer_kinds=kinds, group_sum_complete_admitted=dp > 1)
+
+
+@dataclass(frozen=True)
+class InstanceRankTransportProfile:
+    """Geometry of the transport arena one Instance rank needs: rows of the widest invocation, hidden size, and the
+    rank's place in the attention TP x DP grid (src/xpool/integrations/sglang/hooks/lifecycle.py:507-530)."""
+
+    hidden_size: int
+    payload_row_capacity: int
+    atn_tp_rank: int
+    atn_tp_size: int
+    atn_dp_rank: int
+    atn_dp_size: int
+
+    @classmethod
+    def derive(cls, binding: InstanceRankBinding, profile: InstanceFfnProfile) -> "InstanceRankTransportProfile":
+        tp, dp = max(1, binding.tp_size), max(1, binding.dp_size)
+        return cls(profile.hidden_size, max(profile.max_decode_rows, profile.max_prefill_rows), binding.rank % tp, tp,
+                   (binding.rank // tp) % dp, dp)
 
 
 @dataclass
@@ -64,6 +132,7 @@ class InstanceScope:
     topology: AttentionTopology | None = None
     runtime: Any = None                      # runtime.instance.InstanceRankRuntime
     shims: list[FfnShimModule] = field(default_factory=list)
+    transport_profile: Any = None
     context_state: Any = None
     shutdown: ShutdownHookSet | None = None
     events: list[str] = field(default_factory=list)
@@ -110,7 +179,8 @@ class LifecycleHooks:
         layers = len(s.adapter.decoder_layers(model_runner.model))
         s.shims = s.adapter.validate_after_load(model_runner.model, layers)
         hidden = shape.hidden_size if shape is not None else int(getattr(model_runner.model_config, "hidden_size"))
-        profile = derive_instance_ffn_profile(model_runner, hidden)
+        profile = derive_instance_ffn_profile(model_runner, hidden, s.shims, s.binding.dp_size)
+        s.transport_profile = InstanceRankTransportProfile.derive(s.binding, profile)
         device = int(getattr(model_runner, "gpu_id", 0))
         rank = s.topology.instance_rank if s.topology is not None else s.binding.rank
         s.runtime = self.runtime_factory(s.binding, rank, profile, device)

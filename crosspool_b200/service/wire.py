@@ -75,6 +75,8 @@ class InstanceFfnProfile(WireModel):
     max_decode_rows: int
     payload_dtype: str = "bfloat16"
     hidden_size: int
+    layer_kinds: list[str] = []               # "dense" | "moe" per decoder layer, as installed in the serving process
+    group_sum_complete_admitted: bool = False  # attention DP > 1: the Instance may ask for the group sum
 
 
 class ContextStateProfile(WireModel):

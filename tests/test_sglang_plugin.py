@@ -23,6 +23,7 @@ def _config(tp=1, dp=1):
 
 def _server_args(**kw):
     d = dict(model_path="/models/qwen3", tp_size=1, dp_size=1, tp_rank=0, chunked_prefill_size=2048, cuda_graph_max_bs=64,
+             max_running_requests=48, cuda_graph_bs=[1, 2, 4, 8, 16, 32, 64],
              cuda_graph_backend_decode="full", cuda_graph_backend_prefill="breakable", host="127.0.0.1", port=30000)
     d.update(kw)
     return types.SimpleNamespace(**d)
@@ -183,3 +184,40 @@ def test_elastic_hooks_cut_prefill_to_backing_publish_demand_and_retract_newest_
     assert not hooks.check_decode_mem(batch)
     gone = hooks.retract_decode(batch)
     assert [r.rid for r in gone] == [3, 2] and [r.rid for r in batch.reqs] == [1] and st.stats["retracted"] == 2
+
+
+def test_ffn_profile_is_derived_strictly_from_the_resolved_serving_state():
+    import torch
+
+    from crosspool_b200.integrations.sglang import lifecycle as L
+    from crosspool_b200.integrations.sglang.adapter import InstanceRankBinding
+
+    def runner(**sa):
+        args = dict(chunked_prefill_size=2048, max_running_requests=48, cuda_graph_bs=[1, 8, 64], cuda_graph_max_bs=64)
+        args.update(sa)
+        return types.SimpleNamespace(server_args=types.SimpleNamespace(**args), model_config=types.SimpleNamespace(dtype=torch.bfloat16))
+
+    shims = [types.SimpleNamespace(layer_ordinal=1, hidden_size=64, layer_kind="moe"),
+             types.SimpleNamespace(layer_ordinal=0, hidden_size=64, layer_kind="dense")]
+    p = L.derive_instance_ffn_profile(runner(), 64, shims)
+    assert (p.max_prefill_rows, p.max_decode_rows, p.payload_dtype, p.layer_kinds) == (2048, 64, "bfloat16", ["dense", "moe"])
+    assert not p.group_sum_complete_admitted
+    # graphs off: the eager limit alone; attention DP: one invocation carries every rank's rows and may ask for the sum
+    assert L.derive_instance_ffn_profile(runner(disable_cuda_graph=True), 64, shims).max_decode_rows == 48
+    dp = L.derive_instance_ffn_profile(runner(enable_dp_attention=True, dp_size=4), 64, shims, dp_size=4)
+    assert (dp.max_prefill_rows, dp.max_decode_rows, dp.group_sum_complete_admitted) == (8192, 256, True)
+    for bad, match in ((dict(cuda_graph_bs=[8, 0]), "bucket"), (dict(cuda_graph_max_bs=-1), "maximum"),
+                       (dict(max_running_requests=True), "eager decode")):
+        with pytest.raises(L.ProfileError, match=match):
+            L.derive_instance_ffn_profile(runner(**bad), 64, shims)
+    with pytest.raises(L.ProfileError, match="no FFN shim"):
+        L.derive_instance_ffn_profile(runner(), 64, [])
+    with pytest.raises(L.ProfileError, match="hidden size"):
+        L.derive_instance_ffn_profile(runner(), 64, [types.SimpleNamespace(layer_ordinal=0, hidden_size=128)])
+    fp32 = runner()
+    fp32.model_config.dtype = torch.float32
+    with pytest.raises(L.ProfileError, match="dtype"):
+        L.derive_instance_ffn_profile(fp32, 64, shims)
+    b = InstanceRankBinding("m", rank=5, tp_size=2, dp_size=4)
+    t = L.InstanceRankTransportProfile.derive(b, dp)
+    assert (t.payload_row_capacity, t.atn_tp_rank, t.atn_tp_size, t.atn_dp_rank, t.atn_dp_size) == (8192, 1, 2, 2, 4)
