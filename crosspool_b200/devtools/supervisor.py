@@ -5,7 +5,11 @@ group, identified by (pid, creation time) so that a recycled PID is never signal
 order with a deadline per process: SIGTERM to the group, wait, SIGKILL to the exact survivors. Devices are leased
 so that two deployments (or two test cases) never run on the same GPU, and listening ports are reserved by binding
 them first (reference: src/xpool-dev/xkit/supervisor.py, xkit/device.py, xkit/scheduler.py).
-Processes are only ever signalled through PIDs this supervisor created itself.
+Processes are only ever signalled through PIDs this supervisor created itself, or that the kernel handed to it:
+with ``adopt_orphans=True`` the supervising process becomes a *child subreaper* (``prctl(PR_SET_CHILD_SUBREAPER)``),
+so a grandchild that left its process group (its own session) and lost its parent is re-parented to the supervisor
+instead of to init; after a task's group is gone the supervisor drains exactly those adopted processes, by identity,
+and reports them. Infrastructure children of the interpreter itself (multiprocessing's resource tracker) are protected.
 """
 
 from __future__ import annotations
@@ -19,7 +23,39 @@ from contextlib import contextmanager
 from dataclasses import dataclass, field
 from pathlib import Path
 
+import ctypes
+
+import psutil
+
 from ..utils.procs import ProcUniqId
+
+PR_SET_CHILD_SUBREAPER = 36
+LOG_TAIL_CHARS = 4000
+
+
+def become_child_subreaper() -> None:
+    """Linux: orphaned descendants of this process are re-parented to it (so that it can find and retire them)."""
+    libc = ctypes.CDLL(None, use_errno=True)
+    if libc.prctl(PR_SET_CHILD_SUBREAPER, 1, 0, 0, 0) != 0:
+        e = ctypes.get_errno()
+        raise OSError(e, os.strerror(e))
+
+
+@dataclass(frozen=True)
+class TaskCompletion:
+    """How a supervised task ended: ``completed`` (exit 0), ``failed`` (non-zero exit), ``timed_out`` (retired at its
+    time limit), ``cancelled`` (retired on request), with whatever it left behind."""
+
+    name: str
+    kind: str
+    exit_code: int | None
+    elapsed_s: float
+    orphans: tuple[int, ...] = ()
+    log_tail: str = ""
+
+    @property
+    def ok(self) -> bool:
+        return self.kind == "completed" and not self.orphans
 
 
 @dataclass
@@ -33,10 +69,84 @@ class Owned:
 
 
 class Supervisor:
-    def __init__(self, log_dir: str | os.PathLike | None = None):
+    def __init__(self, log_dir: str | os.PathLike | None = None, adopt_orphans: bool = False):
         self.log_dir = Path(log_dir) if log_dir else None
         self.owned: list[Owned] = []
         self.events: list[tuple[str, str]] = []
+        self.adopt_orphans = adopt_orphans
+        self.protected: set[ProcUniqId] = set()
+        if adopt_orphans:
+            become_child_subreaper()
+            self.protected = set(self._direct_children())     # whatever the interpreter already runs (resource tracker)
+
+    # ------------------------------------------------------------------ adopted descendants
+    @staticmethod
+    def _direct_children() -> list[ProcUniqId]:
+        out = []
+        for c in psutil.Process().children():
+            try:
+                out.append(ProcUniqId(c.pid, c.create_time()))
+            except psutil.NoSuchProcess:
+                pass
+        return out
+
+    def adopted(self) -> list[ProcUniqId]:
+        """Direct children of this process that it neither started nor protects: orphans the kernel re-parented here."""
+        mine = {o.ident for o in self.owned} | self.protected
+        return [c for c in self._direct_children() if c not in mine and c.alive()]
+
+    def drain_adopted(self, term_s: float = 2.0, kill_s: float = 3.0) -> list[int]:
+        """SIGTERM, then SIGKILL, to every adopted process and its tree; returns their PIDs."""
+        if not self.adopt_orphans:
+            return []
+        seen: list[int] = []
+        deadline = time.monotonic() + term_s + kill_s
+        while time.monotonic() < deadline:
+            orphans = self.adopted()
+            if not orphans:
+                break
+            for o in orphans:
+                if o.pid not in seen:
+                    seen.append(o.pid)
+                    self.events.append(("orphan", str(o.pid)))
+                sig = signal.SIGTERM if time.monotonic() < deadline - kill_s else signal.SIGKILL
+                if o.alive():
+                    try:
+                        os.kill(o.pid, sig)
+                    except ProcessLookupError:
+                        pass
+            time.sleep(0.05)
+        for pid in seen:                          # adopted children are ours to wait for: leave no zombie behind
+            try:
+                os.waitpid(pid, os.WNOHANG)
+            except ChildProcessError:
+                pass
+        return seen
+
+    def run(self, name: str, argv: list[str], timeout_s: float, env: dict[str, str] | None = None, cwd: str | None = None,
+            cancel=None) -> TaskCompletion:
+        """Starts a task, waits for it up to ``timeout_s`` (or until ``cancel()`` turns true), retires its process group
+        and whatever it orphaned, and says how it ended."""
+        t0 = time.monotonic()
+        o = self.start(name, argv, env=env, cwd=cwd)
+        kind = None
+        while o.proc.poll() is None:
+            if time.monotonic() - t0 >= timeout_s:
+                kind = "timed_out"
+                break
+            if cancel is not None and cancel():
+                kind = "cancelled"
+                break
+            time.sleep(0.02)
+        rc = self.retire(o)
+        self.owned.remove(o)
+        orphans = tuple(self.drain_adopted())
+        if kind is None:
+            kind = "completed" if rc == 0 else "failed"
+        tail = ""
+        if o.log is not None and o.log.exists():
+            tail = o.log.read_text(errors="replace")[-LOG_TAIL_CHARS:]
+        return TaskCompletion(name, kind, rc, time.monotonic() - t0, orphans, tail)
 
     def start(self, name: str, argv: list[str], env: dict[str, str] | None = None, retire_deadline_s: float = 20.0,
               cwd: str | None = None) -> Owned:

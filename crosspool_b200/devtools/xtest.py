@@ -59,7 +59,12 @@ def visible_gpus() -> list[int]:
         return []
 
 
-def run_case(case: TestCase, leases: DeviceLeases, runner=subprocess.run) -> dict:
+def run_case(case: TestCase, leases: DeviceLeases, runner=None, supervisor=None) -> dict:
+    """``supervisor`` (a :class:`~crosspool_b200.devtools.supervisor.Supervisor`): the case runs as an owned process
+    group; at its time limit the whole group is retired, and processes it orphaned are drained and reported (a case
+    that leaves processes behind fails). ``runner``: a ``subprocess.run`` stand-in for tests of this function."""
+    if runner is None and supervisor is None:
+        runner = subprocess.run
     if case.gpus > len(leases.free) + sum(len(v) for v in leases.taken.values()):
         return {"case": case.name, "status": "skipped", "reason": f"needs {case.gpus} GPUs"}
     with leases.lease(case.name, case.gpus) as devs:
@@ -70,6 +75,17 @@ def run_case(case: TestCase, leases: DeviceLeases, runner=subprocess.run) -> dic
         if case.marker:
             cmd += ["-m", case.marker]
         t0 = time.monotonic()
+        if supervisor is not None:
+            c = supervisor.run(case.name, cmd, case.timeout_s, env=env, cwd=str(ROOT))
+            lines = c.log_tail.strip().splitlines()
+            status = "passed" if c.ok else "failed"
+            summary = lines[-1] if lines else ""
+            if c.kind == "timed_out":
+                summary = f"timed out after {case.timeout_s:.0f} s"
+            elif c.orphans:
+                summary += f" (left {len(c.orphans)} process(es) behind)"
+            return {"case": case.name, "status": status, "rc": c.exit_code, "seconds": round(c.elapsed_s, 1), "devices": devs,
+                    "summary": summary, "ended": c.kind, "orphans": list(c.orphans)}
         try:
             r = runner(cmd, env=env, cwd=str(ROOT), capture_output=True, text=True, timeout=case.timeout_s)
             rc, tail = r.returncode, (r.stdout or "").strip().splitlines()[-1:] or [""]
@@ -96,7 +112,13 @@ def main(argv: list[str] | None = None) -> int:
         return 0
     chosen = [c for c in cases if (not ns.tier or c.tier in ns.tier) and (not ns.case or c.name in ns.case)]
     leases = DeviceLeases(visible_gpus())
-    results = [run_case(c, leases) for c in chosen]
+    import tempfile
+
+    from .supervisor import Supervisor
+
+    with tempfile.TemporaryDirectory(prefix="xtest-logs-") as logs:
+        sup = Supervisor(log_dir=logs, adopt_orphans=sys.platform.startswith("linux"))
+        results = [run_case(c, leases, supervisor=sup) for c in chosen]
     for res in results:
         print(f"{res['status']:8s} {res['case']:32s} {res.get('seconds', '')} {res.get('summary', res.get('reason', ''))}", flush=True)
     if ns.report:
