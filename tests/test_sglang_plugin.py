@@ -221,3 +221,30 @@ def test_ffn_profile_is_derived_strictly_from_the_resolved_serving_state():
     b = InstanceRankBinding("m", rank=5, tp_size=2, dp_size=4)
     t = L.InstanceRankTransportProfile.derive(b, dp)
     assert (t.payload_row_capacity, t.atn_tp_rank, t.atn_tp_size, t.atn_dp_rank, t.atn_dp_size) == (8192, 1, 2, 2, 4)
+
+
+def test_topology_checks_cover_kinds_context_parallelism_and_both_directions_of_the_dp_switch():
+    mk = lambda **kw: ModelShape.load({"hidden_size": 64, "num_attention_heads": 8, **kw})
+    assert mk().attention_kind == "mha" and mk(num_key_value_heads=2).attention_kind == "gqa"
+    assert mk(num_key_value_heads=1).attention_kind == "mqa" and mk(kv_lora_rank=16).attention_kind == "mla"
+    assert mk(num_key_value_heads="2", hidden_size=64.0).num_kv_heads == 2
+    for bad in ({"num_key_value_heads": 2.5}, {"num_attention_heads": True}, {"num_key_value_heads": 16}):
+        with pytest.raises(TopologyError):
+            mk(**bad)
+    with pytest.raises(TopologyError, match="lacks hidden_size"):
+        ModelShape.load({"num_attention_heads": 8})
+    shape = mk(num_key_value_heads=2)
+    ok = dict(atn_tp_size=1, atn_dp_size=2, supports_dp_attention=True)
+    t = AttentionTopology.from_runtime(_server_args(tp_size=2, dp_size=2, enable_dp_attention=True, tp_rank=1), shape, **ok)
+    assert (t.tp_rank, t.dp_rank, t.instance_rank) == (0, 1, 1)
+    with pytest.raises(TopologyError, match="context parallel"):
+        AttentionTopology.from_runtime(_server_args(tp_size=2, dp_size=2, enable_dp_attention=True, attn_cp_size=2), shape, **ok)
+    with pytest.raises(TopologyError, match="must be set"):
+        AttentionTopology.from_runtime(_server_args(tp_size=2, dp_size=2), shape, **ok)
+    with pytest.raises(TopologyError, match="must be unset"):
+        AttentionTopology.from_runtime(_server_args(tp_size=2, enable_dp_attention=True), shape, atn_tp_size=2, atn_dp_size=1,
+                                       supports_dp_attention=True)
+    with pytest.raises(TopologyError, match="data-parallel-size must be 2"):
+        AttentionTopology.from_runtime(_server_args(tp_size=2, dp_size=1, enable_dp_attention=True), shape, **ok)
+    with pytest.raises(TopologyError, match="positive integer"):
+        AttentionTopology.from_runtime(_server_args(), shape, atn_tp_size=0, atn_dp_size=1, supports_dp_attention=False)
