@@ -99,7 +99,8 @@ def run_decode_only_single_gpu(args) -> dict:
 def main(argv=None) -> int:
     args = parse_args(argv)
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        if int(os.environ.get("RANK", "0")) == 0:       # one line for the whole job, also under torch.distributed.run
+            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}), flush=True)
         return 0
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.decode_only:
