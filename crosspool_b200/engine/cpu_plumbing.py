@@ -252,3 +252,217 @@ def run_monolithic(preset: str = "tiny-qwen3", seed: int = 0, requests: int = 8,
         tokens.append(t)
         logits.append(l)
     return PlumbingResult(tokens, logits, 0)
+
+
+# ------------------------------------------------------------------ data-parallel attention ranks
+
+DP_LAYOUTS = {"packed": rt.DP_PACKED_BY_RANK, "uniform": rt.DP_UNIFORM_BY_RANK}
+
+
+def dp_ffn_main(names: list[str], preset: str, seed: int, max_rows: int, ready, layout: int, stats,
+                idle_timeout_s: float = 30.0) -> None:
+    """FFN role of an Instance whose attention runs data-parallel: one mailbox per attention rank. Every layer call
+    is a rendezvous: the role takes one invocation from every rank (in rank order), checks the row table with the
+    native ``dp_inspect_rows``, evaluates the layer ONCE over the rows of all non-idle ranks and scatters the slices
+    back, so a rank that has nothing to run still takes part with an Idle invocation. A table that does not add up,
+    or ranks that disagree about the layer, end every rank's call with a protocol mismatch. Reference:
+    src/cext/fabric/coordinator.cu:55-117 (row inspection), src/cext/fabric/executor.cu (merged evaluation)."""
+    torch.set_num_threads(1)
+    cfg = model_config.preset(preset)
+    hidden = cfg.hidden_size
+    weights = random_ffn_weights(cfg, seed, dtype=torch.float32)
+    boxes = [rt.CpuMailbox.attach(n, max_rows, hidden * 4) for n in names]
+    for mb in boxes:
+        mb.activate()
+    ready.set()
+    try:
+        while True:
+            reqs = []
+            for mb in boxes:
+                rc, req = mb.take(idle_timeout_s)
+                if rc != rt.WAIT_READY:
+                    return
+                reqs.append(req)
+            modes = [q[2] for q in reqs]
+            rows = [q[0] for q in reqs]
+            layer = reqs[0][1]
+            payload = sum(rows)
+            table = rt.dp_inspect_rows(layout, payload, modes, rows) if len(boxes) > 1 else (modes[0], [0])
+            if table is None or any(q[1] != layer for q in reqs) or layer >= cfg.num_layers:
+                for mb in boxes:
+                    mb.complete(rt.RESULT_PROTOCOL_MISMATCH)
+                return
+            merged_mode, offsets = table
+            live = [r for r in range(len(boxes)) if modes[r] != rt.MODE_IDLE]
+            x = torch.cat([_view(boxes[r].input_address, rows[r], hidden) for r in live])
+            with torch.no_grad():
+                y = ffn_forward(x, weights[layer], cfg)
+            at = 0
+            for r in live:
+                _view(boxes[r].output_address, rows[r], hidden).copy_(y[at:at + rows[r]])
+                at += rows[r]
+            stats[0] += 1                                   # merged evaluations
+            stats[1] += len(boxes) - len(live)              # idle participations
+            stats[2] += int(merged_mode == rt.MODE_PREFILL and any(modes[r] == rt.MODE_DECODE for r in live))
+            for mb in boxes:
+                mb.complete(rt.RESULT_OK)
+    finally:
+        for mb in boxes:
+            mb.close()
+
+
+def _dp_attention_main(rank: int, dp: int, name: str, preset: str, seed: int, max_rows: int, requests: int, prompt_len: int,
+                       new_tokens: int, layout: int, barrier, table, out_q) -> None:
+    """One data-parallel attention rank: its own requests, its own KV, its own mailbox. Before every forward the
+    ranks exchange (mode, rows) on the host (a serving engine gathers the same table for its batch metadata); a rank
+    without work joins the layer calls with Idle invocations until every rank is done. ``table`` holds 2 words per
+    rank: forward mode and row count of the coming forward (mode 0 = this rank is finished for good)."""
+    torch.set_num_threads(1)
+    cfg = model_config.preset(preset)
+    mb = rt.CpuMailbox.attach(name, max_rows, cfg.hidden_size * 4)
+    model = ReferenceModel(cfg, random_attention_weights(cfg, seed, dtype=torch.float32), ffn=[])
+    shim = RemoteFfn(mb, cfg.hidden_size, timeout_s=30.0)
+    gen = torch.Generator().manual_seed(seed + 12345 + 1000 * rank)
+    hidden = cfg.hidden_size
+
+    def rendezvous(mode: int, rows: int) -> tuple[bool, int]:
+        table[2 * rank], table[2 * rank + 1] = mode, rows
+        barrier.wait(60)
+        snap = list(table)
+        barrier.wait(60)                 # nobody overwrites the table before everyone has read it
+        return all(snap[2 * r] == 0 for r in range(dp)), max(snap[2 * r + 1] for r in range(dp))
+
+    def forward(ids, positions, cache):
+        mode = rt.MODE_DECODE if ids.numel() == 1 else rt.MODE_PREFILL
+        _, widest = rendezvous(mode, ids.numel())
+        if layout == rt.DP_UNIFORM_BY_RANK and widest > ids.numel():
+            pad = widest - ids.numel()   # uniform layout: every rank ships the widest rank's row count
+
+            def padded(layer, x, _mode=None):
+                y = shim(layer, torch.cat([x, x.new_zeros(pad, hidden)]), mode)
+                return y[:x.shape[0]]
+            return model.forward(ids, positions, cache, padded)
+        return model.forward(ids, positions, cache, lambda layer, x: shim(layer, x, mode))
+
+    tokens, logits = [], []
+    try:
+        for i in range(requests):
+            n = prompt_len + 3 * ((rank + i) % 3)          # unequal lengths: prefill and decode steps interleave over ranks
+            prompt = torch.randint(0, cfg.vocab_size, (n,), generator=gen)
+            cache = model.new_cache()
+            lg = forward(prompt, torch.arange(n), cache)[-1:]
+            out, per = [], []
+            for t in range(new_tokens):
+                per.append(lg[-1])
+                nxt = int(lg[-1].argmax())
+                out.append(nxt)
+                if t + 1 == new_tokens:
+                    break
+                lg = forward(torch.tensor([nxt]), torch.tensor([n + t]), cache)
+            tokens.append(out)
+            logits.append(torch.stack(per))
+        while True:                                         # finished: keep the others' layer calls complete
+            all_done, widest = rendezvous(0, 0)
+            if all_done:
+                break
+            rows = widest if layout == rt.DP_UNIFORM_BY_RANK else 0
+            x = torch.zeros(rows, hidden)
+            for layer in range(cfg.num_layers):
+                shim(layer, x, rt.MODE_IDLE)
+        out_q.put((rank, tokens, [l.numpy() for l in logits], shim.calls, None))
+    except Exception as e:                                  # reported to the parent, which fails the run
+        barrier.abort()
+        out_q.put((rank, [], [], shim.calls, repr(e)))
+    finally:
+        mb.close()
+
+
+@dataclass
+class DpPlumbingResult:
+    ranks: list[PlumbingResult]       # per attention rank
+    merged_evaluations: int           # layer evaluations the FFN role ran (one per rendezvous)
+    idle_participations: int          # Idle invocations that took part in them
+    mixed_mode_evaluations: int       # evaluations that merged a prefilling rank with a decoding one
+
+
+def dp_rank_requests(rank: int, requests: int) -> int:
+    """Requests of attention rank ``rank``: later ranks get one fewer each (at least one), so they finish early."""
+    return max(1, requests - rank)
+
+
+def dp_rank_new_tokens(rank: int, new_tokens: int) -> int:
+    """Output length of rank ``rank``'s requests: one more per rank, so the ranks fall out of step and a prefill of
+    one meets decode steps of another in the same rendezvous."""
+    return new_tokens + rank
+
+
+def run_dp_topology(preset: str = "tiny-qwen3", dp: int = 2, layout: str = "packed", seed: int = 0, requests: int = 3,
+                    prompt_len: int = 12, new_tokens: int = 6) -> DpPlumbingResult:
+    """``dp`` attention processes of one Instance (data parallel: different requests, same weights) and one FFN
+    process that evaluates every layer once per rendezvous over all ranks' rows."""
+    import queue
+
+    cfg = model_config.preset(preset)
+    code = DP_LAYOUTS[layout]
+    max_rows = prompt_len + 6
+    ctx = mp.get_context("spawn")
+    names = [f"/xpool-cpu-{os.getpid()}-{seed}-dp{r}" for r in range(dp)]
+    boxes = [rt.CpuMailbox.create(n, max_rows, cfg.hidden_size * 4) for n in names]
+    ready, barrier = ctx.Event(), ctx.Barrier(dp)
+    table, stats = ctx.Array("i", 2 * dp, lock=False), ctx.Array("q", 3, lock=False)
+    out_q = ctx.Queue()
+    ffn = ctx.Process(target=dp_ffn_main, args=(names, preset, seed, max_rows, ready, code, stats), daemon=True)
+    ffn.start()
+    ranks = []
+    try:
+        if not ready.wait(120):
+            raise RuntimeError("FFN role did not come up")
+        for mb in boxes:
+            if mb.wait_status(rt.MBOX_IDLE, 10.0) != rt.WAIT_READY:
+                raise RuntimeError("a mailbox never became idle")
+        for r in range(dp):
+            p = ctx.Process(target=_dp_attention_main, daemon=True,
+                            args=(r, dp, names[r], preset, seed, max_rows, dp_rank_requests(r, requests), prompt_len,
+                                  dp_rank_new_tokens(r, new_tokens),
+                                  code, barrier, table, out_q))
+            p.start()
+            ranks.append(p)
+        got: dict[int, PlumbingResult] = {}
+        for _ in range(dp):
+            try:
+                rank, tokens, logits, calls, err = out_q.get(timeout=300)
+            except queue.Empty:
+                raise RuntimeError("an attention rank did not finish") from None
+            if err:
+                raise RuntimeError(f"attention rank {rank} failed: {err}")
+            got[rank] = PlumbingResult(tokens, [torch.from_numpy(l) for l in logits], calls)
+        return DpPlumbingResult([got[r] for r in range(dp)], int(stats[0]), int(stats[1]), int(stats[2]))
+    finally:
+        for mb in boxes:
+            mb.shutdown()
+        for p in ranks + [ffn]:
+            p.join(10)
+            if p.is_alive():
+                p.kill()
+        for mb in boxes:
+            mb.close()
+
+
+def run_dp_monolithic(preset: str = "tiny-qwen3", dp: int = 2, seed: int = 0, requests: int = 3, prompt_len: int = 12,
+                      new_tokens: int = 6) -> list[PlumbingResult]:
+    """What every attention rank of ``run_dp_topology`` must produce, from one undivided model."""
+    torch.set_num_threads(1)
+    cfg = model_config.preset(preset)
+    model = ReferenceModel(cfg, random_attention_weights(cfg, seed, dtype=torch.float32),
+                           random_ffn_weights(cfg, seed, dtype=torch.float32))
+    out = []
+    for rank in range(dp):
+        gen = torch.Generator().manual_seed(seed + 12345 + 1000 * rank)
+        tokens, logits = [], []
+        for i in range(dp_rank_requests(rank, requests)):
+            prompt = torch.randint(0, cfg.vocab_size, (prompt_len + 3 * ((rank + i) % 3),), generator=gen)
+            t, l = model.generate(prompt, dp_rank_new_tokens(rank, new_tokens))
+            tokens.append(t)
+            logits.append(l)
+        out.append(PlumbingResult(tokens, logits, 0))
+    return out
