@@ -21,6 +21,7 @@ src/xpool-dev/xtest/harness/support/ffn.py:20-28).
 
     python -m crosspool_b200.devtools.qualification --arch all
     python -m crosspool_b200.devtools.qualification --config /path/to/config.json --shrink
+    python -m crosspool_b200.devtools.qualification --arch all --against hf     # the transformers model as the other side
 """
 
 from __future__ import annotations
@@ -143,6 +144,8 @@ def synthesize_ffn_tensors(spec: FfnModelSpec, seed: int = 0, scale: float = 0.2
                 stem = key[: -len("_blocks")] if key.endswith("_blocks") else key
                 t[key] = q["blocks"].reshape(*shape[:-1], shape[-1] // 32, 16)
                 t[stem + ex.scales_suffix] = q["scales"]
+        elif ex.input_major:         # stored for ``x @ W``: [experts, in, out]
+            t[ex.packed_key], t[ex.down_key] = rnd(e, h, 2 * i), rnd(e, i, h)
         else:
             t[ex.packed_key], t[ex.down_key] = rnd(e, 2 * i, h), rnd(e, h, i)
         if ex.gate_bias_key:
@@ -261,6 +264,9 @@ def direct_ffn(l: DenseFfnSpec | MoeFfnSpec, t: dict[str, torch.Tensor], x: torc
             packed = _mx_decode(t[ex.packed_key][e], t[stem_p + ex.scales_suffix][e])
             gw, uw = _split(packed, l.source_order)
             dw = _mx_decode(t[ex.down_key][e], t[stem_d + ex.scales_suffix][e])
+        elif ex.input_major:
+            gw, uw = _split(t[ex.packed_key][e].t(), l.source_order)
+            dw = t[ex.down_key][e].t()
         else:
             gw, uw = _split(t[ex.packed_key][e], l.source_order)
             dw = t[ex.down_key][e]
@@ -438,7 +444,13 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--shrink", action="store_true", help="replace the sizes of --config by the family's tiny ones")
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--against", choices=("direct", "hf"), default="direct",
+                    help="'hf': compare with the transformers implementation of the architecture (devtools/hf_parity.py)")
     ns = ap.parse_args(argv)
+    if ns.against == "hf":
+        from . import hf_parity
+
+        return hf_parity.main(["--arch", ns.arch] + (["--json"] if ns.json else []))
     if ns.config:
         p = Path(ns.config)
         cfg = json.loads((p / "config.json" if p.is_dir() else p).read_text())

@@ -29,6 +29,7 @@ class TensorRead:
     cols: slice | None = None   # slice of dim -1
     expert: int | None = None   # leading index of a stacked tensor
     deinterleave: int | None = None  # 0: even rows (gate), 1: odd rows (up) of an interleaved tensor
+    transposed: bool = False    # stored [.., in, out]: rows / cols / deinterleave name the [out, in] view that is returned
 
 
 def _local(n: int, rank: int, size: int, quantum: int = 1) -> slice:
@@ -61,14 +62,21 @@ class _Reader:
         idx: list = [slice(None)] * nd
         if r.expert is not None:
             idx[0] = r.expert
+        row_dim, col_dim = (-1, -2) if r.transposed else (-2, -1)
         if r.deinterleave is not None:
-            n = sl.get_shape()[-2]
+            n = sl.get_shape()[row_dim]
             rows = r.rows or slice(0, n // 2)
-            idx[-2] = slice(2 * rows.start + r.deinterleave, 2 * rows.stop, 2)
+            idx[row_dim] = slice(2 * rows.start + r.deinterleave, 2 * rows.stop, 2)
         elif r.rows is not None:
-            idx[-2 if nd >= 2 else -1] = r.rows
+            idx[row_dim if nd >= 2 else -1] = r.rows
         if r.cols is not None:
-            idx[-1] = r.cols
+            idx[col_dim] = r.cols
+        if r.transposed:
+            return self._sliced(sl, idx).transpose(-1, -2).contiguous()
+        return self._sliced(sl, idx)
+
+    @staticmethod
+    def _sliced(sl, idx: list) -> torch.Tensor:
         strided = [i for i, v in enumerate(idx) if isinstance(v, slice) and v.step not in (None, 1)]
         if strided:   # safetensors slices take unit steps only: read the span, stride in memory
             steps = {i: idx[i].step for i in strided}
@@ -188,12 +196,13 @@ def _moe_reads(l: MoeFfnSpec, rank: int, size: int, experts: range, packed_weigh
         else:
             inter = l.moe_intermediate_size
             if l.source_order == GateUpOrder.INTERLEAVED:
-                reads[f"gate{e}"] = TensorRead(ex.packed_key, rows=rows, expert=e, deinterleave=0)
-                reads[f"up{e}"] = TensorRead(ex.packed_key, rows=rows, expert=e, deinterleave=1)
+                reads[f"gate{e}"] = TensorRead(ex.packed_key, rows=rows, expert=e, deinterleave=0, transposed=ex.input_major)
+                reads[f"up{e}"] = TensorRead(ex.packed_key, rows=rows, expert=e, deinterleave=1, transposed=ex.input_major)
             else:
-                reads[f"gate{e}"] = TensorRead(ex.packed_key, rows=rows, expert=e)
-                reads[f"up{e}"] = TensorRead(ex.packed_key, rows=slice(inter + rows.start, inter + rows.stop), expert=e)
-            reads[f"down{e}"] = TensorRead(ex.down_key, cols=rows, expert=e)
+                reads[f"gate{e}"] = TensorRead(ex.packed_key, rows=rows, expert=e, transposed=ex.input_major)
+                reads[f"up{e}"] = TensorRead(ex.packed_key, rows=slice(inter + rows.start, inter + rows.stop), expert=e,
+                                             transposed=ex.input_major)
+            reads[f"down{e}"] = TensorRead(ex.down_key, cols=rows, expert=e, transposed=ex.input_major)
     if l.num_shared_experts:
         srows = _local(l.shared_intermediate_size, rank, size)
         reads["shared_gate"] = TensorRead(l.shared_gate_key, rows=srows)

@@ -97,7 +97,8 @@ class DenseFfnSpec:
 @dataclass(frozen=True)
 class ExpertSource:
     """Where expert tensors live: ``per_expert`` keys contain ``{expert}``; ``stacked`` tensors carry
-    a leading expert dimension."""
+    a leading expert dimension. ``input_major`` stacked tensors are stored ``[experts, in, out]`` (the unquantised
+    GPT-OSS form, multiplied as ``x @ W``) instead of ``[experts, out, in]``."""
 
     per_expert: bool
     gate_key: str | None
@@ -107,6 +108,7 @@ class ExpertSource:
     gate_bias_key: str | None = None
     down_bias_key: str | None = None
     scales_suffix: str | None = None
+    input_major: bool = False
 
 
 @dataclass(frozen=True)

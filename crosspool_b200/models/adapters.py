@@ -41,6 +41,13 @@ class FfnSourceConfig:
     def int(self, key, default=None, required=True) -> int:
         return self._get(key, int, default, required)
 
+    def int_any(self, *keys: str) -> int:
+        """The first of ``keys`` the config holds (library versions write the same field under different names)."""
+        for k in keys:
+            if self.cfg.get(k) is not None:
+                return self._get(k, int)
+        raise UnsupportedModel(f"config.json misses {keys[0]!r}")
+
     def float(self, key, default=None, required=True) -> float:
         return self._get(key, float, default, required)
 
@@ -128,7 +135,8 @@ def _per_expert_source(prefix: str) -> ExpertSource:
 
 def _qwen3_moe(model_id: str, src: FfnSourceConfig, keys: Iterable[str]) -> FfnModelSpec:
     hidden, n = src.int("hidden_size"), src.int("num_hidden_layers")
-    experts, topk, minter = src.int("num_experts"), src.int("num_experts_per_tok"), src.int("moe_intermediate_size")
+    experts = src.int_any("num_experts", "num_local_experts")
+    topk, minter = src.int("num_experts_per_tok"), src.int("moe_intermediate_size")
     if src.int("decoder_sparse_step", 1) != 1 or (src.cfg.get("mlp_only_layers") or []):
         raise UnsupportedModel("Qwen3-MoE with dense interleaving is not supported")
     act = _activation(src.str("hidden_act", "silu"))
@@ -183,7 +191,7 @@ def _gpt_oss(model_id: str, src: FfnSourceConfig, keys: Iterable[str]) -> FfnMod
         ex = ExpertSource(False, None, None, f"{p}.experts.gate_up_proj" + ("_blocks" if mx else ""),
                           f"{p}.experts.down_proj" + ("_blocks" if mx else ""),
                           gate_bias_key=f"{p}.experts.gate_up_proj_bias", down_bias_key=f"{p}.experts.down_proj_bias",
-                          scales_suffix="_scales" if mx else None)
+                          scales_suffix="_scales" if mx else None, input_major=not mx)
         layers.append(MoeFfnSpec(
             i, hidden, inter, experts, topk, ActivationKind.SILU, ex, router_weight_key=f"{p}.router.weight",
             router_bias_key=f"{p}.router.bias", router_algorithm=RouterAlgorithm.SOFTMAX,

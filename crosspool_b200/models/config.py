@@ -140,7 +140,7 @@ def from_hf_config(cfg: dict[str, Any], name: str = "") -> ModelConfig:
         intermediate_size=int(cfg.get("intermediate_size") or cfg.get("ffn_dim") or 0),
         vocab_size=int(cfg["vocab_size"]),
         rms_norm_eps=float(cfg.get("rms_norm_eps", cfg.get("layer_norm_eps", 1e-6))),
-        rope_theta=float(cfg.get("rope_theta", 10000.0)),
+        rope_theta=float(cfg.get("rope_theta") or (cfg.get("rope_parameters") or {}).get("rope_theta") or 10000.0),
         qk_norm=arch.startswith("Qwen3"),
         tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)),
         attention_bias=bool(cfg.get("attention_bias", arch.startswith("Qwen2"))),
