@@ -34,10 +34,37 @@ FFN_ATOL = 2e-5        # fp32 on both sides: only summation order differs
 LOGITS_ATOL = 2e-4
 
 # architectures whose attention the oracle implements: the whole model is compared, not only its FFN layers
-FULL_MODEL = ("Qwen2ForCausalLM", "Qwen3ForCausalLM", "LlamaForCausalLM", "Qwen3MoeForCausalLM")
+FULL_MODEL = ("Qwen2ForCausalLM", "Qwen3ForCausalLM", "LlamaForCausalLM", "Qwen3MoeForCausalLM", "OPTForCausalLM",
+              "GptOssForCausalLM", "DeepseekV2ForCausalLM", "Glm4MoeLiteForCausalLM")
+
+
+# harder settings of the same families: a window shorter than the sequence with YaRN-scaled rotary embeddings, latent
+# attention with a plain query projection and YaRN magnitude correction, small latent ranks with a query bottleneck
+_YARN = {"rope_type": "yarn", "factor": 32.0, "beta_fast": 32.0, "beta_slow": 1.0, "original_max_position_embeddings": 4096}
+VARIANTS: dict[str, tuple[str, dict]] = {
+    "GptOssForCausalLM/window-yarn": ("GptOssForCausalLM", {
+        "sliding_window": 8, "max_position_embeddings": 131072,
+        "rope_parameters": {**_YARN, "truncate": False, "rope_theta": 150000.0}}),
+    "DeepseekV2ForCausalLM/plain-q-yarn": ("DeepseekV2ForCausalLM", {
+        "q_lora_rank": None, "kv_lora_rank": 32, "qk_nope_head_dim": 16, "qk_rope_head_dim": 8, "v_head_dim": 16,
+        "max_position_embeddings": 163840,
+        # no mscale_all_dim: the library's port of this family omits the softmax-scale correction that comes with it
+        "rope_parameters": {**_YARN, "factor": 40.0, "rope_theta": 10000.0}}),
+    "Glm4MoeLiteForCausalLM/small-latent-yarn": ("Glm4MoeLiteForCausalLM", {
+        "q_lora_rank": 24, "kv_lora_rank": 32, "qk_nope_head_dim": 16, "qk_rope_head_dim": 8, "v_head_dim": 24,
+        "max_position_embeddings": 163840,
+        "rope_parameters": {**_YARN, "factor": 40.0, "mscale": 1.0, "mscale_all_dim": 1.0, "rope_theta": 10000.0}}),
+}
+
+
+def resolve(name: str) -> tuple[str, dict]:
+    """(architecture, tiny configuration fields) of an architecture name or one of :data:`VARIANTS`."""
+    arch, extra = VARIANTS.get(name, (name, {}))
+    return arch, {**{k: v for k, v in TINY_CONFIGS[arch].items() if k != "torch_dtype"}, **extra}
 
 
 def available(arch: str) -> bool:
+    arch = resolve(arch)[0] if arch in VARIANTS else arch
     try:
         import transformers
     except ImportError:
@@ -50,8 +77,8 @@ def build_tiny_model(arch: str, seed: int = 0):
     routing, clamping and biases all matter (norm weights around one, everything else N(0, 0.08))."""
     import transformers
 
+    arch, fields = resolve(arch)
     cls = getattr(transformers, arch)
-    fields = {k: v for k, v in TINY_CONFIGS[arch].items() if k != "torch_dtype"}
     torch.manual_seed(seed)
     model = cls(cls.config_class(**fields)).float().eval()
     g = torch.Generator().manual_seed(seed + 1)
@@ -104,6 +131,7 @@ def parity(arch: str, *, tokens: int = 19, seed: int = 0, workdir: str | None = 
     from ..models import weights as mw
 
     model = build_tiny_model(arch, seed)
+    arch = resolve(arch)[0]
     tmp = None
     if workdir is None:
         tmp = tempfile.TemporaryDirectory(prefix="xp-hf-parity-")
@@ -146,6 +174,14 @@ def parity(arch: str, *, tokens: int = 19, seed: int = 0, workdir: str | None = 
                                     {"max_abs_err": err, "ref_max": float(logits.abs().max())}))
             same = bool((mine.argmax(-1) == logits.argmax(-1)).all())
             rep.checks.append(Check("whole model: greedy tokens equal the library's", same))
+            # the serving shape of the same computation: a prefill chunk, then one token at a time against the cache
+            cache, cut = oracle.new_cache(), max(1, tokens * 2 // 3)
+            with torch.no_grad():
+                steps = [oracle.forward(ids[:cut], torch.arange(cut), cache)]
+                steps += [oracle.forward(ids[t:t + 1], torch.tensor([t]), cache) for t in range(cut, tokens)]
+            err = float((torch.cat(steps) - logits).abs().max())
+            rep.checks.append(Check("whole model: prefill + token-by-token decode equals the library's full pass",
+                                    err <= LOGITS_ATOL * max(1.0, float(logits.abs().max())), {"max_abs_err": err}))
         return rep
     finally:
         if tmp is not None:
@@ -157,7 +193,7 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--arch", default="all")
     ap.add_argument("--json", action="store_true")
     ns = ap.parse_args(argv)
-    archs = [a for a in sorted(TINY_CONFIGS) if "+" not in a] if ns.arch == "all" else [ns.arch]
+    archs = [a for a in sorted(TINY_CONFIGS) if "+" not in a] + sorted(VARIANTS) if ns.arch == "all" else [ns.arch]
     bad = 0
     for a in archs:
         if not available(a):
@@ -168,7 +204,7 @@ def main(argv: list[str] | None = None) -> int:
         if ns.json:
             print(json.dumps(rep.to_json()))
         else:
-            print(f"{a}: {'PASS' if rep.ok else 'FAIL'} ({len(rep.checks)} checks{', whole model' if a in FULL_MODEL else ''})")
+            print(f"{a}: {'PASS' if rep.ok else 'FAIL'} ({len(rep.checks)} checks{', whole model' if resolve(a)[0] in FULL_MODEL else ''})")
             for c in rep.checks:
                 if not c.ok:
                     print(f"   FAILED {c.name}: {c.detail}")

@@ -54,7 +54,7 @@ TINY_CONFIGS: dict[str, dict] = {
                               "routed_scaling_factor": 2.0, "norm_topk_prob": False},
     "Glm4MoeLiteForCausalLM": {**_BASE, "intermediate_size": 128, "moe_intermediate_size": 64, "n_routed_experts": 8,
                                "num_experts_per_tok": 2, "first_k_dense_replace": 1, "n_shared_experts": 1,
-                               "routed_scaling_factor": 1.5, "norm_topk_prob": True, "scoring_func": "sigmoid"},
+                               "routed_scaling_factor": 1.5, "norm_topk_prob": True, "scoring_func": "sigmoid", "rms_norm_eps": 1e-6},
     "GptOssForCausalLM": {**_BASE, "intermediate_size": 64, "num_local_experts": 4, "num_experts_per_tok": 2,
                           "swiglu_limit": 7.0},
     "GptOssForCausalLM+mxfp4": {**_BASE, "intermediate_size": 64, "num_local_experts": 4, "num_experts_per_tok": 2,

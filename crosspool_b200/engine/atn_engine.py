@@ -98,6 +98,10 @@ class Sequence:
         return len(self.generated) >= self.max_new_tokens
 
 
+class UnsupportedAttention(NotImplementedError):
+    """The model's attention form is not one the GPU attention engine computes."""
+
+
 class FfnPort:
     """Where a layer's FFN runs. ``run`` receives the normalised hidden states of ``rows`` tokens
     and returns the tensors whose fixed-order sum is the FFN output (one per FFN TP rank)."""
@@ -132,6 +136,11 @@ class AttentionEngine:
         """``tp``: a connected ``parallel.atn_tp.TpGroup`` when this engine is one attention TP rank;
         ``cfg`` and ``weights`` are then the rank-local ones (``atn_tp.local_config`` /
         ``shard_attention_weights``)."""
+        if not cfg.gpu_attention_supported:
+            raise UnsupportedAttention(
+                f"{cfg.architecture}: this engine runs rotary grouped-query attention with RMSNorm; LayerNorm with learned "
+                "positions, sliding windows, attention sinks, scaled rotary embeddings and latent attention run in the "
+                "PyTorch oracle and the CPU deployment only (engine/cpu_plumbing.py). The FFN tier serves this architecture.")
         self.cfg, self.w, self.port = cfg, weights, port
         self.tp = tp
         self.ecfg = ecfg or EngineConfig()

@@ -11,6 +11,12 @@ shard or its range of experts and serving its own mailbox; the attention side ha
 folds the partial outputs in rank order with fp32 accumulation, as the GPU Fabric does (no FFN rank waits for
 another). The reference tests its topologies the same way, with one child process per PE
 (src/xpool-dev/xtest/harness/native/fabric/topology.py).
+
+Every entry point takes a preset name (random tensors) or a checkpoint directory (``config.json`` + safetensors): the
+attention process then loads every tensor except the decoder FFNs, each FFN process its shard through the production
+loader. Since the PyTorch oracle implements every supported attention form (rotary GQA, LayerNorm with learned
+positions, sliding windows with sinks, latent attention), all architectures run disaggregated here, including the ones
+the GPU attention engine does not run.
 """
 
 from __future__ import annotations
@@ -24,8 +30,61 @@ import torch
 
 from ..models import config as model_config
 from ..models.reference import ReferenceModel, ffn_forward
-from ..models.weights import random_attention_weights, random_ffn_layer, random_ffn_weights
+from ..models.weights import random_attention_weights, random_ffn_layer
 from ..native import runtime as rt
+
+
+def _is_checkpoint(source: str) -> bool:
+    return source not in model_config.PRESETS
+
+
+def attention_side(source: str, seed: int):
+    """Config and attention-side tensors of ``source``: a preset (random tensors from ``seed``) or a checkpoint
+    directory (``config.json`` + safetensors; every tensor except the decoder FFNs)."""
+    cfg = model_config.load(source)
+    if _is_checkpoint(source):
+        from ..models.weights import load_attention_from_safetensors
+
+        return cfg, load_attention_from_safetensors(cfg, source, dtype=torch.float32)
+    return cfg, random_attention_weights(cfg, seed, dtype=torch.float32)
+
+
+def ffn_side(source: str, seed: int, rank: int = 0, size: int = 1, moe_parallel: str = "tp"):
+    """Config and one FFN rank's share of every layer: rows ``rank`` of ``size`` of the intermediate dimension, or with
+    ``moe_parallel="ep"`` its range of experts (shared experts ride with the rank that owns expert 0). A checkpoint
+    directory goes through the production path: FFN description, coverage check, sharded loader."""
+    cfg = model_config.load(source)
+    ep = moe_parallel == "ep"
+    if not _is_checkpoint(source):
+        out = []
+        for l in range(cfg.num_layers):
+            if cfg.layer_is_moe(l) and ep:
+                per = cfg.num_experts // size
+                out.append(random_ffn_layer(cfg, l, seed, dtype=torch.float32, expert_range=(rank * per, (rank + 1) * per)))
+            else:
+                out.append(random_ffn_layer(cfg, l, seed, dtype=torch.float32, tp_rank=rank, tp_size=size))
+        return cfg, out
+    import json
+    from pathlib import Path
+
+    from ..models import adapters
+    from . import checkpoint as ck
+    from . import loader
+
+    view = ck.read_checkpoint_key_view(source)
+    spec = adapters.compile_ffn_spec(cfg.name, json.loads((Path(source) / "config.json").read_text()), view.keys())
+    ck.validate_ffn_coverage(spec, view)
+    out = []
+    for l in range(cfg.num_layers):
+        if cfg.layer_is_moe(l) and ep:
+            per = cfg.num_experts // size
+            w = loader.materialize_layer_weights(spec, view, l, dtype=torch.float32, experts=range(rank * per, (rank + 1) * per))
+            if rank != 0:
+                w.shared_gate_up = w.shared_down = None
+        else:
+            w = loader.materialize_layer_weights(spec, view, l, dtype=torch.float32, tp_rank=rank, tp_size=size)
+        out.append(w)
+    return cfg, out
 
 
 def _view(address: int, rows: int, hidden: int) -> torch.Tensor:
@@ -37,8 +96,7 @@ def ffn_role_main(arena_name: str, preset: str, seed: int, max_rows: int, ready,
                   ) -> None:
     """FFN role: serve FFN invocations from the mailbox until it is shut down or closed."""
     torch.set_num_threads(1)
-    cfg = model_config.preset(preset)
-    weights = random_ffn_weights(cfg, seed, dtype=torch.float32)
+    cfg, weights = ffn_side(preset, seed)
     mb = rt.CpuMailbox.attach(arena_name, max_rows, cfg.hidden_size * 4)
     mb.activate()
     ready.set()
@@ -92,7 +150,7 @@ def run(preset: str = "tiny-qwen3", seed: int = 0, requests: int = 8, prompt_len
         ) -> PlumbingResult:
     """Runs the acceptance workload: ``requests`` prompts of uniform random ids, greedy decoding."""
     torch.set_num_threads(1)
-    cfg = model_config.preset(preset)
+    cfg, attn = attention_side(preset, seed)
     max_rows = max(prompt_len, 1)
     name = f"/xpool-cpu-{os.getpid()}-{seed}"
     mb = rt.CpuMailbox.create(name, max_rows, cfg.hidden_size * 4)
@@ -105,7 +163,7 @@ def run(preset: str = "tiny-qwen3", seed: int = 0, requests: int = 8, prompt_len
             raise RuntimeError("FFN role did not come up")
         if mb.wait_status(rt.MBOX_IDLE, 10.0) != rt.WAIT_READY:
             raise RuntimeError("mailbox never became idle")
-        model = ReferenceModel(cfg, random_attention_weights(cfg, seed, dtype=torch.float32), ffn=[])
+        model = ReferenceModel(cfg, attn, ffn=[])
         shim = RemoteFfn(mb, cfg.hidden_size)
         gen = torch.Generator().manual_seed(seed + 12345)
         tokens, logits = [], []
@@ -128,14 +186,7 @@ def ffn_rank_main(arena_name: str, preset: str, seed: int, max_rows: int, ready,
     """One rank of an FFN tier: holds its shard of every layer only (rows ``tp_rank`` of ``tp_size`` of the
     intermediate dimension, or with ``moe_parallel="ep"`` its range of experts) and answers with its partial sum."""
     torch.set_num_threads(1)
-    cfg = model_config.preset(preset)
-    weights = []
-    for l in range(cfg.num_layers):
-        if cfg.layer_is_moe(l) and moe_parallel == "ep":
-            per = cfg.num_experts // tp_size
-            weights.append(random_ffn_layer(cfg, l, seed, dtype=torch.float32, expert_range=(tp_rank * per, (tp_rank + 1) * per)))
-        else:
-            weights.append(random_ffn_layer(cfg, l, seed, dtype=torch.float32, tp_rank=tp_rank, tp_size=tp_size))
+    cfg, weights = ffn_side(preset, seed, tp_rank, tp_size, moe_parallel)
     mb = rt.CpuMailbox.attach(arena_name, max_rows, cfg.hidden_size * 4)
     mb.activate()
     ready.set()
@@ -198,7 +249,7 @@ def run_topology(preset: str = "tiny-qwen3", ffn_ranks: int = 2, moe_parallel: s
                  prompt_len: int = 24, new_tokens: int = 8) -> PlumbingResult:
     """One attention process (the caller) and ``ffn_ranks`` FFN processes, each with its own shard and mailbox."""
     torch.set_num_threads(1)
-    cfg = model_config.preset(preset)
+    cfg, attn = attention_side(preset, seed)
     if moe_parallel == "ep" and (not cfg.is_moe or cfg.num_experts % ffn_ranks):
         raise ValueError("expert parallelism needs a MoE model whose experts divide over the FFN ranks")
     max_rows = max(prompt_len, 1)
@@ -217,7 +268,7 @@ def run_topology(preset: str = "tiny-qwen3", ffn_ranks: int = 2, moe_parallel: s
                 raise RuntimeError(f"FFN rank {r} did not come up")
             if boxes[r].wait_status(rt.MBOX_IDLE, 10.0) != rt.WAIT_READY:
                 raise RuntimeError(f"mailbox of FFN rank {r} never became idle")
-        model = ReferenceModel(cfg, random_attention_weights(cfg, seed, dtype=torch.float32), ffn=[])
+        model = ReferenceModel(cfg, attn, ffn=[])
         shim = RemoteFfnTier(boxes, cfg.hidden_size)
         gen = torch.Generator().manual_seed(seed + 12345)
         tokens, logits = [], []
@@ -241,9 +292,8 @@ def run_topology(preset: str = "tiny-qwen3", ffn_ranks: int = 2, moe_parallel: s
 def run_monolithic(preset: str = "tiny-qwen3", seed: int = 0, requests: int = 8, prompt_len: int = 32,
                    new_tokens: int = 16) -> PlumbingResult:
     torch.set_num_threads(1)
-    cfg = model_config.preset(preset)
-    model = ReferenceModel(cfg, random_attention_weights(cfg, seed, dtype=torch.float32),
-                           random_ffn_weights(cfg, seed, dtype=torch.float32))
+    cfg, attn = attention_side(preset, seed)
+    model = ReferenceModel(cfg, attn, ffn_side(preset, seed)[1])
     gen = torch.Generator().manual_seed(seed + 12345)
     tokens, logits = [], []
     for _ in range(requests):
@@ -268,9 +318,8 @@ def dp_ffn_main(names: list[str], preset: str, seed: int, max_rows: int, ready, 
     or ranks that disagree about the layer, end every rank's call with a protocol mismatch. Reference:
     src/cext/fabric/coordinator.cu:55-117 (row inspection), src/cext/fabric/executor.cu (merged evaluation)."""
     torch.set_num_threads(1)
-    cfg = model_config.preset(preset)
+    cfg, weights = ffn_side(preset, seed)
     hidden = cfg.hidden_size
-    weights = random_ffn_weights(cfg, seed, dtype=torch.float32)
     boxes = [rt.CpuMailbox.attach(n, max_rows, hidden * 4) for n in names]
     for mb in boxes:
         mb.activate()
@@ -318,9 +367,9 @@ def _dp_attention_main(rank: int, dp: int, name: str, preset: str, seed: int, ma
     without work joins the layer calls with Idle invocations until every rank is done. ``table`` holds 2 words per
     rank: forward mode and row count of the coming forward (mode 0 = this rank is finished for good)."""
     torch.set_num_threads(1)
-    cfg = model_config.preset(preset)
+    cfg, attn = attention_side(preset, seed)
     mb = rt.CpuMailbox.attach(name, max_rows, cfg.hidden_size * 4)
-    model = ReferenceModel(cfg, random_attention_weights(cfg, seed, dtype=torch.float32), ffn=[])
+    model = ReferenceModel(cfg, attn, ffn=[])
     shim = RemoteFfn(mb, cfg.hidden_size, timeout_s=30.0)
     gen = torch.Generator().manual_seed(seed + 12345 + 1000 * rank)
     hidden = cfg.hidden_size
@@ -402,7 +451,7 @@ def run_dp_topology(preset: str = "tiny-qwen3", dp: int = 2, layout: str = "pack
     process that evaluates every layer once per rendezvous over all ranks' rows."""
     import queue
 
-    cfg = model_config.preset(preset)
+    cfg = model_config.load(preset)
     code = DP_LAYOUTS[layout]
     max_rows = prompt_len + 6
     ctx = mp.get_context("spawn")
@@ -452,9 +501,8 @@ def run_dp_monolithic(preset: str = "tiny-qwen3", dp: int = 2, seed: int = 0, re
                       new_tokens: int = 6) -> list[PlumbingResult]:
     """What every attention rank of ``run_dp_topology`` must produce, from one undivided model."""
     torch.set_num_threads(1)
-    cfg = model_config.preset(preset)
-    model = ReferenceModel(cfg, random_attention_weights(cfg, seed, dtype=torch.float32),
-                           random_ffn_weights(cfg, seed, dtype=torch.float32))
+    cfg, attn = attention_side(preset, seed)
+    model = ReferenceModel(cfg, attn, ffn_side(preset, seed)[1])
     out = []
     for rank in range(dp):
         gen = torch.Generator().manual_seed(seed + 12345 + 1000 * rank)

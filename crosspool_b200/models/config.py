@@ -16,6 +16,23 @@ from typing import Any
 
 
 @dataclass(frozen=True)
+class MlaShape:
+    """Multi-head latent attention (DeepSeek-V2, GLM-4-MoE-Lite): queries optionally through a rank-``q_lora_rank``
+    bottleneck; keys and values expanded per head from one ``kv_lora_rank`` latent plus a ``qk_rope_head_dim`` rotary
+    key shared by all heads."""
+
+    q_lora_rank: int            # 0: a plain query projection
+    kv_lora_rank: int
+    qk_nope_head_dim: int
+    qk_rope_head_dim: int
+    v_head_dim: int
+
+    @property
+    def qk_head_dim(self) -> int:
+        return self.qk_nope_head_dim + self.qk_rope_head_dim
+
+
+@dataclass(frozen=True)
 class ModelConfig:
     name: str
     architecture: str  # HF ``architectures[0]``
@@ -45,7 +62,27 @@ class ModelConfig:
     router_scoring: str = "softmax"  # or "sigmoid"
     router_precision: str = "payload"  # "fp32_logits" (payload weights, fp32 logits) or "fp32" (fp32 weights too)
     dtype: str = "bfloat16"
+    # attention forms beyond rotary GQA with RMSNorm (the only one the GPU attention engine runs; the PyTorch oracle and the
+    # CPU deployment run all of them)
+    norm: str = "rmsnorm"            # or "layernorm" (weights and biases, mean-centred): OPT
+    positions: str = "rope"          # or "learned" (a position table added to the embeddings): OPT
+    sliding_window: int = 0          # > 0: layers named "sliding_attention" in extra["layer_types"] see this many keys
+    attention_sinks: bool = False    # one learned logit per head joins every softmax and takes no value: GPT-OSS
+    o_bias: bool = False
+    mla: MlaShape | None = None
     extra: dict[str, Any] = field(default_factory=dict, compare=False, hash=False)
+
+    @property
+    def gpu_attention_supported(self) -> bool:
+        return (self.norm == "rmsnorm" and self.positions == "rope" and self.mla is None and not self.attention_sinks
+                and not self.sliding_window and not self.o_bias and not self.extra.get("rope_scaling"))
+
+    def layer_window(self, layer: int) -> int:
+        """Keys a query of ``layer`` may look back over (itself included); 0 = all of them."""
+        kinds = self.extra.get("layer_types")
+        if not self.sliding_window or (kinds and kinds[layer] != "sliding_attention"):
+            return 0
+        return self.sliding_window
 
     @property
     def is_moe(self) -> bool:
@@ -126,9 +163,26 @@ def from_hf_config(cfg: dict[str, Any], name: str = "") -> ModelConfig:
     arch = (cfg.get("architectures") or ["Qwen3ForCausalLM"])[0]
     hidden = int(cfg["hidden_size"])
     heads = int(cfg["num_attention_heads"])
-    kv = int(cfg.get("num_key_value_heads") or heads)
+    kv = heads if arch.startswith("OPT") else int(cfg.get("num_key_value_heads") or heads)   # OPT has no grouped KV heads
     head_dim = int(cfg.get("head_dim") or hidden // heads)
     n_exp = int(cfg.get("num_experts") or cfg.get("n_routed_experts") or cfg.get("num_local_experts") or 0)
+    rope = dict(cfg.get("rope_parameters") or cfg.get("rope_scaling") or {})
+    rope_type = rope.get("rope_type", rope.get("type", "default"))
+    mla = None
+    if cfg.get("kv_lora_rank"):
+        mla = MlaShape(int(cfg.get("q_lora_rank") or 0), int(cfg["kv_lora_rank"]), int(cfg["qk_nope_head_dim"]),
+                       int(cfg["qk_rope_head_dim"]), int(cfg["v_head_dim"]))
+    opt = arch.startswith("OPT")
+    if opt and (not cfg.get("do_layer_norm_before", True) or int(cfg.get("word_embed_proj_dim", hidden)) != hidden):
+        raise ValueError("OPT variants with post-layer norms or a projected embedding width are not supported")
+    gpt_oss = arch.startswith("GptOss")
+    extra = {k: v for k, v in cfg.items() if k in ("swiglu_limit", "sliding_window", "quantization_config", "layer_types",
+                                                   "rope_interleave")}
+    if rope_type not in ("default", None):
+        extra["rope_scaling"] = {**rope, "rope_type": rope_type}
+    if gpt_oss and not extra.get("layer_types"):     # the family alternates, starting with a windowed layer
+        extra["layer_types"] = ["sliding_attention" if i % 2 == 0 else "full_attention" for i in range(int(cfg["num_hidden_layers"]))]
+    window = int(cfg.get("sliding_window") or 0) if "sliding_attention" in (extra.get("layer_types") or ()) else 0
     return ModelConfig(
         name=name or cfg.get("_name_or_path", arch),
         architecture=arch,
@@ -139,11 +193,11 @@ def from_hf_config(cfg: dict[str, Any], name: str = "") -> ModelConfig:
         head_dim=head_dim,
         intermediate_size=int(cfg.get("intermediate_size") or cfg.get("ffn_dim") or 0),
         vocab_size=int(cfg["vocab_size"]),
-        rms_norm_eps=float(cfg.get("rms_norm_eps", cfg.get("layer_norm_eps", 1e-6))),
+        rms_norm_eps=float(cfg.get("rms_norm_eps", cfg.get("layer_norm_eps", 1e-5 if opt else 1e-6))),
         rope_theta=float(cfg.get("rope_theta") or (cfg.get("rope_parameters") or {}).get("rope_theta") or 10000.0),
         qk_norm=arch.startswith("Qwen3"),
         tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)),
-        attention_bias=bool(cfg.get("attention_bias", arch.startswith("Qwen2"))),
+        attention_bias=bool(cfg.get("attention_bias", cfg.get("enable_bias", True) if opt else arch.startswith("Qwen2"))),
         mlp_bias=bool(cfg.get("mlp_bias", False)),
         hidden_act=str(cfg.get("hidden_act", cfg.get("activation_function", "silu"))),
         max_position_embeddings=int(cfg.get("max_position_embeddings", 32768)),
@@ -157,7 +211,13 @@ def from_hf_config(cfg: dict[str, Any], name: str = "") -> ModelConfig:
         router_scoring=str(cfg.get("scoring_func", "softmax")),
         router_precision={"DeepseekV2ForCausalLM": "fp32_logits", "Glm4MoeLiteForCausalLM": "fp32"}.get(arch, "payload"),
         dtype=str(cfg.get("torch_dtype", cfg.get("dtype", "bfloat16"))),
-        extra={k: v for k, v in cfg.items() if k in ("swiglu_limit", "sliding_window", "quantization_config")},
+        norm="layernorm" if opt else "rmsnorm",
+        positions="learned" if opt else "rope",
+        sliding_window=window,
+        attention_sinks=gpt_oss,
+        o_bias=bool(cfg.get("attention_bias", False)) and (gpt_oss or mla is not None) or opt and bool(cfg.get("enable_bias", True)),
+        mla=mla,
+        extra=extra,
     )
 
 

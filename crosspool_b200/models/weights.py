@@ -20,6 +20,7 @@ import torch
 from .config import ModelConfig
 
 FFN_KEY = re.compile(r"^model\.layers\.(\d+)\.mlp\.")
+OPT_FFN_KEY = re.compile(r"^model\.decoder\.layers\.(\d+)\.fc[12]\.")
 
 
 def _dtype(cfg: ModelConfig, override: torch.dtype | None) -> torch.dtype:
@@ -37,6 +38,10 @@ class AttnLayerWeights:
     q_norm: torch.Tensor | None     # [d]
     k_norm: torch.Tensor | None
     qkv_bias: torch.Tensor | None = None
+    # Other attention forms (oracle / CPU deployment): "input_norm_bias", "post_attn_norm_bias" (LayerNorm), "o_bias",
+    # "sinks" [q heads]; latent attention leaves ``qkv`` None and holds "q" or ("q_a", "q_a_norm", "q_b"), "kv_a",
+    # "kv_a_norm", "kv_b".
+    extra: dict = field(default_factory=dict)
 
 
 @dataclass
@@ -45,6 +50,7 @@ class AttentionWeights:
     layers: list[AttnLayerWeights]
     final_norm: torch.Tensor
     lm_head: torch.Tensor           # [vocab, hidden] (aliases embed when tied)
+    extra: dict = field(default_factory=dict)   # "positions" [max + offset, hidden], "final_norm_bias" (OPT)
 
 
 @dataclass
@@ -91,6 +97,8 @@ def random_attention_weights(cfg: ModelConfig, seed: int = 0, device="cpu", dtyp
     gen = _generator(seed * 1000003 + 1, device)
     embed = _randn(gen, (cfg.vocab_size, cfg.hidden_size), dt, device)
     layers = []
+    if not cfg.gpu_attention_supported:
+        return _random_attention_other_forms(cfg, gen, embed, dt, device)
     for _ in range(cfg.num_layers):
         layers.append(AttnLayerWeights(
             input_norm=torch.ones(cfg.hidden_size, dtype=dt, device=device),
@@ -104,6 +112,55 @@ def random_attention_weights(cfg: ModelConfig, seed: int = 0, device="cpu", dtyp
     final_norm = torch.ones(cfg.hidden_size, dtype=dt, device=device)
     lm_head = embed if cfg.tie_word_embeddings else _randn(gen, (cfg.vocab_size, cfg.hidden_size), dt, device)
     return AttentionWeights(embed, layers, final_norm, lm_head)
+
+
+def _random_attention_other_forms(cfg: ModelConfig, gen, embed, dt, device) -> AttentionWeights:
+    """Random tensors for the attention forms only the oracle runs (LayerNorm + learned positions, sinks, windows,
+    latent attention); norm weights near one and small biases so every term matters."""
+    h = cfg.hidden_size
+    layernorm = cfg.norm == "layernorm"
+
+    def norm_w(n):
+        return (1 + _randn(gen, (n,), torch.float32, device, std=0.1)).to(dt)
+
+    layers = []
+    for _ in range(cfg.num_layers):
+        extra: dict = {}
+        if layernorm:
+            extra["input_norm_bias"] = _randn(gen, (h,), dt, device)
+            extra["post_attn_norm_bias"] = _randn(gen, (h,), dt, device)
+        if cfg.attention_sinks:
+            extra["sinks"] = _randn(gen, (cfg.num_q_heads,), torch.float32, device, std=1.0)
+        qkv = qkv_bias = None
+        if cfg.mla is not None:
+            m = cfg.mla
+            if m.q_lora_rank:
+                extra["q_a"] = _randn(gen, (m.q_lora_rank, h), dt, device, std=0.08)
+                extra["q_a_norm"] = norm_w(m.q_lora_rank)
+                extra["q_b"] = _randn(gen, (cfg.num_q_heads * m.qk_head_dim, m.q_lora_rank), dt, device, std=0.08)
+            else:
+                extra["q"] = _randn(gen, (cfg.num_q_heads * m.qk_head_dim, h), dt, device, std=0.08)
+            extra["kv_a"] = _randn(gen, (m.kv_lora_rank + m.qk_rope_head_dim, h), dt, device, std=0.08)
+            extra["kv_a_norm"] = norm_w(m.kv_lora_rank)
+            extra["kv_b"] = _randn(gen, (cfg.num_q_heads * (m.qk_nope_head_dim + m.v_head_dim), m.kv_lora_rank), dt, device, std=0.08)
+            o_in = cfg.num_q_heads * m.v_head_dim
+        else:
+            qkv = _randn(gen, (cfg.q_size + 2 * cfg.kv_size, h), dt, device, std=0.08)
+            if cfg.attention_bias:
+                qkv_bias = _randn(gen, (cfg.q_size + 2 * cfg.kv_size,), torch.float32, device)
+            o_in = cfg.q_size
+        if cfg.o_bias:
+            extra["o_bias"] = _randn(gen, (h,), torch.float32, device)
+        layers.append(AttnLayerWeights(input_norm=norm_w(h), post_attn_norm=norm_w(h), qkv=qkv,
+                                       o=_randn(gen, (h, o_in), dt, device, std=0.08), q_norm=None, k_norm=None,
+                                       qkv_bias=qkv_bias, extra=extra))
+    top: dict = {}
+    if cfg.positions == "learned":
+        top["positions"] = _randn(gen, (cfg.max_position_embeddings + 2, h), dt, device)
+    if layernorm:
+        top["final_norm_bias"] = _randn(gen, (h,), dt, device)
+    lm_head = embed if cfg.tie_word_embeddings else _randn(gen, (cfg.vocab_size, h), dt, device)
+    return AttentionWeights(embed, layers, norm_w(h), lm_head, extra=top)
 
 
 def random_ffn_layer(cfg: ModelConfig, layer: int, seed: int = 0, device="cpu", dtype: torch.dtype | None = None,
@@ -191,8 +248,9 @@ def random_ffn_weights(cfg: ModelConfig, seed: int = 0, device="cpu", dtype: tor
 # ------------------------------------------------------------------ safetensors (attention side)
 
 def attention_keys_filter(key: str) -> bool:
-    """True for tensors the attention side loads: everything except ``model.layers.N.mlp.*``."""
-    return FFN_KEY.match(key) is None
+    """True for tensors the attention side loads: everything except the decoder FFNs (``model.layers.N.mlp.*``; for
+    OPT ``model.decoder.layers.N.fc1/fc2.*``)."""
+    return FFN_KEY.match(key) is None and OPT_FFN_KEY.match(key) is None
 
 
 def load_attention_from_safetensors(cfg: ModelConfig, model_dir: str | Path, device="cpu",
@@ -209,18 +267,60 @@ def load_attention_from_safetensors(cfg: ModelConfig, model_dir: str | Path, dev
     def opt(key: str) -> torch.Tensor | None:
         return get(key) if key in view.key_to_file else None
 
+    if cfg.positions == "learned":
+        return _load_opt_attention(cfg, get, opt)
     layers = []
     for i in range(cfg.num_layers):
         p = f"model.layers.{i}."
-        qkv = torch.cat([get(p + f"self_attn.{n}_proj.weight") for n in "qkv"], 0)
-        bias = None
-        if p + "self_attn.q_proj.bias" in view.key_to_file:
-            bias = torch.cat([get(p + f"self_attn.{n}_proj.bias") for n in "qkv"], 0).float()
+        a = p + "self_attn."
+        extra: dict = {}
+        qkv = bias = None
+        if cfg.mla is not None:
+            if cfg.mla.q_lora_rank:
+                extra.update(q_a=get(a + "q_a_proj.weight"), q_a_norm=get(a + "q_a_layernorm.weight"), q_b=get(a + "q_b_proj.weight"))
+            else:
+                extra["q"] = get(a + "q_proj.weight")
+            extra.update(kv_a=get(a + "kv_a_proj_with_mqa.weight"), kv_a_norm=get(a + "kv_a_layernorm.weight"),
+                         kv_b=get(a + "kv_b_proj.weight"))
+            for name, key in (("q_a_bias", "q_a_proj.bias"), ("kv_a_bias", "kv_a_proj_with_mqa.bias")):
+                if a + key in view.key_to_file:
+                    extra[name] = get(a + key).float()
+        else:
+            qkv = torch.cat([get(a + f"{n}_proj.weight") for n in "qkv"], 0)
+            if a + "q_proj.bias" in view.key_to_file:
+                bias = torch.cat([get(a + f"{n}_proj.bias") for n in "qkv"], 0).float()
+        if a + "o_proj.bias" in view.key_to_file:
+            extra["o_bias"] = get(a + "o_proj.bias").float()
+        if a + "sinks" in view.key_to_file:
+            extra["sinks"] = get(a + "sinks").float()
         layers.append(AttnLayerWeights(
             input_norm=get(p + "input_layernorm.weight"),
             post_attn_norm=get(p + "post_attention_layernorm.weight"),
-            qkv=qkv, o=get(p + "self_attn.o_proj.weight"),
-            q_norm=opt(p + "self_attn.q_norm.weight"), k_norm=opt(p + "self_attn.k_norm.weight"), qkv_bias=bias))
+            qkv=qkv, o=get(a + "o_proj.weight"),
+            q_norm=opt(a + "q_norm.weight"), k_norm=opt(a + "k_norm.weight"), qkv_bias=bias, extra=extra))
     embed = get("model.embed_tokens.weight")
     lm = opt("lm_head.weight")
     return AttentionWeights(embed, layers, get("model.norm.weight"), lm if lm is not None else embed)
+
+
+def _load_opt_attention(cfg: ModelConfig, get, opt) -> AttentionWeights:
+    """OPT: ``model.decoder.*`` names, LayerNorm with biases, biased projections, a learned position table."""
+    layers = []
+    for i in range(cfg.num_layers):
+        p = f"model.decoder.layers.{i}."
+        a = p + "self_attn."
+        bias = None
+        if opt(a + "q_proj.bias") is not None:
+            bias = torch.cat([get(a + f"{n}_proj.bias") for n in "qkv"], 0).float()
+        extra = {"input_norm_bias": get(p + "self_attn_layer_norm.bias"), "post_attn_norm_bias": get(p + "final_layer_norm.bias")}
+        ob = opt(a + "out_proj.bias")
+        if ob is not None:
+            extra["o_bias"] = ob.float()
+        layers.append(AttnLayerWeights(
+            input_norm=get(p + "self_attn_layer_norm.weight"), post_attn_norm=get(p + "final_layer_norm.weight"),
+            qkv=torch.cat([get(a + f"{n}_proj.weight") for n in "qkv"], 0), o=get(a + "out_proj.weight"),
+            q_norm=None, k_norm=None, qkv_bias=bias, extra=extra))
+    embed = get("model.decoder.embed_tokens.weight")
+    lm = opt("lm_head.weight")
+    top = {"positions": get("model.decoder.embed_positions.weight"), "final_norm_bias": get("model.decoder.final_layer_norm.bias")}
+    return AttentionWeights(embed, layers, get("model.decoder.final_layer_norm.weight"), lm if lm is not None else embed, extra=top)

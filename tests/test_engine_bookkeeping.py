@@ -208,3 +208,33 @@ def test_event_driven_stepping_sleeps_while_every_instance_waits_on_the_host():
     finally:
         D.time.sleep = real_sleep
     assert slept == [0.123] * 5 and e.launched == 5
+
+
+def test_the_gpu_attention_engine_refuses_attention_forms_it_does_not_compute():
+    """Before anything touches a device: a model with latent attention, sinks, windows, learned positions or scaled
+    rotary embeddings is refused by name instead of being run as plain rotary GQA."""
+    import pytest
+
+    from crosspool_b200.engine.atn_engine import AttentionEngine, UnsupportedAttention
+    from crosspool_b200.models import config as mc
+
+    base = {"hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "vocab_size": 256,
+            "intermediate_size": 128}
+    refused = [
+        {**base, "architectures": ["OPTForCausalLM"], "ffn_dim": 128},
+        {**base, "architectures": ["GptOssForCausalLM"], "sliding_window": 128, "num_local_experts": 4, "num_experts_per_tok": 2},
+        {**base, "architectures": ["DeepseekV2ForCausalLM"], "kv_lora_rank": 32, "qk_nope_head_dim": 16, "qk_rope_head_dim": 8,
+         "v_head_dim": 16},
+        {**base, "architectures": ["Qwen3ForCausalLM"], "rope_scaling": {"rope_type": "yarn", "factor": 4.0,
+                                                                          "original_max_position_embeddings": 32768}},
+    ]
+    for hf in refused:
+        cfg = mc.from_hf_config(hf)
+        assert not cfg.gpu_attention_supported
+        with pytest.raises(UnsupportedAttention, match=cfg.architecture):
+            AttentionEngine(cfg, None, None, device="cpu")
+    # a Qwen2 config.json carries a sliding_window it does not use: still plain GQA
+    plain = mc.from_hf_config({**base, "architectures": ["Qwen2ForCausalLM"], "sliding_window": 4096, "use_sliding_window": False,
+                               "layer_types": ["full_attention", "full_attention"]})
+    assert plain.gpu_attention_supported and plain.sliding_window == 0
+    assert all(mc.preset(n).gpu_attention_supported for n in mc.PRESETS)
