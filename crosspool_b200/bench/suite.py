@@ -22,6 +22,7 @@ from pathlib import Path
 from typing import Callable
 
 from . import serving as S
+from ..utils.files import atomic_write_text
 
 
 @dataclass(frozen=True)
@@ -166,7 +167,7 @@ def run_suite(cases: list[Case], targets: dict[str, str], out: Path, *, cont: bo
                 doc = seal({"case": case.name, "repetition": k, "seed": seed, "errors": errors, "report": report})
             except Exception as e:  # a crashed repetition is recorded, the suite goes on
                 doc = seal({"case": case.name, "repetition": k, "seed": seed, "errors": 1, "exception": repr(e)})
-            rpath.write_text(json.dumps(doc, indent=1))
+            atomic_write_text(rpath, json.dumps(doc, indent=1))   # resumed runs skip repetitions whose file exists
             reps.append(doc)
             (res.failed if doc["errors"] else res.ran).append(tag)
         good = [r["report"]["aggregate"] for r in reps if "report" in r and not r["errors"]]
@@ -177,7 +178,7 @@ def run_suite(cases: list[Case], targets: dict[str, str], out: Path, *, cont: bo
                            p99_tpot_ms_median=statistics.median(g["tpot_ms"]["p99"] for g in good),
                            p50_ttft_ms_median=statistics.median(g["arrival_ttft_ms"]["p50"] for g in good))
         cdir.mkdir(parents=True, exist_ok=True)
-        (cdir / "case.json").write_text(json.dumps(seal(summary), indent=1))
+        atomic_write_text(cdir / "case.json", json.dumps(seal(summary), indent=1))
     return res
 
 

@@ -77,8 +77,13 @@ def derive_instance_ffn_profile(model_runner: Any, hidden_size: int, shims: list
     import torch
 
     dtype = getattr(getattr(model_runner, "model_config", None), "dtype", torch.bfloat16)
-    names = {torch.bfloat16: "bfloat16", torch.float16: "float16", "bfloat16": "bfloat16", "float16": "float16"}
-    if dtype not in names:
+    from ...utils.dtype import encode_dtype
+
+    try:
+        payload = encode_dtype(dtype)
+    except (TypeError, ValueError):
+        payload = None
+    if payload not in ("bfloat16", "float16"):
         raise ProfileError(f"the FFN payload does not support the serving dtype {dtype!r}")
     kinds: list[str] = []
     if shims is not None:
@@ -101,7 +106,7 @@ def derive_instance_ffn_profile(model_runner: Any, hidden_size: int, shims: list
                                       buckets=getattr(sa, "prefill_cuda_graph_bs", None), label="prefill graph")
     dp = max(1, int(dp_size or getattr(sa, "dp_size", 1) or 1)) if getattr(sa, "enable_dp_attention", False) else 1
     return InstanceFfnProfile(max_prefill_rows=prefill * dp, max_decode_rows=decode * dp, hidden_size=hidden_size,
-                              payload_dtype=names[dtype], layer_kinds=kinds, group_sum_complete_admitted=dp > 1)
+                              payload_dtype=payload, layer_kinds=kinds, group_sum_complete_admitted=dp > 1)
 
 
 @dataclass(frozen=True)

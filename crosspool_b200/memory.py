@@ -16,6 +16,7 @@ import hashlib
 import json
 from dataclasses import asdict, dataclass, field
 from pathlib import Path
+from .utils.files import atomic_write_text
 
 ALLOC_GRANULE = 2 << 20      # cudaMalloc hands out physical memory in 2 MiB units
 SMALL_POOL = 20 << 20        # framework caching allocator: small blocks come from 2 MiB, large from >= 20 MiB segments
@@ -86,9 +87,9 @@ class XpoolMemoryCalibrationProfile:
     max_abs_error_bytes: int = 0
 
     def save(self, path: str | Path) -> None:
-        Path(path).write_text(json.dumps({"environment": asdict(self.environment), "coefficients": asdict(self.coefficients),
-                                          "samples": self.samples, "max_abs_error_bytes": self.max_abs_error_bytes,
-                                          "key": self.environment.key()}, indent=1))
+        atomic_write_text(path, json.dumps({"environment": asdict(self.environment), "coefficients": asdict(self.coefficients),
+                                            "samples": self.samples, "max_abs_error_bytes": self.max_abs_error_bytes,
+                                            "key": self.environment.key()}, indent=1))
 
     @classmethod
     def load(cls, path: str | Path, expect: MemoryCalibrationEnvironment | None = None) -> "XpoolMemoryCalibrationProfile":

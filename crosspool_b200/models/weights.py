@@ -18,6 +18,7 @@ from pathlib import Path
 import torch
 
 from .config import ModelConfig
+from ..utils.dtype import decode_dtype
 
 FFN_KEY = re.compile(r"^model\.layers\.(\d+)\.mlp\.")
 OPT_FFN_KEY = re.compile(r"^model\.decoder\.layers\.(\d+)\.fc[12]\.")
@@ -26,7 +27,7 @@ OPT_FFN_KEY = re.compile(r"^model\.decoder\.layers\.(\d+)\.fc[12]\.")
 def _dtype(cfg: ModelConfig, override: torch.dtype | None) -> torch.dtype:
     if override is not None:
         return override
-    return {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}[cfg.dtype]
+    return decode_dtype(cfg.dtype)
 
 
 @dataclass

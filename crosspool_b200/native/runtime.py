@@ -12,6 +12,7 @@ import ctypes as C
 import functools
 from dataclasses import dataclass
 
+from ..utils.integer import ensure_uint32, ensure_uint64
 from . import EXPECTED_ABI, NativeLibraryError, _load
 
 u32, u64, vp = C.c_uint32, C.c_uint64, C.c_void_p
@@ -233,6 +234,7 @@ class SharedMemory:
 
     @classmethod
     def create(cls, name: str, nbytes: int) -> "SharedMemory":
+        ensure_uint64(nbytes)
         err = C.c_int()
         h = lib().xr_shm_create(name.encode(), nbytes, C.byref(err))
         if not h:
@@ -305,6 +307,8 @@ class EcsChannel:
 
     def set_partition(self, idx: int, device: int, group: int, rank: int, floor_bytes: int,
                       reservation_bytes: int) -> None:
+        ensure_uint32(idx, device, group, rank)
+        ensure_uint64(floor_bytes, reservation_bytes)
         _ok(lib().xr_ecs_set_partition(self._h, idx, device, group, rank, floor_bytes, reservation_bytes))
 
     def partition(self, idx: int) -> dict:
@@ -313,6 +317,7 @@ class EcsChannel:
         return dict(device=out[0], group=out[1], rank=out[2], floor_bytes=out[3], reservation_bytes=out[4])
 
     def publish_report(self, idx: int, free_bytes: int, total_bytes: int, sequence: int) -> None:
+        ensure_uint64(free_bytes, total_bytes, sequence)      # a negative byte count must not wrap into a huge quota
         _ok(lib().xr_ecs_publish_report(self._h, idx, free_bytes, total_bytes, sequence))
 
     def read_report(self, idx: int) -> tuple[int, int, int]:
@@ -321,6 +326,7 @@ class EcsChannel:
         return tuple(out)
 
     def publish_command(self, idx: int, sequence: int, target_bytes: int) -> None:
+        ensure_uint64(sequence, target_bytes)
         _ok(lib().xr_ecs_publish_command(self._h, idx, sequence, target_bytes))
 
     def read_command(self, idx: int) -> tuple[int, int]:
@@ -330,6 +336,7 @@ class EcsChannel:
 
     def publish_demand(self, idx: int, evaluated_sequence: int, required_bytes: int, deadline_ns: int,
                        mapped_bytes: int) -> None:
+        ensure_uint64(evaluated_sequence, required_bytes, deadline_ns, mapped_bytes)
         _ok(lib().xr_ecs_publish_demand(self._h, idx, evaluated_sequence, required_bytes, deadline_ns, mapped_bytes))
 
     def read_demand(self, idx: int) -> tuple[int, int, int, int]:
@@ -338,6 +345,7 @@ class EcsChannel:
         return tuple(out)
 
     def publish_completion(self, idx: int, sequence: int, mapped_bytes: int) -> None:
+        ensure_uint64(sequence, mapped_bytes)
         _ok(lib().xr_ecs_publish_completion(self._h, idx, sequence, mapped_bytes))
 
     def read_completion(self, idx: int) -> tuple[int, int]:
@@ -354,6 +362,7 @@ class CpuMailbox:
 
     @classmethod
     def create(cls, name: str, max_rows: int, row_bytes: int) -> "CpuMailbox":
+        ensure_uint32(max_rows, row_bytes)
         err = C.c_int()
         h = lib().xr_mbox_create(name.encode(), max_rows, row_bytes, C.byref(err))
         if not h:
@@ -394,6 +403,8 @@ class CpuMailbox:
 
     def submit(self, in_ptr: int, out_ptr: int, rows: int, layer: int, mode: int, requirement: int = 1,
                dp_layout: int = 0, timeout_s: float = 5.0) -> int:
+        ensure_uint64(in_ptr, out_ptr)
+        ensure_uint32(rows, layer, mode, requirement, dp_layout)
         return lib().xr_mbox_submit(self._h, in_ptr, out_ptr, rows, layer, mode, requirement, dp_layout,
                                     int(timeout_s * 1e9))
 

@@ -17,6 +17,7 @@ from pathlib import Path
 from typing import Callable
 
 from .. import memory as M
+from ..utils.files import atomic_write_text
 
 
 @dataclass(frozen=True)
@@ -131,8 +132,9 @@ class EvidenceStore:
     def save(self, exp: Experiment, measured_bytes: int) -> None:
         self.dir.mkdir(parents=True, exist_ok=True)
         f = features_of(exp)
-        self.path(exp).write_text(json.dumps({"experiment": asdict(exp), "measured_bytes": int(measured_bytes),
-                                              "features": asdict(f), "environment": asdict(self.environment)}, indent=1))
+        # a fit resumes from these files: an interrupted run must leave each one whole or absent
+        atomic_write_text(self.path(exp), json.dumps({"experiment": asdict(exp), "measured_bytes": int(measured_bytes),
+                                                      "features": asdict(f), "environment": asdict(self.environment)}, indent=1))
 
     def all(self) -> list[tuple[Experiment, int]]:
         out = []

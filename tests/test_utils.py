@@ -161,3 +161,80 @@ def test_owned_mps_scope_against_a_stand_in_control_binary(tmp_path):
         return types.SimpleNamespace(returncode=1, stdout="", stderr="cannot create pipe")
     with pytest.raises(mps.MpsControlError, match="cannot create pipe"):
         mps.OwnedMpsScope(ep, mps.MpsControl(ep, run=failing)).start()
+
+
+def test_atomic_write_replaces_whole_files_and_leaves_no_temporaries(tmp_path):
+    from crosspool_b200.utils.files import atomic_write_text
+
+    p = tmp_path / "sub" / "state.json"
+    atomic_write_text(p, "one")
+    atomic_write_text(p, "two")
+    assert p.read_text() == "two"
+    assert [f.name for f in p.parent.iterdir()] == ["state.json"]
+
+    import os
+
+    import pytest
+
+    def refuse(*_a):
+        raise OSError("no rename today")
+
+    real, os.replace = os.replace, refuse          # the failure comes after the temporary file exists
+    try:
+        with pytest.raises(OSError):
+            atomic_write_text(p, "three")
+    finally:
+        os.replace = real
+    assert p.read_text() == "two"
+    assert [f.name for f in p.parent.iterdir()] == ["state.json"]
+
+
+def test_dtype_names_round_trip_and_reject_unknown_types():
+    import pytest
+    import torch
+
+    from crosspool_b200.utils.dtype import decode_dtype, element_bytes, encode_dtype
+
+    for name, dt in (("bfloat16", torch.bfloat16), ("float16", torch.float16), ("float32", torch.float32),
+                     ("float8_e4m3fn", torch.float8_e4m3fn)):
+        assert decode_dtype(name) is dt and encode_dtype(dt) == name and encode_dtype(name) == name
+    assert decode_dtype("torch.bfloat16") is torch.bfloat16 and decode_dtype("BF16") is torch.bfloat16
+    assert element_bytes("bf16") == 2 and element_bytes(torch.float8_e4m3fn) == 1
+    with pytest.raises(ValueError):
+        decode_dtype("float64x")
+    with pytest.raises(ValueError):
+        decode_dtype(torch.complex64)
+    with pytest.raises(TypeError):
+        decode_dtype(16)
+
+
+def test_integers_are_range_checked_before_they_reach_native_code():
+    import os
+
+    import pytest
+
+    from crosspool_b200.native import runtime as rt
+    from crosspool_b200.utils.integer import ensure_sint64_nonnegative, ensure_uint32, ensure_uint64
+
+    ensure_uint64(0, (1 << 64) - 1)
+    ensure_uint32(0, (1 << 32) - 1)
+    ensure_sint64_nonnegative(0, (1 << 63) - 1)
+    for bad in (-1, 1 << 64):
+        with pytest.raises(OverflowError):
+            ensure_uint64(bad)
+    with pytest.raises(OverflowError):
+        ensure_sint64_nonnegative(1 << 63)
+    with pytest.raises(OverflowError):
+        ensure_uint32(1 << 32)
+    for bad in (1.0, True, "3"):
+        with pytest.raises(TypeError):
+            ensure_uint64(bad)
+    # the ECS channel refuses a negative quota instead of publishing 2**64 - 1 bytes
+    ch = rt.EcsChannel.create(f"/xpool-int-{os.getpid()}", 1, 1)
+    try:
+        with pytest.raises(OverflowError):
+            ch.publish_command(0, 1, -1)
+        ch.publish_command(0, 1, 4096)
+        assert ch.read_command(0) == (1, 4096)
+    finally:
+        ch.close()
