@@ -245,48 +245,69 @@ class RemoteFfnTier:
         return out
 
 
+class FfnTierProcesses:
+    """``ranks`` FFN processes, each with its own shard of ``source`` and its own mailbox; ``shim`` is the attention
+    side's handle on all of them. A context manager: leaving it shuts the mailboxes down and reaps the processes."""
+
+    def __init__(self, source: str, ranks: int = 2, moe_parallel: str = "tp", seed: int = 0, max_rows: int = 64, tag: str = "r"):
+        cfg = model_config.load(source)
+        if moe_parallel == "ep" and (not cfg.is_moe or cfg.num_experts % ranks):
+            raise ValueError("expert parallelism needs a MoE model whose experts divide over the FFN ranks")
+        self.cfg, self.source, self.ranks, self.moe_parallel, self.seed, self.max_rows = cfg, source, ranks, moe_parallel, seed, max_rows
+        self.tag = tag
+        self.boxes: list[rt.CpuMailbox] = []
+        self.procs: list = []
+        self.shim: RemoteFfnTier | None = None
+
+    def __enter__(self) -> "FfnTierProcesses":
+        ctx = mp.get_context("spawn")
+        try:
+            for r in range(self.ranks):
+                name = f"/xpool-cpu-{os.getpid()}-{self.seed}-{self.tag}{r}"
+                self.boxes.append(rt.CpuMailbox.create(name, self.max_rows, self.cfg.hidden_size * 4))
+                ready = ctx.Event()
+                p = ctx.Process(target=ffn_rank_main, daemon=True,
+                                args=(name, self.source, self.seed, self.max_rows, ready, r, self.ranks, self.moe_parallel))
+                p.start()
+                self.procs.append((p, ready))
+            for r, (p, ready) in enumerate(self.procs):
+                if not ready.wait(120):
+                    raise RuntimeError(f"FFN rank {r} did not come up")
+                if self.boxes[r].wait_status(rt.MBOX_IDLE, 10.0) != rt.WAIT_READY:
+                    raise RuntimeError(f"mailbox of FFN rank {r} never became idle")
+        except BaseException:
+            self.__exit__(None, None, None)
+            raise
+        self.shim = RemoteFfnTier(self.boxes, self.cfg.hidden_size)
+        return self
+
+    def __exit__(self, *exc) -> None:
+        for mb in self.boxes:
+            mb.shutdown()
+        for p, _ in self.procs:
+            p.join(10)
+            if p.is_alive():
+                p.kill()
+        for mb in self.boxes:
+            mb.close()
+        self.boxes, self.procs = [], []
+
+
 def run_topology(preset: str = "tiny-qwen3", ffn_ranks: int = 2, moe_parallel: str = "tp", seed: int = 0, requests: int = 4,
                  prompt_len: int = 24, new_tokens: int = 8) -> PlumbingResult:
     """One attention process (the caller) and ``ffn_ranks`` FFN processes, each with its own shard and mailbox."""
     torch.set_num_threads(1)
     cfg, attn = attention_side(preset, seed)
-    if moe_parallel == "ep" and (not cfg.is_moe or cfg.num_experts % ffn_ranks):
-        raise ValueError("expert parallelism needs a MoE model whose experts divide over the FFN ranks")
-    max_rows = max(prompt_len, 1)
-    ctx = mp.get_context("spawn")
-    boxes, procs = [], []
-    try:
-        for r in range(ffn_ranks):
-            name = f"/xpool-cpu-{os.getpid()}-{seed}-r{r}"
-            boxes.append(rt.CpuMailbox.create(name, max_rows, cfg.hidden_size * 4))
-            ready = ctx.Event()
-            p = ctx.Process(target=ffn_rank_main, args=(name, preset, seed, max_rows, ready, r, ffn_ranks, moe_parallel), daemon=True)
-            p.start()
-            procs.append((p, ready))
-        for r, (p, ready) in enumerate(procs):
-            if not ready.wait(120):
-                raise RuntimeError(f"FFN rank {r} did not come up")
-            if boxes[r].wait_status(rt.MBOX_IDLE, 10.0) != rt.WAIT_READY:
-                raise RuntimeError(f"mailbox of FFN rank {r} never became idle")
+    with FfnTierProcesses(preset, ffn_ranks, moe_parallel, seed, max_rows=max(prompt_len, 1)) as tier:
         model = ReferenceModel(cfg, attn, ffn=[])
-        shim = RemoteFfnTier(boxes, cfg.hidden_size)
         gen = torch.Generator().manual_seed(seed + 12345)
         tokens, logits = [], []
         for _ in range(requests):
             prompt = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=gen)
-            t, l = model.generate(prompt, new_tokens, ffn=shim)
+            t, l = model.generate(prompt, new_tokens, ffn=tier.shim)
             tokens.append(t)
             logits.append(l)
-        return PlumbingResult(tokens, logits, shim.calls)
-    finally:
-        for mb in boxes:
-            mb.shutdown()
-        for p, _ in procs:
-            p.join(10)
-            if p.is_alive():
-                p.kill()
-        for mb in boxes:
-            mb.close()
+        return PlumbingResult(tokens, logits, tier.shim.calls)
 
 
 def run_monolithic(preset: str = "tiny-qwen3", seed: int = 0, requests: int = 8, prompt_len: int = 32,

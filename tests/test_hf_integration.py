@@ -1,0 +1,42 @@
+"""A transformers model as the attention side: its own forward / generate, FFNs served by the disaggregated tier."""
+
+import pytest
+import torch
+
+from crosspool_b200.devtools import hf_parity
+
+
+@pytest.mark.parametrize("name,ranks,moe_parallel", [
+    ("Qwen3ForCausalLM", 2, "tp"), ("OPTForCausalLM", 2, "tp"), ("GptOssForCausalLM", 2, "ep"),
+    ("DeepseekV2ForCausalLM/plain-q-yarn", 2, "tp"), ("Qwen3MoeForCausalLM", 2, "ep")])
+def test_library_model_with_detached_ffns_generates_what_the_whole_model_generates(tmp_path, name, ranks, moe_parallel):
+    from crosspool_b200.engine.cpu_plumbing import FfnTierProcesses
+    from crosspool_b200.integrations import transformers as xhf
+
+    if not hf_parity.available(name):
+        pytest.skip(f"the installed transformers has no {name}")
+    model = hf_parity.build_tiny_model(name)
+    model.save_pretrained(tmp_path, safe_serialization=True)
+    ids = torch.randint(0, model.config.vocab_size, (2, 11), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        want_logits = model(ids).logits
+        want_tokens = model.generate(ids, max_new_tokens=6, do_sample=False)
+    before = sum(p.numel() for p in model.parameters())
+    rep = xhf.detach_ffn(model)
+    assert len(rep.shims) == model.config.num_hidden_layers
+    assert rep.freed_parameters > 0 and rep.kept_parameters == before - rep.freed_parameters
+    assert not [n for n, _ in model.named_parameters() if ".mlp." in n or ".fc1." in n or ".fc2." in n]
+    with pytest.raises(RuntimeError, match="before an Instance runtime was bound"):
+        model(ids)                                    # nothing serves the FFNs yet
+    with FfnTierProcesses(str(tmp_path), ranks, moe_parallel, max_rows=64, tag="hf") as tier:
+        xhf.bind_cpu_tier(tier.shim)
+        try:
+            with torch.no_grad():
+                got_logits = model(ids).logits
+                got_tokens = model.generate(ids, max_new_tokens=6, do_sample=False)
+        finally:
+            xhf.unbind()
+        # one prefill pass + (1 prefill + 5 decode) passes of generate, every layer each
+        assert tier.shim.calls == 7 * model.config.num_hidden_layers
+    torch.testing.assert_close(got_logits, want_logits, rtol=2e-4, atol=2e-4)
+    assert got_tokens.tolist() == want_tokens.tolist()
