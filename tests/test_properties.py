@@ -1,0 +1,372 @@
+"""Property-based tests: random operation sequences against the bookkeeping that must never lose or double-book a
+page, and random tables against the native admission rules."""
+
+from hypothesis import HealthCheck, given, settings
+from hypothesis import strategies as st
+from hypothesis.stateful import RuleBasedStateMachine, invariant, precondition, rule
+
+from crosspool_b200.engine.kv_cache import OutOfPages, PageAllocator
+from crosspool_b200.engine.prefix_cache import PrefixCache
+from crosspool_b200.native import runtime as rt
+
+PAGE = 4
+
+
+class KvBookkeeping(RuleBasedStateMachine):
+    """The engine's page life cycle (admission with prefix match, prefill completion with insertion, decode growth,
+    finish, LRU eviction, vacating and retiring a memory bundle, mapping one back) on the real allocator and prefix
+    cache. After every step each mapped page is in exactly one place: free, cached, or private to a live sequence."""
+
+    def __init__(self):
+        super().__init__()
+        self.alloc = PageAllocator(24, pages_per_bundle=4)
+        self.cache = PrefixCache(PAGE)
+        self.live: dict[int, dict] = {}
+        self.next_id = 0
+
+    # ---- rules
+    @rule(prompt=st.lists(st.integers(0, 1), min_size=1, max_size=14))
+    def admit(self, prompt):
+        shared = self.cache.match(prompt)
+        need = (len(prompt) + 1 + PAGE - 1) // PAGE - len(shared)
+        if need > self.alloc.free_pages:
+            self.alloc.free(self.cache.evict(need - self.alloc.free_pages))
+        if need > self.alloc.free_pages:
+            self.cache.release(shared)
+            return
+        table = list(shared) + self.alloc.alloc(need)
+        self.live[self.next_id] = {"prompt": prompt, "table": table, "shared": list(shared), "prefilled": False, "len": len(prompt)}
+        self.next_id += 1
+
+    @precondition(lambda self: any(not s["prefilled"] for s in self.live.values()))
+    @rule(data=st.data())
+    def finish_prefill(self, data):
+        sid = data.draw(st.sampled_from(sorted(k for k, s in self.live.items() if not s["prefilled"])))
+        s = self.live[sid]
+        taken = self.cache.insert(s["prompt"], s["table"])
+        assert set(taken) <= set(s["table"]) - set(s["shared"])
+        s["shared"] += taken
+        s["prefilled"] = True
+
+    @precondition(lambda self: any(s["prefilled"] for s in self.live.values()))
+    @rule(data=st.data())
+    def decode_token(self, data):
+        sid = data.draw(st.sampled_from(sorted(k for k, s in self.live.items() if s["prefilled"])))
+        s = self.live[sid]
+        s["len"] += 1
+        if (s["len"] + 1 + PAGE - 1) // PAGE > len(s["table"]):
+            try:
+                s["table"] += self.alloc.alloc(1)
+            except OutOfPages:
+                s["len"] -= 1
+
+    @precondition(lambda self: self.live)
+    @rule(data=st.data())
+    def finish(self, data):
+        sid = data.draw(st.sampled_from(sorted(self.live)))
+        s = self.live.pop(sid)
+        keep = set(s["shared"])
+        self.alloc.free([p for p in s["table"] if p not in keep])
+        self.cache.release(s["shared"])
+
+    @rule(n=st.integers(1, 6))
+    def evict_lru(self, n):
+        pinned = self._pinned()
+        out = self.cache.evict(n)
+        assert not set(out) & pinned
+        self.alloc.free(out)
+
+    @rule()
+    def vacate_and_retire_a_bundle(self):
+        for b in self.alloc.mapped_bundles():
+            used = self.alloc.used_in_bundle(b)
+            pages = self.alloc.bundle_pages(b)
+            if used and self.cache.evictable_among(pages) == used:
+                pinned = self._pinned()
+                out = self.cache.evict_pages(pages)
+                assert not set(out) & pinned
+                self.alloc.free(out)
+                break
+        empty = self.alloc.empty_bundles()
+        if empty and len(self.alloc.mapped_bundles()) > 1:
+            self.alloc.begin_retirement(empty[-1])
+
+    @precondition(lambda self: self.alloc.unmapped_bundles())
+    @rule()
+    def map_a_bundle(self):
+        self.alloc.publish_bundle(self.alloc.unmapped_bundles()[0])
+
+    # ---- helpers and invariants
+    def _pinned(self) -> set[int]:
+        return {p for p, n in self.cache._by_page.items() if n.refs > 0}
+
+    @invariant()
+    def every_mapped_page_is_in_exactly_one_place(self):
+        free = [p for f in self.alloc._free for p in f]
+        cached = set(self.cache._by_page)
+        private = [p for s in self.live.values() for p in s["table"] if p not in cached]
+        assert len(free) == len(set(free)) and len(private) == len(set(private))
+        assert not set(free) & cached and not set(free) & set(private)
+        mapped = {p for b in self.alloc.mapped_bundles() for p in self.alloc.bundle_pages(b)}
+        assert set(free) | cached | set(private) == mapped
+        for b in range(self.alloc.num_bundles):
+            held = sum(1 for p in self.alloc.bundle_pages(b) if p in cached or p in private)
+            assert self.alloc.used_in_bundle(b) == held
+
+    @invariant()
+    def pins_count_the_live_sequences_and_cover_whole_paths(self):
+        want: dict[int, int] = {}
+        for s in self.live.values():
+            for p in s["shared"]:
+                want[p] = want.get(p, 0) + 1
+        for p, n in self.cache._by_page.items():
+            assert n.refs == want.get(p, 0)
+            if n.refs and n.parent is not self.cache.root:
+                assert n.parent.refs > 0            # a pinned page pins the prefix in front of it
+
+    def teardown(self):
+        for sid in list(self.live):
+            s = self.live.pop(sid)
+            keep = set(s["shared"])
+            self.alloc.free([p for p in s["table"] if p not in keep])
+            self.cache.release(s["shared"])
+        self.alloc.free(self.cache.evict(10 ** 6))
+        assert len(self.cache) == 0
+        assert self.alloc.free_pages == self.alloc.mapped_pages
+
+
+KvBookkeeping.TestCase.settings = settings(max_examples=120, stateful_step_count=40, deadline=None,
+                                           suppress_health_check=[HealthCheck.too_slow])
+test_kv_pages_are_never_lost_or_double_booked = KvBookkeeping.TestCase
+
+
+def _dp_model(layout, payload, modes, rows):
+    """The admission rules of a merged data-parallel invocation, restated: one rank has no layout; a uniform table
+    gives every rank the same positive count and the payload is their product; a packed table gives idle ranks no
+    rows, busy ranks some, and the counts add up to the payload. At least one rank must have work."""
+    n = len(modes)
+    if (n == 1) != (layout == rt.DP_NONE):
+        return None
+    if any(m not in (rt.MODE_PREFILL, rt.MODE_DECODE, rt.MODE_IDLE) for m in modes):
+        return None
+    if all(m == rt.MODE_IDLE for m in modes):
+        return None
+    if layout == rt.DP_NONE:
+        if rows[0] != payload:
+            return None
+        offsets = [0]
+    elif layout == rt.DP_UNIFORM_BY_RANK:
+        if rows[0] == 0 or any(r != rows[0] for r in rows) or payload != n * rows[0]:
+            return None
+        offsets = [i * rows[0] for i in range(n)]
+    else:
+        if any((m == rt.MODE_IDLE) != (r == 0) for m, r in zip(modes, rows)) or sum(rows) != payload:
+            return None
+        offsets = [sum(rows[:i]) for i in range(n)]
+    merged = rt.MODE_PREFILL if rt.MODE_PREFILL in modes else rt.MODE_DECODE
+    return merged, offsets
+
+
+@settings(max_examples=600, deadline=None)
+@given(layout=st.sampled_from([rt.DP_NONE, rt.DP_UNIFORM_BY_RANK, rt.DP_PACKED_BY_RANK]),
+       table=st.lists(st.tuples(st.sampled_from([rt.MODE_PREFILL, rt.MODE_DECODE, rt.MODE_IDLE, 3]), st.integers(0, 5)),
+                      min_size=1, max_size=5),
+       slack=st.sampled_from([0, 0, 0, 1, -1]), force_consistent=st.booleans())
+def test_native_dp_row_inspection_agrees_with_the_stated_rules(layout, table, slack, force_consistent):
+    modes, rows = [m for m, _ in table], [r for _, r in table]
+    if force_consistent:            # steer half of the cases towards valid tables, which random draws rarely hit
+        if layout == rt.DP_UNIFORM_BY_RANK:
+            rows = [max(1, rows[0])] * len(rows)
+        elif layout == rt.DP_PACKED_BY_RANK:
+            rows = [0 if m == rt.MODE_IDLE else max(1, r) for m, r in zip(modes, rows)]
+    payload = max(0, sum(rows) + slack)
+    assert rt.dp_inspect_rows(layout, payload, modes, rows) == _dp_model(layout, payload, modes, rows)
+
+
+class LaneSchedulerModel(RuleBasedStateMachine):
+    """The native Lane scheduler under random enqueue / schedule / release traffic, for every policy: an Instance is
+    queued or running at most once, a Lane serves one Instance at a time, leases are single-use, FIFO serves in
+    arrival order and the SLO policy the earliest deadline; nothing queued waits while a Lane is free."""
+
+    INSTANCES, LANES = 5, 2
+
+    def __init__(self):
+        super().__init__()
+        self.policy = None
+
+    @precondition(lambda self: self.policy is None)
+    @rule(policy=st.sampled_from([rt.POLICY_FIFO, rt.POLICY_RANDOM, rt.POLICY_SLO]), seed=st.integers(0, 3))
+    def start(self, policy, seed):
+        self.policy = policy
+        self.s = rt.LaneScheduler(self.INSTANCES, self.LANES, policy, seed)
+        self.queued: list[tuple[int, int, int]] = []          # (instance, sequence, deadline) in arrival order
+        self.running: dict[int, tuple[int, int]] = {}          # instance -> (lane, lease)
+        self.next_seq = [1] * self.INSTANCES
+        self.spent: list[tuple[int, int]] = []
+
+    @precondition(lambda self: self.policy is not None)
+    @rule(i=st.integers(0, INSTANCES - 1), deadline=st.integers(1, 1000))
+    def enqueue(self, i, deadline):
+        busy = i in self.running or any(q[0] == i for q in self.queued)
+        ok = self.s.enqueue(i, self.next_seq[i], deadline)
+        assert ok == (not busy)
+        if ok:
+            self.queued.append((i, self.next_seq[i], deadline))
+
+    @precondition(lambda self: self.policy is not None)
+    @rule(i=st.integers(0, INSTANCES - 1))
+    def enqueue_with_a_stale_sequence_is_refused(self, i):
+        if self.next_seq[i] > 1 and i not in self.running and not any(q[0] == i for q in self.queued):
+            assert not self.s.enqueue(i, self.next_seq[i] - 1, 5)
+
+    @precondition(lambda self: self.policy is not None)
+    @rule()
+    def schedule(self):
+        got = self.s.try_schedule()
+        free_lanes = set(range(self.LANES)) - {l for l, _ in self.running.values()}
+        if not self.queued or not free_lanes:
+            assert got is None
+            return
+        assert got is not None                                   # work-conserving
+        i, lane, lease = got
+        assert lane in free_lanes and i not in self.running
+        entry = next(q for q in self.queued if q[0] == i)
+        if self.policy == rt.POLICY_FIFO:
+            assert entry == self.queued[0]
+        elif self.policy == rt.POLICY_SLO:
+            assert entry[2] == min(q[2] for q in self.queued)
+        self.queued.remove(entry)
+        self.running[i] = (lane, lease)
+        assert self.s.active(i) == (lane, lease)
+
+    @precondition(lambda self: self.policy is not None and self.running)
+    @rule(data=st.data())
+    def release(self, data):
+        i = data.draw(st.sampled_from(sorted(self.running)))
+        lane, lease = self.running.pop(i)
+        assert not self.s.release(i, lease + 1)                   # someone else's lease
+        assert self.s.release(i, lease)
+        assert not self.s.release(i, lease)                       # single use
+        assert self.s.active(i) is None
+        self.next_seq[i] += 1
+        self.spent.append((i, lease))
+
+    @invariant()
+    def lanes_serve_one_instance_each(self):
+        if self.policy is None:
+            return
+        lanes = [l for l, _ in self.running.values()]
+        assert len(lanes) == len(set(lanes)) <= self.LANES
+        for i in range(self.INSTANCES):
+            assert (self.s.active(i) is not None) == (i in self.running)
+
+    def teardown(self):
+        if self.policy is not None:
+            self.s.close()
+
+
+LaneSchedulerModel.TestCase.settings = settings(max_examples=150, stateful_step_count=50, deadline=None,
+                                                suppress_health_check=[HealthCheck.too_slow])
+test_lane_scheduler_against_its_model = LaneSchedulerModel.TestCase
+
+
+class _Channel:
+    def __init__(self, n, report):
+        self.demand = {i: (0, 0, 0, 0) for i in range(n)}
+        self.completion = {i: (0, 0) for i in range(n)}
+        self.commands = {i: [] for i in range(n)}
+        self.report = report
+
+    def read_demand(self, i):
+        return self.demand[i]
+
+    def read_completion(self, i):
+        return self.completion[i]
+
+    def publish_command(self, i, seq, target):
+        self.commands[i].append((seq, target))
+
+    def read_report(self, i):
+        return self.report
+
+
+class CapacityPolicyModel(RuleBasedStateMachine):
+    """The daemon's elastic-KV arbitration under random demands, completions and clock movement. Bytes are conserved
+    (targets + bytes still held by unfinished shrinks + unassigned = the frozen budget), so the memory Instances may
+    have mapped never exceeds the budget; targets stay between floor and reservation in whole bundles; a partition
+    gets no second command before it has answered the first; one command per tick at most."""
+
+    N, BUNDLE, FLOOR, RESERVATION, FREE = 3, 4, 8, 40, 64
+
+    def __init__(self):
+        super().__init__()
+        from crosspool_b200.service.daemon.ecs import CapacityPolicy, Partition
+
+        self.ch = _Channel(self.N, (self.FREE, 1000, 1))
+        self.parts = [Partition(i, f"m{i}:0", device=0, floor_bytes=self.FLOOR, reservation_bytes=self.RESERVATION,
+                                bundle_bytes=self.BUNDLE) for i in range(self.N)]
+        self.now = [0.0]
+        self.pol = CapacityPolicy(self.ch, self.parts, {0: 0}, utilization=1.0, clock=lambda: self.now[0])
+        self.pol.freeze_pools()
+        self.budget = self.pol.pools[0].budget_bytes
+        self.demand_seq = [0] * self.N
+        self.commands_seen = sum(len(c) for c in self.ch.commands.values())
+
+    @rule(i=st.integers(0, N - 1), need=st.integers(0, 48), deadline_ms=st.integers(0, 50))
+    def publish_demand(self, i, need, deadline_ms):
+        self.demand_seq[i] += 1
+        seq_done, mapped = self.ch.completion[i]
+        self.ch.demand[i] = (self.demand_seq[i], need, int(deadline_ms * 1e6), mapped)
+
+    @rule(i=st.integers(0, N - 1))
+    def complete_latest_command(self, i):
+        if self.ch.commands[i]:
+            seq, target = self.ch.commands[i][-1]
+            self.ch.completion[i] = (seq, target)
+
+    @rule(ms=st.integers(0, 20))
+    def advance_clock(self, ms):
+        self.now[0] += ms / 1e3
+
+    @rule()
+    def tick(self):
+        pending_before = {p.index for p in self.parts if p.pending}
+        self.pol._refresh()
+        still_pending = {p.index for p in self.parts if p.pending}
+        ev = self.pol.tick()
+        total = sum(len(c) for c in self.ch.commands.values())
+        assert total - self.commands_seen <= 1
+        if total > self.commands_seen:
+            assert ev is not None and ev.kind in ("grow", "shrink")
+            who = next(p for p in self.parts if p.key == ev.partition)
+            assert who.index not in still_pending          # never a second order to a partition that owes an answer
+        self.commands_seen = total
+        del pending_before
+
+    @invariant()
+    def bytes_are_conserved_and_bounded(self):
+        pool = self.pol.pools[0]
+        held = sum(getattr(p, "_giving", 0) for p in self.parts)
+        assert pool.unassigned_bytes >= 0
+        assert sum(p.target_bytes for p in self.parts) + held + pool.unassigned_bytes == self.budget
+        for p in self.parts:
+            assert p.floor_bytes <= p.target_bytes <= p.reservation_bytes
+            assert (p.target_bytes - p.floor_bytes) % self.BUNDLE == 0
+            seqs = [s for s, _ in self.ch.commands[p.index]]
+            assert seqs == list(range(1, len(seqs) + 1))          # command sequences advance by one
+
+    @invariant()
+    def what_instances_may_have_mapped_fits_the_budget(self):
+        # an Instance may hold its previous mapping until it completes a shrink, and may map up to a grown target at once
+        worst = 0
+        for p in self.parts:
+            done = [t for s, t in self.ch.commands[p.index] if s <= self.ch.completion[p.index][0]]
+            last_done = done[-1] if done else None
+            outstanding = [t for s, t in self.ch.commands[p.index] if s > self.ch.completion[p.index][0]]
+            worst += max([t for t in [last_done] + outstanding if t is not None], default=0)
+        assert worst <= self.budget
+
+
+CapacityPolicyModel.TestCase.settings = settings(max_examples=150, stateful_step_count=60, deadline=None,
+                                                 suppress_health_check=[HealthCheck.too_slow])
+test_capacity_policy_conserves_bytes_under_any_traffic = CapacityPolicyModel.TestCase
