@@ -370,3 +370,39 @@ class CapacityPolicyModel(RuleBasedStateMachine):
 CapacityPolicyModel.TestCase.settings = settings(max_examples=150, stateful_step_count=60, deadline=None,
                                                  suppress_health_check=[HealthCheck.too_slow])
 test_capacity_policy_conserves_bytes_under_any_traffic = CapacityPolicyModel.TestCase
+
+
+@settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(models=st.lists(st.tuples(st.integers(1, 6), st.sampled_from([0.5, 1.0, 2.0]), st.sampled_from([1, 2])), min_size=1, max_size=4),
+       devices=st.lists(st.sampled_from([8, 16, 32]), min_size=2, max_size=4))
+def test_any_placement_that_is_returned_covers_every_layer_once_and_fits_every_device(models, devices):
+    from crosspool_b200.service.daemon.placement import DeviceSupply, ModelDemand, PlacementError, place_ffn_models
+
+    gb = 1 << 30
+    demands = [ModelDemand(f"m{i}", tuple([int(size * gb)] * layers), tp, 1024, max_rows=64, max_intermediate=4096)
+               for i, (layers, size, tp) in enumerate(models)]
+    supply = [DeviceSupply(d, cap * gb) for d, cap in enumerate(devices)]
+    try:
+        r = place_ffn_models(demands, supply, ws_per_lane=1 << 20)
+    except PlacementError:
+        return                                        # refusing is always allowed; a wrong answer is not
+    by_model: dict[str, list] = {}
+    for g in r.groups:
+        by_model.setdefault(g.model_id, []).append(g)
+    assert set(by_model) == {m.model_id for m in demands}
+    weights = {d.device: 0 for d in supply}
+    for m in demands:
+        gs = sorted(by_model[m.model_id], key=lambda g: g.layer_begin)
+        assert gs[0].layer_begin == 0 and gs[-1].layer_end == len(m.layer_bytes)
+        assert all(a.layer_end == b.layer_begin for a, b in zip(gs, gs[1:]))          # contiguous, no overlap
+        for g in gs:
+            assert len(g.devices) == m.tp_size and len(set(g.devices)) == m.tp_size   # TP ranks on distinct devices
+            for d in g.devices:
+                weights[d] += sum(m.layer_bytes[g.layer_begin:g.layer_end]) // m.tp_size
+    for d in supply:
+        assert r.headroom[d.device] >= 0
+        assert r.stages[d.device].peak <= d.free_bytes if d.device in r.stages else weights[d.device] == 0
+        if d.device in r.stages:
+            assert r.stages[d.device].retained >= weights[d.device]                     # the ledger covers the weights
+    again = place_ffn_models(demands, supply, ws_per_lane=1 << 20)
+    assert again.groups == r.groups                                                   # deterministic
