@@ -78,3 +78,37 @@ def test_disaggregated_processes_serve_a_library_checkpoint_with_the_librarys_lo
         assert want.argmax(-1).tolist() == tokens
         torch.testing.assert_close(logits, want, rtol=2e-4, atol=2e-4)
     assert got.invocations == 2 * (1 + new_tokens - 1) * model.config.num_hidden_layers
+
+
+def test_mxfp4_expert_tensors_decode_to_what_the_librarys_dequantiser_gives(tmp_path):
+    """The MXFP4 form of GPT-OSS experts (16-byte blocks of 32 four-bit values, one power-of-two scale per block)
+    through the production loader, against the library's own dequantisation of the same bytes."""
+    import torch
+
+    from crosspool_b200.devtools import qualification as q
+    from crosspool_b200.engine import checkpoint as ck
+    from crosspool_b200.engine import loader
+    from crosspool_b200.models import adapters
+
+    try:
+        from transformers.integrations.mxfp4 import convert_moe_packed_tensors
+    except ImportError:
+        pytest.skip("the installed transformers has no MXFP4 helpers")
+    hf = q.tiny_config("GptOssForCausalLM+mxfp4")
+    spec = adapters.compile_ffn_spec("mx", hf)
+    tensors = q.synthesize_ffn_tensors(spec, seed=3)
+    q.write_ffn_checkpoint(tmp_path, hf, tensors)
+    view = ck.read_checkpoint_key_view(tmp_path)
+    spec = adapters.compile_ffn_spec("mx", hf, view.keys())
+    l = spec.layers[0]
+    w = loader.materialize_layer_weights(spec, view, 0)
+    stem = "model.layers.0.mlp.experts."
+    gu = convert_moe_packed_tensors(tensors[stem + "gate_up_proj_blocks"], tensors[stem + "gate_up_proj_scales"])   # [E, in, out]
+    dn = convert_moe_packed_tensors(tensors[stem + "down_proj_blocks"], tensors[stem + "down_proj_scales"])
+    inter = l.moe_intermediate_size
+    assert gu.shape == (l.num_experts, l.hidden_size, 2 * inter) and dn.shape == (l.num_experts, inter, l.hidden_size)
+    rows = gu.transpose(1, 2)                                        # [E, 2I, H], gate and up rows interleaved
+    assert torch.equal(w.gate_up[:, :inter].float(), rows[:, 0::2].float())
+    assert torch.equal(w.gate_up[:, inter:].float(), rows[:, 1::2].float())
+    assert torch.equal(w.down.float(), dn.transpose(1, 2).float())
+    assert float(w.gate_up.float().abs().max()) > 0
