@@ -33,7 +33,10 @@ def _parser() -> argparse.ArgumentParser:
     e = sub.add_parser("exec", help="run a command in the deployment's environment")
     e.add_argument("argv", nargs=argparse.REMAINDER)
     c = sub.add_parser("config")
-    c.add_subparsers(dest="config_command", required=True).add_parser("dump")
+    cs = c.add_subparsers(dest="config_command", required=True)
+    cs.add_parser("dump", help="the resolved configuration with the source of every value")
+    cs.add_parser("reference", help="every setting with its TOML key, environment variable, flag and default (markdown)")
+    cs.add_parser("models", help="supported architectures and what runs where (markdown)")
     mp = sub.add_parser("memory-profile")
     mp.add_argument("--calibrate", action="store_true", help="measure a corpus of synthetic deployments on this GPU and fit the model")
     mp.add_argument("--out", default="xpool-memory-profile.json")
@@ -51,6 +54,18 @@ def _load(ns, require=True) -> C.XpoolConfig:
 def cmd_config_dump(ns) -> int:
     cfg = _load(ns, require=False)
     print(json.dumps({"digest": cfg.digest(), "config": cfg.as_dict(), "sources": dict(cfg.sources)}, indent=2))
+    return 0
+
+
+def cmd_config_reference(ns) -> int:
+    print(C.reference_markdown(), end="")
+    return 0
+
+
+def cmd_config_models(ns) -> int:
+    from ..models.support import support_markdown
+
+    print(support_markdown(), end="")
     return 0
 
 
@@ -179,7 +194,7 @@ def main(argv: list[str] | None = None) -> int:
         ns.rest = passthrough
     try:
         if ns.command == "config":
-            return cmd_config_dump(ns)
+            return {"dump": cmd_config_dump, "reference": cmd_config_reference, "models": cmd_config_models}[ns.config_command](ns)
         if ns.command == "daemon":
             return cmd_daemon_serve(ns) if ns.daemon_command == "serve" else cmd_daemon_check(ns)
         if ns.command == "exec":

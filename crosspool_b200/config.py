@@ -167,31 +167,45 @@ CONFIG_REGISTRY: tuple[ConfigSetting, ...] = (
     ConfigSetting("config", None, str, "", cli="--config", env_var="XPOOL_CONFIG",
                   description="path of the deployment TOML"),
     ConfigSetting("logging_level", ("logging", "level"), _choice("debug", "info", "warning", "error"), "info",
-                  cli="--log-level", env_var="XPOOL_LOG_LEVEL"),
-    ConfigSetting("logging_color", ("logging", "color"), _choice("auto", "always", "never"), "auto"),
+                  cli="--log-level", env_var="XPOOL_LOG_LEVEL", description="log level of every process of the deployment"),
+    ConfigSetting("logging_color", ("logging", "color"), _choice("auto", "always", "never"), "auto",
+                  description="coloured log lines: when attached to a terminal, always or never"),
     *_observer("graph"), *_observer("transport"), *_observer("fabric"), *_observer("ffn_routing"),
-    ConfigSetting("vendor_model_base_uri", ("vendor", "model_base_uri"), str, ""),
-    ConfigSetting("atn_devices", ("atn", "devices"), _devices, required=True),
-    ConfigSetting("atn_device_memory_utilization", ("atn", "device_memory_utilization"), _float(0.05, 1.0), 0.95),
+    ConfigSetting("vendor_model_base_uri", ("vendor", "model_base_uri"), str, "",
+                  description="directory that relative model paths are resolved against"),
+    ConfigSetting("atn_devices", ("atn", "devices"), _devices, required=True,
+                  description="GPUs that run attention Instances (indices; disjoint from [ffn].devices)"),
+    ConfigSetting("atn_device_memory_utilization", ("atn", "device_memory_utilization"), _float(0.05, 1.0), 0.95,
+                  description="fraction of an attention GPU's memory the KV budget may use"),
     ConfigSetting("atn_elastic_kv", ("atn", "elastic_kv"), _bool, False, env_var="XPOOL_ATN_ELASTIC_KV",
                   description="back the KV caches with VMM bundles lent between co-located Instances"),
-    ConfigSetting("ffn_devices", ("ffn", "devices"), _devices, required=True),
+    ConfigSetting("ffn_devices", ("ffn", "devices"), _devices, required=True,
+                  description="GPUs of the shared FFN tier"),
     ConfigSetting("ffn_device_memory_calibration", ("ffn", "device_memory_calibration"), _bool, False,
-                  env_var="XPOOL_FFN_DEVICE_MEMORY_CALIBRATION"),
-    ConfigSetting("ffn_device_memory_extra_margin_bytes", ("ffn", "device_memory_extra_margin_bytes"), _int(0), 0),
+                  env_var="XPOOL_FFN_DEVICE_MEMORY_CALIBRATION",
+                  description="admit placements with the persisted calibration profile (xpool memory-profile) instead of the analytic ledger alone"),
+    ConfigSetting("ffn_device_memory_extra_margin_bytes", ("ffn", "device_memory_extra_margin_bytes"), _int(0), 0,
+                  description="bytes kept free on every FFN GPU on top of the admitted peak"),
     ConfigSetting("ffn_loader_parallelism", ("ffn", "loader", "parallelism"), _int(1, 256), 4,
-                  cli="--ffn-loader-parallelism", env_var="XPOOL_FFN_LOADER_PARALLELISM"),
+                  cli="--ffn-loader-parallelism", env_var="XPOOL_FFN_LOADER_PARALLELISM",
+                  description="checkpoint reader threads (and pinned staging slots) per FFN rank"),
     ConfigSetting("ffn_placement_parallelism", ("ffn", "placement", "parallelism"), _int(1, 256), 1,
-                  cli="--ffn-placement-parallelism", env_var="XPOOL_FFN_PLACEMENT_PARALLELISM"),
-    ConfigSetting("ffn_placement_timeout_seconds", ("ffn", "placement", "timeout_seconds"), _float(0.001), 60.0),
-    ConfigSetting("daemon_host", ("daemon", "host"), str, "127.0.0.1", cli="--daemon-host"),
-    ConfigSetting("daemon_port", ("daemon", "port"), _int(1, 65535), 9810, cli="--daemon-port"),
+                  cli="--ffn-placement-parallelism", env_var="XPOOL_FFN_PLACEMENT_PARALLELISM",
+                  description="worker threads of the placement search"),
+    ConfigSetting("ffn_placement_timeout_seconds", ("ffn", "placement", "timeout_seconds"), _float(0.001), 60.0,
+                  description="time limit of the placement search; the best placement found so far is used"),
+    ConfigSetting("daemon_host", ("daemon", "host"), str, "127.0.0.1", cli="--daemon-host",
+                  description="address the daemon listens on and agents connect to"),
+    ConfigSetting("daemon_port", ("daemon", "port"), _int(1, 65535), 9810, cli="--daemon-port",
+                  description="daemon HTTP port"),
     ConfigSetting("scheduler_ffn_concurrency", ("scheduler", "ffn_concurrency"), _int(1, 64), 1,
                   cli="--ffn-concurrency", description="Executor Lanes per FFN device"),
     ConfigSetting("scheduler_ffn_policy", ("scheduler", "ffn_policy"), _choice("fifo", "random", "slo"), "fifo",
-                  cli="--ffn-policy"),
-    ConfigSetting("scheduler_ffn_random_seed", ("scheduler", "ffn_random_seed"), _int(0), 0),
-    ConfigSetting("scheduler_slo", ("scheduler", "slo"), _slo, required=True),
+                  cli="--ffn-policy", description="order in which waiting Instances get a free Lane: arrival, seeded random, or earliest SLO deadline"),
+    ConfigSetting("scheduler_ffn_random_seed", ("scheduler", "ffn_random_seed"), _int(0), 0,
+                  description="seed of the random Lane policy"),
+    ConfigSetting("scheduler_slo", ("scheduler", "slo"), _slo, required=True,
+                  description="default service-level objective {ttft_ms, tbt_ms} (time to first token, time between tokens); a [[models]] entry may override it"),
     # engine sizing of the attention ranks this repository hosts itself (covered by the configuration digest: every
     # process of a deployment must agree on the row capacities the slots are sized for)
     ConfigSetting("engine_max_rows", ("engine", "max_rows"), _int(1, 1 << 20), 4096, env_var="XPOOL_MAX_ROWS",
@@ -292,6 +306,21 @@ class XpoolConfig:
 
     def digest(self) -> str:
         return hashlib.sha256(json.dumps(self.as_dict(), sort_keys=True).encode()).hexdigest()
+
+
+def reference_markdown() -> str:
+    """The settings table of the user documentation (``xpool config reference``), generated from the registry so the
+    two cannot drift apart."""
+    def cell(v) -> str:
+        return str(v).replace("|", "\\|")
+
+    lines = ["| TOML key | environment | command line | default | meaning |", "| --- | --- | --- | --- | --- |"]
+    for s in CONFIG_REGISTRY:
+        key = ".".join(s.path) if s.path else "(bootstrap only)"
+        default = "required" if s.required else ("" if s.default is _MISSING else repr(s.default))
+        lines.append(f"| `{key}` | {f'`{s.env_var}`' if s.env_var else ''} | {f'`{s.cli}`' if s.cli else ''} | {cell(default)} | "
+                     f"{cell(s.description or s.name)} |")
+    return "\n".join(lines) + "\n"
 
 
 def add_cli_arguments(parser: argparse.ArgumentParser) -> None:

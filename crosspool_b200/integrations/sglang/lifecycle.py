@@ -70,7 +70,8 @@ def resolved_graph_capacity(eager_capacity: int, *, enabled: bool, buckets: Any 
 def derive_instance_ffn_profile(model_runner: Any, hidden_size: int, shims: list | None = None, dp_size: int = 1
                                 ) -> InstanceFfnProfile:
     """The profile registered with the daemon, from the *resolved* state of the serving process: payload dtype bf16
-    or fp16; at least one installed FFN shim, all of one hidden size; row capacities from the eager limits
+    (fp16 is refused here, before the first operator call would refuse it); at least one installed FFN shim, all of
+    one hidden size; row capacities from the eager limits
     (``max_running_requests`` for decode, the prefill chunk for prefill) widened by the captured graph buckets; with
     attention DP one invocation carries every data-parallel rank's rows and may ask for the group sum.
     Reference: src/xpool/integrations/sglang/hooks/lifecycle.py:402-467."""
@@ -83,8 +84,8 @@ def derive_instance_ffn_profile(model_runner: Any, hidden_size: int, shims: list
         payload = encode_dtype(dtype)
     except (TypeError, ValueError):
         payload = None
-    if payload not in ("bfloat16", "float16"):
-        raise ProfileError(f"the FFN payload does not support the serving dtype {dtype!r}")
+    if payload != "bfloat16":       # the FFN kernels and the ffn_shim operator of this build carry bf16 rows only
+        raise ProfileError(f"the FFN payload does not support the serving dtype {dtype!r} (bfloat16 only)")
     kinds: list[str] = []
     if shims is not None:
         if not shims:

@@ -1,0 +1,52 @@
+"""The user documentation embeds tables that the code prints; they must not drift apart."""
+
+import re
+from pathlib import Path
+
+DOCS = Path(__file__).resolve().parents[1] / "docs"
+
+
+def _generated(page: str) -> str:
+    text = (DOCS / page).read_text()
+    m = re.search(r"<!-- generated: [^>]* -->\n(.*?)<!-- end generated -->", text, re.S)
+    assert m, f"{page} has no generated block"
+    return m.group(1)
+
+
+def test_configuration_page_lists_exactly_the_registry():
+    from crosspool_b200 import config as C
+
+    assert _generated("configuration.md") == C.reference_markdown()
+    assert all(s.description for s in C.CONFIG_REGISTRY)
+
+
+def test_supported_models_page_is_what_the_adapters_and_engines_implement():
+    from crosspool_b200.models import adapters
+    from crosspool_b200.models.support import support_markdown, supported_architectures
+
+    assert _generated("supported-models.md") == support_markdown()
+    rows = {r.architecture: r for r in supported_architectures()}
+    assert set(rows) == set(adapters.ADAPTERS)
+    assert rows["Qwen3ForCausalLM"].gpu_attention and not rows["DeepseekV2ForCausalLM"].gpu_attention
+    assert all(r.engine_adapter for r in rows.values())
+
+
+def test_every_page_of_the_index_exists_and_commands_named_in_the_docs_parse():
+    index = (DOCS / "README.md").read_text()
+    for page in re.findall(r"\]\(([\w\-]+\.md)\)", index):
+        assert (DOCS / page).exists(), page
+    from crosspool_b200.cli.main import _parser
+
+    p = _parser()
+    for argv in (["config", "dump"], ["config", "reference"], ["config", "models"], ["daemon", "check"], ["daemon", "serve"],
+                 ["atnagent", "--device", "0"], ["ffnagent", "--device", "1"], ["memory-profile", "--calibrate", "--out", "p.json"]):
+        p.parse_args(argv)
+
+
+def test_cli_prints_the_generated_tables(capsys):
+    from crosspool_b200.cli.main import main
+
+    assert main(["config", "reference"]) == 0
+    assert "`scheduler.ffn_policy`" in capsys.readouterr().out
+    assert main(["config", "models"]) == 0
+    assert "`GptOssForCausalLM`" in capsys.readouterr().out

@@ -214,10 +214,11 @@ def test_ffn_profile_is_derived_strictly_from_the_resolved_serving_state():
         L.derive_instance_ffn_profile(runner(), 64, [])
     with pytest.raises(L.ProfileError, match="hidden size"):
         L.derive_instance_ffn_profile(runner(), 64, [types.SimpleNamespace(layer_ordinal=0, hidden_size=128)])
-    fp32 = runner()
-    fp32.model_config.dtype = torch.float32
-    with pytest.raises(L.ProfileError, match="dtype"):
-        L.derive_instance_ffn_profile(fp32, 64, shims)
+    for other in (torch.float32, torch.float16, "float16"):      # the operator carries bf16 rows only: refused at registration
+        wide = runner()
+        wide.model_config.dtype = other
+        with pytest.raises(L.ProfileError, match="bfloat16 only"):
+            L.derive_instance_ffn_profile(wide, 64, shims)
     b = InstanceRankBinding("m", rank=5, tp_size=2, dp_size=4)
     t = L.InstanceRankTransportProfile.derive(b, dp)
     assert (t.payload_row_capacity, t.atn_tp_rank, t.atn_tp_size, t.atn_dp_rank, t.atn_dp_size) == (8192, 1, 2, 2, 4)
