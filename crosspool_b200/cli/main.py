@@ -30,6 +30,8 @@ def _parser() -> argparse.ArgumentParser:
     for name in ("atnagent", "ffnagent"):
         a = sub.add_parser(name)
         a.add_argument("--device", type=int, required=True)
+        a.add_argument("--backend", choices=("gpu", "cpu"), default="gpu",
+                       help="cpu: the same control plane with the shared-memory data plane and the PyTorch oracle (no GPU needed)")
     e = sub.add_parser("exec", help="run a command in the deployment's environment")
     e.add_argument("argv", nargs=argparse.REMAINDER)
     c = sub.add_parser("config")
@@ -149,13 +151,12 @@ def cmd_memory_profile(ns) -> int:
         print(json.dumps({"saved": ns.out, "samples": prof.samples, "max_abs_error_bytes": prof.max_abs_error_bytes,
                           "coefficients": vars(prof.coefficients)}, indent=2))
         return 0
-    from ..models import config as mc
     from ..service.daemon.placement import DeviceSupply, ModelDemand, place_ffn_models
 
     cfg = _load(ns)
     demands = []
     for m in cfg.models:
-        c = mc.load(m.path if m.path in mc.PRESETS else m.id)
+        c = cfg.model_shape(m.id)
         inter = c.moe_intermediate_size * max(1, c.num_experts_per_tok) if c.is_moe else c.intermediate_size
         demands.append(ModelDemand(m.id, tuple(c.ffn_param_bytes_per_layer(l) for l in range(c.num_layers)),
                                    cfg.ffn_tp_for(m.id), c.hidden_size, 4096, m.atn_world_size, inter))
@@ -171,7 +172,7 @@ def cmd_agent(ns, role: str) -> int:
     from ..runtime.launch import run_agent
 
     cfg = _load(ns)
-    return run_agent(cfg, role, ns.device)
+    return run_agent(cfg, role, ns.device, backend=ns.backend)
 
 
 def cmd_bench(ns) -> int:

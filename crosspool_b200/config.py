@@ -282,6 +282,22 @@ class XpoolConfig:
                 return m
         raise KeyError(model_id)
 
+    def model_shape(self, model_id: str):
+        """The model's shape (``models.config.ModelConfig``): the preset named by ``path`` or ``id``, else the
+        ``config.json`` of the checkpoint directory ``path``. Daemon, agents and tools all resolve it here."""
+        from .models import config as mc
+
+        m = self.model(model_id)
+        for name in (m.path, m.id):
+            if name and name in mc.PRESETS:
+                return mc.PRESETS[name]
+        if not m.path:
+            raise ConfigError(f"model {model_id!r} is not a preset and has no path to a checkpoint directory")
+        try:
+            return mc.load(m.path)
+        except FileNotFoundError as e:
+            raise ConfigError(f"model {model_id!r}: {e}") from None
+
     def slo_for(self, model_id: str) -> Slo:
         m = self.model(model_id)
         return m.slo or self.values["scheduler_slo"]

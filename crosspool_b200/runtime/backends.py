@@ -15,7 +15,6 @@ import torch
 
 from ..config import XpoolConfig
 from ..engine.atn_engine import AttentionEngine, EngineConfig
-from ..models import config as mc
 from ..models.weights import load_attention_from_safetensors, random_attention_weights
 from ..native import runtime as rt
 from ..parallel import fabric as F
@@ -26,11 +25,7 @@ _POLICY = {"fifo": rt.POLICY_FIFO, "random": rt.POLICY_RANDOM, "slo": rt.POLICY_
 
 def model_config_for(cfg: XpoolConfig, model_id: str):
     """The model's shape: a preset named by ``path`` or ``id``, else the ``config.json`` under ``path``."""
-    m = cfg.model(model_id)
-    for name in (m.path, m.id):
-        if name in mc.PRESETS:
-            return mc.PRESETS[name]
-    return mc.load(m.path)
+    return cfg.model_shape(model_id)
 
 
 def checkpoint_dir_for(cfg: XpoolConfig, model_id: str) -> str | None:

@@ -22,7 +22,44 @@ def hosted_instances(cfg: XpoolConfig, device: int) -> list[tuple[str, int]]:
     return out
 
 
-def run_agent(cfg: XpoolConfig, role: str, device: int) -> int:
+def run_cpu_agent(cfg: XpoolConfig, role: str, device: int) -> int:
+    """The agent of ``role`` for "device" ``device`` on the CPU data plane (``runtime/cpu_backends.py``): device numbers
+    are only names here; memory admission sees the host's free memory."""
+    import psutil
+
+    from ..native import EXPECTED_ABI
+    from ..service.client import self_ref
+    from .backends import model_config_for
+    from .cpu_backends import CPU_MAX_ROWS, CpuAtnBackend, CpuFfnBackend
+    from .roles import AtnAgent, FfnAgent
+
+    log = init_logging("AtnAgent" if role == "atnagent" else "FfnAgent", cfg.logging_level, cfg.logging_color)
+    client = XpoolClient(cfg.daemon_host, cfg.daemon_port)
+    owner = self_ref(EXPECTED_ABI)
+    client.check_config(owner, cfg.digest())
+    client.startup_agent(owner, Role.ATNAGENT if role == "atnagent" else Role.FFNAGENT, device)
+    rows = min(cfg.engine_max_rows, CPU_MAX_ROWS)
+    if role == "ffnagent":
+        vm = psutil.virtual_memory()
+        agent = FfnAgent(client, device, CpuFfnBackend(cfg, device, capacity_rows=rows), int(vm.available), int(vm.total), owner=owner)
+    else:
+        insts = hosted_instances(cfg, device)
+        port = cfg.serving_base_port + cfg.atn_devices.index(device)
+        backend = CpuAtnBackend(cfg, device, insts, listen=("127.0.0.1", port), capacity_rows=rows,
+                                max_batch=min(cfg.engine_max_batch, 16), max_seq_len=min(cfg.engine_max_seq_len, rows))
+        profs = [(m, r, InstanceFfnProfile(max_prefill_rows=rows, max_decode_rows=rows,
+                                           hidden_size=model_config_for(cfg, m).hidden_size)) for m, r in insts]
+        agent = AtnAgent(client, device, backend, profs, owner=owner)
+    log.info(kv(event="start", role=role, device=device, pid=os.getpid(), backend="cpu"))
+    rc = agent.run()
+    if agent.failed:
+        get_logger().error(kv(event="failed", reason=agent.failed, retained=agent.retained))
+    return rc
+
+
+def run_agent(cfg: XpoolConfig, role: str, device: int, backend: str = "gpu") -> int:
+    if backend == "cpu":
+        return run_cpu_agent(cfg, role, device)
     import torch
 
     from ..engine.atn_engine import EngineConfig

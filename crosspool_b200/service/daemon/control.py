@@ -216,10 +216,8 @@ class ControlPlane:
     def _demand_for(self, model_id: str) -> ModelDemand:
         if self._model_demand is not None:
             return self._model_demand(model_id)
-        from ...models import config as mc
-
         m = self.config.model(model_id)
-        cfg = mc.load(m.path if m.path in mc.PRESETS else m.id)
+        cfg = self.config.model_shape(model_id)
         regs = [r.payload for (mid, _), r in self.instances.items() if mid == model_id]
         rows = max([max(p.ffn_profile.max_prefill_rows, p.ffn_profile.max_decode_rows) for p in regs] or [1])
         inter = cfg.moe_intermediate_size * max(1, cfg.num_experts_per_tok) if cfg.is_moe else cfg.intermediate_size

@@ -1,0 +1,131 @@
+"""The whole product as real processes without a GPU: ``xpool daemon serve`` + ``xpool ffnagent --backend cpu`` x 2 +
+``xpool atnagent --backend cpu``; registration, placement, generation phases, handle brokering and readiness go
+through the daemon; requests over HTTP; the answer must be the undivided model's; quiesce retires every agent."""
+import os
+import signal
+import socket
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import httpx
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _toml(daemon_port: int, serve_port: int, models: str) -> str:
+    return f"""
+[daemon]
+port = {daemon_port}
+[atn]
+devices = [0]
+[ffn]
+devices = [1, 2]
+[scheduler.slo]
+ttft_ms = 2000
+tbt_ms = 50
+[serving]
+base_port = {serve_port}
+{models}
+"""
+
+
+def _run(tmp_path, models_toml, check):
+    dport, sport = _free_port(), _free_port()
+    cfgp = tmp_path / "xpool.toml"
+    cfgp.write_text(_toml(dport, sport, models_toml))
+    env = dict(os.environ, XPOOL_CONFIG=str(cfgp), PYTHONPATH=str(ROOT), XPOOL_MAX_ROWS="128", XPOOL_MAX_BATCH="4",
+               XPOOL_MAX_SEQ_LEN="128")
+    xp = [sys.executable, "-m", "crosspool_b200.cli.main"]
+    base = f"http://127.0.0.1:{dport}"
+    procs = [subprocess.Popen(xp + ["daemon", "serve"], env=env)]
+    try:
+        for _ in range(150):
+            try:
+                if httpx.get(base + "/health", timeout=1).status_code == 200:
+                    break
+            except httpx.HTTPError:
+                time.sleep(0.2)
+        for role, dev in (("ffnagent", 1), ("ffnagent", 2), ("atnagent", 0)):
+            procs.append(subprocess.Popen(xp + [role, "--device", str(dev), "--backend", "cpu"], env=env))
+        ready = False
+        for _ in range(400):
+            r = httpx.get(base + "/ready", timeout=2).json()
+            if r["system_ready"]:
+                ready = True
+                break
+            assert r["failure"] is None, r
+            assert all(p.poll() is None for p in procs), [p.poll() for p in procs]
+            time.sleep(0.25)
+        assert ready
+        assert subprocess.run(xp + ["daemon", "check"], env=env, capture_output=True).returncode == 0
+        check(f"http://127.0.0.1:{sport}", httpx.get(base + "/fabric/plan", timeout=2).json())
+        assert httpx.post(base + "/fabric/quiesce", json={"reason": "test"}, timeout=5).status_code == 200
+        for p in procs[1:]:
+            assert p.wait(60) == 0
+        assert httpx.get(base + "/fabric/plan", timeout=2).json()["phase"] == "stopped"
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.send_signal(signal.SIGTERM)
+        for p in procs:
+            try:
+                p.wait(10)
+            except subprocess.TimeoutExpired:
+                p.kill()
+
+
+def test_two_preset_models_on_a_shared_cpu_ffn_tier_answer_like_the_undivided_models(tmp_path):
+    import zlib
+
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.models.reference import ReferenceModel
+    from crosspool_b200.models.weights import random_attention_weights, random_ffn_weights
+
+    models = '[[models]]\nid = "tiny-qwen3"\nffn_tp_size = 2\n[[models]]\nid = "tiny-qwen3-moe"\nffn_tp_size = 2\n'
+
+    def check(url, plan):
+        assert {s["model_id"] for s in plan["shards"]} == {"tiny-qwen3", "tiny-qwen3-moe"}
+        for mid in ("tiny-qwen3", "tiny-qwen3-moe"):
+            prompt = list(range(3, 20))
+            out = httpx.post(url + "/generate", json={"model": mid, "input_ids": prompt, "max_new_tokens": 5}, timeout=120).json()
+            cfg, seed = mc.preset(mid), zlib.crc32(mid.encode()) % 1000
+            whole = ReferenceModel(cfg, random_attention_weights(cfg, seed, dtype=torch.float32), random_ffn_weights(cfg, seed, dtype=torch.float32))
+            want, _ = whole.generate(torch.tensor(prompt), 5)
+            assert out["output_ids"] == want
+        bad = httpx.post(url + "/generate", json={"model": "tiny-qwen3", "input_ids": [], "max_new_tokens": 5}, timeout=30)
+        assert bad.status_code == 422                               # a malformed request is answered, the service goes on
+        again = httpx.post(url + "/generate", json={"model": "tiny-qwen3", "input_ids": [5, 6, 7], "max_new_tokens": 2}, timeout=60)
+        assert again.status_code == 200 and len(again.json()["output_ids"]) == 2
+
+    _run(tmp_path, models, check)
+
+
+def test_a_library_checkpoint_with_latent_attention_is_served_through_the_daemon(tmp_path):
+    from crosspool_b200.devtools import hf_parity
+
+    name = "DeepseekV2ForCausalLM/plain-q-yarn"
+    if not hf_parity.available(name):
+        pytest.skip("the installed transformers has no DeepseekV2")
+    model = hf_parity.build_tiny_model(name)
+    ckpt = tmp_path / "ckpt"
+    model.save_pretrained(ckpt, safe_serialization=True)
+    models = f'[[models]]\nid = "dsv2"\npath = "{ckpt}"\nffn_tp_size = 2\n'
+
+    def check(url, plan):
+        prompt = list(range(7, 21))
+        out = httpx.post(url + "/generate", json={"input_ids": prompt, "max_new_tokens": 4}, timeout=120).json()
+        with torch.no_grad():
+            want = model.generate(torch.tensor([prompt]), max_new_tokens=4, do_sample=False)[0, len(prompt):].tolist()
+        assert out["output_ids"] == want
+
+    _run(tmp_path, models, check)
