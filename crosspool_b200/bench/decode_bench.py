@@ -16,8 +16,8 @@ from dataclasses import dataclass
 
 import torch
 
-from ..deployment import Deployment, InstanceHandle, percentile
-from ..engine.atn_engine import AttentionEngine, EngineConfig
+from ..deployment import Deployment, percentile
+from ..engine.atn_engine import EngineConfig
 from ..models.config import ModelConfig
 
 PAGE = 16

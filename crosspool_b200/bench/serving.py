@@ -25,7 +25,7 @@ import json
 import math
 import random
 import time
-from dataclasses import asdict, dataclass, field
+from dataclasses import dataclass, field
 from statistics import NormalDist
 
 from ..deployment import percentile

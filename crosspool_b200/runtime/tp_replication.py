@@ -10,7 +10,6 @@ deployment before stepping. The broadcast also carries the stop signal, so all r
 
 from __future__ import annotations
 
-import time
 
 from .serving import EngineLoop, Pending
 

@@ -18,7 +18,7 @@ through the shared-memory control channel; the policy answers with quota command
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Protocol
 
 
