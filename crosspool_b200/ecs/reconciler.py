@@ -151,13 +151,22 @@ class CapacityReconciler:
             return
         seq, target = self._pending
         live = len(self.cache.allocator.mapped_bundles())
-        if target > live + len(self._retiring):
-            free = self.cache.allocator.unmapped_bundles()
-            retiring = {r.bundle for r in self._retiring}
-            take = [b for b in free if b not in retiring][: target - live - len(self._retiring)]
-            if take and vmm.grow(self.cache, take) == 0:
-                self.events.append(("grow", len(take)))
-            self._complete(seq)   # partial growth is reported through mapped_bytes
+        if target > live:
+            # A bundle still waiting for its retirement gate is physically mapped: a command that grows past it takes it
+            # back instead of mapping another one. (The daemon sends no command to a partition that owes an answer, so
+            # this arises only when a command is superseded, e.g. by a restarted policy.)
+            while self._retiring and live < target:
+                r = self._retiring.pop()
+                self.cache.allocator.publish_bundle(r.bundle)
+                self.events.append(("reclaim", r.bundle))
+                live += 1
+            if target > live:
+                retiring = {r.bundle for r in self._retiring}
+                take = [b for b in self.cache.allocator.unmapped_bundles() if b not in retiring][: target - live]
+                if take and vmm.grow(self.cache, take) == 0:
+                    self.events.append(("grow", len(take)))
+            if not self._retiring:
+                self._complete(seq)   # partial growth is reported through mapped_bytes
             return
         # shrink: retire empty bundles (highest index first keeps low addresses dense)
         excess = live - target

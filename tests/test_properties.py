@@ -406,3 +406,121 @@ def test_any_placement_that_is_returned_covers_every_layer_once_and_fits_every_d
             assert r.stages[d.device].retained >= weights[d.device]                     # the ledger covers the weights
     again = place_ffn_models(demands, supply, ws_per_lane=1 << 20)
     assert again.groups == r.groups                                                   # deterministic
+
+
+class ReconcilerModel(RuleBasedStateMachine):
+    """An Instance rank's capacity reconciler under random commands, sequence traffic and gate openings, over the real
+    seqlock channel and the fake VMM driver. Physical memory matches the bookkeeping at every step, a bundle that holds
+    a page of a live sequence is never unmapped, a bundle waiting for its gate hands out no pages, completions only
+    move forward and always state the mapped bytes, and the floor stays mapped."""
+
+    BUNDLES = 5
+
+    def __init__(self):
+        super().__init__()
+        import os
+
+        from crosspool_b200.ecs import reconciler as R
+        from crosspool_b200.ecs import vmm
+        from crosspool_b200.models import config as mc
+        from crosspool_b200.native.runtime import EcsChannel
+
+        cfg = mc.preset("Qwen/Qwen3-0.6B")
+        self.ppb, _ = vmm.bundle_geometry(cfg, 16)
+        self.drv = vmm.Driver.fake(1 << 40)
+        self.cache = vmm.elastic_kv_cache(cfg, max_pages=self.BUNDLES * self.ppb, page_size=16, device="cpu", driver=self.drv,
+                                          quota=None, initial_bundles=2, make_tensors=False)
+        ReconcilerModel._n = getattr(ReconcilerModel, "_n", 0) + 1
+        self.ch = EcsChannel.create(f"/xp-prop-recon-{os.getpid()}-{ReconcilerModel._n}", 1, 1, 1)
+        self.gates: list[dict] = []
+
+        def gate_factory():
+            g = {"open": False}
+            self.gates.append(g)
+            return lambda: g["open"]
+
+        self.rec = R.CapacityReconciler(self.cache, self.ch, 0, gate_factory=gate_factory)
+        self.bb = self.rec.bundle_bytes
+        self.seq = 0
+        self.live: dict[int, int] = {}          # sequence id -> tokens
+        self.next_id = 0
+        self.last_completion = (0, 0)
+
+    @rule(target_bundles=st.integers(0, BUNDLES + 1))
+    def command(self, target_bundles):
+        self.seq += 1
+        self.ch.publish_command(0, self.seq, target_bundles * self.bb)
+
+    @rule()
+    def poll(self):
+        self.rec.poll()
+
+    @rule(pages=st.integers(1, 40))
+    def start_sequence(self, pages):
+        sid = self.next_id
+        self.next_id += 1
+        try:
+            self.cache.ensure(sid, 16 * pages)
+            self.live[sid] = 16 * pages
+        except OutOfPages:
+            self.cache.tables.pop(sid, None)
+
+    @precondition(lambda self: self.live)
+    @rule(data=st.data())
+    def finish_sequence(self, data):
+        sid = data.draw(st.sampled_from(sorted(self.live)))
+        self.cache.release(sid)
+        del self.live[sid]
+
+    @precondition(lambda self: any(not g["open"] for g in self.gates))
+    @rule(data=st.data())
+    def open_a_gate(self, data):
+        closed = [g for g in self.gates if not g["open"]]
+        data.draw(st.sampled_from(closed))["open"] = True
+
+    @invariant()
+    def memory_matches_the_books(self):
+        alloc, backing = self.cache.allocator, self.cache.backing
+        handing_out = set(alloc.mapped_bundles())
+        retiring = {r.bundle for r in self.rec._retiring}
+        assert not handing_out & retiring
+        physically = {b for b in range(self.BUNDLES) if backing.is_mapped(b)}
+        assert physically == handing_out | retiring
+        assert self.drv.counts()["allocated_bytes"] == len(physically) * self.bb == self.rec.mapped_bytes
+        assert 0 in handing_out                                      # the floor
+        for sid, table in self.cache.tables.items():
+            for p in table:
+                assert p // self.ppb in handing_out                  # live pages sit in bundles that stay mapped
+        for b in retiring:
+            assert alloc.used_in_bundle(b) == 0 and not alloc._free[b]
+
+    @invariant()
+    def completions_move_forward_and_state_the_mapping(self):
+        seq, mapped = self.ch.read_completion(0)
+        assert seq >= self.last_completion[0] and seq <= self.seq
+        if seq != self.last_completion[0]:
+            assert mapped == self.rec.mapped_bytes                   # written at the moment of completion
+        self.last_completion = (seq, mapped)
+
+    def teardown(self):
+        # everything drains: finish the sequences, open the gates, poll -> the last command is carried out in full
+        for sid in list(self.live):
+            self.cache.release(sid)
+        for g in self.gates:
+            g["open"] = True
+        for _ in range(4):
+            self.rec.poll()
+            for g in self.gates:
+                g["open"] = True
+        if self.seq:
+            seq, target = self.ch.read_command(0)
+            want = min(self.BUNDLES, max(1, target // self.bb))
+            assert self.ch.read_completion(0)[0] == seq
+            assert self.rec.mapped_bundles == want
+        self.cache.backing.close()
+        self.ch.close()
+
+
+ReconcilerModel.TestCase.settings = settings(max_examples=80, stateful_step_count=40, deadline=None,
+                                             suppress_health_check=[HealthCheck.too_slow])
+test_capacity_reconciler_keeps_memory_and_books_equal = ReconcilerModel.TestCase
