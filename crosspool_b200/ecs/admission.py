@@ -32,7 +32,7 @@ def largest_chunk_that_fits(*, cached_tokens: int, have_pages: int, want_tokens:
     def need(n: int) -> int:
         return max(0, pages_for(cached_tokens + n, page_size) - have_pages)
 
-    budget = free_pages - reserve_pages
+    budget = max(0, free_pages - reserve_pages)     # tokens that fit the pages the sequence already holds always run
     full = need(want_tokens)
     if full <= budget:
         return PrefillProposal(want_tokens, 0)
@@ -43,7 +43,7 @@ def largest_chunk_that_fits(*, cached_tokens: int, have_pages: int, want_tokens:
             lo = mid
         else:
             hi = mid
-    return PrefillProposal(lo if lo >= min_tokens else 0, full - max(0, budget))
+    return PrefillProposal(lo if lo >= min_tokens else 0, full - budget)
 
 
 def coordinate_prefill(local: PrefillProposal, agree_min: Callable[[int], int] | None = None) -> PrefillProposal:

@@ -524,3 +524,42 @@ class ReconcilerModel(RuleBasedStateMachine):
 ReconcilerModel.TestCase.settings = settings(max_examples=80, stateful_step_count=40, deadline=None,
                                              suppress_health_check=[HealthCheck.too_slow])
 test_capacity_reconciler_keeps_memory_and_books_equal = ReconcilerModel.TestCase
+
+
+@settings(max_examples=400, deadline=None)
+@given(cached=st.integers(0, 200), extra_pages=st.integers(0, 3), want=st.integers(1, 300), free=st.integers(0, 24),
+       reserve=st.integers(0, 4), page=st.sampled_from([4, 16]), min_tokens=st.integers(1, 40))
+def test_prefill_admission_returns_the_longest_chunk_that_fits(cached, extra_pages, want, free, reserve, page, min_tokens):
+    from crosspool_b200.ecs.admission import largest_chunk_that_fits, pages_for
+
+    have = pages_for(cached, page) + extra_pages
+    got = largest_chunk_that_fits(cached_tokens=cached, have_pages=have, want_tokens=want, free_pages=free, page_size=page,
+                                  reserve_pages=reserve, min_tokens=min_tokens)
+    budget = max(0, free - reserve)         # what needs no new page always fits, whatever the reserve
+    need = lambda n: max(0, pages_for(cached + n, page) - have)
+    fitting = [n for n in range(0, want + 1) if need(n) <= budget]
+    best = max(fitting) if fitting else 0
+    if best == want:
+        assert (got.tokens, got.missing_pages) == (want, 0)
+    else:
+        assert got.tokens == (best if best >= min_tokens else 0)
+        assert got.missing_pages == need(want) - budget > 0
+    assert need(got.tokens) <= budget
+
+
+@settings(max_examples=300, deadline=None)
+@given(seqs=st.lists(st.tuples(st.integers(1, 80), st.integers(0, 2)), min_size=0, max_size=8), free=st.integers(0, 4),
+       page=st.sampled_from([4, 16]))
+def test_decode_retraction_takes_the_fewest_newest_sequences(seqs, free, page):
+    from crosspool_b200.ecs.admission import check_decode_mem, pages_for, retract_decode
+
+    lens = [n for n, _ in seqs]
+    pages = [pages_for(n, page) + extra for n, extra in seqs]
+    out = retract_decode(lens, pages, free, page)
+    assert out == sorted(out, reverse=True) and out == list(range(len(lens) - 1, len(lens) - 1 - len(out), -1))   # a suffix, newest first
+    kept = lens[: len(lens) - len(out)]
+    freed = free + sum(pages[i] for i in out)
+    assert check_decode_mem(kept, freed, page)[0]
+    if out:      # one retraction fewer would not have been enough
+        fewer = out[:-1]
+        assert not check_decode_mem(lens[: len(lens) - len(fewer)], free + sum(pages[i] for i in fewer), page)[0]
