@@ -7,6 +7,14 @@ ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
+try:    # property-based tests draw the same examples on every run: a suite run is a regression check, not a search
+    from hypothesis import settings as _hyp_settings
+
+    _hyp_settings.register_profile("suite", derandomize=True, deadline=None, print_blob=True)
+    _hyp_settings.load_profile("suite")
+except ImportError:  # pragma: no cover
+    pass
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a real B200 (run with -m gpu)")

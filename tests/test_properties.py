@@ -563,3 +563,200 @@ def test_decode_retraction_takes_the_fewest_newest_sequences(seqs, free, page):
     if out:      # one retraction fewer would not have been enough
         fewer = out[:-1]
         assert not check_decode_mem(lens[: len(lens) - len(fewer)], free + sum(pages[i] for i in fewer), page)[0]
+
+
+class GenerationLifecycle(RuleBasedStateMachine):
+    """The daemon's generation barrier under random scheduling of three real agents (fake backends, in-process HTTP),
+    process deaths, stale heartbeats, backend failures, reported invocation failures and operator quiesce. The fabric
+    phase only moves along the allowed edges; it is executable only while every participant is registered and has
+    activated; after any disturbance the survivors retire the generation to STOPPED (fail-stop: no re-planning while
+    serving), and an undisturbed run becomes executable."""
+
+    EDGES = {"preparing_join": {"joining"}, "joining": {"preparing_execution"}, "preparing_execution": {"activating"},
+             "activating": {"executable"}, "executable": {"quiescing"}, "quiescing": {"draining"},
+             "aborting": {"draining"}, "draining": {"finalizing"}, "finalizing": {"stopped"}, "stopped": set()}
+
+    def __init__(self):
+        super().__init__()
+        from fastapi.testclient import TestClient
+
+        from crosspool_b200 import config as C
+        from crosspool_b200.native import EXPECTED_ABI
+        from crosspool_b200.runtime.roles import AtnAgent, FfnAgent
+        from crosspool_b200.service.client import XpoolClient
+        from crosspool_b200.service.daemon.app import create_app
+        from crosspool_b200.service.daemon.control import ControlPlane
+        from crosspool_b200.service.wire import InstanceFfnProfile, ProcessRef
+
+        toml = ('[atn]\ndevices = [0]\n[ffn]\ndevices = [1, 2]\n[scheduler.slo]\nttft_ms = 2000\ntbt_ms = 50\n'
+                '[[models]]\nid = "Qwen/Qwen3-0.6B"\nffn_tp_size = 2\n')
+        cfg = C.load_config(env={}, toml_text=toml)
+        self.now = [0.0]
+        self.dead: set[int] = set()
+        self.cp = ControlPlane(cfg, clock=lambda: self.now[0], process_alive=lambda ref: ref.pid not in self.dead)
+        self.http = TestClient(create_app(cfg, self.cp, background=False))
+        self.http.__enter__()
+
+        class Client(XpoolClient):
+            def __init__(self, http):
+                self._http = http
+
+        class Backend:
+            def __init__(self):
+                self.fail_in, self.failure, self.calls = None, None, []
+
+            def _do(self, what):
+                self.calls.append(what)
+                if self.fail_in == what:
+                    raise RuntimeError(f"broke in {what}")
+
+            def prepare_join(self, plan):
+                self._do("prepare_join")
+                return {f"slot:{id(self)}": "ab" * 8}
+
+            def join(self, plan):
+                self._do("join")
+
+            def prepare_execution(self, plan):
+                self._do("prepare_execution")
+
+            def activate(self, plan):
+                self._do("activate")
+
+            def poll_health(self):
+                return self.failure
+
+            def quiesce(self):
+                self._do("quiesce")
+
+            def drain(self):
+                self._do("drain")
+                return True
+
+            def finalize(self):
+                self._do("finalize")
+
+        client = Client(self.http)
+        prof = InstanceFfnProfile(max_prefill_rows=512, max_decode_rows=64, hidden_size=1024)
+        own = lambda pid: ProcessRef(abi_version=EXPECTED_ABI, pid=pid, create_time=1.0)
+        self.agents = [AtnAgent(client, 0, Backend(), [("Qwen/Qwen3-0.6B", 0, prof)], owner=own(10)),
+                       FfnAgent(client, 1, Backend(), 64 << 30, 180 << 30, owner=own(21)),
+                       FfnAgent(client, 2, Backend(), 64 << 30, 180 << 30, owner=own(22))]
+        for a in self.agents:
+            a.register()
+        self.disturbed = False
+        self.seen = [self._phase()]
+
+    def _phase(self):
+        g = self.cp.generation
+        return g.phase.value if g else None
+
+    def _alive(self, a):
+        if a.failed:                       # a failed agent reports once and exits non-zero (Agent.run)
+            self.dead.add(a.owner.pid)
+        return a.owner.pid not in self.dead
+
+    def _beat(self):
+        for a in self.agents:
+            if self._alive(a):
+                try:
+                    a.heartbeat()
+                except Exception:
+                    pass            # a participant the daemon has dropped gets "gone"; it stops, the others go on
+
+    # ---- rules
+    @rule(i=st.integers(0, 2))
+    def one_agent_takes_a_step(self, i):
+        a = self.agents[i]
+        if self._alive(a):
+            try:
+                a.advance()
+            except Exception:
+                pass                # "gone" after the daemon dropped it
+            self._note()
+
+    @rule(ms=st.integers(100, 4000))
+    def time_passes_with_heartbeats(self, ms):
+        self.now[0] += ms / 1e3
+        self._beat()
+        self.cp.watchdog()
+        self._note()
+
+    @rule(i=st.integers(0, 2))
+    def a_process_dies(self, i):
+        self.dead.add(self.agents[i].owner.pid)
+        self.disturbed = True
+        self.cp.watchdog()
+        self._note()
+
+    @rule(i=st.integers(0, 2), where=st.sampled_from(["prepare_join", "join", "prepare_execution", "activate"]))
+    def a_backend_will_break(self, i, where):
+        b = self.agents[i].backend
+        if where not in b.calls:
+            b.fail_in = where
+            self.disturbed = True
+
+    @rule(i=st.integers(1, 2))
+    def a_lane_reports_an_invocation_failure(self, i):
+        from crosspool_b200.service.wire import InvocationFailure
+
+        if self._phase() == "executable":
+            self.agents[i].backend.failure = InvocationFailure(result_code=3, origin_pe=i, instance_index=0, invocation_sequence=7,
+                                                               layer_ordinal=1)
+            self.disturbed = True
+
+    @rule()
+    def the_operator_quiesces(self):
+        if self.cp.generation is not None:
+            self.cp.quiesce("test")
+            self.disturbed = True
+            self._note()
+
+    # ---- bookkeeping and invariants
+    def _note(self):
+        p = self._phase()
+        if p != self.seen[-1]:
+            prev = self.seen[-1]
+            if prev is not None:      # several edges may be taken inside one daemon call (nobody left to wait for)
+                reach, frontier = set(), {prev}
+                while frontier:
+                    nxt = {q for f in frontier for q in self.EDGES[f]} - reach
+                    reach |= nxt
+                    frontier = nxt
+                assert p in reach or p == "aborting" and prev not in ("draining", "finalizing", "stopped"), (prev, p)
+            self.seen.append(p)
+
+    @invariant()
+    def executable_means_everyone_is_there_and_active(self):
+        self._note()
+        from crosspool_b200.service.wire import ParticipantPhase
+
+        if self._phase() == "executable":
+            g = self.cp.generation
+            regs = [self.cp._participant(k) for k in g.participants.values()]
+            assert len(regs) == 3 and all(r is not None and r.phase == ParticipantPhase.ACTIVE for r in regs)
+            assert g.failure is None
+
+    def teardown(self):
+        # the survivors keep following the protocol; time passes; the daemon's watchdog runs
+        for _ in range(16):
+            for a in self.agents:
+                if self._alive(a):
+                    try:
+                        a.advance()
+                    except Exception:
+                        pass
+            self.now[0] += 1.0
+            self._beat()
+            self.cp.watchdog()
+            self._note()
+        if self.disturbed:
+            assert self._phase() in ("stopped", None), self.seen      # None: a participant was lost before any plan existed
+        else:
+            assert self._phase() == "executable", self.seen
+        self.http.__exit__(None, None, None)
+
+
+GenerationLifecycle.TestCase.settings = settings(max_examples=50, stateful_step_count=25, deadline=None,
+                                                 suppress_health_check=[HealthCheck.too_slow])
+test_generation_barrier_under_random_disturbances = GenerationLifecycle.TestCase
