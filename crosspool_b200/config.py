@@ -19,6 +19,8 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any, Callable, Mapping, Sequence
 
+from .model import ModelId
+
 _MISSING = object()
 
 
@@ -249,6 +251,10 @@ def _parse_models(doc: Mapping[str, Any], ffn_devices: tuple[int, ...]) -> tuple
         if "id" not in m:
             raise ConfigError(f"models[{i}] misses id")
         mid = str(m["id"])
+        try:
+            ModelId.parse(mid)
+        except ValueError as e:
+            raise ConfigError(f"models[{i}]: {e}") from None
         if mid in seen:
             raise ConfigError(f"duplicate model id {mid}")
         seen.add(mid)
@@ -291,12 +297,22 @@ class XpoolConfig:
         for name in (m.path, m.id):
             if name and name in mc.PRESETS:
                 return mc.PRESETS[name]
-        if not m.path:
-            raise ConfigError(f"model {model_id!r} is not a preset and has no path to a checkpoint directory")
         try:
-            return mc.load(m.path)
+            return mc.load(str(self.model_path(model_id)))
         except FileNotFoundError as e:
             raise ConfigError(f"model {model_id!r}: {e}") from None
+
+    def model_path(self, model_id: str) -> Path | None:
+        """Where the model's checkpoint is looked for: ``path`` (default: the id written as a relative path), taken
+        relative to ``vendor.model_base_uri`` unless absolute. None for a preset, which has no files."""
+        from .models import config as mc
+
+        m = self.model(model_id)
+        if m.path in mc.PRESETS or (m.path == m.id and m.id in mc.PRESETS):
+            return None
+        p = Path(m.path)
+        base = self.values.get("vendor_model_base_uri") or ""
+        return p if p.is_absolute() or not base else Path(base) / p
 
     def slo_for(self, model_id: str) -> Slo:
         m = self.model(model_id)

@@ -11,10 +11,17 @@ _PART = r"[A-Za-z0-9][A-Za-z0-9._-]*"
 _RE = re.compile(rf"^(?:({_PART})/)?({_PART})$")
 
 
-@dataclass(frozen=True, order=True)
+@dataclass(frozen=True)
 class ModelId:
     namespace: str
     name: str
+
+    def __lt__(self, other: "ModelId") -> bool:
+        """Identifiers sort as their text does (``a-/x`` before ``a/z``), the order every listing and the placement
+        search use, so two processes that sort the same set agree whatever the components are."""
+        if not isinstance(other, ModelId):
+            return NotImplemented
+        return str(self) < str(other)
 
     @classmethod
     def parse(cls, text: str) -> "ModelId":

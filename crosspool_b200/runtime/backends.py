@@ -29,10 +29,10 @@ def model_config_for(cfg: XpoolConfig, model_id: str):
 
 
 def checkpoint_dir_for(cfg: XpoolConfig, model_id: str) -> str | None:
-    """The model's checkpoint directory when ``path`` names one (``config.json`` plus safetensors files); None
-    for presets, which run on random-init weights."""
-    p = Path(cfg.model(model_id).path or "")
-    if p.is_dir() and (p / "config.json").exists() and any(p.glob("*.safetensors")):
+    """The model's checkpoint directory when its path (``XpoolConfig.model_path``) names one (``config.json`` plus
+    safetensors files); None for presets, which run on random-init weights."""
+    p = cfg.model_path(model_id)
+    if p is not None and p.is_dir() and (p / "config.json").exists() and any(p.glob("*.safetensors")):
         return str(p)
     return None
 

@@ -90,3 +90,48 @@ def test_engine_knobs_and_ports_are_registry_settings_covered_by_the_digest():
     assert a.digest() != b.digest()      # two processes that disagree on slot sizing fail the config check
     with pytest.raises(C.ConfigError, match="page_size"):
         C.load_config(toml_text=base + "[engine]\npage_size=48\n", env={})
+
+
+def test_model_paths_resolve_against_the_vendor_base_and_ids_must_be_canonical(tmp_path):
+    import json
+
+    import pytest
+
+    from crosspool_b200 import config as C
+    from crosspool_b200.runtime.backends import checkpoint_dir_for
+
+    base = tmp_path / "models"
+    (base / "acme" / "tiny").mkdir(parents=True)
+    hf = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4,
+          "num_key_value_heads": 2, "intermediate_size": 128, "vocab_size": 256, "head_dim": 16}
+    (base / "acme" / "tiny" / "config.json").write_text(json.dumps(hf))
+    (base / "acme" / "tiny" / "model.safetensors").write_bytes(b"")
+    toml = f"""
+[vendor]
+model_base_uri = "{base}"
+[atn]
+devices = [0]
+[ffn]
+devices = [1]
+[scheduler.slo]
+ttft_ms = 2000
+tbt_ms = 50
+[[models]]
+id = "acme/tiny"
+[[models]]
+id = "Qwen/Qwen3-0.6B"
+[[models]]
+id = "elsewhere"
+path = "{tmp_path}/absolute"
+"""
+    cfg = C.load_config(toml_text=toml, env={})
+    assert cfg.model_path("acme/tiny") == base / "acme" / "tiny"            # the id, under the base
+    assert cfg.model_shape("acme/tiny").hidden_size == 64
+    assert checkpoint_dir_for(cfg, "acme/tiny") == str(base / "acme" / "tiny")
+    assert cfg.model_path("Qwen/Qwen3-0.6B") is None and cfg.model_shape("Qwen/Qwen3-0.6B").num_layers == 28   # a preset
+    assert cfg.model_path("elsewhere") == tmp_path / "absolute"              # absolute paths ignore the base
+    with pytest.raises(C.ConfigError, match="elsewhere"):
+        cfg.model_shape("elsewhere")
+    for bad in ("org/a/b", "../x", " org/model"):
+        with pytest.raises(C.ConfigError, match="invalid model id"):
+            C.load_config(toml_text=toml.replace('id = "acme/tiny"', f'id = "{bad}"'), env={})

@@ -238,3 +238,22 @@ def test_integers_are_range_checked_before_they_reach_native_code():
         assert ch.read_command(0) == (1, 4096)
     finally:
         ch.close()
+
+
+def test_model_ids_follow_the_references_rules_for_canonical_components_and_order():
+    """Vectors of the reference's identity test (tests/suites/unit/test_model.py): what is refused, how an id is
+    written into a URI, and that ids sort as their text. A bare preset name without a namespace is this repository's
+    own addition."""
+    import pytest
+
+    from crosspool_b200.model import ModelId
+
+    m = ModelId.parse("Qwen/Qwen3-14B")
+    assert (m.namespace, m.name, str(m), m.uri()) == ("Qwen", "Qwen3-14B", "Qwen/Qwen3-14B", "Qwen%2FQwen3-14B")
+    assert m != "Qwen/Qwen3-14B" and len({m, ModelId.parse(str(m))}) == 1
+    assert sorted((ModelId.parse("a/z"), ModelId.parse("a-/x"))) == [ModelId.parse("a-/x"), ModelId.parse("a/z")]
+    for bad in ["/model", "org/", "org/a/b", "../model", "org/.", " org/model", "组织/model", ""]:
+        with pytest.raises(ValueError):
+            ModelId.parse(bad)
+    with pytest.raises(Exception):
+        m.name = "Other"            # frozen
