@@ -9,7 +9,6 @@ from __future__ import annotations
 
 import threading
 import zlib
-from pathlib import Path
 
 import torch
 
