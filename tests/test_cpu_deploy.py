@@ -22,14 +22,14 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _toml(daemon_port: int, serve_port: int, models: str) -> str:
+def _toml(daemon_port: int, serve_port: int, models: str, atn=(0,), ffn=(1, 2)) -> str:
     return f"""
 [daemon]
 port = {daemon_port}
 [atn]
-devices = [0]
+devices = {list(atn)}
 [ffn]
-devices = [1, 2]
+devices = {list(ffn)}
 [scheduler.slo]
 ttft_ms = 2000
 tbt_ms = 50
@@ -39,10 +39,10 @@ base_port = {serve_port}
 """
 
 
-def _run(tmp_path, models_toml, check):
+def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2)):
     dport, sport = _free_port(), _free_port()
     cfgp = tmp_path / "xpool.toml"
-    cfgp.write_text(_toml(dport, sport, models_toml))
+    cfgp.write_text(_toml(dport, sport, models_toml, atn, ffn))
     env = dict(os.environ, XPOOL_CONFIG=str(cfgp), PYTHONPATH=str(ROOT), XPOOL_MAX_ROWS="128", XPOOL_MAX_BATCH="4",
                XPOOL_MAX_SEQ_LEN="128")
     xp = [sys.executable, "-m", "crosspool_b200.cli.main"]
@@ -55,7 +55,7 @@ def _run(tmp_path, models_toml, check):
                     break
             except httpx.HTTPError:
                 time.sleep(0.2)
-        for role, dev in (("ffnagent", 1), ("ffnagent", 2), ("atnagent", 0)):
+        for role, dev in [("ffnagent", d) for d in ffn] + [("atnagent", d) for d in atn]:
             procs.append(subprocess.Popen(xp + [role, "--device", str(dev), "--backend", "cpu"], env=env))
         ready = False
         for _ in range(400):
@@ -129,3 +129,44 @@ def test_a_library_checkpoint_with_latent_attention_is_served_through_the_daemon
         assert out["output_ids"] == want
 
     _run(tmp_path, models, check)
+
+
+def test_data_parallel_attention_ranks_share_the_ffn_tier_behind_the_request_router(tmp_path):
+    """One model as two data-parallel Instance ranks (two attention agents), FFN tensor-parallel over two FFN agents
+    that keep one copy of the shard for both ranks; the request router spreads requests over the ranks by outstanding
+    tokens and every answer is the undivided model's."""
+    import asyncio
+    import zlib
+
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.models.reference import ReferenceModel
+    from crosspool_b200.models.weights import random_attention_weights, random_ffn_weights
+    from crosspool_b200.runtime.dp_router import DpRouter, create_router_app
+
+    models = '[[models]]\nid = "tiny-qwen3"\natn_dp_size = 2\nffn_tp_size = 2\n'
+
+    def check(url, plan):
+        base = int(url.rsplit(":", 1)[1])
+        ranks = [f"http://127.0.0.1:{base}", f"http://127.0.0.1:{base + 1}"]
+        assert sorted((r["model_id"], r["rank"]) for r in plan["instance_ranks"]) == [("tiny-qwen3", 0), ("tiny-qwen3", 1)]
+        router = DpRouter()
+        for u in ranks:
+            router.register("tiny-qwen3", u)
+        app = create_router_app(router)
+        cfg, seed = mc.preset("tiny-qwen3"), zlib.crc32(b"tiny-qwen3") % 1000
+        whole = ReferenceModel(cfg, random_attention_weights(cfg, seed, dtype=torch.float32), random_ffn_weights(cfg, seed, dtype=torch.float32))
+        prompts = [list(range(3 + i, 15 + 2 * i)) for i in range(4)]
+
+        async def go():
+            async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://router", timeout=120) as c:
+                return await asyncio.gather(*[c.post("/generate", json={"model": "tiny-qwen3", "input_ids": p, "max_new_tokens": 4})
+                                              for p in prompts])
+
+        outs = asyncio.run(go())
+        for p, r in zip(prompts, outs):
+            assert r.status_code == 200
+            assert r.json()["output_ids"] == whole.generate(torch.tensor(p), 4)[0]
+        served = [b.served for b in router.backends["tiny-qwen3"]]
+        assert sum(served) == 4 and min(served) >= 1              # both ranks took part
+
+    _run(tmp_path, models, check, atn=(0, 1), ffn=(2, 3))
