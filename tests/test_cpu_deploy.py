@@ -39,7 +39,7 @@ base_port = {serve_port}
 """
 
 
-def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2)):
+def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2), retire=True):
     dport, sport = _free_port(), _free_port()
     cfgp = tmp_path / "xpool.toml"
     cfgp.write_text(_toml(dport, sport, models_toml, atn, ffn))
@@ -68,6 +68,9 @@ def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2)):
             time.sleep(0.25)
         assert ready
         assert subprocess.run(xp + ["daemon", "check"], env=env, capture_output=True).returncode == 0
+        if not retire:
+            check(f"http://127.0.0.1:{sport}", base, procs)
+            return
         check(f"http://127.0.0.1:{sport}", httpx.get(base + "/fabric/plan", timeout=2).json())
         assert httpx.post(base + "/fabric/quiesce", json={"reason": "test"}, timeout=5).status_code == 200
         for p in procs[1:]:
@@ -170,3 +173,34 @@ def test_data_parallel_attention_ranks_share_the_ffn_tier_behind_the_request_rou
         assert sum(served) == 4 and min(served) >= 1              # both ranks took part
 
     _run(tmp_path, models, check, atn=(0, 1), ffn=(2, 3))
+
+
+def test_an_ffn_agent_that_dies_is_noticed_and_the_survivors_retire_the_generation(tmp_path):
+    """Failure detection end to end, made on the host: an FFN agent process is killed between requests. The daemon's
+    watchdog classifies the owner as exited and aborts the generation (fail-stop, no re-planning while serving);
+    readiness reports the failure; the surviving agents quiesce, drain, finalise and exit cleanly."""
+    models = '[[models]]\nid = "tiny-qwen3"\nffn_tp_size = 2\n'
+
+    def check(url, base, procs):
+        ok = httpx.post(url + "/generate", json={"input_ids": [4, 5, 6, 7], "max_new_tokens": 3}, timeout=120)
+        assert ok.status_code == 200 and len(ok.json()["output_ids"]) == 3
+        victim = procs[2]                                   # the second FFN agent
+        victim.kill()
+        victim.wait(10)
+        failure = None
+        for _ in range(120):
+            r = httpx.get(base + "/ready", timeout=2).json()
+            failure = r["failure"]
+            if failure:
+                break
+            time.sleep(0.25)
+        assert failure and "ffnagent:2" in failure and "exited" in failure, failure
+        assert not r["system_ready"]
+        for p in (procs[1], procs[3]):                      # the other FFN agent and the attention agent
+            assert p.wait(60) == 0
+        plan = httpx.get(base + "/fabric/plan", timeout=2).json()
+        assert plan["phase"] == "stopped"
+        with pytest.raises(httpx.HTTPError):                # the Instance no longer serves
+            httpx.post(url + "/generate", json={"input_ids": [4, 5, 6], "max_new_tokens": 2}, timeout=5)
+
+    _run(tmp_path, models, check, retire=False)
