@@ -26,6 +26,7 @@ import torch
 from ..config import XpoolConfig
 from ..engine.atn_engine import Sequence
 from ..engine.cpu_plumbing import RemoteFfn, _view
+from ..engine.kv_cache import OutOfPages
 from ..models import reference
 from ..models.weights import load_attention_from_safetensors, random_attention_weights, random_ffn_layer
 from ..native import runtime as rt
@@ -210,10 +211,35 @@ class CpuOracleEngine:
         self.running: list[Sequence] = []
         self._caches: dict[int, object] = {}
         self._next_id = 0
-        self.stats = {"prefill_steps": 0, "decode_steps": 0}
+        self.stats = {"prefill_steps": 0, "decode_steps": 0, "stalled_for_pages": 0}
+        self.kv = None                  # page accounting (engine/kv_cache.py) when the deployment runs elastic KV
+        self.capacity = None
+        self.ttft_slo_s = 0.0
+        self._demand_pages = 0
 
     def warmup(self) -> None:
         pass
+
+    def attach_kv(self, kv, reconciler=None, ttft_slo_s: float = 0.0) -> None:
+        """Accounts the sequences' KV in pages of ``kv`` (tensors stay the oracle's own): a prompt is admitted when its
+        pages fit what is mapped, a decode step takes a page when it crosses a boundary, and when pages are missing
+        the engine publishes demand through ``reconciler`` and waits for the daemon's grow command, exactly the loop
+        the GPU engine runs (``AttentionEngine.attach_capacity``)."""
+        self.kv, self.capacity, self.ttft_slo_s = kv, reconciler, ttft_slo_s
+
+    def idle_tick(self) -> None:
+        if self.capacity is not None:
+            self.capacity.poll()
+
+    def _demand(self, missing_pages: int, head: Sequence | None) -> None:
+        if self.capacity is None or missing_pages == self._demand_pages:
+            return
+        self._demand_pages = missing_pages
+        if missing_pages <= 0:
+            self.capacity.withdraw_demand()
+            return
+        deadline = int((head.arrival + self.ttft_slo_s) * 1e9) if head is not None and self.ttft_slo_s > 0 else 0
+        self.capacity.publish_demand(missing_pages, deadline)
 
     def add_request(self, prompt: list[int], max_new_tokens: int, arrival: float | None = None, deadline: float = 0.0,
                     temperature: float = 0.0, seed: int = 0) -> Sequence:
@@ -246,6 +272,8 @@ class CpuOracleEngine:
         if s.finished:
             s.finish_time = now
             self._caches.pop(s.seq_id, None)
+            if self.kv is not None:
+                self.kv.release(s.seq_id)
             if s in self.running:
                 self.running.remove(s)
         elif s not in self.running:
@@ -254,7 +282,20 @@ class CpuOracleEngine:
     @torch.no_grad()
     def step(self) -> list[tuple[Sequence, int]]:
         out: list[tuple[Sequence, int]] = []
-        if self.waiting and len(self.running) < self.max_batch:
+        if self.capacity is not None:
+            self.capacity.poll()
+        admit = bool(self.waiting) and len(self.running) < self.max_batch
+        if admit and self.kv is not None:
+            head = self.waiting[0]
+            missing = self.kv.pages_needed(head.seq_id, len(head.prompt) + 1) - self.kv.allocator.free_pages
+            if missing > 0:
+                self._demand(missing, head)              # wait for the daemon's grow command; running work goes on
+                self.stats["stalled_for_pages"] += 1
+                admit = False
+            else:
+                self._demand(0, None)
+                self.kv.ensure(head.seq_id, len(head.prompt) + 1)
+        if admit:
             s = self.waiting.popleft()
             cache = self._caches[s.seq_id] = self.model.new_cache()
             n = len(s.prompt)
@@ -264,10 +305,19 @@ class CpuOracleEngine:
             self._emit(s, lg, time.monotonic(), out)
             return out
         for s in list(self.running):
+            if self.kv is not None:
+                try:
+                    self.kv.ensure(s.seq_id, s.total_len + 1)
+                except OutOfPages:
+                    self._demand(1, s)                   # this sequence skips the step until a page is mapped
+                    self.stats["stalled_for_pages"] += 1
+                    continue
             pos = s.total_len - 1
             lg = self.model.forward(torch.tensor([s.generated[-1]]), torch.tensor([pos]), self._caches[s.seq_id], self.ffn)
             self._emit(s, lg, time.monotonic(), out)
         self.stats["decode_steps"] += 1
+        if not out:
+            time.sleep(0.002)                            # everything waits for memory: do not spin on the channel
         return out
 
 
@@ -291,7 +341,13 @@ class CpuDeployment:
         for model_id, e in self.engines.items():
             if e.has_work:
                 res.tokens[model_id] = e.step()
+            else:
+                e.idle_tick()
         return res
+
+    def idle_tick(self) -> None:
+        for e in self.engines.values():
+            e.idle_tick()
 
 
 class CpuAtnBackend:
@@ -307,6 +363,44 @@ class CpuAtnBackend:
         self._server = None
         self.loop = None
         self.listener: ServingListener | None = None
+        self.ecs_ref = None              # callable(generation) -> EcsChannelRef, set by the launcher when elastic KV is on
+        self.kv_budget_bytes = 64 << 20  # what this "device" reports as its memory to the capacity policy
+        self._ecs_channel = None
+        self.reconcilers: list = []
+
+    def _attach_elastic_kv(self, plan: FabricPlan) -> None:
+        """Elastic KV on the CPU data plane: page accounting over the fake VMM driver (no tensors behind it), the real
+        seqlock channel, reconciler and daemon policy. Bundles are 16 KiB per buffer so that tiny models move memory
+        in steps of a few pages."""
+        from ..ecs import reconciler as R
+        from ..ecs import vmm
+        from ..native.runtime import EcsChannel
+
+        ref = None
+        for _ in range(400):                                  # the daemon opens the channel on its next policy tick
+            try:
+                ref = self.ecs_ref(plan.generation)
+                break
+            except Exception:
+                time.sleep(0.05)
+        if ref is None:
+            raise RuntimeError("the daemon did not publish an ECS control channel")
+        self._ecs_channel = EcsChannel.attach(ref.name)
+        gran, page = 16 << 10, 16
+        mapped = 0
+        for (model_id, rank), place in self.places.items():
+            eng = self.engines[model_id]
+            pages = eng.max_batch * ((eng.max_seq_len + page - 1) // page)
+            kv = vmm.elastic_kv_cache(place.cfg, pages, page, "cpu", vmm.Driver.fake(1 << 40, granularity=gran), None,
+                                      initial_bundles=1, make_tensors=False, granularity=gran)
+            idx = ref.partitions[f"{model_id}:{rank}"]
+            bb = kv.backing.bundle_bytes
+            self._ecs_channel.set_partition(idx, self.device, 0, rank, bb, kv.backing.bundle_count * bb)
+            rec = R.CapacityReconciler(kv, self._ecs_channel, idx)
+            eng.attach_kv(kv, rec, ttft_slo_s=self.cfg.slo_for(model_id).ttft_ms / 1e3)
+            self.reconcilers.append(rec)
+            mapped += bb
+        self._ecs_channel.publish_report(ref.devices[str(self.device)], max(0, self.kv_budget_bytes - mapped), self.kv_budget_bytes, 1)
 
     def prepare_join(self, plan: FabricPlan) -> dict[str, str]:
         torch.set_num_threads(1)
@@ -339,6 +433,8 @@ class CpuAtnBackend:
                 aw = random_attention_weights(place.cfg, place.seed, dtype=torch.float32)
             self.engines[model_id] = CpuOracleEngine(place.cfg, aw, self.ports[model_id], self.max_batch,
                                                      min(self.max_seq_len, self.capacity_rows))
+        if self.cfg.atn_elastic_kv and self.ecs_ref is not None:
+            self._attach_elastic_kv(plan)
 
     def activate(self, plan: FabricPlan) -> None:
         pass
@@ -378,3 +474,6 @@ class CpuAtnBackend:
             mb.close()
         self._boxes = []
         self.engines.clear()
+        if self._ecs_channel is not None:
+            self._ecs_channel.close()
+            self._ecs_channel = None

@@ -47,6 +47,9 @@ def run_cpu_agent(cfg: XpoolConfig, role: str, device: int) -> int:
         port = cfg.serving_base_port + cfg.atn_devices.index(device)
         backend = CpuAtnBackend(cfg, device, insts, listen=("127.0.0.1", port), capacity_rows=rows,
                                 max_batch=min(cfg.engine_max_batch, 16), max_seq_len=min(cfg.engine_max_seq_len, rows))
+        if cfg.atn_elastic_kv:
+            backend.ecs_ref = client.ecs_channel
+            backend.kv_budget_bytes = int(os.environ.get("XPOOL_CPU_KV_BYTES", backend.kv_budget_bytes))
         profs = [(m, r, InstanceFfnProfile(max_prefill_rows=rows, max_decode_rows=rows,
                                            hidden_size=model_config_for(cfg, m).hidden_size)) for m, r in insts]
         agent = AtnAgent(client, device, backend, profs, owner=owner)

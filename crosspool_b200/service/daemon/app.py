@@ -165,6 +165,12 @@ def create_app(config: XpoolConfig, control: ControlPlane | None = None, *, back
     def terminate_owner(owner: ProcessRef):
         return {"signalled": cp.terminate_owner(owner)}
 
+    @app.get("/ecs/state")
+    def ecs_state():
+        if app.state.ecs is None:
+            raise DaemonError("not_ready", "elastic KV is not enabled in this deployment")
+        return app.state.ecs.state()
+
     @app.get("/ecs/control-channel/{generation}")
     def ecs_channel(generation: int):
         ref: EcsChannelRef | None = app.state.ecs_channel_ref

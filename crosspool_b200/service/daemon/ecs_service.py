@@ -69,6 +69,21 @@ class EcsService:
         self.frozen = True
         return True
 
+    def state(self) -> dict:
+        """What an operator wants to see of the arbitration: pools, every partition's floor / reservation / target /
+        mapped bytes and current demand, and the most recent policy events (``GET /ecs/state``)."""
+        out: dict = {"generation": self.generation, "frozen": self.frozen, "pools": {}, "partitions": [], "events": []}
+        pol = self.policy
+        if pol is None:
+            return out
+        out["pools"] = {str(d): {"budget_bytes": p.budget_bytes, "unassigned_bytes": p.unassigned_bytes} for d, p in pol.pools.items()}
+        out["partitions"] = [{"key": p.key, "device": p.device, "floor_bytes": p.floor_bytes, "reservation_bytes": p.reservation_bytes,
+                              "target_bytes": p.target_bytes, "mapped_bytes": p.mapped_bytes, "demand_bytes": p.demand_bytes,
+                              "pending": p.pending} for p in pol.parts.values()]
+        out["events"] = [{"step": e.step, "kind": e.kind, "partition": e.partition, "bytes": e.bytes, "detail": e.detail}
+                         for e in pol.events[-200:]]
+        return out
+
     def tick(self):
         gen = self.cp.generation
         if gen is None or gen.phase in (FabricPhase.STOPPED, FabricPhase.ABORTING, FabricPhase.FINALIZING):

@@ -22,12 +22,13 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _toml(daemon_port: int, serve_port: int, models: str, atn=(0,), ffn=(1, 2)) -> str:
+def _toml(daemon_port: int, serve_port: int, models: str, atn=(0,), ffn=(1, 2), atn_extra="") -> str:
     return f"""
 [daemon]
 port = {daemon_port}
 [atn]
 devices = {list(atn)}
+{atn_extra}
 [ffn]
 devices = {list(ffn)}
 [scheduler.slo]
@@ -39,12 +40,12 @@ base_port = {serve_port}
 """
 
 
-def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2), retire=True):
+def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2), retire=True, atn_extra="", extra_env=None):
     dport, sport = _free_port(), _free_port()
     cfgp = tmp_path / "xpool.toml"
-    cfgp.write_text(_toml(dport, sport, models_toml, atn, ffn))
+    cfgp.write_text(_toml(dport, sport, models_toml, atn, ffn, atn_extra))
     env = dict(os.environ, XPOOL_CONFIG=str(cfgp), PYTHONPATH=str(ROOT), XPOOL_MAX_ROWS="128", XPOOL_MAX_BATCH="4",
-               XPOOL_MAX_SEQ_LEN="128")
+               XPOOL_MAX_SEQ_LEN="128", **(extra_env or {}))
     xp = [sys.executable, "-m", "crosspool_b200.cli.main"]
     base = f"http://127.0.0.1:{dport}"
     procs = [subprocess.Popen(xp + ["daemon", "serve"], env=env)]
@@ -204,3 +205,53 @@ def test_an_ffn_agent_that_dies_is_noticed_and_the_survivors_retire_the_generati
             httpx.post(url + "/generate", json={"input_ids": [4, 5, 6], "max_new_tokens": 2}, timeout=5)
 
     _run(tmp_path, models, check, retire=False)
+
+
+def test_elastic_kv_is_lent_from_an_idle_model_to_a_loaded_one_through_the_daemons_policy(tmp_path):
+    """Two co-located models with elastic KV on a "device" of ten bundles: each starts with five. Four long requests
+    for one model need seven; the engine publishes demand over the shared-memory channel, the daemon's policy shrinks
+    the idle neighbour, then grows the borrower, the reconcilers carry the commands out, and every request is
+    answered as the undivided model answers it."""
+    import concurrent.futures as cf
+    import zlib
+
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.models.reference import ReferenceModel
+    from crosspool_b200.models.weights import random_attention_weights, random_ffn_weights
+
+    models = '[[models]]\nid = "tiny-qwen3"\nffn_tp_size = 2\n[[models]]\nid = "tiny-qwen3-moe"\nffn_tp_size = 2\n'
+    bundle = 4 * (16 << 10)                     # 2 layers x (K, V) x 16 KiB
+
+    def check(url, base, procs):
+        st = {}
+        for _ in range(100):                    # the policy freezes the pools once both partitions are described
+            st = httpx.get(base + "/ecs/state", timeout=2).json()
+            if st["frozen"] and all(p["mapped_bytes"] == 5 * bundle for p in st["partitions"]):
+                break
+            time.sleep(0.1)
+        assert st["frozen"] and st["pools"]["0"]["budget_bytes"] == 10 * bundle
+        assert sorted(p["target_bytes"] for p in st["partitions"]) == [5 * bundle, 5 * bundle]
+        cfg, seed = mc.preset("tiny-qwen3"), zlib.crc32(b"tiny-qwen3") % 1000
+        whole = ReferenceModel(cfg, random_attention_weights(cfg, seed, dtype=torch.float32), random_ffn_weights(cfg, seed, dtype=torch.float32))
+        prompts = [[(7 * i + j) % 4000 + 1 for j in range(100)] for i in range(4)]      # 7 pages each: 28 pages = 7 bundles
+        with cf.ThreadPoolExecutor(4) as pool:
+            outs = list(pool.map(lambda p: httpx.post(url + "/generate", json={"model": "tiny-qwen3", "input_ids": p, "max_new_tokens": 6},
+                                                      timeout=180).json(), prompts))
+        for p, o in zip(prompts, outs):
+            assert o["output_ids"] == whole.generate(torch.tensor(p), 6)[0]
+        st = httpx.get(base + "/ecs/state", timeout=2).json()
+        kinds = [(e["kind"], e["partition"]) for e in st["events"]]
+        assert ("shrink", "tiny-qwen3-moe:0") in kinds and ("grow", "tiny-qwen3:0") in kinds
+        assert kinds.index(("shrink", "tiny-qwen3-moe:0")) < kinds.index(("grow", "tiny-qwen3:0"))
+        by = {p["key"]: p for p in st["partitions"]}
+        assert by["tiny-qwen3:0"]["target_bytes"] >= 7 * bundle and by["tiny-qwen3-moe:0"]["target_bytes"] <= 3 * bundle
+        assert sum(p["target_bytes"] for p in st["partitions"]) + st["pools"]["0"]["unassigned_bytes"] <= 10 * bundle
+        # the lender still serves
+        ok = httpx.post(url + "/generate", json={"model": "tiny-qwen3-moe", "input_ids": [3, 4, 5], "max_new_tokens": 2}, timeout=60)
+        assert ok.status_code == 200
+        assert httpx.post(base + "/fabric/quiesce", json={"reason": "test"}, timeout=5).status_code == 200
+        for p in procs[1:]:
+            assert p.wait(60) == 0
+
+    _run(tmp_path, models, check, retire=False, atn_extra="elastic_kv = true\ndevice_memory_utilization = 1.0",
+         extra_env={"XPOOL_CPU_KV_BYTES": str(10 * bundle)})
