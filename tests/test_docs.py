@@ -50,3 +50,13 @@ def test_cli_prints_the_generated_tables(capsys):
     assert "`scheduler.ffn_policy`" in capsys.readouterr().out
     assert main(["config", "models"]) == 0
     assert "`GptOssForCausalLM`" in capsys.readouterr().out
+
+
+def test_every_variable_of_the_example_environment_file_is_one_the_code_reads():
+    from crosspool_b200 import config as C
+
+    root = DOCS.parent
+    names = set(re.findall(r"^#?\s*([A-Z][A-Z0-9_]+)=", (root / ".env.example").read_text(), re.M))
+    known = {s.env_var for s in C.CONFIG_REGISTRY if s.env_var} | {"XPOOL_NVTX", "XPOOL_CPU_KV_BYTES", "SGLANG_PLUGINS"}
+    assert names <= known, names - known
+    assert (root / "configs" / "xpool.example.toml").exists()
