@@ -1,57 +1,54 @@
-"""Physical geometry of an Instance rank's elastic KV: what one bundle costs, how many there can be, how many stay.
+"""What an Instance rank tells the daemon about its elastic KV before the capacity policy starts: how large one bundle
+is, how many bundles its address range can ever hold, and how many it never gives up.
 
-A *pool* is one elastic backing (here: the K and V buffers of all layers of one KV cache, grown and shrunk together one
-bundle at a time). The profile is what the rank tells the daemon when it describes its partition: the floor it never
-gives up and the reservation it can never exceed. It holds no residency state; that lives in the page allocator and
-the backing. Reference: src/xpool/ecs.py (``PoolProfile``, ``ElasticContextStateProfile``).
+In this repository an Instance rank has exactly one elastic backing (the K and V buffers of all layers of its KV cache
+grow and shrink together, one bundle at a time), so the geometry is one record; the reference describes a tuple of
+pools per rank (src/xpool/ecs.py, ``ElasticContextStateProfile``). The record holds no residency state: which bundles
+are mapped is the page allocator's and the backing's business.
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass
 
-from ..utils.integer import ensure_uint64
+from ..utils.integer import ensure_uint32, ensure_uint64
 
 
 @dataclass(frozen=True)
-class PoolProfile:
-    bundle_bytes: int        # physical cost of one bundle over all buffers of the pool
-    bundle_capacity: int     # bundles the address range can hold (the reservation)
-    floor_bundles: int       # bundles that stay mapped for the life of the cache
+class KvPartitionGeometry:
+    bundle_bytes: int
+    bundles: int
+    floor_bundles: int = 1
 
     def __post_init__(self):
-        ensure_uint64(self.bundle_bytes, self.bundle_capacity, self.floor_bundles)
-        if self.bundle_bytes == 0 or self.floor_bundles > self.bundle_capacity:
-            raise ValueError("a pool needs a positive bundle size and a floor inside its reservation")
-        ensure_uint64(self.bundle_bytes * self.bundle_capacity)
+        ensure_uint64(self.bundle_bytes, self.bundles, self.floor_bundles, self.bundle_bytes * self.bundles)
+        if self.bundle_bytes == 0 or self.bundles == 0:
+            raise ValueError("an elastic KV partition needs at least one bundle of at least one byte")
+        if self.floor_bundles > self.bundles:
+            raise ValueError(f"a floor of {self.floor_bundles} bundles does not fit a range of {self.bundles}")
 
-    def bytes_for(self, bundles: int) -> int:
-        ensure_uint64(bundles)
-        if bundles > self.bundle_capacity:
-            raise ValueError(f"{bundles} bundles exceed the pool's reservation of {self.bundle_capacity}")
-        return bundles * self.bundle_bytes
-
-
-@dataclass(frozen=True)
-class ElasticKvProfile:
-    pools: tuple[PoolProfile, ...]
-
-    def __post_init__(self):
-        if not isinstance(self.pools, tuple):
-            raise ValueError("pools must be a tuple")
-        ensure_uint64(self.floor_bytes, self.reservation_bytes)
+    @classmethod
+    def of(cls, cache, floor_bundles: int = 1) -> "KvPartitionGeometry":
+        """Geometry of an elastic ``PagedKvCache`` (``ecs/vmm.py::elastic_kv_cache``)."""
+        if cache.backing is None:
+            raise ValueError("the KV cache has no elastic backing")
+        return cls(cache.backing.bundle_bytes, cache.backing.bundle_count, floor_bundles)
 
     @property
     def floor_bytes(self) -> int:
-        return sum(p.floor_bundles * p.bundle_bytes for p in self.pools)
+        return self.floor_bundles * self.bundle_bytes
 
     @property
     def reservation_bytes(self) -> int:
-        return sum(p.bundle_capacity * p.bundle_bytes for p in self.pools)
+        return self.bundles * self.bundle_bytes
 
+    def whole_bundles(self, nbytes: int) -> int:
+        """Bundles a byte target pays for, kept between the floor and the range."""
+        ensure_uint64(nbytes)
+        return max(self.floor_bundles, min(self.bundles, nbytes // self.bundle_bytes))
 
-def profile_of(cache, floor_bundles: int = 1) -> ElasticKvProfile:
-    """The profile of an elastic ``PagedKvCache`` (``ecs/vmm.py::elastic_kv_cache``): one pool."""
-    if cache.backing is None:
-        raise ValueError("the KV cache has no elastic backing")
-    return ElasticKvProfile((PoolProfile(cache.backing.bundle_bytes, cache.backing.bundle_count, floor_bundles),))
+    def describe(self, channel, index: int, device: int, rank: int, group: int = 0) -> None:
+        """Writes the partition's description into the control channel; the policy freezes the device pools once
+        every partition of the generation has one."""
+        ensure_uint32(index, device, rank, group)
+        channel.set_partition(index, device, group, rank, self.floor_bytes, self.reservation_bytes)

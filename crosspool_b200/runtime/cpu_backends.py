@@ -374,7 +374,7 @@ class CpuAtnBackend:
         in steps of a few pages."""
         from ..ecs import reconciler as R
         from ..ecs import vmm
-        from ..ecs.profile import profile_of
+        from ..ecs.profile import KvPartitionGeometry
         from ..native.runtime import EcsChannel
 
         ref = None
@@ -395,10 +395,10 @@ class CpuAtnBackend:
             kv = vmm.elastic_kv_cache(place.cfg, pages, page, "cpu", vmm.Driver.fake(1 << 40, granularity=gran), None,
                                       initial_bundles=1, make_tensors=False, granularity=gran)
             idx = ref.partitions[f"{model_id}:{rank}"]
-            prof = profile_of(kv, floor_bundles=1)
-            bb = prof.pools[0].bundle_bytes
-            self._ecs_channel.set_partition(idx, self.device, 0, rank, prof.floor_bytes, prof.reservation_bytes)
-            rec = R.CapacityReconciler(kv, self._ecs_channel, idx, floor_bundles=prof.pools[0].floor_bundles)
+            geo = KvPartitionGeometry.of(kv, floor_bundles=1)
+            bb = geo.bundle_bytes
+            geo.describe(self._ecs_channel, idx, self.device, rank)
+            rec = R.CapacityReconciler(kv, self._ecs_channel, idx, floor_bundles=geo.floor_bundles)
             eng.attach_kv(kv, rec, ttft_slo_s=self.cfg.slo_for(model_id).ttft_ms / 1e3)
             self.reconcilers.append(rec)
             mapped += bb

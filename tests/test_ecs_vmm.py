@@ -90,30 +90,33 @@ def test_allocator_only_hands_out_pages_of_mapped_bundles_and_retires_empty_ones
     assert q.charged == 2 * cache.backing.bundle_bytes
 
 
-def test_pool_profiles_state_floor_and_reservation_and_refuse_impossible_geometry():
+def test_partition_geometry_states_floor_and_reservation_and_refuses_impossible_shapes():
+    import os
+
     import pytest
 
     from crosspool_b200.ecs import vmm
-    from crosspool_b200.ecs.profile import ElasticKvProfile, PoolProfile, profile_of
+    from crosspool_b200.ecs.profile import KvPartitionGeometry
     from crosspool_b200.models import config as mc
+    from crosspool_b200.native.runtime import EcsChannel
 
-    p = PoolProfile(bundle_bytes=4096, bundle_capacity=10, floor_bundles=2)
-    assert p.bytes_for(3) == 12288
-    with pytest.raises(ValueError):
-        p.bytes_for(11)
-    for bad in (dict(bundle_bytes=0, bundle_capacity=1, floor_bundles=0), dict(bundle_bytes=1, bundle_capacity=1, floor_bundles=2)):
+    g = KvPartitionGeometry(bundle_bytes=4096, bundles=10, floor_bundles=2)
+    assert (g.floor_bytes, g.reservation_bytes) == (8192, 40960)
+    assert [g.whole_bundles(n) for n in (0, 4095, 12288, 12289, 1 << 30)] == [2, 2, 3, 3, 10]
+    for bad in (dict(bundle_bytes=0, bundles=1), dict(bundle_bytes=1, bundles=0), dict(bundle_bytes=1, bundles=1, floor_bundles=2)):
         with pytest.raises(ValueError):
-            PoolProfile(**bad)
+            KvPartitionGeometry(**bad)
     with pytest.raises(OverflowError):
-        PoolProfile(bundle_bytes=1 << 40, bundle_capacity=1 << 40, floor_bundles=0)
-    prof = ElasticKvProfile((p, PoolProfile(100, 5, 1)))
-    assert (prof.floor_bytes, prof.reservation_bytes) == (2 * 4096 + 100, 10 * 4096 + 500)
-    with pytest.raises(ValueError):
-        ElasticKvProfile([p])
+        KvPartitionGeometry(bundle_bytes=1 << 40, bundles=1 << 40)
     cfg = mc.preset("tiny-qwen3")
     cache = vmm.elastic_kv_cache(cfg, 32, 16, "cpu", vmm.Driver.fake(1 << 30, granularity=16 << 10), None, initial_bundles=1,
                                  make_tensors=False, granularity=16 << 10)
-    got = profile_of(cache)
-    assert got.pools[0].bundle_bytes == cache.backing.bundle_bytes == 4 * (16 << 10)
-    assert got.reservation_bytes == 8 * cache.backing.bundle_bytes and got.floor_bytes == cache.backing.bundle_bytes
-    cache.backing.close()
+    got = KvPartitionGeometry.of(cache)
+    assert got.bundle_bytes == cache.backing.bundle_bytes == 4 * (16 << 10) and got.bundles == 8
+    ch = EcsChannel.create(f"/xp-geo-{os.getpid()}", 1, 1, 1)
+    try:
+        got.describe(ch, 0, device=3, rank=1)
+        assert ch.partition(0) == dict(device=3, group=0, rank=1, floor_bytes=got.floor_bytes, reservation_bytes=got.reservation_bytes)
+    finally:
+        ch.close()
+        cache.backing.close()
