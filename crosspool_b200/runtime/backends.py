@@ -281,7 +281,10 @@ class AtnBackend:
         if self._listen is not None and leader:
             import uvicorn
 
-            app = create_serving_app(self.loop, list(self.engines))
+            from .serving import load_tokenizers
+
+            toks = load_tokenizers({m: place.checkpoint for (m, _), place in self.places.items()})
+            app = create_serving_app(self.loop, list(self.engines), tokenizer=toks)
             conf = uvicorn.Config(app, host=self._listen[0], port=self._listen[1], log_level="warning")
             self._server = uvicorn.Server(conf)
             threading.Thread(target=self._server.run, daemon=True, name="serving-http").start()

@@ -442,7 +442,7 @@ class CpuAtnBackend:
         pass
 
     def warm_and_serve(self) -> None:
-        from .serving import EngineLoop, create_serving_app
+        from .serving import EngineLoop, create_serving_app, load_tokenizers
 
         for mb in self._boxes:                                   # the FFN agents have activated their arenas by now
             if mb.wait_status(rt.MBOX_IDLE, 30.0) != rt.WAIT_READY:
@@ -452,7 +452,8 @@ class CpuAtnBackend:
         if self._listen is not None:
             import uvicorn
 
-            app = create_serving_app(self.loop, list(self.engines))
+            toks = load_tokenizers({m: place.checkpoint for (m, _), place in self.places.items()})
+            app = create_serving_app(self.loop, list(self.engines), tokenizer=toks)
             self._server = uvicorn.Server(uvicorn.Config(app, host=self._listen[0], port=self._listen[1], log_level="warning"))
             threading.Thread(target=self._server.run, daemon=True, name="serving-http").start()
             self.listener = ServingListener(host=self._listen[0], port=self._listen[1])

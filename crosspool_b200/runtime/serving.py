@@ -180,7 +180,33 @@ class GenerateRequest(BaseModel):
     seed: int = 0
 
 
+def load_tokenizers(checkpoints: dict[str, str | None]) -> dict:
+    """Tokenizers of the models whose checkpoint directory ships one (``tokenizer.json`` or ``tokenizer_config.json``),
+    through ``transformers.AutoTokenizer``; models without one (presets, weights-only directories) are served by token
+    ids only. A tokenizer that fails to load is skipped with a warning: text is a convenience of this endpoint, not a
+    reason to refuse serving."""
+    import os
+
+    out: dict = {}
+    for model_id, path in checkpoints.items():
+        if not path or not any(os.path.exists(os.path.join(path, f)) for f in ("tokenizer.json", "tokenizer_config.json")):
+            continue
+        try:
+            from transformers import AutoTokenizer
+
+            out[model_id] = AutoTokenizer.from_pretrained(path, local_files_only=True)
+        except Exception as e:       # pragma: no cover - depends on the files found
+            from ..logging import get_logger, kv
+
+            get_logger().warning(kv(event="tokenizer_skipped", model=model_id, error=repr(e)[:200]))
+    return out
+
+
 def create_serving_app(loop: EngineLoop, models: list[str], tokenizer=None):
+    """``tokenizer``: one tokenizer for every model, or ``{model id: tokenizer}`` (see :func:`load_tokenizers`)."""
+    def tok_for(model: str):
+        return tokenizer.get(model) if isinstance(tokenizer, dict) else tokenizer
+
     from fastapi import FastAPI, HTTPException
     from fastapi.responses import StreamingResponse
 
@@ -201,10 +227,11 @@ def create_serving_app(loop: EngineLoop, models: list[str], tokenizer=None):
         if model not in models:
             raise HTTPException(status_code=404, detail=f"model {model} is not served here")
         ids = req.input_ids
+        tok_model = tok_for(model)
         if ids is None:
-            if req.text is None or tokenizer is None:
+            if req.text is None or tok_model is None:
                 raise HTTPException(status_code=422, detail="input_ids required (no tokenizer configured)")
-            ids = tokenizer.encode(req.text)
+            ids = tok_model.encode(req.text)
         p = loop.submit(model, list(ids), req.max_new_tokens, req.temperature, req.seed, aio=True)
         if req.stream:
             async def sse():
@@ -230,6 +257,6 @@ def create_serving_app(loop: EngineLoop, models: list[str], tokenizer=None):
             out.append(item[0])
             if item[1]:
                 break
-        return {"output_ids": out, "text": tokenizer.decode(out) if tokenizer else None}
+        return {"output_ids": out, "text": tok_model.decode(out) if tok_model else None}
 
     return app

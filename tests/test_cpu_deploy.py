@@ -125,12 +125,34 @@ def test_a_library_checkpoint_with_latent_attention_is_served_through_the_daemon
     model.save_pretrained(ckpt, safe_serialization=True)
     models = f'[[models]]\nid = "dsv2"\npath = "{ckpt}"\nffn_tp_size = 2\n'
 
+    # the checkpoint ships a tokenizer: requests may carry text, answers carry the decoded text too
+    from tokenizers import Tokenizer, pre_tokenizers
+    from tokenizers import models as tok_models
+    from transformers import PreTrainedTokenizerFast
+
+    words = [f"w{i}" for i in range(1, 200)]
+    wl = Tokenizer(tok_models.WordLevel({"<unk>": 0, **{w: i + 1 for i, w in enumerate(words)}}, unk_token="<unk>"))
+    wl.pre_tokenizer = pre_tokenizers.Whitespace()
+    PreTrainedTokenizerFast(tokenizer_object=wl, unk_token="<unk>").save_pretrained(ckpt)
+
     def check(url, plan):
+        import json
+
         prompt = list(range(7, 21))
         out = httpx.post(url + "/generate", json={"input_ids": prompt, "max_new_tokens": 4}, timeout=120).json()
         with torch.no_grad():
             want = model.generate(torch.tensor([prompt]), max_new_tokens=4, do_sample=False)[0, len(prompt):].tolist()
         assert out["output_ids"] == want
+        text = " ".join(f"w{i}" for i in prompt)             # word wN has id N
+        by_text = httpx.post(url + "/generate", json={"text": text, "max_new_tokens": 4}, timeout=120).json()
+        assert by_text["output_ids"] == want
+        assert by_text["text"].split() == [f"w{i}" if 0 < i < 200 else "<unk>" for i in want]
+        # streaming: one server-sent event per token, the last one marked finished
+        with httpx.stream("POST", url + "/generate", json={"input_ids": prompt, "max_new_tokens": 4, "stream": True}, timeout=120) as r:
+            events = [line[6:] for line in r.iter_lines() if line.startswith("data: ")]
+        assert events[-1] == "[DONE]"
+        toks = [json.loads(e) for e in events[:-1]]
+        assert [t["token_id"] for t in toks] == want and [t["finished"] for t in toks] == [False, False, False, True]
 
     _run(tmp_path, models, check)
 
