@@ -17,6 +17,7 @@ import asyncio
 import hashlib
 import json
 import statistics
+import sys
 from dataclasses import asdict, dataclass, field
 from pathlib import Path
 from typing import Callable
@@ -182,8 +183,80 @@ def run_suite(cases: list[Case], targets: dict[str, str], out: Path, *, cont: bo
     return res
 
 
+def rate_tag(rate: float) -> str:
+    """``0.5`` -> ``0p5rps``, ``4`` -> ``4rps`` (the naming of the catalogue's rate sweeps)."""
+    text = f"{rate:g}".replace(".", "p")
+    return f"{text}rps"
+
+
+def generate_cases(deployment: str, models: int, rates: list[float], *, split: tuple[float, ...] | None = None,
+                   extra: dict | None = None) -> str:
+    """TOML for one sweep of a catalogue: a case per rate for ``deployment`` with ``models`` co-located models.
+    ``split`` skews the offered load between the models (fractions of ``models`` x rate, e.g. ``(0.8, 0.2)``);
+    ``extra`` adds the same keys (``duration_s``, ``prompt``, ...) to every case. The reference generates its
+    catalogue the same way (``xbench case-gen``)."""
+    if models < 1 or not rates:
+        raise ValueError("a sweep needs at least one model and one rate")
+    if split is not None and (len(split) != models or abs(sum(split) - 1.0) > 1e-9 or min(split) < 0):
+        raise ValueError("split needs one non-negative fraction per model, summing to 1")
+
+    def value(v) -> str:
+        if isinstance(v, dict):
+            return "{" + ", ".join(f"{k} = {value(x)}" for k, x in v.items()) + "}"
+        if isinstance(v, str):
+            return json.dumps(v)
+        if isinstance(v, bool):
+            return "true" if v else "false"
+        if isinstance(v, (list, tuple)):
+            return "[" + ", ".join(value(x) for x in v) + "]"
+        return repr(float(v)) if isinstance(v, float) else str(v)
+
+    out = []
+    for r in rates:
+        per = [r] * models if split is None else [round(r * models * f, 6) for f in split]
+        name = f"{deployment}-{rate_tag(r)}" + ("" if split is None else "-skew" + "-".join(f"{int(round(100 * f))}" for f in split))
+        lines = [f"[cases.{name}]", f'deployment = "{deployment}"', f"rate_per_s = {value([float(x) for x in per])}"]
+        lines += [f"{k} = {value(v)}" for k, v in (extra or {}).items()]
+        out.append("\n".join(lines))
+    return "\n\n".join(out) + "\n"
+
+
+def _case_gen(argv: list[str]) -> int:
+    ap = argparse.ArgumentParser(prog="python -m crosspool_b200.bench.suite case-gen")
+    ap.add_argument("--deployment", required=True)
+    ap.add_argument("--models", type=int, required=True)
+    ap.add_argument("--rates", type=float, nargs="+", required=True)
+    ap.add_argument("--split", type=float, nargs="*", default=None)
+    ap.add_argument("--duration-s", type=float, default=None)
+    ns = ap.parse_args(argv)
+    extra = {"duration_s": ns.duration_s} if ns.duration_s else None
+    print(generate_cases(ns.deployment, ns.models, ns.rates, split=tuple(ns.split) if ns.split else None, extra=extra), end="")
+    return 0
+
+
+def _list_cases(argv: list[str]) -> int:
+    ap = argparse.ArgumentParser(prog="python -m crosspool_b200.bench.suite list")
+    ap.add_argument("--catalogue", default="")
+    ns = ap.parse_args(argv)
+    cases = dict(CASES)
+    if ns.catalogue:
+        cases.update(load_catalogue(ns.catalogue))
+    for name, c in sorted(cases.items()):
+        dep = c.deployment_dict()
+        where = f"{len(dep.get('models', ()))} models on atn {list(dep.get('atn', ()))} / ffn {list(dep.get('ffn', ()))}" if dep else "any deployment"
+        print(f"{name:40s} rates {list(c.rate_per_s)} req/s  {c.duration_s:g} s x {c.repetitions}  {where}")
+    return 0
+
+
 def main(argv: list[str] | None = None) -> int:
-    ap = argparse.ArgumentParser(prog="python -m crosspool_b200.bench.suite")
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv[:1] == ["case-gen"]:
+        return _case_gen(argv[1:])
+    if argv[:1] == ["list"]:
+        return _list_cases(argv[1:])
+    ap = argparse.ArgumentParser(prog="python -m crosspool_b200.bench.suite",
+                                 epilog="other forms: `suite list [--catalogue F]`, `suite case-gen --deployment D --models N --rates ...`; "
+                                        "reports: python -m crosspool_b200.bench.report")
     ap.add_argument("--targets", nargs="+", required=True, help="model=http://host:port ...")
     ap.add_argument("--out", required=True)
     ap.add_argument("--cases", nargs="*", default=[], help=f"subset of {sorted(CASES)} (default: all but smoke)")
