@@ -86,6 +86,9 @@ def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2), retire=True, atn_ex
                 p.wait(10)
             except subprocess.TimeoutExpired:
                 p.kill()
+        # an agent that was killed cannot unlink its arenas: names carry this deployment's daemon port
+        for f in Path("/dev/shm").glob(f"xp{dport}g*"):
+            f.unlink(missing_ok=True)
 
 
 def test_two_preset_models_on_a_shared_cpu_ffn_tier_answer_like_the_undivided_models(tmp_path):
