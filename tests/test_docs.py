@@ -60,3 +60,20 @@ def test_every_variable_of_the_example_environment_file_is_one_the_code_reads():
     known = {s.env_var for s in C.CONFIG_REGISTRY if s.env_var} | {"XPOOL_NVTX", "XPOOL_CPU_KV_BYTES", "SGLANG_PLUGINS"}
     assert names <= known, names - known
     assert (root / "configs" / "xpool.example.toml").exists()
+
+
+def test_http_api_page_lists_exactly_the_routes_the_apps_serve():
+    from crosspool_b200 import config as C
+    from crosspool_b200.runtime.serving import create_serving_app
+    from crosspool_b200.service.daemon.app import create_app
+    from crosspool_b200.service.daemon.control import ControlPlane
+
+    text = (DOCS / "http-api.md").read_text()
+    instance_part, daemon_part = text.split("## Daemon")
+    rows = lambda part: {(m, p.replace("{model_id}", "{model_id:path}")) for m, p in re.findall(r"^\| (GET|POST) \| `([^`]+)` \|", part, re.M)}
+    builtin = {"/openapi.json", "/docs", "/docs/oauth2-redirect", "/redoc"}
+    served = lambda app: {(m, r.path) for r in app.routes if hasattr(r, "methods") and r.path not in builtin for m in r.methods
+                          if m in ("GET", "POST")}
+    cfg = C.load_config(toml_text="[atn]\ndevices=[0]\n[ffn]\ndevices=[1]\n[scheduler.slo]\nttft_ms=1\ntbt_ms=1\n", env={})
+    assert rows(daemon_part) == served(create_app(cfg, ControlPlane(cfg), background=False))
+    assert rows(instance_part) == served(create_serving_app(None, ["m"]))
