@@ -86,6 +86,7 @@ class EngineLoop:
         self.error: Exception | None = None
         self.steps = 0
         self.tokens = 0
+        self.metrics = None      # runtime/metrics.py::InstanceMetrics once an HTTP endpoint serves GET /metrics
 
     def submit(self, model_id: str, prompt: list[int], max_new_tokens: int, temperature: float = 0.0, seed: int = 0,
                aio: bool = False, queued: bool = True, tag: object = None) -> Pending:
@@ -152,6 +153,11 @@ class EngineLoop:
                         self.tokens += 1
                         if done:
                             del self._by_seq[(model_id, seq.seq_id)]
+                            if self.metrics is not None:
+                                try:
+                                    self.metrics.finished(model_id, seq)
+                                except Exception:      # a statistic must never stop the serving loop
+                                    pass
                 if self.sink is not None:
                     self.sink(batch, time.perf_counter())
                 deliver_batch(batch)
@@ -210,7 +216,18 @@ def create_serving_app(loop: EngineLoop, models: list[str], tokenizer=None):
     from fastapi import FastAPI, HTTPException
     from fastapi.responses import StreamingResponse
 
+    from fastapi.responses import PlainTextResponse
+
+    from .metrics import InstanceMetrics
+
     app = FastAPI(title="xpool instance")
+    if loop is not None and loop.metrics is None:
+        loop.metrics = InstanceMetrics()
+
+    @app.get("/metrics", response_class=PlainTextResponse)
+    def metrics():
+        m = loop.metrics if loop is not None else None
+        return (m or InstanceMetrics()).render(loop)
 
     @app.get("/health")
     def health():

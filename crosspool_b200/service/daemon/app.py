@@ -165,6 +165,14 @@ def create_app(config: XpoolConfig, control: ControlPlane | None = None, *, back
     def terminate_owner(owner: ProcessRef):
         return {"signalled": cp.terminate_owner(owner)}
 
+    @app.get("/metrics")
+    def metrics():
+        from fastapi.responses import PlainTextResponse
+
+        from ...runtime.metrics import render_daemon
+
+        return PlainTextResponse(render_daemon(cp, app.state.ecs))
+
     @app.get("/ecs/state")
     def ecs_state():
         if app.state.ecs is None:

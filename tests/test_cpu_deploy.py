@@ -40,8 +40,12 @@ base_port = {serve_port}
 """
 
 
+plan_port = [0]          # the daemon port of the deployment a check callback is looking at
+
+
 def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2), retire=True, atn_extra="", extra_env=None):
     dport, sport = _free_port(), _free_port()
+    plan_port[0] = dport
     cfgp = tmp_path / "xpool.toml"
     cfgp.write_text(_toml(dport, sport, models_toml, atn, ffn, atn_extra))
     env = dict(os.environ, XPOOL_CONFIG=str(cfgp), PYTHONPATH=str(ROOT), XPOOL_MAX_ROWS="128", XPOOL_MAX_BATCH="4",
@@ -113,6 +117,14 @@ def test_two_preset_models_on_a_shared_cpu_ffn_tier_answer_like_the_undivided_mo
         assert bad.status_code == 422                               # a malformed request is answered, the service goes on
         again = httpx.post(url + "/generate", json={"model": "tiny-qwen3", "input_ids": [5, 6, 7], "max_new_tokens": 2}, timeout=60)
         assert again.status_code == 200 and len(again.json()["output_ids"]) == 2
+        # both processes answer a Prometheus scrape
+        text = httpx.get(url + "/metrics", timeout=5).text
+        assert 'xpool_requests_finished_total{model="tiny-qwen3"} 2' in text
+        assert 'xpool_output_tokens_total{model="tiny-qwen3-moe"} 5' in text
+        assert 'xpool_time_to_first_token_seconds_count{model="tiny-qwen3"} 2' in text and "xpool_engine_failed 0" in text
+        dtext = httpx.get(url.rsplit(":", 1)[0] + f":{plan_port[0]}/metrics", timeout=5).text
+        assert 'xpool_fabric_phase{phase="executable"} 1' in dtext and "xpool_system_ready 1" in dtext
+        assert 'xpool_registered{role="ffnagent"} 2' in dtext
 
     _run(tmp_path, models, check)
 

@@ -122,3 +122,31 @@ def test_percentile_is_linear_rank():
     from crosspool_b200.deployment import percentile
 
     assert percentile([1, 2, 3, 4], 50) == 2.5 and percentile([10], 99) == 10 and percentile([0, 10], 90) == 9.0
+
+
+def test_metrics_are_prometheus_text_and_a_broken_statistic_cannot_stop_the_loop(served):
+    import types
+
+    from fastapi.testclient import TestClient
+
+    from crosspool_b200.runtime.metrics import InstanceMetrics
+
+    app, loop = served
+    with TestClient(app) as http:
+        assert http.post("/generate", json={"model": "a", "input_ids": [1, 2, 3], "max_new_tokens": 4}).status_code == 200
+        text = http.get("/metrics").text
+        # the fake sequences carry no timing: requests are counted, histograms stay empty, serving went on
+        assert 'xpool_requests_finished_total{model="a"} 1' in text and "xpool_engine_steps_total" in text
+        assert "xpool_requests_in_flight 0" in text and "xpool_engine_failed 0" in text
+    m = InstanceMetrics()
+    seq = types.SimpleNamespace(prompt=[1] * 10, generated=[5] * 5, arrival=100.0, first_token_time=100.03, finish_time=100.11)
+    m.finished("x/y", seq)
+    m.finished("x/y", types.SimpleNamespace(prompt=[1], generated=[2], arrival=1.0, first_token_time=1.5, finish_time=1.5))
+    out = m.render()
+    assert 'xpool_time_to_first_token_seconds_bucket{le="0.05",model="x/y"} 1' in out
+    assert 'xpool_time_to_first_token_seconds_bucket{le="+Inf",model="x/y"} 2' in out
+    assert 'xpool_time_per_output_token_seconds_bucket{le="0.02",model="x/y"} 1' in out          # (0.11 - 0.03) / 4 = 20 ms
+    assert 'xpool_time_per_output_token_seconds_count{model="x/y"} 1' in out                      # one-token answers have no TPOT
+    assert 'xpool_prompt_tokens_total{model="x/y"} 11' in out and out.endswith("\n")
+    for line in out.splitlines():
+        assert line.startswith("#") or len(line.rsplit(" ", 1)) == 2
