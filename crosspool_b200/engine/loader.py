@@ -135,6 +135,39 @@ def _dense_reads(l: DenseFfnSpec, rank: int, size: int):
     return reads
 
 
+def _dense_fp8_block(l: DenseFfnSpec, reader: "_Reader", rank: int, size: int, stager: "PinnedStager", dtype: torch.dtype
+                     ) -> FfnLayerWeights:
+    """One gated dense layer of a block-scaled fp8 checkpoint: e4m3 ``weight`` plus ``weight_scale_inv`` (fp32, one per
+    128 x 128 block; the weight is ``code * scale``). The local tensor-parallel shard is cut on block boundaries. The
+    layer is returned expanded to ``dtype`` (what the Lanes compute in) and, under ``extra["fp8"]``, as the stored
+    codes and scales in the layout of the fp8 GEMM path (``ops/gemm.py::linear_fp8``), so nothing is re-quantised."""
+    from ..quantization import Fp8Block
+
+    inter = l.intermediate_size
+    if inter % (size * 128):
+        raise ValueError(f"intermediate size {inter} does not split into {size} shards of whole 128-wide blocks")
+    rows = _local(inter, rank, size, 128)
+    blocks = slice(rows.start // 128, rows.stop // 128)
+    fmt = Fp8Block()
+
+    def part(p, **cut):
+        blk = {k: (blocks if v is rows else v) for k, v in cut.items()}
+        return {"weight": reader.read(TensorRead(p.weight_key, **cut)), "scale": reader.read(TensorRead(p.scales_key, **blk)).float()}
+
+    gate, up, down = part(l.i_proj.gate, rows=rows), part(l.i_proj.up, rows=rows), part(l.o_proj, cols=rows)
+    for name, t in (("gate", gate), ("up", up), ("down", down)):
+        if t["weight"].dtype != torch.float8_e4m3fn:
+            raise ValueError(f"{name} projection of layer {l.layer}: expected e4m3 codes, found {t['weight'].dtype}")
+    gu = {"weight": torch.cat([gate["weight"].view(torch.uint8), up["weight"].view(torch.uint8)], 0).view(torch.float8_e4m3fn),
+          "scale": torch.cat([gate["scale"], up["scale"]], 0)}
+    w = FfnLayerWeights(stager.to_device(fmt.dequantize(gu, dtype), dtype), stager.to_device(fmt.dequantize(down, dtype), dtype))
+    w.extra["gated"] = True
+    dev = stager.device
+    w.extra["fp8"] = {"gate_up": gu["weight"].to(dev), "gate_up_scale": gu["scale"].contiguous().to(dev),
+                      "down": down["weight"].contiguous().to(dev), "down_scale": down["scale"].contiguous().to(dev)}
+    return w
+
+
 def _mxfp4_expert(reader: "_Reader", blocks_key: str, suffix: str, expert: int) -> torch.Tensor:
     """One expert's projection of a stacked MXFP4 tensor, dequantised to bf16 ``[rows, k]``. The checkpoint holds
     ``*_blocks`` ``[experts, rows, k / 32, 16]`` (two e2m1 codes per byte, low nibble first) and ``*_scales``
@@ -215,9 +248,13 @@ def materialize_layer_weights(spec: FfnModelSpec, view: CheckpointKeyView, layer
                               device="cpu", dtype: torch.dtype = torch.bfloat16, parallelism: int = 4,
                               experts: range | None = None) -> FfnLayerWeights:
     """Loads one layer's local shard. ``experts`` restricts a MoE layer to a range (expert parallelism)."""
-    if spec.quantization not in ("none", "mxfp4"):
+    if spec.quantization not in ("none", "mxfp4", "fp8_block"):
         raise NotImplementedError(f"checkpoints quantised with {spec.quantization} are not loadable")
     l = spec.layers[layer]
+    if spec.quantization == "fp8_block":
+        if not isinstance(l, DenseFfnSpec) or l.i_proj.gate is None or l.i_proj.gate.scales_key is None:
+            raise NotImplementedError("block-scaled fp8 checkpoints are loadable for gated dense layers only")
+        return _dense_fp8_block(l, _Reader(view), tp_rank, tp_size, PinnedStager(parallelism, device), dtype)
     mx = spec.quantization == "mxfp4" and isinstance(l, MoeFfnSpec) and l.experts.scales_suffix is not None
     stager, reader = PinnedStager(parallelism, device), _Reader(view)
     if isinstance(l, DenseFfnSpec):

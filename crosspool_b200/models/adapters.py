@@ -96,10 +96,16 @@ def _activation(name: str) -> ActivationKind:
         raise UnsupportedModel(f"unsupported activation {name!r}") from None
 
 
-def _gated_dense(layer: int, hidden: int, inter: int, act: ActivationKind, prefix: str, bias: bool = False
-                 ) -> DenseFfnSpec:
+def _gated_dense(layer: int, hidden: int, inter: int, act: ActivationKind, prefix: str, bias: bool = False,
+                 fp8_block: bool = False) -> DenseFfnSpec:
+    """``fp8_block``: the checkpoint stores e4m3 weights with one ``weight_scale_inv`` per 128 x 128 block (the
+    fine-grained fp8 layout of published ``*-FP8`` checkpoints); both dimensions must be whole blocks."""
+    if fp8_block and (hidden % 128 or inter % 128):
+        raise UnsupportedModel(f"block-scaled fp8 needs hidden ({hidden}) and intermediate ({inter}) sizes in multiples of 128")
+
     def proj(name, o, i):
-        return ProjectionSpec(f"{prefix}.{name}.weight", o, i, f"{prefix}.{name}.bias" if bias else None)
+        return ProjectionSpec(f"{prefix}.{name}.weight", o, i, f"{prefix}.{name}.bias" if bias else None,
+                              f"{prefix}.{name}.weight_scale_inv" if fp8_block else None)
 
     return DenseFfnSpec(layer, hidden, inter, act,
                         GatedProjectionSpec(proj("gate_proj", inter, hidden), proj("up_proj", inter, hidden)),
@@ -110,7 +116,8 @@ def _llama_like(model_id: str, src: FfnSourceConfig, keys: Iterable[str]) -> Ffn
     hidden, inter, n = src.int("hidden_size"), src.int("intermediate_size"), src.int("num_hidden_layers")
     act = _activation(src.str("hidden_act", "silu"))
     bias = src.bool("mlp_bias", False)
-    layers = tuple(_gated_dense(i, hidden, inter, act, f"model.layers.{i}.mlp", bias) for i in range(n))
+    fp8 = src.quantization == "fp8_block"
+    layers = tuple(_gated_dense(i, hidden, inter, act, f"model.layers.{i}.mlp", bias, fp8) for i in range(n))
     return FfnModelSpec(model_id, src.architecture, src.payload_dtype, hidden, src.quantization, layers)
 
 

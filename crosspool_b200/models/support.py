@@ -99,7 +99,8 @@ def supported_architectures() -> list[ArchitectureSupport]:
         kinds = tuple(dict.fromkeys(l.kind.value for l in spec.layers))
         # checkpoints in bf16 / fp16 / fp32 are all computed in bf16 (the payload and kernel dtype of this build)
         quant = ("bf16",) + (("mxfp4 (expanded to bf16 at load)",) if arch.startswith("GptOss") else ()) + \
-            (("block fp8 (decode-size rows)",) if kinds == ("dense",) and c.hidden_act == "silu" else ())
+            (("block fp8 checkpoints (expanded to bf16 for the Lanes; stored codes feed the decode-size fp8 GEMM)",)
+             if kinds == ("dense",) and c.hidden_act == "silu" else ())
         rows.append(ArchitectureSupport(arch, kinds, _ffn_features(spec), _attention_form(c), c.gpu_attention_supported,
                                         arch in with_adapter, quant))
     return rows

@@ -263,7 +263,20 @@ def load_attention_from_safetensors(cfg: ModelConfig, model_dir: str | Path, dev
 
     def get(key: str) -> torch.Tensor:
         assert attention_keys_filter(key)
-        return open_tensor(view, key).to(dtype=dt, device=device)
+        t = open_tensor(view, key)
+        if t.dtype == torch.float8_e4m3fn:
+            # a block-scaled fp8 checkpoint quantises the attention projections too: codes x per-block scale
+            scale_key = key + "_scale_inv"
+            if scale_key not in view.key_to_file:
+                raise ValueError(f"{key} holds e4m3 codes but the checkpoint has no {scale_key}")
+            from ..quantization import Fp8Block
+
+            n, k = t.shape
+            pad = torch.zeros((n + 127) // 128 * 128, (k + 127) // 128 * 128, dtype=torch.uint8)
+            pad[:n, :k] = t.view(torch.uint8)
+            full = Fp8Block().dequantize({"weight": pad.view(torch.float8_e4m3fn), "scale": open_tensor(view, scale_key).float()}, torch.float32)
+            return full[:n, :k].to(dtype=dt, device=device)
+        return t.to(dtype=dt, device=device)
 
     def opt(key: str) -> torch.Tensor | None:
         return get(key) if key in view.key_to_file else None

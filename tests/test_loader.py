@@ -192,3 +192,108 @@ def test_an_fp32_router_checkpoint_keeps_its_router_weights_in_fp32(tmp_path):
             assert torch.equal(w.extra["router_fp32"], router) and torch.equal(w.router, router.bfloat16())
         else:
             assert "router_fp32" not in w.extra
+
+
+def test_block_scaled_fp8_checkpoint_loads_on_block_boundaries_and_keeps_the_stored_codes(tmp_path):
+    """A ``*-FP8`` style checkpoint (e4m3 weights + ``weight_scale_inv`` per 128 x 128 block): the loader expands the
+    local shard to the compute dtype for the Lanes and hands the stored codes and scales to the fp8 GEMM path; TP
+    shards are cut on block boundaries and sum to the whole layer."""
+    import json
+
+    import pytest
+    import torch
+    from safetensors.torch import save_file
+
+    from crosspool_b200.engine import checkpoint as ck
+    from crosspool_b200.engine import loader
+    from crosspool_b200.models import adapters, reference
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.quantization import Fp8Block
+
+    hidden, inter = 256, 512
+    hf = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": hidden, "num_hidden_layers": 2, "num_attention_heads": 4,
+          "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": inter, "vocab_size": 512, "hidden_act": "silu",
+          "quantization_config": {"quant_method": "fp8", "weight_block_size": [128, 128]}}
+    g = torch.Generator().manual_seed(0)
+    fmt, tensors, dense = Fp8Block(), {}, {}
+    for l in range(2):
+        for name, shape in (("gate_proj", (inter, hidden)), ("up_proj", (inter, hidden)), ("down_proj", (hidden, inter))):
+            q = fmt.quantize(torch.randn(shape, generator=g) * 0.2)
+            key = f"model.layers.{l}.mlp.{name}"
+            tensors[key + ".weight"], tensors[key + ".weight_scale_inv"] = q["weight"], q["scale"]
+            dense[key] = fmt.dequantize(q, torch.float32)
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    view = ck.read_checkpoint_key_view(tmp_path)
+    spec = adapters.compile_ffn_spec("q8", hf, view.keys())
+    assert spec.quantization == "fp8_block"
+    ck.validate_ffn_coverage(spec, view)                         # the scales are FFN tensors too
+    cfg = mc.from_hf_config(hf, "q8")
+    x = torch.randn(9, hidden, generator=g) * 0.5
+    p = "model.layers.1.mlp."
+    want = (torch.nn.functional.silu(x @ dense[p + "gate_proj"].t()) * (x @ dense[p + "up_proj"].t())) @ dense[p + "down_proj"].t()
+    whole = loader.materialize_layer_weights(spec, view, 1, dtype=torch.float32)
+    torch.testing.assert_close(reference.ffn_forward(x, whole, cfg), want, rtol=1e-5, atol=1e-5)
+    assert whole.extra["fp8"]["gate_up"].dtype == torch.float8_e4m3fn and whole.extra["fp8"]["gate_up_scale"].shape == (2 * inter // 128, hidden // 128)
+    assert torch.equal(whole.extra["fp8"]["down"].view(torch.uint8), tensors[p + "down_proj.weight"].view(torch.uint8))
+    parts = [reference.ffn_forward(x, loader.materialize_layer_weights(spec, view, 1, tp_rank=r, tp_size=2, dtype=torch.float32), cfg)
+             for r in range(2)]
+    torch.testing.assert_close(sum(parts), want, rtol=1e-5, atol=1e-5)
+    half = loader.materialize_layer_weights(spec, view, 1, tp_rank=1, tp_size=2, dtype=torch.float32)
+    assert half.gate_up.shape == (inter, hidden) and half.extra["fp8"]["down_scale"].shape == (hidden // 128, inter // 2 // 128)
+    with pytest.raises(ValueError, match="whole 128-wide blocks"):
+        loader.materialize_layer_weights(spec, view, 1, tp_rank=0, tp_size=8)          # 512 / 8 = 64 rows: not a block
+    with pytest.raises(adapters.UnsupportedModel, match="multiples of 128"):
+        adapters.compile_ffn_spec("q8", {**hf, "intermediate_size": 320})
+
+
+def test_attention_side_of_a_block_scaled_fp8_checkpoint_is_dequantised_with_its_scales(tmp_path):
+    """Published fp8 checkpoints quantise q/k/v/o as well (shapes need not be whole blocks: the last block is partial).
+    The attention loader multiplies the codes by their block scales instead of casting the bare codes."""
+    import json
+
+    import pytest
+    import torch
+    from safetensors.torch import save_file
+
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.models.weights import load_attention_from_safetensors
+    from crosspool_b200.quantization import Fp8Block
+
+    hf = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 192, "num_hidden_layers": 1, "num_attention_heads": 4,
+          "num_key_value_heads": 2, "head_dim": 48, "intermediate_size": 256, "vocab_size": 64,
+          "quantization_config": {"quant_method": "fp8", "weight_block_size": [128, 128]}}
+    g = torch.Generator().manual_seed(1)
+    fmt, tensors, dense = Fp8Block(), {}, {}
+
+    def fp8(key, n, k):
+        w = torch.randn(n, k, generator=g) * 0.3
+        np_, kp = (n + 127) // 128 * 128, (k + 127) // 128 * 128
+        padded = torch.zeros(np_, kp)
+        padded[:n, :k] = w
+        q = fmt.quantize(padded)
+        tensors[key] = q["weight"].view(torch.uint8)[:n, :k].contiguous().view(torch.float8_e4m3fn)
+        tensors[key + "_scale_inv"] = q["scale"]
+        dense[key] = fmt.dequantize(q, torch.float32)[:n, :k]
+
+    p = "model.layers.0."
+    for name, n in (("q", 192), ("k", 96), ("v", 96)):
+        fp8(p + f"self_attn.{name}_proj.weight", n, 192)
+    fp8(p + "self_attn.o_proj.weight", 192, 192)
+    for key, shape in ((p + "input_layernorm.weight", 192), (p + "post_attention_layernorm.weight", 192), ("model.norm.weight", 192),
+                       (p + "self_attn.q_norm.weight", 48), (p + "self_attn.k_norm.weight", 48)):
+        tensors[key] = torch.ones(shape, dtype=torch.bfloat16)
+    tensors["model.embed_tokens.weight"] = (torch.randn(64, 192, generator=g) * 0.1).to(torch.bfloat16)
+    tensors["lm_head.weight"] = (torch.randn(64, 192, generator=g) * 0.1).to(torch.bfloat16)
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    cfg = mc.from_hf_config(hf, "q8")
+    aw = load_attention_from_safetensors(cfg, tmp_path, dtype=torch.float32)
+    want = torch.cat([dense[p + f"self_attn.{n}_proj.weight"] for n in "qkv"], 0)
+    torch.testing.assert_close(aw.layers[0].qkv, want, rtol=0, atol=0)
+    torch.testing.assert_close(aw.layers[0].o, dense[p + "self_attn.o_proj.weight"], rtol=0, atol=0)
+    assert float(aw.layers[0].qkv.abs().max()) < 3.0              # bare codes would reach hundreds
+    del tensors[p + "self_attn.o_proj.weight_scale_inv"]
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    with pytest.raises(ValueError, match="scale_inv"):
+        load_attention_from_safetensors(cfg, tmp_path, dtype=torch.float32)
