@@ -40,3 +40,17 @@ def test_library_model_with_detached_ffns_generates_what_the_whole_model_generat
         assert tier.shim.calls == 7 * model.config.num_hidden_layers
     torch.testing.assert_close(got_logits, want_logits, rtol=2e-4, atol=2e-4)
     assert got_tokens.tolist() == want_tokens.tolist()
+
+
+def test_command_line_demo_generates_from_a_local_checkpoint_and_verifies_against_the_whole_model(tmp_path, capsys):
+    from crosspool_b200.integrations.transformers import __main__ as demo
+
+    name = "Qwen3MoeForCausalLM"
+    if not hf_parity.available(name):
+        pytest.skip(f"the installed transformers has no {name}")
+    hf_parity.build_tiny_model(name).save_pretrained(tmp_path, safe_serialization=True)
+    rc = demo.main(["--checkpoint", str(tmp_path), "--ffn-ranks", "2", "--moe-parallel", "ep", "--ids", "5", "9", "11", "3",
+                    "--max-new-tokens", "5", "--verify"])
+    out = capsys.readouterr()
+    assert rc == 0 and "same tokens as the whole model" in out.err
+    assert len(out.out.split()) == 5 and "detached 2 FFN layers" in out.err
