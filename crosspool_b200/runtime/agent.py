@@ -66,6 +66,7 @@ class Agent:
         self.failed: str | None = None
         self.retained = False
         self._sleep = sleep
+        self.daemon_lost_seconds = 15.0      # how long the daemon may stay unreachable before the agent retires on its own
         self._stop = threading.Event()
         self._hb: threading.Thread | None = None
 
@@ -156,9 +157,23 @@ class Agent:
         """Main loop. ``until(agent, phase)`` may end it (tests). Exit code 0 clean, 1 failed."""
         self.register()
         self.start_heartbeat()
+        lost_since: float | None = None
         try:
             while not self._stop.is_set():
-                fp = self.advance()
+                try:
+                    fp = self.advance()
+                    lost_since = None
+                except ClientError as e:
+                    # The daemon does not answer. It is the only authority of the deployment, so after a grace period
+                    # the agent stops serving on its own: quiesce, drain, finalise in order, exit non-zero.
+                    now = time.monotonic()
+                    lost_since = now if lost_since is None else lost_since
+                    if now - lost_since < self.daemon_lost_seconds:
+                        self._sleep(min(1.0, max(poll_seconds, 0.2)))
+                        continue
+                    self.failed = f"daemon lost for {now - lost_since:.0f} s: {e}"
+                    self._retire_locally()
+                    break
                 if self.failed:
                     break
                 if until is not None and until(self, fp):
@@ -173,6 +188,16 @@ class Agent:
             self.retained = True
             return 1
         return 0
+
+    def _retire_locally(self) -> None:
+        """Orderly local shutdown without the daemon's barrier (it is gone): every step is attempted, a failing one does
+        not keep the later ones from running."""
+        for step in (self.backend.quiesce, self.backend.drain, self.backend.finalize):
+            try:
+                step()
+            except Exception:
+                pass
+        self.phase = ParticipantPhase.FINALIZED
 
     def stop(self) -> None:
         self._stop.set()

@@ -2,6 +2,7 @@
 the generation reaches EXECUTABLE only when every agent went through every phase; a backend failure
 is reported and aborts the generation; retirement drains to STOPPED."""
 import threading
+import time
 
 import httpx
 import pytest
@@ -132,4 +133,49 @@ def test_invocation_failure_seen_by_a_lane_aborts_the_generation():
     agents[2].backend.failure = None
     _spin(agents)
     assert cp.generation.phase == FabricPhase.STOPPED
+    http.__exit__(None, None, None)
+
+
+def test_an_agent_whose_daemon_disappears_retires_on_its_own_after_a_grace_period():
+    """The daemon is the only authority of a deployment: when it stops answering, an agent keeps trying for a grace
+    period (a restart of the HTTP server is survivable), then quiesces, drains and finalises locally and exits non-zero
+    instead of dying with a traceback in the middle of serving."""
+    from crosspool_b200.service.errors import ClientError
+
+    cp, http, agents = _world()
+    for a in agents:
+        a.register()
+    _spin(agents)
+    assert cp.generation.phase == FabricPhase.EXECUTABLE
+    ffn = agents[1]
+    real_plan, state = ffn.client.fabric_plan, {"down": False, "calls": 0}
+
+    class Flaky:
+        def __getattr__(self, name):
+            target = getattr(agents[0].client, name)
+
+            def call(*a, **kw):
+                if state["down"]:
+                    state["calls"] += 1
+                    raise ClientError("daemon unreachable: connection refused")
+                return target(*a, **kw)
+            return call
+
+    ffn.client = Flaky()
+    ffn.register = lambda: None
+    ffn.start_heartbeat = lambda *a, **kw: None
+    ffn.daemon_lost_seconds = 0.3
+    ffn._sleep = lambda s: time.sleep(0.02)
+    # a short outage is survived: the loop keeps polling and carries on when the daemon is back
+    state["down"] = True
+    threading.Timer(0.1, lambda: state.__setitem__("down", False)).start()
+    rc = ffn.run(poll_seconds=0.01, until=lambda a, fp: not state["down"] and state["calls"] > 0)
+    assert rc == 0 and ffn.failed is None and "quiesce" not in ffn.backend.calls
+    # a lasting one ends in an orderly local retirement
+    ffn._stop.clear()
+    state["down"] = True
+    rc = ffn.run(poll_seconds=0.01)
+    assert rc == 1 and ffn.failed.startswith("daemon lost") and ffn.retained
+    assert ffn.backend.calls[-3:] == ["quiesce", "drain", "finalize"]
+    del real_plan
     http.__exit__(None, None, None)
