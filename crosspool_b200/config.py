@@ -132,6 +132,9 @@ class ModelEntry:
     ffn_tp_size: int | None = None  # None: all FFN devices
     ffn_ep_size: int = 1            # expert parallelism (not in the reference, which rejects EP)
     slo: Slo | None = None
+    # The Instance ranks run in other processes (an external serving engine with the plugin, or a transformers model):
+    # the attention agent of their device only brokers their Transport arenas instead of hosting an engine for them.
+    external: bool = False
 
     @property
     def atn_world_size(self) -> int:
@@ -245,7 +248,7 @@ def _parse_models(doc: Mapping[str, Any], ffn_devices: tuple[int, ...]) -> tuple
     for i, m in enumerate(doc.get("models", []) or []):
         if not isinstance(m, Mapping):
             raise ConfigError(f"models[{i}] is not a table")
-        extra = set(m) - {"id", "path", "atn_tp_size", "atn_dp_size", "ffn_tp_size", "ffn_ep_size", "slo"}
+        extra = set(m) - {"id", "path", "atn_tp_size", "atn_dp_size", "ffn_tp_size", "ffn_ep_size", "slo", "external"}
         if extra:
             raise ConfigError(f"models[{i}] has unknown keys {sorted(extra)}")
         if "id" not in m:
@@ -266,7 +269,8 @@ def _parse_models(doc: Mapping[str, Any], ffn_devices: tuple[int, ...]) -> tuple
         ftp = m.get("ffn_tp_size")
         ftp = _int(1, max(1, len(ffn_devices)))(ftp) if ftp is not None else None
         ep = _int(1, max(1, len(ffn_devices)))(m.get("ffn_ep_size", 1))
-        out.append(ModelEntry(mid, str(m.get("path", mid)), tp, dp, ftp, ep, _slo(m["slo"]) if "slo" in m else None))
+        out.append(ModelEntry(mid, str(m.get("path", mid)), tp, dp, ftp, ep, _slo(m["slo"]) if "slo" in m else None,
+                              external=_bool(m.get("external", False))))
     return tuple(out)
 
 
@@ -332,7 +336,8 @@ class XpoolConfig:
 
         d = {k: enc(v) for k, v in sorted(self.values.items()) if k != "config"}
         d["models"] = [{"id": m.id, "path": m.path, "atn_tp_size": m.atn_tp_size, "atn_dp_size": m.atn_dp_size,
-                        "ffn_tp_size": m.ffn_tp_size, "ffn_ep_size": m.ffn_ep_size, "slo": enc(m.slo) if m.slo else None}
+                        "ffn_tp_size": m.ffn_tp_size, "ffn_ep_size": m.ffn_ep_size, "slo": enc(m.slo) if m.slo else None,
+                        **({"external": True} if m.external else {})}
                        for m in self.models]
         return d
 

@@ -1,0 +1,62 @@
+"""A ``transformers`` model as an Instance rank in a process of its own, inside a deployment run by the daemon.
+
+This is the reference's process model (an engine process per Instance rank, an attention agent that brokers its
+Transport arena, FFN agents, one daemon; src/xpool/runtime/instance.py, src/xpool/integrations/sglang/hooks/lifecycle.py)
+with the library model standing where the serving engine stands:
+
+    register -> wait until the generation is executable -> lease the arena from the daemon -> map the FFN ranks' arenas
+    -> detach the decoder FFNs and bind ``torch.ops.xpool.ffn_shim`` -> publish *initialised* -> wait for system ready
+
+after which the model's own ``forward`` / ``generate`` run attention here and every FFN on the tier. ``leave()`` retires
+the rank in order. The data plane is the CPU one (a deployment started with ``--backend cpu`` and the model marked
+``external = true``); on GPUs the same sequence ends in ``integrations.sglang.transport.FabricInstanceTransport``.
+"""
+
+from __future__ import annotations
+
+from ...config import XpoolConfig
+from ...runtime.instance import InstanceRankRuntime
+from ...service.client import XpoolClient, self_ref
+from ...service.wire import InstanceFfnProfile
+from .attach import DetachReport, bind_cpu_tier, detach_ffn, unbind
+
+
+class ExternalInstance:
+    def __init__(self, cfg: XpoolConfig, model_id: str, rank: int = 0, capacity_rows: int = 512, client: XpoolClient | None = None):
+        from ...native import EXPECTED_ABI
+
+        self.cfg, self.model_id, self.rank, self.capacity_rows = cfg, model_id, rank, capacity_rows
+        if not cfg.model(model_id).external:
+            raise ValueError(f"model {model_id!r} is not marked external in the deployment's configuration")
+        self.client = client or XpoolClient(cfg.daemon_host, cfg.daemon_port)
+        self.owner = self_ref(EXPECTED_ABI)
+        self.device = cfg.atn_devices[rank]
+        self.runtime: InstanceRankRuntime | None = None
+        self.report: DetachReport | None = None
+
+    def join(self, model, timeout_s: float = 120.0) -> DetachReport:
+        """Runs the start-up sequence for ``model`` (a loaded ``*ForCausalLM`` on the CPU) and returns what was detached."""
+        from ...runtime.cpu_backends import attach_cpu_instance
+
+        self.client.check_config(self.owner, self.cfg.digest())
+        shape = self.cfg.model_shape(self.model_id)
+        profile = InstanceFfnProfile(max_prefill_rows=self.capacity_rows, max_decode_rows=self.capacity_rows, hidden_size=shape.hidden_size)
+        rt = InstanceRankRuntime(self.client, self.model_id, self.rank, self.device, profile, owner=self.owner,
+                                 attach=lambda binding, plan: attach_cpu_instance(self.cfg, plan, self.model_id, self.rank, self.capacity_rows))
+        self.runtime = rt
+        rt.start()
+        plan = rt.wait_for_fabric_executable(timeout_s=timeout_s)
+        transport = rt.attach_arena_from_daemon(plan)
+        self.report = detach_ffn(model)
+        bind_cpu_tier(transport.port)
+        rt.publish_initialized(None)
+        rt.wait_for_ready(timeout_s=timeout_s)
+        return self.report
+
+    @property
+    def ffn_calls(self) -> int:
+        return self.runtime.transport.port.calls if self.runtime is not None and self.runtime.transport is not None else 0
+
+    def leave(self) -> bool:
+        unbind()
+        return self.runtime.detach() if self.runtime is not None else True

@@ -352,8 +352,13 @@ class CpuDeployment:
 
 class CpuAtnBackend:
     def __init__(self, cfg: XpoolConfig, device: int, instances: list[tuple[str, int]], listen: tuple[str, int] | None = None,
-                 capacity_rows: int = CPU_MAX_ROWS, max_batch: int = 8, max_seq_len: int = 512):
+                 capacity_rows: int = CPU_MAX_ROWS, max_batch: int = 8, max_seq_len: int = 512,
+                 external: list[tuple[str, int]] | None = None, publish_arenas=None):
+        """``external``: Instance ranks of this device that live in other processes; for them the backend only brokers
+        the Transport arena (``publish_arenas(generation, [TransportArenaBinding])`` hands it to the daemon, which
+        leases it to the rank's own process) and hosts no engine."""
         self.cfg, self.device, self.instances, self.capacity_rows = cfg, device, instances, capacity_rows
+        self.external, self.publish_arenas = list(external or ()), publish_arenas
         self.max_batch, self.max_seq_len = max_batch, max_seq_len
         self.places: dict[tuple[str, int], object] = {}
         self.ports: dict[str, CpuTierPort] = {}
@@ -412,6 +417,15 @@ class CpuAtnBackend:
                 raise NotImplementedError("the CPU attention backend runs attention on one rank per Instance")
             self.places[(model_id, rank)] = _placement(self.cfg, plan, model_id, rank, self.capacity_rows)
             handles[f"atn:{model_id}:{rank}"] = b"cpu".hex()       # the attention side owns no arena on the CPU
+        if self.external:
+            from ..service.wire import TransportArenaBinding
+
+            arenas = []
+            for model_id, rank in self.external:
+                handles[f"atn:{model_id}:{rank}"] = b"cpu".hex()
+                arenas.append(TransportArenaBinding(model_id=model_id, rank=rank, handle_hex=b"cpu".hex(), nbytes=0))
+            if self.publish_arenas is not None:
+                self.publish_arenas(plan.generation, arenas)
         return handles
 
     def join(self, plan: FabricPlan) -> None:
@@ -447,6 +461,8 @@ class CpuAtnBackend:
         for mb in self._boxes:                                   # the FFN agents have activated their arenas by now
             if mb.wait_status(rt.MBOX_IDLE, 30.0) != rt.WAIT_READY:
                 raise RuntimeError("an FFN arena never became idle")
+        if not self.engines:
+            return                                               # every rank of this device is served by another process
         self.loop = EngineLoop(CpuDeployment(self.engines))
         self.loop.start()
         if self._listen is not None:
@@ -480,3 +496,33 @@ class CpuAtnBackend:
         if self._ecs_channel is not None:
             self._ecs_channel.close()
             self._ecs_channel = None
+
+
+def attach_cpu_instance(cfg: XpoolConfig, plan: FabricPlan, model_id: str, rank: int, capacity_rows: int = CPU_MAX_ROWS) -> "CpuInstanceTransport":
+    """What an Instance rank in a process of its own does once the fabric is executable and the daemon has leased it
+    its arena: it maps the FFN ranks' arenas named in the plan and gets a handle that evaluates one layer
+    (``CpuTierPort``). The GPU counterpart maps IPC handles (``integrations/sglang/transport.py::from_handles``)."""
+    place = _placement(cfg, plan, model_id, rank, capacity_rows)
+    boxes, groups = [], []
+    for lo, hi, pes in place.groups():
+        ranks = []
+        for pe in pes:
+            name = bytes.fromhex(plan.slot_handles[f"ffn:{model_id}:{rank}:{pe}"]).decode()
+            mb = rt.CpuMailbox.attach(name, capacity_rows, place.cfg.hidden_size * 4)
+            boxes.append(mb)
+            ranks.append(RemoteFfn(mb, place.cfg.hidden_size, timeout_s=30.0))
+        groups.append((lo, hi, ranks))
+    return CpuInstanceTransport(CpuTierPort(groups), boxes)
+
+
+class CpuInstanceTransport:
+    def __init__(self, port: CpuTierPort, boxes: list):
+        self.port, self._boxes = port, boxes
+
+    def failure(self):
+        return None
+
+    def close(self) -> None:
+        for mb in self._boxes:
+            mb.close()
+        self._boxes = []

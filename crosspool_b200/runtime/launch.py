@@ -43,10 +43,17 @@ def run_cpu_agent(cfg: XpoolConfig, role: str, device: int) -> int:
         vm = psutil.virtual_memory()
         agent = FfnAgent(client, device, CpuFfnBackend(cfg, device, capacity_rows=rows), int(vm.available), int(vm.total), owner=owner)
     else:
-        insts = hosted_instances(cfg, device)
+        from ..service.wire import TransportArenaUpsert
+
+        here = hosted_instances(cfg, device)
+        insts = [(m, r) for m, r in here if not cfg.model(m).external]
+        outside = [(m, r) for m, r in here if cfg.model(m).external]
         port = cfg.serving_base_port + cfg.atn_devices.index(device)
         backend = CpuAtnBackend(cfg, device, insts, listen=("127.0.0.1", port), capacity_rows=rows,
-                                max_batch=min(cfg.engine_max_batch, 16), max_seq_len=min(cfg.engine_max_seq_len, rows))
+                                max_batch=min(cfg.engine_max_batch, 16), max_seq_len=min(cfg.engine_max_seq_len, rows),
+                                external=outside,
+                                publish_arenas=lambda gen, arenas: client.upsert_arenas(device, TransportArenaUpsert(
+                                    owner=owner, generation=gen, arenas=arenas)))
         if cfg.atn_elastic_kv:
             backend.ecs_ref = client.ecs_channel
             backend.kv_budget_bytes = int(os.environ.get("XPOOL_CPU_KV_BYTES", backend.kv_budget_bytes))
@@ -86,6 +93,11 @@ def run_agent(cfg: XpoolConfig, role: str, device: int, backend: str = "gpu") ->
                          owner=owner)
     else:
         insts = hosted_instances(cfg, device)
+        outside = [m for m, _ in insts if cfg.model(m).external]
+        if outside:
+            raise NotImplementedError(f"models {sorted(set(outside))} are marked external: the GPU attention agent hosts its "
+                                      "Instances itself; arena brokering for Instance ranks in other processes is "
+                                      "implemented by the CPU backend (--backend cpu)")
         chunk = min(max_rows, cfg.engine_prefill_chunk)   # tokens per prefill step
         ecfg = EngineConfig(max_batch=cfg.engine_max_batch, prefill_chunk=chunk, max_seq_len=cfg.engine_max_seq_len,
                             page_size=cfg.engine_page_size)

@@ -43,7 +43,7 @@ base_port = {serve_port}
 plan_port = [0]          # the daemon port of the deployment a check callback is looking at
 
 
-def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2), retire=True, atn_extra="", extra_env=None):
+def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2), retire=True, atn_extra="", extra_env=None, before_ready=None):
     dport, sport = _free_port(), _free_port()
     plan_port[0] = dport
     cfgp = tmp_path / "xpool.toml"
@@ -62,6 +62,8 @@ def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2), retire=True, atn_ex
                 time.sleep(0.2)
         for role, dev in [("ffnagent", d) for d in ffn] + [("atnagent", d) for d in atn]:
             procs.append(subprocess.Popen(xp + [role, "--device", str(dev), "--backend", "cpu"], env=env))
+        if before_ready is not None:
+            before_ready(cfgp, base)
         ready = False
         for _ in range(400):
             r = httpx.get(base + "/ready", timeout=2).json()
@@ -292,3 +294,62 @@ def test_elastic_kv_is_lent_from_an_idle_model_to_a_loaded_one_through_the_daemo
 
     _run(tmp_path, models, check, retire=False, atn_extra="elastic_kv = true\ndevice_memory_utilization = 1.0",
          extra_env={"XPOOL_CPU_KV_BYTES": str(10 * bundle)})
+
+
+def test_a_library_model_joins_as_an_instance_rank_of_its_own_and_serves_through_the_brokered_arena(tmp_path):
+    """The reference's process model on the CPU data plane: the engine (here the library model, in this test process)
+    is an Instance rank of its own; the attention agent hosts nothing and only brokers the rank's arena; the rank
+    registers, waits for the executable fabric, leases the arena from the daemon, maps the FFN ranks' arenas, detaches
+    its FFNs, publishes *initialised*; then its own ``generate`` is served by the FFN agents. It leaves in order."""
+    import threading
+
+    from crosspool_b200 import config as C
+    from crosspool_b200.devtools import hf_parity
+    from crosspool_b200.integrations.transformers.instance import ExternalInstance
+
+    name = "Qwen3MoeForCausalLM"
+    if not hf_parity.available(name):
+        pytest.skip(f"the installed transformers has no {name}")
+    model = hf_parity.build_tiny_model(name)
+    ckpt = tmp_path / "ckpt"
+    model.save_pretrained(ckpt, safe_serialization=True)
+    ids = torch.randint(0, model.config.vocab_size, (1, 9), generator=torch.Generator().manual_seed(3))
+    with torch.no_grad():
+        want = model.generate(ids, max_new_tokens=5, do_sample=False)
+    models = f'[[models]]\nid = "acme/moe"\npath = "{ckpt}"\nffn_tp_size = 2\nexternal = true\n'
+    box: dict = {}
+
+    def before_ready(cfgp, base):
+        # the rank joins while the agents come up: the daemon plans only once it has registered
+        cfg = C.load_config(env={"XPOOL_CONFIG": str(cfgp), "XPOOL_MAX_ROWS": "128", "XPOOL_MAX_BATCH": "4", "XPOOL_MAX_SEQ_LEN": "128"})
+        inst = ExternalInstance(cfg, "acme/moe", rank=0, capacity_rows=128)
+        box["inst"] = inst
+
+        def join():
+            try:
+                box["report"] = inst.join(model)
+            except Exception as e:       # surfaced by the assertions below
+                box["error"] = e
+
+        box["thread"] = threading.Thread(target=join)
+        box["thread"].start()
+
+    def check(url, base, procs):
+        box["thread"].join(60)
+        assert "error" not in box, box.get("error")
+        inst = box["inst"]
+        assert len(box["report"].shims) == model.config.num_hidden_layers and inst.runtime.state == "ready"
+        insts = httpx.get(base + "/instances", timeout=2).json()
+        assert "acme/moe" in str(insts)
+        with pytest.raises(httpx.HTTPError):            # the attention agent hosts no engine for an external rank
+            httpx.get(url + "/health", timeout=2)
+        with torch.no_grad():
+            got = model.generate(ids, max_new_tokens=5, do_sample=False)
+        assert got.tolist() == want.tolist()
+        assert inst.ffn_calls == 5 * model.config.num_hidden_layers
+        assert inst.leave()
+        assert httpx.post(base + "/fabric/quiesce", json={"reason": "test"}, timeout=5).status_code == 200
+        for p in procs[1:]:
+            assert p.wait(60) == 0
+
+    _run(tmp_path, models, check, retire=False, before_ready=before_ready)
