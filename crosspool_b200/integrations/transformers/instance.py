@@ -22,10 +22,11 @@ from .attach import DetachReport, bind_cpu_tier, detach_ffn, unbind
 
 
 class ExternalInstance:
-    def __init__(self, cfg: XpoolConfig, model_id: str, rank: int = 0, capacity_rows: int = 512, client: XpoolClient | None = None):
+    def __init__(self, cfg: XpoolConfig, model_id: str, rank: int = 0, client: XpoolClient | None = None):
         from ...native import EXPECTED_ABI
+        from ...runtime.cpu_backends import cpu_capacity_rows
 
-        self.cfg, self.model_id, self.rank, self.capacity_rows = cfg, model_id, rank, capacity_rows
+        self.cfg, self.model_id, self.rank, self.capacity_rows = cfg, model_id, rank, cpu_capacity_rows(cfg)
         if not cfg.model(model_id).external:
             raise ValueError(f"model {model_id!r} is not marked external in the deployment's configuration")
         self.client = client or XpoolClient(cfg.daemon_host, cfg.daemon_port)
@@ -42,7 +43,7 @@ class ExternalInstance:
         shape = self.cfg.model_shape(self.model_id)
         profile = InstanceFfnProfile(max_prefill_rows=self.capacity_rows, max_decode_rows=self.capacity_rows, hidden_size=shape.hidden_size)
         rt = InstanceRankRuntime(self.client, self.model_id, self.rank, self.device, profile, owner=self.owner,
-                                 attach=lambda binding, plan: attach_cpu_instance(self.cfg, plan, self.model_id, self.rank, self.capacity_rows))
+                                 attach=lambda binding, plan: attach_cpu_instance(self.cfg, plan, self.model_id, self.rank))
         self.runtime = rt
         rt.start()
         plan = rt.wait_for_fabric_executable(timeout_s=timeout_s)

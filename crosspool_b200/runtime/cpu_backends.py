@@ -36,6 +36,11 @@ from .backends import _placement
 CPU_MAX_ROWS = 512
 
 
+def cpu_capacity_rows(cfg: XpoolConfig) -> int:
+    """Row capacity of every arena of a CPU deployment: all processes size and map the arenas with this number."""
+    return min(cfg.engine_max_rows, CPU_MAX_ROWS)
+
+
 def arena_name(cfg: XpoolConfig, plan: FabricPlan, model_id: str, atn_rank: int, pe: int) -> str:
     """Deterministic shared-memory name of one (Instance rank, FFN rank) arena of one generation of one deployment."""
     return f"/xp{cfg.daemon_port}g{plan.generation}m{zlib.crc32(model_id.encode()):08x}r{atn_rank}p{pe}"
@@ -498,10 +503,11 @@ class CpuAtnBackend:
             self._ecs_channel = None
 
 
-def attach_cpu_instance(cfg: XpoolConfig, plan: FabricPlan, model_id: str, rank: int, capacity_rows: int = CPU_MAX_ROWS) -> "CpuInstanceTransport":
+def attach_cpu_instance(cfg: XpoolConfig, plan: FabricPlan, model_id: str, rank: int) -> "CpuInstanceTransport":
     """What an Instance rank in a process of its own does once the fabric is executable and the daemon has leased it
     its arena: it maps the FFN ranks' arenas named in the plan and gets a handle that evaluates one layer
     (``CpuTierPort``). The GPU counterpart maps IPC handles (``integrations/sglang/transport.py::from_handles``)."""
+    capacity_rows = cpu_capacity_rows(cfg)
     place = _placement(cfg, plan, model_id, rank, capacity_rows)
     boxes, groups = [], []
     for lo, hi, pes in place.groups():

@@ -30,7 +30,7 @@ def run_cpu_agent(cfg: XpoolConfig, role: str, device: int) -> int:
     from ..native import EXPECTED_ABI
     from ..service.client import self_ref
     from .backends import model_config_for
-    from .cpu_backends import CPU_MAX_ROWS, CpuAtnBackend, CpuFfnBackend
+    from .cpu_backends import CpuAtnBackend, CpuFfnBackend, cpu_capacity_rows
     from .roles import AtnAgent, FfnAgent
 
     log = init_logging("AtnAgent" if role == "atnagent" else "FfnAgent", cfg.logging_level, cfg.logging_color)
@@ -38,7 +38,7 @@ def run_cpu_agent(cfg: XpoolConfig, role: str, device: int) -> int:
     owner = self_ref(EXPECTED_ABI)
     client.check_config(owner, cfg.digest())
     client.startup_agent(owner, Role.ATNAGENT if role == "atnagent" else Role.FFNAGENT, device)
-    rows = min(cfg.engine_max_rows, CPU_MAX_ROWS)
+    rows = cpu_capacity_rows(cfg)
     if role == "ffnagent":
         vm = psutil.virtual_memory()
         agent = FfnAgent(client, device, CpuFfnBackend(cfg, device, capacity_rows=rows), int(vm.available), int(vm.total), owner=owner)

@@ -322,7 +322,7 @@ def test_a_library_model_joins_as_an_instance_rank_of_its_own_and_serves_through
     def before_ready(cfgp, base):
         # the rank joins while the agents come up: the daemon plans only once it has registered
         cfg = C.load_config(env={"XPOOL_CONFIG": str(cfgp), "XPOOL_MAX_ROWS": "128", "XPOOL_MAX_BATCH": "4", "XPOOL_MAX_SEQ_LEN": "128"})
-        inst = ExternalInstance(cfg, "acme/moe", rank=0, capacity_rows=128)
+        inst = ExternalInstance(cfg, "acme/moe", rank=0)
         box["inst"] = inst
 
         def join():
