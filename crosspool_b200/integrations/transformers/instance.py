@@ -41,22 +41,42 @@ class ExternalInstance:
 
         self.client.check_config(self.owner, self.cfg.digest())
         shape = self.cfg.model_shape(self.model_id)
-        profile = InstanceFfnProfile(max_prefill_rows=self.capacity_rows, max_decode_rows=self.capacity_rows, hidden_size=shape.hidden_size)
+        rows = self.cfg.engine_max_rows if next(model.parameters()).is_cuda else self.capacity_rows
+        profile = InstanceFfnProfile(max_prefill_rows=rows, max_decode_rows=rows, hidden_size=shape.hidden_size)
+        on_gpu = next(model.parameters()).is_cuda
+
+        def attach_gpu(binding, plan):
+            # The GPU form of the same step: map the leased attention-side slot and the FFN ranks' slots by their IPC
+            # handles and point the native operator at them. Written against the brokering of AtnBackend; it has not
+            # run on GPUs yet (the CPU form below is what the tests exercise).
+            from ...runtime.backends import _placement
+            from ..sglang.transport import FabricInstanceTransport
+
+            place = _placement(self.cfg, plan, self.model_id, self.rank, self.cfg.engine_max_rows)
+            t = FabricInstanceTransport.from_handles(place, binding.handle_hex,
+                                                     [plan.slot_handles[f"ffn:{self.model_id}:{self.rank}:{pe}"] for pe in place.ffn_ranks],
+                                                     next(model.parameters()).device)
+            t.make_current()
+            return t
+
         rt = InstanceRankRuntime(self.client, self.model_id, self.rank, self.device, profile, owner=self.owner,
-                                 attach=lambda binding, plan: attach_cpu_instance(self.cfg, plan, self.model_id, self.rank))
+                                 attach=attach_gpu if on_gpu else
+                                 (lambda binding, plan: attach_cpu_instance(self.cfg, plan, self.model_id, self.rank)))
         self.runtime = rt
         rt.start()
         plan = rt.wait_for_fabric_executable(timeout_s=timeout_s)
         transport = rt.attach_arena_from_daemon(plan)
         self.report = detach_ffn(model)
-        bind_cpu_tier(transport.port)
+        if not on_gpu:
+            bind_cpu_tier(transport.port)
         rt.publish_initialized(None)
         rt.wait_for_ready(timeout_s=timeout_s)
         return self.report
 
     @property
     def ffn_calls(self) -> int:
-        return self.runtime.transport.port.calls if self.runtime is not None and self.runtime.transport is not None else 0
+        port = getattr(getattr(self.runtime, "transport", None), "port", None)
+        return port.calls if port is not None else 0
 
     def leave(self) -> bool:
         unbind()

@@ -118,8 +118,15 @@ class FfnBackend:
 
 class AtnBackend:
     def __init__(self, cfg: XpoolConfig, device: int, instances: list[tuple[str, int]], ecfg: EngineConfig,
-                 capacity_rows: int = 4096, local_index: int | None = None, listen: tuple[str, int] | None = None):
+                 capacity_rows: int = 4096, local_index: int | None = None, listen: tuple[str, int] | None = None,
+                 external: list[tuple[str, int]] | None = None, publish_arenas=None):
+        """``external``: Instance ranks of this device that run in processes of their own (``[[models]] external = true``).
+        For them the agent allocates the attention-side slot, publishes its IPC handle to the FFN ranks (plan) and to
+        the daemon's arena broker (``publish_arenas(generation, [TransportArenaBinding])``), and hosts no engine; the
+        rank's process maps it with ``integrations.sglang.transport.FabricInstanceTransport.from_handles``. This half has
+        run on the CPU data plane only (``runtime/cpu_backends.py``), not yet on GPUs."""
         self.cfg, self.device, self.instances, self.ecfg = cfg, device, instances, ecfg
+        self.external, self.publish_arenas = list(external or ()), publish_arenas
         self.capacity_rows = max(capacity_rows, ecfg.max_batch, ecfg.prefill_chunk)
         self.cuda = torch.device(f"cuda:{device if local_index is None else local_index}")
         self.buffers: dict[tuple[str, int], F.PeerBuffer] = {}
@@ -157,6 +164,21 @@ class AtnBackend:
                 g = atn_tp.TpGroup(tpr, tps, max(self.ecfg.max_batch, self.ecfg.prefill_chunk), place.cfg.hidden_size, self.cuda)
                 self.tp_groups[(model_id, rank)] = g
                 handles[f"atp:{model_id}:{rank}"] = g.handle().hex()
+        if self.external:
+            from ..service.wire import TransportArenaBinding
+
+            arenas = []
+            for model_id, rank in self.external:
+                if self.cfg.model(model_id).atn_tp_size != 1:
+                    raise NotImplementedError("external Instance ranks with attention tensor parallelism are not brokered")
+                place = _placement(self.cfg, plan, model_id, rank, self.capacity_rows)
+                nbytes = F.atn_slot_layout(place).total_bytes
+                buf = F.PeerBuffer(nbytes)
+                self.buffers[(model_id, rank)] = buf                 # freed in finalize with the hosted ranks' slots
+                handles[f"atn:{model_id}:{rank}"] = buf.handle().hex()
+                arenas.append(TransportArenaBinding(model_id=model_id, rank=rank, handle_hex=buf.handle().hex(), nbytes=nbytes))
+            if self.publish_arenas is not None:
+                self.publish_arenas(plan.generation, arenas)
         return handles
 
     def join(self, plan: FabricPlan) -> None:
@@ -249,6 +271,8 @@ class AtnBackend:
         from ..deployment import Deployment, InstanceHandle
         from .serving import EngineLoop, create_serving_app
 
+        if not self.engines:
+            return                   # every Instance rank of this device runs in a process of its own
         tp_members = {self._tp(m, r) for m, r in self.instances if self._tp(m, r)[1] > 1}
         order = sorted(self.engines, key=lambda m: self.cfg.model(m).atn_tp_size == 1)   # TP engines warm up first, in step
         dep = Deployment([InstanceHandle(m, self.engines[m].cfg, self.engines[m]) for m in order])

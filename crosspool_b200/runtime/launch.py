@@ -92,17 +92,19 @@ def run_agent(cfg: XpoolConfig, role: str, device: int, backend: str = "gpu") ->
         agent = FfnAgent(client, device, FfnBackend(cfg, device, capacity_rows=max_rows, local_index=local), free, total,
                          owner=owner)
     else:
-        insts = hosted_instances(cfg, device)
-        outside = [m for m, _ in insts if cfg.model(m).external]
-        if outside:
-            raise NotImplementedError(f"models {sorted(set(outside))} are marked external: the GPU attention agent hosts its "
-                                      "Instances itself; arena brokering for Instance ranks in other processes is "
-                                      "implemented by the CPU backend (--backend cpu)")
+        from ..service.wire import TransportArenaUpsert
+
+        here = hosted_instances(cfg, device)
+        insts = [(m, r) for m, r in here if not cfg.model(m).external]
+        outside = [(m, r) for m, r in here if cfg.model(m).external]     # ranks that run in processes of their own
         chunk = min(max_rows, cfg.engine_prefill_chunk)   # tokens per prefill step
         ecfg = EngineConfig(max_batch=cfg.engine_max_batch, prefill_chunk=chunk, max_seq_len=cfg.engine_max_seq_len,
                             page_size=cfg.engine_page_size)
         port = cfg.serving_base_port + cfg.atn_devices.index(device)
-        backend = AtnBackend(cfg, device, insts, ecfg, capacity_rows=max_rows, local_index=local, listen=("127.0.0.1", port))
+        backend = AtnBackend(cfg, device, insts, ecfg, capacity_rows=max_rows, local_index=local, listen=("127.0.0.1", port),
+                             external=outside,
+                             publish_arenas=lambda gen, arenas: client.upsert_arenas(device, TransportArenaUpsert(
+                                 owner=owner, generation=gen, arenas=arenas)))
         if cfg.atn_elastic_kv:
             backend.ecs_ref = client.ecs_channel
         profs = [(m, r, InstanceFfnProfile(max_prefill_rows=ecfg.prefill_chunk, max_decode_rows=ecfg.max_batch,
