@@ -157,6 +157,8 @@ def test_an_agent_whose_daemon_disappears_retires_on_its_own_after_a_grace_perio
             def call(*a, **kw):
                 if state["down"]:
                     state["calls"] += 1
+                    if state.get("recover_after") and state["calls"] >= state["recover_after"]:
+                        state["down"] = False           # the daemon is back for the next call
                     raise ClientError("daemon unreachable: connection refused")
                 return target(*a, **kw)
             return call
@@ -167,13 +169,12 @@ def test_an_agent_whose_daemon_disappears_retires_on_its_own_after_a_grace_perio
     ffn.daemon_lost_seconds = 0.3
     ffn._sleep = lambda s: time.sleep(0.02)
     # a short outage is survived: the loop keeps polling and carries on when the daemon is back
-    state["down"] = True
-    threading.Timer(0.1, lambda: state.__setitem__("down", False)).start()
-    rc = ffn.run(poll_seconds=0.01, until=lambda a, fp: not state["down"] and state["calls"] > 0)
+    state["down"], state["recover_after"] = True, 3
+    rc = ffn.run(poll_seconds=0.01, until=lambda a, fp: not state["down"] and state["calls"] >= 3)
     assert rc == 0 and ffn.failed is None and "quiesce" not in ffn.backend.calls
     # a lasting one ends in an orderly local retirement
     ffn._stop.clear()
-    state["down"] = True
+    state["down"], state["recover_after"] = True, 0
     rc = ffn.run(poll_seconds=0.01)
     assert rc == 1 and ffn.failed.startswith("daemon lost") and ffn.retained
     assert ffn.backend.calls[-3:] == ["quiesce", "drain", "finalize"]
