@@ -35,8 +35,9 @@ class ExternalInstance:
         self.runtime: InstanceRankRuntime | None = None
         self.report: DetachReport | None = None
 
-    def join(self, model, timeout_s: float = 120.0) -> DetachReport:
-        """Runs the start-up sequence for ``model`` (a loaded ``*ForCausalLM`` on the CPU) and returns what was detached."""
+    def join(self, model, timeout_s: float = 120.0, listener: tuple[str, int] | None = None) -> DetachReport:
+        """Runs the start-up sequence for ``model`` (a loaded ``*ForCausalLM``) and returns what was detached.
+        ``listener``: the (host, port) this rank serves requests on, published with *initialised*."""
         from ...runtime.cpu_backends import attach_cpu_instance
 
         self.client.check_config(self.owner, self.cfg.digest())
@@ -69,7 +70,7 @@ class ExternalInstance:
         self.report = detach_ffn(model)
         if not on_gpu:
             bind_cpu_tier(transport.port)
-        rt.publish_initialized(None)
+        rt.publish_initialized(listener)
         rt.wait_for_ready(timeout_s=timeout_s)
         return self.report
 

@@ -104,11 +104,16 @@ def create_app(config: XpoolConfig, control: ControlPlane | None = None, *, back
 
     @app.get("/ffnagents")
     def ffnagents():
-        return {str(d): {"pid": r.owner.pid, "phase": r.phase, "pe": r.pe} for d, r in cp.ffnagents.items()}
+        return {str(d): {"pid": r.owner.pid, "phase": r.phase, "pe": r.pe, "free_bytes": r.payload.device_free_memory_bytes,
+                         "total_bytes": r.payload.device_total_memory_bytes} for d, r in cp.ffnagents.items()}
 
     @app.get("/instances")
     def instances():
-        return {f"{k[0]}:{k[1]}": {"pid": r.owner.pid, "initialized": r.initialized} for k, r in cp.instances.items()}
+        return {f"{k[0]}:{k[1]}": {"pid": r.owner.pid, "initialized": r.initialized, "device": r.payload.device,
+                                   "listener": f"{r.listener[0]}:{r.listener[1]}" if r.listener else None,
+                                   "max_prefill_rows": r.payload.ffn_profile.max_prefill_rows,
+                                   "max_decode_rows": r.payload.ffn_profile.max_decode_rows}
+                for k, r in cp.instances.items()}
 
     @app.post("/atnagent/register")
     def atn_register(r: AtnAgentRegistration):

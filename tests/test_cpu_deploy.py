@@ -353,3 +353,61 @@ def test_a_library_model_joins_as_an_instance_rank_of_its_own_and_serves_through
             assert p.wait(60) == 0
 
     _run(tmp_path, models, check, retire=False, before_ready=before_ready)
+
+
+def test_an_engine_process_around_a_library_model_serves_requests_as_an_external_instance_rank(tmp_path):
+    """Five processes: daemon, two FFN agents, the attention agent that brokers the arena, and an engine process of its
+    own (``integrations.transformers.serve``) that loads an OPT checkpoint (LayerNorm, learned positions: an attention
+    form the repository's GPU engine does not compute), joins as the model's Instance rank and answers over HTTP with
+    the whole model's tokens. SIGTERM makes it leave in order."""
+    from crosspool_b200.devtools import hf_parity
+
+    name = "OPTForCausalLM"
+    if not hf_parity.available(name):
+        pytest.skip(f"the installed transformers has no {name}")
+    model = hf_parity.build_tiny_model(name)
+    ckpt = tmp_path / "ckpt"
+    model.save_pretrained(ckpt, safe_serialization=True)
+    models = f'[[models]]\nid = "acme/opt"\npath = "{ckpt}"\nffn_tp_size = 2\nexternal = true\n'
+    eport = _free_port()
+    box: dict = {}
+
+    def before_ready(cfgp, base):
+        env = dict(os.environ, XPOOL_CONFIG=str(cfgp), PYTHONPATH=str(ROOT), XPOOL_MAX_ROWS="128", XPOOL_MAX_BATCH="4",
+                   XPOOL_MAX_SEQ_LEN="128")
+        box["engine"] = subprocess.Popen([sys.executable, "-m", "crosspool_b200.integrations.transformers.serve", "--model-id", "acme/opt",
+                                          "--port", str(eport)], env=env, stderr=subprocess.PIPE, text=True)
+
+    def check(url, base, procs):
+        engine = box["engine"]
+        try:
+            eurl = f"http://127.0.0.1:{eport}"
+            for _ in range(200):
+                try:
+                    if httpx.get(eurl + "/health", timeout=1).status_code == 200:
+                        break
+                except httpx.HTTPError:
+                    assert engine.poll() is None, engine.stderr.read()
+                    time.sleep(0.25)
+            inst = httpx.get(base + "/instances", timeout=2).json()
+            assert str(eport) in str(inst)                               # the rank published its own serving listener
+            prompt = list(range(5, 17))
+            resp = httpx.post(eurl + "/generate", json={"input_ids": prompt, "max_new_tokens": 5}, timeout=120)
+            assert resp.status_code == 200, resp.text
+            out = resp.json()
+            with torch.no_grad():
+                want = model.generate(torch.tensor([prompt]), max_new_tokens=5, do_sample=False)[0, len(prompt):].tolist()
+            assert out["output_ids"] == want
+            assert httpx.get(eurl + "/health", timeout=2).json()["ffn_calls"] == 5 * model.config.num_hidden_layers
+            assert httpx.post(eurl + "/generate", json={"input_ids": [], "max_new_tokens": 5}, timeout=10).status_code == 422
+            engine.send_signal(signal.SIGTERM)
+            assert engine.wait(30) == 0
+            assert "left the deployment (clean)" in engine.stderr.read()
+        finally:
+            if engine.poll() is None:
+                engine.kill()
+        assert httpx.post(base + "/fabric/quiesce", json={"reason": "test"}, timeout=5).status_code == 200
+        for p in procs[1:]:
+            assert p.wait(60) == 0
+
+    _run(tmp_path, models, check, retire=False, before_ready=before_ready)
