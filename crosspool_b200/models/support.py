@@ -108,8 +108,9 @@ def supported_architectures() -> list[ArchitectureSupport]:
 
 def support_markdown() -> str:
     lines = ["| architecture | FFN tier | FFN features | attention form | GPU attention engine | engine shim adapter | "
-             "CPU deployment and oracle | weight formats |", "| --- | --- | --- | --- | --- | --- | --- | --- |"]
+             "library-attention engine process | CPU deployment and oracle | weight formats |",
+             "| --- | --- | --- | --- | --- | --- | --- | --- | --- |"]
     for r in supported_architectures():
         lines.append(f"| `{r.architecture}` | {' + '.join(r.ffn_kinds)} | {r.ffn_features} | {r.attention_form} | "
-                     f"{'yes' if r.gpu_attention else 'no'} | {'yes' if r.engine_adapter else 'no'} | yes | {', '.join(r.quantization)} |")
+                     f"{'yes' if r.gpu_attention else 'no'} | {'yes' if r.engine_adapter else 'no'} | yes | yes | {', '.join(r.quantization)} |")
     return "\n".join(lines) + "\n"
