@@ -411,3 +411,102 @@ def test_an_engine_process_around_a_library_model_serves_requests_as_an_external
             assert p.wait(60) == 0
 
     _run(tmp_path, models, check, retire=False, before_ready=before_ready)
+
+
+def test_the_serving_engine_plugin_runs_its_whole_lifecycle_against_the_real_daemon_and_ffn_agents(tmp_path):
+    """The plugin (hooks, adapter, lifecycle, shutdown) with a fake engine in this process, but nothing else faked:
+    the daemon, the attention agent that brokers the arena and two FFN agents are real processes, the client is the real
+    HTTP client, the FFN weights come from a checkpoint through the production loader. Loading the engine's model
+    registers the Instance rank, waits for the executable fabric, leases the arena and binds the operator; a forward
+    pass of the engine's own model then equals the same model with its FFNs computed locally from the checkpoint."""
+    import types
+
+    from safetensors.torch import save_file
+
+    from crosspool_b200 import config as C
+    from crosspool_b200.integrations.sglang import plugin, shim
+    from crosspool_b200.integrations.transformers.attach import bind_cpu_tier
+    from crosspool_b200.runtime.cpu_backends import attach_cpu_instance
+    from crosspool_b200.runtime.instance import InstanceRankRuntime
+    from crosspool_b200.service.client import XpoolClient
+    from tests.sglang_fakes import PatchingHookRegistry, install_fake_engine
+
+    hidden, inter, layers = 8, 16, 3
+    ckpt = tmp_path / "ckpt"
+    ckpt.mkdir()
+    hf = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": hidden, "num_hidden_layers": layers, "num_attention_heads": 4,
+          "num_key_value_heads": 2, "head_dim": 2, "intermediate_size": inter, "vocab_size": 32, "hidden_act": "silu"}
+    (ckpt / "config.json").write_text(__import__("json").dumps(hf))
+    g = torch.Generator().manual_seed(11)
+    tensors = {}
+    for l in range(layers):
+        for name, shape in (("gate_proj", (inter, hidden)), ("up_proj", (inter, hidden)), ("down_proj", (hidden, inter))):
+            tensors[f"model.layers.{l}.mlp.{name}.weight"] = torch.randn(shape, generator=g) * 0.3
+    save_file(tensors, str(ckpt / "model.safetensors"))
+    models = f'[[models]]\nid = "acme/fake"\npath = "{ckpt}"\nffn_tp_size = 2\nexternal = true\n'
+    box: dict = {}
+
+    def before_ready(cfgp, base):
+        import threading
+
+        cfg = C.load_config(env={"XPOOL_CONFIG": str(cfgp), "XPOOL_MAX_ROWS": "128", "XPOOL_MAX_BATCH": "4", "XPOOL_MAX_SEQ_LEN": "128"})
+        fake, reg = install_fake_engine(), PatchingHookRegistry()
+        box.update(cfg=cfg, fake=fake, reg=reg)
+
+        def runtime_factory(binding, rank, profile, device):
+            def attach(arena, plan):
+                t = attach_cpu_instance(cfg, plan, binding.model_id, rank)
+                bind_cpu_tier(t.port)
+                return t
+            box["runtime"] = InstanceRankRuntime(XpoolClient(cfg.daemon_host, cfg.daemon_port), binding.model_id, rank, 0, profile, attach=attach)
+            return box["runtime"]
+
+        plugin.install(reg, environ={}, config=cfg, runtime_factory=runtime_factory)
+        args = types.SimpleNamespace(model_path=str(ckpt), tp_size=1, dp_size=1, tp_rank=0, chunked_prefill_size=128, cuda_graph_max_bs=4,
+                                     max_running_requests=4, cuda_graph_bs=[1, 2, 4], cuda_graph_backend_decode="full",
+                                     cuda_graph_backend_prefill="breakable", host="127.0.0.1", port=30000)
+
+        def boot():        # the engine starts: its scheduler constructs the model runner, which loads the model (hooked)
+            try:
+                box["sched"] = fake.sched.Scheduler(args)
+                box["info"] = box["sched"].get_init_info()          # hooked: publishes initialised, waits for system ready
+            except Exception as e:
+                box["error"] = e
+
+        box["thread"] = threading.Thread(target=boot)
+        box["thread"].start()
+
+    def check(url, base, procs):
+        try:
+            box["thread"].join(90)
+            assert "error" not in box, repr(box.get("error"))
+            sched, rt_ = box["sched"], box["runtime"]
+            model = sched.model_runner.model
+            assert [type(l.mlp).__name__ for l in model.model.layers] == ["FfnShimModule"] * layers and rt_.state == "ready"
+            assert box["info"] == {"status": "ready"}
+            inst = httpx.get(base + "/instances", timeout=2).json()["acme/fake:0"]
+            assert inst["initialized"] and inst["max_prefill_rows"] == 128
+            fb = types.SimpleNamespace(forward_mode=types.SimpleNamespace(name="DECODE"), dp_padding_mode=None)
+            x = torch.randn(4, hidden, generator=g)
+            with torch.no_grad():
+                got = model(x, fb)
+                want = x
+                for l, layer in enumerate(model.model.layers):     # the same model with its FFNs computed here
+                    want = want + layer.self_attn(want)
+                    p = f"model.layers.{l}.mlp."
+                    gate, up = want @ tensors[p + "gate_proj.weight"].t(), want @ tensors[p + "up_proj.weight"].t()
+                    want = want + (torch.nn.functional.silu(gate) * up) @ tensors[p + "down_proj.weight"].t()
+            torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4)
+            assert rt_.transport.port.calls == layers
+            assert sched.run_event_loop() == "loop-done"
+            assert sched.release_host_resources() == "released"     # ordered retirement through the plugin's shutdown hooks
+            assert rt_.state == "detached"
+            assert "acme/fake:0" not in httpx.get(base + "/instances", timeout=2).json()
+        finally:
+            box["reg"].restore()
+            shim.bind_submit(None)
+        assert httpx.post(base + "/fabric/quiesce", json={"reason": "test"}, timeout=5).status_code == 200
+        for p in procs[1:]:
+            assert p.wait(60) == 0
+
+    _run(tmp_path, models, check, retire=False, before_ready=before_ready)
