@@ -455,7 +455,7 @@ class CpuAtnBackend:
             self.engines[model_id] = CpuOracleEngine(place.cfg, aw, self.ports[model_id], self.max_batch,
                                                      min(self.max_seq_len, self.capacity_rows))
         if self.cfg.atn_elastic_kv and self.ecs_ref is not None:
-            self._attach_elastic_kv(plan)
+            self._attach_elastic_kv(plan)       # also with no hosted engine: the agent reports the device's memory
 
     def activate(self, plan: FabricPlan) -> None:
         pass

@@ -510,3 +510,103 @@ def test_the_serving_engine_plugin_runs_its_whole_lifecycle_against_the_real_dae
             assert p.wait(60) == 0
 
     _run(tmp_path, models, check, retire=False, before_ready=before_ready)
+
+
+def test_an_external_ranks_elastic_kv_state_borrows_from_a_hosted_neighbour_through_the_daemon(tmp_path):
+    """The plugin's elastic-KV state (what its hooks drive inside a serving engine) against the real control plane: an
+    external Instance rank describes its partition in the daemon's channel next to a hosted model of the same device,
+    its prefill is cut to the mapped backing, it publishes demand, the daemon shrinks the idle hosted neighbour and
+    grows the external rank, and the same prefill then fits."""
+    import threading
+
+    from crosspool_b200 import config as C
+    from crosspool_b200.ecs import reconciler as R
+    from crosspool_b200.ecs import vmm
+    from crosspool_b200.ecs.profile import KvPartitionGeometry
+    from crosspool_b200.integrations.sglang.ecs_hooks import ElasticContextState
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.native.runtime import EcsChannel
+    from crosspool_b200.runtime.cpu_backends import attach_cpu_instance
+    from crosspool_b200.runtime.instance import InstanceRankRuntime
+    from crosspool_b200.service.client import XpoolClient
+    from crosspool_b200.service.wire import InstanceFfnProfile
+
+    models = ('[[models]]\nid = "tiny-qwen3"\nffn_tp_size = 2\n'
+              '[[models]]\nid = "tiny-qwen3-moe"\nffn_tp_size = 2\nexternal = true\n')
+    bundle = 4 * (16 << 10)
+    box: dict = {}
+
+    def before_ready(cfgp, base):
+        cfg = C.load_config(env={"XPOOL_CONFIG": str(cfgp), "XPOOL_MAX_ROWS": "128", "XPOOL_MAX_BATCH": "4", "XPOOL_MAX_SEQ_LEN": "128"})
+        client = XpoolClient(cfg.daemon_host, cfg.daemon_port)
+        shape = mc.preset("tiny-qwen3-moe")
+        rt_ = InstanceRankRuntime(client, "tiny-qwen3-moe", 0, 0, InstanceFfnProfile(max_prefill_rows=128, max_decode_rows=128,
+                                                                                   hidden_size=shape.hidden_size),
+                                  attach=lambda b, plan: attach_cpu_instance(cfg, plan, "tiny-qwen3-moe", 0))
+
+        def boot():
+            try:
+                rt_.start()
+                plan = rt_.wait_for_fabric_executable(timeout_s=90)
+                rt_.attach_arena_from_daemon(plan)
+                ref = None
+                for _ in range(200):
+                    try:
+                        ref = client.ecs_channel(plan.generation)
+                        break
+                    except Exception:
+                        time.sleep(0.05)
+                ch = EcsChannel.attach(ref.name)
+                cache = vmm.elastic_kv_cache(shape, 32, 16, "cpu", vmm.Driver.fake(1 << 40, granularity=16 << 10), None,
+                                             initial_bundles=1, make_tensors=False, granularity=16 << 10)
+                idx = ref.partitions["tiny-qwen3-moe:0"]
+                KvPartitionGeometry.of(cache).describe(ch, idx, device=0, rank=0)
+                box.update(state=ElasticContextState(cache, R.CapacityReconciler(cache, ch, idx), 16, ttft_slo_s=2.0), channel=ch, rt=rt_)
+                rt_.publish_initialized(None)
+                rt_.wait_for_ready(timeout_s=90)
+            except Exception as e:
+                box["error"] = e
+
+        box["thread"] = threading.Thread(target=boot)
+        box["thread"].start()
+
+    def check(url, base, procs):
+        box["thread"].join(120)
+        assert "error" not in box, repr(box.get("error"))
+        st = box["state"]
+        for _ in range(100):                       # pools frozen, initial targets handed out and carried out on both sides
+            st.begin_scheduling()
+            view = httpx.get(base + "/ecs/state", timeout=2).json()
+            if view["frozen"] and st.reconciler.mapped_bundles == 5:
+                break
+            time.sleep(0.1)
+        # the agent reports the device's memory less what its own ranks hold; the policy adds every partition's floor back,
+        # the external rank's included: one bundle more than the ten configured, left unassigned after the equal split
+        assert st.reconciler.mapped_bundles == 5 and view["pools"]["0"]["budget_bytes"] == 11 * bundle
+        want = 27 * 16                                                   # 28 pages with the next token: seven bundles
+        cut = st.plan_prefill(seq_id=1, cached_tokens=0, want_tokens=want)
+        assert cut.tokens == 20 * 16 and cut.missing_pages == 7 and st.stats["prefill_cut"] == 1
+        st.finish_scheduling(cut.missing_pages, head_arrival_s=time.monotonic())
+        fits = None
+        for _ in range(100):
+            st.begin_scheduling()
+            fits = st.plan_prefill(seq_id=1, cached_tokens=0, want_tokens=want)
+            if fits.tokens == want:
+                break
+            time.sleep(0.1)
+        assert fits.tokens == want and st.reconciler.mapped_bundles == 7
+        view = httpx.get(base + "/ecs/state", timeout=2).json()
+        kinds = [(e["kind"], e["partition"]) for e in view["events"]]
+        assert ("shrink", "tiny-qwen3:0") in kinds and ("grow", "tiny-qwen3-moe:0") in kinds
+        # the hosted neighbour still serves while two of its bundles are on loan
+        ok = httpx.post(url + "/generate", json={"model": "tiny-qwen3", "input_ids": [3, 4, 5], "max_new_tokens": 2}, timeout=60)
+        assert ok.status_code == 200
+        st.finish_scheduling(0)
+        box["channel"].close()
+        assert box["rt"].detach()
+        assert httpx.post(base + "/fabric/quiesce", json={"reason": "test"}, timeout=5).status_code == 200
+        for p in procs[1:]:
+            assert p.wait(60) == 0
+
+    _run(tmp_path, models, check, retire=False, before_ready=before_ready,
+         atn_extra="elastic_kv = true\ndevice_memory_utilization = 1.0", extra_env={"XPOOL_CPU_KV_BYTES": str(10 * bundle)})
