@@ -22,6 +22,27 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
+def _free_port_run(n: int, avoid: set[int]) -> int:
+    """First of ``n`` consecutive free ports, none of them in ``avoid`` (attention device i listens on base + i)."""
+    for _ in range(200):
+        base = _free_port()
+        if any(base + i in avoid for i in range(n)):
+            continue
+        held = []
+        try:
+            for i in range(n):
+                sock = socket.socket()
+                held.append(sock)
+                sock.bind(("127.0.0.1", base + i))
+            return base
+        except OSError:
+            continue
+        finally:
+            for sock in held:
+                sock.close()
+    raise RuntimeError("no run of free ports found")
+
+
 def _toml(daemon_port: int, serve_port: int, models: str, atn=(0,), ffn=(1, 2), atn_extra="") -> str:
     return f"""
 [daemon]
@@ -44,7 +65,8 @@ plan_port = [0]          # the daemon port of the deployment a check callback is
 
 
 def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2), retire=True, atn_extra="", extra_env=None, before_ready=None):
-    dport, sport = _free_port(), _free_port()
+    dport = _free_port()
+    sport = _free_port_run(len(atn), {dport})
     plan_port[0] = dport
     cfgp = tmp_path / "xpool.toml"
     cfgp.write_text(_toml(dport, sport, models_toml, atn, ffn, atn_extra))
@@ -369,17 +391,20 @@ def test_an_engine_process_around_a_library_model_serves_requests_as_an_external
     ckpt = tmp_path / "ckpt"
     model.save_pretrained(ckpt, safe_serialization=True)
     models = f'[[models]]\nid = "acme/opt"\npath = "{ckpt}"\nffn_tp_size = 2\nexternal = true\n'
-    eport = _free_port()
     box: dict = {}
 
     def before_ready(cfgp, base):
+        import tomllib
+
+        doc = tomllib.loads(cfgp.read_text())
+        box["eport"] = _free_port_run(1, {doc["daemon"]["port"], doc["serving"]["base_port"]})
         env = dict(os.environ, XPOOL_CONFIG=str(cfgp), PYTHONPATH=str(ROOT), XPOOL_MAX_ROWS="128", XPOOL_MAX_BATCH="4",
                    XPOOL_MAX_SEQ_LEN="128")
         box["engine"] = subprocess.Popen([sys.executable, "-m", "crosspool_b200.integrations.transformers.serve", "--model-id", "acme/opt",
-                                          "--port", str(eport)], env=env, stderr=subprocess.PIPE, text=True)
+                                          "--port", str(box["eport"])], env=env, stderr=subprocess.PIPE, text=True)
 
     def check(url, base, procs):
-        engine = box["engine"]
+        engine, eport = box["engine"], box["eport"]
         try:
             eurl = f"http://127.0.0.1:{eport}"
             for _ in range(200):
