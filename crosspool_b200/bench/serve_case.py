@@ -25,17 +25,20 @@ ROOT = Path(__file__).resolve().parents[2]
 
 
 def toml_for(models: list[str], atn: list[int], ffn: list[int], port: int, ffn_tp: int, lanes: int, atn_tp: int = 1,
-             elastic: bool = False) -> str:
+             elastic: bool = False, serving_port: int = 30000) -> str:
     t = [f"[daemon]\nport = {port}", f"[atn]\ndevices = {atn}" + ("\nelastic_kv = true" if elastic else ""), f"[ffn]\ndevices = {ffn}",
-         f"[scheduler]\nffn_concurrency = {lanes}", "[scheduler.slo]\nttft_ms = 2000\ntbt_ms = 50"]
+         f"[scheduler]\nffn_concurrency = {lanes}", "[scheduler.slo]\nttft_ms = 2000\ntbt_ms = 50", f"[serving]\nbase_port = {serving_port}"]
     for m in models:
         t.append(f'[[models]]\nid = "{m}"\nffn_tp_size = {ffn_tp}\natn_tp_size = {atn_tp}')
     return "\n".join(t) + "\n"
 
 
 class LocalDeployment:
-    def __init__(self, toml_text: str, atn: list[int], ffn: list[int], port: int, env: dict[str, str] | None = None):
+    def __init__(self, toml_text: str, atn: list[int], ffn: list[int], port: int, env: dict[str, str] | None = None,
+                 backend: str = "gpu", serving_port: int = 30000):
+        """``backend="cpu"``: the agents run the shared-memory data plane and the PyTorch oracle (no GPU needed)."""
         self.toml_text, self.atn, self.ffn, self.port = toml_text, atn, ffn, port
+        self.backend, self.serving_port = backend, serving_port
         self.env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0", **(env or {}))
         self.procs: list[subprocess.Popen] = []
         self._dir = tempfile.TemporaryDirectory(prefix="xpool-deploy-")
@@ -60,9 +63,9 @@ class LocalDeployment:
             except httpx.HTTPError:
                 time.sleep(0.2)
         for d in self.ffn:
-            self._xp("ffnagent", "--device", str(d))
+            self._xp("ffnagent", "--device", str(d), "--backend", self.backend)
         for d in self.atn:
-            self._xp("atnagent", "--device", str(d))
+            self._xp("atnagent", "--device", str(d), "--backend", self.backend)
         for _ in range(1200):
             r = httpx.get(base + "/ready", timeout=5).json()
             if r.get("failure"):
@@ -75,7 +78,7 @@ class LocalDeployment:
         raise TimeoutError("deployment did not become ready")
 
     def targets(self, models: list[str]) -> dict[str, str]:
-        return {m: "http://127.0.0.1:30000" for m in models}   # all Instances of attention device 0 share one listener
+        return {m: f"http://127.0.0.1:{self.serving_port}" for m in models}   # all Instances of attention device 0 share one listener
 
     def __exit__(self, *exc) -> None:
         import httpx
@@ -104,6 +107,19 @@ class LocalDeployment:
         self._dir.cleanup()
 
 
+def _vocab_sizes(models: list[str]) -> dict[str, int]:
+    """Vocabulary of every model that is a preset or a checkpoint directory, so that random prompt ids are valid ones."""
+    from ..models import config as mc
+
+    out = {}
+    for m in models:
+        try:
+            out[m] = mc.load(m).vocab_size
+        except (FileNotFoundError, KeyError, ValueError):
+            pass
+    return out
+
+
 def main(argv: list[str] | None = None) -> int:
     from . import suite
 
@@ -118,6 +134,9 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--elastic", action="store_true", default=None, help="elastic KV: co-located Instances lend physical KV memory")
     ap.add_argument("--lanes", type=int, default=None)
     ap.add_argument("--port", type=int, default=9841)
+    ap.add_argument("--serving-port", type=int, default=30000, help="HTTP port of the first attention device's Instances")
+    ap.add_argument("--backend", choices=("gpu", "cpu"), default="gpu", help="cpu: run the deployment on the CPU data plane")
+    ap.add_argument("--max-rows", type=int, default=4096, help="row capacity of an FFN invocation")
     ap.add_argument("--max-batch", type=int, default=None)
     ap.add_argument("--max-seq-len", type=int, default=None)
     ap.add_argument("--prefill-chunk", type=int, default=4096, help="tokens per prefill step of the attention engines")
@@ -143,13 +162,14 @@ def main(argv: list[str] | None = None) -> int:
 
         case = dataclasses.replace(case, duration_s=ns.duration or case.duration_s,
                                    rate_per_s=(ns.rate,) if ns.rate > 0 else case.rate_per_s)
-    env = {"XPOOL_MAX_BATCH": str(ns.max_batch), "XPOOL_MAX_SEQ_LEN": str(ns.max_seq_len), "XPOOL_MAX_ROWS": "4096",
-           "XPOOL_PREFILL_CHUNK": str(ns.prefill_chunk)}
-    text = toml_for(ns.models, ns.atn, ns.ffn, ns.port, ns.ffn_tp, ns.lanes, ns.atn_tp, ns.elastic)
-    with LocalDeployment(text, ns.atn, ns.ffn, ns.port, env) as dep:
-        report = suite.default_runner(case, dep.targets(ns.models), ns.seed)
+    env = {"XPOOL_MAX_BATCH": str(ns.max_batch), "XPOOL_MAX_SEQ_LEN": str(ns.max_seq_len), "XPOOL_MAX_ROWS": str(ns.max_rows),
+           "XPOOL_PREFILL_CHUNK": str(min(ns.prefill_chunk, ns.max_rows))}
+    text = toml_for(ns.models, ns.atn, ns.ffn, ns.port, ns.ffn_tp, ns.lanes, ns.atn_tp, ns.elastic, ns.serving_port)
+    with LocalDeployment(text, ns.atn, ns.ffn, ns.port, env, backend=ns.backend, serving_port=ns.serving_port) as dep:
+        report = suite.default_runner(case, dep.targets(ns.models), ns.seed, vocab_sizes=_vocab_sizes(ns.models))
     report["case"] = ns.case
-    report["deployment"] = {"models": ns.models, "atn": ns.atn, "ffn": ns.ffn, "ffn_tp": ns.ffn_tp, "atn_tp": ns.atn_tp, "lanes": ns.lanes, "elastic_kv": ns.elastic}
+    report["deployment"] = {"models": ns.models, "atn": ns.atn, "ffn": ns.ffn, "ffn_tp": ns.ffn_tp, "atn_tp": ns.atn_tp, "lanes": ns.lanes,
+                            "elastic_kv": ns.elastic, "backend": ns.backend}
     agg = report["aggregate"]
     line = {"case": ns.case, "output_tok_per_s": round(agg["output_tok_per_s"], 1), "completed": agg["completed"],
             "errors": agg["errors"], "tpot_p50_ms": round(agg["tpot_ms"]["p50"], 2), "tpot_p99_ms": round(agg["tpot_ms"]["p99"], 2),

@@ -127,10 +127,14 @@ def sealed_ok(path: Path) -> dict | None:
     return doc if want and seal(dict(doc))["seal"] == want else None
 
 
-def default_runner(case: Case, targets: dict[str, str], seed: int) -> dict:
+def default_runner(case: Case, targets: dict[str, str], seed: int, vocab_sizes: dict[str, int] | None = None) -> dict:
+    """``vocab_sizes``: per model, the range random prompt ids are drawn from (default: the Qwen vocabulary; a model with
+    a smaller one would refuse ids beyond it)."""
     models = list(targets)
+    vocab = vocab_sizes or {}
     streams = [S.StreamSpec(m, case.rate_per_s[i % len(case.rate_per_s)], case.prompt, case.output, burst_factor=case.burst[0],
-                            burst_seconds=case.burst[1], burst_period=case.burst[2]) for i, m in enumerate(models)]
+                            burst_seconds=case.burst[1], burst_period=case.burst[2],
+                            **({"vocab_size": int(vocab[m])} if m in vocab else {})) for i, m in enumerate(models)]
     reqs = S.plan_workload(streams, case.duration_s, seed, case.warmup_requests)
     records, window = asyncio.run(S.run_client(targets, reqs))
     return {"digest": S.workload_digest(reqs), "window_s": window,
@@ -262,6 +266,7 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--cases", nargs="*", default=[], help=f"subset of {sorted(CASES)} (default: all but smoke)")
     ap.add_argument("--all", action="store_true")
     ap.add_argument("--catalogue", default="", help="TOML file with [cases.<name>] tables (adds to the built-in cases)")
+    ap.add_argument("--vocab", nargs="*", default=[], help="model=N: vocabulary size random prompt ids are drawn from (default 151936)")
     ap.add_argument("--continue", dest="cont", action="store_true")
     ap.add_argument("--rerun-failure", action="store_true")
     ns = ap.parse_args(argv)
@@ -272,7 +277,9 @@ def main(argv: list[str] | None = None) -> int:
     if unknown:
         ap.error(f"unknown cases {unknown}")
     targets = dict(t.split("=", 1) for t in ns.targets)
-    res = run_suite([CASES[n] for n in names], targets, Path(ns.out), cont=ns.cont, rerun_failure=ns.rerun_failure)
+    vocab = {m: int(n) for m, n in (v.split("=", 1) for v in ns.vocab)}
+    runner = (lambda c, t, seed: default_runner(c, t, seed, vocab)) if vocab else default_runner
+    res = run_suite([CASES[n] for n in names], targets, Path(ns.out), cont=ns.cont, rerun_failure=ns.rerun_failure, runner=runner)
     print(json.dumps(asdict(res), indent=1))
     return 3 if res.failed else 0
 

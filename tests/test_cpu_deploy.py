@@ -635,3 +635,29 @@ def test_an_external_ranks_elastic_kv_state_borrows_from_a_hosted_neighbour_thro
 
     _run(tmp_path, models, check, retire=False, before_ready=before_ready,
          atn_extra="elastic_kv = true\ndevice_memory_utilization = 1.0", extra_env={"XPOOL_CPU_KV_BYTES": str(10 * bundle)})
+
+
+def test_the_benchmark_tool_brings_up_a_cpu_deployment_runs_a_case_and_its_result_is_reportable(tmp_path, capsys):
+    """The serving benchmark end to end without a GPU: ``bench.serve_case`` starts the deployment as processes, drives
+    the open-loop client of the smoke case against it (streaming requests, client-side TTFT / TPOT), retires it, and
+    the suite runner's sealed result of the same runner is turned into a report."""
+    import json
+
+    from crosspool_b200.bench import report as R
+    from crosspool_b200.bench import serve_case, suite
+
+    dport = _free_port()
+    sport = _free_port_run(1, {dport})
+    out = tmp_path / "case.json"
+    rc = serve_case.main(["--case", "smoke", "--models", "tiny-qwen3", "--atn", "0", "--ffn", "1", "2", "--ffn-tp", "2", "--backend", "cpu",
+                          "--port", str(dport), "--serving-port", str(sport), "--max-batch", "4", "--max-seq-len", "128", "--max-rows", "128",
+                          "--out", str(out)])
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and line["case"] == "smoke" and line["errors"] == 0 and line["completed"] > 0 and line["output_tok_per_s"] > 0
+    doc = json.loads(out.read_text())
+    assert doc["deployment"]["backend"] == "cpu" and doc["aggregate"]["tpot_ms"]["n"] > 0 and set(doc["per_model"]) == {"tiny-qwen3"}
+    # the same result as a sealed suite repetition -> report
+    run = tmp_path / "run"
+    suite.run_suite([suite.CASES["smoke"]], {"tiny-qwen3": "unused"}, run, runner=lambda c, t, seed: doc)
+    made = R.make_reports(run)
+    assert (made[0] / "report.md").read_text().startswith("# smoke") and (made[0] / "throughput.svg").exists()
