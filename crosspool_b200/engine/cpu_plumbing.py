@@ -87,7 +87,8 @@ def ffn_side(source: str, seed: int, rank: int = 0, size: int = 1, moe_parallel:
     return cfg, out
 
 
-def _view(address: int, rows: int, hidden: int) -> torch.Tensor:
+def arena_view(address: int, rows: int, hidden: int) -> torch.Tensor:
+    """``rows x hidden`` fp32 view of an arena's input or output region."""
     buf = (ctypes.c_float * (rows * hidden)).from_address(address)
     return torch.frombuffer(buf, dtype=torch.float32).view(rows, hidden)
 
@@ -109,8 +110,8 @@ def ffn_role_main(arena_name: str, preset: str, seed: int, max_rows: int, ready,
             if layer >= cfg.num_layers or rows > max_rows:
                 mb.complete(rt.RESULT_PROTOCOL_MISMATCH)
                 break
-            x = _view(mb.input_address, rows, cfg.hidden_size)
-            y = _view(mb.output_address, rows, cfg.hidden_size)
+            x = arena_view(mb.input_address, rows, cfg.hidden_size)
+            y = arena_view(mb.output_address, rows, cfg.hidden_size)
             if mode == rt.MODE_IDLE:
                 y.zero_()
             else:
@@ -199,8 +200,8 @@ def ffn_rank_main(arena_name: str, preset: str, seed: int, max_rows: int, ready,
             if layer >= cfg.num_layers or rows > max_rows:
                 mb.complete(rt.RESULT_PROTOCOL_MISMATCH)
                 break
-            x = _view(mb.input_address, rows, cfg.hidden_size)
-            y = _view(mb.output_address, rows, cfg.hidden_size)
+            x = arena_view(mb.input_address, rows, cfg.hidden_size)
+            y = arena_view(mb.output_address, rows, cfg.hidden_size)
             if mode == rt.MODE_IDLE:
                 y.zero_()
             else:
@@ -364,12 +365,12 @@ def dp_ffn_main(names: list[str], preset: str, seed: int, max_rows: int, ready, 
                 return
             merged_mode, offsets = table
             live = [r for r in range(len(boxes)) if modes[r] != rt.MODE_IDLE]
-            x = torch.cat([_view(boxes[r].input_address, rows[r], hidden) for r in live])
+            x = torch.cat([arena_view(boxes[r].input_address, rows[r], hidden) for r in live])
             with torch.no_grad():
                 y = ffn_forward(x, weights[layer], cfg)
             at = 0
             for r in live:
-                _view(boxes[r].output_address, rows[r], hidden).copy_(y[at:at + rows[r]])
+                arena_view(boxes[r].output_address, rows[r], hidden).copy_(y[at:at + rows[r]])
                 at += rows[r]
             stats[0] += 1                                   # merged evaluations
             stats[1] += len(boxes) - len(live)              # idle participations

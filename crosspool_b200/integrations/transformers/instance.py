@@ -50,10 +50,10 @@ class ExternalInstance:
             # The GPU form of the same step: map the leased attention-side slot and the FFN ranks' slots by their IPC
             # handles and point the native operator at them. Written against the brokering of AtnBackend; it has not
             # run on GPUs yet (the CPU form below is what the tests exercise).
-            from ...runtime.backends import _placement
+            from ...runtime.backends import placement_for
             from ..sglang.transport import FabricInstanceTransport
 
-            place = _placement(self.cfg, plan, self.model_id, self.rank, self.cfg.engine_max_rows)
+            place = placement_for(self.cfg, plan, self.model_id, self.rank, self.cfg.engine_max_rows)
             t = FabricInstanceTransport.from_handles(place, binding.handle_hex,
                                                      [plan.slot_handles[f"ffn:{self.model_id}:{self.rank}:{pe}"] for pe in place.ffn_ranks],
                                                      next(model.parameters()).device)

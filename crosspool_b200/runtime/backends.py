@@ -36,7 +36,9 @@ def checkpoint_dir_for(cfg: XpoolConfig, model_id: str) -> str | None:
     return None
 
 
-def _placement(cfg: XpoolConfig, plan: FabricPlan, model_id: str, atn_rank: int, capacity_rows: int) -> F.InstancePlacement:
+def placement_for(cfg: XpoolConfig, plan: FabricPlan, model_id: str, atn_rank: int, capacity_rows: int) -> F.InstancePlacement:
+    """The placement of one Instance rank as the plan states it: FFN ranks per layer group in TP order, the attention TP
+    followers, seed or checkpoint. Every backend (GPU, CPU, an engine process of its own) derives it here."""
     shards = [s for s in plan.shards if s.model_id == model_id]
     ranges = sorted({(s.layer_begin, s.layer_end) for s in shards})
     groups = tuple((lo, hi, tuple(s.pe for s in sorted((x for x in shards if (x.layer_begin, x.layer_end) == (lo, hi)),
@@ -51,6 +53,9 @@ def _placement(cfg: XpoolConfig, plan: FabricPlan, model_id: str, atn_rank: int,
     return F.InstancePlacement(model_id, model_config_for(cfg, model_id), seed, rank.pe, union, capacity_rows,
                                layer_groups=groups if len(groups) > 1 else (),
                                checkpoint=checkpoint_dir_for(cfg, model_id), atn_tp_followers=followers)
+
+
+_placement = placement_for      # earlier name, still imported by the plugin and by tests
 
 
 class FfnBackend:
@@ -69,7 +74,7 @@ class FfnBackend:
         for r in plan.instance_ranks:
             if r.rank % self.cfg.model(r.model_id).atn_tp_size:
                 continue    # an attention TP follower: the group's first rank talks to the FFN tier for all of them
-            place = _placement(self.cfg, plan, r.model_id, r.rank, self.capacity_rows)
+            place = placement_for(self.cfg, plan, r.model_id, r.rank, self.capacity_rows)
             if my_pe not in place.ffn_ranks:
                 continue
             tp_rank, lo, hi = place.locate(my_pe)
@@ -153,7 +158,7 @@ class AtnBackend:
         torch.cuda.set_device(self.cuda)
         handles = {}
         for model_id, rank in self.instances:
-            place = _placement(self.cfg, plan, model_id, rank, self.capacity_rows)
+            place = placement_for(self.cfg, plan, model_id, rank, self.capacity_rows)
             self.places[(model_id, rank)] = place
             tpr, tps, _ = self._tp(model_id, rank)
             if tpr == 0:
@@ -171,7 +176,7 @@ class AtnBackend:
             for model_id, rank in self.external:
                 if self.cfg.model(model_id).atn_tp_size != 1:
                     raise NotImplementedError("external Instance ranks with attention tensor parallelism are not brokered")
-                place = _placement(self.cfg, plan, model_id, rank, self.capacity_rows)
+                place = placement_for(self.cfg, plan, model_id, rank, self.capacity_rows)
                 nbytes = F.atn_slot_layout(place).total_bytes
                 buf = F.PeerBuffer(nbytes)
                 self.buffers[(model_id, rank)] = buf                 # freed in finalize with the hosted ranks' slots

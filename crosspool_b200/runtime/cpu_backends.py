@@ -25,13 +25,13 @@ import torch
 
 from ..config import XpoolConfig
 from ..engine.atn_engine import Sequence
-from ..engine.cpu_plumbing import RemoteFfn, _view
+from ..engine.cpu_plumbing import RemoteFfn, arena_view
 from ..engine.kv_cache import OutOfPages
 from ..models import reference
 from ..models.weights import load_attention_from_safetensors, random_attention_weights, random_ffn_layer
 from ..native import runtime as rt
 from ..service.wire import FabricPlan, InvocationFailure, ServingListener
-from .backends import _placement
+from .backends import placement_for
 
 CPU_MAX_ROWS = 512
 
@@ -97,7 +97,7 @@ class CpuFfnBackend:
         for r in plan.instance_ranks:
             if r.rank % self.cfg.model(r.model_id).atn_tp_size:
                 continue
-            place = _placement(self.cfg, plan, r.model_id, r.rank, self.capacity_rows)
+            place = placement_for(self.cfg, plan, r.model_id, r.rank, self.capacity_rows)
             if my_pe not in place.ffn_ranks:
                 continue
             tp_rank, lo, hi = place.locate(my_pe)
@@ -137,12 +137,12 @@ class CpuFfnBackend:
                     mb.complete(rt.RESULT_PROTOCOL_MISMATCH)
                     self.errors.append(f"{a['name']}: invocation for layer {layer} with {rows} rows refused")
                     return
-                y = _view(mb.output_address, rows, cfg.hidden_size)
+                y = arena_view(mb.output_address, rows, cfg.hidden_size)
                 if mode == rt.MODE_IDLE:
                     y.zero_()
                 else:
                     with torch.no_grad():
-                        y.copy_(reference.ffn_forward(_view(mb.input_address, rows, cfg.hidden_size), a["weights"][layer - a["lo"]], cfg))
+                        y.copy_(reference.ffn_forward(arena_view(mb.input_address, rows, cfg.hidden_size), a["weights"][layer - a["lo"]], cfg))
                 mb.complete(rt.RESULT_OK)
                 self.served += 1
         except Exception as e:      # reported by poll_health, which fails the generation
@@ -420,7 +420,7 @@ class CpuAtnBackend:
         for model_id, rank in self.instances:
             if self.cfg.model(model_id).atn_tp_size != 1:
                 raise NotImplementedError("the CPU attention backend runs attention on one rank per Instance")
-            self.places[(model_id, rank)] = _placement(self.cfg, plan, model_id, rank, self.capacity_rows)
+            self.places[(model_id, rank)] = placement_for(self.cfg, plan, model_id, rank, self.capacity_rows)
             handles[f"atn:{model_id}:{rank}"] = b"cpu".hex()       # the attention side owns no arena on the CPU
         if self.external:
             from ..service.wire import TransportArenaBinding
@@ -508,7 +508,7 @@ def attach_cpu_instance(cfg: XpoolConfig, plan: FabricPlan, model_id: str, rank:
     its arena: it maps the FFN ranks' arenas named in the plan and gets a handle that evaluates one layer
     (``CpuTierPort``). The GPU counterpart maps IPC handles (``integrations/sglang/transport.py::from_handles``)."""
     capacity_rows = cpu_capacity_rows(cfg)
-    place = _placement(cfg, plan, model_id, rank, capacity_rows)
+    place = placement_for(cfg, plan, model_id, rank, capacity_rows)
     boxes, groups = [], []
     for lo, hi, pes in place.groups():
         ranks = []

@@ -71,7 +71,7 @@ def test_attention_backend_allocates_and_brokers_the_slot_of_an_external_rank_an
     handles = backend.prepare_join(plan)
     # one attention-side slot per rank, hosted or not, named in the plan for the FFN ranks to open
     assert set(handles) == {"atn:tiny-qwen3:0", "atn:tiny-qwen3-moe:0"} and len(FakePeerBuffer.made) == 2
-    ext_place = B._placement(cfg, plan, "tiny-qwen3-moe", 0, backend.capacity_rows)
+    ext_place = B.placement_for(cfg, plan, "tiny-qwen3-moe", 0, backend.capacity_rows)
     assert FakePeerBuffer.made[1].nbytes == F.atn_slot_layout(ext_place).total_bytes > 0
     # ... and the external rank's slot handed to the daemon's broker, for the rank's own process to lease
     (gen, arenas), = published
