@@ -105,7 +105,7 @@ def default_runtime_factory(config: Any) -> Callable:
     """Instance runtimes that reach the daemon named in ``config`` and bind the native transport from the handles
     the daemon brokers (the attention-side arena through the lease, the FFN slots through the plan)."""
     def make(binding, rank, profile, device):
-        from ...runtime.backends import _placement
+        from ...runtime.backends import placement_for
         from ...runtime.instance import InstanceRankRuntime
         from ...service.client import XpoolClient
         from .transport import FabricInstanceTransport
@@ -113,7 +113,7 @@ def default_runtime_factory(config: Any) -> Callable:
         client = XpoolClient(getattr(config, "daemon_host", "127.0.0.1"), getattr(config, "daemon_port", 9810))
 
         def attach(arena, plan):
-            place = _placement(config, plan, binding.model_id, rank, max(profile.max_prefill_rows, profile.max_decode_rows))
+            place = placement_for(config, plan, binding.model_id, rank, max(profile.max_prefill_rows, profile.max_decode_rows))
             ffn = [plan.slot_handles[f"ffn:{binding.model_id}:{rank}:{pe}"] for pe in place.ffn_ranks]
             tr = FabricInstanceTransport.from_handles(place, arena.handle_hex, ffn, f"cuda:{device}")
             tr.make_current()

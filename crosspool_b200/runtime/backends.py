@@ -55,8 +55,6 @@ def placement_for(cfg: XpoolConfig, plan: FabricPlan, model_id: str, atn_rank: i
                                checkpoint=checkpoint_dir_for(cfg, model_id), atn_tp_followers=followers)
 
 
-_placement = placement_for      # earlier name, still imported by the plugin and by tests
-
 
 class FfnBackend:
     def __init__(self, cfg: XpoolConfig, device: int, capacity_rows: int = 4096, local_index: int | None = None):

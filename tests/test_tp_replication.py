@@ -91,7 +91,7 @@ def test_deployed_placement_names_the_tp_group_from_its_first_rank():
     """Every rank of an attention TP group resolves the same placement: the group's first rank talks to the FFN
     tier, the others follow it (reference: atn_tp_size in src/xpool/config.py)."""
     from crosspool_b200.config import load_config
-    from crosspool_b200.runtime.backends import _placement
+    from crosspool_b200.runtime.backends import placement_for
     from crosspool_b200.service.wire import FabricPhase, FabricPlan, InstanceRankTopology, ShardPlacement
 
     cfg = load_config(env={}, toml_text="""
@@ -114,7 +114,7 @@ atn_tp_size = 2
                                              device=2, pe=2, bytes=1)],
                       instance_ranks=[InstanceRankTopology(model_id="Qwen/Qwen3-0.6B", rank=r, device=r, pe=r, instance_index=r)
                                       for r in (0, 1)])
-    a, b = (_placement(cfg, plan, "Qwen/Qwen3-0.6B", r, 256) for r in (0, 1))
+    a, b = (placement_for(cfg, plan, "Qwen/Qwen3-0.6B", r, 256) for r in (0, 1))
     assert a == b and a.atn_rank == 0 and a.atn_tp_followers == (1,) and a.ffn_ranks == (2,)
 
 
