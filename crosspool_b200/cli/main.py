@@ -32,6 +32,10 @@ def _parser() -> argparse.ArgumentParser:
         a.add_argument("--device", type=int, required=True)
         a.add_argument("--backend", choices=("gpu", "cpu"), default="gpu",
                        help="cpu: the same control plane with the shared-memory data plane and the PyTorch oracle (no GPU needed)")
+    r = sub.add_parser("router", help="one POST /generate endpoint in front of the data-parallel ranks the daemon lists")
+    r.add_argument("--host", default="127.0.0.1")
+    r.add_argument("--port", type=int, required=True)
+    r.add_argument("--model", action="append", default=None, help="restrict to these models (default: every model with a listener)")
     e = sub.add_parser("exec", help="run a command in the deployment's environment")
     e.add_argument("argv", nargs=argparse.REMAINDER)
     c = sub.add_parser("config")
@@ -200,6 +204,11 @@ def main(argv: list[str] | None = None) -> int:
             return cmd_daemon_serve(ns) if ns.daemon_command == "serve" else cmd_daemon_check(ns)
         if ns.command == "exec":
             return cmd_exec(ns)
+        if ns.command == "router":
+            from ..runtime.dp_router import serve_router
+
+            cfg = _load(ns, require=False)
+            return serve_router(f"http://{cfg.daemon_host}:{cfg.daemon_port}", ns.host, ns.port, ns.model)
         if ns.command == "memory-profile":
             return cmd_memory_profile(ns)
         if ns.command in ("atnagent", "ffnagent"):

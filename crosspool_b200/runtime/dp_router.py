@@ -98,3 +98,54 @@ def create_router_app(router: DpRouter, transport=None):
         return StreamingResponse(relay(), media_type="text/event-stream")
 
     return app
+
+
+def discover_ranks(router: DpRouter, daemon_url: str, models: list[str] | None = None, http=None) -> int:
+    """Registers the serving listeners the daemon knows (``GET /instances``: every initialised Instance rank that
+    published one) with ``router``; ``models`` restricts it. Returns how many ranks are registered afterwards. Ranks
+    that disappeared from the daemon's table are marked unhealthy, new ones are added: call it periodically."""
+    import httpx
+
+    get = (http or httpx).get
+    table = get(daemon_url.rstrip("/") + "/instances", timeout=5).json()
+    seen: dict[str, set[str]] = {}
+    for key, info in table.items():
+        model = key.rsplit(":", 1)[0]
+        if (models and model not in models) or not info.get("initialized") or not info.get("listener"):
+            continue
+        url = "http://" + info["listener"]
+        router.register(model, url)
+        seen.setdefault(model, set()).add(url)
+    for model, ranks in router.backends.items():
+        for b in ranks:
+            if b.url in seen.get(model, ()):
+                b.healthy = True
+            elif not models or model in models:
+                b.healthy = False
+    return sum(len(v) for v in seen.values())
+
+
+def serve_router(daemon_url: str, host: str, port: int, models: list[str] | None = None, refresh_s: float = 2.0) -> int:
+    """``xpool router``: one endpoint in front of every data-parallel rank the daemon lists, refreshed every
+    ``refresh_s`` seconds."""
+    import threading
+
+    import uvicorn
+
+    router = DpRouter()
+    stop = threading.Event()
+
+    def refresh():
+        while not stop.is_set():
+            try:
+                discover_ranks(router, daemon_url, models)
+            except Exception:
+                pass            # the daemon may be restarting: keep the ranks already known
+            stop.wait(refresh_s)
+
+    threading.Thread(target=refresh, daemon=True, name="dp-router-discovery").start()
+    try:
+        uvicorn.run(create_router_app(router), host=host, port=port, log_level="warning")
+    finally:
+        stop.set()
+    return 0

@@ -233,6 +233,27 @@ def test_data_parallel_attention_ranks_share_the_ffn_tier_behind_the_request_rou
             assert r.json()["output_ids"] == whole.generate(torch.tensor(p), 4)[0]
         served = [b.served for b in router.backends["tiny-qwen3"]]
         assert sum(served) == 4 and min(served) >= 1              # both ranks took part
+        # the same front end as a process that finds the ranks through the daemon (`xpool router`)
+        rport = _free_port_run(1, {plan_port[0], base, base + 1})
+        env = dict(os.environ, XPOOL_CONFIG=str(tmp_path / "xpool.toml"), PYTHONPATH=str(ROOT), XPOOL_MAX_ROWS="128", XPOOL_MAX_BATCH="4",
+                   XPOOL_MAX_SEQ_LEN="128")
+        proc = subprocess.Popen([sys.executable, "-m", "crosspool_b200.cli.main", "router", "--port", str(rport)], env=env)
+        try:
+            ranks_seen = {}
+            for _ in range(100):
+                try:
+                    ranks_seen = httpx.get(f"http://127.0.0.1:{rport}/ranks", timeout=1).json()
+                    if len(ranks_seen.get("tiny-qwen3", [])) == 2:
+                        break
+                except httpx.HTTPError:
+                    pass
+                time.sleep(0.2)
+            assert sorted(b["url"] for b in ranks_seen["tiny-qwen3"]) == sorted(ranks)
+            r = httpx.post(f"http://127.0.0.1:{rport}/generate", json={"model": "tiny-qwen3", "input_ids": prompts[0], "max_new_tokens": 4}, timeout=120)
+            assert r.status_code == 200 and r.json()["output_ids"] == whole.generate(torch.tensor(prompts[0]), 4)[0]
+        finally:
+            proc.terminate()
+            proc.wait(10)
 
     _run(tmp_path, models, check, atn=(0, 1), ffn=(2, 3))
 
