@@ -48,3 +48,25 @@ def test_router_app_relays_plain_and_streaming_requests():
         snap = c.get("/ranks").json()["m"]
         assert sum(b["served"] for b in snap) == 4 and all(b["inflight"] == 0 and b["outstanding_tokens"] == 0 for b in snap)
         assert c.post("/generate", json={"model": "zzz", "input_ids": [1]}).status_code == 503
+
+
+def test_ranks_are_discovered_from_the_daemons_listing_and_vanished_ones_stop_receiving_requests():
+    import types
+
+    from crosspool_b200.runtime.dp_router import DpRouter, discover_ranks
+
+    table = {"m/a:0": {"initialized": True, "listener": "127.0.0.1:30000"}, "m/a:1": {"initialized": True, "listener": "127.0.0.1:30001"},
+             "m/a:2": {"initialized": False, "listener": "127.0.0.1:30002"},             # still warming up
+             "m/b:0": {"initialized": True, "listener": None},                            # hosted, no listener of its own
+             "m/c:0": {"initialized": True, "listener": "127.0.0.1:30100"}}
+    http = types.SimpleNamespace(get=lambda url, timeout: types.SimpleNamespace(json=lambda: table))
+    r = DpRouter()
+    assert discover_ranks(r, "http://daemon", ["m/a"], http=http) == 2
+    assert [b.url for b in r.backends["m/a"]] == ["http://127.0.0.1:30000", "http://127.0.0.1:30001"] and "m/c" not in r.backends
+    del table["m/a:1"]                                                   # the rank left (or its agent died)
+    table["m/a:2"]["initialized"] = True
+    assert discover_ranks(r, "http://daemon", ["m/a"], http=http) == 2
+    health = {b.url: b.healthy for b in r.backends["m/a"]}
+    assert health == {"http://127.0.0.1:30000": True, "http://127.0.0.1:30001": False, "http://127.0.0.1:30002": True}
+    assert r.pick("m/a", 10).url != "http://127.0.0.1:30001" and r.pick("m/a", 10).url != "http://127.0.0.1:30001"
+    assert discover_ranks(r, "http://daemon", None, http=http) == 3 and "m/c" in r.backends
