@@ -25,10 +25,12 @@ def _parser() -> argparse.ArgumentParser:
     sub = p.add_subparsers(dest="command", required=True)
     d = sub.add_parser("daemon", help="control plane")
     ds = d.add_subparsers(dest="daemon_command", required=True)
-    ds.add_parser("serve")
-    ds.add_parser("check")
-    for name in ("atnagent", "ffnagent"):
-        a = sub.add_parser(name)
+    ds.add_parser("serve", help="run the daemon")
+    ds.add_parser("check", help="print a running daemon's readiness snapshot; exit code 0 when the system is ready")
+    for name, what in (("atnagent", "attention agent of one device: hosts its Instances (engine, KV, POST /generate) or brokers "
+                                    "the arenas of external ones"),
+                       ("ffnagent", "FFN agent of one device: loads the FFN shards the plan assigns to it and serves them")):
+        a = sub.add_parser(name, help=what)
         a.add_argument("--device", type=int, required=True)
         a.add_argument("--backend", choices=("gpu", "cpu"), default="gpu",
                        help="cpu: the same control plane with the shared-memory data plane and the PyTorch oracle (no GPU needed)")
@@ -38,15 +40,15 @@ def _parser() -> argparse.ArgumentParser:
     r.add_argument("--model", action="append", default=None, help="restrict to these models (default: every model with a listener)")
     e = sub.add_parser("exec", help="run a command in the deployment's environment")
     e.add_argument("argv", nargs=argparse.REMAINDER)
-    c = sub.add_parser("config")
+    c = sub.add_parser("config", help="dump the resolved configuration; print the settings and supported-model references")
     cs = c.add_subparsers(dest="config_command", required=True)
     cs.add_parser("dump", help="the resolved configuration with the source of every value")
     cs.add_parser("reference", help="every setting with its TOML key, environment variable, flag and default (markdown)")
     cs.add_parser("models", help="supported architectures and what runs where (markdown)")
-    mp = sub.add_parser("memory-profile")
+    mp = sub.add_parser("memory-profile", help="placement and memory admission of the configured models; --calibrate fits the overhead model")
     mp.add_argument("--calibrate", action="store_true", help="measure a corpus of synthetic deployments on this GPU and fit the model")
     mp.add_argument("--out", default="xpool-memory-profile.json")
-    b = sub.add_parser("bench")
+    b = sub.add_parser("bench", help="open-loop load generator against running Instances (--targets MODEL=URL ...)")
     b.add_argument("rest", nargs=argparse.REMAINDER)
     q = sub.add_parser("qualify", help="check an architecture's FFN path against its checkpoint description")
     q.add_argument("rest", nargs=argparse.REMAINDER)

@@ -363,7 +363,7 @@ def reference_markdown() -> str:
 def add_cli_arguments(parser: argparse.ArgumentParser) -> None:
     for s in CONFIG_REGISTRY:
         if s.cli:
-            parser.add_argument(s.cli, dest=f"cfg_{s.name}", default=None, help=s.description or s.name)
+            parser.add_argument(s.cli, dest=f"cfg_{s.name}", default=None, metavar="VALUE", help=s.description or s.name)
 
 
 def cli_overrides(ns: argparse.Namespace) -> dict[str, Any]:
