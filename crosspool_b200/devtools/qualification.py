@@ -22,6 +22,7 @@ src/xpool-dev/xtest/harness/support/ffn.py:20-28).
     python -m crosspool_b200.devtools.qualification --arch all
     python -m crosspool_b200.devtools.qualification --config /path/to/config.json --shrink
     python -m crosspool_b200.devtools.qualification --arch all --against hf     # the transformers model as the other side
+    python -m crosspool_b200.devtools.qualification --arch all --against served # a CPU deployment per architecture, over HTTP
 """
 
 from __future__ import annotations
@@ -444,9 +445,18 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--shrink", action="store_true", help="replace the sizes of --config by the family's tiny ones")
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--json", action="store_true")
-    ap.add_argument("--against", choices=("direct", "hf"), default="direct",
-                    help="'hf': compare with the transformers implementation of the architecture (devtools/hf_parity.py)")
+    ap.add_argument("--against", choices=("direct", "hf", "served"), default="direct",
+                    help="'hf': compare with the transformers implementation of the architecture (devtools/hf_parity.py); "
+                         "'served': bring up a CPU deployment per architecture and compare its answers with the library's "
+                         "(devtools/served_qualification.py)")
     ns = ap.parse_args(argv)
+    if ns.against == "served":
+        from . import served_qualification
+
+        if ns.config:
+            p = Path(ns.config)
+            return served_qualification.main(["--checkpoint", str(p if p.is_dir() else p.parent)] + (["--json"] if ns.json else []))
+        return served_qualification.main(["--arch", ns.arch] + (["--json"] if ns.json else []))
     if ns.against == "hf":
         from . import hf_parity
 

@@ -315,6 +315,10 @@ class AtnBackend:
             conf = uvicorn.Config(app, host=self._listen[0], port=self._listen[1], log_level="warning")
             self._server = uvicorn.Server(conf)
             threading.Thread(target=self._server.run, daemon=True, name="serving-http").start()
+            for _ in range(1000):                    # the listener is published only once it accepts connections
+                if self._server.started:
+                    break
+                threading.Event().wait(0.01)
             self.listener = ServingListener(host=self._listen[0], port=self._listen[1])
 
     def poll_health(self) -> InvocationFailure | None:

@@ -477,6 +477,10 @@ class CpuAtnBackend:
             app = create_serving_app(self.loop, list(self.engines), tokenizer=toks)
             self._server = uvicorn.Server(uvicorn.Config(app, host=self._listen[0], port=self._listen[1], log_level="warning"))
             threading.Thread(target=self._server.run, daemon=True, name="serving-http").start()
+            for _ in range(1000):                    # the listener is published only once it accepts connections
+                if self._server.started:
+                    break
+                time.sleep(0.01)
             self.listener = ServingListener(host=self._listen[0], port=self._listen[1])
 
     def poll_health(self) -> InvocationFailure | None:

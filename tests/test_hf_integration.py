@@ -54,3 +54,17 @@ def test_command_line_demo_generates_from_a_local_checkpoint_and_verifies_agains
     out = capsys.readouterr()
     assert rc == 0 and "same tokens as the whole model" in out.err
     assert len(out.out.split()) == 5 and "detached 2 FFN layers" in out.err
+
+
+def test_served_qualification_brings_up_a_deployment_and_compares_its_answers_with_the_librarys(capsys):
+    from crosspool_b200.devtools import served_qualification as sq
+
+    name = "Glm4MoeLiteForCausalLM/small-latent-yarn"
+    if not hf_parity.available(name):
+        pytest.skip(f"the installed transformers has no {name}")
+    assert sq.main(["--arch", name, "--prompts", "2", "--new-tokens", "4", "--json"]) == 0
+    import json
+
+    rep = json.loads([l for l in capsys.readouterr().out.splitlines() if l.startswith("{")][-1])
+    assert rep["ok"] and rep["architecture"] == "Glm4MoeLiteForCausalLM" and rep["ffn_ranks"] == 2
+    assert [p["equal"] for p in rep["prompts"]] == [True, True] and all(len(p["served"]) == 4 for p in rep["prompts"])
