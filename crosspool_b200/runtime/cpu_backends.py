@@ -209,8 +209,8 @@ class CpuOracleEngine:
     step admits waiting requests (a whole prompt is one prefill pass) up to ``max_batch`` running sequences, or
     advances every running sequence by one token."""
 
-    def __init__(self, cfg, attn_weights, ffn, max_batch: int = 8, max_seq_len: int = 512):
-        self.cfg, self.model, self.ffn = cfg, reference.ReferenceModel(cfg, attn_weights, ffn=[]), ffn
+    def __init__(self, cfg, attn_weights, ffn, max_batch: int = 8, max_seq_len: int = 512, model=None):
+        self.cfg, self.model, self.ffn = cfg, model or reference.ReferenceModel(cfg, attn_weights, ffn=[]), ffn
         self.max_batch, self.max_seq_len = max_batch, max_seq_len
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
@@ -326,6 +326,37 @@ class CpuOracleEngine:
         return out
 
 
+class TpOracle(reference.ReferenceModel):
+    """The oracle on one attention tensor-parallel rank: its share of the heads (``parallel/atn_tp.py`` sharding), the
+    output projections summed over the group after every attention block (a gloo all-reduce here; the GPU ranks fold the
+    same sum into the norm kernel through peer memory)."""
+
+    def attention_half(self, layer, resid, ffn_out, positions, cache):
+        import torch.distributed as dist
+
+        cfg, lw = self.cfg, self.attn.layers[layer]
+        if ffn_out is not None:
+            resid = resid + ffn_out
+        x = reference.block_norm(cfg, resid, lw.input_norm, lw.extra.get("input_norm_bias"))
+        part = reference.attention_core(cfg, lw, x, positions, cache, layer).contiguous()
+        dist.all_reduce(part)
+        resid = resid + part
+        return resid, reference.block_norm(cfg, resid, lw.post_attn_norm, lw.extra.get("post_attn_norm_bias"))
+
+
+def tp_ffn(port, leader: bool):
+    """FFN of a tensor-parallel Instance: the group's first rank talks to the FFN tier for all of them and hands the
+    result to the others (the GPU followers read it from the first rank's slot)."""
+    import torch.distributed as dist
+
+    def call(layer: int, x: torch.Tensor, mode: int | None = None) -> torch.Tensor:
+        y = port(layer, x, mode).contiguous() if leader else torch.empty_like(x)
+        dist.broadcast(y, src=0)
+        return y
+
+    return call
+
+
 class CpuDeployment:
     """The stepped-deployment protocol of ``runtime/serving.py::EngineLoop`` over CPU engines."""
 
@@ -373,6 +404,7 @@ class CpuAtnBackend:
         self._server = None
         self.loop = None
         self.listener: ServingListener | None = None
+        self._tp: tuple[int, int, int] | None = None     # (TP rank, TP size, first rank) when this device hosts a TP member
         self.ecs_ref = None              # callable(generation) -> EcsChannelRef, set by the launcher when elastic KV is on
         self.kv_budget_bytes = 64 << 20  # what this "device" reports as its memory to the capacity policy
         self._ecs_channel = None
@@ -418,8 +450,8 @@ class CpuAtnBackend:
         torch.set_num_threads(1)
         handles = {}
         for model_id, rank in self.instances:
-            if self.cfg.model(model_id).atn_tp_size != 1:
-                raise NotImplementedError("the CPU attention backend runs attention on one rank per Instance")
+            if self.cfg.model(model_id).atn_tp_size != 1 and self.cfg.atn_elastic_kv:
+                raise NotImplementedError("the CPU attention backend does not combine attention tensor parallelism with elastic KV")
             self.places[(model_id, rank)] = placement_for(self.cfg, plan, model_id, rank, self.capacity_rows)
             handles[f"atn:{model_id}:{rank}"] = b"cpu".hex()       # the attention side owns no arena on the CPU
         if self.external:
@@ -435,6 +467,8 @@ class CpuAtnBackend:
 
     def join(self, plan: FabricPlan) -> None:
         for (model_id, rank), place in self.places.items():
+            if rank % self.cfg.model(model_id).atn_tp_size:
+                continue                 # a tensor-parallel follower: the group's first rank talks to the FFN tier
             groups = []
             for lo, hi, pes in place.groups():
                 ranks = []
@@ -452,6 +486,17 @@ class CpuAtnBackend:
                 aw = load_attention_from_safetensors(place.cfg, place.checkpoint, dtype=torch.float32)
             else:
                 aw = random_attention_weights(place.cfg, place.seed, dtype=torch.float32)
+            tps = self.cfg.model(model_id).atn_tp_size
+            if tps > 1:
+                from ..parallel import atn_tp
+
+                tpr = rank % tps
+                local = atn_tp.local_config(place.cfg, tps)
+                model = TpOracle(local, atn_tp.shard_attention_weights(aw, place.cfg, tpr, tps), ffn=[])
+                self.engines[model_id] = CpuOracleEngine(local, None, tp_ffn(self.ports.get(model_id), tpr == 0), self.max_batch,
+                                                         min(self.max_seq_len, self.capacity_rows), model=model)
+                self._tp = (tpr, tps, rank - tpr)
+                continue
             self.engines[model_id] = CpuOracleEngine(place.cfg, aw, self.ports[model_id], self.max_batch,
                                                      min(self.max_seq_len, self.capacity_rows))
         if self.cfg.atn_elastic_kv and self.ecs_ref is not None:
@@ -468,9 +513,25 @@ class CpuAtnBackend:
                 raise RuntimeError("an FFN arena never became idle")
         if not self.engines:
             return                                               # every rank of this device is served by another process
-        self.loop = EngineLoop(CpuDeployment(self.engines))
+        leader = True
+        if self._tp is not None:
+            # the ranks of the group meet before any of them runs a forward pass; they share the host
+            import os
+
+            import torch.distributed as dist
+
+            from .tp_replication import TpEngineLoop
+
+            tpr, tps, first = self._tp
+            leader = tpr == 0
+            os.environ.setdefault("GLOO_SOCKET_IFNAME", "lo")
+            dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{self.cfg.serving_tp_rendezvous_base_port + first}",
+                                    rank=tpr, world_size=tps)
+            self.loop = TpEngineLoop(CpuDeployment(self.engines), None, leader)
+        else:
+            self.loop = EngineLoop(CpuDeployment(self.engines))
         self.loop.start()
-        if self._listen is not None:
+        if self._listen is not None and leader:
             import uvicorn
 
             toks = load_tokenizers({m: place.checkpoint for (m, _), place in self.places.items()})
@@ -502,6 +563,11 @@ class CpuAtnBackend:
             mb.close()
         self._boxes = []
         self.engines.clear()
+        if self._tp is not None:
+            import torch.distributed as dist
+
+            if dist.is_initialized():
+                dist.destroy_process_group()
         if self._ecs_channel is not None:
             self._ecs_channel.close()
             self._ecs_channel = None

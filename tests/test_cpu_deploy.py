@@ -43,7 +43,7 @@ def _free_port_run(n: int, avoid: set[int]) -> int:
     raise RuntimeError("no run of free ports found")
 
 
-def _toml(daemon_port: int, serve_port: int, models: str, atn=(0,), ffn=(1, 2), atn_extra="") -> str:
+def _toml(daemon_port: int, serve_port: int, models: str, atn=(0,), ffn=(1, 2), atn_extra="", serving_extra="") -> str:
     return f"""
 [daemon]
 port = {daemon_port}
@@ -57,6 +57,7 @@ ttft_ms = 2000
 tbt_ms = 50
 [serving]
 base_port = {serve_port}
+{serving_extra}
 {models}
 """
 
@@ -64,12 +65,13 @@ base_port = {serve_port}
 plan_port = [0]          # the daemon port of the deployment a check callback is looking at
 
 
-def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2), retire=True, atn_extra="", extra_env=None, before_ready=None):
+def _run(tmp_path, models_toml, check, atn=(0,), ffn=(1, 2), retire=True, atn_extra="", extra_env=None, before_ready=None,
+         serving_extra=""):
     dport = _free_port()
     sport = _free_port_run(len(atn), {dport})
     plan_port[0] = dport
     cfgp = tmp_path / "xpool.toml"
-    cfgp.write_text(_toml(dport, sport, models_toml, atn, ffn, atn_extra))
+    cfgp.write_text(_toml(dport, sport, models_toml, atn, ffn, atn_extra, serving_extra))
     env = dict(os.environ, XPOOL_CONFIG=str(cfgp), PYTHONPATH=str(ROOT), XPOOL_MAX_ROWS="128", XPOOL_MAX_BATCH="4",
                XPOOL_MAX_SEQ_LEN="128", **(extra_env or {}))
     xp = [sys.executable, "-m", "crosspool_b200.cli.main"]
@@ -682,3 +684,31 @@ def test_the_benchmark_tool_brings_up_a_cpu_deployment_runs_a_case_and_its_resul
     suite.run_suite([suite.CASES["smoke"]], {"tiny-qwen3": "unused"}, run, runner=lambda c, t, seed: doc)
     made = R.make_reports(run)
     assert (made[0] / "report.md").read_text().startswith("# smoke") and (made[0] / "throughput.svg").exists()
+
+
+def test_attention_tensor_parallel_pair_serves_through_the_daemon_on_the_cpu_data_plane(tmp_path):
+    """One Instance whose attention runs tensor-parallel over two attention agents (half of the heads each, output
+    projections all-reduced, requests replicated from the first rank, which alone talks to the FFN tier and owns the
+    HTTP endpoint); FFN tensor-parallel over two FFN agents. Answers equal the undivided model's."""
+    import zlib
+
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.models.reference import ReferenceModel
+    from crosspool_b200.models.weights import random_attention_weights, random_ffn_weights
+
+    rendezvous = _free_port_run(2, set())
+    models = '[[models]]\nid = "tiny-qwen3"\natn_tp_size = 2\nffn_tp_size = 2\n'
+
+    def check(url, plan):
+        assert sorted((r["model_id"], r["rank"]) for r in plan["instance_ranks"]) == [("tiny-qwen3", 0), ("tiny-qwen3", 1)]
+        cfg, seed = mc.preset("tiny-qwen3"), zlib.crc32(b"tiny-qwen3") % 1000
+        whole = ReferenceModel(cfg, random_attention_weights(cfg, seed, dtype=torch.float32), random_ffn_weights(cfg, seed, dtype=torch.float32))
+        for prompt in (list(range(3, 20)), [9, 8, 7, 6, 5]):
+            out = httpx.post(url + "/generate", json={"input_ids": prompt, "max_new_tokens": 5}, timeout=120)
+            assert out.status_code == 200, out.text
+            assert out.json()["output_ids"] == whole.generate(torch.tensor(prompt), 5)[0]
+        base = int(url.rsplit(":", 1)[1])
+        with pytest.raises(httpx.HTTPError):                 # the second rank has no endpoint of its own
+            httpx.get(f"http://127.0.0.1:{base + 1}/health", timeout=2)
+
+    _run(tmp_path, models, check, atn=(0, 1), ffn=(2, 3), serving_extra=f"tp_rendezvous_base_port = {rendezvous}")
