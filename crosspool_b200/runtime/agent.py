@@ -183,6 +183,9 @@ class Agent:
                 self._sleep(poll_seconds)
         finally:
             self._stop.set()
+            hb = getattr(self, "_hb", None)
+            if hb is not None:
+                hb.join(2.0)       # no thread of this process is inside a request while the interpreter shuts down
         if self.failed:
             # cleanup of a failed generation cannot be confirmed: keep the resources, exit non-zero
             self.retained = True

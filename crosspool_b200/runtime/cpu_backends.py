@@ -361,7 +361,10 @@ class CpuDeployment:
     """The stepped-deployment protocol of ``runtime/serving.py::EngineLoop`` over CPU engines."""
 
     def __init__(self, engines: dict[str, CpuOracleEngine]):
+        import types
+
         self.engines = engines
+        self.instances = [types.SimpleNamespace(model_id=m, engine=e) for m, e in engines.items()]   # what this device hosts
 
     def add_request(self, model_id: str, prompt: list[int], max_new_tokens: int, arrival: float | None = None, **sampling):
         return self.engines[model_id].add_request(prompt, max_new_tokens, arrival, **sampling)
@@ -440,7 +443,13 @@ class CpuAtnBackend:
             geo = KvPartitionGeometry.of(kv, floor_bundles=1)
             bb = geo.bundle_bytes
             geo.describe(self._ecs_channel, idx, self.device, rank)
-            rec = R.CapacityReconciler(kv, self._ecs_channel, idx, floor_bundles=geo.floor_bundles)
+            if self.cfg.model(model_id).atn_tp_size > 1:
+                # the ranks of a TP group change capacity in the same engine step: they agree every poll over their gloo
+                # group, which exists from warm_and_serve on (before the first step)
+                rec = R.TpAgreedReconciler(kv, self._ecs_channel, idx, floor_bundles=geo.floor_bundles,
+                                           agree=lambda v: R.gloo_agreement(None)(v))
+            else:
+                rec = R.CapacityReconciler(kv, self._ecs_channel, idx, floor_bundles=geo.floor_bundles)
             eng.attach_kv(kv, rec, ttft_slo_s=self.cfg.slo_for(model_id).ttft_ms / 1e3)
             self.reconcilers.append(rec)
             mapped += bb
@@ -450,8 +459,6 @@ class CpuAtnBackend:
         torch.set_num_threads(1)
         handles = {}
         for model_id, rank in self.instances:
-            if self.cfg.model(model_id).atn_tp_size != 1 and self.cfg.atn_elastic_kv:
-                raise NotImplementedError("the CPU attention backend does not combine attention tensor parallelism with elastic KV")
             self.places[(model_id, rank)] = placement_for(self.cfg, plan, model_id, rank, self.capacity_rows)
             handles[f"atn:{model_id}:{rank}"] = b"cpu".hex()       # the attention side owns no arena on the CPU
         if self.external:
@@ -527,11 +534,14 @@ class CpuAtnBackend:
             os.environ.setdefault("GLOO_SOCKET_IFNAME", "lo")
             dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{self.cfg.serving_tp_rendezvous_base_port + first}",
                                     rank=tpr, world_size=tps)
-            self.loop = TpEngineLoop(CpuDeployment(self.engines), None, leader)
+            replicated = {m.id for m in self.cfg.models if m.atn_tp_size > 1}
+            self.loop = TpEngineLoop(CpuDeployment(self.engines), None, leader, replicated=replicated)
+            serves_http = leader or any(m not in replicated for m in self.engines)   # a follower answers for its other Instances
         else:
             self.loop = EngineLoop(CpuDeployment(self.engines))
+            serves_http = True
         self.loop.start()
-        if self._listen is not None and leader:
+        if self._listen is not None and serves_http:
             import uvicorn
 
             toks = load_tokenizers({m: place.checkpoint for (m, _), place in self.places.items()})

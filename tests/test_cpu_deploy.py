@@ -712,3 +712,60 @@ def test_attention_tensor_parallel_pair_serves_through_the_daemon_on_the_cpu_dat
             httpx.get(f"http://127.0.0.1:{base + 1}/health", timeout=2)
 
     _run(tmp_path, models, check, atn=(0, 1), ffn=(2, 3), serving_extra=f"tp_rendezvous_base_port = {rendezvous}")
+
+
+def test_tensor_parallel_ranks_agree_on_elastic_kv_growth_funded_by_their_neighbours(tmp_path):
+    """A tensor-parallel Instance (one rank per attention device) next to a data-parallel co-tenant on each device, with
+    elastic KV and four bundles per device. Long requests make both TP ranks publish demand; the daemon shrinks the idle
+    co-tenant on each device and orders both ranks to grow; the ranks change capacity in the same engine step (they
+    agree every poll over their gloo group), and the answers are the undivided model's."""
+    import concurrent.futures as cf
+    import zlib
+
+    from crosspool_b200.models import config as mc
+    from crosspool_b200.models.reference import ReferenceModel
+    from crosspool_b200.models.weights import random_attention_weights, random_ffn_weights
+
+    rendezvous = _free_port_run(2, set())
+    models = ('[[models]]\nid = "tiny-qwen3"\natn_tp_size = 2\nffn_tp_size = 2\n'
+              '[[models]]\nid = "tiny-qwen3-moe"\natn_dp_size = 2\nffn_tp_size = 2\n')
+    bundle = 4 * (16 << 10)
+
+    def check(url, base, procs):
+        view = {}
+        for _ in range(150):
+            view = httpx.get(base + "/ecs/state", timeout=2).json()
+            if view["frozen"] and all(p["mapped_bytes"] == p["target_bytes"] == 2 * bundle for p in view["partitions"]):
+                break
+            time.sleep(0.1)
+        assert view["frozen"] and len(view["partitions"]) == 4, view
+        cfg, seed = mc.preset("tiny-qwen3"), zlib.crc32(b"tiny-qwen3") % 1000
+        whole = ReferenceModel(cfg, random_attention_weights(cfg, seed, dtype=torch.float32), random_ffn_weights(cfg, seed, dtype=torch.float32))
+        prompts = [[(5 * i + j) % 4000 + 1 for j in range(100)] for i in range(3)]      # 7 pages each: 21 pages > the 16 mapped
+        with cf.ThreadPoolExecutor(3) as pool:
+            outs = list(pool.map(lambda p: httpx.post(url + "/generate", json={"model": "tiny-qwen3", "input_ids": p, "max_new_tokens": 5},
+                                                      timeout=240).json(), prompts))
+        for p, o in zip(prompts, outs):
+            assert o["output_ids"] == whole.generate(torch.tensor(p), 5)[0]
+        # the co-tenant's second data-parallel rank lives on the TP follower's device and answers there
+        inst = httpx.get(base + "/instances", timeout=2).json()
+        mcfg, mseed = mc.preset("tiny-qwen3-moe"), zlib.crc32(b"tiny-qwen3-moe") % 1000
+        moe = ReferenceModel(mcfg, random_attention_weights(mcfg, mseed, dtype=torch.float32), random_ffn_weights(mcfg, mseed, dtype=torch.float32))
+        for r in (0, 1):
+            o = httpx.post(f"http://{inst[f'tiny-qwen3-moe:{r}']['listener']}/generate",
+                           json={"model": "tiny-qwen3-moe", "input_ids": [3, 1, 4, 1, 5], "max_new_tokens": 4}, timeout=120).json()
+            assert o["output_ids"] == moe.generate(torch.tensor([3, 1, 4, 1, 5]), 4)[0]
+        assert inst["tiny-qwen3-moe:0"]["listener"] != inst["tiny-qwen3-moe:1"]["listener"]
+        view = httpx.get(base + "/ecs/state", timeout=2).json()
+        kinds = [(e["kind"], e["partition"]) for e in view["events"]]
+        for r in (0, 1):
+            assert ("shrink", f"tiny-qwen3-moe:{r}") in kinds and ("grow", f"tiny-qwen3:{r}") in kinds
+        by = {p["key"]: p for p in view["partitions"]}
+        assert by["tiny-qwen3:0"]["target_bytes"] == by["tiny-qwen3:1"]["target_bytes"] == 3 * bundle
+        assert by["tiny-qwen3:0"]["mapped_bytes"] == by["tiny-qwen3:1"]["mapped_bytes"] == 3 * bundle      # grown together
+        assert httpx.post(base + "/fabric/quiesce", json={"reason": "test"}, timeout=5).status_code == 200
+        for p in procs[1:]:
+            assert p.wait(90) == 0
+
+    _run(tmp_path, models, check, atn=(0, 1), ffn=(2, 3), retire=False, atn_extra="elastic_kv = true\ndevice_memory_utilization = 1.0",
+         serving_extra=f"tp_rendezvous_base_port = {rendezvous}", extra_env={"XPOOL_CPU_KV_BYTES": str(4 * bundle)})
