@@ -87,6 +87,77 @@ def test_followers_see_the_leaders_requests_in_order_and_stop_with_it():
     assert res[0][3] is None and res[1][3] is None
 
 
+class PerModelDeployment(FakeDeployment):
+    """Tokens grouped by the model of each sequence, as a deployment with several Instances reports them."""
+
+    def add_request(self, model, prompt, max_new_tokens, **kw):
+        s = super().add_request(model, prompt, max_new_tokens, **kw)
+        s.model = model
+        return s
+
+    def step(self):
+        pairs = super().step().tokens["m"]
+        out = {}
+        for s, t in pairs:
+            out.setdefault(s.model, []).append((s, t))
+        return types.SimpleNamespace(tokens=out)
+
+
+def _drain(p):
+    toks = []
+    while True:
+        item = p.out.get(timeout=10)
+        if isinstance(item, Exception):
+            return item
+        toks.append(item[0])
+        if item[1]:
+            return toks
+
+
+def _mixed_rank(rank, port, q):
+    import torch.distributed as dist
+
+    from crosspool_b200.runtime.tp_replication import TpEngineLoop
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=2)
+    dep = PerModelDeployment()
+    loop = TpEngineLoop(dep, None, leader=rank == 0, idle_sleep=0.001, replicated={"m"})
+    loop.start()
+    time.sleep(0.05)
+    if rank == 0:
+        out = (_drain(loop.submit("m", [1, 2, 3], 3)), _drain(loop.submit("own0", [4], 2)))
+        time.sleep(0.5)          # the follower's own request is served while the leader idles
+        loop.stop()
+    else:
+        mine = _drain(loop.submit("own1", [7, 7], 4))
+        refused = _drain(loop.submit("m", [5], 1))
+        out = (mine, type(refused).__name__)
+        loop._thread.join(20)
+    q.put((rank, out, [e for e in dep.log if e[0] == "add"], loop.error))
+    dist.destroy_process_group()
+
+
+def test_a_rank_admits_requests_for_its_unreplicated_instances_itself_and_followers_refuse_replicated_ones():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29850 + os.getpid() % 100
+    ps = [ctx.Process(target=_mixed_rank, args=(r, port, q)) for r in (0, 1)]
+    for p in ps:
+        p.start()
+    res = {}
+    for _ in ps:
+        r = q.get(timeout=60)
+        res[r[0]] = r
+    for p in ps:
+        p.join(30)
+    assert res[0][3] is None and res[1][3] is None
+    assert [len(t) for t in res[0][1]] == [3, 2]
+    assert len(res[1][1][0]) == 4 and res[1][1][1] == "RuntimeError"
+    # the replicated request reached both ranks; each rank's own request reached only that rank
+    assert [e[1] for e in res[0][2]] == ["m", "own0"] and sorted(e[1] for e in res[1][2]) == ["m", "own1"]
+
+
 def test_deployed_placement_names_the_tp_group_from_its_first_rank():
     """Every rank of an attention TP group resolves the same placement: the group's first rank talks to the FFN
     tier, the others follow it (reference: atn_tp_size in src/xpool/config.py)."""
